@@ -1,0 +1,145 @@
+/*
+ * kan_b200.h -- C ABI of the B200 (sm_100a) KANLinear hot path.
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes and a CUDA stream
+ * (passed as void*, 0 = default stream), launches on that stream without
+ * synchronising, and returns 0 on success or a negative KANB200_E* code.
+ * kanb200_last_error() returns the message of the calling thread's last
+ * failure.  Nothing here allocates device memory: scratch space is provided
+ * by the caller (size from kanb200_workspace_bytes).  There is no CPU path.
+ *
+ * Shapes (row-major, contiguous):  x [N,I], grid [I,T] with T = G+2k+1,
+ * base_weight [O,I], spline_weight [O,I,R] with R = G+k, spline_scaler [O,I],
+ * y / grad_out [N,O], basis H [N,I,R].  dtype: KANB200_F32 or KANB200_F64.
+ * A NULL base_weight / spline_scaler pointer means "absent" (the reference
+ * passes an empty tensor: csrc/kan_ops.h:22-24).
+ *
+ * Each declaration cites the function of the reference project
+ * (yefanliuming/TORCHSPLINEKAN) that it replaces.
+ */
+#ifndef KAN_B200_H
+#define KAN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define KANB200_API __attribute__((visibility("default")))
+#else
+#define KANB200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KANB200_F32 0
+#define KANB200_F64 1
+
+/* Arithmetic used for the contraction (fp32 inputs only; fp64 always SIMT). */
+#define KANB200_MODE_AUTO     0  /* tensor cores when the shape allows, else SIMT   */
+#define KANB200_MODE_SIMT     1  /* fp32/fp64 FMA pipes, gathers the k+1 non-zeros   */
+#define KANB200_MODE_TC_BF16X3 2 /* tcgen05, operands split hi+lo bf16, 3 MMAs/step  */
+#define KANB200_MODE_TC_BF16X1 3 /* tcgen05, single bf16 MMA (fast, ~3e-3 relative)  */
+
+#define KANB200_OK            0
+#define KANB200_EINVAL       -1  /* bad argument (shape, limit, NULL, dtype)         */
+#define KANB200_EUNSUPPORTED -2  /* valid request the chosen mode cannot run         */
+#define KANB200_EWORKSPACE   -3  /* workspace missing or too small                   */
+#define KANB200_ECUDA        -4  /* CUDA runtime error at launch                     */
+#define KANB200_EDEVICE      -5  /* a kernel reported a timed-out wait (status word) */
+
+/* Limits shared with the reference (csrc/kan_ops.h:15-17). */
+#define KANB200_MAX_DEG0_BASIS  71     /* G + 2k                          */
+#define KANB200_MAX_IN_FEATURES 65535
+
+#define KANB200_OP_FORWARD  0
+#define KANB200_OP_BACKWARD 1
+#define KANB200_OP_EDGE_FWD 2
+#define KANB200_OP_EDGE_BWD 3
+
+KANB200_API const char* kanb200_last_error(void);
+KANB200_API int kanb200_version(void);
+
+/* Process-global basis-kernel selector kept for API compatibility
+ * (kan_set_basis_impl / kan_get_basis_impl, csrc/kan_cuda.cu:274-279):
+ * 0 and 1 are accepted (both run the local k+1 evaluation here), anything
+ * else is KANB200_EINVAL. */
+KANB200_API int kanb200_set_basis_impl(int impl);
+KANB200_API int kanb200_get_basis_impl(void);
+
+/* Shape / limit validation run by every entry point before any launch
+ * (kan_check_inputs, csrc/kan_ops.h:27-78). */
+KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int k, int dtype);
+
+/* The mode KANB200_MODE_AUTO resolves to for this problem. */
+KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k);
+
+/* Bytes of caller-provided scratch the given op needs (0 = none). */
+KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype,
+                               int64_t N, int64_t I, int64_t O, int G, int k,
+                               int need_x, int need_param);
+
+/* H[n,i,r] = B_{r,k}(x[n,i]) on knots grid[i,:]
+ * (kan_basis_cuda, csrc/kan_cuda.cu:666-680). */
+KANB200_API int kanb200_basis(int dtype, const void* x, const void* grid, void* H,
+                  int64_t N, int64_t I, int G, int k, void* stream);
+
+/* gx[n,i] = sum_r gH[n,i,r] dB_r/dx
+ * (kan_basis_grad_cuda, csrc/kan_cuda.cu:682-699). */
+KANB200_API int kanb200_basis_grad(int dtype, const void* x, const void* grid, const void* gH, void* gx,
+                       int64_t N, int64_t I, int G, int k, void* stream);
+
+/* y = silu(x) bw^T + H(x) (spline_weight * spline_scaler)^T, basis never
+ * materialised (kan_forward_cuda, csrc/kan_cuda.cu:469-532; the dense basis
+ * output of that function is produced separately by kanb200_basis). */
+KANB200_API int kanb200_forward(int dtype, int mode,
+                    const void* x, const void* grid, const void* base_weight,
+                    const void* spline_weight, const void* spline_scaler,
+                    void* y, int64_t N, int64_t I, int64_t O, int G, int k,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* First-order backward; any of the four outputs may be NULL = not needed
+ * (kan_backward_cuda_ex, csrc/kan_cuda.cu:537-630).  The basis is recomputed
+ * from x, nothing saved by the forward is required. */
+KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out,
+                     const void* x, const void* grid, const void* base_weight,
+                     const void* spline_weight, const void* spline_scaler,
+                     void* grad_x, void* grad_base_weight,
+                     void* grad_spline_weight, void* grad_spline_scaler,
+                     int64_t N, int64_t I, int64_t O, int G, int k,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* a[o,i] = mean_n | s[n,i] bw[o,i] + sum_r H[n,i,r] W[o,i,r] |; s and bw may
+ * both be NULL (edge_abs_mean_cuda, csrc/kan_reg_cuda.cu:263-280).  No atomics:
+ * per-split partial sums go to the workspace and are reduced in a fixed order. */
+KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, const void* bw, const void* W,
+                          void* a, int64_t N, int64_t I, int64_t O, int R,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Gradients of kanb200_edge_abs_mean; NULL output = not needed
+ * (edge_abs_mean_backward_cuda, csrc/kan_reg_cuda.cu:284-312). */
+KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a,
+                                   const void* s, const void* H, const void* bw, const void* W,
+                                   void* ds, void* dH, void* dbw, void* dW,
+                                   int64_t N, int64_t I, int64_t O, int R,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* Reads (and clears) the status word the tensor-core kernels keep at the start
+ * of a workspace; synchronises the stream.  0 = every wait completed. */
+KANB200_API int kanb200_check_status(void* workspace, void* stream);
+
+/* Layout self-test for the tensor-core operand formats: copies two byte images
+ * into shared memory, issues `ksteps` tcgen05 MMAs (M = 128, N = ncols, K = 16
+ * each, start addresses advanced by a_step / b_step bytes per step) with the
+ * given matrix / instruction descriptors and writes the fp32 accumulator
+ * D[128, ncols].  Has no counterpart in the reference; used by the tests to pin
+ * the K-major and MN-major 128-byte-swizzle layouts the kernels rely on. */
+KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
+                       uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps,
+                       uint32_t a_step, uint32_t b_step, int ncols, float* D, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KAN_B200_H */

@@ -1,0 +1,288 @@
+"""GPU parity tests: every call goes through the C ABI (ctypes) of libkan_b200.so
+and is compared with the numpy oracle / the golden vectors of the reference."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden, rel_err
+from gpu_util import dev, make_layer_case, oracle_step
+from oracle import kan_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+nat = pytest.importorskip("torchsplinekan_b200._native")
+
+# fp32 tolerance of the north-star (relative to max|ref| per tensor); fp64: 1e-12
+TOL32 = 1e-5
+TOL64 = 1e-12
+
+
+# ---------------------------------------------------------------------------
+# tensor-core operand layouts (self-test kernel)
+# ---------------------------------------------------------------------------
+def _bf16_bits(a):
+    """float32 array with bf16-representable values -> uint16 bit patterns."""
+    return (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def _sdesc(lbo, sbo):
+    return ((lbo >> 4) & 0x3FFF) << 16 | ((sbo >> 4) & 0x3FFF) << 32 | 1 << 46 | 2 << 61
+
+
+def _idesc(n, a_mn, b_mn):
+    return (1 << 4) | (1 << 7) | (1 << 10) | (int(a_mn) << 15) | (int(b_mn) << 16) | ((n >> 3) << 17) | ((128 >> 4) << 24)
+
+
+def _img_kmajor(M):
+    """[rows, 64] matrix -> K-major 128B-swizzled byte image (rows x 128 B)."""
+    rows = M.shape[0]
+    img = np.zeros(rows * 64, dtype=np.uint16)
+    bits = _bf16_bits(M)
+    for r in range(rows):
+        for c in range(8):
+            off = (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)
+            img[off // 2: off // 2 + 8] = bits[r, c * 8: c * 8 + 8]
+    return img
+
+
+def _img_mnmajor(M):
+    """[mn, 64(k)] matrix -> MN-major image [mn group of 64][k group of 8][8 k rows][128 B]."""
+    mn = M.shape[0]
+    img = np.zeros(mn * 64, dtype=np.uint16)
+    bits = _bf16_bits(M)
+    for g in range(mn // 64):
+        for kk in range(64):
+            for ch in range(8):
+                off = (g * 8 + (kk >> 3)) * 1024 + (kk & 7) * 128 + ((ch ^ (kk & 7)) << 4)
+                img[off // 2: off // 2 + 8] = bits[g * 64 + ch * 8: g * 64 + ch * 8 + 8, kk]
+    return img
+
+
+def _run_probe(a_img, b_img, a_desc, b_desc, idesc, ksteps, a_step, b_step, ncols):
+    import ctypes
+    a = torch.from_numpy(a_img.view(np.int16)).cuda()
+    b = torch.from_numpy(b_img.view(np.int16)).cuda()
+    D = torch.zeros(128, ncols, dtype=torch.float32, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = nat.lib().kanb200_umma_probe(ctypes.c_void_p(a.data_ptr()), a.numel() * 2, ctypes.c_void_p(b.data_ptr()),
+                                      b.numel() * 2, a_desc, b_desc, idesc, ksteps, a_step, b_step, ncols,
+                                      ctypes.c_void_p(D.data_ptr()), ctypes.c_void_p(st.data_ptr()), None)
+    assert rc == 0, nat.last_error()
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0, "probe kernel reported a timed-out wait"
+    return D.cpu().numpy()
+
+
+def _small_int_matrix(rng, rows):
+    return rng.integers(-4, 5, size=(rows, 64)).astype(np.float32)
+
+
+def test_umma_layout_k_major():
+    rng = np.random.default_rng(0)
+    A, B = _small_int_matrix(rng, 128), _small_int_matrix(rng, 256)
+    D = _run_probe(_img_kmajor(A), _img_kmajor(B), _sdesc(16, 1024), _sdesc(16, 1024), _idesc(256, False, False),
+                   4, 32, 32, 256)
+    assert np.array_equal(D, A @ B.T)
+
+
+def test_umma_layout_mn_major():
+    rng = np.random.default_rng(1)
+    A, B = _small_int_matrix(rng, 128), _small_int_matrix(rng, 256)
+    D = _run_probe(_img_mnmajor(A), _img_mnmajor(B), _sdesc(8192, 1024), _sdesc(8192, 1024),
+                   _idesc(256, True, True), 4, 2048, 2048, 256)
+    assert np.array_equal(D, A @ B.T)
+
+
+# ---------------------------------------------------------------------------
+# basis / basis gradient
+# ---------------------------------------------------------------------------
+def test_basis_matches_golden_fp64():
+    z = load_golden("basis.npz")
+    for name in [str(n) for n in z["names"]]:
+        k = int(name[1])
+        x, grid = dev(z[name + "/x"]), dev(z[name + "/grid"])
+        H = nat.basis(x, grid, k).cpu().numpy()
+        assert np.abs(H - z[name + "/H"]).max() <= 1e-13, name
+        gH = np.random.default_rng(3).standard_normal(H.shape)
+        gx = nat.basis_grad(x, grid, k, dev(gH)).cpu().numpy()
+        ref = (gH * z[name + "/dH"]).sum(-1)
+        assert np.abs(gx - ref).max() <= 1e-10 * max(1.0, np.abs(ref).max()), name
+
+
+@pytest.mark.parametrize("G,k", [(5, 3), (64, 3), (17, 2), (1, 1)])
+def test_basis_fp32_random(G, k):
+    c = make_layer_case(777, 5, 3, G, k, np.float32, seed=G + k, nonuniform=True, xscale=1.4)
+    H = nat.basis(dev(c["x"]), dev(c["grid"]), k).cpu().numpy()
+    ref = ko.compute_basis(c["x"].astype(np.float64), c["grid"].astype(np.float64), k)
+    assert np.abs(H - ref).max() < 5e-6
+    # out-of-range inputs give exactly zero rows
+    out = (c["x"] < c["grid"][:, 0]) | (c["x"] > c["grid"][:, -1])
+    assert (H[out] == 0).all()
+
+
+def test_basis_empty_batch():
+    c = make_layer_case(4, 3, 2, 5, 3, np.float32, seed=0)
+    H = nat.basis(torch.empty(0, 3, device="cuda"), dev(c["grid"]), 3)
+    assert H.shape == (0, 3, 8)
+
+
+# ---------------------------------------------------------------------------
+# layer forward / backward
+# ---------------------------------------------------------------------------
+def _run_layer(case, mode, need_x=True):
+    t = {n: dev(v) for n, v in case.items() if n != "k"}
+    k = case["k"]
+    y = nat.forward(t["x"], t["grid"], t["bw"], t["sw"], t["sc"], k, mode)
+    D = 2.0 * y
+    gx, gb, gs, gc = nat.backward(D, t["x"], t["grid"], t["bw"], t["sw"], t["sc"], k,
+                                  need_x, True, True, True, mode)
+    torch.cuda.synchronize()
+    for tag in ("fwd", "bwd"):
+        for key, buf in list(nat._ws_cache.items()):
+            if key[2] == tag and mode in (nat.MODE_TC_BF16X3, nat.MODE_TC_BF16X1):
+                nat.check_status(buf)
+    f = lambda a: None if a is None else a.cpu().numpy()
+    return f(y), f(D), f(gx), f(gb), f(gs), f(gc)
+
+
+def _compare_layer(case, mode, tol, need_x=True):
+    y, D, gx, gb, gs, gc = _run_layer(case, mode, need_x)
+    c64 = {n: (None if v is None or isinstance(v, int) else v.astype(np.float64)) for n, v in case.items()}
+    ry, _ = ko.kan_forward(c64["x"], c64["grid"], c64["bw"], c64["sw"], c64["sc"], case["k"])
+    # backward is checked for the kernel's own dY so forward error does not leak in
+    rgx, rgb, rgs, rgc = ko.kan_backward(D.astype(np.float64), c64["x"], c64["grid"], c64["bw"], c64["sw"],
+                                         c64["sc"], case["k"])
+    errs = {"y": rel_err(y, ry), "g_spline": rel_err(gs, rgs)}
+    if need_x:
+        errs["gx"] = rel_err(gx, rgx)
+    if case["bw"] is not None:
+        errs["g_base"] = rel_err(gb, rgb)
+    if case["sc"] is not None:
+        errs["g_scaler"] = rel_err(gc, rgc)
+    bad = {n: e for n, e in errs.items() if not e < tol}
+    assert not bad, f"errors above {tol}: {bad} (all: {errs})"
+    return errs
+
+
+def test_layer_golden_simt():
+    z = load_golden("layer.npz")
+    for name in [str(n) for n in z["names"]]:
+        f64 = z[name + "/x"].dtype == np.float64
+        t = {n: dev(z[name + "/" + n]) for n in ("x", "grid", "base_weight", "spline_weight")}
+        sc = dev(z[name + "/spline_scaler"]) if name + "/spline_scaler" in z.files else None
+        k = int(z[name + "/k"])
+        y = nat.forward(t["x"], t["grid"], t["base_weight"], t["spline_weight"], sc, k, nat.MODE_SIMT)
+        gx, gb, gs, gc = nat.backward(2.0 * y, t["x"], t["grid"], t["base_weight"], t["spline_weight"], sc, k,
+                                      True, True, True, sc is not None, nat.MODE_SIMT)
+        tol = TOL64 if f64 else TOL32
+        assert rel_err(y.cpu().numpy(), z[name + "/y"]) < tol, name
+        assert rel_err(gx.cpu().numpy(), z[name + "/gx"]) < tol, name
+        assert rel_err(gb.cpu().numpy(), z[name + "/g_base_weight"]) < tol, name
+        assert rel_err(gs.cpu().numpy(), z[name + "/g_spline_weight"]) < tol, name
+        if sc is not None:
+            assert rel_err(gc.cpu().numpy(), z[name + "/g_spline_scaler"]) < tol, name
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float64, TOL64), (np.float32, TOL32)])
+@pytest.mark.parametrize("shape", [
+    dict(N=1, I=1, O=1, G=1, k=1),
+    dict(N=257, I=19, O=70, G=5, k=3),
+    dict(N=300, I=7, O=5, G=64, k=3, nonuniform=True),
+    dict(N=130, I=33, O=3, G=12, k=2, scaler=False),
+    dict(N=64, I=9, O=40, G=20, k=3, base=False, nonuniform=True),
+    dict(N=515, I=2, O=64, G=8, k=3),
+    dict(N=515, I=64, O=1, G=8, k=3),
+])
+def test_layer_simt_vs_oracle(shape, dtype, tol):
+    case = make_layer_case(dtype=dtype, seed=11, **shape)
+    _compare_layer(case, nat.MODE_SIMT, tol)
+
+
+@pytest.mark.parametrize("shape", [
+    dict(N=128, I=8, O=256, G=5, k=3),
+    dict(N=300, I=40, O=70, G=5, k=3, nonuniform=True),
+    dict(N=1024, I=64, O=256, G=5, k=3),
+    dict(N=777, I=100, O=300, G=5, k=3, scaler=False),
+    dict(N=640, I=72, O=128, G=4, k=2, nonuniform=True),
+    dict(N=513, I=33, O=65, G=3, k=1, base=False),
+    dict(N=2048, I=256, O=512, G=5, k=3, nonuniform=True),
+])
+def test_layer_tensor_core_bf16x3_vs_oracle(shape):
+    case = make_layer_case(dtype=np.float32, seed=5, **shape)
+    errs = _compare_layer(case, nat.MODE_TC_BF16X3, TOL32)
+    print("bf16x3", shape, errs)
+
+
+def test_layer_tensor_core_bf16x1_stated_tolerance():
+    """Single-MMA bf16 mode: operands rounded to 8 significand bits; stated tolerance 1e-2."""
+    case = make_layer_case(dtype=np.float32, seed=6, N=1024, I=64, O=256, G=5, k=3)
+    errs = _compare_layer(case, nat.MODE_TC_BF16X1, 1e-2)
+    print("bf16x1", errs)
+    assert errs["y"] > 1e-6          # it really is the reduced-precision path
+
+
+def test_auto_mode_resolution():
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 65536, 1024, 1024, 5, 3) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float64, 65536, 1024, 1024, 5, 3) == nat.MODE_SIMT
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 16384, 512, 512, 64, 3) == nat.MODE_SIMT
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 16, 32, 5, 3) == nat.MODE_SIMT
+
+
+def test_backward_skips_unrequested_outputs():
+    case = make_layer_case(200, 12, 9, 5, 3, np.float32, seed=2)
+    t = {n: dev(v) for n, v in case.items() if n != "k"}
+    D = torch.randn(200, 9, device="cuda")
+    gx, gb, gs, gc = nat.backward(D, t["x"], t["grid"], t["bw"], t["sw"], t["sc"], 3, True, False, False, False)
+    assert gx is not None and gb is None and gs is None and gc is None
+    gx, gb, gs, gc = nat.backward(D, t["x"], t["grid"], t["bw"], t["sw"], t["sc"], 3, False, True, True, True)
+    assert gx is None and gb is not None and gs is not None and gc is not None
+
+
+# ---------------------------------------------------------------------------
+# regulariser statistic
+# ---------------------------------------------------------------------------
+def test_edge_abs_mean_matches_golden():
+    z = load_golden("reg.npz")
+    for name in [str(n) for n in z["names"]]:
+        s, H, bw, W, ga = (dev(z[name + "/" + n]) for n in ("s", "H", "bw", "W", "ga"))
+        tol = TOL64 if z[name + "/H"].dtype == np.float64 else TOL32
+        a = nat.edge_abs_mean(s, H, bw, W)
+        assert rel_err(a.cpu().numpy(), z[name + "/a"]) < tol, name
+        a0 = nat.edge_abs_mean(None, H, None, W)
+        assert rel_err(a0.cpu().numpy(), z[name + "/a_nobase"]) < tol, name
+        ds, dH, dbw, dW = nat.edge_abs_mean_backward(ga, s, H, bw, W, True, True, True, True)
+        for got, key in ((ds, "ds"), (dH, "dH"), (dbw, "dbw"), (dW, "dW")):
+            assert rel_err(got.cpu().numpy(), z[name + "/" + key]) < tol, (name, key)
+
+
+@pytest.mark.parametrize("dtype,tol", [(np.float64, 1e-11), (np.float32, 5e-5)])
+@pytest.mark.parametrize("N,I,O,R", [(1000, 37, 70, 8), (333, 5, 200, 11), (129, 9, 6, 23), (64, 3, 4, 67)])
+def test_edge_abs_mean_vs_oracle(N, I, O, R, dtype, tol):
+    rng = np.random.default_rng(N)
+    H = rng.uniform(0, 1, size=(N, I, R)).astype(dtype)
+    s = rng.standard_normal((N, I)).astype(dtype)
+    bw = rng.standard_normal((O, I)).astype(dtype)
+    W = rng.standard_normal((O, I, R)).astype(dtype)
+    ga = rng.uniform(0.5, 1.5, size=(O, I)).astype(dtype)
+    a = nat.edge_abs_mean(dev(s), dev(H), dev(bw), dev(W)).cpu().numpy()
+    ra = ko.edge_abs_mean(s.astype(np.float64), H.astype(np.float64), bw.astype(np.float64), W.astype(np.float64))
+    assert rel_err(a, ra) < tol
+    ds, dH, dbw, dW = nat.edge_abs_mean_backward(dev(ga), dev(s), dev(H), dev(bw), dev(W), True, True, True, True)
+    rds, rdH, rdbw, rdW = ko.edge_abs_mean_backward(ga.astype(np.float64), s.astype(np.float64),
+                                                    H.astype(np.float64), bw.astype(np.float64),
+                                                    W.astype(np.float64))
+    # sign(phi) may flip for |phi| at rounding level in fp32; compare in the max norm
+    for got, ref in ((ds, rds), (dH, rdH), (dbw, rdbw), (dW, rdW)):
+        assert rel_err(got.cpu().numpy(), ref) < max(tol, 2e-3 if dtype == np.float32 else tol)
+
+
+# ---------------------------------------------------------------------------
+# validation happens before any launch
+# ---------------------------------------------------------------------------
+def test_limits_rejected_before_launch():
+    x = torch.zeros(4, 2, device="cuda")
+    grid = torch.zeros(2, 73, device="cuda")       # G + 2k = 72 > 71
+    with pytest.raises(RuntimeError, match=r"G \+ 2k"):
+        nat.basis(x, grid, 3)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        nat.basis(torch.zeros(4, 2), torch.zeros(2, 12), 3)

@@ -1,0 +1,255 @@
+"""ctypes binding of ``lib/libkan_b200.so`` (the C ABI in ``include/kan_b200.h``).
+
+PyTorch is used here only for device memory, streams and dtype bookkeeping:
+every function takes CUDA tensors, passes their raw pointers and the current
+stream to the library and returns freshly allocated outputs.  There is no CPU
+implementation behind these calls -- a missing library or a CPU tensor raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+from .build import LIB_PATH
+
+F32, F64 = 0, 1
+MODE_AUTO, MODE_SIMT, MODE_TC_BF16X3, MODE_TC_BF16X1 = 0, 1, 2, 3
+MODES = {"auto": MODE_AUTO, "simt": MODE_SIMT, "bf16x3": MODE_TC_BF16X3, "bf16x1": MODE_TC_BF16X1}
+OP_FORWARD, OP_BACKWARD, OP_EDGE_FWD, OP_EDGE_BWD = 0, 1, 2, 3
+EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = -1, -2, -3, -4, -5
+MAX_DEG0_BASIS = 71
+MAX_IN_FEATURES = 65535
+
+_c_void_p, _c_int, _c_i64, _c_size = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+
+# name -> (restype, argtypes); must list every symbol of include/kan_b200.h
+SIGNATURES = {
+    "kanb200_last_error": (ctypes.c_char_p, []),
+    "kanb200_version": (_c_int, []),
+    "kanb200_set_basis_impl": (_c_int, [_c_int]),
+    "kanb200_get_basis_impl": (_c_int, []),
+    "kanb200_check_shapes": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int]),
+    "kanb200_resolve_mode": (_c_int, [_c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
+    "kanb200_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int,
+                                          _c_int, _c_int]),
+    "kanb200_basis": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int, _c_int, _c_void_p]),
+    "kanb200_basis_grad": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int,
+                                    _c_int, _c_void_p]),
+    "kanb200_forward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
+                                                                     _c_void_p, _c_size, _c_void_p]),
+    "kanb200_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
+                                                                       _c_void_p, _c_size, _c_void_p]),
+    "kanb200_edge_abs_mean": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int,
+                                                                   _c_void_p, _c_size, _c_void_p]),
+    "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
+                                                                            _c_void_p, _c_size, _c_void_p]),
+    "kanb200_check_status": (_c_int, [_c_void_p, _c_void_p]),
+    "kanb200_umma_probe": (_c_int, [_c_void_p, ctypes.c_uint32, _c_void_p, ctypes.c_uint32, ctypes.c_uint64,
+                                    ctypes.c_uint64, ctypes.c_uint32, _c_int, ctypes.c_uint32, ctypes.c_uint32,
+                                    _c_int, _c_void_p, _c_void_p, _c_void_p]),
+}
+
+_lib = None
+_lock = threading.Lock()
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(LIB_PATH):
+                    raise RuntimeError(
+                        f"{LIB_PATH} is missing: build it with `python -m torchsplinekan_b200.build` "
+                        "(needs nvcc).  This package has no fallback implementation.")
+                handle = ctypes.CDLL(LIB_PATH)
+                for name, (res, args) in SIGNATURES.items():
+                    fn = getattr(handle, name)
+                    fn.restype, fn.argtypes = res, args
+                _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return lib().kanb200_last_error().decode("utf-8", "replace")
+
+
+def _check(rc: int) -> None:
+    if rc == 0:
+        return
+    msg = last_error()
+    if rc == EINVAL:
+        raise RuntimeError(msg)
+    raise RuntimeError(f"kan_b200 error {rc}: {msg}")
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.float64:
+        return F64
+    raise RuntimeError(f"only FP32 and FP64 inputs are supported, got {dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None or t.numel() == 0 else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev: torch.device):
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None or t.numel() == 0:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("kan_b200: expected CUDA tensors (there is no CPU path in this library)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("kan_b200: all tensors must be on the same device")
+    if dev is None:
+        raise RuntimeError("kan_b200: no CUDA tensor given")
+    return dev
+
+
+_ws_cache = {}
+
+
+def workspace(dev: torch.device, nbytes: int, tag: str = "") -> Optional[torch.Tensor]:
+    """Per (device, stream, tag) scratch buffer, grown on demand and reused."""
+    if nbytes <= 0:
+        return None
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream, tag)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = None
+        _ws_cache.pop(key, None)
+        buf = torch.empty(int(nbytes * 1.0) + 256, dtype=torch.uint8, device=dev)
+        buf[:256].zero_()
+        _ws_cache[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    _ws_cache.clear()
+
+
+def resolve_mode(mode: int, dtype: torch.dtype, N: int, I: int, O: int, G: int, k: int) -> int:
+    m = lib().kanb200_resolve_mode(mode, _code(dtype), N, I, O, G, k)
+    if m < 0:
+        _check(m)
+    return m
+
+
+def workspace_bytes(op, mode, dtype, N, I, O, G, k, need_x=True, need_param=True) -> int:
+    return int(lib().kanb200_workspace_bytes(op, mode, _code(dtype), N, I, O, G, k, int(need_x), int(need_param)))
+
+
+def basis(x: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
+    dev = _need_cuda(x, grid)
+    N, I = x.shape
+    G = grid.shape[1] - 2 * k - 1
+    H = torch.empty((N, I, G + k), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib().kanb200_basis(_code(x.dtype), _p(x), _p(grid), _p(H), N, I, G, k, _stream(dev)))
+    return H
+
+
+def basis_grad(x: torch.Tensor, grid: torch.Tensor, k: int, gH: torch.Tensor) -> torch.Tensor:
+    dev = _need_cuda(x, grid, gH)
+    N, I = x.shape
+    G = grid.shape[1] - 2 * k - 1
+    gx = torch.empty((N, I), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(lib().kanb200_basis_grad(_code(x.dtype), _p(x), _p(grid), _p(gH), _p(gx), N, I, G, k, _stream(dev)))
+    return gx
+
+
+def forward(x, grid, base_weight, spline_weight, spline_scaler, k: int, mode: int = MODE_AUTO,
+            ws: Optional[torch.Tensor] = None) -> torch.Tensor:
+    dev = _need_cuda(x, grid, spline_weight)
+    N, I = x.shape
+    O = spline_weight.shape[0]
+    G = grid.shape[1] - 2 * k - 1
+    y = torch.empty((N, O), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        if ws is None:
+            ws = workspace(dev, workspace_bytes(OP_FORWARD, mode, x.dtype, N, I, O, G, k), "fwd")
+        _check(lib().kanb200_forward(_code(x.dtype), mode, _p(x), _p(grid), _p(base_weight), _p(spline_weight),
+                                     _p(spline_scaler), _p(y), N, I, O, G, k, _p(ws),
+                                     0 if ws is None else ws.numel(), _stream(dev)))
+    return y
+
+
+def backward(grad_out, x, grid, base_weight, spline_weight, spline_scaler, k: int,
+             need_x: bool, need_base: bool, need_spline: bool, need_scaler: bool, mode: int = MODE_AUTO,
+             ws: Optional[torch.Tensor] = None
+             ) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor], Optional[torch.Tensor]]:
+    dev = _need_cuda(x, grid, spline_weight, grad_out)
+    N, I = x.shape
+    O = spline_weight.shape[0]
+    G = grid.shape[1] - 2 * k - 1
+    has_base = base_weight is not None and base_weight.numel() > 0
+    has_scaler = spline_scaler is not None and spline_scaler.numel() > 0
+    need_base = need_base and has_base
+    need_scaler = need_scaler and has_scaler
+    gx = torch.empty_like(x) if need_x else None
+    gb = torch.empty_like(base_weight) if need_base else None
+    gs = torch.empty_like(spline_weight) if need_spline else None
+    gc = torch.empty_like(spline_scaler) if need_scaler else None
+    with torch.cuda.device(dev):
+        if ws is None:
+            nb = workspace_bytes(OP_BACKWARD, mode, x.dtype, N, I, O, G, k, need_x,
+                                 need_base or need_spline or need_scaler)
+            ws = workspace(dev, nb, "bwd")
+        _check(lib().kanb200_backward(_code(x.dtype), mode, _p(grad_out), _p(x), _p(grid), _p(base_weight),
+                                      _p(spline_weight), _p(spline_scaler), _p(gx), _p(gb), _p(gs), _p(gc),
+                                      N, I, O, G, k, _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+    return gx, gb, gs, gc
+
+
+def edge_abs_mean(s, H, bw, W) -> torch.Tensor:
+    dev = _need_cuda(H, W)
+    N, I, R = H.shape
+    O = W.shape[0]
+    a = torch.empty((O, I), dtype=H.dtype, device=dev)
+    with torch.cuda.device(dev):
+        nb = workspace_bytes(OP_EDGE_FWD, MODE_SIMT, H.dtype, N, I, O, max(R - 1, 1), 1)
+        ws = workspace(dev, nb, "edge")
+        _check(lib().kanb200_edge_abs_mean(_code(H.dtype), _p(s), _p(H), _p(bw), _p(W), _p(a), N, I, O, R,
+                                           _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+    return a
+
+
+def edge_abs_mean_backward(ga, s, H, bw, W, need_s, need_H, need_bw, need_W):
+    dev = _need_cuda(H, W, ga)
+    N, I, R = H.shape
+    O = W.shape[0]
+    has_base = bw is not None and bw.numel() > 0
+    ds = torch.empty((N, I), dtype=H.dtype, device=dev) if (need_s and has_base) else None
+    dH = torch.empty_like(H) if need_H else None
+    dbw = torch.empty((O, I), dtype=H.dtype, device=dev) if (need_bw and has_base) else None
+    dW = torch.empty_like(W) if need_W else None
+    with torch.cuda.device(dev):
+        nb = workspace_bytes(OP_EDGE_BWD, MODE_SIMT, H.dtype, N, I, O, max(R - 1, 1), 1)
+        ws = workspace(dev, nb, "edge")
+        _check(lib().kanb200_edge_abs_mean_backward(_code(H.dtype), _p(ga), _p(s), _p(H), _p(bw), _p(W),
+                                                    _p(ds), _p(dH), _p(dbw), _p(dW), N, I, O, R,
+                                                    _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+    return ds, dH, dbw, dW
+
+
+def check_status(ws: Optional[torch.Tensor]) -> None:
+    """Raises if a tensor-core kernel that used ``ws`` reported a timed-out wait."""
+    if ws is None:
+        return
+    with torch.cuda.device(ws.device):
+        _check(lib().kanb200_check_status(_p(ws), _stream(ws.device)))

@@ -1,0 +1,280 @@
+// C ABI of the library (declared in include/kan_b200.h): argument validation,
+// mode resolution, workspace sizing and dispatch to the kernel launchers.
+#include "../../include/kan_b200.h"
+#include "kan_internal.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+using namespace kanb200;
+
+namespace {
+
+thread_local char g_err[512] = "";
+int g_basis_impl = 1;
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    if (e == cudaErrorMemoryAllocation)
+        return fail(KANB200_EWORKSPACE, "%s: workspace missing or too small", what);
+    return fail(KANB200_ECUDA, "%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
+}
+
+bool make_shape(int64_t N, int64_t I, int64_t O, int G, int k, LayerShape& s) {
+    s.N = N;
+    s.I = (int)I;
+    s.O = (int)O;
+    s.G = G;
+    s.K = k;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+KANB200_API const char* kanb200_last_error(void) { return g_err; }
+
+KANB200_API int kanb200_version(void) { return 100; }
+
+KANB200_API int kanb200_set_basis_impl(int impl) {
+    if (impl != 0 && impl != 1) return fail(KANB200_EINVAL, "basis impl must be 0 (recurrence) or 1 (local)");
+    g_basis_impl = impl;
+    return KANB200_OK;
+}
+
+KANB200_API int kanb200_get_basis_impl(void) { return g_basis_impl; }
+
+KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int k, int dtype) {
+    if (dtype != KANB200_F32 && dtype != KANB200_F64)
+        return fail(KANB200_EINVAL, "only FP32 and FP64 inputs are supported");
+    if (k < 1 || k > 3) return fail(KANB200_EINVAL, "spline_order must be 1, 2 or 3; got %d", k);
+    if (G < 1) return fail(KANB200_EINVAL, "grid has %d knots, too few for spline_order %d", G + 2 * k + 1, k);
+    if (N < 0 || I < 1 || O < 1) return fail(KANB200_EINVAL, "bad sizes N=%lld I=%lld O=%lld",
+                                             (long long)N, (long long)I, (long long)O);
+    if (G + 2 * k > KANB200_MAX_DEG0_BASIS)
+        return fail(KANB200_EINVAL, "CUDA kernel supports G + 2k <= %d (got G=%d, k=%d); use backend='reference' "
+                                    "for larger grids", KANB200_MAX_DEG0_BASIS, G, k);
+    if (I > KANB200_MAX_IN_FEATURES)
+        return fail(KANB200_EINVAL, "CUDA kernel supports in_features <= %d, got %lld", KANB200_MAX_IN_FEATURES,
+                    (long long)I);
+    if (O > (int64_t)1 << 24) return fail(KANB200_EINVAL, "out_features too large: %lld", (long long)O);
+    return KANB200_OK;
+}
+
+KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k) {
+    LayerShape s;
+    make_shape(N, I, O, G, k, s);
+    const bool tc_ok = dtype == KANB200_F32 && tc_supported(s);
+    if (mode == KANB200_MODE_AUTO) {
+        // Tensor cores pay off once a 128 x 256 tile is reasonably filled.
+        if (tc_ok && N >= 512 && O >= 64 && I >= 32) return KANB200_MODE_TC_BF16X3;
+        return KANB200_MODE_SIMT;
+    }
+    if (mode == KANB200_MODE_SIMT) return mode;
+    if (mode == KANB200_MODE_TC_BF16X3 || mode == KANB200_MODE_TC_BF16X1)
+        return tc_ok ? mode : fail(KANB200_EUNSUPPORTED, "tensor-core modes need float32 and G + k <= 8");
+    return fail(KANB200_EINVAL, "unknown mode %d", mode);
+}
+
+KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k,
+                               int need_x, int need_param) {
+    if (kanb200_check_shapes(N, I, O, G, k, dtype) != KANB200_OK) return 0;
+    LayerShape s;
+    make_shape(N, I, O, G, k, s);
+    if (op == KANB200_OP_EDGE_FWD || op == KANB200_OP_EDGE_BWD) {
+        const bool b = op == KANB200_OP_EDGE_BWD;
+        if (N < 1) return 0;
+        return dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
+                                    : edge_workspace<double>(N, s.I, s.O, s.R(), b);
+    }
+    const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
+    if (m < 0) return 0;
+    if (m == KANB200_MODE_SIMT) {
+        if (op == KANB200_OP_FORWARD) return 0;
+        return dtype == KANB200_F32 ? simt_backward_workspace<float>(s, need_param != 0)
+                                    : simt_backward_workspace<double>(s, need_param != 0);
+    }
+    return tc_workspace(op, s, need_x != 0, need_param != 0);
+}
+
+KANB200_API int kanb200_basis(int dtype, const void* x, const void* grid, void* H, int64_t N, int64_t I, int G, int k,
+                  void* stream) {
+    int rc = kanb200_check_shapes(N, I, 1, G, k, dtype);
+    if (rc) return rc;
+    if (N == 0) return KANB200_OK;
+    if (!x || !grid || !H) return fail(KANB200_EINVAL, "kan_basis: NULL pointer");
+    LayerShape s;
+    make_shape(N, I, 1, G, k, s);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = dtype == KANB200_F32
+                        ? simt_basis<float>((const float*)x, (const float*)grid, (float*)H, s, st)
+                        : simt_basis<double>((const double*)x, (const double*)grid, (double*)H, s, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis");
+}
+
+KANB200_API int kanb200_basis_grad(int dtype, const void* x, const void* grid, const void* gH, void* gx,
+                       int64_t N, int64_t I, int G, int k, void* stream) {
+    int rc = kanb200_check_shapes(N, I, 1, G, k, dtype);
+    if (rc) return rc;
+    if (N == 0) return KANB200_OK;
+    if (!x || !grid || !gH || !gx) return fail(KANB200_EINVAL, "kan_basis_grad: NULL pointer");
+    LayerShape s;
+    make_shape(N, I, 1, G, k, s);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = dtype == KANB200_F32
+                        ? simt_basis_grad<float>((const float*)x, (const float*)grid, (const float*)gH, (float*)gx, s, st)
+                        : simt_basis_grad<double>((const double*)x, (const double*)grid, (const double*)gH,
+                                                  (double*)gx, s, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis_grad");
+}
+
+KANB200_API int kanb200_forward(int dtype, int mode, const void* x, const void* grid, const void* base_weight,
+                    const void* spline_weight, const void* spline_scaler, void* y,
+                    int64_t N, int64_t I, int64_t O, int G, int k,
+                    void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = kanb200_check_shapes(N, I, O, G, k, dtype);
+    if (rc) return rc;
+    if (N == 0) return KANB200_OK;
+    if (!x || !grid || !spline_weight || !y) return fail(KANB200_EINVAL, "kan_forward: NULL pointer");
+    const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
+    if (m < 0) return m;
+    LayerShape s;
+    make_shape(N, I, O, G, k, s);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (m == KANB200_MODE_SIMT) {
+        e = dtype == KANB200_F32
+                ? simt_forward<float>((const float*)x, (const float*)grid, (const float*)base_weight,
+                                      (const float*)spline_weight, (const float*)spline_scaler, (float*)y, s, st)
+                : simt_forward<double>((const double*)x, (const double*)grid, (const double*)base_weight,
+                                       (const double*)spline_weight, (const double*)spline_scaler, (double*)y, s, st);
+    } else {
+        e = tc_forward(m == KANB200_MODE_TC_BF16X3 ? 3 : 1, (const float*)x, (const float*)grid,
+                       (const float*)base_weight, (const float*)spline_weight, (const float*)spline_scaler,
+                       (float*)y, s, workspace, workspace_bytes, st);
+    }
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_forward");
+}
+
+KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out, const void* x, const void* grid,
+                     const void* base_weight, const void* spline_weight, const void* spline_scaler,
+                     void* grad_x, void* grad_base_weight, void* grad_spline_weight, void* grad_spline_scaler,
+                     int64_t N, int64_t I, int64_t O, int G, int k,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = kanb200_check_shapes(N, I, O, G, k, dtype);
+    if (rc) return rc;
+    if (!spline_weight || (N > 0 && (!grad_out || !x || !grid)))
+        return fail(KANB200_EINVAL, "kan_backward: NULL pointer");
+    if (grad_spline_scaler && !spline_scaler)
+        return fail(KANB200_EINVAL, "kan_backward: grad_spline_scaler requested without spline_scaler");
+    if (!base_weight) grad_base_weight = nullptr;
+    const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
+    if (m < 0) return m;
+    LayerShape s;
+    make_shape(N, I, O, G, k, s);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (m == KANB200_MODE_SIMT) {
+        e = dtype == KANB200_F32
+                ? simt_backward<float>((const float*)grad_out, (const float*)x, (const float*)grid,
+                                       (const float*)base_weight, (const float*)spline_weight,
+                                       (const float*)spline_scaler, (float*)grad_x, (float*)grad_base_weight,
+                                       (float*)grad_spline_weight, (float*)grad_spline_scaler, s, workspace,
+                                       workspace_bytes, st)
+                : simt_backward<double>((const double*)grad_out, (const double*)x, (const double*)grid,
+                                        (const double*)base_weight, (const double*)spline_weight,
+                                        (const double*)spline_scaler, (double*)grad_x, (double*)grad_base_weight,
+                                        (double*)grad_spline_weight, (double*)grad_spline_scaler, s, workspace,
+                                        workspace_bytes, st);
+    } else {
+        e = tc_backward(m == KANB200_MODE_TC_BF16X3 ? 3 : 1, (const float*)grad_out, (const float*)x,
+                        (const float*)grid, (const float*)base_weight, (const float*)spline_weight,
+                        (const float*)spline_scaler, (float*)grad_x, (float*)grad_base_weight,
+                        (float*)grad_spline_weight, (float*)grad_spline_scaler, s, workspace, workspace_bytes, st);
+    }
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_backward");
+}
+
+static int check_edge(int dtype, int64_t N, int64_t I, int64_t O, int R) {
+    if (dtype != KANB200_F32 && dtype != KANB200_F64)
+        return fail(KANB200_EINVAL, "edge_abs_mean: only FP32/FP64 supported");
+    if (R < 1 || R > 72) return fail(KANB200_EINVAL, "edge_abs_mean: R must be <= 72, got %d", R);
+    if (I < 1 || I > KANB200_MAX_IN_FEATURES) return fail(KANB200_EINVAL, "edge_abs_mean: too many input features");
+    if (N < 1) return fail(KANB200_EINVAL, "edge_abs_mean: need at least one sample");
+    if (O < 1) return fail(KANB200_EINVAL, "edge_abs_mean: bad out_features");
+    return KANB200_OK;
+}
+
+KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, const void* bw, const void* W, void* a,
+                          int64_t N, int64_t I, int64_t O, int R,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_edge(dtype, N, I, O, R);
+    if (rc) return rc;
+    if (!H || !W || !a) return fail(KANB200_EINVAL, "edge_abs_mean: NULL pointer");
+    if ((s == nullptr) != (bw == nullptr))
+        return fail(KANB200_EINVAL, "edge_abs_mean: s and base_weight must both be given or both be absent");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = dtype == KANB200_F32
+                        ? edge_abs_mean_fwd<float>((const float*)s, (const float*)H, (const float*)bw, (const float*)W,
+                                                   (float*)a, N, (int)I, (int)O, R, workspace, workspace_bytes, st)
+                        : edge_abs_mean_fwd<double>((const double*)s, (const double*)H, (const double*)bw,
+                                                    (const double*)W, (double*)a, N, (int)I, (int)O, R, workspace,
+                                                    workspace_bytes, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean");
+}
+
+KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a, const void* s, const void* H, const void* bw,
+                                   const void* W, void* ds, void* dH, void* dbw, void* dW,
+                                   int64_t N, int64_t I, int64_t O, int R,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_edge(dtype, N, I, O, R);
+    if (rc) return rc;
+    if (!H || !W || !grad_a) return fail(KANB200_EINVAL, "edge_abs_mean_backward: NULL pointer");
+    if ((s == nullptr) != (bw == nullptr))
+        return fail(KANB200_EINVAL, "edge_abs_mean_backward: s and base_weight must both be given or both be absent");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e =
+        dtype == KANB200_F32
+            ? edge_abs_mean_bwd<float>((const float*)grad_a, (const float*)s, (const float*)H, (const float*)bw,
+                                       (const float*)W, (float*)ds, (float*)dH, (float*)dbw, (float*)dW, N, (int)I,
+                                       (int)O, R, workspace, workspace_bytes, st)
+            : edge_abs_mean_bwd<double>((const double*)grad_a, (const double*)s, (const double*)H, (const double*)bw,
+                                        (const double*)W, (double*)ds, (double*)dH, (double*)dbw, (double*)dW, N,
+                                        (int)I, (int)O, R, workspace, workspace_bytes, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_backward");
+}
+
+KANB200_API int kanb200_check_status(void* workspace, void* stream) {
+    if (!workspace) return KANB200_OK;
+    int code = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemcpyAsync(&code, workspace, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "check_status");
+    if (code != 0) {
+        cudaMemsetAsync(workspace, 0, sizeof(int), st);
+        return fail(KANB200_EDEVICE, "a tensor-core kernel gave up waiting (status %d)", code);
+    }
+    return KANB200_OK;
+}
+
+KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
+                       uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps,
+                       uint32_t a_step, uint32_t b_step, int ncols, float* D, int* status, void* stream) {
+    if (!a_img || !b_img || !D || !status || (a_bytes & 15) || (b_bytes & 15))
+        return fail(KANB200_EINVAL, "umma_probe: bad arguments");
+    cudaError_t e = umma_probe(a_img, a_bytes, b_img, b_bytes, a_desc, b_desc, idesc, ksteps, a_step, b_step,
+                               ncols, D, status, (cudaStream_t)stream);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "umma_probe");
+}
+
+}  // extern "C"

@@ -1,0 +1,72 @@
+// Internal launcher interface between the C-ABI file and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace kanb200 {
+
+struct LayerShape {
+    int64_t N;      // samples
+    int I, O;       // in / out features
+    int G, K;       // grid intervals, spline order
+    int R() const { return G + K; }
+    int T() const { return G + 2 * K + 1; }
+};
+
+// ---- SIMT path (kan_simt.cu), T = float or double ---------------------------
+template <typename T>
+cudaError_t simt_basis(const T* x, const T* grid, T* H, const LayerShape& s, cudaStream_t st);
+template <typename T>
+cudaError_t simt_basis_grad(const T* x, const T* grid, const T* gH, T* gx, const LayerShape& s, cudaStream_t st);
+template <typename T>
+cudaError_t simt_forward(const T* x, const T* grid, const T* bw, const T* sw, const T* scaler, T* y,
+                         const LayerShape& s, cudaStream_t st);
+template <typename T>
+size_t simt_backward_workspace(const LayerShape& s, bool need_param);
+template <typename T>
+cudaError_t simt_backward(const T* dY, const T* x, const T* grid, const T* bw, const T* sw, const T* scaler,
+                          T* gx, T* gbw, T* gsw, T* gscaler, const LayerShape& s,
+                          void* ws, size_t ws_bytes, cudaStream_t st);
+
+// Sums `splits` partial parameter-gradient slabs and applies the scaler
+// algebra: gsw = scaler * D, gscaler = sum_r sw * D, gbw = base slot.
+// Element (o,i,r) of a slab sits at o*ldo + i*sI + r, its base slot at
+// o*ldo + boff + i*sB.
+template <typename T>
+cudaError_t finalize_param_grads(const T* partial, int splits, int64_t split_stride,
+                                 int64_t ldo, int sI, int64_t boff, int sB,
+                                 const T* sw, const T* scaler, T* gsw, T* gscaler, T* gbw,
+                                 int O, int I, int R, cudaStream_t st);
+
+// ---- edge statistic (kan_reg.cu) -------------------------------------------
+template <typename T>
+size_t edge_workspace(int64_t N, int I, int O, int R, bool backward);
+template <typename T>
+cudaError_t edge_abs_mean_fwd(const T* s, const T* H, const T* bw, const T* W, T* a,
+                              int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st);
+template <typename T>
+cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, const T* W,
+                              T* ds, T* dH, T* dbw, T* dW,
+                              int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st);
+
+// ---- tensor-core path (kan_tc.cu), fp32 I/O ---------------------------------
+bool tc_supported(const LayerShape& s);
+size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param);
+cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const float* bw, const float* sw,
+                       const float* scaler, float* y, const LayerShape& s,
+                       void* ws, size_t ws_bytes, cudaStream_t st);
+cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const float* grid, const float* bw,
+                        const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
+                        float* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st);
+
+// Layout self-test (kan_probe.cu).
+cudaError_t umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
+                       uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps, uint32_t a_step,
+                       uint32_t b_step, int ncols, float* D, int* status, cudaStream_t st);
+
+// Workspaces start with a 256-byte header whose first word is a status code
+// written by kernels whose bounded waits ran out.
+constexpr size_t kWsHeader = 256;
+
+}  // namespace kanb200

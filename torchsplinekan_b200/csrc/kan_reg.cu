@@ -1,0 +1,321 @@
+// Activation-regulariser statistic and its gradients, without ever storing
+// phi[n,o,i] = s[n,i] bw[o,i] + sum_r H[n,i,r] W[o,i,r]:
+//
+//   forward   a[o,i]   = (1/N) sum_n |phi|
+//   backward  g        = ga[o,i] sign(phi) / N        (sign(0) = 0)
+//             dbw[o,i] = sum_n g s      dW[o,i,r] = sum_n g H[n,i,r]
+//             ds[n,i]  = sum_o g bw     dH[n,i,r] = sum_o g W[o,i,r]
+//
+// Bound by the FP32/FP64 FMA pipe (N O I (R+1) FMAs against N I (R+1) + O I (R+1)
+// input elements).  Sums over samples are split across blocks; each split
+// writes its own slab in the caller's workspace and a second kernel adds the
+// slabs in a fixed order -- no atomics, bit-reproducible results.
+#include "kan_device.cuh"
+#include "kan_internal.h"
+
+namespace kanb200 {
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ T sign_t(T v) { return T((v > T(0)) - (v < T(0))); }
+
+constexpr int EA_TI = 4, EA_THREADS = 128;
+
+// Thread = OPT outputs x one feature, W rows in registers; loops over the
+// samples of its split with H / s tiles staged in shared memory.
+template <typename T, int RMAX, int OPT, int TNS, bool GRAD>
+__global__ void __launch_bounds__(EA_THREADS)
+edge_param_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __restrict__ bw,
+                  const T* __restrict__ W, const T* __restrict__ ga,
+                  T* __restrict__ part_a, T* __restrict__ part_dbw, T* __restrict__ part_dW,
+                  int64_t N, int I, int O, int R, int64_t n_per_split) {
+    constexpr int TO = 32 * OPT;
+    __shared__ T Hs[TNS][EA_TI][RMAX];
+    __shared__ T ss[TNS][EA_TI];
+    const int tid = threadIdx.x;
+    const int lane_o = tid & 31, ti = tid >> 5;
+    const int o0 = blockIdx.x * TO, i0 = blockIdx.y * EA_TI;
+    const int i = i0 + ti;
+    const int64_t nb = (int64_t)blockIdx.z * n_per_split;
+    const int64_t ne = (nb + n_per_split < N) ? nb + n_per_split : N;
+    const T invN = T(1) / T(N);
+    const bool has_base = (bw != nullptr);
+
+    T w[OPT][RMAX], bwv[OPT], gav[OPT];
+    T acc_a[OPT], acc_b[OPT];
+    T dw[GRAD ? OPT : 1][GRAD ? RMAX : 1];
+#pragma unroll
+    for (int u = 0; u < OPT; ++u) {
+        const int o = o0 + lane_o + 32 * u;
+        const bool ok = (o < O) && (i < I);
+        const size_t oi = ok ? (size_t)o * I + i : 0;
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) w[u][r] = (ok && r < R) ? W[oi * R + r] : T(0);
+        bwv[u] = (ok && has_base) ? bw[oi] : T(0);
+        gav[u] = (GRAD && ok) ? ga[oi] * invN : T(0);
+        acc_a[u] = T(0);
+        acc_b[u] = T(0);
+        if (GRAD) {
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) dw[u][r] = T(0);
+        }
+    }
+
+    for (int64_t nt = nb; nt < ne; nt += TNS) {
+        __syncthreads();
+        for (int e = tid; e < TNS * EA_TI * RMAX; e += EA_THREADS) {
+            const int n = e / (EA_TI * RMAX);
+            const int rem = e - n * (EA_TI * RMAX);
+            const int ii = rem / RMAX, r = rem - ii * RMAX;
+            T v = T(0);
+            if (nt + n < ne && i0 + ii < I && r < R) v = H[((size_t)(nt + n) * I + i0 + ii) * R + r];
+            Hs[n][ii][r] = v;
+        }
+        for (int e = tid; e < TNS * EA_TI; e += EA_THREADS) {
+            const int n = e / EA_TI, ii = e - n * EA_TI;
+            ss[n][ii] = (has_base && nt + n < ne && i0 + ii < I) ? s[(size_t)(nt + n) * I + i0 + ii] : T(0);
+        }
+        __syncthreads();
+        const int lim = (int)((ne - nt < TNS) ? (ne - nt) : TNS);
+        for (int n = 0; n < lim; ++n) {
+            const T sv = ss[n][ti];
+            T phi[OPT];
+#pragma unroll
+            for (int u = 0; u < OPT; ++u) phi[u] = sv * bwv[u];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) {
+                const T h = Hs[n][ti][r];
+#pragma unroll
+                for (int u = 0; u < OPT; ++u) phi[u] += h * w[u][r];
+            }
+            if (!GRAD) {
+#pragma unroll
+                for (int u = 0; u < OPT; ++u) acc_a[u] += fabs(phi[u]);
+            } else {
+                T g[OPT];
+#pragma unroll
+                for (int u = 0; u < OPT; ++u) {
+                    g[u] = gav[u] * sign_t<T>(phi[u]);
+                    acc_b[u] += g[u] * sv;
+                }
+#pragma unroll
+                for (int r = 0; r < RMAX; ++r) {
+                    const T h = Hs[n][ti][r];
+#pragma unroll
+                    for (int u = 0; u < OPT; ++u) dw[u][r] += g[u] * h;
+                }
+            }
+        }
+    }
+    if (i < I) {
+#pragma unroll
+        for (int u = 0; u < OPT; ++u) {
+            const int o = o0 + lane_o + 32 * u;
+            if (o >= O) continue;
+            const size_t oi = (size_t)blockIdx.z * O * I + (size_t)o * I + i;
+            if (!GRAD) {
+                part_a[oi] = acc_a[u];
+            } else {
+                if (part_dbw) part_dbw[oi] = acc_b[u];
+                if (part_dW) {
+#pragma unroll
+                    for (int r = 0; r < RMAX; ++r)
+                        if (r < R) part_dW[oi * R + r] = dw[u][r];
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void sum_slabs_kernel(const T* __restrict__ part, T* __restrict__ out, int64_t elems,
+                                 int splits, T scale) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < elems;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        T v = T(0);
+        for (int s = 0; s < splits; ++s) v += part[(size_t)s * elems + e];
+        out[e] = v * scale;
+    }
+}
+
+// Thread = one (n, i): H row and dH accumulators in registers, loops over
+// tiles of outputs staged in shared memory.
+constexpr int EB_TI = 4, EB_TN = 32, EB_THREADS = 128;
+
+template <typename T, int RMAX, int TOC>
+__global__ void __launch_bounds__(EB_THREADS)
+edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __restrict__ bw,
+                  const T* __restrict__ W, const T* __restrict__ ga,
+                  T* __restrict__ ds, T* __restrict__ dH,
+                  int64_t N, int I, int O, int R) {
+    __shared__ T Ws[TOC][EB_TI][RMAX + 2];        // [..][RMAX] = bw, [..][RMAX+1] = ga/N
+    const int tid = threadIdx.x;
+    const int ti = tid & (EB_TI - 1), tn = tid / EB_TI;
+    const int i0 = blockIdx.y * EB_TI;
+    const int i = i0 + ti;
+    const int64_t n = (int64_t)blockIdx.x * EB_TN + tn;
+    const bool live = (i < I) && (n < N);
+    const bool has_base = (bw != nullptr);
+    const T invN = T(1) / T(N);
+
+    T h[RMAX], dh[RMAX];
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) {
+        h[r] = (live && r < R) ? H[((size_t)n * I + i) * R + r] : T(0);
+        dh[r] = T(0);
+    }
+    const T sv = (live && has_base) ? s[(size_t)n * I + i] : T(0);
+    T dsv = T(0);
+
+    for (int oc = 0; oc < O; oc += TOC) {
+        __syncthreads();
+        for (int e = tid; e < TOC * EB_TI * (RMAX + 2); e += EB_THREADS) {
+            const int o = e / (EB_TI * (RMAX + 2));
+            const int rem = e - o * (EB_TI * (RMAX + 2));
+            const int ii = rem / (RMAX + 2), r = rem - ii * (RMAX + 2);
+            T v = T(0);
+            if (oc + o < O && i0 + ii < I) {
+                const size_t oi = (size_t)(oc + o) * I + i0 + ii;
+                if (r < RMAX) v = (r < R) ? W[oi * R + r] : T(0);
+                else if (r == RMAX) v = has_base ? bw[oi] : T(0);
+                else v = ga[oi] * invN;
+            }
+            Ws[o][ii][r] = v;
+        }
+        __syncthreads();
+        for (int o = 0; o < TOC; ++o) {
+            const T* wr = &Ws[o][ti][0];
+            T phi = sv * wr[RMAX];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) phi += h[r] * wr[r];
+            const T g = wr[RMAX + 1] * sign_t<T>(phi);
+            dsv += g * wr[RMAX];
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) dh[r] += g * wr[r];
+        }
+    }
+    if (live) {
+        if (ds) ds[(size_t)n * I + i] = dsv;
+        if (dH) {
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r)
+                if (r < R) dH[((size_t)n * I + i) * R + r] = dh[r];
+        }
+    }
+}
+
+struct EdgePlan {
+    int rmax, opt, tns, to, splits;
+    int64_t n_per_split;
+};
+
+template <typename T>
+EdgePlan plan_edge(int64_t N, int I, int O, int R) {
+    EdgePlan p;
+    p.rmax = R <= 8 ? 8 : (R <= 16 ? 16 : (R <= 32 ? 32 : 72));
+    p.opt = p.rmax <= 8 ? 4 : (p.rmax == 16 ? 2 : 1);
+    p.tns = p.rmax >= 32 ? 8 : 32;
+    p.to = 32 * p.opt;
+    const int64_t bxy = (int64_t)((O + p.to - 1) / p.to) * ((I + EA_TI - 1) / EA_TI);
+    int64_t splits = (4 * 148 + bxy - 1) / bxy;
+    const int64_t max_splits = (N + 127) / 128;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    p.n_per_split = (N + splits - 1) / splits;
+    p.splits = (int)((N + p.n_per_split - 1) / p.n_per_split);
+    if (p.splits < 1) p.splits = 1;
+    return p;
+}
+
+template <typename T, bool GRAD>
+cudaError_t launch_edge_param(const EdgePlan& p, const T* s, const T* H, const T* bw, const T* W, const T* ga,
+                              T* pa, T* pdbw, T* pdW, int64_t N, int I, int O, int R, cudaStream_t st) {
+    dim3 g((O + p.to - 1) / p.to, (I + EA_TI - 1) / EA_TI, p.splits);
+#define KAN_EP(RM, OP, TN)                                                                           \
+    edge_param_kernel<T, RM, OP, TN, GRAD><<<g, EA_THREADS, 0, st>>>(s, H, bw, W, ga, pa, pdbw, pdW, \
+                                                                     N, I, O, R, p.n_per_split)
+    if (p.rmax == 8) KAN_EP(8, 4, 32);
+    else if (p.rmax == 16) KAN_EP(16, 2, 32);
+    else if (p.rmax == 32) KAN_EP(32, 1, 8);
+    else KAN_EP(72, 1, 8);
+#undef KAN_EP
+    return cudaGetLastError();
+}
+
+inline int grid_1d(int64_t work, int threads, int cap = 148 * 32) {
+    int64_t b = (work + threads - 1) / threads;
+    if (b < 1) b = 1;
+    if (b > cap) b = cap;
+    return (int)b;
+}
+
+}  // namespace
+
+template <typename T>
+size_t edge_workspace(int64_t N, int I, int O, int R, bool backward) {
+    EdgePlan p = plan_edge<T>(N, I, O, R);
+    const size_t oi = (size_t)O * I;
+    return (size_t)p.splits * oi * (backward ? (size_t)(R + 1) : 1) * sizeof(T);
+}
+
+template <typename T>
+cudaError_t edge_abs_mean_fwd(const T* s, const T* H, const T* bw, const T* W, T* a,
+                              int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st) {
+    EdgePlan p = plan_edge<T>(N, I, O, R);
+    const size_t oi = (size_t)O * I;
+    if (!ws || ws_bytes < (size_t)p.splits * oi * sizeof(T)) return cudaErrorMemoryAllocation;
+    T* pa = reinterpret_cast<T*>(ws);
+    cudaError_t e = launch_edge_param<T, false>(p, s, H, bw, W, nullptr, pa, nullptr, nullptr, N, I, O, R, st);
+    if (e != cudaSuccess) return e;
+    sum_slabs_kernel<T><<<grid_1d((int64_t)oi, 256), 256, 0, st>>>(pa, a, (int64_t)oi, p.splits, T(1) / T(N));
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, const T* W,
+                              T* ds, T* dH, T* dbw, T* dW,
+                              int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st) {
+    cudaError_t e = cudaSuccess;
+    const size_t oi = (size_t)O * I;
+    if (dbw || dW) {
+        EdgePlan p = plan_edge<T>(N, I, O, R);
+        if (!ws || ws_bytes < (size_t)p.splits * oi * (R + 1) * sizeof(T)) return cudaErrorMemoryAllocation;
+        T* pdW = reinterpret_cast<T*>(ws);
+        T* pdbw = pdW + (size_t)p.splits * oi * R;
+        e = launch_edge_param<T, true>(p, s, H, bw, W, ga, nullptr, (dbw && bw) ? pdbw : nullptr,
+                                       dW ? pdW : nullptr, N, I, O, R, st);
+        if (e != cudaSuccess) return e;
+        if (dW) {
+            sum_slabs_kernel<T><<<grid_1d((int64_t)oi * R, 256), 256, 0, st>>>(pdW, dW, (int64_t)oi * R, p.splits, T(1));
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
+        if (dbw && bw) {
+            sum_slabs_kernel<T><<<grid_1d((int64_t)oi, 256), 256, 0, st>>>(pdbw, dbw, (int64_t)oi, p.splits, T(1));
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
+    }
+    if ((ds && bw) || dH) {
+        const int rmax = R <= 8 ? 8 : (R <= 16 ? 16 : (R <= 32 ? 32 : 72));
+        dim3 g((unsigned)((N + EB_TN - 1) / EB_TN), (I + EB_TI - 1) / EB_TI);
+        T* dsp = (ds && bw) ? ds : nullptr;
+        if (rmax == 8) edge_input_kernel<T, 8, 32><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        else if (rmax == 16) edge_input_kernel<T, 16, 32><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        else if (rmax == 32) edge_input_kernel<T, 32, 16><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        else edge_input_kernel<T, 72, 8><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        e = cudaGetLastError();
+    }
+    return e;
+}
+
+#define KAN_INSTANTIATE(T)                                                                               \
+    template size_t edge_workspace<T>(int64_t, int, int, int, bool);                                     \
+    template cudaError_t edge_abs_mean_fwd<T>(const T*, const T*, const T*, const T*, T*, int64_t, int,  \
+                                              int, int, void*, size_t, cudaStream_t);                    \
+    template cudaError_t edge_abs_mean_bwd<T>(const T*, const T*, const T*, const T*, const T*, T*, T*,  \
+                                              T*, T*, int64_t, int, int, int, void*, size_t, cudaStream_t);
+KAN_INSTANTIATE(float)
+KAN_INSTANTIATE(double)
+
+}  // namespace kanb200
