@@ -27,3 +27,10 @@ def rel_err(a, b):
     b = np.asarray(b, dtype=np.float64)
     den = max(float(np.abs(b).max()) if b.size else 0.0, 1e-300)
     return float(np.abs(a - b).max() / den) if b.size else 0.0
+
+
+def pytest_sessionstart(session):
+    """The package refuses to import without its CUDA library: build it (nvcc cross-compiles
+    without a GPU) when it is missing or older than its sources."""
+    from torchsplinekan_b200.build import build_library
+    build_library()

@@ -110,3 +110,22 @@ def test_config0_matches_reference():
 def test_uniform_grid_matches_reference_layout():
     z = load_golden("config0.npz")
     assert np.array_equal(ko.uniform_grid(16, 5, 3), z["l0/grid"])
+
+
+def test_torch_cpu_baseline_matches_reference():
+    """The multi-threaded CPU baseline timed by bench.py is pinned to the same golden vectors."""
+    import torch
+    from oracle import kan_oracle_torch as kt
+    z = load_golden("layer.npz")
+    for name in _names(z):
+        t = lambda a: None if a is None else torch.from_numpy(a)
+        sc = z[name + "/spline_scaler"] if name + "/spline_scaler" in z.files else None
+        y, gx, gb, gs, gsc = kt.layer_step_sum_sq(t(z[name + "/x"]), t(z[name + "/grid"]), t(z[name + "/base_weight"]),
+                                                  t(z[name + "/spline_weight"]), t(sc), int(z[name + "/k"]), True)
+        tol = 1e-12 if z[name + "/x"].dtype == np.float64 else 2e-6
+        assert rel_err(y.numpy(), z[name + "/y"]) < tol, name
+        assert rel_err(gx.numpy(), z[name + "/gx"]) < tol, name
+        assert rel_err(gb.numpy(), z[name + "/g_base_weight"]) < tol, name
+        assert rel_err(gs.numpy(), z[name + "/g_spline_weight"]) < tol, name
+        if sc is not None:
+            assert rel_err(gsc.numpy(), z[name + "/g_spline_scaler"]) < tol, name

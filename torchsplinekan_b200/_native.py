@@ -122,6 +122,28 @@ def _need_cuda(*tensors: torch.Tensor) -> torch.device:
 
 _ws_cache = {}
 
+# When set to a list, forward()/backward() append (name, start_event, end_event) recorded on the
+# launching stream around the library call; the benchmark uses it for per-kernel durations.
+EVENT_LOG = None
+
+
+class _Timed:
+    def __init__(self, name: str, dev: torch.device):
+        self.name, self.dev = name, dev
+
+    def __enter__(self):
+        if EVENT_LOG is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.dev))
+        return self
+
+    def __exit__(self, *exc):
+        if EVENT_LOG is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(torch.cuda.current_stream(self.dev))
+            EVENT_LOG.append((self.name, self.start, end))
+        return False
+
 
 def workspace(dev: torch.device, nbytes: int, tag: str = "") -> Optional[torch.Tensor]:
     """Per (device, stream, tag) scratch buffer, grown on demand and reused."""
@@ -183,9 +205,10 @@ def forward(x, grid, base_weight, spline_weight, spline_scaler, k: int, mode: in
     with torch.cuda.device(dev):
         if ws is None:
             ws = workspace(dev, workspace_bytes(OP_FORWARD, mode, x.dtype, N, I, O, G, k), "fwd")
-        _check(lib().kanb200_forward(_code(x.dtype), mode, _p(x), _p(grid), _p(base_weight), _p(spline_weight),
-                                     _p(spline_scaler), _p(y), N, I, O, G, k, _p(ws),
-                                     0 if ws is None else ws.numel(), _stream(dev)))
+        with _Timed("forward", dev):
+            _check(lib().kanb200_forward(_code(x.dtype), mode, _p(x), _p(grid), _p(base_weight),
+                                         _p(spline_weight), _p(spline_scaler), _p(y), N, I, O, G, k, _p(ws),
+                                         0 if ws is None else ws.numel(), _stream(dev)))
     return y
 
 
@@ -210,9 +233,10 @@ def backward(grad_out, x, grid, base_weight, spline_weight, spline_scaler, k: in
             nb = workspace_bytes(OP_BACKWARD, mode, x.dtype, N, I, O, G, k, need_x,
                                  need_base or need_spline or need_scaler)
             ws = workspace(dev, nb, "bwd")
-        _check(lib().kanb200_backward(_code(x.dtype), mode, _p(grad_out), _p(x), _p(grid), _p(base_weight),
-                                      _p(spline_weight), _p(spline_scaler), _p(gx), _p(gb), _p(gs), _p(gc),
-                                      N, I, O, G, k, _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+        with _Timed("backward", dev):
+            _check(lib().kanb200_backward(_code(x.dtype), mode, _p(grad_out), _p(x), _p(grid), _p(base_weight),
+                                          _p(spline_weight), _p(spline_scaler), _p(gx), _p(gb), _p(gs), _p(gc),
+                                          N, I, O, G, k, _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return gx, gb, gs, gc
 
 

@@ -11,6 +11,13 @@ using namespace kanb200;
 
 namespace {
 
+// Scratch handed to the SIMT / regulariser launchers starts after the status
+// header, so the first word of every workspace keeps the same meaning.
+inline void* ws_body(void* ws, size_t bytes) {
+    return (ws && bytes > kWsHeader) ? static_cast<char*>(ws) + kWsHeader : nullptr;
+}
+inline size_t ws_body_bytes(void* ws, size_t bytes) { return (ws && bytes > kWsHeader) ? bytes - kWsHeader : 0; }
+
 thread_local char g_err[512] = "";
 int g_basis_impl = 1;
 
@@ -93,15 +100,16 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
     if (op == KANB200_OP_EDGE_FWD || op == KANB200_OP_EDGE_BWD) {
         const bool b = op == KANB200_OP_EDGE_BWD;
         if (N < 1) return 0;
-        return dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
-                                    : edge_workspace<double>(N, s.I, s.O, s.R(), b);
+        return kWsHeader + (dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
+                                                 : edge_workspace<double>(N, s.I, s.O, s.R(), b));
     }
     const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
     if (m < 0) return 0;
     if (m == KANB200_MODE_SIMT) {
         if (op == KANB200_OP_FORWARD) return 0;
-        return dtype == KANB200_F32 ? simt_backward_workspace<float>(s, need_param != 0)
-                                    : simt_backward_workspace<double>(s, need_param != 0);
+        const size_t b = dtype == KANB200_F32 ? simt_backward_workspace<float>(s, need_param != 0)
+                                              : simt_backward_workspace<double>(s, need_param != 0);
+        return b ? kWsHeader + b : 0;
     }
     return tc_workspace(op, s, need_x != 0, need_param != 0);
 }
@@ -188,13 +196,15 @@ KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out, cons
                 ? simt_backward<float>((const float*)grad_out, (const float*)x, (const float*)grid,
                                        (const float*)base_weight, (const float*)spline_weight,
                                        (const float*)spline_scaler, (float*)grad_x, (float*)grad_base_weight,
-                                       (float*)grad_spline_weight, (float*)grad_spline_scaler, s, workspace,
-                                       workspace_bytes, st)
+                                       (float*)grad_spline_weight, (float*)grad_spline_scaler, s,
+                                       ws_body(workspace, workspace_bytes),
+                                       ws_body_bytes(workspace, workspace_bytes), st)
                 : simt_backward<double>((const double*)grad_out, (const double*)x, (const double*)grid,
                                         (const double*)base_weight, (const double*)spline_weight,
                                         (const double*)spline_scaler, (double*)grad_x, (double*)grad_base_weight,
-                                        (double*)grad_spline_weight, (double*)grad_spline_scaler, s, workspace,
-                                        workspace_bytes, st);
+                                        (double*)grad_spline_weight, (double*)grad_spline_scaler, s,
+                                        ws_body(workspace, workspace_bytes),
+                                        ws_body_bytes(workspace, workspace_bytes), st);
     } else {
         e = tc_backward(m == KANB200_MODE_TC_BF16X3 ? 3 : 1, (const float*)grad_out, (const float*)x,
                         (const float*)grid, (const float*)base_weight, (const float*)spline_weight,
@@ -225,10 +235,12 @@ KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, c
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = dtype == KANB200_F32
                         ? edge_abs_mean_fwd<float>((const float*)s, (const float*)H, (const float*)bw, (const float*)W,
-                                                   (float*)a, N, (int)I, (int)O, R, workspace, workspace_bytes, st)
+                                                   (float*)a, N, (int)I, (int)O, R, ws_body(workspace, workspace_bytes),
+                                                   ws_body_bytes(workspace, workspace_bytes), st)
                         : edge_abs_mean_fwd<double>((const double*)s, (const double*)H, (const double*)bw,
-                                                    (const double*)W, (double*)a, N, (int)I, (int)O, R, workspace,
-                                                    workspace_bytes, st);
+                                                    (const double*)W, (double*)a, N, (int)I, (int)O, R,
+                                                    ws_body(workspace, workspace_bytes),
+                                                    ws_body_bytes(workspace, workspace_bytes), st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean");
 }
 
@@ -246,10 +258,12 @@ KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a, co
         dtype == KANB200_F32
             ? edge_abs_mean_bwd<float>((const float*)grad_a, (const float*)s, (const float*)H, (const float*)bw,
                                        (const float*)W, (float*)ds, (float*)dH, (float*)dbw, (float*)dW, N, (int)I,
-                                       (int)O, R, workspace, workspace_bytes, st)
+                                       (int)O, R, ws_body(workspace, workspace_bytes),
+                                       ws_body_bytes(workspace, workspace_bytes), st)
             : edge_abs_mean_bwd<double>((const double*)grad_a, (const double*)s, (const double*)H, (const double*)bw,
                                         (const double*)W, (double*)ds, (double*)dH, (double*)dbw, (double*)dW, N,
-                                        (int)I, (int)O, R, workspace, workspace_bytes, st);
+                                        (int)I, (int)O, R, ws_body(workspace, workspace_bytes),
+                                        ws_body_bytes(workspace, workspace_bytes), st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_backward");
 }
 

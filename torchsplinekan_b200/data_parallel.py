@@ -1,0 +1,143 @@
+"""
+Batch-sharded data parallelism for KAN layers: one process per GPU, rows of the
+batch split in contiguous blocks, weights and knots replicated, and ONE
+collective per layer and step -- an all-reduce (sum) of that layer's parameter
+gradients, started as soon as the layer's backward has produced them so that it
+overlaps the backward of the layers below.  The reference has no multi-device
+code; this module is what a data-parallel user of it needs on top.
+
+Per layer the gradients live in one flat bucket ``[d spline_weight | d spline_scaler |
+d base_weight]`` and ``param.grad`` are views into it, so nothing is copied
+before or after the collective.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+def shard_rows(n_rows: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """``[start, end)`` of the contiguous row block owned by ``rank``; blocks differ by at most one row."""
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of size {world_size}")
+    base, extra = divmod(n_rows, world_size)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def _layer_params(layer: nn.Module) -> List[nn.Parameter]:
+    seen, out = set(), []
+    for p in layer.parameters():
+        if p.requires_grad and id(p) not in seen:
+            seen.add(id(p))
+            out.append(p)
+    return out
+
+
+class GradientBucket:
+    """Flat per-layer gradient buckets with an overlapped all-reduce.
+
+    ``layers``: modules in forward order (each gets one bucket).  Call
+    :meth:`finish` after ``loss.backward()`` and before the optimiser step.
+    ``average=True`` divides by the world size (for mean-type losses); sum-type
+    losses keep the plain sum.
+    """
+
+    def __init__(self, layers: Iterable[nn.Module], process_group: Optional[dist.ProcessGroup] = None,
+                 average: bool = False) -> None:
+        self.group = process_group
+        self.average = average
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self._buckets: List[Tuple[torch.Tensor, List[nn.Parameter]]] = []
+        self._pending: List[int] = []
+        self._works: list = []
+        self._comm_stream = None
+        self._hooks = []
+        for layer in layers:
+            params = _layer_params(layer)
+            if not params:
+                continue
+            ref = params[0]
+            flat = torch.zeros(sum(p.numel() for p in params), dtype=ref.dtype, device=ref.device)
+            offset = 0
+            for p in params:
+                p.grad = flat[offset:offset + p.numel()].view_as(p)
+                offset += p.numel()
+            index = len(self._buckets)
+            self._buckets.append((flat, params))
+            self._pending.append(len(params))
+            for p in params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(index)))
+            if ref.is_cuda and self._comm_stream is None:
+                self._comm_stream = torch.cuda.Stream(device=ref.device)
+
+    @property
+    def buckets(self) -> List[torch.Tensor]:
+        return [flat for flat, _ in self._buckets]
+
+    def bucket_bytes(self) -> int:
+        return sum(flat.numel() * flat.element_size() for flat, _ in self._buckets)
+
+    def _make_hook(self, index: int):
+        def hook(param: nn.Parameter) -> None:
+            flat, params = self._buckets[index]
+            # autograd may have replaced the view with a fresh tensor: fold it back.
+            lo = 0
+            for p in params:
+                if p is param:
+                    view = flat[lo:lo + p.numel()].view_as(p)
+                    if p.grad is not None and p.grad.data_ptr() != view.data_ptr():
+                        view.copy_(p.grad)
+                        p.grad = view
+                    break
+                lo += p.numel()
+            self._pending[index] -= 1
+            if self._pending[index] == 0:
+                self._launch(index)
+        return hook
+
+    def _launch(self, index: int) -> None:
+        flat, _ = self._buckets[index]
+        if self.world == 1:
+            return
+        if flat.is_cuda:
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(flat.device))
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ready)
+                self._works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        else:
+            self._works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+
+    def finish(self) -> None:
+        """Waits for the collectives (the current stream waits for the communication stream)."""
+        for i, left in enumerate(self._pending):
+            if left > 0 and left < len(self._buckets[i][1]):
+                self._launch(i)                   # partially used layer: reduce what is there
+        for w in self._works:
+            w.wait()
+        self._works.clear()
+        if self._comm_stream is not None:
+            torch.cuda.current_stream(self._comm_stream.device).wait_stream(self._comm_stream)
+        if self.average and self.world > 1:
+            for flat, _ in self._buckets:
+                flat.div_(self.world)
+        self._pending = [len(params) for _, params in self._buckets]
+
+    def zero_grad(self) -> None:
+        """Zeros the buckets in place (keeps ``param.grad`` as views)."""
+        for flat, params in self._buckets:
+            flat.zero_()
+            lo = 0
+            for p in params:
+                if p.grad is None or p.grad.data_ptr() != flat[lo:lo + 1].data_ptr():
+                    p.grad = flat[lo:lo + p.numel()].view_as(p)
+                lo += p.numel()
+
+    def remove(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks.clear()

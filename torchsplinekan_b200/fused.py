@@ -1,0 +1,102 @@
+"""
+Autograd wrappers around the native basis and edge-statistic kernels
+(counterpart of spline_kan/fused.py).
+
+``EdgeAbsMean`` evaluates ``a[o,i] = mean_n |s[n,i] bw[o,i] + sum_r H[n,i,r] W[o,i,r]|``
+without storing phi [N, O, I]; its backward recomputes phi to obtain sign(phi).
+``NativeBasis`` evaluates H natively and contracts the incoming gradient with
+dB/dx in registers.  When the backward is itself being recorded
+(``create_graph=True``) both switch to dense differentiable PyTorch formulas
+written in terms of the saved inputs, so higher-order derivatives stay exact.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _C
+from .dense_backend import compute_basis, compute_basis_derivative, edge_abs_mean_dense
+
+HAS_FUSED_KERNELS = bool(_C.HAS_FUSED_KERNELS)
+
+
+class NativeBasis(torch.autograd.Function):
+    """``H = basis(x) [B, I, R]`` from the native kernel (spline_kan/fused.py:43-61)."""
+
+    @staticmethod
+    def forward(ctx, x, grid, k: int):
+        ctx.k = k
+        ctx.save_for_backward(x, grid)
+        return _C.basis(x, grid, k)
+
+    @staticmethod
+    def backward(ctx, gH):
+        x, grid = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None, None
+        if torch.is_grad_enabled():
+            return (gH * compute_basis_derivative(x, grid, ctx.k)).sum(-1), None, None
+        return _C.basis_grad(x.contiguous(), grid, ctx.k, gH.contiguous()), None, None
+
+
+class EdgeAbsMean(torch.autograd.Function):
+    """Per-edge mean |phi| without the [N, O, I] tensor (spline_kan/fused.py:64-102)."""
+
+    @staticmethod
+    def forward(ctx, s, H, bw, W):
+        has_base = bw is not None
+        none = H.new_empty(0)
+        ctx.has_base = has_base
+        ctx.save_for_backward(s if has_base else none, H, bw if has_base else none, W)
+        return _C.edge_abs_mean(s if has_base else none, H, bw if has_base else none, W)
+
+    @staticmethod
+    def backward(ctx, ga):
+        s, H, bw, W = ctx.saved_tensors
+        has_base = ctx.has_base
+        need_s, need_H, need_bw, need_W = ctx.needs_input_grad
+        if torch.is_grad_enabled():
+            # Partial derivatives written in the saved tensors themselves, so mixed
+            # second derivatives (e.g. d(dbw)/ds) survive; sign(0) = 0 as in |.|'s subgradient.
+            phi = torch.einsum("oir,nir->noi", W, H)
+            if has_base:
+                phi = s.unsqueeze(1) * bw.unsqueeze(0) + phi
+            g = phi.sign() * ga.unsqueeze(0) / H.shape[0]
+            return ((g * bw.unsqueeze(0)).sum(1) if need_s and has_base else None,
+                    torch.einsum("noi,oir->nir", g, W) if need_H else None,
+                    (g * s.unsqueeze(1)).sum(0) if need_bw and has_base else None,
+                    torch.einsum("noi,nir->oir", g, H) if need_W else None)
+        ds, dH, dbw, dW = _C.edge_abs_mean_backward(ga, s, H, bw, W, bool(need_s and has_base), bool(need_H),
+                                                    bool(need_bw and has_base), bool(need_W))
+        return (ds if need_s and has_base else None, dH if need_H else None,
+                dbw if need_bw and has_base else None, dW if need_W else None)
+
+
+def native_basis(x: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
+    return NativeBasis.apply(x, grid, k)
+
+
+def edge_abs_mean(s: Optional[torch.Tensor], H: torch.Tensor, bw: Optional[torch.Tensor],
+                  W: torch.Tensor) -> torch.Tensor:
+    return EdgeAbsMean.apply(s, H, bw, W)
+
+
+def edge_abs_mean_chunked(s: Optional[torch.Tensor], x: torch.Tensor, grid: torch.Tensor, k: int,
+                          bw: Optional[torch.Tensor], W: torch.Tensor, chunk_size: int) -> torch.Tensor:
+    """Pure-PyTorch low-memory variant: per-chunk phi, recomputed in backward through activation
+    checkpointing (spline_kan/fused.py:114-137).  Any device, any derivative order."""
+    from torch.utils.checkpoint import checkpoint
+
+    N = x.shape[0]
+
+    def weighted(xc, sc, bw_, W_):
+        return edge_abs_mean_dense(sc, compute_basis(xc, grid, k), bw_, W_) * xc.shape[0]
+
+    total = None
+    for start in range(0, N, chunk_size):
+        xc = x[start:start + chunk_size]
+        sc = s[start:start + chunk_size] if s is not None else None
+        part = checkpoint(weighted, xc, sc, bw, W, use_reentrant=False)
+        total = part if total is None else total + part
+    return total / N

@@ -1,0 +1,291 @@
+"""
+KANLinear: one B-spline KAN layer with a native B200 backend
+(API of spline_kan/kan_linear.py: same constructor, attributes, methods,
+state-dict keys and error behaviour).
+"""
+from __future__ import annotations
+
+import copy
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _C
+from . import fused as _fused
+from .dense_backend import (ReferenceKANLayer, compute_basis, edge_abs_mean_dense, fit_spline_coeffs,
+                            regularization_from_edge_means)
+
+_CUDA_EXT_LOADED: bool = True            # importing ._C raises when the library is missing
+REG_IMPLS = ("auto", "dense", "fused", "checkpoint")
+CUDA_MAX_DEG0_BASIS = int(_C.CUDA_MAX_DEG0_BASIS)
+CUDA_MAX_IN_FEATURES = int(_C.CUDA_MAX_IN_FEATURES)
+
+
+def native_config_supported(in_features: int, grid_size: int, spline_order: int) -> Tuple[bool, str]:
+    """``(ok, reason)``: whether the native kernels accept a layer shape (kan_linear.py:43-55)."""
+    if grid_size + 2 * spline_order > CUDA_MAX_DEG0_BASIS:
+        return False, (f"grid_size + 2*spline_order = {grid_size + 2 * spline_order} exceeds the "
+                       f"CUDA kernel limit of {CUDA_MAX_DEG0_BASIS}")
+    if in_features > CUDA_MAX_IN_FEATURES:
+        return False, f"in_features = {in_features} exceeds the CUDA kernel limit of {CUDA_MAX_IN_FEATURES}"
+    return True, ""
+
+
+class KANLinear(nn.Module):
+    """
+    B-spline KAN layer ``y = base_activation(x) @ base_weight^T + B(x) @ (spline_weight * spline_scaler)^T``.
+
+    Parameters and defaults as in the reference (kan_linear.py:103-117).
+    ``backend``: "auto" (native kernels for CUDA inputs when the shape is
+    supported, else the dense PyTorch formulation), "cuda" (native only; raises
+    on unsupported shapes and CPU inputs) or "reference" (always dense PyTorch).
+    The native kernels fuse SiLU; any other base activation is evaluated with
+    PyTorch and only the spline branch runs natively.  ``create_graph=True``
+    is exact on every backend.
+    """
+
+    def __init__(self, in_features: int, out_features: int, grid_size: int = 5, spline_order: int = 3,
+                 scale_noise: float = 0.1, scale_base: float = 1.0, scale_spline: float = 1.0,
+                 enable_standalone_scale_spline: bool = True, base_activation=nn.SiLU, grid_eps: float = 0.02,
+                 grid_range: Tuple[float, float] = (-1.0, 1.0), backend: str = "auto") -> None:
+        super().__init__()
+        if grid_size < 1:
+            raise ValueError(f"grid_size must be >= 1, got {grid_size}")
+        if spline_order not in (1, 2, 3):
+            raise ValueError(f"spline_order must be 1, 2, or 3, got {spline_order}")
+        if backend not in ("auto", "cuda", "reference"):
+            raise ValueError(f"backend must be 'auto', 'cuda', or 'reference', got {backend!r}")
+        native_ok, why_not = native_config_supported(in_features, grid_size, spline_order)
+        if backend == "cuda":
+            if not native_ok:
+                raise ValueError(f"backend='cuda' does not support this configuration: {why_not}. "
+                                 "Use backend='reference' (or 'auto', which falls back automatically).")
+            self._use_cuda = True
+        elif backend == "reference":
+            self._use_cuda = False
+        else:
+            self._use_cuda = native_ok
+        self.backend = backend
+        self.last_backend: Optional[str] = None      # plain string: cannot keep a graph alive
+
+        # The dense layer owns parameters and buffers; they are aliased here so
+        # that state dicts carry both key sets, as the reference's do.
+        self._ref = ReferenceKANLayer(
+            in_features=in_features, out_features=out_features, grid_size=grid_size, spline_order=spline_order,
+            scale_noise=scale_noise, scale_base=scale_base, scale_spline=scale_spline,
+            enable_standalone_scale_spline=enable_standalone_scale_spline, base_activation=base_activation,
+            grid_eps=grid_eps, grid_range=grid_range)
+        self.base_weight = self._ref.base_weight
+        self.spline_weight = self._ref.spline_weight
+        if enable_standalone_scale_spline:
+            self.spline_scaler = self._ref.spline_scaler
+        self.register_buffer("grid", self._ref.grid)
+
+        self.in_features = in_features
+        self.out_features = out_features
+        self.grid_size = grid_size
+        self.spline_order = spline_order
+        self.enable_standalone_scale_spline = enable_standalone_scale_spline
+
+    # -- backend choice ----------------------------------------------------
+    @property
+    def selected_backend(self) -> str:
+        """Backend used for CUDA inputs: "cuda" or "reference"."""
+        return "cuda" if self._use_cuda else "reference"
+
+    def backend_for(self, x: torch.Tensor) -> str:
+        """Backend :meth:`forward` will use for ``x``."""
+        if not self._use_cuda:
+            return "reference"
+        if self.backend == "cuda" or x.is_cuda:
+            return "cuda"
+        return "reference"
+
+    @property
+    def _native_fuses_base(self) -> bool:
+        return type(self._ref.base_activation) is nn.SiLU
+
+    # -- forward -----------------------------------------------------------
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        which = self.backend_for(x)
+        self.last_backend = which
+        return self._cuda_forward(x) if which == "cuda" else self._ref(x)
+
+    def _cuda_forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("KANLinear with backend='cuda' received a CPU tensor. "
+                               "Move the input and model to a CUDA device, or use backend='reference'.")
+        lead = x.shape[:-1]
+        xf = x.reshape(-1, self.in_features)
+        absent = xf.new_empty(0)
+        has_scaler = self.enable_standalone_scale_spline
+        fuse_base = self._native_fuses_base
+        out = _C.kan_apply(xf, self.grid, self.base_weight if fuse_base else absent, self.spline_weight,
+                           self.spline_scaler if has_scaler else absent, self.spline_order, has_scaler)
+        if not fuse_base:
+            out = out + F.linear(self._ref.base_activation(xf), self.base_weight)
+        return out.reshape(lead + (self.out_features,))
+
+    # -- knots from data ---------------------------------------------------
+    def update_grid(self, x: torch.Tensor, margin: float = 0.01) -> None:
+        """Moves the knots to the distribution of ``x`` and refits ``spline_weight``
+        (see :meth:`ReferenceKANLayer.update_grid`)."""
+        self._ref.update_grid(x, margin=margin)
+        with torch.no_grad():
+            self.grid.copy_(self._ref.grid)
+
+    # -- regularisation ----------------------------------------------------
+    def regularization_loss(self, reg_act: float = 1.0, reg_entropy: float = 1.0, *,
+                            x: Optional[torch.Tensor] = None, mode: str = "activation",
+                            reg_impl: str = "auto", chunk_size: int = 1024) -> torch.Tensor:
+        """Scalar sparsity penalty (kan_linear.py:275-334).  ``mode="activation"`` needs ``x``;
+        ``reg_impl`` selects how mean|phi| is evaluated (see :meth:`forward_with_regularization`)."""
+        if mode not in ("activation", "coefficient"):
+            raise ValueError(f"mode must be 'activation' or 'coefficient', got {mode!r}")
+        if mode == "coefficient":
+            return self._ref.regularization_loss(regularize_activation=reg_act, regularize_entropy=reg_entropy,
+                                                 mode="coefficient")
+        if x is None:
+            return self._ref.regularization_loss(reg_act, reg_entropy, x=None)     # canonical error
+        xf = x.reshape(-1, self.in_features)
+        s = self._ref.base_activation(xf)
+        impl = self._resolve_reg_impl(reg_impl, xf)
+        H = self._basis(xf, impl)
+        a = self._edge_abs_mean(xf, s, H, self._ref.effective_spline_weight(), impl, chunk_size)
+        return regularization_from_edge_means(a, reg_act, reg_entropy)
+
+    def forward_with_regularization(self, x: torch.Tensor, reg_act: float = 1.0, reg_entropy: float = 1.0, *,
+                                    mode: str = "activation", reg_impl: str = "auto", chunk_size: int = 1024
+                                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``(self(x), self.regularization_loss(reg_act, reg_entropy, x=x))`` from one evaluation of the
+        base activation and the basis (kan_linear.py:340-389).
+
+        ``reg_impl``: "auto" ("fused" when the native kernels can run, else "dense"), "dense"
+        (phi [N,O,I] in PyTorch), "fused" (native kernel, phi never stored, recomputed in backward)
+        or "checkpoint" (chunked PyTorch with activation checkpointing).  All give the same value
+        and gradients up to rounding and keep the full graph to ``x`` and the parameters.
+        """
+        if mode == "coefficient":
+            return self(x), self.regularization_loss(reg_act, reg_entropy, mode="coefficient")
+        if mode != "activation":
+            raise ValueError(f"mode must be 'activation' or 'coefficient', got {mode!r}")
+        lead = x.shape[:-1]
+        xf = x.reshape(-1, self.in_features)
+        impl = self._resolve_reg_impl(reg_impl, xf)
+        s = self._ref.base_activation(xf)
+        H = self._basis(xf, impl)
+        W = self._ref.effective_spline_weight()
+        y = F.linear(s, self.base_weight) + F.linear(H.reshape(xf.shape[0], -1), W.reshape(self.out_features, -1))
+        self.last_backend = "cuda" if impl == "fused" else "reference"
+        a = self._edge_abs_mean(xf, s, H, W, impl, chunk_size)
+        return y.reshape(lead + (self.out_features,)), regularization_from_edge_means(a, reg_act, reg_entropy)
+
+    def _resolve_reg_impl(self, reg_impl: str, x_flat: torch.Tensor) -> str:
+        if reg_impl not in REG_IMPLS:
+            raise ValueError(f"reg_impl must be one of {REG_IMPLS}, got {reg_impl!r}")
+        native_ok = _fused.HAS_FUSED_KERNELS and x_flat.is_cuda and self.backend_for(x_flat) == "cuda"
+        if reg_impl == "auto":
+            return "fused" if native_ok else "dense"
+        if reg_impl == "fused" and not native_ok:
+            raise RuntimeError("reg_impl='fused' needs the native CUDA kernels, a CUDA input and a layer "
+                               "configuration supported by backend='cuda'.  Use reg_impl='dense' or "
+                               "'checkpoint' instead.")
+        return reg_impl
+
+    def _basis(self, x_flat: torch.Tensor, impl: str) -> torch.Tensor:
+        if impl == "fused":
+            return _fused.native_basis(x_flat, self.grid, self.spline_order)
+        return compute_basis(x_flat, self.grid, self.spline_order)
+
+    def _edge_abs_mean(self, x_flat, s, H, W, impl, chunk_size):
+        if impl == "fused":
+            return _fused.edge_abs_mean(s, H, self.base_weight, W)
+        if impl == "checkpoint":
+            if chunk_size < 1:
+                raise ValueError(f"chunk_size must be >= 1, got {chunk_size}")
+            return _fused.edge_abs_mean_chunked(s, x_flat, self.grid, self.spline_order, self.base_weight, W,
+                                                chunk_size)
+        return edge_abs_mean_dense(s, H, self.base_weight, W)
+
+    @torch.no_grad()
+    def edge_l1(self, x: torch.Tensor) -> torch.Tensor:
+        """Per-edge L1 norm ``mean_n |phi_{o,i}(x_n)|`` -> [O, I] (kan_linear.py:451-458)."""
+        xf = x.reshape(-1, self.in_features)
+        impl = self._resolve_reg_impl("auto", xf)
+        s = self._ref.base_activation(xf)
+        return self._edge_abs_mean(xf, s, self._basis(xf, impl), self._ref.effective_spline_weight(), impl, 1024)
+
+    # -- construction helpers ---------------------------------------------
+    def make_like(self, in_features: Optional[int] = None, out_features: Optional[int] = None,
+                  grid_size: Optional[int] = None,
+                  enable_standalone_scale_spline: Optional[bool] = None) -> "KANLinear":
+        """Freshly initialised layer with this layer's hyper-parameters, dtype and device, optionally
+        with another shape (kan_linear.py:424-449)."""
+        ref = self._ref
+        scaler = self.enable_standalone_scale_spline if enable_standalone_scale_spline is None \
+            else enable_standalone_scale_spline
+        twin = KANLinear(
+            self.in_features if in_features is None else in_features,
+            self.out_features if out_features is None else out_features,
+            grid_size=self.grid_size if grid_size is None else grid_size, spline_order=self.spline_order,
+            scale_noise=ref.scale_noise, scale_base=ref.scale_base, scale_spline=ref.scale_spline,
+            enable_standalone_scale_spline=scaler, base_activation=copy.deepcopy(ref.base_activation),
+            grid_eps=ref.grid_eps, grid_range=ref.grid_range, backend=self.backend)
+        return twin.to(device=self.grid.device, dtype=self.grid.dtype)
+
+    @torch.no_grad()
+    def _copy_grid_(self, grid: torch.Tensor) -> None:
+        # .to() / .double() re-create buffers per module: keep both copies equal.
+        self.grid.copy_(grid)
+        self._ref.grid.copy_(grid)
+
+    def export_inference(self, requires_grad: bool = False) -> "KANLinear":
+        """Independent layer computing the same function with ``spline_scaler`` folded into the
+        coefficients (``enable_standalone_scale_spline=False``); frozen and in eval mode unless
+        ``requires_grad`` (kan_linear.py:471-496)."""
+        out = self.make_like(enable_standalone_scale_spline=False)
+        with torch.no_grad():
+            out.base_weight.copy_(self.base_weight)
+            out.spline_weight.copy_(self._ref.effective_spline_weight())
+            out._copy_grid_(self.grid)
+        out.requires_grad_(requires_grad)
+        return out.train(self.training and requires_grad)
+
+    @torch.no_grad()
+    def extend_grid(self, new_grid_size: int, x: torch.Tensor, *, margin: float = 0.01,
+                    adapt_knots: bool = False, ridge: float = 1e-12, n_dense: int = 0) -> "KANLinear":
+        """NEW layer with ``new_grid_size`` intervals whose coefficients are the least-squares fit of
+        this layer's spline curves on ``x`` (plus ``n_dense`` uniform points); base weight, scaler
+        and activation are copied.  ``adapt_knots=False`` puts uniform knots over the interior
+        domain widened to the sample range, ``True`` uses the quantile/uniform mix of
+        :meth:`update_grid` (kan_linear.py:502-588)."""
+        if new_grid_size < 1:
+            raise ValueError(f"new_grid_size must be >= 1, got {new_grid_size}")
+        xf = x.reshape(-1, self.in_features).to(self.grid)
+        if xf.shape[0] < 2:
+            raise ValueError("extend_grid needs at least 2 samples")
+        k = self.spline_order
+        fine = self.make_like(grid_size=new_grid_size)
+        if adapt_knots:
+            knots = fine._ref.grid_from_samples(xf, new_grid_size, margin)
+        else:
+            lo0, hi0 = self.grid[:, k], self.grid[:, k + self.grid_size]
+            xmin, xmax = xf.amin(0), xf.amax(0)
+            lo = torch.maximum(torch.where(xmin < lo0, xmin - margin, lo0), self.grid[:, 0])
+            hi = torch.minimum(torch.where(xmax > hi0, xmax + margin, hi0), self.grid[:, -1])
+            steps = torch.arange(new_grid_size + 2 * k + 1, device=lo.device, dtype=lo.dtype) - k
+            knots = lo[:, None] + steps[None] * ((hi - lo) / new_grid_size)[:, None]
+        pts = xf
+        if n_dense > 0:
+            a, b = knots[:, k], knots[:, k + new_grid_size]
+            ramp = torch.linspace(0, 1, n_dense, device=a.device, dtype=a.dtype)
+            pts = torch.cat([xf, a[None] + ramp[:, None] * (b - a)[None]], 0)
+        curve = torch.einsum("oir,bir->obi", self.spline_weight, compute_basis(pts, self.grid, k))
+        fine.base_weight.copy_(self.base_weight)
+        fine.spline_weight.copy_(fit_spline_coeffs(pts, curve, knots, k, ridge=ridge))
+        if self.enable_standalone_scale_spline:
+            fine.spline_scaler.copy_(self.spline_scaler)
+        fine._copy_grid_(knots)
+        return fine.train(self.training)
