@@ -34,10 +34,13 @@ def _idesc(n, a_mn, b_mn):
 
 
 def _img_kmajor(M):
-    """[rows, 64] matrix -> K-major 128B-swizzled byte image (rows x 128 B)."""
-    rows = M.shape[0]
+    """[rows, 64] matrix -> K-major 128B-swizzled byte image (rows x 128 B), bf16."""
+    return _img_kmajor_bits(_bf16_bits(M))
+
+
+def _img_kmajor_bits(bits):
+    rows = bits.shape[0]
     img = np.zeros(rows * 64, dtype=np.uint16)
-    bits = _bf16_bits(M)
     for r in range(rows):
         for c in range(8):
             off = (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)

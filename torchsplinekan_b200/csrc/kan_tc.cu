@@ -6,6 +6,10 @@
 // layout the MMA unit reads.  fp32 accuracy is kept on 16-bit tensor-core
 // inputs by splitting every operand value v into hi = bf16(v) and
 // lo = bf16(v - hi) and issuing three MMAs per step (hi*hi + lo*hi + hi*lo).
+// The tensor-core accumulator truncates on every accumulation, so a long
+// reduction is cut into chunks: after a bounded number of k-blocks the TMEM
+// accumulator is drained and added, in fp32 with round-to-nearest, to the
+// running result in global memory (which stays in L2).
 //
 // Column space ("c") of the generated operand, shared by all kernels:
 //   spline part : c = i * 8 + r            (R <= 8, slots r >= R are zero)
@@ -16,11 +20,15 @@
 //   pack_grad_out_kernel   dY                  -> bf16 hi/lo tile images
 //   tc_forward_kernel      y   = A(x) W^T           M = samples,  K = c
 //   tc_bwd_param_kernel    D   = dY^T A(x)          M = outputs,  K = samples
-// All are persistent, warp-specialised (bulk-copy thread, MMA thread, operand
-// producer warps, epilogue warps) and every wait is bounded.
+// Both contraction kernels are persistent and warp-specialised: 16 worker warps
+// (they evaluate the generated operand and, between chunks, drain the
+// accumulator), one MMA-issuing thread and one bulk-copy thread.  Every wait is
+// bounded.
 #include "kan_device.cuh"
 #include "kan_internal.h"
 #include "kan_tc_ptx.cuh"
+
+#include <cstdlib>
 
 namespace kanb200 {
 
@@ -41,96 +49,138 @@ constexpr uint32_t TILE_A_BYTES = BLOCK_M * BLOCK_K * 2;   // 16 KB: 128 x 64 bf
 constexpr uint32_t TILE_B_BYTES = BLOCK_N * BLOCK_K * 2;   // 32 KB: 256 x 64 bf16
 
 // ---------------------------------------------------------------------------
-// Local basis with approximate reciprocals (2 ulp) for the operand producers.
+// Per-span polynomial table.
+//
+// On a knot span [t_m, t_{m+1}) each of the k+1 non-zero basis functions is a
+// polynomial of degree k in u = x - t_m.  A small kernel expands the de Boor
+// recurrence symbolically (in double) once per call and stores, per feature,
+//   floats [0, 12)   : knots t_0 .. t_{T-2} (padded with +inf), slot 11 = t_{T-1}
+//   floats [16 + 20 e, 16 + 20 e + 20), e = 0 .. 11 : entry of span e
+//       16 coefficients c[j][p] (function j of the window, power p of u),
+//       t_m, the window start s = m - k (as int bits), 2 unused;
+//       coefficients of window slots outside [0, R) are zero, and entry 11 is
+//       all zero -- it is the one inputs outside the knot range select.
+// The operand producers then need one compare-and-count for the span, five
+// 16-byte loads and a Horner evaluation per input; the same code serves uniform
+// and non-uniform knots.  Conventions (half-open spans, last span closed,
+// zero-length spans contribute zero) are those of the dense recurrence.
 // ---------------------------------------------------------------------------
-template <int K>
-__device__ __forceinline__ void local_basis_fast(const float* __restrict__ t, int nk, int m, float x,
-                                                 float (&val)[K + 1]) {
-    float tk[2 * K];
-#pragma unroll
-    for (int q = 0; q < 2 * K; ++q) {
-        int idx = m - K + 1 + q;
-        idx = idx < 0 ? 0 : (idx > nk - 1 ? nk - 1 : idx);
-        tk[q] = t[idx];
-    }
-    float nd[K + 1];
-    nd[0] = 1.0f;
-#pragma unroll
-    for (int j = 1; j <= K; ++j) nd[j] = 0.0f;
-#pragma unroll
-    for (int d = 1; d <= K; ++d) {
-        float carry = 0.0f;
-#pragma unroll
-        for (int j = 0; j < d; ++j) {
-            const float hi_k = tk[K + j], lo_k = tk[K - d + j];
-            const float den = hi_k - lo_k;
-            const float w = (den != 0.0f) ? __fdividef(nd[j], den) : 0.0f;
-            nd[j] = fmaf(hi_k - x, w, carry);
-            carry = (x - lo_k) * w;
-        }
-        nd[d] = carry;
-    }
-#pragma unroll
-    for (int j = 0; j <= K; ++j) val[j] = nd[j];
-}
+constexpr int TAB_FEATURE_FLOATS = 256;       // 1 KB per feature
+constexpr int TAB_ENTRY_FLOATS = 20;
+constexpr int TAB_ENTRIES = 12;
+constexpr int TAB_ZERO_ENTRY = 11;
 
-// Span of x among nk <= 12 sorted knots: compare-and-count (knot reads are
-// warp-uniform or conflict-free shared-memory reads).
-__device__ __forceinline__ int span_by_count(const float* __restrict__ t, int nk, float x) {
-    if (!(x >= t[0]) || !(x <= t[nk - 1])) return -1;
-    int c = 0;
-#pragma unroll
-    for (int q = 1; q <= 10; ++q)
-        if (q < nk - 1) c += (x >= t[q]) ? 1 : 0;
-    return c;
+__global__ void build_poly_table_kernel(const float* __restrict__ grid, float* __restrict__ tab,
+                                        int I, int G, int K) {
+    const int nk = G + 2 * K + 1, R = G + K;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= I * (TAB_ENTRIES + 1)) return;
+    const int f = idx / (TAB_ENTRIES + 1), e = idx - f * (TAB_ENTRIES + 1);
+    const float* t = grid + (size_t)f * nk;
+    float* out = tab + (size_t)f * TAB_FEATURE_FLOATS;
+    if (e == TAB_ENTRIES) {                    // knot block
+        for (int q = 0; q < 11; ++q) out[q] = (q <= nk - 2) ? t[q] : __int_as_float(0x7f800000);
+        out[11] = t[nk - 1];
+        for (int q = 12; q < 16; ++q) out[q] = 0.0f;
+        return;
+    }
+    float* ent = out + 16 + e * TAB_ENTRY_FLOATS;
+    double c[4][4];
+    for (int j = 0; j < 4; ++j)
+        for (int p = 0; p < 4; ++p) c[j][p] = 0.0;
+    const int m = e;
+    float tm = 0.0f;
+    int s = 0;
+    if (m <= nk - 2 && e != TAB_ZERO_ENTRY) {
+        auto knot = [&](int i) -> double { return (double)t[i < 0 ? 0 : (i > nk - 1 ? nk - 1 : i)]; };
+        tm = t[m];
+        s = m - K;
+        c[0][0] = 1.0;
+        for (int d = 1; d <= K; ++d) {
+            double carry[4] = {0.0, 0.0, 0.0, 0.0};
+            for (int j = 0; j < d; ++j) {
+                const double hi_k = knot(m + j + 1), lo_k = knot(m + 1 - d + j);
+                const double den = hi_k - lo_k;
+                double w[4];
+                for (int p = 0; p < 4; ++p) w[p] = (den != 0.0) ? c[j][p] / den : 0.0;
+                // (hi_k - x) w = ((hi_k - t_m) - u) w ;  (x - lo_k) w = (u + (t_m - lo_k)) w
+                const double a = hi_k - (double)tm, b = (double)tm - lo_k;
+                double left[4], right[4];
+                for (int p = 0; p < 4; ++p) {
+                    const double wm1 = (p > 0) ? w[p - 1] : 0.0;
+                    left[p] = a * w[p] - wm1;
+                    right[p] = b * w[p] + wm1;
+                }
+                for (int p = 0; p < 4; ++p) {
+                    c[j][p] = carry[p] + left[p];
+                    carry[p] = right[p];
+                }
+            }
+            for (int p = 0; p < 4; ++p) c[d][p] = carry[p];
+        }
+        for (int j = 0; j < 4; ++j) {
+            const int r = s + j;
+            if (j > K || r < 0 || r >= R)
+                for (int p = 0; p < 4; ++p) c[j][p] = 0.0;
+        }
+    }
+    for (int j = 0; j < 4; ++j)
+        for (int p = 0; p < 4; ++p) ent[j * 4 + p] = (float)c[j][p];
+    ent[16] = tm;
+    ent[17] = __int_as_float(s);
+    ent[18] = 0.0f;
+    ent[19] = 0.0f;
 }
 
 __device__ __forceinline__ float silu_fast(float x) {
     return __fdividef(x, 1.0f + __expf(-x));
 }
 
-// Evaluates the basis of one input and returns the 8 column slots of its
-// feature as two 128-bit rows (hi and lo bf16 parts).  SPLIT = false leaves lo
-// untouched.
-template <int K, bool SPLIT>
-__device__ __forceinline__ void eval_feature_row(const float* __restrict__ t, int nk, int R, float xv,
-                                                 uint4& hi, uint4& lo) {
-    const int m = span_by_count(t, nk, xv);
-    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    int s = 0;
-    if (m >= 0) {
-        float w[K + 1];
-        local_basis_fast<K>(t, nk, m, xv, w);
-        s = m - K;
-#pragma unroll
-        for (int j = 0; j <= K; ++j) {
-            const int r = s + j;
-            v[j] = (r >= 0 && r < R) ? w[j] : 0.0f;
-        }
-    }
+// Evaluates the basis of one input from its feature's table and returns the 8
+// column slots of the feature as two 128-bit rows (hi and lo bf16 parts).
+// Branch-free.  SPLIT = false leaves lo untouched.
+template <bool SPLIT>
+__device__ __forceinline__ void eval_feature_row(const float* __restrict__ ftab, float xv, uint4& hi, uint4& lo) {
+    const float4 k0 = __ldg(reinterpret_cast<const float4*>(ftab));
+    const float4 k1 = __ldg(reinterpret_cast<const float4*>(ftab) + 1);
+    const float4 k2 = __ldg(reinterpret_cast<const float4*>(ftab) + 2);
+    const bool inside = (xv >= k0.x) && (xv <= k2.w);
+    int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
+            (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
+    m = inside ? m : TAB_ZERO_ENTRY;
+    const float4* ent = reinterpret_cast<const float4*>(ftab + 16 + m * TAB_ENTRY_FLOATS);
+    const float4 c0 = __ldg(ent), c1 = __ldg(ent + 1), c2 = __ldg(ent + 2), c3 = __ldg(ent + 3), meta = __ldg(ent + 4);
+    const float u = xv - meta.x;
+    const int s = __float_as_int(meta.y);
+    const float v0 = fmaf(fmaf(fmaf(c0.w, u, c0.z), u, c0.y), u, c0.x);
+    const float v1 = fmaf(fmaf(fmaf(c1.w, u, c1.z), u, c1.y), u, c1.x);
+    const float v2 = fmaf(fmaf(fmaf(c2.w, u, c2.z), u, c2.y), u, c2.x);
+    const float v3 = fmaf(fmaf(fmaf(c3.w, u, c3.z), u, c3.y), u, c3.x);
     uint32_t h01, h23, l01 = 0, l23 = 0;
     if (SPLIT) {
-        split2(v[0], v[1], h01, l01);
-        split2(v[2], v[3], h23, l23);
+        split2(v0, v1, h01, l01);
+        split2(v2, v3, h23, l23);
     } else {
-        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
-        const __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v0, v1);
+        const __nv_bfloat162 b = __floats2bfloat162_rn(v2, v3);
         h01 = *reinterpret_cast<const uint32_t*>(&a);
         h23 = *reinterpret_cast<const uint32_t*>(&b);
     }
-    // Place the 4 half-words at half-word offset s (in [-3, 7]) of a 128-bit row.
+    // Place the 4 half-words at half-word offset s (in [-3, 7]) of the 8-slot row.  With
+    // s = 2 q + odd the payload becomes three words (t0, t1, t2) that start at word q.
+    const int odd = s & 1;
+    const int q = (s - odd) >> 1;                          // -2 .. 3
+    const bool at0 = (q == 0), at1 = (q == 1), at2 = (q == 2), at3 = (q == 3), atm1 = (q == -1), atm2 = (q == -2);
     auto place = [&](uint32_t w01, uint32_t w23) -> uint4 {
-        const uint64_t p = (uint64_t)w01 | ((uint64_t)w23 << 32);
-        uint64_t lo64, hi64;
-        if (s >= 0) {
-            const int nb = 16 * s;
-            lo64 = (nb < 64) ? (p << nb) : 0ull;
-            hi64 = (nb == 0) ? 0ull : ((nb < 64) ? (p >> (64 - nb)) : (p << (nb - 64)));
-        } else {
-            lo64 = p >> (-16 * s);
-            hi64 = 0ull;
-        }
-        return make_uint4((uint32_t)lo64, (uint32_t)(lo64 >> 32), (uint32_t)hi64, (uint32_t)(hi64 >> 32));
+        const uint32_t t0 = odd ? (w01 << 16) : w01;
+        const uint32_t t1 = odd ? __funnelshift_r(w01, w23, 16) : w23;
+        const uint32_t t2 = odd ? (w23 >> 16) : 0u;
+        uint4 o;
+        o.x = at0 ? t0 : (atm1 ? t1 : (atm2 ? t2 : 0u));
+        o.y = at1 ? t0 : (at0 ? t1 : (atm1 ? t2 : 0u));
+        o.z = at2 ? t0 : (at1 ? t1 : (at0 ? t2 : 0u));
+        o.w = at3 ? t0 : (at2 ? t1 : (at1 ? t2 : 0u));
+        return o;
     };
     hi = place(h01, h23);
     if (SPLIT) lo = place(l01, l23);
@@ -283,43 +333,82 @@ __global__ void pack_grad_out_kernel(const float* __restrict__ dY, uint8_t* __re
 }
 
 // ---------------------------------------------------------------------------
-// Forward kernel
+// Common geometry of the two contraction kernels
 // ---------------------------------------------------------------------------
-constexpr int FWD_EPI_WARPS = 4, FWD_PROD_WARPS = 8;
-constexpr int FWD_THREADS = (FWD_EPI_WARPS + FWD_PROD_WARPS + 2) * 32;   // 448
+constexpr int WORKER_WARPS = 16;                       // operand producers + accumulator drain
+constexpr int WORKER_THREADS = WORKER_WARPS * 32;
+constexpr int TC_THREADS = (WORKER_WARPS + 2) * 32;    // + MMA warp + bulk-copy warp
+constexpr int MMA_WARP = WORKER_WARPS;              // warp MMA_WARP + 1 issues the bulk copies
+
+// Adds (or, for the first chunk, stores) 32 accumulator columns of one row.
+__device__ __forceinline__ void drain_row32(float* __restrict__ dst, const uint32_t (&r)[32], bool first,
+                                            int valid, bool vec) {
+    if (vec && valid >= 32) {
+        float4* d4 = reinterpret_cast<float4*>(dst);
+        if (first) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                d4[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                    __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        } else {
+            float4 old[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) old[q] = d4[q];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                d4[q] = make_float4(old[q].x + __uint_as_float(r[4 * q]), old[q].y + __uint_as_float(r[4 * q + 1]),
+                                    old[q].z + __uint_as_float(r[4 * q + 2]), old[q].w + __uint_as_float(r[4 * q + 3]));
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 32; ++q)
+            if (q < valid) dst[q] = first ? __uint_as_float(r[q]) : dst[q] + __uint_as_float(r[q]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Forward kernel:  y[n, o] = sum_c A[n, c] W[o, c]
+// ---------------------------------------------------------------------------
+// Tile = 128 samples x up to 512 outputs (one or two 256-wide sub-tiles sharing
+// the generated A tile; all 512 TMEM columns).  A stage = 128 x 64 bf16 hi + lo.
 constexpr int FWD_A_STAGES = 2, FWD_B_SLOTS = 5;
 constexpr uint32_t FWD_A_STAGE_BYTES = 2 * TILE_A_BYTES;                  // hi + lo
 constexpr uint32_t FWD_SMEM_A = 0;
 constexpr uint32_t FWD_SMEM_B = FWD_SMEM_A + FWD_A_STAGES * FWD_A_STAGE_BYTES;
 constexpr uint32_t FWD_SMEM_CTRL = FWD_SMEM_B + FWD_B_SLOTS * TILE_B_BYTES;
-constexpr uint32_t FWD_KNOT_FLOATS = 4 * 12;                              // per producer warp
-constexpr uint32_t FWD_CTRL_BYTES = 256 + FWD_PROD_WARPS * FWD_KNOT_FLOATS * 4;
+constexpr uint32_t FWD_CTRL_BYTES = 256;
 constexpr uint32_t FWD_SMEM_BYTES = FWD_SMEM_CTRL + FWD_CTRL_BYTES;
 static_assert(FWD_SMEM_BYTES <= 232448, "forward kernel shared memory exceeds 227 KB");
 
 struct FwdCtrl {
     uint64_t fullA[FWD_A_STAGES], emptyA[FWD_A_STAGES];
     uint64_t fullB[FWD_B_SLOTS], emptyB[FWD_B_SLOTS];
-    uint64_t accFull[2], accEmpty[2];
+    uint64_t chunkFull, drained;
     uint32_t tmem_base;
     int abort_flag;
 };
 static_assert(sizeof(FwdCtrl) <= 256, "control block too large");
 
-template <int K, int NTERMS>
-__global__ void __launch_bounds__(FWD_THREADS, 1)
-tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ grid, const uint8_t* __restrict__ wimg,
-                  float* __restrict__ y, int* __restrict__ status,
-                  int64_t N, int I, int O, int G, int kb_spline, int kb_total,
-                  int n_otiles, int64_t n_tiles, int vec_ok) {
+struct FwdParams {
+    int64_t N;
+    int I, O, G;
+    int kb_spline, kb_total;
+    int n_otiles, n_opairs;
+    int64_t n_tiles;
+    int chunk_kb;          // k-blocks accumulated in TMEM between drains
+    int vec_x, vec_x2, vec_y;
+};
+
+template <int NTERMS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
+                  float* __restrict__ y, int* __restrict__ status, const FwdParams P) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr bool SPLIT = (NTERMS == 3);
     const uint32_t sbase = smem_u32(smem);
     FwdCtrl* ctrl = reinterpret_cast<FwdCtrl*>(smem + FWD_SMEM_CTRL);
-    float* knot_stage = reinterpret_cast<float*>(smem + FWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int R = G + K, nk = G + 2 * K + 1;
 
     if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
@@ -327,21 +416,18 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ grid, c
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < FWD_A_STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->fullA[s]), FWD_PROD_WARPS * 32);
+            mbar_init(smem_u32(&ctrl->fullA[s]), WORKER_THREADS);
             mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
         }
         for (int s = 0; s < FWD_B_SLOTS; ++s) {
             mbar_init(smem_u32(&ctrl->fullB[s]), 1);
             mbar_init(smem_u32(&ctrl->emptyB[s]), 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&ctrl->accFull[s]), 1);
-            mbar_init(smem_u32(&ctrl->accEmpty[s]), FWD_EPI_WARPS * 32);
-        }
+        mbar_init(smem_u32(&ctrl->chunkFull), 1);
+        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
-    constexpr int MMA_WARP = FWD_EPI_WARPS + FWD_PROD_WARPS, TMA_WARP = MMA_WARP + 1;
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
         tmem_relinquish();
@@ -351,174 +437,197 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ grid, c
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    if (warp < FWD_EPI_WARPS) {
-        // ===== epilogue: TMEM -> registers -> y =====
-        const int row = warp * 32 + lane;
-        uint32_t tcount = 0;
-        for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
-            const int64_t mt = tile / n_otiles;
-            const int ot = (int)(tile - mt * n_otiles);
-            const uint32_t buf = tcount & 1u;
-            if (!mbar_wait(smem_u32(&ctrl->accFull[buf]), (tcount >> 1) & 1u, abort_flag)) break;
+    if (warp < WORKER_WARPS) {
+        // ===== workers: x -> basis / silu -> swizzled A tile; drain between chunks =====
+        const int quad = warp & 3;                        // TMEM lane quadrant = row group
+        const int part = warp >> 2;                       // which quarter of the k-block / column groups
+        const int row = quad * 32 + lane;
+        uint32_t it = 0, n_drained = 0;
+        bool ok = true;
+        // drain bookkeeping: the chunk that ended most recently and is not yet added to y
+        bool pend = false, pend_first = false;
+        int64_t pend_mt = 0;
+        int pend_op = 0;
+
+        auto drain = [&]() -> bool {
+            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
+            ++n_drained;
             tc_fence_after_sync();
-            const int64_t n = mt * BLOCK_M + row;
-            float* yrow = y + (size_t)n * O + (size_t)ot * BLOCK_N;
-            const int ocount = O - ot * BLOCK_N;           // valid columns in this tile (may exceed 256)
-            const bool vec_store = ((O & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+            const int64_t n = pend_mt * BLOCK_M + row;
+            const int nsub = (P.n_otiles - 2 * pend_op) >= 2 ? 2 : 1;
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
+            for (int c = part; c < nsub * (BLOCK_N / 32); c += 4) {
                 uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BLOCK_N + c * 32, r);
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, r);
                 tmem_ld_wait();
-                if (n < N) {
-                    const int c0 = c * 32;
-                    if (vec_store && c0 + 32 <= ocount) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            *reinterpret_cast<float4*>(yrow + c0 + 4 * q) =
-                                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                    } else {
-#pragma unroll
-                        for (int q = 0; q < 32; ++q)
-                            if (c0 + q < ocount) yrow[c0 + q] = __uint_as_float(r[q]);
-                    }
-                }
+                const int col0 = pend_op * 2 * BLOCK_N + c * 32;
+                if (n < P.N && col0 < P.O)
+                    drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
             }
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->accEmpty[buf]));
-        }
-    } else if (warp < FWD_EPI_WARPS + FWD_PROD_WARPS) {
-        // ===== operand producers: x -> basis / silu -> swizzled bf16 A tile =====
-        const int pw = warp - FWD_EPI_WARPS;
-        const int row = (pw & 3) * 32 + lane;
-        const int half = pw >> 2;                         // which half of the k-block's chunks
-        float* kn = knot_stage + pw * FWD_KNOT_FLOATS;    // this warp's knots of 4 features
-        uint32_t it = 0;
-        bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-            const int64_t mt = tile / n_otiles;
+            mbar_arrive(smem_u32(&ctrl->drained));
+            pend = false;
+            return true;
+        };
+
+        for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+            const int64_t mt = tile / P.n_opairs;
+            const int op = (int)(tile - mt * P.n_opairs);
             const int64_t n = mt * BLOCK_M + row;
-            const bool row_ok = n < N;
-            for (int kb = 0; kb < kb_total; ++kb, ++it) {
+            const bool row_ok = n < P.N;
+            const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
+            // software prefetch: the inputs of the next k-block are loaded one iteration ahead
+            float nx0 = 0.f, nx1 = 0.f;
+            auto prefetch_spline = [&](int kb) {
+                const int f0 = kb * 8 + part * 2;
+                if (P.vec_x2 && row_ok && f0 + 1 < P.I) {
+                    const float2 v = __ldg(reinterpret_cast<const float2*>(xrow + f0));
+                    nx0 = v.x;
+                    nx1 = v.y;
+                } else {
+                    nx0 = (row_ok && f0 < P.I) ? __ldg(xrow + f0) : 0.f;
+                    nx1 = (row_ok && f0 + 1 < P.I) ? __ldg(xrow + f0 + 1) : 0.f;
+                }
+            };
+            if (P.kb_spline > 0) prefetch_spline(0);
+            for (int kb = 0; kb < P.kb_total; ++kb, ++it) {
                 const uint32_t stage = it % FWD_A_STAGES;
                 const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                 const uint32_t a_lo = a_hi + TILE_A_BYTES;
-                if (kb < kb_spline) {
-                    const int f0 = kb * 8 + half * 4;
-                    float xv[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (row_ok && f0 < I) {
-                        const float* p = x + (size_t)n * I + f0;
-                        if (vec_ok && f0 + 4 <= I) {
-                            const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-                            xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (f0 + e < I) xv[e] = __ldg(p + e);
-                        }
-                    }
-                    __syncwarp();
-                    for (int e = lane; e < 4 * nk; e += 32) {
-                        const int f = f0 + e / nk;
-                        kn[e] = (f < I) ? __ldg(grid + (size_t)f0 * nk + e) : 0.0f;
-                    }
-                    __syncwarp();
+                const bool chunk_start = (kb % P.chunk_kb) == 0;
+                if (kb < P.kb_spline) {
+                    const int f0 = kb * 8 + part * 2;
+                    const float x0 = nx0, x1 = nx1;
+                    if (kb + 1 < P.kb_spline) prefetch_spline(kb + 1);
+                    const bool ok0 = row_ok && f0 < P.I, ok1 = row_ok && f0 + 1 < P.I;
+                    // features beyond I read the last feature's table; their rows are zeroed below
+                    const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * TAB_FEATURE_FLOATS;
+                    const float* t1 = tab + (size_t)(f0 + 1 < P.I ? f0 + 1 : P.I - 1) * TAB_FEATURE_FLOATS;
+                    uint4 hi0, lo0, hi1, lo1;
+                    eval_feature_row<SPLIT>(t0, x0, hi0, lo0);
+                    eval_feature_row<SPLIT>(t1, x1, hi1, lo1);
                     if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / FWD_A_STAGES) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        uint4 hi, lo;
-                        if (row_ok && f0 + e < I) {
-                            eval_feature_row<K, SPLIT>(kn + e * nk, nk, R, xv[e], hi, lo);
-                        } else {
-                            hi = make_uint4(0, 0, 0, 0);
-                            lo = hi;
-                        }
-                        const uint32_t off = sw128_chunk_offset((uint32_t)row, (uint32_t)(half * 4 + e));
-                        st_shared_v4(a_hi + off, hi);
-                        if (SPLIT) st_shared_v4(a_lo + off, lo);
+                    const uint4 zero = make_uint4(0, 0, 0, 0);
+                    const uint32_t off0 = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2));
+                    const uint32_t off1 = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2 + 1));
+                    st_shared_v4(a_hi + off0, ok0 ? hi0 : zero);
+                    st_shared_v4(a_hi + off1, ok1 ? hi1 : zero);
+                    if (SPLIT) {
+                        st_shared_v4(a_lo + off0, ok0 ? lo0 : zero);
+                        st_shared_v4(a_lo + off1, ok1 ? lo1 : zero);
                     }
                 } else {
-                    const int f0 = (kb - kb_spline) * 64 + half * 32;
-                    float xv[4][8];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) load_x8(x, n, row_ok, I, f0 + c * 8, vec_ok != 0, xv[c]);
+                    const int f0 = (kb - P.kb_spline) * 64 + part * 16;
+                    float xv[2][8];
+                    load_x8(x, n, row_ok, P.I, f0, P.vec_x != 0, xv[0]);
+                    load_x8(x, n, row_ok, P.I, f0 + 8, P.vec_x != 0, xv[1]);
                     if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / FWD_A_STAGES) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint4 hi, lo;
                         silu_chunk<SPLIT>(xv[c], hi, lo);
-                        const uint32_t off = sw128_chunk_offset((uint32_t)row, (uint32_t)(half * 4 + c));
+                        const uint32_t off = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2 + c));
                         st_shared_v4(a_hi + off, hi);
                         if (SPLIT) st_shared_v4(a_lo + off, lo);
                     }
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(smem_u32(&ctrl->fullA[stage]));
+                // The previous chunk is drained only after the first k-block of the next one has
+                // been produced, so the MMA pipe restarts without waiting for the producers.
+                if (pend && chunk_start) {
+                    if (!drain()) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                    pend = true;
+                    pend_first = kb < P.chunk_kb;
+                    pend_mt = mt;
+                    pend_op = op;
+                }
             }
         }
+        if (ok && pend) drain();
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
             // ===== MMA issue =====
             constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, false, false);
             constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
-            uint32_t it = 0, bslot = 0, tcount = 0;
+            uint32_t it = 0, bslot = 0, n_chunks = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
-                const uint32_t buf = tcount & 1u;
-                if (!mbar_wait(smem_u32(&ctrl->accEmpty[buf]), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) break;
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+                const int64_t mt = tile / P.n_opairs;
+                const int op = (int)(tile - mt * P.n_opairs);
+                const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
+                for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
                     const uint32_t stage = it % FWD_A_STAGES;
                     const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                     const uint32_t a_lo = a_hi + TILE_A_BYTES;
-                    const uint32_t slot_h = bslot % FWD_B_SLOTS;
-                    const uint32_t par_h = (bslot / FWD_B_SLOTS) & 1u;
-                    if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FWD_A_STAGES) & 1u, abort_flag) ||
-                        !mbar_wait(smem_u32(&ctrl->fullB[slot_h]), par_h, abort_flag)) {
+                    const bool chunk_start = (kb % P.chunk_kb) == 0;
+                    if (chunk_start && n_chunks > 0) {
+                        // the accumulator may be overwritten only after the workers have drained it
+                        if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FWD_A_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t b_hi = sbase + FWD_SMEM_B + slot_h * TILE_B_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                        mma_f16_ss(d_tmem, sdesc_at(dbase, a_hi + ks * 32), sdesc_at(dbase, b_hi + ks * 32), idesc,
-                                   (kb > 0 || ks > 0) ? 1u : 0u);
-                    if (SPLIT) {
-#pragma unroll
-                        for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                            mma_f16_ss(d_tmem, sdesc_at(dbase, a_lo + ks * 32), sdesc_at(dbase, b_hi + ks * 32),
-                                       idesc, 1u);
-                    }
-                    mma_commit(smem_u32(&ctrl->emptyB[slot_h]));
-                    ++bslot;
-                    if (SPLIT) {
-                        const uint32_t slot_l = bslot % FWD_B_SLOTS;
-                        const uint32_t par_l = (bslot / FWD_B_SLOTS) & 1u;
-                        if (!mbar_wait(smem_u32(&ctrl->fullB[slot_l]), par_l, abort_flag)) {
+                    for (int j = 0; j < nsub && ok; ++j) {
+                        const uint32_t d_tmem = tmem_base + j * BLOCK_N;
+                        const uint32_t slot_h = bslot % FWD_B_SLOTS;
+                        if (!mbar_wait(smem_u32(&ctrl->fullB[slot_h]), (bslot / FWD_B_SLOTS) & 1u, abort_flag)) {
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t b_lo = sbase + FWD_SMEM_B + slot_l * TILE_B_BYTES;
+                        const uint32_t b_hi = sbase + FWD_SMEM_B + slot_h * TILE_B_BYTES;
 #pragma unroll
                         for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                            mma_f16_ss(d_tmem, sdesc_at(dbase, a_hi + ks * 32), sdesc_at(dbase, b_lo + ks * 32),
-                                       idesc, 1u);
-                        mma_commit(smem_u32(&ctrl->emptyB[slot_l]));
+                            mma_f16_ss(d_tmem, sdesc_at(dbase, a_hi + ks * 32), sdesc_at(dbase, b_hi + ks * 32),
+                                       idesc, (!chunk_start || ks > 0) ? 1u : 0u);
+                        if (SPLIT) {
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ss(d_tmem, sdesc_at(dbase, a_lo + ks * 32), sdesc_at(dbase, b_hi + ks * 32),
+                                           idesc, 1u);
+                        }
+                        mma_commit(smem_u32(&ctrl->emptyB[slot_h]));
                         ++bslot;
+                        if (SPLIT) {
+                            const uint32_t slot_l = bslot % FWD_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->fullB[slot_l]), (bslot / FWD_B_SLOTS) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t b_lo = sbase + FWD_SMEM_B + slot_l * TILE_B_BYTES;
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ss(d_tmem, sdesc_at(dbase, a_hi + ks * 32), sdesc_at(dbase, b_lo + ks * 32),
+                                           idesc, 1u);
+                            mma_commit(smem_u32(&ctrl->emptyB[slot_l]));
+                            ++bslot;
+                        }
                     }
+                    if (!ok) break;
                     mma_commit(smem_u32(&ctrl->emptyA[stage]));
+                    if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                        mma_commit(smem_u32(&ctrl->chunkFull));
+                        ++n_chunks;
+                    }
                 }
-                if (ok) mma_commit(smem_u32(&ctrl->accFull[buf]));
             }
         }
     } else {
@@ -526,21 +635,25 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ grid, c
             // ===== bulk-copy producer for weight tiles =====
             uint32_t bslot = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                const int64_t mt = tile / n_otiles;
-                const int ot = (int)(tile - mt * n_otiles);
-                for (int kb = 0; kb < kb_total && ok; ++kb) {
-                    const uint8_t* src = wimg + ((size_t)ot * kb_total + kb) * (2 * (size_t)TILE_B_BYTES);
-                    for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
-                        const uint32_t slot = bslot % FWD_B_SLOTS;
-                        if (!mbar_wait(smem_u32(&ctrl->emptyB[slot]), ((bslot / FWD_B_SLOTS) & 1u) ^ 1u, abort_flag)) {
-                            ok = false;
-                            break;
+            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+                const int64_t mt = tile / P.n_opairs;
+                const int op = (int)(tile - mt * P.n_opairs);
+                const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
+                for (int kb = 0; kb < P.kb_total && ok; ++kb) {
+                    for (int j = 0; j < nsub && ok; ++j) {
+                        const uint8_t* src = wimg + ((size_t)(2 * op + j) * P.kb_total + kb) * (2 * (size_t)TILE_B_BYTES);
+                        for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
+                            const uint32_t slot = bslot % FWD_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->emptyB[slot]), ((bslot / FWD_B_SLOTS) & 1u) ^ 1u,
+                                           abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
+                            mbar_arrive_expect_tx(bar, TILE_B_BYTES);
+                            bulk_g2s(sbase + FWD_SMEM_B + slot * TILE_B_BYTES, src + (size_t)term * TILE_B_BYTES,
+                                     TILE_B_BYTES, bar);
                         }
-                        const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
-                        mbar_arrive_expect_tx(bar, TILE_B_BYTES);
-                        bulk_g2s(sbase + FWD_SMEM_B + slot * TILE_B_BYTES, src + (size_t)term * TILE_B_BYTES,
-                                 TILE_B_BYTES, bar);
                     }
                 }
             }
@@ -567,25 +680,22 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ grid, c
 // Work item = (output tile of 256, column tile of 256, sample split).  The
 // accumulator is two 128-row halves (all 512 TMEM columns).  Both operands are
 // MN-major: dY tiles come in as pre-swizzled images by bulk copy, the basis /
-// silu operand is generated by the producer warps.
-constexpr int BWD_EPI_WARPS = 4, BWD_PROD_WARPS = 8;
-constexpr int BWD_THREADS = (BWD_EPI_WARPS + BWD_PROD_WARPS + 2) * 32;
+// silu operand is generated by the worker warps.  Every `chunk_kb` blocks of 64
+// samples the accumulator is drained into the item's slab of partial sums.
 constexpr int BWD_G_STAGES = 2, BWD_D_SLOTS = 3;
 constexpr uint32_t BWD_G_STAGE_BYTES = 2 * TILE_B_BYTES;                 // hi + lo, 256 c x 64 n
 constexpr uint32_t BWD_D_SLOT_BYTES = 2 * TILE_A_BYTES;                  // hi + lo, 128 o x 64 n
 constexpr uint32_t BWD_SMEM_G = 0;
 constexpr uint32_t BWD_SMEM_D = BWD_SMEM_G + BWD_G_STAGES * BWD_G_STAGE_BYTES;
 constexpr uint32_t BWD_SMEM_CTRL = BWD_SMEM_D + BWD_D_SLOTS * BWD_D_SLOT_BYTES;
-constexpr uint32_t BWD_KNOT_STRIDE = 13;
-constexpr uint32_t BWD_CTRL_BYTES = 256 + 32 * BWD_KNOT_STRIDE * 4;
+constexpr uint32_t BWD_CTRL_BYTES = 256;
 constexpr uint32_t BWD_SMEM_BYTES = BWD_SMEM_CTRL + BWD_CTRL_BYTES;
 static_assert(BWD_SMEM_BYTES <= 232448, "backward kernel shared memory exceeds 227 KB");
 
 struct BwdCtrl {
     uint64_t fullG[BWD_G_STAGES], emptyG[BWD_G_STAGES];
     uint64_t fullD[BWD_D_SLOTS], emptyD[BWD_D_SLOTS];
-    uint64_t accFull, accEmpty;
-    uint64_t prodBar;      // producer-warp rendezvous around the per-item knot reload
+    uint64_t chunkFull, drained;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -596,6 +706,7 @@ struct BwdPlan {
     int ct_spline;         // column tiles of 32 features
     int ct_base;           // column tiles of 256 base features
     int splits;
+    int chunk_kb;          // 64-sample blocks accumulated in TMEM between drains
     int64_t kb_total;      // 64-sample blocks
     int64_t kb_per_split;
     __host__ __device__ int n_ctiles() const { return ct_spline + ct_base; }
@@ -603,19 +714,17 @@ struct BwdPlan {
     __host__ __device__ int64_t ld_partial() const { return (int64_t)n_ctiles() * BLOCK_N; }
 };
 
-template <int K, int NTERMS>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
-tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ grid, const uint8_t* __restrict__ dyimg,
+template <int NTERMS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ dyimg,
                     float* __restrict__ partial, int* __restrict__ status,
-                    int64_t N, int I, int O, int G, BwdPlan plan, int vec_ok) {
+                    int64_t N, int I, int O, BwdPlan plan, int vec_ok) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr bool SPLIT = (NTERMS == 3);
     const uint32_t sbase = smem_u32(smem);
     BwdCtrl* ctrl = reinterpret_cast<BwdCtrl*>(smem + BWD_SMEM_CTRL);
-    float* knots = reinterpret_cast<float*>(smem + BWD_SMEM_CTRL + 256);    // [32][13]
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int R = G + K, nk = G + 2 * K + 1;
     const int n_ohalves = plan.n_otiles * 2;
     const int n_ctiles = plan.n_ctiles();
     const int64_t n_items = plan.n_items();
@@ -626,20 +735,18 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ grid,
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < BWD_G_STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->fullG[s]), BWD_PROD_WARPS * 32);
+            mbar_init(smem_u32(&ctrl->fullG[s]), WORKER_THREADS);
             mbar_init(smem_u32(&ctrl->emptyG[s]), 1);
         }
         for (int s = 0; s < BWD_D_SLOTS; ++s) {
             mbar_init(smem_u32(&ctrl->fullD[s]), 1);
             mbar_init(smem_u32(&ctrl->emptyD[s]), 1);
         }
-        mbar_init(smem_u32(&ctrl->accFull), 1);
-        mbar_init(smem_u32(&ctrl->accEmpty), BWD_EPI_WARPS * 32);
-        mbar_init(smem_u32(&ctrl->prodBar), BWD_PROD_WARPS * 32);
+        mbar_init(smem_u32(&ctrl->chunkFull), 1);
+        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
-    constexpr int MMA_WARP = BWD_EPI_WARPS + BWD_PROD_WARPS, TMA_WARP = MMA_WARP + 1;
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
         tmem_relinquish();
@@ -656,144 +763,168 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ grid,
         ot = (int)(rest % plan.n_otiles);
         sp = (int)(rest / plan.n_otiles);
     };
+    auto k_range = [&](int sp, int64_t& kb0, int64_t& kb1) {
+        kb0 = (int64_t)sp * plan.kb_per_split;
+        kb1 = kb0 + plan.kb_per_split;
+        if (kb1 > plan.kb_total) kb1 = plan.kb_total;
+    };
 
-    if (warp < BWD_EPI_WARPS) {
-        // ===== epilogue: both accumulator halves -> partial slab =====
-        uint32_t icount = 0;
-        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x, ++icount) {
-            int sp, ot, ct;
-            decode(item, sp, ot, ct);
-            if (!mbar_wait(smem_u32(&ctrl->accFull), icount & 1u, abort_flag)) break;
+    if (warp < WORKER_WARPS) {
+        // ===== workers: 64 samples x 256 columns per block, MN-major; drain between chunks =====
+        const int quad = warp & 3, part = warp >> 2;
+        // spline tiles: thread = (sample, 4 features); base tiles: thread = (4 samples, 8 features)
+        const int n_loc = (warp & 1) * 32 + lane;       // sample within the block (spline tiles)
+        const int fq = warp >> 1;                       // group of 4 features (spline tiles)
+        const int kg = warp >> 1;                       // group of 8 samples (base tiles)
+        const int r0 = (warp & 1) * 4;                  // first of this warp's 4 rows in the group
+        uint32_t it = 0, n_drained = 0;
+        bool ok = true;
+        bool pend = false, pend_first = false;
+        int pend_sp = 0, pend_ot = 0, pend_ct = 0;
+        auto drain = [&]() -> bool {
+            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
+            ++n_drained;
             tc_fence_after_sync();
-            float* slab = partial + (size_t)sp * ((size_t)O * plan.ld_partial());
+            float* slab = partial + (size_t)pend_sp * ((size_t)O * plan.ld_partial());
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
-                const int o = ot * BLOCK_N + h * BLOCK_M + warp * 32 + lane;
-                float* prow = slab + (size_t)o * plan.ld_partial() + (size_t)ct * BLOCK_N;
+                const int o = pend_ot * BLOCK_N + h * BLOCK_M + quad * 32 + lane;
+                float* prow = slab + (size_t)o * plan.ld_partial() + (size_t)pend_ct * BLOCK_N;
 #pragma unroll 1
-                for (int c = 0; c < BLOCK_N / 32; ++c) {
+                for (int c = part; c < BLOCK_N / 32; c += 4) {
                     uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + h * BLOCK_N + c * 32, r);
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + h * BLOCK_N + c * 32, r);
                     tmem_ld_wait();
-                    if (o < O) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            *reinterpret_cast<float4*>(prow + c * 32 + 4 * q) =
-                                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                    }
+                    if (o < O) drain_row32(prow + c * 32, r, pend_first, 32, true);
                 }
             }
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->accEmpty));
-        }
-    } else if (warp < BWD_EPI_WARPS + BWD_PROD_WARPS) {
-        // ===== operand producers: 64 samples x 256 columns, MN-major =====
-        const int pw = warp - BWD_EPI_WARPS;
-        const int ptid = pw * 32 + lane;
-        uint32_t it = 0, sync_phase = 0;
-        bool ok = true;
-        // Bounded rendezvous of the producer warps (an mbarrier, not bar.sync,
-        // so that a role that gave up cannot leave the others waiting forever).
-        auto producer_sync = [&]() -> bool {
-            const uint32_t bar = smem_u32(&ctrl->prodBar);
-            mbar_arrive(bar);
-            const bool r = mbar_wait(bar, sync_phase & 1u, abort_flag);
-            ++sync_phase;
-            return r;
+            mbar_arrive(smem_u32(&ctrl->drained));
+            pend = false;
+            return true;
         };
+
         for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
             int sp, ot, ct;
             decode(item, sp, ot, ct);
             const bool spline = ct < plan.ct_spline;
             const int f_tile0 = spline ? ct * 32 : (ct - plan.ct_spline) * 256;
-            if (spline) {
-                if (!producer_sync()) break;       // previous item's knot reads are done
-                for (int e = ptid; e < 32 * nk; e += BWD_PROD_WARPS * 32) {
-                    const int fl = e / nk, q = e - fl * nk;
-                    const int f = f_tile0 + fl;
-                    knots[fl * BWD_KNOT_STRIDE + q] = (f < I) ? __ldg(grid + (size_t)f * nk + q) : 0.0f;
+            int64_t kb0, kb1;
+            k_range(sp, kb0, kb1);
+            // spline tiles: inputs of the next block of samples are loaded one iteration ahead
+            const int f_sp = f_tile0 + fq * 4;
+            float nx[4] = {0.f, 0.f, 0.f, 0.f};
+            auto prefetch_spline = [&](int64_t kb) {
+                const int64_t n = kb * BLOCK_K + n_loc;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) nx[q] = 0.f;
+                if (n < N && f_sp < I) {
+                    const float* p = x + (size_t)n * I + f_sp;
+                    if (vec_ok && f_sp + 4 <= I) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+                        nx[0] = v.x; nx[1] = v.y; nx[2] = v.z; nx[3] = v.w;
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (f_sp + q < I) nx[q] = __ldg(p + q);
+                    }
                 }
-                if (!producer_sync()) break;
-            }
-            const int64_t kb0 = (int64_t)sp * plan.kb_per_split;
-            int64_t kb1 = kb0 + plan.kb_per_split;
-            if (kb1 > plan.kb_total) kb1 = plan.kb_total;
+            };
+            if (spline) prefetch_spline(kb0);
             for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t stage = it % BWD_G_STAGES;
                 const uint32_t g_hi = sbase + BWD_SMEM_G + stage * BWD_G_STAGE_BYTES;
                 const uint32_t g_lo = g_hi + TILE_B_BYTES;
-                // this warp's 8 samples of the block: rows pw*8 .. pw*8+7 = one group of 8 K rows
-                const int64_t nrow0 = kb * BLOCK_K + pw * 8;
+                const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
                 if (spline) {
-                    const int f = f_tile0 + lane;
-                    float xv[8];
+                    float xv[4];
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        xv[q] = (nrow0 + q < N && f < I) ? __ldg(x + (size_t)(nrow0 + q) * I + f) : 0.0f;
+                    for (int q = 0; q < 4; ++q) xv[q] = nx[q];
+                    if (kb + 1 < kb1) prefetch_spline(kb + 1);
+                    const bool n_ok = kb * BLOCK_K + n_loc < N;
                     if (!mbar_wait(smem_u32(&ctrl->emptyG[stage]), ((it / BWD_G_STAGES) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t atom = (uint32_t)((lane >> 3) * 8 + pw) * 1024u;   // [col group][sample group]
+                    // row = sample (k index), 128 B = 64 columns = 8 features of 8 slots
+                    const int kk = n_loc & 7;
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
+                    for (int q = 0; q < 4; ++q) {
+                        const int f = f_sp + q;
                         uint4 hi, lo;
-                        if (nrow0 + q < N && f < I) {
-                            eval_feature_row<K, SPLIT>(knots + lane * BWD_KNOT_STRIDE, nk, R, xv[q], hi, lo);
-                        } else {
+                        eval_feature_row<SPLIT>(tab + (size_t)(f < I ? f : I - 1) * TAB_FEATURE_FLOATS, xv[q], hi, lo);
+                        if (!(n_ok && f < I)) {
                             hi = make_uint4(0, 0, 0, 0);
                             lo = hi;
                         }
-                        const uint32_t off = atom + (uint32_t)q * 128u + (uint32_t)(((lane & 7) ^ q) << 4);
+                        const int fl = fq * 4 + q;                       // feature within the tile, 0..31
+                        const uint32_t off = (uint32_t)((fl >> 3) * 8 + (n_loc >> 3)) * 1024u + (uint32_t)kk * 128u +
+                                             (uint32_t)(((fl & 7) ^ kk) << 4);
                         st_shared_v4(g_hi + off, hi);
                         if (SPLIT) st_shared_v4(g_lo + off, lo);
                     }
                 } else {
                     // lane = chunk of 8 base features; columns c = 8*lane .. 8*lane+7
+                    const int64_t nrow0 = kb * BLOCK_K + kg * 8 + r0;
+                    const uint32_t atom = (uint32_t)((lane >> 3) * 8 + kg) * 1024u;   // [col group][sample group]
                     const int f0 = f_tile0 + lane * 8;
+                    float xv[4][8];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) load_x8(x, nrow0 + q, nrow0 + q < N, I, f0, vec_ok != 0, xv[q]);
                     if (!mbar_wait(smem_u32(&ctrl->emptyG[stage]), ((it / BWD_G_STAGES) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t atom = (uint32_t)((lane >> 3) * 8 + pw) * 1024u;
-#pragma unroll 2
-                    for (int q = 0; q < 8; ++q) {
-                        float xv[8];
-                        load_x8(x, nrow0 + q, nrow0 + q < N, I, f0, vec_ok != 0, xv);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
                         uint4 hi, lo;
-                        silu_chunk<SPLIT>(xv, hi, lo);
-                        if (!(nrow0 + q < N)) {
-                            hi = make_uint4(0, 0, 0, 0);
-                            lo = hi;
-                        }
-                        const uint32_t off = atom + (uint32_t)q * 128u + (uint32_t)(((lane & 7) ^ q) << 4);
+                        silu_chunk<SPLIT>(xv[q], hi, lo);
+                        const int rr = r0 + q;
+                        const uint32_t off = atom + (uint32_t)rr * 128u + (uint32_t)(((lane & 7) ^ rr) << 4);
                         st_shared_v4(g_hi + off, hi);
                         if (SPLIT) st_shared_v4(g_lo + off, lo);
                     }
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(smem_u32(&ctrl->fullG[stage]));
+                if (pend && chunk_start) {
+                    if (!drain()) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
+                    pend = true;
+                    pend_first = (kb - kb0) < plan.chunk_kb;
+                    pend_sp = sp;
+                    pend_ot = ot;
+                    pend_ct = ct;
+                }
             }
         }
+        if (ok && pend) drain();
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, true, true);
             constexpr uint64_t dbase = make_sdesc_sw128(8192, 1024);
-            uint32_t it = 0, dslot = 0, icount = 0;
+            uint32_t it = 0, dslot = 0, n_chunks = 0;
             bool ok = true;
-            for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++icount) {
+            for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 int sp, ot, ct;
                 decode(item, sp, ot, ct);
-                if (!mbar_wait(smem_u32(&ctrl->accEmpty), (icount & 1u) ^ 1u, abort_flag)) break;
-                tc_fence_after_sync();
-                const int64_t kb0 = (int64_t)sp * plan.kb_per_split;
-                int64_t kb1 = kb0 + plan.kb_per_split;
-                if (kb1 > plan.kb_total) kb1 = plan.kb_total;
+                int64_t kb0, kb1;
+                k_range(sp, kb0, kb1);
                 for (int64_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
                     const uint32_t stage = it % BWD_G_STAGES;
                     const uint32_t g_hi = sbase + BWD_SMEM_G + stage * BWD_G_STAGE_BYTES;
                     const uint32_t g_lo = g_hi + TILE_B_BYTES;
+                    const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
+                    if (chunk_start && n_chunks > 0) {
+                        if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                    }
                     if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), (it / BWD_G_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -808,11 +939,10 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ grid,
                         const uint32_t d_hi = sbase + BWD_SMEM_D + slot * BWD_D_SLOT_BYTES;
                         const uint32_t d_lo = d_hi + TILE_A_BYTES;
                         const uint32_t d_tmem = tmem_base + h * BLOCK_N;
-                        const uint32_t first = (kb > kb0) ? 1u : 0u;
 #pragma unroll
                         for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
                             mma_f16_ss(d_tmem, sdesc_at(dbase, d_hi + ks * 2048), sdesc_at(dbase, g_hi + ks * 2048),
-                                       idesc, (first || ks > 0) ? 1u : 0u);
+                                       idesc, (!chunk_start || ks > 0) ? 1u : 0u);
                         if (SPLIT) {
 #pragma unroll
                             for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
@@ -825,9 +955,13 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ grid,
                         }
                         mma_commit(smem_u32(&ctrl->emptyD[slot]));
                     }
-                    if (ok) mma_commit(smem_u32(&ctrl->emptyG[stage]));
+                    if (!ok) break;
+                    mma_commit(smem_u32(&ctrl->emptyG[stage]));
+                    if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
+                        mma_commit(smem_u32(&ctrl->chunkFull));
+                        ++n_chunks;
+                    }
                 }
-                if (ok) mma_commit(smem_u32(&ctrl->accFull));
             }
         }
     } else {
@@ -837,9 +971,8 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ grid,
             for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
                 int sp, ot, ct;
                 decode(item, sp, ot, ct);
-                const int64_t kb0 = (int64_t)sp * plan.kb_per_split;
-                int64_t kb1 = kb0 + plan.kb_per_split;
-                if (kb1 > plan.kb_total) kb1 = plan.kb_total;
+                int64_t kb0, kb1;
+                k_range(sp, kb0, kb1);
                 for (int64_t kb = kb0; kb < kb1 && ok; ++kb) {
                     for (int h = 0; h < 2; ++h, ++dslot) {
                         const uint32_t slot = dslot % BWD_D_SLOTS;
@@ -884,12 +1017,25 @@ inline int sm_count() {
     return cached;
 }
 
+// Chunk lengths (k-blocks accumulated in TMEM between drains).  Every tensor-core accumulation
+// truncates, so the error of a chain grows with its length; these defaults keep it below the
+// operand-split error.  KAN_B200_FWD_CHUNK / KAN_B200_BWD_CHUNK override them (tuning only).
+inline int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    if (!v || !*v) return dflt;
+    const int n = atoi(v);
+    return n > 0 ? n : dflt;
+}
+inline int fwd_chunk_kb() { static int c = env_int("KAN_B200_FWD_CHUNK", 36); return c; }
+inline int bwd_chunk_kb() { static int c = env_int("KAN_B200_BWD_CHUNK", 16); return c; }
+
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     BwdPlan p;
     p.n_otiles = (s.O + BLOCK_N - 1) / BLOCK_N;
     p.ct_spline = (s.I + 31) / 32;
     p.ct_base = has_base ? (s.I + 255) / 256 : 0;
     p.kb_total = (s.N + BLOCK_K - 1) / BLOCK_K;
+    p.chunk_kb = bwd_chunk_kb();
     const int64_t tiles = (int64_t)p.n_otiles * p.n_ctiles();
     int64_t splits = sm_count() / tiles;
     if (splits < 1) splits = 1;
@@ -901,6 +1047,14 @@ inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
 }
 
 inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+inline size_t table_bytes(const LayerShape& s) { return (size_t)s.I * TAB_FEATURE_FLOATS * sizeof(float); }
+
+inline cudaError_t launch_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
+    const int work = s.I * (TAB_ENTRIES + 1);
+    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, s.I, s.G, s.K);
+    return cudaGetLastError();
+}
 
 struct FwdLayout {
     ColumnSpace cs;
@@ -935,8 +1089,8 @@ bool tc_supported(const LayerShape& s) {
 
 size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param) {
     // Sized for a layer with a base branch (the larger case).
-    if (op == 0) return kWsHeader + align256(fwd_layout(s, true).wimg_bytes);
-    size_t b = kWsHeader;
+    if (op == 0) return kWsHeader + table_bytes(s) + align256(fwd_layout(s, true).wimg_bytes);
+    size_t b = kWsHeader + table_bytes(s);
     if (need_param) {
         BwdLayout L = bwd_layout(s, true);
         b += align256(L.dyimg_bytes) + align256(L.partial_bytes);
@@ -951,13 +1105,15 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     if (s.N == 0) return cudaSuccess;
     const bool has_base = bw != nullptr;
     FwdLayout L = fwd_layout(s, has_base);
-    if (!ws || ws_bytes < kWsHeader + L.wimg_bytes) return cudaErrorMemoryAllocation;
+    if (!ws || ws_bytes < kWsHeader + table_bytes(s) + L.wimg_bytes) return cudaErrorMemoryAllocation;
     int* status = reinterpret_cast<int*>(ws);
-    uint8_t* wimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader;
+    float* tab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kWsHeader);
+    uint8_t* wimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
     const int kb_total = L.cs.kb_total();
     {
         cudaError_t e0 = cudaMemsetAsync(status, 0, sizeof(int), st);
         if (e0 != cudaSuccess) return e0;
+        if ((e0 = launch_table(grid, tab, s, st)) != cudaSuccess) return e0;
         const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
         int blocks = (int)((chunks + 255) / 256);
         if (blocks > sm_count() * 16) blocks = sm_count() * 16;
@@ -966,25 +1122,25 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    const int64_t n_mtiles = (s.N + BLOCK_M - 1) / BLOCK_M;
-    const int64_t n_tiles = n_mtiles * L.n_otiles;
-    int blocks = (int)(n_tiles < sm_count() ? n_tiles : sm_count());
-    const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    FwdParams P;
+    P.N = s.N; P.I = s.I; P.O = s.O; P.G = s.G;
+    P.kb_spline = L.cs.kb_spline; P.kb_total = kb_total;
+    P.n_otiles = L.n_otiles; P.n_opairs = (L.n_otiles + 1) / 2;
+    P.n_tiles = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_opairs;
+    P.chunk_kb = fwd_chunk_kb();
+    P.vec_x = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    P.vec_x2 = ((s.I & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 7) == 0);
+    P.vec_y = ((s.O & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
     cudaError_t e = cudaSuccess;
-#define KAN_FWD(KK, NT)                                                                                        \
-    do {                                                                                                       \
-        e = cudaFuncSetAttribute(tc_forward_kernel<KK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
-                                 (int)FWD_SMEM_BYTES);                                                         \
-        if (e == cudaSuccess)                                                                                  \
-            tc_forward_kernel<KK, NT><<<blocks, FWD_THREADS, FWD_SMEM_BYTES, st>>>(                            \
-                x, grid, wimg, y, status, s.N, s.I, s.O, s.G, L.cs.kb_spline, kb_total, L.n_otiles, n_tiles,   \
-                vec_ok);                                                                                       \
+#define KAN_FWD(NT)                                                                                           \
+    do {                                                                                                      \
+        e = cudaFuncSetAttribute(tc_forward_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                 (int)FWD_SMEM_BYTES);                                                        \
+        if (e == cudaSuccess)                                                                                 \
+            tc_forward_kernel<NT><<<blocks, TC_THREADS, FWD_SMEM_BYTES, st>>>(x, tab, wimg, y, status, P);    \
     } while (0)
-    if (split_terms == 3) {
-        if (s.K == 1) KAN_FWD(1, 3); else if (s.K == 2) KAN_FWD(2, 3); else KAN_FWD(3, 3);
-    } else {
-        if (s.K == 1) KAN_FWD(1, 1); else if (s.K == 2) KAN_FWD(2, 1); else KAN_FWD(3, 1);
-    }
+    if (split_terms == 3) KAN_FWD(3); else KAN_FWD(1);
 #undef KAN_FWD
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
@@ -999,13 +1155,15 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
     if (s.N == 0) return simt_backward<float>(dY, x, grid, bw, sw, scaler, gx, gbw, gsw, gscaler, s, nullptr, 0, st);
     if (need_param) {
         BwdLayout L = bwd_layout(s, has_base);
-        const size_t need = kWsHeader + align256(L.dyimg_bytes) + L.partial_bytes;
+        const size_t need = kWsHeader + table_bytes(s) + align256(L.dyimg_bytes) + L.partial_bytes;
         if (!ws || ws_bytes < need) return cudaErrorMemoryAllocation;
         int* status = reinterpret_cast<int*>(ws);
-        uint8_t* dyimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader;
+        float* tab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kWsHeader);
+        uint8_t* dyimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
         float* partial = reinterpret_cast<float*>(dyimg + align256(L.dyimg_bytes));
         {
             if ((e = cudaMemsetAsync(status, 0, sizeof(int), st)) != cudaSuccess) return e;
+            if ((e = launch_table(grid, tab, s, st)) != cudaSuccess) return e;
             const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
             int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
                                                                                 : (int64_t)sm_count() * 16);
@@ -1015,19 +1173,15 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
         const int64_t items = L.plan.n_items();
         const int blocks = (int)(items < sm_count() ? items : sm_count());
         const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
-#define KAN_BWD(KK, NT)                                                                                        \
-    do {                                                                                                       \
-        e = cudaFuncSetAttribute(tc_bwd_param_kernel<KK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
-                                 (int)BWD_SMEM_BYTES);                                                         \
-        if (e == cudaSuccess)                                                                                  \
-            tc_bwd_param_kernel<KK, NT><<<blocks, BWD_THREADS, BWD_SMEM_BYTES, st>>>(                          \
-                x, grid, dyimg, partial, status, s.N, s.I, s.O, s.G, L.plan, vec_ok);                          \
+#define KAN_BWD(NT)                                                                                           \
+    do {                                                                                                      \
+        e = cudaFuncSetAttribute(tc_bwd_param_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                 (int)BWD_SMEM_BYTES);                                                        \
+        if (e == cudaSuccess)                                                                                 \
+            tc_bwd_param_kernel<NT><<<blocks, TC_THREADS, BWD_SMEM_BYTES, st>>>(                              \
+                x, tab, dyimg, partial, status, s.N, s.I, s.O, L.plan, vec_ok);                               \
     } while (0)
-        if (split_terms == 3) {
-            if (s.K == 1) KAN_BWD(1, 3); else if (s.K == 2) KAN_BWD(2, 3); else KAN_BWD(3, 3);
-        } else {
-            if (s.K == 1) KAN_BWD(1, 1); else if (s.K == 2) KAN_BWD(2, 1); else KAN_BWD(3, 1);
-        }
+        if (split_terms == 3) KAN_BWD(3); else KAN_BWD(1);
 #undef KAN_BWD
         if (e != cudaSuccess) return e;
         if ((e = cudaGetLastError()) != cudaSuccess) return e;

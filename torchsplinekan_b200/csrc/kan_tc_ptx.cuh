@@ -5,6 +5,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace kanb200 {
@@ -143,7 +144,6 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int n, bool a_mn_major, b
     return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
            ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
-
 // Shared-memory matrix descriptor, 128-byte swizzle.  Bit layout: [0,14) start
 // address >> 4, [16,30) leading-dimension byte offset >> 4, [32,46) stride-
 // dimension byte offset >> 4, [46,48) version (1 on sm_100), [61,64) layout
@@ -168,8 +168,11 @@ __host__ __device__ constexpr uint32_t sw128_chunk_offset(uint32_t row, uint32_t
     return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
 }
 
-// ---- bf16 split -------------------------------------------------------------
-// v ~= hi + lo with hi = bf16(v), lo = bf16(v - hi): 16 significand bits kept.
+// ---- operand split ----------------------------------------------------------
+// v ~= hi + lo with hi = bf16(v), lo = bf16(v - hi): 16 significand bits kept,
+// full fp32 exponent range.  Both parts are bf16 because one tcgen05 kind::f16
+// instruction takes a single 16-bit format for A and B: mixing bf16 with fp16
+// operands raises an illegal-instruction fault.
 __device__ __forceinline__ void split2(float a, float b, uint32_t& hi, uint32_t& lo) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     hi = *reinterpret_cast<const uint32_t*>(&h);
