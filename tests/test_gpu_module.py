@@ -190,6 +190,8 @@ def test_mnist_shaped_step_with_updated_grid():
     net.update_grid(x[:512])
     ref = sk.KAN([784, 256, 256, 10], backend="reference").to("cuda", torch.float64)
     ref.load_state_dict({n: v.double() for n, v in net.state_dict().items()})
+    ref32 = sk.KAN([784, 256, 256, 10], backend="reference").cuda()
+    ref32.load_state_dict(net.state_dict())
 
     def run(model, xin, impl):
         for p in model.parameters():
@@ -198,13 +200,34 @@ def test_mnist_shaped_step_with_updated_grid():
         (torch.nn.functional.cross_entropy(y, labels) + r).backward()
         return [y, r] + [p.grad for p in model.parameters()]
 
-    got, want = run(net, x, "fused"), run(ref, x.double(), "dense")
-    for a, b in zip(got, want):
-        assert _err(a, b) < 5e-5
+    got, want, want32 = run(net, x, "fused"), run(ref, x.double(), "dense"), run(ref32, x, "dense")
+    names = ["y", "reg"] + [n for n, _ in net.named_parameters()]
+    errs = {n: _err(a, b) for n, a, b in zip(names, got, want)}
+    errs32 = {n: _err(a, b) for n, a, b in zip(names, got, want32)}
+    dense_gap = {n: _err(a, b) for n, a, b in zip(names, want32, want)}
+    print("fused32 vs dense64", errs)
+    print("fused32 vs dense32", errs32)
+    print("dense32 vs dense64", dense_gap)
+    # y and the penalty itself are smooth in the rounding error.
+    assert errs["y"] < 5e-5 and errs["reg"] < 5e-5, errs
+    # The penalty's gradient contains sign(phi): where |phi| is at rounding level two float32
+    # evaluations (or float32 and float64) disagree on the sign, which moves single entries by
+    # 2 ga / N.  The native result must therefore be as close to float64 as the dense float32
+    # evaluation of the same expression is (factor 3 of slack), not closer than rounding allows.
+    for n in names:
+        assert errs[n] < max(5e-5, 3.0 * dense_gap[n]), (n, errs[n], dense_gap[n])
     # plain forward/backward goes through kan_apply (tensor cores for the two wide layers)
+    for p in net.parameters():
+        p.grad = None
+    for p in ref.parameters():
+        p.grad = None
     y = net(x)
     torch.nn.functional.cross_entropy(y, labels).backward()
-    assert _err(y, ref(x.double())) < TOL32
+    y64 = ref(x.double())
+    torch.nn.functional.cross_entropy(y64, labels).backward()
+    assert _err(y, y64) < TOL32
+    for (n, p), q in zip(net.named_parameters(), ref.parameters()):
+        assert _err(p.grad, q.grad) < 5e-5, n
 
 
 def test_wide_grid_layer_gather_path():

@@ -132,6 +132,21 @@ __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* _
     ent[19] = 0.0f;
 }
 
+// flag[0] = 1 when every feature has the knot row of feature 0 (the default uniform grid): the
+// kernels then keep that single 1-KB table in shared memory instead of reading per-feature
+// tables through L1.
+__global__ void grid_shared_kernel(const float* __restrict__ grid, int* __restrict__ flag, int I, int nk) {
+    __shared__ int differs;
+    if (threadIdx.x == 0) differs = 0;
+    __syncthreads();
+    int d = 0;
+    for (int e = threadIdx.x; e < I * nk; e += blockDim.x)
+        if (grid[e] != grid[e % nk]) d = 1;
+    if (d) differs = 1;
+    __syncthreads();
+    if (threadIdx.x == 0) *flag = differs ? 0 : 1;
+}
+
 __device__ __forceinline__ float silu_fast(float x) {
     return __fdividef(x, 1.0f + __expf(-x));
 }
@@ -139,17 +154,18 @@ __device__ __forceinline__ float silu_fast(float x) {
 // Evaluates the basis of one input from its feature's table and returns the 8
 // column slots of the feature as two 128-bit rows (hi and lo bf16 parts).
 // Branch-free.  SPLIT = false leaves lo untouched.
-template <bool SPLIT>
+template <bool SPLIT, bool SMEM_TAB>
 __device__ __forceinline__ void eval_feature_row(const float* __restrict__ ftab, float xv, uint4& hi, uint4& lo) {
-    const float4 k0 = __ldg(reinterpret_cast<const float4*>(ftab));
-    const float4 k1 = __ldg(reinterpret_cast<const float4*>(ftab) + 1);
-    const float4 k2 = __ldg(reinterpret_cast<const float4*>(ftab) + 2);
+    auto ld4 = [](const float4* p) -> float4 { return SMEM_TAB ? *p : __ldg(p); };
+    const float4 k0 = ld4(reinterpret_cast<const float4*>(ftab));
+    const float4 k1 = ld4(reinterpret_cast<const float4*>(ftab) + 1);
+    const float4 k2 = ld4(reinterpret_cast<const float4*>(ftab) + 2);
     const bool inside = (xv >= k0.x) && (xv <= k2.w);
     int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
             (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
     m = inside ? m : TAB_ZERO_ENTRY;
     const float4* ent = reinterpret_cast<const float4*>(ftab + 16 + m * TAB_ENTRY_FLOATS);
-    const float4 c0 = __ldg(ent), c1 = __ldg(ent + 1), c2 = __ldg(ent + 2), c3 = __ldg(ent + 3), meta = __ldg(ent + 4);
+    const float4 c0 = ld4(ent), c1 = ld4(ent + 1), c2 = ld4(ent + 2), c3 = ld4(ent + 3), meta = ld4(ent + 4);
     const float u = xv - meta.x;
     const int s = __float_as_int(meta.y);
     const float v0 = fmaf(fmaf(fmaf(c0.w, u, c0.z), u, c0.y), u, c0.x);
@@ -376,7 +392,7 @@ constexpr uint32_t FWD_A_STAGE_BYTES = 2 * TILE_A_BYTES;                  // hi 
 constexpr uint32_t FWD_SMEM_A = 0;
 constexpr uint32_t FWD_SMEM_B = FWD_SMEM_A + FWD_A_STAGES * FWD_A_STAGE_BYTES;
 constexpr uint32_t FWD_SMEM_CTRL = FWD_SMEM_B + FWD_B_SLOTS * TILE_B_BYTES;
-constexpr uint32_t FWD_CTRL_BYTES = 256;
+constexpr uint32_t FWD_CTRL_BYTES = 256 + TAB_FEATURE_FLOATS * 4;   // barriers + the shared-grid table
 constexpr uint32_t FWD_SMEM_BYTES = FWD_SMEM_CTRL + FWD_CTRL_BYTES;
 static_assert(FWD_SMEM_BYTES <= 232448, "forward kernel shared memory exceeds 227 KB");
 
@@ -407,8 +423,11 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
     constexpr bool SPLIT = (NTERMS == 3);
     const uint32_t sbase = smem_u32(smem);
     FwdCtrl* ctrl = reinterpret_cast<FwdCtrl*>(smem + FWD_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + FWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool shared_grid = status[1] != 0;
+    if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
@@ -504,8 +523,13 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                     const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * TAB_FEATURE_FLOATS;
                     const float* t1 = tab + (size_t)(f0 + 1 < P.I ? f0 + 1 : P.I - 1) * TAB_FEATURE_FLOATS;
                     uint4 hi0, lo0, hi1, lo1;
-                    eval_feature_row<SPLIT>(t0, x0, hi0, lo0);
-                    eval_feature_row<SPLIT>(t1, x1, hi1, lo1);
+                    if (shared_grid) {
+                        eval_feature_row<SPLIT, true>(stab, x0, hi0, lo0);
+                        eval_feature_row<SPLIT, true>(stab, x1, hi1, lo1);
+                    } else {
+                        eval_feature_row<SPLIT, false>(t0, x0, hi0, lo0);
+                        eval_feature_row<SPLIT, false>(t1, x1, hi1, lo1);
+                    }
                     if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / FWD_A_STAGES) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -688,7 +712,7 @@ constexpr uint32_t BWD_D_SLOT_BYTES = 2 * TILE_A_BYTES;                  // hi +
 constexpr uint32_t BWD_SMEM_G = 0;
 constexpr uint32_t BWD_SMEM_D = BWD_SMEM_G + BWD_G_STAGES * BWD_G_STAGE_BYTES;
 constexpr uint32_t BWD_SMEM_CTRL = BWD_SMEM_D + BWD_D_SLOTS * BWD_D_SLOT_BYTES;
-constexpr uint32_t BWD_CTRL_BYTES = 256;
+constexpr uint32_t BWD_CTRL_BYTES = 256 + TAB_FEATURE_FLOATS * 4;   // barriers + the shared-grid table
 constexpr uint32_t BWD_SMEM_BYTES = BWD_SMEM_CTRL + BWD_CTRL_BYTES;
 static_assert(BWD_SMEM_BYTES <= 232448, "backward kernel shared memory exceeds 227 KB");
 
@@ -711,7 +735,8 @@ struct BwdPlan {
     int64_t kb_per_split;
     __host__ __device__ int n_ctiles() const { return ct_spline + ct_base; }
     __host__ __device__ int64_t n_items() const { return (int64_t)n_otiles * n_ctiles() * splits; }
-    __host__ __device__ int64_t ld_partial() const { return (int64_t)n_ctiles() * BLOCK_N; }
+    // floats of one split's slab: every (o-tile, c-tile) owns a 256 x 256 block
+    __host__ __device__ int64_t slab_floats() const { return (int64_t)n_otiles * n_ctiles() * 256 * 256; }
 };
 
 template <int NTERMS>
@@ -723,8 +748,11 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     constexpr bool SPLIT = (NTERMS == 3);
     const uint32_t sbase = smem_u32(smem);
     BwdCtrl* ctrl = reinterpret_cast<BwdCtrl*>(smem + BWD_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + BWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool shared_grid = status[1] != 0;
+    if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
     const int n_ohalves = plan.n_otiles * 2;
     const int n_ctiles = plan.n_ctiles();
     const int64_t n_items = plan.n_items();
@@ -785,17 +813,33 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
             ++n_drained;
             tc_fence_after_sync();
-            float* slab = partial + (size_t)pend_sp * ((size_t)O * plan.ld_partial());
+            // Partial sums live in a blocked layout so that a warp (32 consecutive rows) touches
+            // contiguous memory: tile (split, o-tile, c-tile) -> [half][column / 4][row][4 floats].
+            float4* tile = reinterpret_cast<float4*>(partial) +
+                           (((size_t)pend_sp * plan.n_otiles + pend_ot) * n_ctiles + pend_ct) * (size_t)(2 * 64 * 128);
+            const int row = quad * 32 + lane;
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
-                const int o = pend_ot * BLOCK_N + h * BLOCK_M + quad * 32 + lane;
-                float* prow = slab + (size_t)o * plan.ld_partial() + (size_t)pend_ct * BLOCK_N;
 #pragma unroll 1
                 for (int c = part; c < BLOCK_N / 32; c += 4) {
+                    float4* dst = tile + ((size_t)h * 64 + c * 8) * 128 + row;
+                    float4 old[8];
+                    if (!pend_first) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) old[q] = dst[(size_t)q * 128];
+                    }
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + h * BLOCK_N + c * 32, r);
                     tmem_ld_wait();
-                    if (o < O) drain_row32(prow + c * 32, r, pend_first, 32, true);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        if (!pend_first) {
+                            v.x += old[q].x; v.y += old[q].y; v.z += old[q].z; v.w += old[q].w;
+                        }
+                        dst[(size_t)q * 128] = v;
+                    }
                 }
             }
             tc_fence_before_sync();
@@ -852,7 +896,11 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                     for (int q = 0; q < 4; ++q) {
                         const int f = f_sp + q;
                         uint4 hi, lo;
-                        eval_feature_row<SPLIT>(tab + (size_t)(f < I ? f : I - 1) * TAB_FEATURE_FLOATS, xv[q], hi, lo);
+                        if (shared_grid)
+                            eval_feature_row<SPLIT, true>(stab, xv[q], hi, lo);
+                        else
+                            eval_feature_row<SPLIT, false>(tab + (size_t)(f < I ? f : I - 1) * TAB_FEATURE_FLOATS,
+                                                           xv[q], hi, lo);
                         if (!(n_ok && f < I)) {
                             hi = make_uint4(0, 0, 0, 0);
                             lo = hi;
@@ -1004,6 +1052,54 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 }
 
+// Sums the per-split slabs (blocked layout of the drain) and applies the scaler algebra:
+// gsw = scaler * D, gscaler = sum_r sw * D, gbw = base column.  Thread = (feature, output) with the
+// output index fastest, so the 16-byte reads of a warp are contiguous.
+__global__ void finalize_blocked_kernel(const float* __restrict__ partial, BwdPlan plan,
+                                        const float* __restrict__ sw, const float* __restrict__ scaler,
+                                        float* __restrict__ gsw, float* __restrict__ gscaler,
+                                        float* __restrict__ gbw, int O, int I, int R) {
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)O * I) return;
+    const int o = (int)(idx % O), i = (int)(idx / O);
+    const int ot = o >> 8, h = (o >> 7) & 1, row = o & 127;
+    const int n_ctiles = plan.n_ctiles();
+    const size_t oi = (size_t)o * I + i;
+    auto tile_ptr = [&](int sp, int ct) -> const float4* {
+        return reinterpret_cast<const float4*>(partial) +
+               ((((size_t)sp * plan.n_otiles + ot) * n_ctiles + ct) * 2 + h) * (size_t)(64 * 128) + row;
+    };
+    if (gsw || gscaler) {
+        const int ct = i >> 5, fl = i & 31;
+        float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int sp = 0; sp < plan.splits; ++sp) {
+            const float4* t = tile_ptr(sp, ct);
+            const float4 a = t[(size_t)(fl * 2) * 128], b = t[(size_t)(fl * 2 + 1) * 128];
+            d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+            d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+        }
+        const float sc = scaler ? scaler[oi] : 1.0f;
+        float gs = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < R) {
+                if (gsw) gsw[oi * R + r] = scaler ? sc * d[r] : d[r];
+                if (gscaler) gs += sw[oi * R + r] * d[r];
+            }
+        }
+        if (gscaler) gscaler[oi] = gs;
+    }
+    if (gbw) {
+        const int ct = plan.ct_spline + (i >> 8), c = i & 255;
+        float d = 0.f;
+        for (int sp = 0; sp < plan.splits; ++sp) {
+            const float4 a = tile_ptr(sp, ct)[(size_t)(c >> 2) * 128];
+            d += (c & 3) == 0 ? a.x : ((c & 3) == 1 ? a.y : ((c & 3) == 2 ? a.z : a.w));
+        }
+        gbw[oi] = d;
+    }
+}
+
 inline int sm_count() {
     static int cached = 0;
     if (cached == 0) {
@@ -1026,7 +1122,7 @@ inline int env_int(const char* name, int dflt) {
     const int n = atoi(v);
     return n > 0 ? n : dflt;
 }
-inline int fwd_chunk_kb() { static int c = env_int("KAN_B200_FWD_CHUNK", 36); return c; }
+inline int fwd_chunk_kb() { static int c = env_int("KAN_B200_FWD_CHUNK", 144); return c; }
 inline int bwd_chunk_kb() { static int c = env_int("KAN_B200_BWD_CHUNK", 16); return c; }
 
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
@@ -1050,9 +1146,11 @@ inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 inline size_t table_bytes(const LayerShape& s) { return (size_t)s.I * TAB_FEATURE_FLOATS * sizeof(float); }
 
-inline cudaError_t launch_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
+inline cudaError_t launch_table(const float* grid, float* tab, int* shared_flag, const LayerShape& s,
+                                cudaStream_t st) {
     const int work = s.I * (TAB_ENTRIES + 1);
     build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, s.I, s.G, s.K);
+    grid_shared_kernel<<<1, 1024, 0, st>>>(grid, shared_flag, s.I, s.T());
     return cudaGetLastError();
 }
 
@@ -1077,7 +1175,7 @@ inline BwdLayout bwd_layout(const LayerShape& s, bool has_base) {
     BwdLayout L;
     L.plan = plan_bwd(s, has_base);
     L.dyimg_bytes = (size_t)L.plan.kb_total * L.plan.n_otiles * 2 * BWD_D_SLOT_BYTES;
-    L.partial_bytes = (size_t)L.plan.splits * s.O * L.plan.ld_partial() * sizeof(float);
+    L.partial_bytes = (size_t)L.plan.splits * L.plan.slab_floats() * sizeof(float);
     return L;
 }
 
@@ -1113,7 +1211,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     {
         cudaError_t e0 = cudaMemsetAsync(status, 0, sizeof(int), st);
         if (e0 != cudaSuccess) return e0;
-        if ((e0 = launch_table(grid, tab, s, st)) != cudaSuccess) return e0;
+        if ((e0 = launch_table(grid, tab, status + 1, s, st)) != cudaSuccess) return e0;
         const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
         int blocks = (int)((chunks + 255) / 256);
         if (blocks > sm_count() * 16) blocks = sm_count() * 16;
@@ -1163,7 +1261,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
         float* partial = reinterpret_cast<float*>(dyimg + align256(L.dyimg_bytes));
         {
             if ((e = cudaMemsetAsync(status, 0, sizeof(int), st)) != cudaSuccess) return e;
-            if ((e = launch_table(grid, tab, s, st)) != cudaSuccess) return e;
+            if ((e = launch_table(grid, tab, status + 1, s, st)) != cudaSuccess) return e;
             const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
             int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
                                                                                 : (int64_t)sm_count() * 16);
@@ -1185,10 +1283,13 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
 #undef KAN_BWD
         if (e != cudaSuccess) return e;
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        const int64_t ld = L.plan.ld_partial();
-        e = finalize_param_grads<float>(partial, L.plan.splits, (int64_t)s.O * ld, ld, RP,
-                                        (int64_t)L.plan.ct_spline * BLOCK_N, 1, sw, scaler, gsw, gscaler,
-                                        has_base ? gbw : nullptr, s.O, s.I, s.R(), st);
+        {
+            const int64_t work = (int64_t)s.O * s.I;
+            const int fblocks = (int)((work + 255) / 256);
+            finalize_blocked_kernel<<<fblocks, 256, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
+                                                             has_base ? gbw : nullptr, s.O, s.I, s.R());
+            e = cudaGetLastError();
+        }
         if (e != cudaSuccess) return e;
     }
     if (gx) {
