@@ -32,5 +32,9 @@ def rel_err(a, b):
 def pytest_sessionstart(session):
     """The package refuses to import without its CUDA library: build it (nvcc cross-compiles
     without a GPU) when it is missing or older than its sources."""
-    from torchsplinekan_b200.build import build_library
-    build_library()
+    import importlib.util
+    # loaded by path: importing the package itself already needs an up-to-date library
+    spec = importlib.util.spec_from_file_location("_kan_b200_build", os.path.join(ROOT, "torchsplinekan_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build_library()

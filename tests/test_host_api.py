@@ -48,8 +48,9 @@ def test_mode_resolution_and_workspace_sizes():
     with pytest.raises(RuntimeError, match="tensor-core"):
         _native.resolve_mode(_native.MODE_TC_BF16X3, f64, 1024, 64, 64, 5, 3)
     fw = _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_AUTO, f32, 65536, 1024, 1024, 5, 3)
-    # packed weights: 4 output tiles x 144 column blocks x (hi + lo) x 32 KiB
-    assert fw == 256 + 4 * 144 * 2 * 32768
+    # header + 1 KiB polynomial table per feature + packed weights: 4 output tiles x 144 column
+    # blocks x (hi + lo) x 32 KiB
+    assert fw == 256 + 1024 * 1024 + 4 * 144 * 2 * 32768
     bw = _native.workspace_bytes(_native.OP_BACKWARD, _native.MODE_AUTO, f32, 65536, 1024, 1024, 5, 3, False, True)
     assert bw > 65536 * 1024 * 4          # bf16 hi/lo image of dY plus the partial slab
     assert _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_SIMT, f64, 1024, 16, 8, 5, 3) == 0

@@ -4,7 +4,7 @@ Drop-in for the ``spline_kan`` package of torch-spline-kan: same classes,
 constructor arguments, state-dict keys and operator names; the native backend
 is a C-ABI CUDA library (``lib/libkan_b200.so``) written for Blackwell.
 Importing the package loads that library and fails if it has not been built
-(``python -m torchsplinekan_b200.build``); there is no fallback implementation
+(``python torchsplinekan_b200/build.py``); there is no fallback implementation
 of the native operators.
 """
 from . import _C                      # noqa: F401  (loads the library, registers torch.ops.spline_kan.*)

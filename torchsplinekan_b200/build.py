@@ -1,6 +1,6 @@
 """Builds ``lib/libkan_b200.so`` (the C-ABI library) with nvcc for sm_100a.
 
-    python -m torchsplinekan_b200.build [--force] [--verbose]
+    python torchsplinekan_b200/build.py [--force] [--verbose]
 
 The library has no dependency on PyTorch or on libcuda at link time; it is
 loaded with ctypes.  nvcc cross-compiles without a GPU.
