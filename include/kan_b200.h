@@ -117,6 +117,27 @@ KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, c
                           void* a, int64_t N, int64_t I, int64_t O, int R,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same result as kanb200_edge_abs_mean, for callers that cannot hand over scratch memory.
+ * No counterpart in the reference.  Some hosts plan all device memory ahead of time -- a serving
+ * process that gives its whole heap to a static planner at start-up, a plugin interface that only
+ * passes the tensors of the operator -- and have nothing to allocate a workspace from when the
+ * call is made.  For them the per-split partial sums go to a 4 MiB buffer built into the library
+ * (a file-scope __device__ array: every GPU that loads the library keeps it until the process
+ * exits).  Limits and rules:
+ *   - shapes whose partial sums need more than 4 MiB (splits * O * I * sizeof(dtype); see
+ *     kanb200_workspace_bytes(KANB200_OP_EDGE_FWD, ...) minus its 256-byte header) are refused
+ *     with KANB200_EWORKSPACE and a message; nothing is launched;
+ *   - the call itself allocates nothing (no cudaMalloc / cudaFree, no allocating library call);
+ *   - the first call on each device looks up the buffer's device address (cudaGetSymbolAddress,
+ *     with that device current) and caches it; make that first call during set-up, before any
+ *     stream capture is started;
+ *   - all calls on a device share the one buffer, which keeps the previous call's contents.
+ *     Every slot a call reads is written earlier by the same call, so nothing needs clearing,
+ *     but two calls that overlap on the GPU (different streams) race on it: serialise them. */
+KANB200_API int kanb200_edge_abs_mean_noalloc(int dtype, const void* s, const void* H, const void* bw,
+                                              const void* W, void* a,
+                                              int64_t N, int64_t I, int64_t O, int R, void* stream);
+
 /* Gradients of kanb200_edge_abs_mean; NULL output = not needed
  * (edge_abs_mean_backward_cuda, csrc/kan_reg_cuda.cu:284-312). */
 KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a,

@@ -45,6 +45,7 @@ SIGNATURES = {
                                                                        _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                    _c_void_p, _c_size, _c_void_p]),
+    "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
     "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                             _c_void_p, _c_size, _c_void_p]),
     "kanb200_check_status": (_c_int, [_c_void_p, _c_void_p]),
@@ -65,10 +66,13 @@ def lib() -> ctypes.CDLL:
             if _lib is None:
                 if not os.path.exists(LIB_PATH):
                     raise RuntimeError(
-                        f"{LIB_PATH} is missing: build it with `python -m torchsplinekan_b200.build` "
+                        f"{LIB_PATH} is missing: build it with `python torchsplinekan_b200/build.py` "
                         "(needs nvcc).  This package has no fallback implementation.")
                 handle = ctypes.CDLL(LIB_PATH)
                 for name, (res, args) in SIGNATURES.items():
+                    if not hasattr(handle, name):
+                        raise RuntimeError(f"{LIB_PATH} is older than this package (no symbol {name}): "
+                                           "rebuild it with `python torchsplinekan_b200/build.py`")
                     fn = getattr(handle, name)
                     fn.restype, fn.argtypes = res, args
                 _lib = handle

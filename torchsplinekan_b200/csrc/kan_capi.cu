@@ -244,6 +244,33 @@ KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, c
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean");
 }
 
+KANB200_API int kanb200_edge_abs_mean_noalloc(int dtype, const void* s, const void* H, const void* bw,
+                                               const void* W, void* a, int64_t N, int64_t I, int64_t O, int R,
+                                               void* stream) {
+    int rc = check_edge(dtype, N, I, O, R);
+    if (rc) return rc;
+    if (!H || !W || !a) return fail(KANB200_EINVAL, "edge_abs_mean_noalloc: NULL pointer");
+    if ((s == nullptr) != (bw == nullptr))
+        return fail(KANB200_EINVAL, "edge_abs_mean_noalloc: s and base_weight must both be given or both be absent");
+    const size_t need = dtype == KANB200_F32 ? edge_workspace<float>(N, (int)I, (int)O, R, false)
+                                             : edge_workspace<double>(N, (int)I, (int)O, R, false);
+    if (need > edge_static_scratch_bytes())
+        return fail(KANB200_EWORKSPACE,
+                    "edge_abs_mean_noalloc: this shape needs %zu bytes of scratch, the built-in buffer holds %zu; "
+                    "use kanb200_edge_abs_mean with a caller-provided workspace",
+                    need, edge_static_scratch_bytes());
+    void* scratch = nullptr;
+    cudaError_t e = edge_static_scratch(&scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "edge_abs_mean_noalloc (scratch address)");
+    cudaStream_t st = (cudaStream_t)stream;
+    e = dtype == KANB200_F32
+            ? edge_abs_mean_fwd<float>((const float*)s, (const float*)H, (const float*)bw, (const float*)W, (float*)a,
+                                       N, (int)I, (int)O, R, scratch, edge_static_scratch_bytes(), st)
+            : edge_abs_mean_fwd<double>((const double*)s, (const double*)H, (const double*)bw, (const double*)W,
+                                        (double*)a, N, (int)I, (int)O, R, scratch, edge_static_scratch_bytes(), st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_noalloc");
+}
+
 KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a, const void* s, const void* H, const void* bw,
                                    const void* W, void* ds, void* dH, void* dbw, void* dW,
                                    int64_t N, int64_t I, int64_t O, int R,

@@ -50,6 +50,10 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
                               T* ds, T* dH, T* dbw, T* dW,
                               int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// Fixed device scratch of the allocation-free edge statistic (kan_reg.cu).
+size_t edge_static_scratch_bytes();
+cudaError_t edge_static_scratch(void** ptr);
+
 // ---- tensor-core path (kan_tc.cu), fp32 I/O ---------------------------------
 bool tc_supported(const LayerShape& s);
 size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param);

@@ -309,6 +309,35 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
     return e;
 }
 
+// ---------------------------------------------------------------------------
+// Edge statistic without caller-provided scratch
+// ---------------------------------------------------------------------------
+// Fixed scratch for kanb200_edge_abs_mean_noalloc: the per-split partial sums of the forward
+// statistic.  4 MiB per GPU that loads the library, held until the process exits.
+constexpr size_t kStaticEdgeScratchBytes = 4u << 20;
+static __device__ __align__(256) unsigned char g_edge_scratch[kStaticEdgeScratchBytes];
+
+size_t edge_static_scratch_bytes() { return kStaticEdgeScratchBytes; }
+
+// Device address of g_edge_scratch on the CURRENT device.  In host code the symbol is only a
+// handle, so the address is looked up once per device (cudaGetSymbolAddress) and cached.
+cudaError_t edge_static_scratch(void** ptr) {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    void* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        e = cudaGetSymbolAddress(&p, g_edge_scratch);
+        if (e != cudaSuccess) return e;
+        __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);      // same value from every thread
+    }
+    *ptr = p;
+    return cudaSuccess;
+}
+
 #define KAN_INSTANTIATE(T)                                                                               \
     template size_t edge_workspace<T>(int64_t, int, int, int, bool);                                     \
     template cudaError_t edge_abs_mean_fwd<T>(const T*, const T*, const T*, const T*, T*, int64_t, int,  \
