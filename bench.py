@@ -281,6 +281,83 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_micro(args):
+    """Times the secondary kernels of the path one by one (CUDA events, inputs larger than L2) and
+    prints one JSON line per kernel: achieved GB/s against the measured HBM peak for the
+    bandwidth-bound ones, achieved GFLOP/s for the FMA-bound ones.  Not the headline benchmark."""
+    import torch
+    from torchsplinekan_b200 import _native as nat
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    _, hbm_peak, src = measured_peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def timeit(fn, reps=args.steps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+        ev[0].record()
+        for r in range(reps):
+            fn()
+            ev[r + 1].record()
+        torch.cuda.synchronize()
+        return statistics.median(ev[r].elapsed_time(ev[r + 1]) for r in range(reps))
+
+    def emit(name, ms, bytes_=None, flops=None, **extra):
+        line = {"kernel": name, "ms": ms}
+        if bytes_ is not None:
+            line.update(bound="hbm", achieved=bytes_ / ms / 1e6, peak=hbm_peak, unit="GB/s",
+                        frac=bytes_ / ms / 1e6 / hbm_peak, peak_source=f"of {src}")
+        if flops is not None:
+            line.update(gflops=flops / ms / 1e6)
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+
+    # standalone basis / basis gradient: N x I x (R+1) elements, fp32, c1 feature count
+    N, I, G, k = args.micro_rows, 1024, 5, 3
+    R = G + k
+    x = torch.randn(N, I, device=dev, generator=g).clamp_(-1, 1)
+    grid = ((torch.arange(G + 2 * k + 1, device=dev, dtype=torch.float32) - k) * (2.0 / G) - 1.0)[None] \
+        .expand(I, -1).contiguous()
+    ms = timeit(lambda: nat.basis(x, grid, k))
+    emit("basis_kernel<float,3>", ms, bytes_=4.0 * N * I * (R + 1), rows=N, I=I)
+    gH = torch.randn(N, I, R, device=dev, generator=g)
+    ms = timeit(lambda: nat.basis_grad(x, grid, k, gH))
+    emit("basis_grad_kernel<float,3>", ms, bytes_=4.0 * N * I * (R + 2), rows=N, I=I)
+    del gH
+
+    # edge statistic on the first layer of the 784-256-256-10 network (8192 rows)
+    Ne, Ie, Oe = 8192, 784, 256
+    H = torch.rand(Ne, Ie, R, device=dev, generator=g)
+    s = torch.randn(Ne, Ie, device=dev, generator=g)
+    bw = torch.randn(Oe, Ie, device=dev, generator=g)
+    W = torch.randn(Oe, Ie, R, device=dev, generator=g)
+    ga = torch.rand(Oe, Ie, device=dev, generator=g)
+    fl = 2.0 * Ne * Oe * Ie * (R + 1)
+    ms = timeit(lambda: nat.edge_abs_mean(s, H, bw, W))
+    emit("edge_param_kernel<forward>", ms, flops=fl, bytes_moved_GB=4e-9 * (Ne * Ie * (R + 1) + Oe * Ie * (R + 2)))
+    ms = timeit(lambda: nat.edge_abs_mean_backward(ga, s, H, bw, W, False, False, True, True))
+    emit("edge_param_kernel<grad> + sum_slabs", ms, flops=2 * fl)
+    ms = timeit(lambda: nat.edge_abs_mean_backward(ga, s, H, bw, W, True, True, False, False))
+    emit("edge_input_kernel", ms, flops=2 * fl)
+    del H, s, W
+
+    # float64 SIMT layer (PINN-style 64 -> 64, G = 8)
+    Nd, Id, Od, Gd = 131072, 64, 64, 8
+    xd = torch.rand(Nd, Id, device=dev, dtype=torch.float64, generator=g) * 2 - 1
+    gd = ((torch.arange(Gd + 2 * k + 1, device=dev, dtype=torch.float64) - k) * (2.0 / Gd) - 1.0)[None] \
+        .expand(Id, -1).contiguous()
+    bwd_ = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
+    swd = torch.randn(Od, Id, Gd + k, device=dev, dtype=torch.float64, generator=g)
+    scd = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
+    ms = timeit(lambda: nat.forward(xd, gd, bwd_, swd, scd, k, nat.MODE_SIMT))
+    emit("fwd_simt_kernel<double,3>", ms, flops=2.0 * Nd * Od * Id * (k + 2), note="useful flops: k+2 terms per edge")
+    D = torch.randn(Nd, Od, device=dev, dtype=torch.float64, generator=g)
+    ms = timeit(lambda: nat.backward(D, xd, gd, bwd_, swd, scd, k, True, True, True, True, nat.MODE_SIMT))
+    emit("bwd_simt (param + input)<double,3>", ms, flops=4.0 * Nd * Od * Id * (k + 2))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -290,8 +367,12 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--mode", default=None, choices=[None, "auto", "simt", "bf16x3", "bf16x1"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", action="store_true", help="time the secondary kernels instead of the training step")
+    ap.add_argument("--micro-rows", type=int, default=16384)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

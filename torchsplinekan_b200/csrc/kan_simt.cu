@@ -53,6 +53,93 @@ __global__ void basis_kernel(const T* __restrict__ x, const T* __restrict__ grid
     }
 }
 
+// R == 8, float: one pair per lane, then the warp's 32 rows (1 KB) leave as 64 float4 in two fully
+// coalesced store instructions; the row pieces are fetched from the owning lane by shuffles.
+template <int K>
+__global__ void __launch_bounds__(256)
+basis_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid, float* __restrict__ H,
+                int64_t pairs, int I, int G) {
+    __shared__ float knots_s[256 / 32][32][13];           // per warp: this lane's knot row (conflict-free stride)
+    const int nk = G + 2 * K + 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t wbase = ((int64_t)blockIdx.x * (blockDim.x >> 5) + warp) * 32; wbase < pairs;
+         wbase += warps_total * 32) {
+        const int64_t idx = wbase + lane;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        int s = 0;
+        if (idx < pairs) {
+            const int i = (int)(idx % I);
+            float* t = &knots_s[warp][lane][0];
+            for (int q = 0; q < nk; ++q) t[q] = __ldg(grid + (size_t)i * nk + q);
+            const float xv = x[idx];
+            const int m = find_span<float>(t, nk, xv);
+            if (m >= 0) {
+                float w[K + 1], d[K + 1];
+                local_basis<K, float, false>(t, nk, m, xv, w, d);
+                s = m - K;
+#pragma unroll
+                for (int j = 0; j <= K; ++j) v[j] = w[j];
+            } else {
+                s = -100;                                  // nothing lands in [0, 8)
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int q4 = lane + 32 * h;                  // float4 index within the warp's 64
+            const int src = q4 >> 1;                       // lane that owns the pair
+            const int r0 = (q4 & 1) * 4;                   // first slot of this float4
+            float pv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pv[j] = __shfl_sync(0xffffffffu, v[j], src);
+            const int ps = __shfl_sync(0xffffffffu, s, src);
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = r0 + e - ps;                 // index into the window, valid 0..K
+                float val = 0.f;
+#pragma unroll
+                for (int jj = 0; jj <= K; ++jj) val = (j == jj) ? pv[jj] : val;
+                o[e] = val;
+            }
+            if (wbase + src < pairs)
+                reinterpret_cast<float4*>(H + wbase * 8)[q4] = make_float4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// R == 8, float: each lane reads its whole 32-byte gradient row with two 16-byte loads.
+template <int K>
+__global__ void __launch_bounds__(256)
+basis_grad_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid, const float* __restrict__ gH,
+                     float* __restrict__ gx, int64_t pairs, int I, int G) {
+    const int nk = G + 2 * K + 1;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < pairs;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int i = (int)(idx % I);
+        const float* t = grid + (size_t)i * nk;
+        const float4 a = __ldg(reinterpret_cast<const float4*>(gH + idx * 8));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(gH + idx * 8) + 1);
+        const float g[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const float xv = x[idx];
+        const int m = find_span<float>(t, nk, xv);
+        float acc = 0.f;
+        if (m >= 0) {
+            float v[K + 1], d[K + 1];
+            local_basis<K, float, true>(t, nk, m, xv, v, d);
+#pragma unroll
+            for (int j = 0; j <= K; ++j) {
+                const int r = m - K + j;
+                float gr = 0.f;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) gr = (r == q) ? g[q] : gr;
+                acc += gr * d[j];
+            }
+        }
+        gx[idx] = acc;
+    }
+}
+
 template <typename T, int K>
 __global__ void basis_grad_kernel(const T* __restrict__ x, const T* __restrict__ grid,
                                   const T* __restrict__ gH, T* __restrict__ gx,
@@ -471,6 +558,13 @@ cudaError_t simt_basis(const T* x, const T* grid, T* H, const LayerShape& s, cud
     const int64_t pairs = s.N * s.I;
     if (pairs == 0) return cudaSuccess;
     const int R = s.R();
+    if (sizeof(T) == 4 && R == 8 && s.T() <= 13 && (reinterpret_cast<uintptr_t>(H) & 15) == 0) {
+        const int blocks = grid_1d((pairs + 31) / 32, 8, 148 * 8);
+        KAN_DISPATCH_K(s.K, (basis_r8_kernel<KK><<<blocks, 256, 0, st>>>(
+                                 reinterpret_cast<const float*>(x), reinterpret_cast<const float*>(grid),
+                                 reinterpret_cast<float*>(H), pairs, s.I, s.G)));
+        return cudaGetLastError();
+    }
     int P = 128;
     while (P > 32 && (size_t)P * R * sizeof(T) > 40 * 1024) P >>= 1;
     const size_t smem = (size_t)P * R * sizeof(T);
@@ -484,6 +578,12 @@ cudaError_t simt_basis_grad(const T* x, const T* grid, const T* gH, T* gx, const
     const int64_t pairs = s.N * s.I;
     if (pairs == 0) return cudaSuccess;
     const int blocks = grid_1d(pairs, 256);
+    if (sizeof(T) == 4 && s.R() == 8 && (reinterpret_cast<uintptr_t>(gH) & 15) == 0) {
+        KAN_DISPATCH_K(s.K, (basis_grad_r8_kernel<KK><<<blocks, 256, 0, st>>>(
+                                 reinterpret_cast<const float*>(x), reinterpret_cast<const float*>(grid),
+                                 reinterpret_cast<const float*>(gH), reinterpret_cast<float*>(gx), pairs, s.I, s.G)));
+        return cudaGetLastError();
+    }
     KAN_DISPATCH_K(s.K, (basis_grad_kernel<T, KK><<<blocks, 256, 0, st>>>(x, grid, gH, gx, pairs, s.I, s.G)));
     return cudaGetLastError();
 }

@@ -202,6 +202,35 @@ __device__ __forceinline__ void eval_feature_row(const float* __restrict__ ftab,
     if (SPLIT) lo = place(l01, l23);
 }
 
+// Derivatives of the window functions of one input from its feature's table:
+// d/du (c0 + c1 u + c2 u^2 + c3 u^3) = c1 + 2 c2 u + 3 c3 u^2.  Returns the window start; inputs
+// outside the knot range select the all-zero entry.
+template <bool SMEM_TAB>
+__device__ __forceinline__ int eval_feature_deriv(const float* __restrict__ ftab, float xv, float (&d)[4]) {
+    auto ld4 = [](const float4* p) -> float4 { return SMEM_TAB ? *p : __ldg(p); };
+    const float4 k0 = ld4(reinterpret_cast<const float4*>(ftab));
+    const float4 k1 = ld4(reinterpret_cast<const float4*>(ftab) + 1);
+    const float4 k2 = ld4(reinterpret_cast<const float4*>(ftab) + 2);
+    const bool inside = (xv >= k0.x) && (xv <= k2.w);
+    int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
+            (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
+    m = inside ? m : TAB_ZERO_ENTRY;
+    const float4* ent = reinterpret_cast<const float4*>(ftab + 16 + m * TAB_ENTRY_FLOATS);
+    const float4 c0 = ld4(ent), c1 = ld4(ent + 1), c2 = ld4(ent + 2), c3 = ld4(ent + 3), meta = ld4(ent + 4);
+    const float u = xv - meta.x;
+    d[0] = fmaf(fmaf(3.0f * c0.w, u, 2.0f * c0.z), u, c0.y);
+    d[1] = fmaf(fmaf(3.0f * c1.w, u, 2.0f * c1.z), u, c1.y);
+    d[2] = fmaf(fmaf(3.0f * c2.w, u, 2.0f * c2.z), u, c2.y);
+    d[3] = fmaf(fmaf(3.0f * c3.w, u, 2.0f * c3.z), u, c3.y);
+    return __float_as_int(meta.y);
+}
+
+// sigma(x) (1 + x (1 - sigma(x)))
+__device__ __forceinline__ float silu_grad_fast(float x) {
+    const float sg = __fdividef(1.0f, 1.0f + __expf(-x));
+    return sg * fmaf(x, 1.0f - sg, 1.0f);
+}
+
 // 8 consecutive silu values -> one 16-byte chunk (hi) and one (lo).
 template <bool SPLIT>
 __device__ __forceinline__ void silu_chunk(const float (&xv)[8], uint4& hi, uint4& lo) {
@@ -1052,6 +1081,361 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 }
 
+// ---------------------------------------------------------------------------
+// Input-gradient kernel:
+//   DW[n, c] = sum_o dY[n, o] W[o, c]                       (tensor cores, K = outputs)
+//   gx[n, f] = sum_j DW[n, 8 f + s + j] dB_j/dx(x[n,f]) + DW[n, CS + f] silu'(x[n,f])
+// ---------------------------------------------------------------------------
+// Both operands already exist as images: the dY image of the parameter-gradient kernel read as a
+// K-major A operand (rows = samples, 128 B = 64 outputs) and the forward's weight image read as an
+// MN-major B operand (rows = outputs, 128 B = 64 columns), so nothing is generated here: the 16
+// worker warps only run the epilogue, which contracts every group of 8 accumulator columns with
+// the derivative of the basis.  Work item = (128 samples, 256 features): one sub-tile of 256 base
+// columns (stores gx) followed by eight sub-tiles of 32 features x 8 slots (add to gx); the two
+// 256-column accumulators in TMEM alternate between consecutive sub-tiles.
+constexpr int DX_A_STAGES = 2, DX_B_SLOTS = 5;
+constexpr uint32_t DX_A_STAGE_BYTES = 2 * TILE_A_BYTES;                  // hi + lo, 128 n x 64 o
+constexpr uint32_t DX_SMEM_A = 0;
+constexpr uint32_t DX_SMEM_B = DX_SMEM_A + DX_A_STAGES * DX_A_STAGE_BYTES;
+constexpr uint32_t DX_SMEM_CTRL = DX_SMEM_B + DX_B_SLOTS * TILE_B_BYTES;
+constexpr uint32_t DX_CTRL_BYTES = 256 + TAB_FEATURE_FLOATS * 4;
+constexpr uint32_t DX_SMEM_BYTES = DX_SMEM_CTRL + DX_CTRL_BYTES;
+static_assert(DX_SMEM_BYTES <= 232448, "input-gradient kernel shared memory exceeds 227 KB");
+
+struct DxCtrl {
+    uint64_t fullA[DX_A_STAGES], emptyA[DX_A_STAGES];
+    uint64_t fullB[DX_B_SLOTS], emptyB[DX_B_SLOTS];
+    uint64_t accFull[2], accEmpty[2];
+    uint64_t epiDone;      // workers: the previous sub-tile's gx stores are visible
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(DxCtrl) <= 256, "control block too large");
+
+struct DxParams {
+    int64_t N;
+    int I, O;
+    int kb_spline, kb_total;       // column blocks of the forward weight image
+    int n_otiles;                  // 256-output tiles of the weight image
+    int n_ohalves;                 // 128-output groups of the dY image
+    int64_t n_blocks64;            // 64-sample blocks of the dY image
+    int kb_o;                      // 64-output k-blocks
+    int n_fgroups;                 // groups of 256 features
+    int has_base;
+    int64_t n_items;
+    int vec_ok;
+};
+
+template <int NTERMS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ dyimg,
+                    const uint8_t* __restrict__ wimg, float* __restrict__ gx, int* __restrict__ status,
+                    const DxParams P) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr bool SPLIT = (NTERMS == 3);
+    const uint32_t sbase = smem_u32(smem);
+    DxCtrl* ctrl = reinterpret_cast<DxCtrl*>(smem + DX_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + DX_SMEM_CTRL + 256);
+    volatile int* abort_flag = &ctrl->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool shared_grid = status[1] != 0;
+    if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
+
+    if ((sbase & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DX_A_STAGES; ++s) {
+            mbar_init(smem_u32(&ctrl->fullA[s]), 1);
+            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
+        }
+        for (int s = 0; s < DX_B_SLOTS; ++s) {
+            mbar_init(smem_u32(&ctrl->fullB[s]), 1);
+            mbar_init(smem_u32(&ctrl->emptyB[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&ctrl->accFull[s]), 1);
+            mbar_init(smem_u32(&ctrl->accEmpty[s]), WORKER_THREADS);
+        }
+        mbar_init(smem_u32(&ctrl->epiDone), WORKER_THREADS);
+        ctrl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    const int n_sub = P.has_base ? 9 : 8;                   // sub-tiles per item
+    // sub-tile j of feature group fg -> first column block of the weight image, and whether it is
+    // the base sub-tile
+    auto sub_info = [&](int fg, int j, bool& is_base, int& cb0) {
+        is_base = P.has_base && j == 0;
+        const int t = P.has_base ? j - 1 : j;               // spline sub-tile index 0..7
+        cb0 = is_base ? P.kb_spline + fg * 4 : (fg * 8 + t) * 4;
+    };
+
+    if (warp < WORKER_WARPS) {
+        // ===== workers: epilogue only =====
+        const int quad = warp & 3, part = warp >> 2;
+        const int row = quad * 32 + lane;
+        uint32_t sub = 0;                                   // running sub-tile counter
+        for (int64_t item = blockIdx.x; item < P.n_items; item += gridDim.x) {
+            const int64_t mt = item / P.n_fgroups;
+            const int fg = (int)(item - mt * P.n_fgroups);
+            const int64_t n = mt * BLOCK_M + row;
+            const bool row_ok = n < P.N;
+            const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
+            float* grow = gx + (size_t)(row_ok ? n : 0) * P.I;
+            bool ok = true;
+            for (int j = 0; j < n_sub; ++j, ++sub) {
+                bool is_base;
+                int cb0;
+                sub_info(fg, j, is_base, cb0);
+                const uint32_t buf = sub & 1u;
+                if (!mbar_wait(smem_u32(&ctrl->accFull[buf]), (sub >> 1) & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                // gx of this item was (partly) written by other threads in the previous sub-tile
+                if (sub > 0 && !mbar_wait(smem_u32(&ctrl->epiDone), (sub - 1) & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+#pragma unroll 1
+                for (int c = part; c < BLOCK_N / 32; c += 4) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BLOCK_N + c * 32, r);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    if (is_base) {
+                        const int f0 = fg * 256 + c * 32;           // 32 features
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int f = f0 + 4 * q;
+                            if (f >= P.I) break;
+                            float xv[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (P.vec_ok && f + 4 <= P.I) {
+                                const float4 v = __ldg(reinterpret_cast<const float4*>(xrow + f));
+                                xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+                            } else {
+                                for (int e = 0; e < 4; ++e)
+                                    if (f + e < P.I) xv[e] = __ldg(xrow + f + e);
+                            }
+                            float o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) o[e] = __uint_as_float(r[4 * q + e]) * silu_grad_fast(xv[e]);
+                            if (P.vec_ok && f + 4 <= P.I) {
+                                *reinterpret_cast<float4*>(grow + f) = make_float4(o[0], o[1], o[2], o[3]);
+                            } else {
+                                for (int e = 0; e < 4; ++e)
+                                    if (f + e < P.I) grow[f + e] = o[e];
+                            }
+                        }
+                    } else {
+                        const int t = P.has_base ? j - 1 : j;
+                        const int f0 = fg * 256 + t * 32 + c * 4;   // 4 features x 8 slots
+                        if (f0 >= P.I) continue;
+                        float xv[4] = {0.f, 0.f, 0.f, 0.f};
+                        if (P.vec_ok && f0 + 4 <= P.I) {
+                            const float4 v = __ldg(reinterpret_cast<const float4*>(xrow + f0));
+                            xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+                        } else {
+                            for (int e = 0; e < 4; ++e)
+                                if (f0 + e < P.I) xv[e] = __ldg(xrow + f0 + e);
+                        }
+                        float o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int f = f0 + e;
+                            float d[4];
+                            int s;
+                            if (shared_grid)
+                                s = eval_feature_deriv<true>(stab, xv[e], d);
+                            else
+                                s = eval_feature_deriv<false>(tab + (size_t)(f < P.I ? f : P.I - 1) * TAB_FEATURE_FLOATS,
+                                                              xv[e], d);
+                            float acc = 0.f;
+#pragma unroll
+                            for (int slot = 0; slot < 8; ++slot) {
+                                const int jj = slot - s;               // window index of this slot
+                                float dv = 0.f;
+#pragma unroll
+                                for (int w = 0; w < 4; ++w) dv = (jj == w) ? d[w] : dv;
+                                acc = fmaf(__uint_as_float(r[8 * e + slot]), dv, acc);
+                            }
+                            o[e] = acc;
+                        }
+                        if (P.vec_ok && f0 + 4 <= P.I) {
+                            float4* dst = reinterpret_cast<float4*>(grow + f0);
+                            if (P.has_base) {
+                                const float4 old = *dst;
+                                o[0] += old.x; o[1] += old.y; o[2] += old.z; o[3] += old.w;
+                            }
+                            *dst = make_float4(o[0], o[1], o[2], o[3]);
+                        } else {
+                            for (int e = 0; e < 4; ++e)
+                                if (f0 + e < P.I) grow[f0 + e] = P.has_base ? grow[f0 + e] + o[e] : o[e];
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->accEmpty[buf]));
+                mbar_arrive(smem_u32(&ctrl->epiDone));
+            }
+            if (!ok) break;
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, false, true);       // A K-major, B MN-major
+            constexpr uint64_t da = make_sdesc_sw128(16, 1024);
+            constexpr uint64_t db = make_sdesc_sw128(8192, 1024);
+            uint32_t it = 0, bslot = 0, sub = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
+                for (int j = 0; j < n_sub && ok; ++j, ++sub) {
+                    const uint32_t buf = sub & 1u;
+                    if (!mbar_wait(smem_u32(&ctrl->accEmpty[buf]), ((sub >> 1) & 1u) ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+                    for (int ko = 0; ko < P.kb_o; ++ko, ++it) {
+                        const uint32_t stage = it % DX_A_STAGES;
+                        const uint32_t a_hi = sbase + DX_SMEM_A + stage * DX_A_STAGE_BYTES;
+                        const uint32_t a_lo = a_hi + TILE_A_BYTES;
+                        const uint32_t slot_h = bslot % DX_B_SLOTS;
+                        if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / DX_A_STAGES) & 1u, abort_flag) ||
+                            !mbar_wait(smem_u32(&ctrl->fullB[slot_h]), (bslot / DX_B_SLOTS) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t b_hi = sbase + DX_SMEM_B + slot_h * TILE_B_BYTES;
+#pragma unroll
+                        for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                            mma_f16_ss(d_tmem, sdesc_at(da, a_hi + ks * 32), sdesc_at(db, b_hi + ks * 2048), idesc,
+                                       (ko > 0 || ks > 0) ? 1u : 0u);
+                        if (SPLIT) {
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ss(d_tmem, sdesc_at(da, a_lo + ks * 32), sdesc_at(db, b_hi + ks * 2048),
+                                           idesc, 1u);
+                        }
+                        mma_commit(smem_u32(&ctrl->emptyB[slot_h]));
+                        ++bslot;
+                        if (SPLIT) {
+                            const uint32_t slot_l = bslot % DX_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->fullB[slot_l]), (bslot / DX_B_SLOTS) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t b_lo = sbase + DX_SMEM_B + slot_l * TILE_B_BYTES;
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ss(d_tmem, sdesc_at(da, a_hi + ks * 32), sdesc_at(db, b_lo + ks * 2048),
+                                           idesc, 1u);
+                            mma_commit(smem_u32(&ctrl->emptyB[slot_l]));
+                            ++bslot;
+                        }
+                        mma_commit(smem_u32(&ctrl->emptyA[stage]));
+                    }
+                    if (ok) mma_commit(smem_u32(&ctrl->accFull[buf]));
+                }
+            }
+        }
+    } else {
+        if (lane == 0) {
+            // ===== bulk copies: dY tiles (A) and weight tiles (B) =====
+            uint32_t it = 0, bslot = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
+                const int64_t mt = item / P.n_fgroups;
+                const int fg = (int)(item - mt * P.n_fgroups);
+                for (int j = 0; j < n_sub && ok; ++j) {
+                    bool is_base;
+                    int cb0;
+                    sub_info(fg, j, is_base, cb0);
+                    for (int ko = 0; ko < P.kb_o && ok; ++ko, ++it) {
+                        // A: 128 samples x 64 outputs = two 64-sample blocks of the dY image
+                        const uint32_t stage = it % DX_A_STAGES;
+                        if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / DX_A_STAGES) & 1u) ^ 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        {
+                            const uint32_t bar = smem_u32(&ctrl->fullA[stage]);
+                            const int terms = SPLIT ? 2 : 1;
+                            // the second 64-sample block may lie beyond the batch: its rows are then
+                            // left as they are (they only feed accumulator rows that are never stored)
+                            const int halves = (mt * 2 + 1 < P.n_blocks64) ? 2 : 1;
+                            mbar_arrive_expect_tx(bar, (uint32_t)(terms * halves) * 8192u);
+                            const int oh = ko >> 1, og = ko & 1;
+                            for (int term = 0; term < terms; ++term)
+                                for (int hn = 0; hn < halves; ++hn) {
+                                    const int64_t nb = mt * 2 + hn;
+                                    const uint8_t* src = dyimg + (((size_t)nb * P.n_ohalves + oh) * 2 + term) * TILE_A_BYTES +
+                                                         (size_t)og * 8192;
+                                    bulk_g2s(sbase + DX_SMEM_A + stage * DX_A_STAGE_BYTES + term * TILE_A_BYTES + hn * 8192,
+                                             src, 8192, bar);
+                                }
+                        }
+                        // B: 256 columns x 64 outputs = four column blocks of the weight image
+                        const int ot = ko >> 2, og8 = ko & 3;
+                        int n_cb = P.kb_total - cb0;
+                        if (is_base) {
+                            const int left = P.kb_total - cb0;
+                            n_cb = left < 4 ? left : 4;
+                        } else {
+                            const int left = P.kb_spline - cb0;
+                            n_cb = left < 4 ? left : 4;
+                        }
+                        if (n_cb < 0) n_cb = 0;
+                        for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
+                            const uint32_t slot = bslot % DX_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->emptyB[slot]), ((bslot / DX_B_SLOTS) & 1u) ^ 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
+                            if (n_cb == 0) {
+                                mbar_arrive(bar);
+                            } else {
+                                mbar_arrive_expect_tx(bar, (uint32_t)n_cb * 8192u);
+                                for (int cg = 0; cg < n_cb; ++cg) {
+                                    const uint8_t* src = wimg + (((size_t)ot * P.kb_total + cb0 + cg) * 2 + term) * TILE_B_BYTES +
+                                                         (size_t)og8 * 8192;
+                                    bulk_g2s(sbase + DX_SMEM_B + slot * TILE_B_BYTES + cg * 8192, src, 8192, bar);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        if (lane == 0) atomicExch(status, kStatusTimeout);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // Sums the per-split slabs (blocked layout of the drain) and applies the scaler algebra:
 // gsw = scaler * D, gscaler = sum_r sw * D, gbw = base column.  Thread = (feature, output) with the
 // output index fastest, so the 16-byte reads of a warp are contiguous.
@@ -1189,11 +1573,10 @@ size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param) {
     // Sized for a layer with a base branch (the larger case).
     if (op == 0) return kWsHeader + table_bytes(s) + align256(fwd_layout(s, true).wimg_bytes);
     size_t b = kWsHeader + table_bytes(s);
-    if (need_param) {
-        BwdLayout L = bwd_layout(s, true);
-        b += align256(L.dyimg_bytes) + align256(L.partial_bytes);
-    }
-    (void)need_x;
+    BwdLayout L = bwd_layout(s, true);
+    if (need_param || need_x) b += align256(L.dyimg_bytes);
+    if (need_param) b += align256(L.partial_bytes);
+    if (need_x) b += align256(fwd_layout(s, true).wimg_bytes);
     return b;
 }
 
@@ -1250,27 +1633,37 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
     cudaError_t e = cudaSuccess;
     const bool has_base = bw != nullptr;
     const bool need_param = gsw || gscaler || (gbw && has_base);
+    const bool need_x = gx != nullptr;
     if (s.N == 0) return simt_backward<float>(dY, x, grid, bw, sw, scaler, gx, gbw, gsw, gscaler, s, nullptr, 0, st);
+    if (!need_param && !need_x) return cudaSuccess;
+
+    BwdLayout L = bwd_layout(s, has_base);
+    FwdLayout F = fwd_layout(s, has_base);
+    size_t need = kWsHeader + table_bytes(s) + align256(L.dyimg_bytes);
+    if (need_param) need += align256(L.partial_bytes);
+    if (need_x) need += F.wimg_bytes;
+    if (!ws || ws_bytes < need) return cudaErrorMemoryAllocation;
+    int* status = reinterpret_cast<int*>(ws);
+    float* tab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kWsHeader);
+    uint8_t* dyimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
+    uint8_t* cursor = dyimg + align256(L.dyimg_bytes);
+    float* partial = reinterpret_cast<float*>(cursor);
+    if (need_param) cursor += align256(L.partial_bytes);
+    uint8_t* wimg = cursor;
+
+    if ((e = cudaMemsetAsync(status, 0, sizeof(int), st)) != cudaSuccess) return e;
+    if ((e = launch_table(grid, tab, status + 1, s, st)) != cudaSuccess) return e;
+    {
+        const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
+        int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
+                                                                            : (int64_t)sm_count() * 16);
+        pack_grad_out_kernel<<<blocks, 256, 0, st>>>(dY, dyimg, s.N, s.O, L.plan.kb_total, L.plan.n_otiles * 2);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (need_param) {
-        BwdLayout L = bwd_layout(s, has_base);
-        const size_t need = kWsHeader + table_bytes(s) + align256(L.dyimg_bytes) + L.partial_bytes;
-        if (!ws || ws_bytes < need) return cudaErrorMemoryAllocation;
-        int* status = reinterpret_cast<int*>(ws);
-        float* tab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kWsHeader);
-        uint8_t* dyimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
-        float* partial = reinterpret_cast<float*>(dyimg + align256(L.dyimg_bytes));
-        {
-            if ((e = cudaMemsetAsync(status, 0, sizeof(int), st)) != cudaSuccess) return e;
-            if ((e = launch_table(grid, tab, status + 1, s, st)) != cudaSuccess) return e;
-            const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
-            int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
-                                                                                : (int64_t)sm_count() * 16);
-            pack_grad_out_kernel<<<blocks, 256, 0, st>>>(dY, dyimg, s.N, s.O, L.plan.kb_total, L.plan.n_otiles * 2);
-            if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        }
         const int64_t items = L.plan.n_items();
         const int blocks = (int)(items < sm_count() ? items : sm_count());
-        const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
 #define KAN_BWD(NT)                                                                                           \
     do {                                                                                                      \
         e = cudaFuncSetAttribute(tc_bwd_param_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
@@ -1283,18 +1676,45 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
 #undef KAN_BWD
         if (e != cudaSuccess) return e;
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        {
-            const int64_t work = (int64_t)s.O * s.I;
-            const int fblocks = (int)((work + 255) / 256);
-            finalize_blocked_kernel<<<fblocks, 256, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
-                                                             has_base ? gbw : nullptr, s.O, s.I, s.R());
-            e = cudaGetLastError();
-        }
-        if (e != cudaSuccess) return e;
+        const int64_t work = (int64_t)s.O * s.I;
+        const int fblocks = (int)((work + 255) / 256);
+        finalize_blocked_kernel<<<fblocks, 256, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
+                                                         has_base ? gbw : nullptr, s.O, s.I, s.R());
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
-    if (gx) {
-        // Input gradient: gather formulation on the FMA pipes.
-        e = simt_backward<float>(dY, x, grid, bw, sw, scaler, gx, nullptr, nullptr, nullptr, s, nullptr, 0, st);
+    if (need_x) {
+        const int kb_total = F.cs.kb_total();
+        {
+            const int64_t chunks = (int64_t)F.n_otiles * kb_total * BLOCK_N * 8;
+            int blocks = (int)((chunks + 255) / 256);
+            if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+            pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), F.cs.kb_spline,
+                                                        kb_total, F.n_otiles);
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
+        DxParams P;
+        P.N = s.N; P.I = s.I; P.O = s.O;
+        P.kb_spline = F.cs.kb_spline; P.kb_total = kb_total;
+        P.n_otiles = F.n_otiles; P.n_ohalves = L.plan.n_otiles * 2;
+        P.n_blocks64 = L.plan.kb_total;
+        P.kb_o = (s.O + BLOCK_K - 1) / BLOCK_K;
+        P.n_fgroups = (s.I + 255) / 256;
+        P.has_base = has_base ? 1 : 0;
+        P.n_items = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_fgroups;
+        P.vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(gx) & 15) == 0);
+        const int blocks = (int)(P.n_items < sm_count() ? P.n_items : sm_count());
+#define KAN_DX(NT)                                                                                            \
+    do {                                                                                                      \
+        e = cudaFuncSetAttribute(tc_bwd_input_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                 (int)DX_SMEM_BYTES);                                                         \
+        if (e == cudaSuccess)                                                                                 \
+            tc_bwd_input_kernel<NT><<<blocks, TC_THREADS, DX_SMEM_BYTES, st>>>(x, tab, dyimg, wimg, gx,       \
+                                                                                status, P);                   \
+    } while (0)
+        if (split_terms == 3) KAN_DX(3); else KAN_DX(1);
+#undef KAN_DX
+        if (e != cudaSuccess) return e;
+        e = cudaGetLastError();
     }
     return e;
 }
