@@ -171,6 +171,8 @@ def run_gpu_arm(args):
     gen = torch.Generator().manual_seed(0)
     x_host = torch.randn(args.batch, IN_F, generator=gen).clamp_(-1, 1)[r0:r1].contiguous().pin_memory()
     x_dev = x_host.to(dev)
+    if args.need_x:
+        x_dev.requires_grad_(True)
     bucket = sk.GradientBucket([layer]) if world > 1 else None
 
     def step_resident():
@@ -179,6 +181,7 @@ def run_gpu_arm(args):
         else:
             for p in layer.parameters():
                 p.grad = None
+        x_dev.grad = None
         y = layer(x_dev)
         loss = y.square().sum()
         loss.backward()
@@ -186,10 +189,12 @@ def run_gpu_arm(args):
             bucket.finish()
         return loss
 
-    x_stage = torch.empty_like(x_dev)
+    x_stage = torch.empty_like(x_dev, requires_grad=bool(args.need_x))
 
     def step_e2e():
-        x_stage.copy_(x_host, non_blocking=True)
+        with torch.no_grad():
+            x_stage.copy_(x_host, non_blocking=True)
+        x_stage.grad = None
         if bucket is not None:
             bucket.zero_grad()
         else:
@@ -244,7 +249,7 @@ def run_gpu_arm(args):
         ms_step = ms_total / args.steps
         value = args.batch / (ms_step * 1e-3)
         dom = max(kernel_ms, key=kernel_ms.get) if kernel_ms else None
-        pass_flops = algorithmic_flops(rows) / 2
+        pass_flops = algorithmic_flops(rows) / 2 * (2 if (args.need_x and dom == "backward") else 1)
         achieved = pass_flops / (kernel_ms[dom] * 1e-3) / 1e12 if dom else None
         mode = _C.get_mma_mode()
         terms = 1 if mode == "bf16x1" else 3
@@ -252,14 +257,15 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "KANLinear 1024->1024 G=5 k=3 fp32, fwd+bwd of sum(y^2), x without grad",
+            "config": {"workload": "KANLinear 1024->1024 G=5 k=3 fp32, fwd+bwd of sum(y^2), x "
+                                   + ("with grad (input gradient computed)" if args.need_x else "without grad"),
                        "global_batch": args.batch, "rows_per_gpu": rows,
                        "parallelism": f"dp{world} batch shards + NCCL all-reduce of parameter gradients",
                        "mma_mode": "bf16x3 (hi/lo split operands, fp32-level accuracy)" if terms == 3 else mode,
                        "l2": "inputs larger than L2 (x and dY are 268 MB each at 65536 rows)"},
             "e2e": {"value": args.batch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": rows * IN_F * 4, "d2h_bytes_per_step": 4},
-            "gpu_launches": 5 * args.steps,
+            "gpu_launches": (11 if args.need_x else 9) * args.steps,
             "kernel_ms": kernel_ms,
             "roofline": {"bound": "tensor", "kernel": f"{dom} (tcgen05 contraction + operand producers)",
                          "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s",
@@ -367,6 +373,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--mode", default=None, choices=[None, "auto", "simt", "bf16x3", "bf16x1"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--need-x", action="store_true", help="also compute the input gradient (x.requires_grad)")
     ap.add_argument("--micro", action="store_true", help="time the secondary kernels instead of the training step")
     ap.add_argument("--micro-rows", type=int, default=16384)
     args = ap.parse_args()

@@ -31,6 +31,11 @@ __device__ __forceinline__ int find_span(const T* __restrict__ t, int nk, T x) {
     return lo;
 }
 
+// Quotient used inside the recurrence: IEEE division for double, the 2-ulp reciprocal-multiply
+// for float (the float kernels are compared at 1e-5, the double ones at 1e-12).
+template <typename T> __device__ __forceinline__ T ratio(T a, T b) { return a / b; }
+template <> __device__ __forceinline__ float ratio<float>(float a, float b) { return __fdividef(a, b); }
+
 // The K+1 basis functions that can be non-zero on span m are B_{m-K+j,K},
 // j = 0..K.  val[j] receives their values at x; with DERIV, der[j] receives
 // d/dx.  Built bottom-up over the degree (triangular de Boor table); knot
@@ -60,11 +65,11 @@ __device__ __forceinline__ void local_basis(const T* __restrict__ t, int nk, int
                 T a = T(0), b = T(0);
                 if (j >= 1) {           // B_{r,K-1}/(t_{r+K}-t_r), r = m-K+j
                     const T den = tk[K - 1 + j] - tk[j - 1];
-                    if (den != T(0)) a = nd[j - 1] / den;
+                    if (den != T(0)) a = ratio<T>(nd[j - 1], den);
                 }
                 if (j <= K - 1) {       // B_{r+1,K-1}/(t_{r+K+1}-t_{r+1})
                     const T den = tk[K + j] - tk[j];
-                    if (den != T(0)) b = nd[j] / den;
+                    if (den != T(0)) b = ratio<T>(nd[j], den);
                 }
                 der[j] = T(K) * (a - b);
             }
@@ -75,7 +80,7 @@ __device__ __forceinline__ void local_basis(const T* __restrict__ t, int nk, int
             const T hi_k = tk[K + j];               // t[m + j + 1]
             const T lo_k = tk[K - d + j];           // t[m + 1 - d + j]
             const T den = hi_k - lo_k;
-            const T w = (den != T(0)) ? nd[j] / den : T(0);
+            const T w = (den != T(0)) ? ratio<T>(nd[j], den) : T(0);
             nd[j] = carry + (hi_k - x) * w;
             carry = (x - lo_k) * w;
         }

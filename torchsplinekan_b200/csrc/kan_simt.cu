@@ -59,7 +59,6 @@ template <int K>
 __global__ void __launch_bounds__(256)
 basis_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid, float* __restrict__ H,
                 int64_t pairs, int I, int G) {
-    __shared__ float knots_s[256 / 32][32][13];           // per warp: this lane's knot row (conflict-free stride)
     const int nk = G + 2 * K + 1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t warps_total = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -70,8 +69,7 @@ basis_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid, flo
         int s = 0;
         if (idx < pairs) {
             const int i = (int)(idx % I);
-            float* t = &knots_s[warp][lane][0];
-            for (int q = 0; q < nk; ++q) t[q] = __ldg(grid + (size_t)i * nk + q);
+            const float* t = grid + (size_t)i * nk;           // knot rows stay in L1
             const float xv = x[idx];
             const int m = find_span<float>(t, nk, xv);
             if (m >= 0) {
