@@ -81,7 +81,12 @@ __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* _
     if (e == TAB_ENTRIES) {                    // knot block
         for (int q = 0; q < 11; ++q) out[q] = (q <= nk - 2) ? t[q] : __int_as_float(0x7f800000);
         out[11] = t[nk - 1];
-        for (int q = 12; q < 16; ++q) out[q] = 0.0f;
+        // slot 12: 1 when this knot row differs from the row of feature 0 (see grid_is_shared)
+        float differs = 0.0f;
+        for (int q = 0; q < nk; ++q)
+            if (t[q] != grid[q]) differs = 1.0f;
+        out[12] = differs;
+        for (int q = 13; q < 16; ++q) out[q] = 0.0f;
         return;
     }
     float* ent = out + 16 + e * TAB_ENTRY_FLOATS;
@@ -132,19 +137,15 @@ __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* _
     ent[19] = 0.0f;
 }
 
-// flag[0] = 1 when every feature has the knot row of feature 0 (the default uniform grid): the
-// kernels then keep that single 1-KB table in shared memory instead of reading per-feature
-// tables through L1.
-__global__ void grid_shared_kernel(const float* __restrict__ grid, int* __restrict__ flag, int I, int nk) {
-    __shared__ int differs;
-    if (threadIdx.x == 0) differs = 0;
-    __syncthreads();
-    int d = 0;
-    for (int e = threadIdx.x; e < I * nk; e += blockDim.x)
-        if (grid[e] != grid[e % nk]) d = 1;
-    if (d) differs = 1;
-    __syncthreads();
-    if (threadIdx.x == 0) *flag = differs ? 0 : 1;
+// True when every feature has the knot row of feature 0 (the default uniform grid): the kernels
+// then keep that single 1-KB table in shared memory instead of reading per-feature tables through
+// L1.  Block-wide vote over the per-feature flags the table kernel left in slot 12; every thread
+// of the CTA must call it.
+__device__ __forceinline__ bool grid_is_shared(const float* __restrict__ tab, int I) {
+    int differs = 0;
+    for (int f = threadIdx.x; f < I; f += blockDim.x)
+        if (__ldg(tab + (size_t)f * TAB_FEATURE_FLOATS + 12) != 0.0f) differs = 1;
+    return __syncthreads_or(differs) == 0;
 }
 
 __device__ __forceinline__ float silu_fast(float x) {
@@ -455,7 +456,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
     float* stab = reinterpret_cast<float*>(smem + FWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool shared_grid = status[1] != 0;
+    const bool shared_grid = grid_is_shared(tab, P.I);
     if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
@@ -780,7 +781,7 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     float* stab = reinterpret_cast<float*>(smem + BWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool shared_grid = status[1] != 0;
+    const bool shared_grid = grid_is_shared(tab, I);
     if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
     const int n_ohalves = plan.n_otiles * 2;
     const int n_ctiles = plan.n_ctiles();
@@ -1138,7 +1139,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     float* stab = reinterpret_cast<float*>(smem + DX_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool shared_grid = status[1] != 0;
+    const bool shared_grid = grid_is_shared(tab, P.I);
     if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {
@@ -1437,50 +1438,72 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
 }
 
 // Sums the per-split slabs (blocked layout of the drain) and applies the scaler algebra:
-// gsw = scaler * D, gscaler = sum_r sw * D, gbw = base column.  Thread = (feature, output) with the
-// output index fastest, so the 16-byte reads of a warp are contiguous.
-__global__ void finalize_blocked_kernel(const float* __restrict__ partial, BwdPlan plan,
-                                        const float* __restrict__ sw, const float* __restrict__ scaler,
-                                        float* __restrict__ gsw, float* __restrict__ gscaler,
-                                        float* __restrict__ gbw, int O, int I, int R) {
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (int64_t)O * I) return;
-    const int o = (int)(idx % O), i = (int)(idx / O);
-    const int ot = o >> 8, h = (o >> 7) & 1, row = o & 127;
+// gsw = scaler * D, gscaler = sum_r sw * D, gbw = base column.  A block handles 32 outputs x 8
+// features: the slabs are read with the output index fastest (contiguous 16-byte pieces per warp),
+// transposed through shared memory, and the parameter-shaped tensors are then read / written with
+// the feature index fastest (256 contiguous bytes per output row).
+constexpr int FIN_TO = 32, FIN_TI = 8;
+__global__ void __launch_bounds__(FIN_TO * FIN_TI)
+finalize_blocked_kernel(const float* __restrict__ partial, BwdPlan plan,
+                        const float* __restrict__ sw, const float* __restrict__ scaler,
+                        float* __restrict__ gsw, float* __restrict__ gscaler,
+                        float* __restrict__ gbw, int O, int I, int R) {
+    __shared__ float Ds[FIN_TO][FIN_TI * 8 + 1];
+    __shared__ float Bs[FIN_TO][FIN_TI + 1];
+    const int o0 = blockIdx.x * FIN_TO, i0 = blockIdx.y * FIN_TI;
     const int n_ctiles = plan.n_ctiles();
-    const size_t oi = (size_t)o * I + i;
-    auto tile_ptr = [&](int sp, int ct) -> const float4* {
-        return reinterpret_cast<const float4*>(partial) +
-               ((((size_t)sp * plan.n_otiles + ot) * n_ctiles + ct) * 2 + h) * (size_t)(64 * 128) + row;
-    };
-    if (gsw || gscaler) {
-        const int ct = i >> 5, fl = i & 31;
+    {
+        const int ol = threadIdx.x & (FIN_TO - 1), il = threadIdx.x / FIN_TO;
+        const int o = o0 + ol, i = i0 + il;
         float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int sp = 0; sp < plan.splits; ++sp) {
-            const float4* t = tile_ptr(sp, ct);
-            const float4 a = t[(size_t)(fl * 2) * 128], b = t[(size_t)(fl * 2 + 1) * 128];
-            d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
-            d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
-        }
-        const float sc = scaler ? scaler[oi] : 1.0f;
-        float gs = 0.f;
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            if (r < R) {
-                if (gsw) gsw[oi * R + r] = scaler ? sc * d[r] : d[r];
-                if (gscaler) gs += sw[oi * R + r] * d[r];
+        float db = 0.f;
+        if (o < O && i < I) {
+            const int ot = o >> 8, h = (o >> 7) & 1, row = o & 127;
+            auto tile_ptr = [&](int sp, int ct) -> const float4* {
+                return reinterpret_cast<const float4*>(partial) +
+                       ((((size_t)sp * plan.n_otiles + ot) * n_ctiles + ct) * 2 + h) * (size_t)(64 * 128) + row;
+            };
+            if (gsw || gscaler) {
+                const int ct = i >> 5, fl = i & 31;
+                for (int sp = 0; sp < plan.splits; ++sp) {
+                    const float4* t = tile_ptr(sp, ct);
+                    const float4 a = t[(size_t)(fl * 2) * 128], b = t[(size_t)(fl * 2 + 1) * 128];
+                    d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+                    d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+                }
+            }
+            if (gbw) {
+                const int ct = plan.ct_spline + (i >> 8), c = i & 255;
+                for (int sp = 0; sp < plan.splits; ++sp) {
+                    const float4 a = tile_ptr(sp, ct)[(size_t)(c >> 2) * 128];
+                    db += (c & 3) == 0 ? a.x : ((c & 3) == 1 ? a.y : ((c & 3) == 2 ? a.z : a.w));
+                }
             }
         }
-        if (gscaler) gscaler[oi] = gs;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) Ds[ol][il * 8 + r] = d[r];
+        Bs[ol][il] = db;
     }
-    if (gbw) {
-        const int ct = plan.ct_spline + (i >> 8), c = i & 255;
-        float d = 0.f;
-        for (int sp = 0; sp < plan.splits; ++sp) {
-            const float4 a = tile_ptr(sp, ct)[(size_t)(c >> 2) * 128];
-            d += (c & 3) == 0 ? a.x : ((c & 3) == 1 ? a.y : ((c & 3) == 2 ? a.z : a.w));
+    __syncthreads();
+    {
+        const int il = threadIdx.x & (FIN_TI - 1), ol = threadIdx.x / FIN_TI;
+        const int o = o0 + ol, i = i0 + il;
+        if (o >= O || i >= I) return;
+        const size_t oi = (size_t)o * I + i;
+        if (gsw || gscaler) {
+            const float sc = scaler ? scaler[oi] : 1.0f;
+            float gs = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                if (r < R) {
+                    const float d = Ds[ol][il * 8 + r];
+                    if (gsw) gsw[oi * R + r] = scaler ? sc * d : d;
+                    if (gscaler) gs += sw[oi * R + r] * d;
+                }
+            }
+            if (gscaler) gscaler[oi] = gs;
         }
-        gbw[oi] = d;
+        if (gbw) gbw[oi] = Bs[ol][il];
     }
 }
 
@@ -1530,11 +1553,9 @@ inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 inline size_t table_bytes(const LayerShape& s) { return (size_t)s.I * TAB_FEATURE_FLOATS * sizeof(float); }
 
-inline cudaError_t launch_table(const float* grid, float* tab, int* shared_flag, const LayerShape& s,
-                                cudaStream_t st) {
+inline cudaError_t launch_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
     const int work = s.I * (TAB_ENTRIES + 1);
     build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, s.I, s.G, s.K);
-    grid_shared_kernel<<<1, 1024, 0, st>>>(grid, shared_flag, s.I, s.T());
     return cudaGetLastError();
 }
 
@@ -1594,7 +1615,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     {
         cudaError_t e0 = cudaMemsetAsync(status, 0, sizeof(int), st);
         if (e0 != cudaSuccess) return e0;
-        if ((e0 = launch_table(grid, tab, status + 1, s, st)) != cudaSuccess) return e0;
+        if ((e0 = launch_table(grid, tab, s, st)) != cudaSuccess) return e0;
         const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
         int blocks = (int)((chunks + 255) / 256);
         if (blocks > sm_count() * 16) blocks = sm_count() * 16;
@@ -1652,7 +1673,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
     uint8_t* wimg = cursor;
 
     if ((e = cudaMemsetAsync(status, 0, sizeof(int), st)) != cudaSuccess) return e;
-    if ((e = launch_table(grid, tab, status + 1, s, st)) != cudaSuccess) return e;
+    if ((e = launch_table(grid, tab, s, st)) != cudaSuccess) return e;
     {
         const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
         int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
@@ -1676,10 +1697,9 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
 #undef KAN_BWD
         if (e != cudaSuccess) return e;
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        const int64_t work = (int64_t)s.O * s.I;
-        const int fblocks = (int)((work + 255) / 256);
-        finalize_blocked_kernel<<<fblocks, 256, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
-                                                         has_base ? gbw : nullptr, s.O, s.I, s.R());
+        dim3 fgrid((s.O + FIN_TO - 1) / FIN_TO, (s.I + FIN_TI - 1) / FIN_TI);
+        finalize_blocked_kernel<<<fgrid, FIN_TO * FIN_TI, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
+                                                                   has_base ? gbw : nullptr, s.O, s.I, s.R());
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     if (need_x) {
