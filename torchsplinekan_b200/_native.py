@@ -175,8 +175,35 @@ def resolve_mode(mode: int, dtype: torch.dtype, N: int, I: int, O: int, G: int, 
     return m
 
 
+_ws_size_cache = {}
+
+
 def workspace_bytes(op, mode, dtype, N, I, O, G, k, need_x=True, need_param=True) -> int:
-    return int(lib().kanb200_workspace_bytes(op, mode, _code(dtype), N, I, O, G, k, int(need_x), int(need_param)))
+    key = (op, mode, dtype, N, I, O, G, k, bool(need_x), bool(need_param))
+    size = _ws_size_cache.get(key)
+    if size is None:
+        size = int(lib().kanb200_workspace_bytes(op, mode, _code(dtype), N, I, O, G, k, int(need_x), int(need_param)))
+        if len(_ws_size_cache) > 4096:
+            _ws_size_cache.clear()
+        _ws_size_cache[key] = size
+    return size
+
+
+class _OnDevice:
+    """Makes ``dev`` current for the duration of a library call; free when it already is."""
+
+    def __init__(self, dev: torch.device):
+        self.ctx = None if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
 
 
 def basis(x: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
@@ -184,7 +211,7 @@ def basis(x: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
     N, I = x.shape
     G = grid.shape[1] - 2 * k - 1
     H = torch.empty((N, I, G + k), dtype=x.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _check(lib().kanb200_basis(_code(x.dtype), _p(x), _p(grid), _p(H), N, I, G, k, _stream(dev)))
     return H
 
@@ -194,7 +221,7 @@ def basis_grad(x: torch.Tensor, grid: torch.Tensor, k: int, gH: torch.Tensor) ->
     N, I = x.shape
     G = grid.shape[1] - 2 * k - 1
     gx = torch.empty((N, I), dtype=x.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         _check(lib().kanb200_basis_grad(_code(x.dtype), _p(x), _p(grid), _p(gH), _p(gx), N, I, G, k, _stream(dev)))
     return gx
 
@@ -206,7 +233,7 @@ def forward(x, grid, base_weight, spline_weight, spline_scaler, k: int, mode: in
     O = spline_weight.shape[0]
     G = grid.shape[1] - 2 * k - 1
     y = torch.empty((N, O), dtype=x.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         if ws is None:
             ws = workspace(dev, workspace_bytes(OP_FORWARD, mode, x.dtype, N, I, O, G, k), "fwd")
         with _Timed("forward", dev):
@@ -232,7 +259,7 @@ def backward(grad_out, x, grid, base_weight, spline_weight, spline_scaler, k: in
     gb = torch.empty_like(base_weight) if need_base else None
     gs = torch.empty_like(spline_weight) if need_spline else None
     gc = torch.empty_like(spline_scaler) if need_scaler else None
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         if ws is None:
             nb = workspace_bytes(OP_BACKWARD, mode, x.dtype, N, I, O, G, k, need_x,
                                  need_base or need_spline or need_scaler)
@@ -249,7 +276,7 @@ def edge_abs_mean(s, H, bw, W) -> torch.Tensor:
     N, I, R = H.shape
     O = W.shape[0]
     a = torch.empty((O, I), dtype=H.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         nb = workspace_bytes(OP_EDGE_FWD, MODE_SIMT, H.dtype, N, I, O, max(R - 1, 1), 1)
         ws = workspace(dev, nb, "edge")
         _check(lib().kanb200_edge_abs_mean(_code(H.dtype), _p(s), _p(H), _p(bw), _p(W), _p(a), N, I, O, R,
@@ -266,7 +293,7 @@ def edge_abs_mean_backward(ga, s, H, bw, W, need_s, need_H, need_bw, need_W):
     dH = torch.empty_like(H) if need_H else None
     dbw = torch.empty((O, I), dtype=H.dtype, device=dev) if (need_bw and has_base) else None
     dW = torch.empty_like(W) if need_W else None
-    with torch.cuda.device(dev):
+    with _OnDevice(dev):
         nb = workspace_bytes(OP_EDGE_BWD, MODE_SIMT, H.dtype, N, I, O, max(R - 1, 1), 1)
         ws = workspace(dev, nb, "edge")
         _check(lib().kanb200_edge_abs_mean_backward(_code(H.dtype), _p(ga), _p(s), _p(H), _p(bw), _p(W),

@@ -82,8 +82,9 @@ KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, 
     make_shape(N, I, O, G, k, s);
     const bool tc_ok = dtype == KANB200_F32 && tc_supported(s);
     if (mode == KANB200_MODE_AUTO) {
-        // Tensor cores pay off once a 128 x 256 tile is reasonably filled.
-        if (tc_ok && N >= 512 && O >= 64 && I >= 32) return KANB200_MODE_TC_BF16X3;
+        // The tensor-core kernels handle ragged tiles; below a few hundred rows the gather
+        // kernels have less fixed cost.
+        if (tc_ok && N >= 256 && O >= 16 && I >= 8) return KANB200_MODE_TC_BF16X3;
         return KANB200_MODE_SIMT;
     }
     if (mode == KANB200_MODE_SIMT) return mode;

@@ -71,9 +71,10 @@ constexpr int TAB_ENTRIES = 12;
 constexpr int TAB_ZERO_ENTRY = 11;
 
 __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* __restrict__ tab,
-                                        int I, int G, int K) {
+                                        int* __restrict__ status, int I, int G, int K) {
     const int nk = G + 2 * K + 1, R = G + K;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx == 0) *status = 0;                 // the contraction kernels that follow report into it
     if (idx >= I * (TAB_ENTRIES + 1)) return;
     const int f = idx / (TAB_ENTRIES + 1), e = idx - f * (TAB_ENTRIES + 1);
     const float* t = grid + (size_t)f * nk;
@@ -1553,10 +1554,24 @@ inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 inline size_t table_bytes(const LayerShape& s) { return (size_t)s.I * TAB_FEATURE_FLOATS * sizeof(float); }
 
-inline cudaError_t launch_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
+inline cudaError_t launch_table(const float* grid, float* tab, int* status, const LayerShape& s,
+                                cudaStream_t st) {
     const int work = s.I * (TAB_ENTRIES + 1);
-    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, s.I, s.G, s.K);
+    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, status, s.I, s.G, s.K);
     return cudaGetLastError();
+}
+
+// Opt-in to more than 48 KB of dynamic shared memory, once per kernel and device.
+template <auto Kernel>
+cudaError_t ensure_dynamic_smem(int bytes) {
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+    return e;
 }
 
 struct FwdLayout {
@@ -1613,9 +1628,8 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     uint8_t* wimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
     const int kb_total = L.cs.kb_total();
     {
-        cudaError_t e0 = cudaMemsetAsync(status, 0, sizeof(int), st);
+        cudaError_t e0 = launch_table(grid, tab, status, s, st);
         if (e0 != cudaSuccess) return e0;
-        if ((e0 = launch_table(grid, tab, s, st)) != cudaSuccess) return e0;
         const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
         int blocks = (int)((chunks + 255) / 256);
         if (blocks > sm_count() * 16) blocks = sm_count() * 16;
@@ -1637,8 +1651,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     cudaError_t e = cudaSuccess;
 #define KAN_FWD(NT)                                                                                           \
     do {                                                                                                      \
-        e = cudaFuncSetAttribute(tc_forward_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
-                                 (int)FWD_SMEM_BYTES);                                                        \
+        e = ensure_dynamic_smem<tc_forward_kernel<NT>>((int)FWD_SMEM_BYTES);                                  \
         if (e == cudaSuccess)                                                                                 \
             tc_forward_kernel<NT><<<blocks, TC_THREADS, FWD_SMEM_BYTES, st>>>(x, tab, wimg, y, status, P);    \
     } while (0)
@@ -1672,8 +1685,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
     if (need_param) cursor += align256(L.partial_bytes);
     uint8_t* wimg = cursor;
 
-    if ((e = cudaMemsetAsync(status, 0, sizeof(int), st)) != cudaSuccess) return e;
-    if ((e = launch_table(grid, tab, s, st)) != cudaSuccess) return e;
+    if ((e = launch_table(grid, tab, status, s, st)) != cudaSuccess) return e;
     {
         const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
         int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
@@ -1687,8 +1699,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
         const int blocks = (int)(items < sm_count() ? items : sm_count());
 #define KAN_BWD(NT)                                                                                           \
     do {                                                                                                      \
-        e = cudaFuncSetAttribute(tc_bwd_param_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
-                                 (int)BWD_SMEM_BYTES);                                                        \
+        e = ensure_dynamic_smem<tc_bwd_param_kernel<NT>>((int)BWD_SMEM_BYTES);                                \
         if (e == cudaSuccess)                                                                                 \
             tc_bwd_param_kernel<NT><<<blocks, TC_THREADS, BWD_SMEM_BYTES, st>>>(                              \
                 x, tab, dyimg, partial, status, s.N, s.I, s.O, L.plan, vec_ok);                               \
@@ -1725,8 +1736,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
         const int blocks = (int)(P.n_items < sm_count() ? P.n_items : sm_count());
 #define KAN_DX(NT)                                                                                            \
     do {                                                                                                      \
-        e = cudaFuncSetAttribute(tc_bwd_input_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
-                                 (int)DX_SMEM_BYTES);                                                         \
+        e = ensure_dynamic_smem<tc_bwd_input_kernel<NT>>((int)DX_SMEM_BYTES);                                 \
         if (e == cudaSuccess)                                                                                 \
             tc_bwd_input_kernel<NT><<<blocks, TC_THREADS, DX_SMEM_BYTES, st>>>(x, tab, dyimg, wimg, gx,       \
                                                                                 status, P);                   \

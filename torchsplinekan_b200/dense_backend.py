@@ -135,10 +135,13 @@ def curve2coeff(x_samples: torch.Tensor, y_samples: torch.Tensor, grid: torch.Te
     system per input feature, all features in one batched call
     (reference_backend.py:218-265 solves the same systems in a Python loop).
     """
-    basis = compute_basis(x_samples, grid, k).to(dtype=torch.float64, device="cpu")     # [B, I, R]
-    targets = y_samples.to(dtype=torch.float64, device="cpu")                             # [O, B, I]
-    A = basis.permute(1, 0, 2).contiguous()                                               # [I, B, R]
-    Y = targets.permute(2, 1, 0).contiguous()                                             # [I, B, O]
+    # Per-feature systems A_i [B, R] c = Y_i [B, O].  The operands are put into the batched
+    # [I, B, *] layout on the samples' device (a cheap transpose there) and only then moved to
+    # the CPU, where one batched LAPACK call solves all features.
+    A = compute_basis(x_samples, grid, k).permute(1, 0, 2).contiguous()                   # [I, B, R]
+    Y = y_samples.permute(2, 1, 0).contiguous()                                            # [I, B, O]
+    A = A.to(device="cpu").to(torch.float64)
+    Y = Y.to(device="cpu").to(torch.float64)
     sol = torch.linalg.lstsq(A, Y).solution                                               # [I, R, O]
     return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype, device=x_samples.device)
 
