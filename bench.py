@@ -370,6 +370,76 @@ def run_micro(args):
     emit("bwd_simt (param + input)<double,3>", ms, flops=4.0 * Nd * Od * Id * (k + 2))
 
 
+def run_config(args):
+    """Times one training step of the other benchmark configurations (1 GPU, CUDA-event median):
+    0 = KAN[16,32,8] MSE, 2 = KAN[784,256,256,10] cross-entropy + fused regulariser on update_grid
+    knots, 3 = KANLinear 512->512 G=64 on update_grid knots, 4 = float64 KAN[2,64,64,1] PINN loss.
+    Synthetic seeded inputs with the shapes and value distributions of those configurations."""
+    import math
+    import torch
+    import torchsplinekan_b200 as sk
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(0)
+    c = args.config
+    if c == 0:
+        net = sk.KAN([16, 32, 8], backend="cuda").to(dev)
+        x = (torch.rand(1024, 16, generator=g) * 2 - 1).to(dev)
+        tgt = torch.randn(1024, 8, generator=torch.Generator().manual_seed(1)).to(dev)
+        loss_fn = lambda: torch.nn.functional.mse_loss(net(x), tgt)
+        name, rows = "c0 KAN[16,32,8] N=1024 fp32, MSE", 1024
+    elif c == 2:
+        net = sk.KAN([784, 256, 256, 10], backend="cuda").to(dev)
+        x = (torch.rand(8192, 784, generator=g) * 2 - 1).to(dev)
+        labels = torch.randint(0, 10, (8192,), generator=torch.Generator().manual_seed(1)).to(dev)
+        t0 = time.perf_counter()
+        net.update_grid(x[:4096])
+        torch.cuda.synchronize()
+        upd = time.perf_counter() - t0
+
+        def loss_fn():
+            y, r = net.forward_with_regularization(x, 1e-2, 1e-2)
+            return torch.nn.functional.cross_entropy(y, labels) + r
+        name, rows = f"c2 KAN[784,256,256,10] N=8192 fp32, CE + fused reg, update_grid(4096 rows) took {upd:.2f} s", 8192
+    elif c == 3:
+        net = sk.KANLinear(512, 512, grid_size=64, backend="cuda").to(dev)
+        x = torch.where(torch.rand(16384, 512, generator=g) < 0.5, -0.5, 0.5) + 0.15 * torch.randn(16384, 512, generator=g)
+        x = x.clamp_(-1, 1).to(dev)
+        net.update_grid(x)
+        loss_fn = lambda: net(x).square().sum()
+        name, rows = "c3 KANLinear 512->512 G=64 N=16384 fp32 (gather kernels), update_grid knots", 16384
+    elif c == 4:
+        net = sk.KAN([2, 64, 64, 1], grid_size=8, backend="cuda").to(dev, torch.float64)
+        x = (torch.rand(131072, 2, generator=g, dtype=torch.float64) * 2 - 1).to(dev)
+        ref = torch.sin(math.pi * x[:, 0]) * torch.sin(math.pi * x[:, 1])
+        loss_fn = lambda: (net(x).squeeze(-1) - ref).square().mean()
+        name, rows = "c4 KAN[2,64,64,1] G=8 N=131072 fp64 PINN loss (SIMT kernels)", 131072
+    else:
+        raise SystemExit("--config must be 0, 2, 3 or 4 (1 is the default benchmark)")
+
+    def step():
+        for p in net.parameters():
+            p.grad = None
+        loss_fn().backward()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(args.steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    ms = statistics.median(times)
+    print(json.dumps({"config": name, "ms_per_step": ms, "samples_per_s": rows / ms * 1e3, "steps": args.steps,
+                      "backends": [getattr(l, "last_backend", None) for l in getattr(net, "layers", [net])]}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -382,8 +452,11 @@ def main():
     ap.add_argument("--need-x", action="store_true", help="also compute the input gradient (x.requires_grad)")
     ap.add_argument("--micro", action="store_true", help="time the secondary kernels instead of the training step")
     ap.add_argument("--micro-rows", type=int, default=16384)
+    ap.add_argument("--config", type=int, default=None, help="time one of the other benchmark configurations")
     args = ap.parse_args()
-    if args.micro:
+    if args.config is not None:
+        run_config(args)
+    elif args.micro:
         run_micro(args)
     elif args.impl == "reference":
         run_reference_arm(args)
