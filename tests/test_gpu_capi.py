@@ -216,6 +216,22 @@ def test_layer_tensor_core_bf16x3_vs_oracle(shape):
     print("bf16x3", shape, errs)
 
 
+@pytest.mark.parametrize("shape", [
+    dict(N=300, I=40, O=70, G=6, k=3),                        # R = 9: two chunks per feature, 13 knots
+    dict(N=515, I=33, O=130, G=8, k=3, nonuniform=True),      # R = 11
+    dict(N=257, I=24, O=64, G=9, k=1, scaler=False),          # R = 10 with the 12-knot table
+    dict(N=640, I=19, O=300, G=20, k=2, base=False, nonuniform=True),
+    dict(N=1000, I=64, O=96, G=64, k=3, nonuniform=True),     # the widest grid: 9 chunks per feature
+    dict(N=2048, I=128, O=256, G=64, k=3),
+    dict(N=384, I=7, O=40, G=65, k=3),                        # G + 2k = 71, the limit
+])
+def test_layer_tensor_core_wide_grid_vs_oracle(shape):
+    """Grids with G + k > 8: a feature owns several 8-column chunks of the contraction space."""
+    case = make_layer_case(dtype=np.float32, seed=9, **shape)
+    errs = _compare_layer(case, nat.MODE_TC_BF16X3, TOL32)
+    print("bf16x3 wide", shape, errs)
+
+
 def test_layer_tensor_core_bf16x1_stated_tolerance():
     """Single-MMA bf16 mode: operands rounded to 8 significand bits; stated tolerance 1e-2."""
     case = make_layer_case(dtype=np.float32, seed=6, N=1024, I=64, O=256, G=5, k=3)
@@ -227,7 +243,7 @@ def test_layer_tensor_core_bf16x1_stated_tolerance():
 def test_auto_mode_resolution():
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 65536, 1024, 1024, 5, 3) == nat.MODE_TC_BF16X3
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float64, 65536, 1024, 1024, 5, 3) == nat.MODE_SIMT
-    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 16384, 512, 512, 64, 3) == nat.MODE_SIMT
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 16384, 512, 512, 64, 3) == nat.MODE_TC_BF16X3
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 16, 32, 5, 3) == nat.MODE_TC_BF16X3
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 128, 16, 32, 5, 3) == nat.MODE_SIMT
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 32, 8, 5, 3) == nat.MODE_SIMT

@@ -231,14 +231,22 @@ def test_mnist_shaped_step_with_updated_grid():
         assert _err(p.grad, q.grad) < 1e-4, n
 
 
-def test_wide_grid_layer_gather_path():
+@pytest.mark.parametrize("mode", ["auto", "simt"])
+def test_wide_grid_layer(mode):
+    """G = 64 after a grid update on bimodal data (clustered knots): tensor-core path (auto at this
+    size) and gather path."""
     nat, ref = _pair(64, 48, G=64, k=3, ref_dtype=torch.float64)
     g = torch.Generator().manual_seed(0)
     x = torch.where(torch.rand(2048, 64, generator=g) < 0.5, -0.5, 0.5) + 0.15 * torch.randn(2048, 64, generator=g)
     x = x.clamp_(-1, 1).cuda()
     ref.update_grid(x.double())
     nat.load_state_dict({n: v.float() for n, v in ref.state_dict().items()})
-    for a, b in zip(_step(nat, x), _step(ref, x.double())):
+    _C.set_mma_mode(mode)
+    try:
+        got = _step(nat, x)
+    finally:
+        _C.set_mma_mode("auto")
+    for a, b in zip(got, _step(ref, x.double())):
         assert _err(a, b) < TOL32
 
 

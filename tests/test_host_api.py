@@ -44,9 +44,15 @@ def test_mode_resolution_and_workspace_sizes():
     f32, f64 = torch.float32, torch.float64
     assert _native.resolve_mode(_native.MODE_AUTO, f32, 65536, 1024, 1024, 5, 3) == _native.MODE_TC_BF16X3
     assert _native.resolve_mode(_native.MODE_AUTO, f64, 65536, 1024, 1024, 5, 3) == _native.MODE_SIMT
-    assert _native.resolve_mode(_native.MODE_AUTO, f32, 16384, 512, 512, 64, 3) == _native.MODE_SIMT
+    # wide grids (a feature owns ceil((G + k) / 8) chunks of 8 columns) stay on the tensor cores
+    assert _native.resolve_mode(_native.MODE_AUTO, f32, 16384, 512, 512, 64, 3) == _native.MODE_TC_BF16X3
+    assert _native.resolve_mode(_native.MODE_AUTO, f32, 16384, 512, 512, 8, 4) == _native.MODE_SIMT   # k > 3
     with pytest.raises(RuntimeError, match="tensor-core"):
         _native.resolve_mode(_native.MODE_TC_BF16X3, f64, 1024, 64, 64, 5, 3)
+    # G = 64, k = 3: 71 knots -> 76 + 20 * 71 floats per feature; 9 chunks per feature -> 576 column
+    # blocks of spline + 8 of base
+    fw64 = _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_TC_BF16X3, f32, 16384, 512, 512, 64, 3)
+    assert fw64 == 256 + 512 * (76 + 20 * 71) * 4 + 2 * (576 + 8) * 2 * 32768
     fw = _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_AUTO, f32, 65536, 1024, 1024, 5, 3)
     # header + 1 KiB polynomial table per feature + packed weights: 4 output tiles x 144 column
     # blocks x (hi + lo) x 32 KiB

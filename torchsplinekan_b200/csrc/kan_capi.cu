@@ -89,7 +89,7 @@ KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, 
     }
     if (mode == KANB200_MODE_SIMT) return mode;
     if (mode == KANB200_MODE_TC_BF16X3 || mode == KANB200_MODE_TC_BF16X1)
-        return tc_ok ? mode : fail(KANB200_EUNSUPPORTED, "tensor-core modes need float32 and G + k <= 8");
+        return tc_ok ? mode : fail(KANB200_EUNSUPPORTED, "tensor-core modes need float32 and spline order k <= 3");
     return fail(KANB200_EINVAL, "unknown mode %d", mode);
 }
 

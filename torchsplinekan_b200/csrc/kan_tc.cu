@@ -53,51 +53,78 @@ constexpr uint32_t TILE_B_BYTES = BLOCK_N * BLOCK_K * 2;   // 32 KB: 256 x 64 bf
 //
 // On a knot span [t_m, t_{m+1}) each of the k+1 non-zero basis functions is a
 // polynomial of degree k in u = x - t_m.  A small kernel expands the de Boor
-// recurrence symbolically (in double) once per call and stores, per feature,
-//   floats [0, 12)   : knots t_0 .. t_{T-2} (padded with +inf), slot 11 = t_{T-1}
-//   floats [16 + 20 e, 16 + 20 e + 20), e = 0 .. 11 : entry of span e
+// recurrence symbolically (in double) once per call and stores, per feature, a header
+// (flag "knots differ from feature 0", the knots) and one 20-float entry per span:
 //       16 coefficients c[j][p] (function j of the window, power p of u),
 //       t_m, the window start s = m - k (as int bits), 2 unused;
-//       coefficients of window slots outside [0, R) are zero, and entry 11 is
-//       all zero -- it is the one inputs outside the knot range select.
-// The operand producers then need one compare-and-count for the span, five
-// 16-byte loads and a Horner evaluation per input; the same code serves uniform
+//       coefficients of window slots outside [0, R) are zero, and the entry after the last
+//       span is all zero -- it is the one inputs outside the knot range select.
+// (TabInfo below gives the offsets.)
+// The operand producers then need one span search (compare-and-count up to 12 knots, a
+// branch-free binary search beyond), five 16-byte loads and a Horner evaluation per input; the same code serves uniform
 // and non-uniform knots.  Conventions (half-open spans, last span closed,
 // zero-length spans contribute zero) are those of the dense recurrence.
 // ---------------------------------------------------------------------------
-constexpr int TAB_FEATURE_FLOATS = 256;       // 1 KB per feature
 constexpr int TAB_ENTRY_FLOATS = 20;
-constexpr int TAB_ENTRIES = 12;
-constexpr int TAB_ZERO_ENTRY = 11;
+constexpr int TAB_FAST_MAX_KNOTS = 12;        // compare-and-count span search up to this many knots
+constexpr int TAB_SMEM_FLOATS = 256;          // table of one feature with <= 12 knots: 16 + 12 * 20
+
+// Geometry of the table and of the column space, passed to every kernel.
+//   feature block : [0] "differs from feature 0" flag, [1,4) unused,
+//                   nk <= 12 : [4,15) knots t_0..t_{nk-2} padded with +inf, [15] = t_{nk-1}
+//                   nk  > 12 : [4, 4+nk) the raw knots
+//                   [es + 20 e, es + 20 e + 20), e = 0..nk-1 : entry of span e; entry nk-1 is all
+//                   zero and is the one inputs outside the knot range select
+//   column space  : a feature owns cpf = ceil(R / 8) chunks of 8 slots; chunk g = f * cpf + cw
+//                   holds slots 8 cw .. 8 cw + 7 (slots >= R are zero)
+struct TabInfo {
+    int nk;        // knots per feature
+    int es;        // offset of the first entry within a feature block
+    int fs;        // floats per feature block
+    int cpf;       // chunks of 8 column slots per feature
+};
+
+inline TabInfo make_tab_info(int G, int K) {
+    TabInfo t;
+    t.nk = G + 2 * K + 1;
+    t.es = t.nk <= TAB_FAST_MAX_KNOTS ? 16 : ((4 + t.nk + 3) / 4) * 4;
+    t.fs = t.es + TAB_ENTRY_FLOATS * t.nk;
+    t.cpf = (G + K + 7) / 8;
+    return t;
+}
 
 __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* __restrict__ tab,
-                                        int* __restrict__ status, int I, int G, int K) {
-    const int nk = G + 2 * K + 1, R = G + K;
+                                        int* __restrict__ status, int I, int G, int K, TabInfo ti) {
+    const int nk = ti.nk, R = G + K;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx == 0) *status = 0;                 // the contraction kernels that follow report into it
-    if (idx >= I * (TAB_ENTRIES + 1)) return;
-    const int f = idx / (TAB_ENTRIES + 1), e = idx - f * (TAB_ENTRIES + 1);
+    if (idx >= I * (nk + 1)) return;
+    const int f = idx / (nk + 1), e = idx - f * (nk + 1);
     const float* t = grid + (size_t)f * nk;
-    float* out = tab + (size_t)f * TAB_FEATURE_FLOATS;
-    if (e == TAB_ENTRIES) {                    // knot block
-        for (int q = 0; q < 11; ++q) out[q] = (q <= nk - 2) ? t[q] : __int_as_float(0x7f800000);
-        out[11] = t[nk - 1];
-        // slot 12: 1 when this knot row differs from the row of feature 0 (see grid_is_shared)
+    float* out = tab + (size_t)f * ti.fs;
+    if (e == nk) {                             // header + knot block
         float differs = 0.0f;
         for (int q = 0; q < nk; ++q)
             if (t[q] != grid[q]) differs = 1.0f;
-        out[12] = differs;
-        for (int q = 13; q < 16; ++q) out[q] = 0.0f;
+        out[0] = differs;
+        out[1] = out[2] = out[3] = 0.0f;
+        if (nk <= TAB_FAST_MAX_KNOTS) {
+            for (int q = 0; q < 11; ++q) out[4 + q] = (q <= nk - 2) ? t[q] : __int_as_float(0x7f800000);
+            out[15] = t[nk - 1];
+        } else {
+            for (int q = 0; q < nk; ++q) out[4 + q] = t[q];
+            for (int q = 4 + nk; q < ti.es; ++q) out[q] = 0.0f;
+        }
         return;
     }
-    float* ent = out + 16 + e * TAB_ENTRY_FLOATS;
+    float* ent = out + ti.es + e * TAB_ENTRY_FLOATS;
     double c[4][4];
     for (int j = 0; j < 4; ++j)
         for (int p = 0; p < 4; ++p) c[j][p] = 0.0;
     const int m = e;
     float tm = 0.0f;
     int s = 0;
-    if (m <= nk - 2 && e != TAB_ZERO_ENTRY) {
+    if (m <= nk - 2) {                         // e == nk - 1 is the zero entry
         auto knot = [&](int i) -> double { return (double)t[i < 0 ? 0 : (i > nk - 1 ? nk - 1 : i)]; };
         tm = t[m];
         s = m - K;
@@ -140,54 +167,95 @@ __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* _
 
 // True when every feature has the knot row of feature 0 (the default uniform grid): the kernels
 // then keep that single 1-KB table in shared memory instead of reading per-feature tables through
-// L1.  Block-wide vote over the per-feature flags the table kernel left in slot 12; every thread
+// L1.  Block-wide vote over the per-feature flags the table kernel left in slot 0; every thread
 // of the CTA must call it.
-__device__ __forceinline__ bool grid_is_shared(const float* __restrict__ tab, int I) {
-    int differs = 0;
+__device__ __forceinline__ bool grid_is_shared(const float* __restrict__ tab, int I, const TabInfo& ti) {
+    int differs = ti.nk > TAB_FAST_MAX_KNOTS ? 1 : 0;      // only the small table fits in shared memory
     for (int f = threadIdx.x; f < I; f += blockDim.x)
-        if (__ldg(tab + (size_t)f * TAB_FEATURE_FLOATS + 12) != 0.0f) differs = 1;
+        if (__ldg(tab + (size_t)f * ti.fs) != 0.0f) differs = 1;
     return __syncthreads_or(differs) == 0;
+}
+
+// Index of the table entry of x: the knot span (last knot <= x; the last span is closed on the
+// right), or the all-zero entry nk - 1 for x outside the knot range / NaN.
+// WIDE = false promises at most 12 knots (G + k <= 8).
+template <bool SMEM_TAB, bool WIDE>
+__device__ __forceinline__ int table_entry_index(const float* __restrict__ ftab, const TabInfo& ti, float xv) {
+    auto ld4 = [](const float4* p) -> float4 { return SMEM_TAB ? *p : __ldg(p); };
+    if (!WIDE || ti.nk <= TAB_FAST_MAX_KNOTS) {
+        const float4 k0 = ld4(reinterpret_cast<const float4*>(ftab + 4));
+        const float4 k1 = ld4(reinterpret_cast<const float4*>(ftab + 4) + 1);
+        const float4 k2 = ld4(reinterpret_cast<const float4*>(ftab + 4) + 2);
+        const bool inside = (xv >= k0.x) && (xv <= k2.w);
+        const int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
+                      (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
+        return inside ? m : ti.nk - 1;
+    }
+    const float* t = ftab + 4;
+    const float t_last = SMEM_TAB ? t[ti.nk - 1] : __ldg(t + ti.nk - 1);
+    const float t_first = SMEM_TAB ? t[0] : __ldg(t);
+    const bool inside = (xv >= t_first) && (xv <= t_last);
+    int lo = 0, hi = ti.nk - 1;                // t[lo] <= x < t[hi] while inside and x < t_last
+#pragma unroll
+    for (int it = 0; it < 7; ++it) {           // 2^7 > 72 knots
+        const int mid = (lo + hi) >> 1;
+        const float tm = SMEM_TAB ? t[mid] : __ldg(t + mid);
+        const bool open = (hi - lo) > 1;
+        const bool right = tm <= xv;
+        lo = (open && right) ? mid : lo;
+        hi = (open && !right) ? mid : hi;
+    }
+    const int m = (xv == t_last) ? ti.nk - 2 : lo;
+    return inside ? m : ti.nk - 1;
 }
 
 __device__ __forceinline__ float silu_fast(float x) {
     return __fdividef(x, 1.0f + __expf(-x));
 }
 
-// Evaluates the basis of one input from its feature's table and returns the 8
-// column slots of the feature as two 128-bit rows (hi and lo bf16 parts).
-// Branch-free.  SPLIT = false leaves lo untouched.
-template <bool SPLIT, bool SMEM_TAB>
-__device__ __forceinline__ void eval_feature_row(const float* __restrict__ ftab, float xv, uint4& hi, uint4& lo) {
+// The k + 1 non-zero basis values of one input (packed as bf16 pairs, hi and lo parts) and the
+// column slot s of the first one.  Inputs outside the knot range select the all-zero entry.
+struct Window {
+    uint32_t h01, h23, l01, l23;
+    int s;
+};
+
+template <bool SPLIT, bool SMEM_TAB, bool WIDE>
+__device__ __forceinline__ Window eval_window(const float* __restrict__ ftab, const TabInfo& ti, float xv) {
     auto ld4 = [](const float4* p) -> float4 { return SMEM_TAB ? *p : __ldg(p); };
-    const float4 k0 = ld4(reinterpret_cast<const float4*>(ftab));
-    const float4 k1 = ld4(reinterpret_cast<const float4*>(ftab) + 1);
-    const float4 k2 = ld4(reinterpret_cast<const float4*>(ftab) + 2);
-    const bool inside = (xv >= k0.x) && (xv <= k2.w);
-    int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
-            (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
-    m = inside ? m : TAB_ZERO_ENTRY;
-    const float4* ent = reinterpret_cast<const float4*>(ftab + 16 + m * TAB_ENTRY_FLOATS);
+    const int m = table_entry_index<SMEM_TAB, WIDE>(ftab, ti, xv);
+    const float4* ent = reinterpret_cast<const float4*>(ftab + ti.es + m * TAB_ENTRY_FLOATS);
     const float4 c0 = ld4(ent), c1 = ld4(ent + 1), c2 = ld4(ent + 2), c3 = ld4(ent + 3), meta = ld4(ent + 4);
     const float u = xv - meta.x;
-    const int s = __float_as_int(meta.y);
     const float v0 = fmaf(fmaf(fmaf(c0.w, u, c0.z), u, c0.y), u, c0.x);
     const float v1 = fmaf(fmaf(fmaf(c1.w, u, c1.z), u, c1.y), u, c1.x);
     const float v2 = fmaf(fmaf(fmaf(c2.w, u, c2.z), u, c2.y), u, c2.x);
     const float v3 = fmaf(fmaf(fmaf(c3.w, u, c3.z), u, c3.y), u, c3.x);
-    uint32_t h01, h23, l01 = 0, l23 = 0;
+    Window w;
+    w.s = __float_as_int(meta.y);
+    w.l01 = 0;
+    w.l23 = 0;
     if (SPLIT) {
-        split2(v0, v1, h01, l01);
-        split2(v2, v3, h23, l23);
+        split2(v0, v1, w.h01, w.l01);
+        split2(v2, v3, w.h23, w.l23);
     } else {
         const __nv_bfloat162 a = __floats2bfloat162_rn(v0, v1);
         const __nv_bfloat162 b = __floats2bfloat162_rn(v2, v3);
-        h01 = *reinterpret_cast<const uint32_t*>(&a);
-        h23 = *reinterpret_cast<const uint32_t*>(&b);
+        w.h01 = *reinterpret_cast<const uint32_t*>(&a);
+        w.h23 = *reinterpret_cast<const uint32_t*>(&b);
     }
-    // Place the 4 half-words at half-word offset s (in [-3, 7]) of the 8-slot row.  With
-    // s = 2 q + odd the payload becomes three words (t0, t1, t2) that start at word q.
+    return w;
+}
+
+// Chunk `cw` of the feature's column slots (slots 8 cw .. 8 cw + 7) as two 128-bit rows (hi and
+// lo bf16 parts): the 4 half-words of the window go to half-word offset s - 8 cw; a window that
+// does not touch the chunk leaves zeros.  Branch-free.  SPLIT = false leaves lo untouched.
+template <bool SPLIT>
+__device__ __forceinline__ void place_window(const Window& w, int cw, uint4& hi, uint4& lo) {
+    const int s = w.s - 8 * cw;
+    // With s = 2 q + odd the payload becomes three words (t0, t1, t2) that start at word q.
     const int odd = s & 1;
-    const int q = (s - odd) >> 1;                          // -2 .. 3
+    const int q = (s - odd) >> 1;                          // -2 .. 3 when the window touches the chunk
     const bool at0 = (q == 0), at1 = (q == 1), at2 = (q == 2), at3 = (q == 3), atm1 = (q == -1), atm2 = (q == -2);
     auto place = [&](uint32_t w01, uint32_t w23) -> uint4 {
         const uint32_t t0 = odd ? (w01 << 16) : w01;
@@ -200,24 +268,19 @@ __device__ __forceinline__ void eval_feature_row(const float* __restrict__ ftab,
         o.w = at3 ? t0 : (at2 ? t1 : (at1 ? t2 : 0u));
         return o;
     };
-    hi = place(h01, h23);
-    if (SPLIT) lo = place(l01, l23);
+    hi = place(w.h01, w.h23);
+    if (SPLIT) lo = place(w.l01, w.l23);
 }
 
 // Derivatives of the window functions of one input from its feature's table:
 // d/du (c0 + c1 u + c2 u^2 + c3 u^3) = c1 + 2 c2 u + 3 c3 u^2.  Returns the window start; inputs
 // outside the knot range select the all-zero entry.
-template <bool SMEM_TAB>
-__device__ __forceinline__ int eval_feature_deriv(const float* __restrict__ ftab, float xv, float (&d)[4]) {
+template <bool SMEM_TAB, bool WIDE>
+__device__ __forceinline__ int eval_feature_deriv(const float* __restrict__ ftab, const TabInfo& ti, float xv,
+                                                  float (&d)[4]) {
     auto ld4 = [](const float4* p) -> float4 { return SMEM_TAB ? *p : __ldg(p); };
-    const float4 k0 = ld4(reinterpret_cast<const float4*>(ftab));
-    const float4 k1 = ld4(reinterpret_cast<const float4*>(ftab) + 1);
-    const float4 k2 = ld4(reinterpret_cast<const float4*>(ftab) + 2);
-    const bool inside = (xv >= k0.x) && (xv <= k2.w);
-    int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
-            (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
-    m = inside ? m : TAB_ZERO_ENTRY;
-    const float4* ent = reinterpret_cast<const float4*>(ftab + 16 + m * TAB_ENTRY_FLOATS);
+    const int m = table_entry_index<SMEM_TAB, WIDE>(ftab, ti, xv);
+    const float4* ent = reinterpret_cast<const float4*>(ftab + ti.es + m * TAB_ENTRY_FLOATS);
     const float4 c0 = ld4(ent), c1 = ld4(ent + 1), c2 = ld4(ent + 2), c3 = ld4(ent + 3), meta = ld4(ent + 4);
     const float u = xv - meta.x;
     d[0] = fmaf(fmaf(3.0f * c0.w, u, 2.0f * c0.z), u, c0.y);
@@ -284,21 +347,21 @@ __device__ __forceinline__ void load_x8(const float* __restrict__ x, int64_t row
 // 128-byte swizzle.  One bulk copy brings a tile in.
 // ---------------------------------------------------------------------------
 struct ColumnSpace {
-    int kb_spline;     // k-blocks (64 columns = 8 features) of the spline part
+    int kb_spline;     // k-blocks (64 columns = 8 chunks of 8 slots) of the spline part
     int kb_base;       // k-blocks (64 features) of the base part, 0 without base
     int kb_total() const { return kb_spline + kb_base; }
 };
 
-inline ColumnSpace column_space(int I, bool has_base) {
+inline ColumnSpace column_space(int I, int cpf, bool has_base) {
     ColumnSpace c;
-    c.kb_spline = (I + 7) / 8;
+    c.kb_spline = (I * cpf + 7) / 8;
     c.kb_base = has_base ? (I + 63) / 64 : 0;
     return c;
 }
 
 __global__ void pack_weights_kernel(const float* __restrict__ sw, const float* __restrict__ scaler,
                                     const float* __restrict__ bw, uint8_t* __restrict__ img,
-                                    int O, int I, int R, int kb_spline, int kb_total, int n_otiles) {
+                                    int O, int I, int R, int cpf, int kb_spline, int kb_total, int n_otiles) {
     // one thread per 16-byte chunk: (o_row in tile, chunk 0..7) of one (o-tile, k-block)
     const int64_t chunks = (int64_t)n_otiles * kb_total * BLOCK_N * 8;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks;
@@ -315,13 +378,14 @@ __global__ void pack_weights_kernel(const float* __restrict__ sw, const float* _
         for (int e = 0; e < 8; ++e) w[e] = 0.0f;
         if (o < O) {
             if (kb < kb_spline) {
-                const int f = kb * 8 + cc;
+                const int g = kb * 8 + cc;                  // chunk -> (feature, 8 of its slots)
+                const int f = g / cpf, r0 = (g - f * cpf) * 8;
                 if (f < I) {
                     const size_t oi = (size_t)o * I + f;
                     const float sc = scaler ? scaler[oi] : 1.0f;
                     for (int e = 0; e < 8; ++e)
-                        if (e < R) {
-                            const float v = sw[oi * R + e];
+                        if (r0 + e < R) {
+                            const float v = sw[oi * R + r0 + e];
                             w[e] = scaler ? v * sc : v;
                         }
                 }
@@ -423,7 +487,7 @@ constexpr uint32_t FWD_A_STAGE_BYTES = 2 * TILE_A_BYTES;                  // hi 
 constexpr uint32_t FWD_SMEM_A = 0;
 constexpr uint32_t FWD_SMEM_B = FWD_SMEM_A + FWD_A_STAGES * FWD_A_STAGE_BYTES;
 constexpr uint32_t FWD_SMEM_CTRL = FWD_SMEM_B + FWD_B_SLOTS * TILE_B_BYTES;
-constexpr uint32_t FWD_CTRL_BYTES = 256 + TAB_FEATURE_FLOATS * 4;   // barriers + the shared-grid table
+constexpr uint32_t FWD_CTRL_BYTES = 256 + TAB_SMEM_FLOATS * 4;   // barriers + the shared-grid table
 constexpr uint32_t FWD_SMEM_BYTES = FWD_SMEM_CTRL + FWD_CTRL_BYTES;
 static_assert(FWD_SMEM_BYTES <= 232448, "forward kernel shared memory exceeds 227 KB");
 
@@ -444,9 +508,10 @@ struct FwdParams {
     int64_t n_tiles;
     int chunk_kb;          // k-blocks accumulated in TMEM between drains
     int vec_x, vec_x2, vec_y;
+    TabInfo ti;
 };
 
-template <int NTERMS>
+template <int NTERMS, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
                   float* __restrict__ y, int* __restrict__ status, const FwdParams P) {
@@ -457,8 +522,8 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
     float* stab = reinterpret_cast<float*>(smem + FWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool shared_grid = grid_is_shared(tab, P.I);
-    if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
+    const bool shared_grid = grid_is_shared(tab, P.I, P.ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
@@ -526,17 +591,31 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
             const int64_t n = mt * BLOCK_M + row;
             const bool row_ok = n < P.N;
             const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
-            // software prefetch: the inputs of the next k-block are loaded one iteration ahead
+            // A thread fills chunks g0 = 8 kb + 2 part and g0 + 1 of the k-block; chunk g belongs to
+            // feature g / cpf and holds its slots 8 (g % cpf) ..  The inputs of the next k-block
+            // are loaded one iteration ahead.
+            const int cpf = WIDE ? P.ti.cpf : 1;
             float nx0 = 0.f, nx1 = 0.f;
+            auto chunk_pair = [&](int kb, int& f0, int& cw0, int& f1, int& cw1) {
+                const int g0 = kb * 8 + part * 2;
+                if (!WIDE) {
+                    f0 = g0; cw0 = 0; f1 = g0 + 1; cw1 = 0;
+                } else {
+                    f0 = g0 / cpf; cw0 = g0 - f0 * cpf;
+                    f1 = f0; cw1 = cw0 + 1;
+                    if (cw1 == cpf) { f1 = f0 + 1; cw1 = 0; }
+                }
+            };
             auto prefetch_spline = [&](int kb) {
-                const int f0 = kb * 8 + part * 2;
-                if (P.vec_x2 && row_ok && f0 + 1 < P.I) {
+                int f0, cw0, f1, cw1;
+                chunk_pair(kb, f0, cw0, f1, cw1);
+                if (!WIDE && P.vec_x2 && row_ok && f0 + 1 < P.I) {
                     const float2 v = __ldg(reinterpret_cast<const float2*>(xrow + f0));
                     nx0 = v.x;
                     nx1 = v.y;
                 } else {
                     nx0 = (row_ok && f0 < P.I) ? __ldg(xrow + f0) : 0.f;
-                    nx1 = (row_ok && f0 + 1 < P.I) ? __ldg(xrow + f0 + 1) : 0.f;
+                    nx1 = (row_ok && f1 < P.I) ? __ldg(xrow + f1) : 0.f;
                 }
             };
             if (P.kb_spline > 0) prefetch_spline(0);
@@ -546,21 +625,22 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                 const uint32_t a_lo = a_hi + TILE_A_BYTES;
                 const bool chunk_start = (kb % P.chunk_kb) == 0;
                 if (kb < P.kb_spline) {
-                    const int f0 = kb * 8 + part * 2;
+                    int f0, cw0, f1, cw1;
+                    chunk_pair(kb, f0, cw0, f1, cw1);
                     const float x0 = nx0, x1 = nx1;
                     if (kb + 1 < P.kb_spline) prefetch_spline(kb + 1);
-                    const bool ok0 = row_ok && f0 < P.I, ok1 = row_ok && f0 + 1 < P.I;
+                    const bool ok0 = row_ok && f0 < P.I, ok1 = row_ok && f1 < P.I;
                     // features beyond I read the last feature's table; their rows are zeroed below
-                    const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * TAB_FEATURE_FLOATS;
-                    const float* t1 = tab + (size_t)(f0 + 1 < P.I ? f0 + 1 : P.I - 1) * TAB_FEATURE_FLOATS;
+                    const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * P.ti.fs;
+                    const float* t1 = tab + (size_t)(f1 < P.I ? f1 : P.I - 1) * P.ti.fs;
                     uint4 hi0, lo0, hi1, lo1;
-                    if (shared_grid) {
-                        eval_feature_row<SPLIT, true>(stab, x0, hi0, lo0);
-                        eval_feature_row<SPLIT, true>(stab, x1, hi1, lo1);
-                    } else {
-                        eval_feature_row<SPLIT, false>(t0, x0, hi0, lo0);
-                        eval_feature_row<SPLIT, false>(t1, x1, hi1, lo1);
-                    }
+                    Window w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x0)
+                                           : eval_window<SPLIT, false, WIDE>(t0, P.ti, x0);
+                    place_window<SPLIT>(w, cw0, hi0, lo0);
+                    if (!WIDE || f1 != f0)                 // uniform over the warp
+                        w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x1)
+                                        : eval_window<SPLIT, false, WIDE>(t1, P.ti, x1);
+                    place_window<SPLIT>(w, cw1, hi1, lo1);
                     if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / FWD_A_STAGES) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -743,7 +823,7 @@ constexpr uint32_t BWD_D_SLOT_BYTES = 2 * TILE_A_BYTES;                  // hi +
 constexpr uint32_t BWD_SMEM_G = 0;
 constexpr uint32_t BWD_SMEM_D = BWD_SMEM_G + BWD_G_STAGES * BWD_G_STAGE_BYTES;
 constexpr uint32_t BWD_SMEM_CTRL = BWD_SMEM_D + BWD_D_SLOTS * BWD_D_SLOT_BYTES;
-constexpr uint32_t BWD_CTRL_BYTES = 256 + TAB_FEATURE_FLOATS * 4;   // barriers + the shared-grid table
+constexpr uint32_t BWD_CTRL_BYTES = 256 + TAB_SMEM_FLOATS * 4;   // barriers + the shared-grid table
 constexpr uint32_t BWD_SMEM_BYTES = BWD_SMEM_CTRL + BWD_CTRL_BYTES;
 static_assert(BWD_SMEM_BYTES <= 232448, "backward kernel shared memory exceeds 227 KB");
 
@@ -758,7 +838,7 @@ static_assert(sizeof(BwdCtrl) <= 256, "control block too large");
 
 struct BwdPlan {
     int n_otiles;          // tiles of 256 outputs
-    int ct_spline;         // column tiles of 32 features
+    int ct_spline;         // column tiles of 32 chunks (8 slots each) of the spline part
     int ct_base;           // column tiles of 256 base features
     int splits;
     int chunk_kb;          // 64-sample blocks accumulated in TMEM between drains
@@ -770,11 +850,11 @@ struct BwdPlan {
     __host__ __device__ int64_t slab_floats() const { return (int64_t)n_otiles * n_ctiles() * 256 * 256; }
 };
 
-template <int NTERMS>
+template <int NTERMS, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ dyimg,
                     float* __restrict__ partial, int* __restrict__ status,
-                    int64_t N, int I, int O, BwdPlan plan, int vec_ok) {
+                    int64_t N, int I, int O, BwdPlan plan, TabInfo ti, int vec_ok) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr bool SPLIT = (NTERMS == 3);
     const uint32_t sbase = smem_u32(smem);
@@ -782,8 +862,8 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     float* stab = reinterpret_cast<float*>(smem + BWD_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool shared_grid = grid_is_shared(tab, I);
-    if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
+    const bool shared_grid = grid_is_shared(tab, I, ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
     const int n_ohalves = plan.n_otiles * 2;
     const int n_ctiles = plan.n_ctiles();
     const int64_t n_items = plan.n_items();
@@ -831,9 +911,9 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     if (warp < WORKER_WARPS) {
         // ===== workers: 64 samples x 256 columns per block, MN-major; drain between chunks =====
         const int quad = warp & 3, part = warp >> 2;
-        // spline tiles: thread = (sample, 4 features); base tiles: thread = (4 samples, 8 features)
+        // spline tiles: thread = (sample, 4 chunks); base tiles: thread = (4 samples, 8 features)
         const int n_loc = (warp & 1) * 32 + lane;       // sample within the block (spline tiles)
-        const int fq = warp >> 1;                       // group of 4 features (spline tiles)
+        const int fq = warp >> 1;                       // group of 4 chunks (spline tiles)
         const int kg = warp >> 1;                       // group of 8 samples (base tiles)
         const int r0 = (warp & 1) * 4;                  // first of this warp's 4 rows in the group
         uint32_t it = 0, n_drained = 0;
@@ -883,25 +963,39 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             int sp, ot, ct;
             decode(item, sp, ot, ct);
             const bool spline = ct < plan.ct_spline;
-            const int f_tile0 = spline ? ct * 32 : (ct - plan.ct_spline) * 256;
+            const int f_tile0 = spline ? 0 : (ct - plan.ct_spline) * 256;
             int64_t kb0, kb1;
             k_range(sp, kb0, kb1);
-            // spline tiles: inputs of the next block of samples are loaded one iteration ahead
-            const int f_sp = f_tile0 + fq * 4;
+            // spline tiles: chunk g = 32 ct + 4 fq + q belongs to feature g / cpf and holds its slots
+            // 8 (g % cpf) ..; the inputs of the next block of samples are loaded one iteration ahead
+            int cf[4], ccw[4];
+            {
+                const int g0 = ct * 32 + fq * 4;
+                const int cpf = WIDE ? ti.cpf : 1;
+                cf[0] = g0 / cpf;
+                ccw[0] = g0 - cf[0] * cpf;
+#pragma unroll
+                for (int q = 1; q < 4; ++q) {
+                    cf[q] = cf[q - 1];
+                    ccw[q] = ccw[q - 1] + 1;
+                    if (ccw[q] == cpf) { cf[q] += 1; ccw[q] = 0; }
+                }
+            }
+            const int f_sp = cf[0];
             float nx[4] = {0.f, 0.f, 0.f, 0.f};
             auto prefetch_spline = [&](int64_t kb) {
                 const int64_t n = kb * BLOCK_K + n_loc;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) nx[q] = 0.f;
                 if (n < N && f_sp < I) {
-                    const float* p = x + (size_t)n * I + f_sp;
-                    if (vec_ok && f_sp + 4 <= I) {
-                        const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+                    const float* xr = x + (size_t)n * I;
+                    if (!WIDE && vec_ok && f_sp + 4 <= I) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(xr + f_sp));
                         nx[0] = v.x; nx[1] = v.y; nx[2] = v.z; nx[3] = v.w;
                     } else {
 #pragma unroll
                         for (int q = 0; q < 4; ++q)
-                            if (f_sp + q < I) nx[q] = __ldg(p + q);
+                            if (cf[q] < I) nx[q] = (q > 0 && cf[q] == cf[q - 1]) ? nx[q - 1] : __ldg(xr + cf[q]);
                     }
                 }
             };
@@ -921,22 +1015,26 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                         ok = false;
                         break;
                     }
-                    // row = sample (k index), 128 B = 64 columns = 8 features of 8 slots
+                    // row = sample (k index), 128 B = 64 columns = 8 chunks of 8 slots
                     const int kk = n_loc & 7;
+                    Window w;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        const int f = f_sp + q;
+                        const int f = cf[q];
+                        if (!WIDE || q == 0 || f != cf[q - 1]) {    // uniform over the warp
+                            if (shared_grid)
+                                w = eval_window<SPLIT, true, WIDE>(stab, ti, xv[q]);
+                            else
+                                w = eval_window<SPLIT, false, WIDE>(tab + (size_t)(f < I ? f : I - 1) * ti.fs, ti,
+                                                                    xv[q]);
+                        }
                         uint4 hi, lo;
-                        if (shared_grid)
-                            eval_feature_row<SPLIT, true>(stab, xv[q], hi, lo);
-                        else
-                            eval_feature_row<SPLIT, false>(tab + (size_t)(f < I ? f : I - 1) * TAB_FEATURE_FLOATS,
-                                                           xv[q], hi, lo);
+                        place_window<SPLIT>(w, ccw[q], hi, lo);
                         if (!(n_ok && f < I)) {
                             hi = make_uint4(0, 0, 0, 0);
                             lo = hi;
                         }
-                        const int fl = fq * 4 + q;                       // feature within the tile, 0..31
+                        const int fl = fq * 4 + q;                       // chunk within the tile, 0..31
                         const uint32_t off = (uint32_t)((fl >> 3) * 8 + (n_loc >> 3)) * 1024u + (uint32_t)kk * 128u +
                                              (uint32_t)(((fl & 7) ^ kk) << 4);
                         st_shared_v4(g_hi + off, hi);
@@ -1100,7 +1198,7 @@ constexpr uint32_t DX_A_STAGE_BYTES = 2 * TILE_A_BYTES;                  // hi +
 constexpr uint32_t DX_SMEM_A = 0;
 constexpr uint32_t DX_SMEM_B = DX_SMEM_A + DX_A_STAGES * DX_A_STAGE_BYTES;
 constexpr uint32_t DX_SMEM_CTRL = DX_SMEM_B + DX_B_SLOTS * TILE_B_BYTES;
-constexpr uint32_t DX_CTRL_BYTES = 256 + TAB_FEATURE_FLOATS * 4;
+constexpr uint32_t DX_CTRL_BYTES = 256 + TAB_SMEM_FLOATS * 4;
 constexpr uint32_t DX_SMEM_BYTES = DX_SMEM_CTRL + DX_CTRL_BYTES;
 static_assert(DX_SMEM_BYTES <= 232448, "input-gradient kernel shared memory exceeds 227 KB");
 
@@ -1109,6 +1207,7 @@ struct DxCtrl {
     uint64_t fullB[DX_B_SLOTS], emptyB[DX_B_SLOTS];
     uint64_t accFull[2], accEmpty[2];
     uint64_t epiDone;      // workers: the previous sub-tile's gx stores are visible
+    uint64_t phaseDone;    // workers: the even chunks of a wide sub-tile have been added to gx
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -1126,9 +1225,10 @@ struct DxParams {
     int has_base;
     int64_t n_items;
     int vec_ok;
+    TabInfo ti;
 };
 
-template <int NTERMS>
+template <int NTERMS, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ dyimg,
                     const uint8_t* __restrict__ wimg, float* __restrict__ gx, int* __restrict__ status,
@@ -1140,8 +1240,8 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     float* stab = reinterpret_cast<float*>(smem + DX_SMEM_CTRL + 256);
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool shared_grid = grid_is_shared(tab, P.I);
-    if (threadIdx.x < TAB_FEATURE_FLOATS) stab[threadIdx.x] = tab[threadIdx.x];
+    const bool shared_grid = grid_is_shared(tab, P.I, P.ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {
         if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
@@ -1161,6 +1261,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             mbar_init(smem_u32(&ctrl->accEmpty[s]), WORKER_THREADS);
         }
         mbar_init(smem_u32(&ctrl->epiDone), WORKER_THREADS);
+        mbar_init(smem_u32(&ctrl->phaseDone), WORKER_THREADS);
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
@@ -1173,13 +1274,16 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    const int n_sub = P.has_base ? 9 : 8;                   // sub-tiles per item
+    // A group of 256 features owns 256 cpf chunks = 8 cpf spline sub-tiles of 32 chunks.
+    const int cpf = WIDE ? P.ti.cpf : 1;
+    const int sub_spline = 8 * cpf;
+    const int n_sub = sub_spline + (P.has_base ? 1 : 0);    // sub-tiles per item
     // sub-tile j of feature group fg -> first column block of the weight image, and whether it is
     // the base sub-tile
     auto sub_info = [&](int fg, int j, bool& is_base, int& cb0) {
         is_base = P.has_base && j == 0;
-        const int t = P.has_base ? j - 1 : j;               // spline sub-tile index 0..7
-        cb0 = is_base ? P.kb_spline + fg * 4 : (fg * 8 + t) * 4;
+        const int t = P.has_base ? j - 1 : j;               // spline sub-tile index
+        cb0 = is_base ? P.kb_spline + fg * 4 : (fg * sub_spline + t) * 4;
     };
 
     if (warp < WORKER_WARPS) {
@@ -1187,6 +1291,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
         const int quad = warp & 3, part = warp >> 2;
         const int row = quad * 32 + lane;
         uint32_t sub = 0;                                   // running sub-tile counter
+        uint32_t n_phase = 0;                               // completed phase barriers (wide grids)
         for (int64_t item = blockIdx.x; item < P.n_items; item += gridDim.x) {
             const int64_t mt = item / P.n_fgroups;
             const int fg = (int)(item - mt * P.n_fgroups);
@@ -1210,6 +1315,67 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                     ok = false;
                     break;
                 }
+                if (WIDE && !is_base) {
+                    // A feature's chunks are spread over column groups (other threads) and sub-tiles,
+                    // but the window of one input touches at most two neighbouring chunks of its
+                    // feature.  Chunks with an even index within their feature are added to gx
+                    // first, the odd ones after a barrier: in each phase an element of gx has at
+                    // most one writer, so the sums do not depend on scheduling.
+                    const int t = P.has_base ? j - 1 : j;
+                    const int gbase = (fg * sub_spline + t) * 32;           // first chunk of the sub-tile
+#pragma unroll 1
+                    for (int phase = 0; phase < 2 && ok; ++phase) {
+                        if (phase == 1) {
+                            mbar_arrive(smem_u32(&ctrl->phaseDone));
+                            if (!mbar_wait(smem_u32(&ctrl->phaseDone), n_phase & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            ++n_phase;
+                        }
+#pragma unroll 1
+                        for (int c = part; c < BLOCK_N / 32; c += 4) {
+                            const int g0 = gbase + c * 4;
+                            int f = g0 / cpf;
+                            int cw = g0 - f * cpf;
+                            if (f >= P.I) continue;                         // uniform over the warp
+                            uint32_t r[32];
+                            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BLOCK_N + c * 32, r);
+                            tmem_ld_wait();
+                            if (!row_ok) continue;
+                            int fprev = -1, s = 0;
+                            float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                if (f < P.I && (cw & 1) == phase) {
+                                    if (f != fprev) {
+                                        s = eval_feature_deriv<false, true>(tab + (size_t)f * P.ti.fs, P.ti,
+                                                                            __ldg(xrow + f), d);
+                                        fprev = f;
+                                    }
+                                    const int sp = s - 8 * cw;              // window start within this chunk
+                                    if (sp > -4 && sp < 8) {
+                                        float acc = 0.f;
+#pragma unroll
+                                        for (int slot = 0; slot < 8; ++slot) {
+                                            const int jj = slot - sp;
+                                            float dv = 0.f;
+#pragma unroll
+                                            for (int w = 0; w < 4; ++w) dv = (jj == w) ? d[w] : dv;
+                                            acc = fmaf(__uint_as_float(r[8 * e + slot]), dv, acc);
+                                        }
+                                        grow[f] += acc;
+                                    }
+                                }
+                                if (++cw == cpf) {
+                                    cw = 0;
+                                    ++f;
+                                }
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                } else {
 #pragma unroll 1
                 for (int c = part; c < BLOCK_N / 32; c += 4) {
                     uint32_t r[32];
@@ -1259,9 +1425,9 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                             float d[4];
                             int s;
                             if (shared_grid)
-                                s = eval_feature_deriv<true>(stab, xv[e], d);
+                                s = eval_feature_deriv<true, false>(stab, P.ti, xv[e], d);
                             else
-                                s = eval_feature_deriv<false>(tab + (size_t)(f < P.I ? f : P.I - 1) * TAB_FEATURE_FLOATS,
+                                s = eval_feature_deriv<false, false>(tab + (size_t)(f < P.I ? f : P.I - 1) * P.ti.fs, P.ti,
                                                               xv[e], d);
                             float acc = 0.f;
 #pragma unroll
@@ -1286,6 +1452,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                                 if (f0 + e < P.I) grow[f0 + e] = P.has_base ? grow[f0 + e] + o[e] : o[e];
                         }
                     }
+                }
                 }
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&ctrl->accEmpty[buf]));
@@ -1508,6 +1675,60 @@ finalize_blocked_kernel(const float* __restrict__ partial, BwdPlan plan,
     }
 }
 
+// The same reduction for features that own more than one chunk of 8 slots (R > 8): one thread
+// per (output, feature) with the output index fastest, so that the slabs are read in contiguous
+// 16-byte pieces per warp.
+__global__ void __launch_bounds__(256)
+finalize_wide_kernel(const float* __restrict__ partial, BwdPlan plan, int cpf,
+                     const float* __restrict__ sw, const float* __restrict__ scaler,
+                     float* __restrict__ gsw, float* __restrict__ gscaler,
+                     float* __restrict__ gbw, int O, int I, int R) {
+    const int n_ctiles = plan.n_ctiles();
+    const int64_t total = (int64_t)O * I;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int o = (int)(idx % O), i = (int)(idx / O);
+        const int ot = o >> 8, h = (o >> 7) & 1, row = o & 127;
+        auto tile_ptr = [&](int sp, int ct) -> const float4* {
+            return reinterpret_cast<const float4*>(partial) +
+                   ((((size_t)sp * plan.n_otiles + ot) * n_ctiles + ct) * 2 + h) * (size_t)(64 * 128) + row;
+        };
+        const size_t oi = (size_t)o * I + i;
+        if (gsw || gscaler) {
+            const float sc = scaler ? scaler[oi] : 1.0f;
+            float gs = 0.f;
+            for (int cw = 0; cw < cpf; ++cw) {
+                const int g = i * cpf + cw, ct = g >> 5, gl = g & 31;
+                float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int sp = 0; sp < plan.splits; ++sp) {
+                    const float4* t = tile_ptr(sp, ct);
+                    const float4 a = t[(size_t)(gl * 2) * 128], b = t[(size_t)(gl * 2 + 1) * 128];
+                    d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w;
+                    d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int r = cw * 8 + e;
+                    if (r < R) {
+                        if (gsw) gsw[oi * R + r] = scaler ? sc * d[e] : d[e];
+                        if (gscaler) gs += sw[oi * R + r] * d[e];
+                    }
+                }
+            }
+            if (gscaler) gscaler[oi] = gs;
+        }
+        if (gbw) {
+            const int ct = plan.ct_spline + (i >> 8), c = i & 255;
+            float db = 0.f;
+            for (int sp = 0; sp < plan.splits; ++sp) {
+                const float4 a = tile_ptr(sp, ct)[(size_t)(c >> 2) * 128];
+                db += (c & 3) == 0 ? a.x : ((c & 3) == 1 ? a.y : ((c & 3) == 2 ? a.z : a.w));
+            }
+            gbw[oi] = db;
+        }
+    }
+}
+
 inline int sm_count() {
     static int cached = 0;
     if (cached == 0) {
@@ -1536,7 +1757,7 @@ inline int bwd_chunk_kb() { static int c = env_int("KAN_B200_BWD_CHUNK", 16); re
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     BwdPlan p;
     p.n_otiles = (s.O + BLOCK_N - 1) / BLOCK_N;
-    p.ct_spline = (s.I + 31) / 32;
+    p.ct_spline = (s.I * make_tab_info(s.G, s.K).cpf + 31) / 32;
     p.ct_base = has_base ? (s.I + 255) / 256 : 0;
     p.kb_total = (s.N + BLOCK_K - 1) / BLOCK_K;
     p.chunk_kb = bwd_chunk_kb();
@@ -1552,12 +1773,15 @@ inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
 
 inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
-inline size_t table_bytes(const LayerShape& s) { return (size_t)s.I * TAB_FEATURE_FLOATS * sizeof(float); }
+inline size_t table_bytes(const LayerShape& s) {
+    return align256((size_t)s.I * make_tab_info(s.G, s.K).fs * sizeof(float));
+}
 
 inline cudaError_t launch_table(const float* grid, float* tab, int* status, const LayerShape& s,
                                 cudaStream_t st) {
-    const int work = s.I * (TAB_ENTRIES + 1);
-    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, status, s.I, s.G, s.K);
+    const TabInfo ti = make_tab_info(s.G, s.K);
+    const int work = s.I * (ti.nk + 1);
+    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, status, s.I, s.G, s.K, ti);
     return cudaGetLastError();
 }
 
@@ -1581,7 +1805,7 @@ struct FwdLayout {
 };
 inline FwdLayout fwd_layout(const LayerShape& s, bool has_base) {
     FwdLayout L;
-    L.cs = column_space(s.I, has_base);
+    L.cs = column_space(s.I, make_tab_info(s.G, s.K).cpf, has_base);
     L.n_otiles = (s.O + BLOCK_N - 1) / BLOCK_N;
     L.wimg_bytes = (size_t)L.n_otiles * L.cs.kb_total() * 2 * TILE_B_BYTES;
     return L;
@@ -1602,7 +1826,9 @@ inline BwdLayout bwd_layout(const LayerShape& s, bool has_base) {
 }  // namespace
 
 bool tc_supported(const LayerShape& s) {
-    return s.K >= 1 && s.K <= 3 && s.R() <= RP && s.N >= 1 && s.I >= 1 && s.O >= 1;
+    // any grid the layer accepts (G + 2 K <= 71); the window of k + 1 <= 4 values is what the
+    // table entries hold
+    return s.K >= 1 && s.K <= 3 && s.G >= 1 && s.T() <= 72 && s.N >= 1 && s.I >= 1 && s.O >= 1;
 }
 
 size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param) {
@@ -1622,6 +1848,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     if (s.N == 0) return cudaSuccess;
     const bool has_base = bw != nullptr;
     FwdLayout L = fwd_layout(s, has_base);
+    const TabInfo ti = make_tab_info(s.G, s.K);
     if (!ws || ws_bytes < kWsHeader + table_bytes(s) + L.wimg_bytes) return cudaErrorMemoryAllocation;
     int* status = reinterpret_cast<int*>(ws);
     float* tab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kWsHeader);
@@ -1633,7 +1860,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
         const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
         int blocks = (int)((chunks + 255) / 256);
         if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-        pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), L.cs.kb_spline,
+        pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), ti.cpf, L.cs.kb_spline,
                                                     kb_total, L.n_otiles);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -1647,15 +1874,20 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     P.vec_x = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     P.vec_x2 = ((s.I & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 7) == 0);
     P.vec_y = ((s.O & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    P.ti = ti;
     const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
     cudaError_t e = cudaSuccess;
-#define KAN_FWD(NT)                                                                                           \
+#define KAN_FWD(NT, W)                                                                                         \
     do {                                                                                                      \
-        e = ensure_dynamic_smem<tc_forward_kernel<NT>>((int)FWD_SMEM_BYTES);                                  \
+        e = ensure_dynamic_smem<tc_forward_kernel<NT, W>>((int)FWD_SMEM_BYTES);                               \
         if (e == cudaSuccess)                                                                                 \
-            tc_forward_kernel<NT><<<blocks, TC_THREADS, FWD_SMEM_BYTES, st>>>(x, tab, wimg, y, status, P);    \
+            tc_forward_kernel<NT, W><<<blocks, TC_THREADS, FWD_SMEM_BYTES, st>>>(x, tab, wimg, y, status, P); \
     } while (0)
-    if (split_terms == 3) KAN_FWD(3); else KAN_FWD(1);
+    if (ti.cpf == 1) {
+        if (split_terms == 3) KAN_FWD(3, false); else KAN_FWD(1, false);
+    } else {
+        if (split_terms == 3) KAN_FWD(3, true); else KAN_FWD(1, true);
+    }
 #undef KAN_FWD
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
@@ -1667,8 +1899,9 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
     cudaError_t e = cudaSuccess;
     const bool has_base = bw != nullptr;
     const bool need_param = gsw || gscaler || (gbw && has_base);
-    const bool need_x = gx != nullptr;
     if (s.N == 0) return simt_backward<float>(dY, x, grid, bw, sw, scaler, gx, gbw, gsw, gscaler, s, nullptr, 0, st);
+    const TabInfo ti = make_tab_info(s.G, s.K);
+    const bool need_x = gx != nullptr;
     if (!need_param && !need_x) return cudaSuccess;
 
     BwdLayout L = bwd_layout(s, has_base);
@@ -1697,20 +1930,32 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
     if (need_param) {
         const int64_t items = L.plan.n_items();
         const int blocks = (int)(items < sm_count() ? items : sm_count());
-#define KAN_BWD(NT)                                                                                           \
+#define KAN_BWD(NT, W)                                                                                         \
     do {                                                                                                      \
-        e = ensure_dynamic_smem<tc_bwd_param_kernel<NT>>((int)BWD_SMEM_BYTES);                                \
+        e = ensure_dynamic_smem<tc_bwd_param_kernel<NT, W>>((int)BWD_SMEM_BYTES);                             \
         if (e == cudaSuccess)                                                                                 \
-            tc_bwd_param_kernel<NT><<<blocks, TC_THREADS, BWD_SMEM_BYTES, st>>>(                              \
-                x, tab, dyimg, partial, status, s.N, s.I, s.O, L.plan, vec_ok);                               \
+            tc_bwd_param_kernel<NT, W><<<blocks, TC_THREADS, BWD_SMEM_BYTES, st>>>(                           \
+                x, tab, dyimg, partial, status, s.N, s.I, s.O, L.plan, ti, vec_ok);                           \
     } while (0)
-        if (split_terms == 3) KAN_BWD(3); else KAN_BWD(1);
+        if (ti.cpf == 1) {
+            if (split_terms == 3) KAN_BWD(3, false); else KAN_BWD(1, false);
+        } else {
+            if (split_terms == 3) KAN_BWD(3, true); else KAN_BWD(1, true);
+        }
 #undef KAN_BWD
         if (e != cudaSuccess) return e;
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        dim3 fgrid((s.O + FIN_TO - 1) / FIN_TO, (s.I + FIN_TI - 1) / FIN_TI);
-        finalize_blocked_kernel<<<fgrid, FIN_TO * FIN_TI, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
-                                                                   has_base ? gbw : nullptr, s.O, s.I, s.R());
+        if (ti.cpf == 1) {
+            dim3 fgrid((s.O + FIN_TO - 1) / FIN_TO, (s.I + FIN_TI - 1) / FIN_TI);
+            finalize_blocked_kernel<<<fgrid, FIN_TO * FIN_TI, 0, st>>>(partial, L.plan, sw, scaler, gsw, gscaler,
+                                                                       has_base ? gbw : nullptr, s.O, s.I, s.R());
+        } else {
+            const int64_t total = (int64_t)s.O * s.I;
+            int fblocks = (int)((total + 255) / 256 < (int64_t)sm_count() * 16 ? (total + 255) / 256
+                                                                               : (int64_t)sm_count() * 16);
+            finalize_wide_kernel<<<fblocks, 256, 0, st>>>(partial, L.plan, ti.cpf, sw, scaler, gsw, gscaler,
+                                                          has_base ? gbw : nullptr, s.O, s.I, s.R());
+        }
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     if (need_x) {
@@ -1719,7 +1964,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
             const int64_t chunks = (int64_t)F.n_otiles * kb_total * BLOCK_N * 8;
             int blocks = (int)((chunks + 255) / 256);
             if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-            pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), F.cs.kb_spline,
+            pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), ti.cpf, F.cs.kb_spline,
                                                         kb_total, F.n_otiles);
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
@@ -1733,15 +1978,23 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
         P.has_base = has_base ? 1 : 0;
         P.n_items = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_fgroups;
         P.vec_ok = vec_ok && ((reinterpret_cast<uintptr_t>(gx) & 15) == 0);
+        P.ti = ti;
         const int blocks = (int)(P.n_items < sm_count() ? P.n_items : sm_count());
-#define KAN_DX(NT)                                                                                            \
+#define KAN_DX(NT, W)                                                                                          \
     do {                                                                                                      \
-        e = ensure_dynamic_smem<tc_bwd_input_kernel<NT>>((int)DX_SMEM_BYTES);                                 \
+        e = ensure_dynamic_smem<tc_bwd_input_kernel<NT, W>>((int)DX_SMEM_BYTES);                              \
         if (e == cudaSuccess)                                                                                 \
-            tc_bwd_input_kernel<NT><<<blocks, TC_THREADS, DX_SMEM_BYTES, st>>>(x, tab, dyimg, wimg, gx,       \
-                                                                                status, P);                   \
+            tc_bwd_input_kernel<NT, W><<<blocks, TC_THREADS, DX_SMEM_BYTES, st>>>(x, tab, dyimg, wimg, gx,    \
+                                                                                   status, P);                \
     } while (0)
-        if (split_terms == 3) KAN_DX(3); else KAN_DX(1);
+        if (ti.cpf == 1) {
+            if (split_terms == 3) KAN_DX(3, false); else KAN_DX(1, false);
+        } else {
+            // without a base branch nothing stores gx first: the spline sub-tiles add to zeros
+            if (!has_base && (e = cudaMemsetAsync(gx, 0, (size_t)s.N * s.I * sizeof(float), st)) != cudaSuccess)
+                return e;
+            if (split_terms == 3) KAN_DX(3, true); else KAN_DX(1, true);
+        }
 #undef KAN_DX
         if (e != cudaSuccess) return e;
         e = cudaGetLastError();
