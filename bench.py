@@ -189,12 +189,16 @@ def run_gpu_arm(args):
             bucket.finish()
         return loss
 
-    x_stage = torch.empty_like(x_dev, requires_grad=bool(args.need_x))
+    # End to end: every step copies one batch from pinned host memory (the next step's, on a side
+    # stream while this step computes) and reads the loss back.
+    prefetch = sk.HostBatchPrefetcher(x_host.shape, x_host.dtype, dev)
+    prefetch.submit(x_host)
 
     def step_e2e():
-        with torch.no_grad():
-            x_stage.copy_(x_host, non_blocking=True)
-        x_stage.grad = None
+        prefetch.submit(x_host)
+        x_stage = prefetch.next()
+        if args.need_x:
+            x_stage = x_stage.detach().requires_grad_(True)
         if bucket is not None:
             bucket.zero_grad()
         else:
@@ -268,7 +272,9 @@ def run_gpu_arm(args):
                        "global_batch": args.batch, "rows_per_gpu": rows,
                        "parallelism": f"dp{world} batch shards + NCCL all-reduce of parameter gradients",
                        "mma_mode": "bf16x3 (hi/lo split operands, fp32-level accuracy)" if terms == 3 else mode,
-                       "l2": "inputs larger than L2 (x and dY are 268 MB each at 65536 rows)"},
+                       "l2": "inputs larger than L2 (x and dY are 268 MB each at 65536 rows)",
+                       "e2e_pipeline": "each step copies the next step's batch from pinned host memory on a side "
+                                       "stream (two device staging buffers) and reads the loss back"},
             "e2e": {"value": args.batch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": rows * IN_F * 4, "d2h_bytes_per_step": 4},
             "gpu_launches": (11 if args.need_x else 9) * args.steps,

@@ -322,3 +322,26 @@ def test_full_size_layer_properties():
     for buf in list(_native._ws_cache.values()):
         _native.check_status(buf)
     _native.release_workspaces()
+
+
+def test_host_batch_prefetcher_order_and_reuse():
+    """Batches come out in submission order with the right contents while copies run ahead of the
+    consumer; a third submit without a next() is refused."""
+    import torchsplinekan_b200 as sk
+    dev = torch.device("cuda", 0)
+    batches = [torch.full((1 << 20,), float(t)).pin_memory() for t in range(6)]
+    pre = sk.HostBatchPrefetcher(batches[0].shape, batches[0].dtype, dev)
+    pre.submit(batches[0])
+    sums = []
+    for t in range(6):
+        if t + 1 < 6:
+            pre.submit(batches[t + 1])
+        x = pre.next()
+        sums.append((x.double().sum() / x.numel()))
+    assert [float(s) for s in sums] == [0.0, 1.0, 2.0, 3.0, 4.0, 5.0]
+    pre.submit(batches[0])
+    pre.submit(batches[1])
+    with pytest.raises(RuntimeError, match="in flight"):
+        pre.submit(batches[2])
+    with pytest.raises(ValueError, match="does not match"):
+        sk.HostBatchPrefetcher((4,), torch.float32, dev).submit(torch.zeros(5).pin_memory())

@@ -10,8 +10,8 @@ of the native operators.
 from . import _C                      # noqa: F401  (loads the library, registers torch.ops.spline_kan.*)
 from .kan_linear import KANLinear
 from .kan import KAN
-from .data_parallel import GradientBucket, shard_rows
+from .data_parallel import GradientBucket, HostBatchPrefetcher, shard_rows
 
 __version__ = "0.1.0"
 
-__all__ = ["KANLinear", "KAN", "GradientBucket", "shard_rows", "__version__"]
+__all__ = ["KANLinear", "KAN", "GradientBucket", "HostBatchPrefetcher", "shard_rows", "__version__"]

@@ -141,3 +141,64 @@ class GradientBucket:
         for h in self._hooks:
             h.remove()
         self._hooks.clear()
+
+
+class HostBatchPrefetcher:
+    """Double-buffered host-to-device staging of input batches.
+
+    ``submit(host_batch)`` starts the copy of a pinned host batch into one of two device buffers
+    on a side stream; ``next()`` returns the oldest submitted batch once the compute stream has
+    been made to wait for its copy.  Submitting batch t+1 before running step t hides the copy
+    behind the step (the PCIe copy engine and the SMs work at the same time)::
+
+        pre = HostBatchPrefetcher(x_host.shape, x_host.dtype, device)
+        pre.submit(batches[0])
+        for t in range(steps):
+            if t + 1 < steps:
+                pre.submit(batches[t + 1])
+            x = pre.next()
+            loss = step(x)
+
+    A buffer is reused only after the step that consumed it has finished on the compute stream
+    (an event recorded by the following ``next()``).
+    """
+
+    def __init__(self, shape, dtype: torch.dtype, device: torch.device) -> None:
+        if torch.device(device).type != "cuda":
+            raise ValueError("HostBatchPrefetcher stages batches on a CUDA device")
+        self.device = torch.device(device)
+        self.stream = torch.cuda.Stream(self.device)
+        self._bufs = [torch.empty(shape, dtype=dtype, device=self.device) for _ in range(2)]
+        self._ready = [torch.cuda.Event(), torch.cuda.Event()]
+        self._released = [None, None]
+        self._submitted = 0
+        self._taken = 0
+
+    def submit(self, host_batch: torch.Tensor) -> None:
+        if self._submitted - self._taken >= 2:
+            raise RuntimeError("both staging buffers are in flight: call next() before submitting again")
+        if host_batch.shape != self._bufs[0].shape or host_batch.dtype != self._bufs[0].dtype:
+            raise ValueError(f"batch of shape {tuple(host_batch.shape)} / {host_batch.dtype} does not match the "
+                             f"staging buffers {tuple(self._bufs[0].shape)} / {self._bufs[0].dtype}")
+        i = self._submitted % 2
+        with torch.cuda.stream(self.stream):
+            if self._released[i] is not None:
+                self.stream.wait_event(self._released[i])
+            self._bufs[i].copy_(host_batch, non_blocking=True)
+            self._ready[i].record(self.stream)
+        self._submitted += 1
+
+    def next(self) -> torch.Tensor:
+        if self._taken >= self._submitted:
+            raise RuntimeError("next() without a submitted batch")
+        cur = torch.cuda.current_stream(self.device)
+        if self._taken > 0:
+            # everything queued so far on the compute stream used the previous buffer
+            j = (self._taken - 1) % 2
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            self._released[j] = ev
+        i = self._taken % 2
+        cur.wait_event(self._ready[i])
+        self._taken += 1
+        return self._bufs[i]
