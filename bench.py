@@ -248,6 +248,8 @@ def run_gpu_arm(args):
 
     for buf in list(_native._ws_cache.values()):
         _native.check_status(buf)
+    if bucket is not None:
+        bucket.check()
 
     per = {}
     for name, a, b in log:
@@ -270,7 +272,8 @@ def run_gpu_arm(args):
             "config": {"workload": "KANLinear 1024->1024 G=5 k=3 fp32, fwd+bwd of sum(y^2), x "
                                    + ("with grad (input gradient computed)" if args.need_x else "without grad"),
                        "global_batch": args.batch, "rows_per_gpu": rows,
-                       "parallelism": f"dp{world} batch shards + NCCL all-reduce of parameter gradients",
+                       "parallelism": f"dp{world} batch shards + all-reduce of parameter gradients ("
+                                      + (bucket.transport if bucket is not None else "single rank") + ")",
                        "mma_mode": "bf16x3 (hi/lo split operands, fp32-level accuracy)" if terms == 3 else mode,
                        "l2": "inputs larger than L2 (x and dY are 268 MB each at 65536 rows)",
                        "e2e_pipeline": "each step copies the next step's batch from pinned host memory on a side "
@@ -414,7 +417,7 @@ def run_config(args):
         x = x.clamp_(-1, 1).to(dev)
         net.update_grid(x)
         loss_fn = lambda: net(x).square().sum()
-        name, rows = "c3 KANLinear 512->512 G=64 N=16384 fp32 (gather kernels), update_grid knots", 16384
+        name, rows = "c3 KANLinear 512->512 G=64 N=16384 fp32, update_grid knots", 16384
     elif c == 4:
         net = sk.KAN([2, 64, 64, 1], grid_size=8, backend="cuda").to(dev, torch.float64)
         x = (torch.rand(131072, 2, generator=g, dtype=torch.float64) * 2 - 1).to(dev)
@@ -429,14 +432,28 @@ def run_config(args):
             p.grad = None
         loss_fn().backward()
 
+    run = step
+    if args.graph:
+        # the whole step (forward, loss, backward) captured once and replayed: one launch per step
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run = graph.replay
+        name += ", CUDA graph replay"
     for _ in range(max(args.warmup, 3)):
-        step()
+        run()
     torch.cuda.synchronize()
     times = []
     for _ in range(args.steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        step()
+        run()
         b.record()
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
@@ -459,6 +476,7 @@ def main():
     ap.add_argument("--micro", action="store_true", help="time the secondary kernels instead of the training step")
     ap.add_argument("--micro-rows", type=int, default=16384)
     ap.add_argument("--config", type=int, default=None, help="time one of the other benchmark configurations")
+    ap.add_argument("--graph", action="store_true", help="with --config: capture the step in a CUDA graph")
     args = ap.parse_args()
     if args.config is not None:
         run_config(args)

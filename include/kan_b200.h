@@ -160,6 +160,28 @@ KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const vo
                        uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps,
                        uint32_t a_step, uint32_t b_step, int ncols, float* D, int* status, void* stream);
 
+/* ---- data-parallel gradient all-reduce over NVLink (no counterpart in the reference, which
+ * is single-device; it is what batch-sharded training of KANLinear needs after
+ * kanb200_backward) ------------------------------------------------------------------------
+ * Every rank owns one allocation of the same size that every rank of the node has mapped
+ * ("symmetric" memory: cuMem / IPC peer mappings, e.g. torch.distributed._symmetric_memory):
+ *     [payload_offset, +n_floats*4)   float32 gradients (n_floats a multiple of 4, 16-byte aligned)
+ *     [pad_offset, +kanb200_allreduce_pad_bytes(world, blocks))   signal words, zero before first use
+ * One call per rank, on its own stream, replaces every rank's payload with `scale` times the sum
+ * over the ranks.  peer_bases[p] is THIS process's mapping of rank p's allocation (world entries,
+ * host array).  multicast_base, when not NULL, is a multicast mapping of the same allocations
+ * (NVSwitch): the kernel then reduces in the switch (multimem.ld_reduce / multimem.st);
+ * otherwise the owner of each slice loads it from every peer and stores the sum to every peer.
+ * local_ranks > 1 runs ranks rank .. rank+local_ranks-1 of ONE device inside a single launch
+ * (peer loads only) - the way to exercise the protocol on one GPU.  *status (device int) is set
+ * to 1 when a bounded wait on another rank ran out; the pad must then be zeroed. */
+#define KANB200_MAX_RANKS 16
+KANB200_API size_t kanb200_allreduce_pad_bytes(int world, int blocks);
+KANB200_API int kanb200_allreduce_sum_f32(const void* const* peer_bases, void* multicast_base,
+                                          size_t payload_offset, size_t pad_offset, size_t n_floats,
+                                          int rank, int world, int local_ranks, int blocks, float scale,
+                                          int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -307,3 +307,69 @@ def test_limits_rejected_before_launch():
         nat.basis(x, grid, 3)
     with pytest.raises(RuntimeError, match="no CPU path"):
         nat.basis(torch.zeros(4, 2), torch.zeros(2, 12), 3)
+
+
+# ---------------------------------------------------------------------------
+# gradient all-reduce kernel: several ranks of one device inside a single launch
+# ---------------------------------------------------------------------------
+def _emulated_ranks(world, n, blocks, seed=0):
+    pad = nat.allreduce_pad_bytes(world, blocks)
+    stride = (n + pad // 4 + 63) // 64 * 64
+    buf = torch.zeros(world, stride, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    buf[:, :n] = torch.randn(world, n, device="cuda", generator=g)
+    return buf, [buf[r].data_ptr() for r in range(world)], n * 4
+
+
+@pytest.mark.parametrize("world,n,blocks", [(2, 4 * 1000, 4), (4, 4 * 123457, 8), (8, 4 * 50001, 16), (3, 8, 2)])
+def test_allreduce_kernel_peer_loads_emulated_ranks(world, n, blocks):
+    """Peer-load variant with all ranks' blocks co-resident in one launch: every rank's copy ends
+    up with the sum taken in rank order (bit-exact), the signal pad returns to zero and can be
+    reused by the next call."""
+    buf, ptrs, pad_off = _emulated_ranks(world, n, blocks)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    before = buf[:, :n].clone()
+    want = torch.zeros(n, device="cuda")
+    for r in range(world):
+        want = want + before[r]
+    want = want * 0.5
+    nat.allreduce_sum(ptrs, 0, 0, pad_off, n, 0, world, status, local_ranks=world, blocks=blocks, scale=0.5)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for r in range(world):
+        assert torch.equal(buf[r, :n], want), r
+    assert int(buf[:, n:].abs().sum().item()) == 0          # pad lowered again
+    # second call on the result: world * 0.5 * want, same pad
+    nat.allreduce_sum(ptrs, 0, 0, pad_off, n, 0, world, status, local_ranks=world, blocks=blocks, scale=1.0)
+    torch.cuda.synchronize()
+    want2 = torch.zeros(n, device="cuda")
+    for r in range(world):
+        want2 = want2 + want
+    assert int(status.item()) == 0 and torch.equal(buf[0, :n], want2) and torch.equal(buf[world - 1, :n], want2)
+
+
+def test_allreduce_kernel_missing_rank_times_out_with_status():
+    """A rank that never launches: the waits of the others run out after two seconds, the kernel
+    returns with status 1 and the context stays usable."""
+    world, n, blocks = 2, 4 * 256, 2
+    buf, ptrs, pad_off = _emulated_ranks(world, n, blocks)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    before = buf.clone()
+    nat.allreduce_sum(ptrs, 0, 0, pad_off, n, 0, world, status, local_ranks=1, blocks=blocks)   # rank 0 only
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    assert torch.equal(buf[:, :n], before[:, :n])            # nothing was reduced
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0  # the device still answers
+
+
+def test_allreduce_argument_checks():
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    buf = torch.zeros(1024, device="cuda")
+    with pytest.raises(RuntimeError, match="world size"):
+        nat.allreduce_sum([buf.data_ptr()] * 17, 0, 0, 2048, 64, 0, 17, status)
+    with pytest.raises(RuntimeError, match="multiple of 4"):
+        nat.allreduce_sum([buf.data_ptr()], 0, 0, 2048, 63, 0, 1, status)
+    with pytest.raises(RuntimeError, match="overlaps"):
+        nat.allreduce_sum([buf.data_ptr()], 0, 0, 128, 64, 0, 1, status)
+    with pytest.raises(RuntimeError, match="peer loads"):
+        nat.allreduce_sum([buf.data_ptr()] * 2, buf.data_ptr(), 0, 2048, 64, 0, 2, status, local_ranks=2)

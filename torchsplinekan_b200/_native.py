@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -52,6 +52,9 @@ SIGNATURES = {
     "kanb200_umma_probe": (_c_int, [_c_void_p, ctypes.c_uint32, _c_void_p, ctypes.c_uint32, ctypes.c_uint64,
                                     ctypes.c_uint64, ctypes.c_uint32, _c_int, ctypes.c_uint32, ctypes.c_uint32,
                                     _c_int, _c_void_p, _c_void_p, _c_void_p]),
+    "kanb200_allreduce_pad_bytes": (_c_size, [_c_int, _c_int]),
+    "kanb200_allreduce_sum_f32": (_c_int, [ctypes.POINTER(_c_void_p), _c_void_p, _c_size, _c_size, _c_size,
+                                           _c_int, _c_int, _c_int, _c_int, ctypes.c_float, _c_void_p, _c_void_p]),
 }
 
 _lib = None
@@ -308,3 +311,32 @@ def check_status(ws: Optional[torch.Tensor]) -> None:
         return
     with torch.cuda.device(ws.device):
         _check(lib().kanb200_check_status(_p(ws), _stream(ws.device)))
+
+
+# ---------------------------------------------------------------------------
+# gradient all-reduce over symmetric memory
+# ---------------------------------------------------------------------------
+MAX_RANKS = 16
+
+
+def allreduce_pad_bytes(world: int, blocks: int) -> int:
+    n = int(lib().kanb200_allreduce_pad_bytes(int(world), int(blocks)))
+    if n == 0:
+        raise RuntimeError(f"all-reduce: world size {world} / {blocks} blocks not supported")
+    return n
+
+
+def allreduce_sum(peer_ptrs: Sequence[int], multicast_ptr: int, payload_offset: int, pad_offset: int,
+                  n_floats: int, rank: int, world: int, status: torch.Tensor, *, local_ranks: int = 1,
+                  blocks: int = 32, scale: float = 1.0) -> None:
+    """Launches the all-reduce kernel of this rank on the current stream of ``status.device``.
+    ``peer_ptrs[p]``: this process's mapping of rank p's allocation; ``multicast_ptr``: multicast
+    mapping of the same allocations or 0; ``status``: one int32 on the device."""
+    if not status.is_cuda or status.dtype != torch.int32 or status.numel() < 1:
+        raise RuntimeError("all-reduce status must be a CUDA int32 tensor")
+    arr = (_c_void_p * len(peer_ptrs))(*[int(v) for v in peer_ptrs])
+    with torch.cuda.device(status.device):
+        _check(lib().kanb200_allreduce_sum_f32(arr, _c_void_p(int(multicast_ptr) or None), int(payload_offset),
+                                               int(pad_offset), int(n_floats), int(rank), int(world),
+                                               int(local_ranks), int(blocks), float(scale), _p(status),
+                                               _stream(status.device)))

@@ -319,4 +319,35 @@ KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const vo
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "umma_probe");
 }
 
+KANB200_API size_t kanb200_allreduce_pad_bytes(int world, int blocks) {
+    if (world < 1 || world > KANB200_MAX_RANKS || blocks < 1) return 0;
+    return allreduce_pad_bytes(world, blocks);
+}
+
+KANB200_API int kanb200_allreduce_sum_f32(const void* const* peer_bases, void* multicast_base,
+                                          size_t payload_offset, size_t pad_offset, size_t n_floats,
+                                          int rank, int world, int local_ranks, int blocks, float scale,
+                                          int* status, void* stream) {
+    if (world < 1 || world > KANB200_MAX_RANKS)
+        return fail(KANB200_EINVAL, "allreduce: world size %d outside [1, %d]", world, KANB200_MAX_RANKS);
+    if (local_ranks < 1 || rank < 0 || rank + local_ranks > world)
+        return fail(KANB200_EINVAL, "allreduce: ranks [%d, %d) outside world of size %d", rank, rank + local_ranks,
+                    world);
+    if (blocks < 1 || blocks > 1024) return fail(KANB200_EINVAL, "allreduce: blocks must be in [1, 1024]");
+    if (!peer_bases || !status) return fail(KANB200_EINVAL, "allreduce: peer_bases and status must not be NULL");
+    for (int p = 0; p < world; ++p)
+        if (!peer_bases[p]) return fail(KANB200_EINVAL, "allreduce: peer_bases[%d] is NULL", p);
+    if (n_floats % 4 != 0 || payload_offset % 16 != 0 || pad_offset % 4 != 0)
+        return fail(KANB200_EINVAL, "allreduce: n_floats must be a multiple of 4 and the payload 16-byte aligned");
+    const size_t pad = allreduce_pad_bytes(world, blocks);
+    if (!(pad_offset >= payload_offset + n_floats * 4 || pad_offset + pad <= payload_offset))
+        return fail(KANB200_EINVAL, "allreduce: signal pad overlaps the payload");
+    if (multicast_base && local_ranks != 1)
+        return fail(KANB200_EINVAL, "allreduce: several ranks in one launch use peer loads (multicast_base NULL)");
+    if (n_floats == 0 && world == 1) return KANB200_OK;
+    cudaError_t e = allreduce_sum(const_cast<void* const*>(peer_bases), multicast_base, payload_offset, pad_offset,
+                                  n_floats, rank, world, local_ranks, blocks, scale, status, (cudaStream_t)stream);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "allreduce_sum");
+}
+
 }  // extern "C"

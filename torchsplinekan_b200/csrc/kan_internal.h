@@ -69,6 +69,12 @@ cudaError_t umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, u
                        uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps, uint32_t a_step,
                        uint32_t b_step, int ncols, float* D, int* status, cudaStream_t st);
 
+// Gradient all-reduce over symmetric memory (kan_collective.cu).
+size_t allreduce_pad_bytes(int world, int blocks);
+cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, size_t payload_off, size_t pad_off,
+                          size_t n_floats, int rank, int world, int local_ranks, int blocks, float scale,
+                          int* status, cudaStream_t st);
+
 // Workspaces start with a 256-byte header whose first word is a status code
 // written by kernels whose bounded waits ran out.
 constexpr size_t kWsHeader = 256;

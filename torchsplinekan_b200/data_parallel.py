@@ -9,9 +9,16 @@ code; this module is what a data-parallel user of it needs on top.
 Per layer the gradients live in one flat bucket ``[d spline_weight | d spline_scaler |
 d base_weight]`` and ``param.grad`` are views into it, so nothing is copied
 before or after the collective.
+
+Two transports: ``"nccl"`` (``torch.distributed.all_reduce``) and ``"nvlink"``, where the buckets
+live in symmetric memory (``torch.distributed._symmetric_memory``: every rank of the node maps
+every rank's allocation, plus a multicast mapping through NVSwitch where the fabric offers one)
+and the reduction is this library's own kernel (``kanb200_allreduce_sum_f32``: in-switch
+``multimem`` reduction, or peer loads/stores).
 """
 from __future__ import annotations
 
+import os
 from typing import Iterable, List, Optional, Tuple
 
 import torch
@@ -44,10 +51,18 @@ class GradientBucket:
     :meth:`finish` after ``loss.backward()`` and before the optimiser step.
     ``average=True`` divides by the world size (for mean-type losses); sum-type
     losses keep the plain sum.
+
+    ``transport``: ``"nccl"``, ``"nvlink"`` (raises when symmetric memory cannot be set up) or
+    ``"auto"`` (``"nvlink"`` for float32 CUDA parameters of one device when the set-up succeeds,
+    else ``"nccl"``; the environment variable ``KAN_B200_ALLREDUCE`` = ``nccl`` / ``nvlink`` /
+    ``p2p`` overrides it, ``p2p`` meaning the NVLink kernel without the multicast mapping).
+    Construction is collective over the group when the NVLink transport is tried.
     """
 
     def __init__(self, layers: Iterable[nn.Module], process_group: Optional[dist.ProcessGroup] = None,
-                 average: bool = False) -> None:
+                 average: bool = False, transport: str = "auto") -> None:
+        if transport not in ("auto", "nccl", "nvlink"):
+            raise ValueError(f"transport must be 'auto', 'nccl' or 'nvlink', got {transport!r}")
         self.group = process_group
         self.average = average
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
@@ -56,12 +71,18 @@ class GradientBucket:
         self._works: list = []
         self._comm_stream = None
         self._hooks = []
-        for layer in layers:
-            params = _layer_params(layer)
-            if not params:
-                continue
+        self.transport = "nccl"
+        self.transport_note = ""
+        self._symm = None
+        per_layer = [_layer_params(layer) for layer in layers]
+        per_layer = [params for params in per_layer if params]
+        self._setup_symmetric(per_layer, transport)
+        for li, params in enumerate(per_layer):
             ref = params[0]
-            flat = torch.zeros(sum(p.numel() for p in params), dtype=ref.dtype, device=ref.device)
+            if self._symm is not None:
+                flat = self._symm.flat(li)
+            else:
+                flat = torch.zeros(sum(p.numel() for p in params), dtype=ref.dtype, device=ref.device)
             offset = 0
             for p in params:
                 p.grad = flat[offset:offset + p.numel()].view_as(p)
@@ -73,6 +94,41 @@ class GradientBucket:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(index)))
             if ref.is_cuda and self._comm_stream is None:
                 self._comm_stream = torch.cuda.Stream(device=ref.device)
+
+    def _setup_symmetric(self, per_layer: List[List[nn.Parameter]], transport: str) -> None:
+        env = os.environ.get("KAN_B200_ALLREDUCE", "").lower()
+        if env in ("nccl", "nvlink", "p2p"):
+            transport = "nccl" if env == "nccl" else "nvlink"
+        if transport == "nccl" or self.world == 1 or not per_layer:
+            return
+        params = [p for layer in per_layer for p in layer]
+        same = all(p.is_cuda and p.dtype == torch.float32 and p.device == params[0].device for p in params)
+        try:
+            if not same:
+                raise RuntimeError("the NVLink transport needs float32 parameters on one CUDA device")
+            if self.world > 16:
+                raise RuntimeError("the NVLink transport serves up to 16 ranks of one node")
+            self._symm = _SymmetricBuckets([sum(p.numel() for p in layer) for layer in per_layer],
+                                           params[0].device, self.group, use_multicast=(env != "p2p"))
+            failure = None
+        except Exception as exc:                       # noqa: BLE001  (any set-up failure -> NCCL)
+            self._symm = None
+            failure = exc
+        # every rank must end up with the same transport (and the same kind of kernel)
+        flags = torch.tensor([1 if self._symm is not None else 0,
+                              1 if self._symm is not None and self._symm.multicast_ptr else 0],
+                             dtype=torch.int32, device=params[0].device if all(p.is_cuda for p in params) else "cpu")
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=self.group)
+        all_ok, all_mc = (int(v) for v in flags.tolist())
+        if not all_ok:
+            self._symm = None
+            if transport == "nvlink":
+                raise RuntimeError(f"NVLink transport unavailable on at least one rank (here: {failure!r})")
+            self.transport_note = f"NVLink transport unavailable ({failure!r}); using NCCL"
+            return
+        if not all_mc:
+            self._symm.multicast_ptr = 0
+        self.transport = "nvlink-multimem" if self._symm.multicast_ptr else "nvlink-p2p"
 
     @property
     def buckets(self) -> List[torch.Tensor]:
@@ -108,7 +164,11 @@ class GradientBucket:
             ready.record(torch.cuda.current_stream(flat.device))
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ready)
-                self._works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                if self._symm is not None:
+                    self._symm.all_reduce(index, 1.0 / self.world if self.average else 1.0)
+                else:
+                    self._works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group,
+                                                       async_op=True))
         else:
             self._works.append(dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
 
@@ -122,7 +182,7 @@ class GradientBucket:
         self._works.clear()
         if self._comm_stream is not None:
             torch.cuda.current_stream(self._comm_stream.device).wait_stream(self._comm_stream)
-        if self.average and self.world > 1:
+        if self.average and self.world > 1 and self._symm is None:
             for flat, _ in self._buckets:
                 flat.div_(self.world)
         self._pending = [len(params) for _, params in self._buckets]
@@ -141,6 +201,63 @@ class GradientBucket:
         for h in self._hooks:
             h.remove()
         self._hooks.clear()
+
+    def check(self) -> None:
+        """Synchronises and raises if an NVLink all-reduce kernel gave up waiting for another rank."""
+        if self._symm is not None:
+            self._symm.check()
+
+
+class _SymmetricBuckets:
+    """One symmetric allocation ``[bucket 0 | bucket 1 | ... | signal pad]`` shared by the ranks of
+    a node, and the launcher of the library's all-reduce kernel on its buckets."""
+
+    # The in-switch reduction is bound by the links, not by the number of requests in flight: a few
+    # blocks reach its rate and leave the SMs to the backward kernels of the layers below.  Peer
+    # loads need many more requests in flight.
+    BLOCKS_MULTIMEM = 8
+    BLOCKS_P2P = 96
+    MAX_BLOCKS = 128
+
+    def __init__(self, sizes: List[int], device: torch.device, group, use_multicast: bool = True) -> None:
+        import torch.distributed._symmetric_memory as symm
+        from . import _native
+        self._native = _native
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.offsets, total = [], 0
+        self.sizes = [(n + 3) // 4 * 4 for n in sizes]          # the kernel moves 16-byte pieces
+        self.used = list(sizes)
+        for n in self.sizes:
+            self.offsets.append(total)
+            total += (n + 63) // 64 * 64                           # 256-byte aligned buckets
+        self.pad_offset = total * 4
+        pad_floats = _native.allreduce_pad_bytes(self.world, self.MAX_BLOCKS) // 4
+        pg = group if group is not None else dist.group.WORLD
+        self.buffer = symm.empty(total + pad_floats, dtype=torch.float32, device=device)
+        self.buffer.zero_()
+        torch.cuda.synchronize(device)
+        self.handle = symm.rendezvous(self.buffer, pg.group_name)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        mc = int(self.handle.multicast_ptr) if use_multicast else 0
+        self.multicast_ptr = mc
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.barrier(group)                                        # every pad is zero before first use
+
+    def flat(self, index: int) -> torch.Tensor:
+        lo = self.offsets[index]
+        return self.buffer[lo:lo + self.used[index]]
+
+    def all_reduce(self, index: int, scale: float) -> None:
+        self._native.allreduce_sum(self.peer_ptrs, self.multicast_ptr, self.offsets[index] * 4, self.pad_offset,
+                                   self.sizes[index], self.rank, self.world, self.status,
+                                   blocks=self.BLOCKS_MULTIMEM if self.multicast_ptr else self.BLOCKS_P2P,
+                                   scale=scale)
+
+    def check(self) -> None:
+        if int(self.status.item()) != 0:
+            raise RuntimeError("NVLink all-reduce: a bounded wait on another rank ran out "
+                               "(a rank is missing or far behind); the signal pad must be zeroed before reuse")
 
 
 class HostBatchPrefetcher:
