@@ -53,7 +53,7 @@ def _worker(rank, world, port, transport_env, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport_env,expect", [("", "nvlink"), ("p2p", "nvlink-p2p"), ("nccl", "nccl")])
+@pytest.mark.parametrize("transport_env,expect", [("nvlink", "nvlink"), ("p2p", "nvlink-p2p"), ("", "nccl")])
 def test_gradient_bucket_transports_match_whole_batch(transport_env, expect):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
