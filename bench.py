@@ -173,7 +173,7 @@ def run_gpu_arm(args):
     x_dev = x_host.to(dev)
     if args.need_x:
         x_dev.requires_grad_(True)
-    bucket = sk.GradientBucket([layer]) if world > 1 else None
+    bucket = sk.GradientBucket([layer], direct=True) if world > 1 else None
 
     def step_resident():
         if bucket is not None:
@@ -256,6 +256,20 @@ def run_gpu_arm(args):
         per.setdefault(name, []).append(a.elapsed_time(b))
     kernel_ms = {k: sum(v) / len(v) for k, v in per.items()}
 
+    # this library's kernels per step: forward = table + weight image + contraction; parameter
+    # backward = table + dY image + contraction + finalize (once per range of output rows when the
+    # gradients go straight into the all-reduce bucket); input gradient = weight image + contraction
+    # (+ table and dY image when it is a call of its own); one all-reduce kernel per range on NVLink
+    if bucket is not None and bucket._sinks:
+        n_ranges = len(bucket._sinks[0].row_ranges(OUT_F))
+        launches_per_step = 3 + 4 * n_ranges + (4 if args.need_x else 0)
+        if bucket.transport.startswith("nvlink"):
+            launches_per_step += n_ranges
+    else:
+        launches_per_step = 7 + (2 if args.need_x else 0)
+        if bucket is not None and bucket.transport.startswith("nvlink"):
+            launches_per_step += 1
+
     if rank == 0:
         bf16_peak, hbm_peak, peak_src = measured_peaks()
         ms_step = ms_total / args.steps
@@ -273,14 +287,17 @@ def run_gpu_arm(args):
                                    + ("with grad (input gradient computed)" if args.need_x else "without grad"),
                        "global_batch": args.batch, "rows_per_gpu": rows,
                        "parallelism": f"dp{world} batch shards + all-reduce of parameter gradients ("
-                                      + (bucket.transport if bucket is not None else "single rank") + ")",
+                                      + ((bucket.transport + (", gradients written into the bucket by ranges of output rows, "
+                                                             "all-reduce of a range overlaps the next"
+                                                             if bucket._sinks else ""))
+                                         if bucket is not None else "single rank") + ")",
                        "mma_mode": "bf16x3 (hi/lo split operands, fp32-level accuracy)" if terms == 3 else mode,
                        "l2": "inputs larger than L2 (x and dY are 268 MB each at 65536 rows)",
                        "e2e_pipeline": "each step copies the next step's batch from pinned host memory on a side "
                                        "stream (two device staging buffers) and reads the loss back"},
             "e2e": {"value": args.batch / (ms_e2e / args.steps * 1e-3), "unit": "samples/s",
                     "h2d_bytes_per_step": rows * IN_F * 4, "d2h_bytes_per_step": 4},
-            "gpu_launches": (11 if args.need_x else 9) * args.steps,
+            "gpu_launches": launches_per_step * args.steps,
             "kernel_ms": kernel_ms,
             "roofline": {"bound": "tensor", "kernel": f"{dom} (tcgen05 contraction + operand producers)",
                          "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s",

@@ -160,6 +160,18 @@ KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const vo
                        uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps,
                        uint32_t a_step, uint32_t b_step, int ncols, float* D, int* status, void* stream);
 
+/* Parameter gradients of the output rows [o_begin, o_end) only (tensor-core modes, float32): the
+ * pointers are those of the FULL tensors as in kanb200_backward; rows outside the range are not
+ * touched.  Calling it range by range lets a data-parallel host start the all-reduce of one
+ * range while the next is being computed.  Workspace as for kanb200_backward with need_param. */
+KANB200_API int kanb200_backward_param_rows(int mode, const void* grad_out, const void* x, const void* grid,
+                                            const void* base_weight, const void* spline_weight,
+                                            const void* spline_scaler, void* grad_base_weight,
+                                            void* grad_spline_weight, void* grad_spline_scaler,
+                                            int64_t N, int64_t I, int64_t O, int G, int k,
+                                            int64_t o_begin, int64_t o_end,
+                                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- data-parallel gradient all-reduce over NVLink (no counterpart in the reference, which
  * is single-device; it is what batch-sharded training of KANLinear needs after
  * kanb200_backward) ------------------------------------------------------------------------
@@ -176,11 +188,20 @@ KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const vo
  * (peer loads only) - the way to exercise the protocol on one GPU.  *status (device int) is set
  * to 1 when a bounded wait on another rank ran out; the pad must then be zeroed. */
 #define KANB200_MAX_RANKS 16
+#define KANB200_MAX_SEGMENTS 4
 KANB200_API size_t kanb200_allreduce_pad_bytes(int world, int blocks);
 KANB200_API int kanb200_allreduce_sum_f32(const void* const* peer_bases, void* multicast_base,
                                           size_t payload_offset, size_t pad_offset, size_t n_floats,
                                           int rank, int world, int local_ranks, int blocks, float scale,
                                           int* status, void* stream);
+
+/* The same reduction over up to KANB200_MAX_SEGMENTS ranges of the allocation in one launch
+ * (offsets[i] bytes from the base, n_floats[i] floats), with `threads` threads per block (a
+ * multiple of 32 up to 512; 128 lets a block share an SM with one of the tensor-core kernels). */
+KANB200_API int kanb200_allreduce_sum_f32_ranges(const void* const* peer_bases, void* multicast_base,
+                                                 const size_t* offsets, const size_t* n_floats, int n_ranges,
+                                                 size_t pad_offset, int rank, int world, int local_ranks,
+                                                 int blocks, int threads, float scale, int* status, void* stream);
 
 #ifdef __cplusplus
 }

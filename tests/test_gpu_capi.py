@@ -373,3 +373,27 @@ def test_allreduce_argument_checks():
         nat.allreduce_sum([buf.data_ptr()], 0, 0, 128, 64, 0, 1, status)
     with pytest.raises(RuntimeError, match="peer loads"):
         nat.allreduce_sum([buf.data_ptr()] * 2, buf.data_ptr(), 0, 2048, 64, 0, 2, status, local_ranks=2)
+
+
+def test_allreduce_kernel_ranges_small_blocks_emulated_ranks():
+    """Three ranges of the allocation in one launch with 128-thread blocks (the configuration that
+    shares the SMs with a tensor-core kernel); data between the ranges is left alone."""
+    world, blocks, n = 4, 8, 4 * 30000
+    buf, ptrs, pad_off = _emulated_ranks(world, n, blocks, seed=3)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    before = buf[:, :n].clone()
+    ranges = [(0, 4 * 5000), (4 * 4 * 6000, 4 * 7001), (4 * 4 * 20000, 4 * 3)]      # (byte offset, floats)
+    nat.allreduce_sum_ranges(ptrs, 0, ranges, pad_off, 0, world, status, local_ranks=world, blocks=blocks,
+                             threads=128)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = before.clone()
+    for off, cnt in ranges:
+        lo = off // 4
+        tot = torch.zeros(cnt, device="cuda")
+        for r in range(world):
+            tot = tot + before[r, lo:lo + cnt]
+        want[:, lo:lo + cnt] = tot
+    assert torch.equal(buf[:, :n], want)
+    with pytest.raises(RuntimeError, match="between 1 and 4 ranges"):
+        nat.allreduce_sum_ranges(ptrs, 0, ranges + ranges, pad_off, 0, world, status, local_ranks=world)

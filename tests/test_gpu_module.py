@@ -382,3 +382,38 @@ def test_training_step_in_cuda_graph():
         assert got[0] == pytest.approx(want[0], rel=1e-6)
         for a, b in zip(got[1:], want[1:]):
             assert _err(a, b) < 1e-6
+
+
+@pytest.mark.parametrize("chunks", [1, 4])
+@pytest.mark.parametrize("need_x", [False, True])
+def test_direct_gradient_sink_matches_autograd(chunks, need_x):
+    """GradientBucket(direct=True): the backward writes the parameter gradients into the bucket
+    range by range of output rows; same numbers as the ordinary autograd path."""
+    import torchsplinekan_b200 as sk
+    torch.manual_seed(3)
+    layer = sk.KANLinear(64, 1000, backend="cuda").cuda()       # 4 ranges of 256 rows, the last ragged
+    plain = sk.KANLinear(64, 1000, backend="cuda").cuda()
+    plain.load_state_dict(layer.state_dict())
+    x = (torch.rand(700, 64, device="cuda") * 2 - 1).requires_grad_(need_x)
+    x2 = x.detach().clone().requires_grad_(need_x)
+    bucket = sk.GradientBucket([layer], direct=True)
+    try:
+        assert len(bucket._sinks) == 1
+        bucket._sinks[0].chunks = chunks
+        assert len(bucket._sinks[0].row_ranges(1000)) == chunks
+        for _ in range(2):                                       # a second step overwrites, not accumulates
+            bucket.zero_grad()
+            layer(x).square().sum().backward()
+            bucket.finish()
+        plain(x2).square().sum().backward()
+        for (n, p), q in zip(layer.named_parameters(), plain.parameters()):
+            assert p.grad.data_ptr() >= bucket.buckets[0].data_ptr()
+            assert _err(p.grad, q.grad) < 1e-6, n
+        if need_x:
+            assert _err(x.grad, 2 * x2.grad) < 1e-6              # x.grad accumulated over the two steps
+    finally:
+        bucket.remove()
+    # after remove() the layer is back on the ordinary path
+    layer.zero_grad()
+    layer(x.detach()).square().sum().backward()
+    assert _err(layer.spline_weight.grad, plain.spline_weight.grad) < 1e-6

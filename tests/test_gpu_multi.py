@@ -19,7 +19,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, transport_env, out):
+def _worker(rank, world, port, transport_env, direct, out):
     import torch.distributed as dist
     import torchsplinekan_b200 as sk
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
@@ -30,11 +30,11 @@ def _worker(rank, world, port, transport_env, out):
     dist.init_process_group("nccl", device_id=dev)
     try:
         torch.manual_seed(0)
-        net = sk.KAN([24, 40, 6], backend="cuda").to(dev)
+        net = sk.KAN([24, 520, 6], backend="cuda").to(dev)
         g = torch.Generator().manual_seed(1)
         x = (torch.rand(1030, 24, generator=g) * 2 - 1)
         r0, r1 = sk.shard_rows(x.shape[0], world, rank)
-        bucket = sk.GradientBucket(net.layers, transport="auto")
+        bucket = sk.GradientBucket(net.layers, transport="auto", direct=direct, chunks=3)
         for step in range(3):                              # the signal pad is reused across steps
             bucket.zero_grad()
             net(x[r0:r1].to(dev)).square().sum().backward()
@@ -44,7 +44,8 @@ def _worker(rank, world, port, transport_env, out):
         if rank == 0:
             out["transport"] = bucket.transport
             out["grads"] = [p.grad.detach().cpu() for p in net.parameters()]
-            ref = sk.KAN([24, 40, 6], backend="cuda").to(dev)
+            out["sinks"] = len(bucket._sinks)
+            ref = sk.KAN([24, 520, 6], backend="cuda").to(dev)
             ref.load_state_dict(net.state_dict())
             ref(x.to(dev)).square().sum().backward()
             out["ref"] = [p.grad.detach().cpu() for p in ref.parameters()]
@@ -53,16 +54,18 @@ def _worker(rank, world, port, transport_env, out):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("direct", [False, True])
 @pytest.mark.parametrize("transport_env,expect", [("nvlink", "nvlink"), ("p2p", "nvlink-p2p"), ("", "nccl")])
-def test_gradient_bucket_transports_match_whole_batch(transport_env, expect):
+def test_gradient_bucket_transports_match_whole_batch(transport_env, expect, direct):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     world = 2
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), transport_env, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), transport_env, direct, out), nprocs=world, join=True)
     assert out["transport"].startswith(expect), out["transport"]
+    assert out["sinks"] == (2 if direct else 0)
     for got, want in zip(out["grads"], out["ref"]):
         err = float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
         assert err < 2e-5, err

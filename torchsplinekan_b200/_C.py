@@ -162,6 +162,51 @@ def kan_backward_composite(grad_output, x, grid, base_weight, spline_weight, spl
     return gx, g_base, g_spline, g_scaler
 
 
+# Gradient sinks: a data-parallel host may register, per layer (keyed by the storage of its
+# spline_weight), an object that receives the parameter gradients directly -- the backward then
+# writes them range by range of output rows into the sink's tensors (no autograd accumulation)
+# and tells the sink after each range, so that the all-reduce of one range overlaps the
+# computation of the next.  See data_parallel.GradientBucket(direct=True).
+_grad_sinks: dict = {}
+
+
+def register_grad_sink(spline_weight: torch.Tensor, sink) -> None:
+    _grad_sinks[spline_weight.data_ptr()] = sink
+
+
+def unregister_grad_sink(spline_weight: torch.Tensor) -> None:
+    _grad_sinks.pop(spline_weight.data_ptr(), None)
+
+
+def _sink_backward(ctx, sink, grad_output, x, grid, base_weight, spline_weight, spline_scaler, k, has_scaler):
+    """Backward through a gradient sink: ``(True, grad_x | None)``, or ``(False, None)`` when this
+    call cannot use it (then nothing has been written)."""
+    has_base = _has(base_weight)
+    wants_all = ctx.needs_input_grad[3] and (ctx.needs_input_grad[2] or not has_base) and \
+        (ctx.needs_input_grad[4] or not has_scaler)
+    if not wants_all or x.dtype != torch.float32 or x.size(0) < 1:
+        return False, None
+    G = grid.size(1) - 2 * k - 1
+    mode = _native.resolve_mode(_mode, x.dtype, x.size(0), x.size(1), spline_weight.size(0), G, k)
+    if mode not in (_native.MODE_TC_BF16X3, _native.MODE_TC_BF16X1):
+        return False, None
+    dest = sink.destinations(base_weight if has_base else None, spline_weight, spline_scaler if has_scaler else None)
+    if dest is None:
+        return False, None
+    gb, gs, gc = dest
+    _check_inputs(x, grid, base_weight, spline_weight, spline_scaler, k, has_scaler)
+    D = _c(grad_output.to(x.dtype))
+    xc, gridc, bwc, swc = _c(x), _c(grid), _c(base_weight), _c(spline_weight)
+    scc = _c(spline_scaler) if has_scaler else None
+    for o0, o1 in sink.row_ranges(spline_weight.size(0)):
+        _native.backward_param_rows(D, xc, gridc, bwc, swc, scc, k, o0, o1, gb, gs, gc, mode)
+        sink.rows_done(o0, o1)
+    gx = None
+    if ctx.needs_input_grad[0]:
+        gx = _native.backward(D, xc, gridc, bwc, swc, scc, k, True, False, False, False, mode)[0]
+    return True, gx
+
+
 class KANFunction(torch.autograd.Function):
     """Autograd node of the native layer (KANFunction, csrc/kan_autograd.cpp:13-111).
 
@@ -186,6 +231,12 @@ class KANFunction(torch.autograd.Function):
             gx, gb, gs, gc = kan_backward_composite(grad_output, x, grid, base_weight, spline_weight,
                                                     spline_scaler, k, has_scaler)
         else:
+            sink = _grad_sinks.get(spline_weight.data_ptr()) if _grad_sinks else None
+            if sink is not None:
+                handled, gx = _sink_backward(ctx, sink, grad_output, x, grid, base_weight, spline_weight,
+                                             spline_scaler, k, has_scaler)
+                if handled:
+                    return (gx, None, None, None, None, None, None)
             need_x = ctx.needs_input_grad[0]
             need_base = ctx.needs_input_grad[2] and has_base
             need_spline = ctx.needs_input_grad[3] or (has_scaler and ctx.needs_input_grad[4])

@@ -52,7 +52,13 @@ SIGNATURES = {
     "kanb200_umma_probe": (_c_int, [_c_void_p, ctypes.c_uint32, _c_void_p, ctypes.c_uint32, ctypes.c_uint64,
                                     ctypes.c_uint64, ctypes.c_uint32, _c_int, ctypes.c_uint32, ctypes.c_uint32,
                                     _c_int, _c_void_p, _c_void_p, _c_void_p]),
+    "kanb200_backward_param_rows": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
+                                                                          _c_i64, _c_i64, _c_void_p, _c_size,
+                                                                          _c_void_p]),
     "kanb200_allreduce_pad_bytes": (_c_size, [_c_int, _c_int]),
+    "kanb200_allreduce_sum_f32_ranges": (_c_int, [ctypes.POINTER(_c_void_p), _c_void_p, ctypes.POINTER(_c_size),
+                                                  ctypes.POINTER(_c_size), _c_int, _c_size, _c_int, _c_int, _c_int,
+                                                  _c_int, _c_int, ctypes.c_float, _c_void_p, _c_void_p]),
     "kanb200_allreduce_sum_f32": (_c_int, [ctypes.POINTER(_c_void_p), _c_void_p, _c_size, _c_size, _c_size,
                                            _c_int, _c_int, _c_int, _c_int, ctypes.c_float, _c_void_p, _c_void_p]),
 }
@@ -274,6 +280,28 @@ def backward(grad_out, x, grid, base_weight, spline_weight, spline_scaler, k: in
     return gx, gb, gs, gc
 
 
+def backward_param_rows(grad_out, x, grid, base_weight, spline_weight, spline_scaler, k: int,
+                        o_begin: int, o_end: int, gb: Optional[torch.Tensor], gs: Optional[torch.Tensor],
+                        gc: Optional[torch.Tensor], mode: int) -> None:
+    """Parameter gradients of the output rows ``[o_begin, o_end)`` written into the given full-size
+    tensors ``gb [O, I]``, ``gs [O, I, R]``, ``gc [O, I]`` (None = not needed); tensor-core modes."""
+    dev = _need_cuda(x, grid, spline_weight, grad_out)
+    N, I = x.shape
+    O = spline_weight.shape[0]
+    G = grid.shape[1] - 2 * k - 1
+    for t in (gb, gs, gc):
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("backward_param_rows: gradient destinations must be contiguous")
+    with _OnDevice(dev):
+        nb = workspace_bytes(OP_BACKWARD, mode, x.dtype, N, I, o_end - o_begin, G, k, False, True)
+        ws = workspace(dev, nb, "bwd")
+        with _Timed("backward", dev):
+            _check(lib().kanb200_backward_param_rows(mode, _p(grad_out), _p(x), _p(grid), _p(base_weight),
+                                                     _p(spline_weight), _p(spline_scaler), _p(gb), _p(gs), _p(gc),
+                                                     N, I, O, G, k, int(o_begin), int(o_end),
+                                                     _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+
+
 def edge_abs_mean(s, H, bw, W) -> torch.Tensor:
     dev = _need_cuda(H, W)
     N, I, R = H.shape
@@ -324,6 +352,22 @@ def allreduce_pad_bytes(world: int, blocks: int) -> int:
     if n == 0:
         raise RuntimeError(f"all-reduce: world size {world} / {blocks} blocks not supported")
     return n
+
+
+def allreduce_sum_ranges(peer_ptrs: Sequence[int], multicast_ptr: int, ranges: Sequence[Tuple[int, int]],
+                         pad_offset: int, rank: int, world: int, status: torch.Tensor, *, local_ranks: int = 1,
+                         blocks: int = 8, threads: int = 512, scale: float = 1.0) -> None:
+    """All-reduce of up to 4 ``(byte offset, float count)`` ranges of the allocation in one launch."""
+    if not status.is_cuda or status.dtype != torch.int32 or status.numel() < 1:
+        raise RuntimeError("all-reduce status must be a CUDA int32 tensor")
+    arr = (_c_void_p * len(peer_ptrs))(*[int(v) for v in peer_ptrs])
+    offs = (_c_size * len(ranges))(*[int(o) for o, _ in ranges])
+    cnts = (_c_size * len(ranges))(*[int(n) for _, n in ranges])
+    with torch.cuda.device(status.device):
+        _check(lib().kanb200_allreduce_sum_f32_ranges(arr, _c_void_p(int(multicast_ptr) or None), offs, cnts,
+                                                      len(ranges), int(pad_offset), int(rank), int(world),
+                                                      int(local_ranks), int(blocks), int(threads), float(scale),
+                                                      _p(status), _stream(status.device)))
 
 
 def allreduce_sum(peer_ptrs: Sequence[int], multicast_ptr: int, payload_offset: int, pad_offset: int,

@@ -207,12 +207,47 @@ KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out, cons
                                         ws_body(workspace, workspace_bytes),
                                         ws_body_bytes(workspace, workspace_bytes), st);
     } else {
-        e = tc_backward(m == KANB200_MODE_TC_BF16X3 ? 3 : 1, (const float*)grad_out, (const float*)x,
+        e = tc_backward(m == KANB200_MODE_TC_BF16X3 ? 3 : 1, (const float*)grad_out, O, (const float*)x,
                         (const float*)grid, (const float*)base_weight, (const float*)spline_weight,
                         (const float*)spline_scaler, (float*)grad_x, (float*)grad_base_weight,
                         (float*)grad_spline_weight, (float*)grad_spline_scaler, s, workspace, workspace_bytes, st);
     }
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_backward");
+}
+
+KANB200_API int kanb200_backward_param_rows(int mode, const void* grad_out, const void* x, const void* grid,
+                                            const void* base_weight, const void* spline_weight,
+                                            const void* spline_scaler, void* grad_base_weight,
+                                            void* grad_spline_weight, void* grad_spline_scaler,
+                                            int64_t N, int64_t I, int64_t O, int G, int k,
+                                            int64_t o_begin, int64_t o_end,
+                                            void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = kanb200_check_shapes(N, I, O, G, k, KANB200_F32);
+    if (rc) return rc;
+    if (o_begin < 0 || o_end > O || o_begin >= o_end)
+        return fail(KANB200_EINVAL, "kan_backward_param_rows: rows [%lld, %lld) outside [0, %lld)",
+                    (long long)o_begin, (long long)o_end, (long long)O);
+    if (N < 1) return fail(KANB200_EINVAL, "kan_backward_param_rows: empty batch");
+    if (!spline_weight || !grad_out || !x || !grid)
+        return fail(KANB200_EINVAL, "kan_backward_param_rows: NULL pointer");
+    if (grad_spline_scaler && !spline_scaler)
+        return fail(KANB200_EINVAL, "kan_backward_param_rows: grad_spline_scaler requested without spline_scaler");
+    if (mode != KANB200_MODE_TC_BF16X3 && mode != KANB200_MODE_TC_BF16X1)
+        return fail(KANB200_EUNSUPPORTED, "kan_backward_param_rows: tensor-core modes only");
+    if (!base_weight) grad_base_weight = nullptr;
+    const int64_t rows = o_end - o_begin;
+    LayerShape s;
+    make_shape(N, I, rows, G, k, s);
+    if (!tc_supported(s)) return fail(KANB200_EUNSUPPORTED, "kan_backward_param_rows: shape not supported");
+    const size_t oi = (size_t)o_begin * (size_t)I, oir = oi * (size_t)(G + k);
+    auto off = [](const void* p, size_t n) -> const float* { return p ? (const float*)p + n : nullptr; };
+    auto offw = [](void* p, size_t n) -> float* { return p ? (float*)p + n : nullptr; };
+    cudaError_t e = tc_backward(mode == KANB200_MODE_TC_BF16X3 ? 3 : 1, (const float*)grad_out + o_begin, O,
+                                (const float*)x, (const float*)grid, off(base_weight, oi), off(spline_weight, oir),
+                                off(spline_scaler, oi), nullptr, offw(grad_base_weight, oi),
+                                offw(grad_spline_weight, oir), offw(grad_spline_scaler, oi), s, workspace,
+                                workspace_bytes, (cudaStream_t)stream);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_backward_param_rows");
 }
 
 static int check_edge(int dtype, int64_t N, int64_t I, int64_t O, int R) {
@@ -324,30 +359,45 @@ KANB200_API size_t kanb200_allreduce_pad_bytes(int world, int blocks) {
     return allreduce_pad_bytes(world, blocks);
 }
 
-KANB200_API int kanb200_allreduce_sum_f32(const void* const* peer_bases, void* multicast_base,
-                                          size_t payload_offset, size_t pad_offset, size_t n_floats,
-                                          int rank, int world, int local_ranks, int blocks, float scale,
-                                          int* status, void* stream) {
+KANB200_API int kanb200_allreduce_sum_f32_ranges(const void* const* peer_bases, void* multicast_base,
+                                                 const size_t* offsets, const size_t* n_floats, int n_ranges,
+                                                 size_t pad_offset, int rank, int world, int local_ranks,
+                                                 int blocks, int threads, float scale, int* status, void* stream) {
     if (world < 1 || world > KANB200_MAX_RANKS)
         return fail(KANB200_EINVAL, "allreduce: world size %d outside [1, %d]", world, KANB200_MAX_RANKS);
     if (local_ranks < 1 || rank < 0 || rank + local_ranks > world)
         return fail(KANB200_EINVAL, "allreduce: ranks [%d, %d) outside world of size %d", rank, rank + local_ranks,
                     world);
     if (blocks < 1 || blocks > 1024) return fail(KANB200_EINVAL, "allreduce: blocks must be in [1, 1024]");
+    if (threads < 32 || threads > 512 || threads % 32 != 0 || threads < world)
+        return fail(KANB200_EINVAL, "allreduce: threads must be a multiple of 32 in [32, 512]");
     if (!peer_bases || !status) return fail(KANB200_EINVAL, "allreduce: peer_bases and status must not be NULL");
     for (int p = 0; p < world; ++p)
         if (!peer_bases[p]) return fail(KANB200_EINVAL, "allreduce: peer_bases[%d] is NULL", p);
-    if (n_floats % 4 != 0 || payload_offset % 16 != 0 || pad_offset % 4 != 0)
-        return fail(KANB200_EINVAL, "allreduce: n_floats must be a multiple of 4 and the payload 16-byte aligned");
+    if (n_ranges < 1 || n_ranges > KANB200_MAX_SEGMENTS || !offsets || !n_floats)
+        return fail(KANB200_EINVAL, "allreduce: between 1 and %d ranges", KANB200_MAX_SEGMENTS);
     const size_t pad = allreduce_pad_bytes(world, blocks);
-    if (!(pad_offset >= payload_offset + n_floats * 4 || pad_offset + pad <= payload_offset))
-        return fail(KANB200_EINVAL, "allreduce: signal pad overlaps the payload");
+    if (pad_offset % 4 != 0) return fail(KANB200_EINVAL, "allreduce: signal pad must be 4-byte aligned");
+    for (int i = 0; i < n_ranges; ++i) {
+        if (n_floats[i] % 4 != 0 || offsets[i] % 16 != 0)
+            return fail(KANB200_EINVAL, "allreduce: n_floats must be a multiple of 4 and the payload 16-byte aligned");
+        if (!(pad_offset >= offsets[i] + n_floats[i] * 4 || pad_offset + pad <= offsets[i]))
+            return fail(KANB200_EINVAL, "allreduce: signal pad overlaps the payload");
+    }
     if (multicast_base && local_ranks != 1)
         return fail(KANB200_EINVAL, "allreduce: several ranks in one launch use peer loads (multicast_base NULL)");
-    if (n_floats == 0 && world == 1) return KANB200_OK;
-    cudaError_t e = allreduce_sum(const_cast<void* const*>(peer_bases), multicast_base, payload_offset, pad_offset,
-                                  n_floats, rank, world, local_ranks, blocks, scale, status, (cudaStream_t)stream);
+    cudaError_t e = allreduce_sum(const_cast<void* const*>(peer_bases), multicast_base, offsets, n_floats, n_ranges,
+                                  pad_offset, rank, world, local_ranks, blocks, threads, scale, status,
+                                  (cudaStream_t)stream);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "allreduce_sum");
+}
+
+KANB200_API int kanb200_allreduce_sum_f32(const void* const* peer_bases, void* multicast_base,
+                                          size_t payload_offset, size_t pad_offset, size_t n_floats,
+                                          int rank, int world, int local_ranks, int blocks, float scale,
+                                          int* status, void* stream) {
+    return kanb200_allreduce_sum_f32_ranges(peer_bases, multicast_base, &payload_offset, &n_floats, 1, pad_offset,
+                                            rank, world, local_ranks, blocks, 512, scale, status, stream);
 }
 
 }  // extern "C"

@@ -107,11 +107,19 @@ __device__ __forceinline__ void st_peer(float4* p, const float4& v) {
                  :: "l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
+// Up to 4 ranges of one allocation reduced by one launch (the gradients of a range of output rows
+// of a layer are three ranges of its bucket: spline weight, scaler, base weight).
+struct Segments {
+    size_t off[KANB200_MAX_SEGMENTS];      // byte offset of the range within the allocation
+    size_t n4[KANB200_MAX_SEGMENTS];       // 16-byte pieces
+    int count;
+};
+
 // gridDim.x blocks per rank; gridDim.y > 1 runs several ranks of one device in a single launch
 // (all blocks co-resident), which is how the protocol is exercised on one GPU.
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(AR_THREADS)
-allreduce_sum_kernel(PeerTable peers, float4* mc_payload, size_t payload_off, size_t pad_off, size_t n4,
+allreduce_sum_kernel(PeerTable peers, char* mc_base, Segments segs, size_t pad_off,
                      int rank0, int world, float scale, int* status) {
     __shared__ int abort_flag;
     if (threadIdx.x == 0) abort_flag = 0;
@@ -120,42 +128,46 @@ allreduce_sum_kernel(PeerTable peers, float4* mc_payload, size_t payload_off, si
     const int block = blockIdx.x;
     if (!rank_barrier(peers, pad_off, rank, world, block, status, &abort_flag)) return;
 
-    const size_t per = (n4 + world - 1) / world;
-    const size_t lo = (size_t)rank * per;
-    size_t hi = lo + per;
-    if (hi > n4) hi = n4;
-    // AR_UNROLL independent 16-byte pieces per thread are in flight at a time: a load through the
-    // switch takes microseconds, so bandwidth comes from the number of outstanding requests.
-    const size_t step = (size_t)gridDim.x * AR_THREADS;
-    for (size_t i0 = lo + (size_t)block * AR_THREADS + threadIdx.x; i0 < hi; i0 += step * AR_UNROLL) {
-        float4 v[AR_UNROLL];
+    for (int sg = 0; sg < segs.count; ++sg) {
+        const size_t n4 = segs.n4[sg], payload_off = segs.off[sg];
+        float4* mc_payload = reinterpret_cast<float4*>(mc_base + payload_off);
+        const size_t per = (n4 + world - 1) / world;
+        const size_t lo = (size_t)rank * per;
+        size_t hi = lo + per;
+        if (hi > n4) hi = n4;
+        // AR_UNROLL independent 16-byte pieces per thread are in flight at a time: a load through
+        // the switch takes microseconds, so bandwidth comes from the number of outstanding requests.
+        const size_t step = (size_t)gridDim.x * blockDim.x;
+        for (size_t i0 = lo + (size_t)block * blockDim.x + threadIdx.x; i0 < hi; i0 += step * AR_UNROLL) {
+            float4 v[AR_UNROLL];
 #pragma unroll
-        for (int u = 0; u < AR_UNROLL; ++u) {
-            const size_t i = i0 + (size_t)u * step;
-            if (i < hi) {
-                if (MULTIMEM) {
-                    v[u] = multimem_ld_reduce_add(mc_payload + i);
-                } else {
-                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int p = 0; p < world; ++p) {
-                        const float4 a = ld_peer(
-                            reinterpret_cast<const float4*>(static_cast<char*>(peers.base[p]) + payload_off) + i);
-                        v[u].x += a.x; v[u].y += a.y; v[u].z += a.z; v[u].w += a.w;
+            for (int u = 0; u < AR_UNROLL; ++u) {
+                const size_t i = i0 + (size_t)u * step;
+                if (i < hi) {
+                    if (MULTIMEM) {
+                        v[u] = multimem_ld_reduce_add(mc_payload + i);
+                    } else {
+                        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int p = 0; p < world; ++p) {
+                            const float4 a = ld_peer(
+                                reinterpret_cast<const float4*>(static_cast<char*>(peers.base[p]) + payload_off) + i);
+                            v[u].x += a.x; v[u].y += a.y; v[u].z += a.z; v[u].w += a.w;
+                        }
                     }
                 }
             }
-        }
 #pragma unroll
-        for (int u = 0; u < AR_UNROLL; ++u) {
-            const size_t i = i0 + (size_t)u * step;
-            if (i < hi) {
-                float4 r = v[u];
-                r.x *= scale; r.y *= scale; r.z *= scale; r.w *= scale;
-                if (MULTIMEM) {
-                    multimem_st(mc_payload + i, r);
-                } else {
-                    for (int p = 0; p < world; ++p)
-                        st_peer(reinterpret_cast<float4*>(static_cast<char*>(peers.base[p]) + payload_off) + i, r);
+            for (int u = 0; u < AR_UNROLL; ++u) {
+                const size_t i = i0 + (size_t)u * step;
+                if (i < hi) {
+                    float4 r = v[u];
+                    r.x *= scale; r.y *= scale; r.z *= scale; r.w *= scale;
+                    if (MULTIMEM) {
+                        multimem_st(mc_payload + i, r);
+                    } else {
+                        for (int p = 0; p < world; ++p)
+                            st_peer(reinterpret_cast<float4*>(static_cast<char*>(peers.base[p]) + payload_off) + i, r);
+                    }
                 }
             }
         }
@@ -169,21 +181,23 @@ size_t allreduce_pad_bytes(int world, int blocks) {
     return ((size_t)world * blocks * sizeof(uint32_t) + 255) / 256 * 256;
 }
 
-cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, size_t payload_off, size_t pad_off,
-                          size_t n_floats, int rank, int world, int local_ranks, int blocks, float scale,
-                          int* status, cudaStream_t st) {
+cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, const size_t* offsets, const size_t* n_floats,
+                          int n_segments, size_t pad_off, int rank, int world, int local_ranks, int blocks,
+                          int threads, float scale, int* status, cudaStream_t st) {
     PeerTable t;
     for (int p = 0; p < KANB200_MAX_RANKS; ++p) t.base[p] = p < world ? peer_bases[p] : nullptr;
-    const size_t n4 = n_floats / 4;
-    dim3 grid((unsigned)blocks, (unsigned)local_ranks);
-    if (multicast_base) {
-        float4* mc = reinterpret_cast<float4*>(static_cast<char*>(multicast_base) + payload_off);
-        allreduce_sum_kernel<true><<<grid, AR_THREADS, 0, st>>>(t, mc, payload_off, pad_off, n4, rank, world,
-                                                               scale, status);
-    } else {
-        allreduce_sum_kernel<false><<<grid, AR_THREADS, 0, st>>>(t, nullptr, payload_off, pad_off, n4, rank, world,
-                                                                scale, status);
+    Segments segs;
+    segs.count = n_segments;
+    for (int i = 0; i < KANB200_MAX_SEGMENTS; ++i) {
+        segs.off[i] = i < n_segments ? offsets[i] : 0;
+        segs.n4[i] = i < n_segments ? n_floats[i] / 4 : 0;
     }
+    dim3 grid((unsigned)blocks, (unsigned)local_ranks);
+    if (multicast_base)
+        allreduce_sum_kernel<true><<<grid, threads, 0, st>>>(t, static_cast<char*>(multicast_base), segs, pad_off,
+                                                            rank, world, scale, status);
+    else
+        allreduce_sum_kernel<false><<<grid, threads, 0, st>>>(t, nullptr, segs, pad_off, rank, world, scale, status);
     return cudaGetLastError();
 }
 

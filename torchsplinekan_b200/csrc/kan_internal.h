@@ -60,8 +60,10 @@ size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param);
 cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const float* bw, const float* sw,
                        const float* scaler, float* y, const LayerShape& s,
                        void* ws, size_t ws_bytes, cudaStream_t st);
-cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const float* grid, const float* bw,
-                        const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
+// ldy = row stride of dY in elements (s.O for a dense matrix; larger when the call covers a range
+// of output columns of a wider matrix)
+cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const float* x, const float* grid,
+                        const float* bw, const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
                         float* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st);
 
 // Layout self-test (kan_probe.cu).
@@ -71,9 +73,9 @@ cudaError_t umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, u
 
 // Gradient all-reduce over symmetric memory (kan_collective.cu).
 size_t allreduce_pad_bytes(int world, int blocks);
-cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, size_t payload_off, size_t pad_off,
-                          size_t n_floats, int rank, int world, int local_ranks, int blocks, float scale,
-                          int* status, cudaStream_t st);
+cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, const size_t* offsets, const size_t* n_floats,
+                          int n_segments, size_t pad_off, int rank, int world, int local_ranks, int blocks,
+                          int threads, float scale, int* status, cudaStream_t st);
 
 // Workspaces start with a 256-byte header whose first word is a status code
 // written by kernels whose bounded waits ran out.

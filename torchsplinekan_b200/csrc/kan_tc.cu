@@ -410,7 +410,7 @@ __global__ void pack_weights_kernel(const float* __restrict__ sw, const float* _
 // samples, group of 128 outputs) two 16-KB tiles (hi, lo), MN-major: rows are
 // samples, 128 B = 64 consecutive outputs, 128-byte swizzle, laid out
 // [output group of 64][sample group of 8][8 rows][128 B].
-__global__ void pack_grad_out_kernel(const float* __restrict__ dY, uint8_t* __restrict__ img,
+__global__ void pack_grad_out_kernel(const float* __restrict__ dY, int64_t ldy, uint8_t* __restrict__ img,
                                      int64_t N, int O, int64_t n_blocks, int n_ohalves) {
     const int64_t chunks = n_blocks * n_ohalves * 64 * 16;   // 64 samples x 16 chunks of 8 outputs
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks;
@@ -427,7 +427,7 @@ __global__ void pack_grad_out_kernel(const float* __restrict__ dY, uint8_t* __re
 #pragma unroll
         for (int e = 0; e < 8; ++e) w[e] = 0.0f;
         if (n < N) {
-            const float* p = dY + (size_t)n * O + o0;
+            const float* p = dY + (size_t)n * ldy + o0;
 #pragma unroll
             for (int e = 0; e < 8; ++e)
                 if (o0 + e < O) w[e] = p[e];
@@ -1893,8 +1893,8 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     return cudaGetLastError();
 }
 
-cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const float* grid, const float* bw,
-                        const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
+cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const float* x, const float* grid,
+                        const float* bw, const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
                         float* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st) {
     cudaError_t e = cudaSuccess;
     const bool has_base = bw != nullptr;
@@ -1923,7 +1923,8 @@ cudaError_t tc_backward(int split_terms, const float* dY, const float* x, const 
         const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
         int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
                                                                             : (int64_t)sm_count() * 16);
-        pack_grad_out_kernel<<<blocks, 256, 0, st>>>(dY, dyimg, s.N, s.O, L.plan.kb_total, L.plan.n_otiles * 2);
+        pack_grad_out_kernel<<<blocks, 256, 0, st>>>(dY, ldy, dyimg, s.N, s.O, L.plan.kb_total,
+                                                     L.plan.n_otiles * 2);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
