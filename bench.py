@@ -433,8 +433,11 @@ def run_config(args):
         x = torch.where(torch.rand(16384, 512, generator=g) < 0.5, -0.5, 0.5) + 0.15 * torch.randn(16384, 512, generator=g)
         x = x.clamp_(-1, 1).to(dev)
         net.update_grid(x)
+        if args.need_x:
+            x.requires_grad_(True)
         loss_fn = lambda: net(x).square().sum()
-        name, rows = "c3 KANLinear 512->512 G=64 N=16384 fp32, update_grid knots", 16384
+        name, rows = "c3 KANLinear 512->512 G=64 N=16384 fp32, update_grid knots" + \
+            (", input gradient computed" if args.need_x else ""), 16384
     elif c == 4:
         net = sk.KAN([2, 64, 64, 1], grid_size=8, backend="cuda").to(dev, torch.float64)
         x = (torch.rand(131072, 2, generator=g, dtype=torch.float64) * 2 - 1).to(dev)

@@ -219,3 +219,27 @@ def test_shard_rows_partitions_the_batch():
         assert all(a[1] == b[0] for a, b in zip(spans[:-1], spans[1:]))
         sizes = [b - a for a, b in spans]
         assert max(sizes) - min(sizes) <= 1
+
+
+def test_gradient_bucket_arguments_and_row_ranges():
+    """Host logic of the data-parallel helpers that needs no device."""
+    import torchsplinekan_b200 as sk
+    from torchsplinekan_b200.data_parallel import _LayerSink
+    with pytest.raises(ValueError, match="transport"):
+        sk.GradientBucket([torch.nn.Linear(2, 2)], transport="bogus")
+    sink = _LayerSink.__new__(_LayerSink)
+    sink.chunks = 4
+    assert sink.row_ranges(1024) == [(0, 256), (256, 512), (512, 768), (768, 1024)]
+    assert sink.row_ranges(1000) == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    assert sink.row_ranges(300) == [(0, 256), (256, 300)]            # whole 256-row tiles
+    sink.chunks = 1
+    assert sink.row_ranges(1000) == [(0, 1000)]
+    # CPU parameters: the bucket falls back to the process group's own all-reduce, no sink is made
+    lin = torch.nn.Linear(3, 2)
+    b = sk.GradientBucket([lin], direct=True)
+    assert b.transport == "nccl" and b._sinks == [] and b.buckets[0].numel() == 8
+    lin(torch.ones(1, 3)).sum().backward()
+    b.finish()
+    assert lin.weight.grad.data_ptr() == b.buckets[0].data_ptr()
+    with pytest.raises(ValueError, match="CUDA device"):
+        sk.HostBatchPrefetcher((2, 2), torch.float32, torch.device("cpu"))
