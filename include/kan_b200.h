@@ -57,6 +57,7 @@ extern "C" {
 #define KANB200_OP_BACKWARD 1
 #define KANB200_OP_EDGE_FWD 2
 #define KANB200_OP_EDGE_BWD 3
+#define KANB200_OP_BASIS    4  /* kanb200_basis_ws / kanb200_basis_grad_ws (O is ignored) */
 
 KANB200_API const char* kanb200_last_error(void);
 KANB200_API int kanb200_version(void);
@@ -87,6 +88,16 @@ KANB200_API int kanb200_basis(int dtype, const void* x, const void* grid, void* 
 
 /* gx[n,i] = sum_r gH[n,i,r] dB_r/dx
  * (kan_basis_grad_cuda, csrc/kan_cuda.cu:682-699). */
+/* The same two operators with caller scratch (kanb200_workspace_bytes(KANB200_OP_BASIS, ...)):
+ * float32 inputs with G + k = 8 then run from a per-span polynomial table built into the scratch
+ * (about twice the rate of the recurrence); anything else, or a NULL / short workspace, behaves
+ * exactly like the calls without scratch. */
+KANB200_API int kanb200_basis_ws(int dtype, const void* x, const void* grid, void* H, int64_t N, int64_t I, int G,
+                                 int k, void* workspace, size_t workspace_bytes, void* stream);
+KANB200_API int kanb200_basis_grad_ws(int dtype, const void* x, const void* grid, const void* gH, void* gx,
+                                      int64_t N, int64_t I, int G, int k, void* workspace, size_t workspace_bytes,
+                                      void* stream);
+
 KANB200_API int kanb200_basis_grad(int dtype, const void* x, const void* grid, const void* gH, void* gx,
                        int64_t N, int64_t I, int G, int k, void* stream);
 

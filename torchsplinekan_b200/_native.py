@@ -19,7 +19,7 @@ from .build import LIB_PATH
 F32, F64 = 0, 1
 MODE_AUTO, MODE_SIMT, MODE_TC_BF16X3, MODE_TC_BF16X1 = 0, 1, 2, 3
 MODES = {"auto": MODE_AUTO, "simt": MODE_SIMT, "bf16x3": MODE_TC_BF16X3, "bf16x1": MODE_TC_BF16X1}
-OP_FORWARD, OP_BACKWARD, OP_EDGE_FWD, OP_EDGE_BWD = 0, 1, 2, 3
+OP_FORWARD, OP_BACKWARD, OP_EDGE_FWD, OP_EDGE_BWD, OP_BASIS = 0, 1, 2, 3, 4
 EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = -1, -2, -3, -4, -5
 MAX_DEG0_BASIS = 71
 MAX_IN_FEATURES = 65535
@@ -39,6 +39,10 @@ SIGNATURES = {
     "kanb200_basis": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int, _c_int, _c_void_p]),
     "kanb200_basis_grad": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int,
                                     _c_int, _c_void_p]),
+    "kanb200_basis_ws": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int, _c_int, _c_void_p,
+                                  _c_size, _c_void_p]),
+    "kanb200_basis_grad_ws": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int,
+                                       _c_int, _c_void_p, _c_size, _c_void_p]),
     "kanb200_forward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                      _c_void_p, _c_size, _c_void_p]),
     "kanb200_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
@@ -221,7 +225,9 @@ def basis(x: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
     G = grid.shape[1] - 2 * k - 1
     H = torch.empty((N, I, G + k), dtype=x.dtype, device=dev)
     with _OnDevice(dev):
-        _check(lib().kanb200_basis(_code(x.dtype), _p(x), _p(grid), _p(H), N, I, G, k, _stream(dev)))
+        ws = workspace(dev, workspace_bytes(OP_BASIS, MODE_AUTO, x.dtype, N, I, 1, G, k), "basis")
+        _check(lib().kanb200_basis_ws(_code(x.dtype), _p(x), _p(grid), _p(H), N, I, G, k,
+                                      _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return H
 
 
@@ -231,7 +237,9 @@ def basis_grad(x: torch.Tensor, grid: torch.Tensor, k: int, gH: torch.Tensor) ->
     G = grid.shape[1] - 2 * k - 1
     gx = torch.empty((N, I), dtype=x.dtype, device=dev)
     with _OnDevice(dev):
-        _check(lib().kanb200_basis_grad(_code(x.dtype), _p(x), _p(grid), _p(gH), _p(gx), N, I, G, k, _stream(dev)))
+        ws = workspace(dev, workspace_bytes(OP_BASIS, MODE_AUTO, x.dtype, N, I, 1, G, k), "basis")
+        _check(lib().kanb200_basis_grad_ws(_code(x.dtype), _p(x), _p(grid), _p(gH), _p(gx), N, I, G, k,
+                                           _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return gx
 
 

@@ -98,6 +98,10 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
     if (kanb200_check_shapes(N, I, O, G, k, dtype) != KANB200_OK) return 0;
     LayerShape s;
     make_shape(N, I, O, G, k, s);
+    if (op == KANB200_OP_BASIS) {
+        // the table-driven basis kernels; 0 = the recurrence kernels run and need nothing
+        return dtype == KANB200_F32 && basis_table_supported(s) ? kWsHeader + tc_table_bytes(s) : 0;
+    }
     if (op == KANB200_OP_EDGE_FWD || op == KANB200_OP_EDGE_BWD) {
         const bool b = op == KANB200_OP_EDGE_BWD;
         if (N < 1) return 0;
@@ -128,6 +132,42 @@ KANB200_API int kanb200_basis(int dtype, const void* x, const void* grid, void* 
                         ? simt_basis<float>((const float*)x, (const float*)grid, (float*)H, s, st)
                         : simt_basis<double>((const double*)x, (const double*)grid, (double*)H, s, st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis");
+}
+
+KANB200_API int kanb200_basis_ws(int dtype, const void* x, const void* grid, void* H, int64_t N, int64_t I, int G,
+                                 int k, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = kanb200_check_shapes(N, I, 1, G, k, dtype);
+    if (rc) return rc;
+    LayerShape s;
+    make_shape(N, I, 1, G, k, s);
+    const bool table = dtype == KANB200_F32 && basis_table_supported(s) && workspace &&
+                       workspace_bytes >= kWsHeader + tc_table_bytes(s) && ((uintptr_t)H & 15) == 0;
+    if (!table) return kanb200_basis(dtype, x, grid, H, N, I, G, k, stream);
+    if (!x || !grid || !H) return fail(KANB200_EINVAL, "kan_basis: NULL pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    float* tab = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWsHeader);
+    cudaError_t e = tc_build_table((const float*)grid, tab, reinterpret_cast<int*>(workspace), s, st);
+    if (e == cudaSuccess) e = simt_basis_table((const float*)x, tab, tc_table_stride(s), (float*)H, s, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis");
+}
+
+KANB200_API int kanb200_basis_grad_ws(int dtype, const void* x, const void* grid, const void* gH, void* gx,
+                                      int64_t N, int64_t I, int G, int k, void* workspace, size_t workspace_bytes,
+                                      void* stream) {
+    int rc = kanb200_check_shapes(N, I, 1, G, k, dtype);
+    if (rc) return rc;
+    LayerShape s;
+    make_shape(N, I, 1, G, k, s);
+    const bool table = dtype == KANB200_F32 && basis_table_supported(s) && workspace &&
+                       workspace_bytes >= kWsHeader + tc_table_bytes(s) && ((uintptr_t)gH & 15) == 0;
+    if (!table) return kanb200_basis_grad(dtype, x, grid, gH, gx, N, I, G, k, stream);
+    if (!x || !grid || !gH || !gx) return fail(KANB200_EINVAL, "kan_basis_grad: NULL pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    float* tab = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWsHeader);
+    cudaError_t e = tc_build_table((const float*)grid, tab, reinterpret_cast<int*>(workspace), s, st);
+    if (e == cudaSuccess)
+        e = simt_basis_grad_table((const float*)x, tab, tc_table_stride(s), (const float*)gH, (float*)gx, s, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis_grad");
 }
 
 KANB200_API int kanb200_basis_grad(int dtype, const void* x, const void* grid, const void* gH, void* gx,

@@ -39,6 +39,14 @@ cudaError_t finalize_param_grads(const T* partial, int splits, int64_t split_str
                                  const T* sw, const T* scaler, T* gsw, T* gscaler, T* gbw,
                                  int O, int I, int R, cudaStream_t st);
 
+// Table-driven dense basis / basis gradient (float, R == 8, at most 12 knots, N >= 256): `tab` is
+// the polynomial table built by tc_build_table, `fs` its floats per feature.
+bool basis_table_supported(const LayerShape& s);
+cudaError_t simt_basis_table(const float* x, const float* tab, int fs, float* H, const LayerShape& s,
+                             cudaStream_t st);
+cudaError_t simt_basis_grad_table(const float* x, const float* tab, int fs, const float* gH, float* gx,
+                                  const LayerShape& s, cudaStream_t st);
+
 // ---- edge statistic (kan_reg.cu) -------------------------------------------
 template <typename T>
 size_t edge_workspace(int64_t N, int I, int O, int R, bool backward);
@@ -65,6 +73,12 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
 cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const float* x, const float* grid,
                         const float* bw, const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
                         float* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st);
+
+// The per-span polynomial table on its own: bytes, floats per feature, and the kernel that fills it
+// (it also clears *status).
+size_t tc_table_bytes(const LayerShape& s);
+int tc_table_stride(const LayerShape& s);
+cudaError_t tc_build_table(const float* grid, float* tab, int* status, const LayerShape& s, cudaStream_t st);
 
 // Layout self-test (kan_probe.cu).
 cudaError_t umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,

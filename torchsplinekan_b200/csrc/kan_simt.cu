@@ -8,6 +8,7 @@
 // in the caller's workspace and a fixed-order second pass.
 #include "kan_device.cuh"
 #include "kan_internal.h"
+#include "kan_table.cuh"
 
 namespace kanb200 {
 
@@ -135,6 +136,188 @@ basis_grad_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid
             }
         }
         gx[idx] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Table-driven basis kernels (float, R == 8, at most 12 knots).
+//
+// A block owns 32 consecutive features and a range of rows; lane = feature.  The lane keeps its
+// feature's knots in registers and the block keeps the polynomial coefficients of its features'
+// spans (kan_table.cuh, built once per call by the table kernel into the caller's workspace) in
+// shared memory.  Per value: one coalesced read of x, a compare-and-count span search in
+// registers, four 16-byte shared-memory loads and a Horner evaluation.  The warp's 32 basis rows
+// (1 KB, contiguous in H) leave as 64 float4 in two coalesced stores.
+// Shared-memory layout: feature stride 356 floats (= 4 mod 32), span stride 32 floats, so the
+// 16-byte loads of a quarter-warp hit distinct banks whatever spans its lanes are in.
+// ---------------------------------------------------------------------------
+constexpr int BT_FEATURES = 32, BT_SPANS = 11, BT_SPAN_STRIDE = 32, BT_STRIDE = BT_SPANS * BT_SPAN_STRIDE + 4;
+constexpr int BT_THREADS = 256, BT_UNROLL = 4;
+
+// Copies the coefficients of the block's 32 features from the table (per feature `fs` floats:
+// 16 of header and knots, then 20 per span of which the first 16 are coefficients).
+__device__ __forceinline__ void basis_table_fill(float* __restrict__ stab, const float* __restrict__ tab,
+                                                 int fs, int nk, int f0, int I) {
+    const int spans = nk - 1;
+    for (int idx = threadIdx.x; idx < BT_FEATURES * spans * 4; idx += blockDim.x) {
+        const int q = idx & 3;                  // which 16-byte piece (coefficients of function q)
+        const int e = (idx >> 2) % spans, fl = (idx >> 2) / spans;
+        const int f = (f0 + fl < I) ? f0 + fl : I - 1;
+        const float4 v = __ldg(reinterpret_cast<const float4*>(tab + (size_t)f * fs + 16 + e * TAB_ENTRY_FLOATS) + q);
+        *reinterpret_cast<float4*>(stab + fl * BT_STRIDE + e * BT_SPAN_STRIDE + q * 4) = v;
+    }
+    __syncthreads();
+}
+
+// The lane's knots: t_0 .. t_{nk-2} padded with +inf (kn[0..10]) and the last knot.
+struct LaneKnots {
+    float kn[11];
+    float last;
+};
+
+__device__ __forceinline__ LaneKnots load_lane_knots(const float* __restrict__ ftab_global) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(ftab_global + 4));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(ftab_global + 4) + 1);
+    const float4 c = __ldg(reinterpret_cast<const float4*>(ftab_global + 4) + 2);
+    LaneKnots k;
+    k.kn[0] = a.x; k.kn[1] = a.y; k.kn[2] = a.z; k.kn[3] = a.w;
+    k.kn[4] = b.x; k.kn[5] = b.y; k.kn[6] = b.z; k.kn[7] = b.w;
+    k.kn[8] = c.x; k.kn[9] = c.y; k.kn[10] = c.z;
+    k.last = c.w;
+    return k;
+}
+
+// DERIV = false: the k+1 window values; true: their derivatives.  Returns the window start
+// (K = spline order); inputs outside the knot range (or NaN) give zeros.
+template <bool DERIV>
+__device__ __forceinline__ int basis_table_eval(const float* __restrict__ fcoef, const LaneKnots& k, int K,
+                                                float xv, float (&v)[4]) {
+    const bool inside = (xv >= k.kn[0]) && (xv <= k.last);
+    int m = 0;
+    float tm = k.kn[0];
+#pragma unroll
+    for (int q = 1; q < 11; ++q) {
+        const bool ge = xv >= k.kn[q];
+        m += ge ? 1 : 0;
+        tm = ge ? k.kn[q] : tm;                 // knots are non-decreasing: ends at t_m
+    }
+    m = inside ? m : 0;
+    const float4* ent = reinterpret_cast<const float4*>(fcoef + m * BT_SPAN_STRIDE);
+    const float4 c0 = ent[0], c1 = ent[1], c2 = ent[2], c3 = ent[3];
+    const float u = xv - tm;
+    if (DERIV) {
+        v[0] = fmaf(fmaf(3.0f * c0.w, u, 2.0f * c0.z), u, c0.y);
+        v[1] = fmaf(fmaf(3.0f * c1.w, u, 2.0f * c1.z), u, c1.y);
+        v[2] = fmaf(fmaf(3.0f * c2.w, u, 2.0f * c2.z), u, c2.y);
+        v[3] = fmaf(fmaf(3.0f * c3.w, u, 2.0f * c3.z), u, c3.y);
+    } else {
+        v[0] = fmaf(fmaf(fmaf(c0.w, u, c0.z), u, c0.y), u, c0.x);
+        v[1] = fmaf(fmaf(fmaf(c1.w, u, c1.z), u, c1.y), u, c1.x);
+        v[2] = fmaf(fmaf(fmaf(c2.w, u, c2.z), u, c2.y), u, c2.x);
+        v[3] = fmaf(fmaf(fmaf(c3.w, u, c3.z), u, c3.y), u, c3.x);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = inside ? v[j] : 0.f;
+    return m - K;
+}
+
+__global__ void __launch_bounds__(BT_THREADS)
+basis_table_kernel(const float* __restrict__ x, const float* __restrict__ tab, int fs, float* __restrict__ H,
+                   int64_t N, int I, int G, int K, int64_t rows_per_block) {
+    __shared__ __align__(16) float stab[BT_FEATURES * BT_STRIDE];
+    const int f0 = blockIdx.x * BT_FEATURES;
+    const int nk = G + 2 * K + 1;
+    basis_table_fill(stab, tab, fs, nk, f0, I);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int f = f0 + lane;
+    const float* fcoef = stab + lane * BT_STRIDE;
+    const LaneKnots knots = load_lane_knots(tab + (size_t)(f < I ? f : I - 1) * fs);
+    const int64_t row0 = (int64_t)blockIdx.y * rows_per_block;
+    int64_t row1 = row0 + rows_per_block;
+    if (row1 > N) row1 = N;
+    const int n_valid = (I - f0 < 32) ? I - f0 : 32;       // features of this group
+    // BT_UNROLL rows per warp and iteration: their x loads are issued together
+    for (int64_t rbase = row0 + warp * BT_UNROLL; rbase < row1; rbase += (BT_THREADS / 32) * BT_UNROLL) {
+        float xv[BT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < BT_UNROLL; ++u)
+            xv[u] = (f < I && rbase + u < row1) ? __ldg(x + (size_t)(rbase + u) * I + f) : 0.f;
+#pragma unroll
+        for (int u = 0; u < BT_UNROLL; ++u) {
+            const int64_t row = rbase + u;
+            if (row >= row1) break;                         // uniform over the warp
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            int s = -100;                                   // nothing lands in [0, 8)
+            if (f < I) s = basis_table_eval<false>(fcoef, knots, K, xv[u], v);
+            float4* dst = reinterpret_cast<float4*>(H + ((size_t)row * I + f0) * 8);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int q4 = lane + 32 * h;               // float4 index within the warp's 64
+                const int src = q4 >> 1;                    // lane that owns the pair
+                const int r0 = (q4 & 1) * 4;                // first slot of this float4
+                float pv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) pv[j] = __shfl_sync(0xffffffffu, v[j], src);
+                const int ps = __shfl_sync(0xffffffffu, s, src);
+                float o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = r0 + e - ps;              // index into the window
+                    float val = 0.f;
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) val = (j == jj) ? pv[jj] : val;
+                    o[e] = val;
+                }
+                if (src < n_valid) dst[q4] = make_float4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(BT_THREADS)
+basis_grad_table_kernel(const float* __restrict__ x, const float* __restrict__ tab, int fs,
+                        const float* __restrict__ gH, float* __restrict__ gx, int64_t N, int I, int G, int K,
+                        int64_t rows_per_block) {
+    __shared__ __align__(16) float stab[BT_FEATURES * BT_STRIDE];
+    const int f0 = blockIdx.x * BT_FEATURES;
+    const int nk = G + 2 * K + 1;
+    basis_table_fill(stab, tab, fs, nk, f0, I);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int f = f0 + lane;
+    const float* fcoef = stab + lane * BT_STRIDE;
+    const LaneKnots knots = load_lane_knots(tab + (size_t)(f < I ? f : I - 1) * fs);
+    const int64_t row0 = (int64_t)blockIdx.y * rows_per_block;
+    int64_t row1 = row0 + rows_per_block;
+    if (row1 > N) row1 = N;
+    if (f >= I) return;                                     // no warp-wide operation below
+    for (int64_t rbase = row0 + warp * BT_UNROLL; rbase < row1; rbase += (BT_THREADS / 32) * BT_UNROLL) {
+        float xv[BT_UNROLL];
+        float4 ga[BT_UNROLL], gb[BT_UNROLL];
+#pragma unroll
+        for (int u = 0; u < BT_UNROLL; ++u) {
+            const bool ok = rbase + u < row1;
+            const size_t idx = (size_t)(ok ? rbase + u : row0) * I + f;
+            xv[u] = __ldg(x + idx);
+            ga[u] = __ldg(reinterpret_cast<const float4*>(gH + idx * 8));
+            gb[u] = __ldg(reinterpret_cast<const float4*>(gH + idx * 8) + 1);
+        }
+#pragma unroll
+        for (int u = 0; u < BT_UNROLL; ++u) {
+            if (rbase + u >= row1) break;
+            const float g[8] = {ga[u].x, ga[u].y, ga[u].z, ga[u].w, gb[u].x, gb[u].y, gb[u].z, gb[u].w};
+            float d[4];
+            const int s = basis_table_eval<true>(fcoef, knots, K, xv[u], d);
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = s + j;
+                float gr = 0.f;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) gr = (r == q) ? g[q] : gr;
+                acc = fmaf(gr, d[j], acc);
+            }
+            gx[(size_t)(rbase + u) * I + f] = acc;
+        }
     }
 }
 
@@ -497,6 +680,19 @@ inline int grid_1d(int64_t work, int threads, int cap = 148 * 32) {
     return (int)b;
 }
 
+// Grid of the table-driven basis kernels: x = groups of 32 features, y = row ranges sized so that
+// about 6 blocks per SM exist, with at least 64 rows each (a block copies 32 KB of tables first).
+inline void basis_table_grid(const LayerShape& s, dim3& g, int64_t& rows_per_block) {
+    const int fgroups = (s.I + BT_FEATURES - 1) / BT_FEATURES;
+    int64_t ry = (148 * 6 + fgroups - 1) / fgroups;
+    const int64_t max_ry = (s.N + 63) / 64;
+    if (ry > max_ry) ry = max_ry;
+    if (ry < 1) ry = 1;
+    if (ry > 65535) ry = 65535;
+    rows_per_block = (s.N + ry - 1) / ry;
+    g = dim3((unsigned)fgroups, (unsigned)((s.N + rows_per_block - 1) / rows_per_block));
+}
+
 #define KAN_DISPATCH_K(Kval, ...)                                   \
     switch (Kval) {                                                 \
         case 1: { constexpr int KK = 1; __VA_ARGS__; break; }       \
@@ -583,6 +779,28 @@ cudaError_t simt_basis_grad(const T* x, const T* grid, const T* gH, T* gx, const
         return cudaGetLastError();
     }
     KAN_DISPATCH_K(s.K, (basis_grad_kernel<T, KK><<<blocks, 256, 0, st>>>(x, grid, gH, gx, pairs, s.I, s.G)));
+    return cudaGetLastError();
+}
+
+bool basis_table_supported(const LayerShape& s) {
+    return s.R() == 8 && s.T() <= 12 && s.K >= 1 && s.K <= 3 && s.N >= 256;
+}
+
+cudaError_t simt_basis_table(const float* x, const float* tab, int fs, float* H, const LayerShape& s,
+                             cudaStream_t st) {
+    dim3 g;
+    int64_t rows_per_block;
+    basis_table_grid(s, g, rows_per_block);
+    basis_table_kernel<<<g, BT_THREADS, 0, st>>>(x, tab, fs, H, s.N, s.I, s.G, s.K, rows_per_block);
+    return cudaGetLastError();
+}
+
+cudaError_t simt_basis_grad_table(const float* x, const float* tab, int fs, const float* gH, float* gx,
+                                  const LayerShape& s, cudaStream_t st) {
+    dim3 g;
+    int64_t rows_per_block;
+    basis_table_grid(s, g, rows_per_block);
+    basis_grad_table_kernel<<<g, BT_THREADS, 0, st>>>(x, tab, fs, gH, gx, s.N, s.I, s.G, s.K, rows_per_block);
     return cudaGetLastError();
 }
 

@@ -26,6 +26,7 @@
 // bounded.
 #include "kan_device.cuh"
 #include "kan_internal.h"
+#include "kan_table.cuh"
 #include "kan_tc_ptx.cuh"
 
 #include <cstdlib>
@@ -65,7 +66,6 @@ constexpr uint32_t TILE_B_BYTES = BLOCK_N * BLOCK_K * 2;   // 32 KB: 256 x 64 bf
 // and non-uniform knots.  Conventions (half-open spans, last span closed,
 // zero-length spans contribute zero) are those of the dense recurrence.
 // ---------------------------------------------------------------------------
-constexpr int TAB_ENTRY_FLOATS = 20;
 constexpr int TAB_FAST_MAX_KNOTS = 12;        // compare-and-count span search up to this many knots
 constexpr int TAB_SMEM_FLOATS = 256;          // table of one feature with <= 12 knots: 16 + 12 * 20
 
@@ -109,60 +109,14 @@ __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* _
         out[0] = differs;
         out[1] = out[2] = out[3] = 0.0f;
         if (nk <= TAB_FAST_MAX_KNOTS) {
-            for (int q = 0; q < 11; ++q) out[4 + q] = (q <= nk - 2) ? t[q] : __int_as_float(0x7f800000);
-            out[15] = t[nk - 1];
+            poly_table_knots12(t, nk, out + 4);
         } else {
             for (int q = 0; q < nk; ++q) out[4 + q] = t[q];
             for (int q = 4 + nk; q < ti.es; ++q) out[q] = 0.0f;
         }
         return;
     }
-    float* ent = out + ti.es + e * TAB_ENTRY_FLOATS;
-    double c[4][4];
-    for (int j = 0; j < 4; ++j)
-        for (int p = 0; p < 4; ++p) c[j][p] = 0.0;
-    const int m = e;
-    float tm = 0.0f;
-    int s = 0;
-    if (m <= nk - 2) {                         // e == nk - 1 is the zero entry
-        auto knot = [&](int i) -> double { return (double)t[i < 0 ? 0 : (i > nk - 1 ? nk - 1 : i)]; };
-        tm = t[m];
-        s = m - K;
-        c[0][0] = 1.0;
-        for (int d = 1; d <= K; ++d) {
-            double carry[4] = {0.0, 0.0, 0.0, 0.0};
-            for (int j = 0; j < d; ++j) {
-                const double hi_k = knot(m + j + 1), lo_k = knot(m + 1 - d + j);
-                const double den = hi_k - lo_k;
-                double w[4];
-                for (int p = 0; p < 4; ++p) w[p] = (den != 0.0) ? c[j][p] / den : 0.0;
-                // (hi_k - x) w = ((hi_k - t_m) - u) w ;  (x - lo_k) w = (u + (t_m - lo_k)) w
-                const double a = hi_k - (double)tm, b = (double)tm - lo_k;
-                double left[4], right[4];
-                for (int p = 0; p < 4; ++p) {
-                    const double wm1 = (p > 0) ? w[p - 1] : 0.0;
-                    left[p] = a * w[p] - wm1;
-                    right[p] = b * w[p] + wm1;
-                }
-                for (int p = 0; p < 4; ++p) {
-                    c[j][p] = carry[p] + left[p];
-                    carry[p] = right[p];
-                }
-            }
-            for (int p = 0; p < 4; ++p) c[d][p] = carry[p];
-        }
-        for (int j = 0; j < 4; ++j) {
-            const int r = s + j;
-            if (j > K || r < 0 || r >= R)
-                for (int p = 0; p < 4; ++p) c[j][p] = 0.0;
-        }
-    }
-    for (int j = 0; j < 4; ++j)
-        for (int p = 0; p < 4; ++p) ent[j * 4 + p] = (float)c[j][p];
-    ent[16] = tm;
-    ent[17] = __int_as_float(s);
-    ent[18] = 0.0f;
-    ent[19] = 0.0f;
+    poly_table_entry(t, nk, K, R, e, out + ti.es + e * TAB_ENTRY_FLOATS);
 }
 
 // True when every feature has the knot row of feature 0 (the default uniform grid): the kernels
@@ -186,10 +140,7 @@ __device__ __forceinline__ int table_entry_index(const float* __restrict__ ftab,
         const float4 k0 = ld4(reinterpret_cast<const float4*>(ftab + 4));
         const float4 k1 = ld4(reinterpret_cast<const float4*>(ftab + 4) + 1);
         const float4 k2 = ld4(reinterpret_cast<const float4*>(ftab + 4) + 2);
-        const bool inside = (xv >= k0.x) && (xv <= k2.w);
-        const int m = (xv >= k0.y) + (xv >= k0.z) + (xv >= k0.w) + (xv >= k1.x) + (xv >= k1.y) + (xv >= k1.z) +
-                      (xv >= k1.w) + (xv >= k2.x) + (xv >= k2.y) + (xv >= k2.z);
-        return inside ? m : ti.nk - 1;
+        return entry_index12(k0, k1, k2, ti.nk, xv);
     }
     const float* t = ftab + 4;
     const float t_last = SMEM_TAB ? t[ti.nk - 1] : __ldg(t + ti.nk - 1);
@@ -1824,6 +1775,12 @@ inline BwdLayout bwd_layout(const LayerShape& s, bool has_base) {
 }
 
 }  // namespace
+
+size_t tc_table_bytes(const LayerShape& s) { return table_bytes(s); }
+int tc_table_stride(const LayerShape& s) { return make_tab_info(s.G, s.K).fs; }
+cudaError_t tc_build_table(const float* grid, float* tab, int* status, const LayerShape& s, cudaStream_t st) {
+    return launch_table(grid, tab, status, s, st);
+}
 
 bool tc_supported(const LayerShape& s) {
     // any grid the layer accepts (G + 2 K <= 71); the window of k + 1 <= 4 values is what the
