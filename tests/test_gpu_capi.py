@@ -123,6 +123,39 @@ def test_basis_fp32_random(G, k):
     assert (H[out] == 0).all()
 
 
+@pytest.mark.parametrize("G,k", [(5, 3), (6, 2), (7, 1)])
+def test_basis_table_kernels_large_batch(G, k):
+    """float32 with G + k = 8 and more than 2^21 values: the table-driven kernels (per-span
+    polynomials, knots in registers); ragged feature group, inputs on knots and out of range."""
+    N, I = 8200, 260
+    c = make_layer_case(N, I, 3, G, k, np.float32, seed=G * 10 + k, nonuniform=True, xscale=1.3)
+    assert nat.workspace_bytes(nat.OP_BASIS, nat.MODE_AUTO, torch.float32, N, I, 1, G, k) > 0
+    assert nat.workspace_bytes(nat.OP_BASIS, nat.MODE_AUTO, torch.float32, 777, 5, 1, G, k) == 0
+    x, grid = dev(c["x"]), dev(c["grid"])
+    H = nat.basis(x, grid, k)
+    rng = np.random.default_rng(1)
+    gH = rng.standard_normal((N, I, 8)).astype(np.float32)
+    gx = nat.basis_grad(x, grid, k, dev(gH))
+    rows = np.sort(rng.choice(N, size=600, replace=False))
+    rows[-1] = N - 1
+    x64, g64 = c["x"][rows].astype(np.float64), c["grid"].astype(np.float64)
+    ref = ko.compute_basis(x64, g64, k)
+    got = H[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert np.abs(got - ref).max() < 5e-6
+    out = (c["x"][rows] < c["grid"][:, 0]) | (c["x"][rows] > c["grid"][:, -1])
+    assert out.any() and (got[out] == 0).all()
+    dref = (ko.compute_basis_derivative(x64, g64, k) * gH[rows].astype(np.float64)).sum(-1)
+    dgot = gx[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert np.abs(dgot - dref).max() < 1e-5 * max(1.0, np.abs(dref).max())
+    # the calls without scratch run the recurrence kernels and agree
+    import ctypes
+    H2 = torch.empty_like(H)
+    rc = nat.lib().kanb200_basis(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(grid.data_ptr()),
+                                 ctypes.c_void_p(H2.data_ptr()), N, I, G, k,
+                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0 and float((H2 - H).abs().max()) < 5e-6
+
+
 def test_basis_empty_batch():
     c = make_layer_case(4, 3, 2, 5, 3, np.float32, seed=0)
     H = nat.basis(torch.empty(0, 3, device="cuda"), dev(c["grid"]), 3)
@@ -195,6 +228,10 @@ def test_layer_golden_simt():
     dict(N=64, I=9, O=40, G=20, k=3, base=False, nonuniform=True),
     dict(N=515, I=2, O=64, G=8, k=3),
     dict(N=515, I=64, O=1, G=8, k=3),
+    dict(N=1, I=300, O=37, G=5, k=3),                        # small-batch forward kernel: 1 row,
+    dict(N=13, I=130, O=9, G=20, k=2, nonuniform=True),      # ragged rows / features / outputs,
+    dict(N=32, I=7, O=70, G=64, k=3, base=False),            # its largest batch, no base branch
+    dict(N=33, I=7, O=70, G=5, k=1, scaler=False),           # first batch of the tiled kernel
 ])
 def test_layer_simt_vs_oracle(shape, dtype, tol):
     case = make_layer_case(dtype=dtype, seed=11, **shape)

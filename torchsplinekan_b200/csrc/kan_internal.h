@@ -39,7 +39,7 @@ cudaError_t finalize_param_grads(const T* partial, int splits, int64_t split_str
                                  const T* sw, const T* scaler, T* gsw, T* gscaler, T* gbw,
                                  int O, int I, int R, cudaStream_t st);
 
-// Table-driven dense basis / basis gradient (float, R == 8, at most 12 knots, N >= 256): `tab` is
+// Table-driven dense basis / basis gradient (float, R == 8, at most 12 knots, N >= 256, N I >= 2^21): `tab` is
 // the polynomial table built by tc_build_table, `fs` its floats per feature.
 bool basis_table_supported(const LayerShape& s);
 cudaError_t simt_basis_table(const float* x, const float* tab, int fs, float* H, const LayerShape& s,

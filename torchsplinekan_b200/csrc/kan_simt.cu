@@ -782,8 +782,87 @@ cudaError_t simt_basis_grad(const T* x, const T* grid, const T* gH, T* gx, const
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Forward for a handful of rows (inference on small batches): the weights are the traffic, so
+// they are streamed exactly once per block of 8 rows.  A block = 8 warps = 8 outputs x 8 rows;
+// the basis windows of the rows are staged in shared memory per chunk of 128 features, then
+// lane = feature: each lane reads the k+1 weights of its window (consecutive lanes read
+// consecutive weight rows) and the warp reduces over the features by shuffles.
+// ---------------------------------------------------------------------------
+constexpr int FR_THREADS = 256, FR_NR = 8, FR_IC = 128, FR_MAX_ROWS = 32;
+
+template <typename T, int K>
+__global__ void __launch_bounds__(FR_THREADS)
+fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ grid, const T* __restrict__ bw,
+                const T* __restrict__ sw, const T* __restrict__ scaler, T* __restrict__ y,
+                int64_t N, int I, int O, int G) {
+    __shared__ T vals[FR_NR][FR_IC][K + 1];
+    __shared__ T sil[FR_NR][FR_IC];
+    __shared__ int st[FR_NR][FR_IC];
+    const int R = G + K, nk = G + 2 * K + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int o = blockIdx.x * (FR_THREADS / 32) + warp;
+    const int64_t n0 = (int64_t)blockIdx.y * FR_NR;
+    T acc[FR_NR];
+#pragma unroll
+    for (int n = 0; n < FR_NR; ++n) acc[n] = T(0);
+
+    for (int i0 = 0; i0 < I; i0 += FR_IC) {
+        const int ic = (I - i0 < FR_IC) ? (I - i0) : FR_IC;
+        __syncthreads();
+        for (int e = tid; e < FR_NR * ic; e += FR_THREADS) {
+            const int n = e / ic, i = e - n * ic;
+            T w[K + 1];
+            int s = 0;
+            T sv = T(0);
+#pragma unroll
+            for (int j = 0; j <= K; ++j) w[j] = T(0);
+            if (n0 + n < N) {
+                const T xv = x[(size_t)(n0 + n) * I + (i0 + i)];
+                const T* t = grid + (size_t)(i0 + i) * nk;
+                const int m = find_span(t, nk, xv);
+                if (m >= 0) {
+                    T v[K + 1], d[K + 1];
+                    local_basis<K, T, false>(t, nk, m, xv, v, d);
+                    s = window_in_range<K, T>(m, R, v, w);
+                }
+                sv = bw ? silu_t<T>(xv) : T(0);
+            }
+#pragma unroll
+            for (int j = 0; j <= K; ++j) vals[n][i][j] = w[j];
+            sil[n][i] = sv;
+            st[n][i] = s;
+        }
+        __syncthreads();
+        if (o < O) {
+            for (int i = lane; i < ic; i += 32) {
+                const size_t oi = (size_t)o * I + (i0 + i);
+                const T* wrow = sw + oi * R;
+                const T sc = scaler ? scaler[oi] : T(1);
+                const T b = bw ? bw[oi] : T(0);
+#pragma unroll
+                for (int n = 0; n < FR_NR; ++n) {
+                    const int s = st[n][i];
+                    T dot = T(0);
+#pragma unroll
+                    for (int j = 0; j <= K; ++j) dot += vals[n][i][j] * wrow[s + j];
+                    acc[n] += sc * dot + sil[n][i] * b;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < FR_NR; ++n) {
+        T v = acc[n];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0 && o < O && n0 + n < N) y[(size_t)(n0 + n) * O + o] = v;
+    }
+}
+
 bool basis_table_supported(const LayerShape& s) {
-    return s.R() == 8 && s.T() <= 12 && s.K >= 1 && s.K <= 3 && s.N >= 256;
+    // below about two million values the extra launch of the table kernel costs more than it saves
+    return s.R() == 8 && s.T() <= 12 && s.K >= 1 && s.K <= 3 && s.N >= 256 && s.N * s.I >= (int64_t)1 << 21;
 }
 
 cudaError_t simt_basis_table(const float* x, const float* tab, int fs, float* H, const LayerShape& s,
@@ -808,6 +887,12 @@ template <typename T>
 cudaError_t simt_forward(const T* x, const T* grid, const T* bw, const T* sw, const T* scaler, T* y,
                          const LayerShape& s, cudaStream_t st) {
     if (s.N == 0) return cudaSuccess;
+    if (s.N <= FR_MAX_ROWS) {
+        dim3 g((s.O + FR_THREADS / 32 - 1) / (FR_THREADS / 32), (unsigned)((s.N + FR_NR - 1) / FR_NR));
+        KAN_DISPATCH_K(s.K, (fwd_rows_kernel<T, KK><<<g, FR_THREADS, 0, st>>>(x, grid, bw, sw, scaler, y, s.N, s.I,
+                                                                              s.O, s.G)));
+        return cudaGetLastError();
+    }
     const int RW = s.R() + 1;
     int CI = (int)(32768 / ((size_t)RW * (FW_TO + 1) * sizeof(T)));
     if (CI > 16) CI = 16;
