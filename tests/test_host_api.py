@@ -243,3 +243,39 @@ def test_gradient_bucket_arguments_and_row_ranges():
     assert lin.weight.grad.data_ptr() == b.buckets[0].data_ptr()
     with pytest.raises(ValueError, match="CUDA device"):
         sk.HostBatchPrefetcher((2, 2), torch.float32, torch.device("cpu"))
+
+
+def test_data_parallel_entry_points_validate_before_any_launch():
+    """Argument checks of the row-range backward and of the all-reduce return error codes without
+    touching a device (no compute call is made here)."""
+    lib = _native.lib()
+    p = ctypes.c_void_p(4096)                 # never dereferenced: every call below is refused
+    rows = lambda o0, o1, mode=_native.MODE_TC_BF16X3: lib.kanb200_backward_param_rows(
+        mode, p, p, p, p, p, p, p, p, p, 512, 64, 1024, 5, 3, o0, o1, p, 1 << 20, None)
+    assert rows(256, 256) == _native.EINVAL and "rows" in _native.last_error()
+    assert rows(0, 2000) == _native.EINVAL
+    assert rows(0, 256, _native.MODE_SIMT) == _native.EUNSUPPORTED
+    assert lib.kanb200_allreduce_pad_bytes(8, 128) == 8 * 128 * 4
+    assert lib.kanb200_allreduce_pad_bytes(17, 8) == 0
+    bases = (ctypes.c_void_p * 2)(4096, 8192)
+    status = ctypes.c_void_p(4096)
+    ar = lambda n, world=2, rank=0, local=1, blocks=8, pad=1 << 20, mc=None: lib.kanb200_allreduce_sum_f32(
+        bases, mc, 0, pad, n, rank, world, local, blocks, 1.0, status, None)
+    assert ar(1023) == _native.EINVAL and "multiple of 4" in _native.last_error()
+    assert ar(1024, pad=1024) == _native.EINVAL and "overlaps" in _native.last_error()
+    assert ar(1024, world=17) == _native.EINVAL
+    assert ar(1024, rank=2) == _native.EINVAL
+    assert ar(1024, blocks=0) == _native.EINVAL
+    assert ar(1024, local=2, mc=ctypes.c_void_p(4096)) == _native.EINVAL and "peer loads" in _native.last_error()
+    offs = (ctypes.c_size_t * 5)(0, 4096, 8192, 12288, 16384)
+    cnts = (ctypes.c_size_t * 5)(64, 64, 64, 64, 64)
+    assert lib.kanb200_allreduce_sum_f32_ranges(bases, None, offs, cnts, 5, 1 << 20, 0, 2, 1, 8, 128, 1.0,
+                                                status, None) == _native.EINVAL
+    assert lib.kanb200_allreduce_sum_f32_ranges(bases, None, offs, cnts, 2, 1 << 20, 0, 2, 1, 8, 100, 1.0,
+                                                status, None) == _native.EINVAL
+    # scratch of the table-driven basis kernels: only float32 with G + k = 8 and enough values
+    f32, f64 = torch.float32, torch.float64
+    assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f32, 65536, 1024, 1, 5, 3) == 256 + 1024 * 1024
+    assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f64, 65536, 1024, 1, 5, 3) == 0
+    assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f32, 65536, 1024, 1, 8, 3) == 0
+    assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f32, 1024, 64, 1, 5, 3) == 0

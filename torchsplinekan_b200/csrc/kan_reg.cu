@@ -22,6 +22,20 @@ __device__ __forceinline__ T sign_t(T v) { return T((v > T(0)) - (v < T(0))); }
 
 constexpr int EA_TI = 4, EA_THREADS = 128;
 
+// Reads CNT consecutive values from a 16-byte aligned shared-memory row with 16-byte loads.
+template <typename T, int CNT>
+__device__ __forceinline__ void load_row16(const T* __restrict__ p, T (&out)[CNT]) {
+    constexpr int PER = 16 / sizeof(T);
+    static_assert(CNT % PER == 0, "row length must be a multiple of 16 bytes");
+    struct __align__(16) Pack { T v[PER]; };
+#pragma unroll
+    for (int q = 0; q < CNT / PER; ++q) {
+        const Pack pk = reinterpret_cast<const Pack*>(p)[q];
+#pragma unroll
+        for (int e = 0; e < PER; ++e) out[q * PER + e] = pk.v[e];
+    }
+}
+
 // Thread = OPT outputs x one feature, W rows in registers; loops over the
 // samples of its split with H / s tiles staged in shared memory.
 template <typename T, int RMAX, int OPT, int TNS, bool GRAD>
@@ -31,7 +45,7 @@ edge_param_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
                   T* __restrict__ part_a, T* __restrict__ part_dbw, T* __restrict__ part_dW,
                   int64_t N, int I, int O, int R, int64_t n_per_split) {
     constexpr int TO = 32 * OPT;
-    __shared__ T Hs[TNS][EA_TI][RMAX];
+    __shared__ __align__(16) T Hs[TNS][EA_TI][RMAX];
     __shared__ T ss[TNS][EA_TI];
     const int tid = threadIdx.x;
     const int lane_o = tid & 31, ti = tid >> 5;
@@ -80,14 +94,15 @@ edge_param_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
         const int lim = (int)((ne - nt < TNS) ? (ne - nt) : TNS);
         for (int n = 0; n < lim; ++n) {
             const T sv = ss[n][ti];
+            T hrow[RMAX];
+            load_row16<T, RMAX>(&Hs[n][ti][0], hrow);
             T phi[OPT];
 #pragma unroll
             for (int u = 0; u < OPT; ++u) phi[u] = sv * bwv[u];
 #pragma unroll
             for (int r = 0; r < RMAX; ++r) {
-                const T h = Hs[n][ti][r];
 #pragma unroll
-                for (int u = 0; u < OPT; ++u) phi[u] += h * w[u][r];
+                for (int u = 0; u < OPT; ++u) phi[u] += hrow[r] * w[u][r];
             }
             if (!GRAD) {
 #pragma unroll
@@ -101,9 +116,8 @@ edge_param_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
                 }
 #pragma unroll
                 for (int r = 0; r < RMAX; ++r) {
-                    const T h = Hs[n][ti][r];
 #pragma unroll
-                    for (int u = 0; u < OPT; ++u) dw[u][r] += g[u] * h;
+                    for (int u = 0; u < OPT; ++u) dw[u][r] += g[u] * hrow[r];
                 }
             }
         }
@@ -149,7 +163,8 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
                   const T* __restrict__ W, const T* __restrict__ ga,
                   T* __restrict__ ds, T* __restrict__ dH,
                   int64_t N, int I, int O, int R) {
-    __shared__ T Ws[TOC][EB_TI][RMAX + 2];        // [..][RMAX] = bw, [..][RMAX+1] = ga/N
+    constexpr int WROW = RMAX + 16 / sizeof(T);   // 16-byte aligned rows: [RMAX] = bw, [RMAX+1] = ga/N
+    __shared__ __align__(16) T Ws[TOC][EB_TI][WROW];
     const int tid = threadIdx.x;
     const int ti = tid & (EB_TI - 1), tn = tid / EB_TI;
     const int i0 = blockIdx.y * EB_TI;
@@ -174,6 +189,7 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
             const int o = e / (EB_TI * (RMAX + 2));
             const int rem = e - o * (EB_TI * (RMAX + 2));
             const int ii = rem / (RMAX + 2), r = rem - ii * (RMAX + 2);
+            // (the padding slots beyond RMAX + 1 are never read as data)
             T v = T(0);
             if (oc + o < O && i0 + ii < I) {
                 const size_t oi = (size_t)(oc + o) * I + i0 + ii;
@@ -185,7 +201,8 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
         }
         __syncthreads();
         for (int o = 0; o < TOC; ++o) {
-            const T* wr = &Ws[o][ti][0];
+            T wr[WROW];
+            load_row16<T, WROW>(&Ws[o][ti][0], wr);
             T phi = sv * wr[RMAX];
 #pragma unroll
             for (int r = 0; r < RMAX; ++r) phi += h[r] * wr[r];
@@ -210,7 +227,49 @@ struct EdgePlan {
     int64_t n_per_split;
 };
 
-template <typename T>
+// Resident blocks per SM of the parameter kernel that plan_edge would launch (asked from the
+// runtime once per instantiation; a build-time estimate when no device can be asked).
+template <typename T, bool GRAD>
+int edge_param_blocks_per_sm(int rmax) {
+    static int cached[4] = {0, 0, 0, 0};
+    const int slot = rmax == 8 ? 0 : (rmax == 16 ? 1 : (rmax == 32 ? 2 : 3));
+    if (cached[slot] > 0) return cached[slot];
+    int n = 0;
+    cudaError_t e;
+    if (rmax == 8)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 8, 4, 32, GRAD>, EA_THREADS, 0);
+    else if (rmax == 16)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 16, 2, 32, GRAD>, EA_THREADS, 0);
+    else if (rmax == 32)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 32, 1, 8, GRAD>, EA_THREADS, 0);
+    else
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 72, 1, 8, GRAD>, EA_THREADS, 0);
+    if (e != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        return GRAD ? 2 : 4;            // not cached: a later call with a device asks again
+    }
+    cached[slot] = n;
+    return n;
+}
+
+inline int edge_sm_count() {
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            cached = n;
+        else {
+            cudaGetLastError();
+            return 148;
+        }
+    }
+    return cached;
+}
+
+// Split of the sample range: the number of blocks is brought close to a whole number of waves
+// (resident blocks on the whole device), since a partly filled last wave costs a full one.
+template <typename T, bool GRAD>
 EdgePlan plan_edge(int64_t N, int I, int O, int R) {
     EdgePlan p;
     p.rmax = R <= 8 ? 8 : (R <= 16 ? 16 : (R <= 32 ? 32 : 72));
@@ -218,12 +277,24 @@ EdgePlan plan_edge(int64_t N, int I, int O, int R) {
     p.tns = p.rmax >= 32 ? 8 : 32;
     p.to = 32 * p.opt;
     const int64_t bxy = (int64_t)((O + p.to - 1) / p.to) * ((I + EA_TI - 1) / EA_TI);
-    int64_t splits = (4 * 148 + bxy - 1) / bxy;
-    const int64_t max_splits = (N + 127) / 128;
-    if (splits > max_splits) splits = max_splits;
-    if (splits > 64) splits = 64;
-    if (splits < 1) splits = 1;
-    p.n_per_split = (N + splits - 1) / splits;
+    const int64_t wave = (int64_t)edge_sm_count() * edge_param_blocks_per_sm<T, GRAD>(p.rmax);
+    int64_t max_splits = (N + 127) / 128;
+    if (max_splits > 64) max_splits = 64;
+    if (max_splits < 1) max_splits = 1;
+    int64_t best = 1;
+    double best_eff = 0.0;
+    for (int64_t sp = 1; sp <= max_splits; ++sp) {
+        const int64_t blocks = bxy * sp;
+        const int64_t waves = (blocks + wave - 1) / wave;
+        // fraction of the occupied block slots that do work, discounted a little per extra slab
+        const double eff = (double)blocks / (double)(waves * wave) - 0.004 * (double)(sp - 1);
+        if (eff > best_eff + 1e-9) {
+            best_eff = eff;
+            best = sp;
+        }
+        if (blocks >= 8 * wave) break;      // many waves: the tail no longer matters
+    }
+    p.n_per_split = (N + best - 1) / best;
     p.splits = (int)((N + p.n_per_split - 1) / p.n_per_split);
     if (p.splits < 1) p.splits = 1;
     return p;
@@ -255,7 +326,7 @@ inline int grid_1d(int64_t work, int threads, int cap = 148 * 32) {
 
 template <typename T>
 size_t edge_workspace(int64_t N, int I, int O, int R, bool backward) {
-    EdgePlan p = plan_edge<T>(N, I, O, R);
+    EdgePlan p = backward ? plan_edge<T, true>(N, I, O, R) : plan_edge<T, false>(N, I, O, R);
     const size_t oi = (size_t)O * I;
     return (size_t)p.splits * oi * (backward ? (size_t)(R + 1) : 1) * sizeof(T);
 }
@@ -263,7 +334,7 @@ size_t edge_workspace(int64_t N, int I, int O, int R, bool backward) {
 template <typename T>
 cudaError_t edge_abs_mean_fwd(const T* s, const T* H, const T* bw, const T* W, T* a,
                               int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st) {
-    EdgePlan p = plan_edge<T>(N, I, O, R);
+    EdgePlan p = plan_edge<T, false>(N, I, O, R);
     const size_t oi = (size_t)O * I;
     if (!ws || ws_bytes < (size_t)p.splits * oi * sizeof(T)) return cudaErrorMemoryAllocation;
     T* pa = reinterpret_cast<T*>(ws);
@@ -280,7 +351,7 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
     cudaError_t e = cudaSuccess;
     const size_t oi = (size_t)O * I;
     if (dbw || dW) {
-        EdgePlan p = plan_edge<T>(N, I, O, R);
+        EdgePlan p = plan_edge<T, true>(N, I, O, R);
         if (!ws || ws_bytes < (size_t)p.splits * oi * (R + 1) * sizeof(T)) return cudaErrorMemoryAllocation;
         T* pdW = reinterpret_cast<T*>(ws);
         T* pdbw = pdW + (size_t)p.splits * oi * R;
