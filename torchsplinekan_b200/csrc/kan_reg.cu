@@ -153,11 +153,23 @@ __global__ void sum_slabs_kernel(const T* __restrict__ part, T* __restrict__ out
     }
 }
 
-// Thread = one (n, i): H row and dH accumulators in registers, loops over
-// tiles of outputs staged in shared memory.
+// ga/N with the sign of phi (0 where phi == 0): the factor g of the backward formulas.
+template <typename T>
+__device__ __forceinline__ T signed_weight(T c, T phi) {
+    return phi > T(0) ? c : (phi < T(0) ? -c : T(0));
+}
+template <>
+__device__ __forceinline__ float signed_weight<float>(float c, float phi) {
+    // c with its sign flipped where phi is negative
+    const float flipped = __int_as_float(__float_as_int(c) ^ (__float_as_int(phi) & 0x80000000));
+    return phi == 0.0f ? 0.0f : flipped;
+}
+
+// Thread = NPT samples x one feature: their H rows and dH accumulators in registers; loops over
+// tiles of outputs staged in shared memory (a weight row is read once per NPT samples).
 constexpr int EB_TI = 4, EB_TN = 32, EB_THREADS = 128;
 
-template <typename T, int RMAX, int TOC>
+template <typename T, int RMAX, int TOC, int NPT>
 __global__ void __launch_bounds__(EB_THREADS)
 edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __restrict__ bw,
                   const T* __restrict__ W, const T* __restrict__ ga,
@@ -169,19 +181,24 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
     const int ti = tid & (EB_TI - 1), tn = tid / EB_TI;
     const int i0 = blockIdx.y * EB_TI;
     const int i = i0 + ti;
-    const int64_t n = (int64_t)blockIdx.x * EB_TN + tn;
-    const bool live = (i < I) && (n < N);
+    const int64_t nbase = (int64_t)blockIdx.x * (EB_TN * NPT) + tn;
     const bool has_base = (bw != nullptr);
     const T invN = T(1) / T(N);
 
-    T h[RMAX], dh[RMAX];
+    T h[NPT][RMAX], dh[NPT][RMAX], sv[NPT], dsv[NPT];
+    bool live[NPT];
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-        h[r] = (live && r < R) ? H[((size_t)n * I + i) * R + r] : T(0);
-        dh[r] = T(0);
+    for (int q = 0; q < NPT; ++q) {
+        const int64_t n = nbase + (int64_t)q * EB_TN;
+        live[q] = (i < I) && (n < N);
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) {
+            h[q][r] = (live[q] && r < R) ? H[((size_t)n * I + i) * R + r] : T(0);
+            dh[q][r] = T(0);
+        }
+        sv[q] = (live[q] && has_base) ? s[(size_t)n * I + i] : T(0);
+        dsv[q] = T(0);
     }
-    const T sv = (live && has_base) ? s[(size_t)n * I + i] : T(0);
-    T dsv = T(0);
 
     for (int oc = 0; oc < O; oc += TOC) {
         __syncthreads();
@@ -200,24 +217,34 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
             Ws[o][ii][r] = v;
         }
         __syncthreads();
+#pragma unroll 1
         for (int o = 0; o < TOC; ++o) {
-            T wr[WROW];
-            load_row16<T, WROW>(&Ws[o][ti][0], wr);
-            T phi = sv * wr[RMAX];
+            // narrow rows are copied to registers with 16-byte loads; wide ones are read in place
+            constexpr int WREG = RMAX <= 16 ? WROW : 1;
+            T wreg[WREG];
+            if constexpr (RMAX <= 16) load_row16<T, WROW>(&Ws[o][ti][0], wreg);
+            const T* wr = RMAX <= 16 ? wreg : &Ws[o][ti][0];
 #pragma unroll
-            for (int r = 0; r < RMAX; ++r) phi += h[r] * wr[r];
-            const T g = wr[RMAX + 1] * sign_t<T>(phi);
-            dsv += g * wr[RMAX];
+            for (int q = 0; q < NPT; ++q) {
+                T phi = sv[q] * wr[RMAX];
 #pragma unroll
-            for (int r = 0; r < RMAX; ++r) dh[r] += g * wr[r];
+                for (int r = 0; r < RMAX; ++r) phi += h[q][r] * wr[r];
+                const T g = signed_weight<T>(wr[RMAX + 1], phi);
+                dsv[q] += g * wr[RMAX];
+#pragma unroll
+                for (int r = 0; r < RMAX; ++r) dh[q][r] += g * wr[r];
+            }
         }
     }
-    if (live) {
-        if (ds) ds[(size_t)n * I + i] = dsv;
+#pragma unroll
+    for (int q = 0; q < NPT; ++q) {
+        if (!live[q]) continue;
+        const int64_t n = nbase + (int64_t)q * EB_TN;
+        if (ds) ds[(size_t)n * I + i] = dsv[q];
         if (dH) {
 #pragma unroll
             for (int r = 0; r < RMAX; ++r)
-                if (r < R) dH[((size_t)n * I + i) * R + r] = dh[r];
+                if (r < R) dH[((size_t)n * I + i) * R + r] = dh[q][r];
         }
     }
 }
@@ -369,12 +396,13 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
     }
     if ((ds && bw) || dH) {
         const int rmax = R <= 8 ? 8 : (R <= 16 ? 16 : (R <= 32 ? 32 : 72));
-        dim3 g((unsigned)((N + EB_TN - 1) / EB_TN), (I + EB_TI - 1) / EB_TI);
+        const int npt = rmax == 8 ? 4 : (rmax == 16 ? 2 : 1);   // samples per thread
+        dim3 g((unsigned)((N + EB_TN * npt - 1) / (EB_TN * npt)), (I + EB_TI - 1) / EB_TI);
         T* dsp = (ds && bw) ? ds : nullptr;
-        if (rmax == 8) edge_input_kernel<T, 8, 32><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        else if (rmax == 16) edge_input_kernel<T, 16, 32><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        else if (rmax == 32) edge_input_kernel<T, 32, 16><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        else edge_input_kernel<T, 72, 8><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        if (rmax == 8) edge_input_kernel<T, 8, 32, 4><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        else if (rmax == 16) edge_input_kernel<T, 16, 32, 2><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        else if (rmax == 32) edge_input_kernel<T, 32, 16, 1><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
+        else edge_input_kernel<T, 72, 8, 1><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
         e = cudaGetLastError();
     }
     return e;
