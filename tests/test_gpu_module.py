@@ -417,3 +417,25 @@ def test_direct_gradient_sink_matches_autograd(chunks, need_x):
     layer.zero_grad()
     layer(x.detach()).square().sum().backward()
     assert _err(layer.spline_weight.grad, plain.spline_weight.grad) < 1e-6
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-9), (torch.float32, 2e-5)])
+def test_update_grid_on_gpu_matches_cpu_solve(dtype, tol):
+    """update_grid on CUDA samples (systems reduced by QR on the GPU, small systems solved on the
+    CPU) against the same layer updated on the CPU (tall systems solved directly)."""
+    import torchsplinekan_b200 as sk
+    torch.manual_seed(4)
+    cpu = sk.KANLinear(24, 17, grid_size=6, backend="reference").to(dtype)
+    gpu = sk.KANLinear(24, 17, grid_size=6, backend="cuda").to("cuda", dtype)
+    gpu.load_state_dict(cpu.state_dict())
+    g = torch.Generator().manual_seed(5)
+    x = torch.where(torch.rand(3000, 24, generator=g) < 0.5, -0.5, 0.5) + 0.2 * torch.randn(3000, 24, generator=g)
+    x = x.clamp_(-1, 1).to(dtype)
+    x[:, 3] = 0.25                                      # a constant feature: rank-deficient system
+    cpu.update_grid(x)
+    gpu.update_grid(x.cuda())
+    assert _err(gpu.grid.cpu(), cpu.grid) < (1e-12 if dtype == torch.float64 else 1e-6)
+    probe = (torch.rand(500, 24, generator=g) * 2 - 1).to(dtype)
+    assert _err(gpu(probe.cuda()).cpu(), cpu(probe)) < tol
+    keep = [i for i in range(24) if i != 3]
+    assert _err(gpu.spline_weight[:, keep].cpu(), cpu.spline_weight[:, keep]) < tol

@@ -131,18 +131,31 @@ def fit_spline_coeffs(x_samples: torch.Tensor, y_samples: torch.Tensor, grid: to
 def curve2coeff(x_samples: torch.Tensor, y_samples: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
     """Least-squares spline coefficients ``[O, I, R]`` reproducing ``y_samples [O, B, I]`` at ``x_samples [B, I]``.
 
-    Solved in float64 on the CPU with LAPACK's minimum-norm least squares, one
-    system per input feature, all features in one batched call
-    (reference_backend.py:218-265 solves the same systems in a Python loop).
+    One system ``A_i [B, R] c = Y_i [B, O]`` per input feature, solved in float64 with LAPACK's
+    minimum-norm least squares in one batched call (reference_backend.py:218-265 solves the same
+    systems in a Python loop).  For samples on a GPU the systems are first reduced there:
+    ``A_i = Q_i R_i`` (Householder QR), ``Z_i = Q_i^T Y_i``; ``min |A c - Y| = min |R c - Z|`` has the
+    same minimisers and the same singular values, so the small ``[R, R]`` systems that go to the
+    CPU give the same minimum-norm solution while ``B / R`` times fewer bytes cross the bus.
     """
-    # Per-feature systems A_i [B, R] c = Y_i [B, O].  The operands are put into the batched
-    # [I, B, *] layout on the samples' device (a cheap transpose there) and only then moved to
-    # the CPU, where one batched LAPACK call solves all features.
     A = compute_basis(x_samples, grid, k).permute(1, 0, 2).contiguous()                   # [I, B, R]
-    Y = y_samples.permute(2, 1, 0).contiguous()                                            # [I, B, O]
-    A = A.to(device="cpu").to(torch.float64)
-    Y = Y.to(device="cpu").to(torch.float64)
-    sol = torch.linalg.lstsq(A, Y).solution                                               # [I, R, O]
+    if not A.is_cuda:
+        Y = y_samples.permute(2, 1, 0).contiguous().to(torch.float64)                      # [I, B, O]
+        sol = torch.linalg.lstsq(A.to(torch.float64), Y).solution                          # [I, R, O]
+        return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype)
+    n_feat, n_samp, n_coef = A.shape
+    n_out = y_samples.shape[0]
+    Q, Rm = torch.linalg.qr(A.to(torch.float64))                                           # [I, B, R], [I, R, R]
+    Z = torch.empty((n_feat, n_coef, n_out), dtype=torch.float64, device=A.device)
+    # Q^T Y in slabs of features, so that the float64 copy of Y stays below ~512 MB
+    step = max(1, int((1 << 26) // max(1, n_samp * n_out)))
+    for lo in range(0, n_feat, step):
+        hi = min(n_feat, lo + step)
+        Yc = y_samples[:, :, lo:hi].permute(2, 1, 0).to(torch.float64)                     # [i, B, O]
+        Z[lo:hi] = torch.bmm(Q[lo:hi].transpose(1, 2), Yc)
+    # the rank cut-off LAPACK would have applied to the tall systems
+    rcond = torch.finfo(torch.float64).eps * max(n_samp, n_coef)
+    sol = torch.linalg.lstsq(Rm.cpu(), Z.cpu(), rcond=rcond).solution                      # [I, R, O]
     return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype, device=x_samples.device)
 
 
