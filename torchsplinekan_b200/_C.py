@@ -168,6 +168,21 @@ def kan_backward_composite(grad_output, x, grid, base_weight, spline_weight, spl
 # and tells the sink after each range, so that the all-reduce of one range overlaps the
 # computation of the next.  See data_parallel.GradientBucket(direct=True).
 _grad_sinks: dict = {}
+_sinks_disabled = 0
+
+
+class no_grad_sinks:
+    """Context in which forwards do not use a registered gradient sink: for call sites whose
+    parameters also receive gradients from other terms (the fused regulariser)."""
+
+    def __enter__(self):
+        global _sinks_disabled
+        _sinks_disabled += 1
+
+    def __exit__(self, *exc):
+        global _sinks_disabled
+        _sinks_disabled -= 1
+        return False
 
 
 def register_grad_sink(spline_weight: torch.Tensor, sink) -> None:
@@ -218,6 +233,7 @@ class KANFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, grid, base_weight, spline_weight, spline_scaler, spline_order: int, has_scaler: bool):
         ctx.spline_order, ctx.has_scaler = int(spline_order), bool(has_scaler)
+        ctx.allow_sink = _sinks_disabled == 0
         y = _forward_impl(x, grid, base_weight, spline_weight, spline_scaler, spline_order, has_scaler)
         ctx.save_for_backward(x, grid, base_weight, spline_weight, spline_scaler)
         return y
@@ -231,7 +247,7 @@ class KANFunction(torch.autograd.Function):
             gx, gb, gs, gc = kan_backward_composite(grad_output, x, grid, base_weight, spline_weight,
                                                     spline_scaler, k, has_scaler)
         else:
-            sink = _grad_sinks.get(spline_weight.data_ptr()) if _grad_sinks else None
+            sink = _grad_sinks.get(spline_weight.data_ptr()) if (_grad_sinks and ctx.allow_sink) else None
             if sink is not None:
                 handled, gx = _sink_backward(ctx, sink, grad_output, x, grid, base_weight, spline_weight,
                                              spline_scaler, k, has_scaler)

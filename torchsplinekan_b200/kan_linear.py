@@ -168,7 +168,11 @@ class KANLinear(nn.Module):
         and gradients up to rounding and keep the full graph to ``x`` and the parameters.
         """
         if mode == "coefficient":
-            return self(x), self.regularization_loss(reg_act, reg_entropy, mode="coefficient")
+            # the parameters get gradients from both terms: a data-parallel gradient sink must not
+            # take over the layer's backward
+            with _C.no_grad_sinks():
+                y = self(x)
+            return y, self.regularization_loss(reg_act, reg_entropy, mode="coefficient")
         if mode != "activation":
             raise ValueError(f"mode must be 'activation' or 'coefficient', got {mode!r}")
         lead = x.shape[:-1]
@@ -177,6 +181,10 @@ class KANLinear(nn.Module):
         s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         W = self._ref.effective_spline_weight()
+        # y is formed from the same H that feeds the edge statistic, in full float32 like the
+        # reference: with the split-bf16 layer kernels the hidden activations of a deep net move by
+        # a few 1e-5, which flips sign(phi) of near-zero edges in the following layers and shows up
+        # as 5e-4 differences in the penalty's gradient (measured on the 784-256-256-10 net).
         y = F.linear(s, self.base_weight) + F.linear(H.reshape(xf.shape[0], -1), W.reshape(self.out_features, -1))
         self.last_backend = "cuda" if impl == "fused" else "reference"
         a = self._edge_abs_mean(xf, s, H, W, impl, chunk_size)
