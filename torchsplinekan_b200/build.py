@@ -18,7 +18,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libkan_b200.so")
 SOURCES = ["kan_capi.cu", "kan_simt.cu", "kan_reg.cu", "kan_tc.cu", "kan_probe.cu", "kan_collective.cu"]
-HEADERS = ["kan_device.cuh", "kan_internal.h", "kan_table.cuh", "kan_tc_ptx.cuh", "kan_tc_bwd2.cuh", os.path.join("..", "..", "include", "kan_b200.h")]
+HEADERS = ["kan_device.cuh", "kan_internal.h", "kan_table.cuh", "kan_tc_ptx.cuh", os.path.join("..", "..", "include", "kan_b200.h")]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]

@@ -1556,8 +1556,6 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 }
 
-#include "kan_tc_bwd2.cuh"
-
 // Sums the per-split slabs (blocked layout of the drain) and applies the scaler algebra:
 // gsw = scaler * D, gscaler = sum_r sw * D, gbw = base column.  A block handles 32 outputs x 8
 // features: the slabs are read with the output index fastest (contiguous 16-byte pieces per warp),
@@ -1724,28 +1722,6 @@ inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     return p;
 }
 
-inline Bwd2Plan plan_bwd2(const LayerShape& s, bool has_base) {
-    Bwd2Plan p;
-    p.n_otiles = (s.O + BLOCK_N - 1) / BLOCK_N;
-    p.n_opairs = (p.n_otiles + 1) / 2;
-    p.ct_spline = (s.I * make_tab_info(s.G, s.K).cpf + 15) / 16;
-    p.ct_base = has_base ? (s.I + 127) / 128 : 0;
-    p.kb_total = (s.N + BLOCK_K - 1) / BLOCK_K;
-    // even, and long enough that the blocks one accumulator runs ahead never reach the other's boundary
-    p.chunk_kb = bwd_chunk_kb() < 8 ? 8 : (bwd_chunk_kb() & ~1);
-    const int64_t tiles = (int64_t)p.n_opairs * p.n_ctiles();
-    int64_t splits = sm_count() / tiles;
-    if (splits < 1) splits = 1;
-    if (splits > p.kb_total) splits = p.kb_total;
-    if (splits > 32) splits = 32;
-    p.kb_per_split = (p.kb_total + splits - 1) / splits;
-    p.splits = (int)((p.kb_total + p.kb_per_split - 1) / p.kb_per_split);
-    return p;
-}
-
-// Which formulation of the parameter-gradient kernel runs (KAN_B200_BWD_V2=1 selects the second).
-inline bool use_bwd2() { static int v = env_int("KAN_B200_BWD_V2", 0); return v != 0; }
-
 inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 inline size_t table_bytes(const LayerShape& s) {
@@ -1795,10 +1771,6 @@ inline BwdLayout bwd_layout(const LayerShape& s, bool has_base) {
     L.plan = plan_bwd(s, has_base);
     L.dyimg_bytes = (size_t)L.plan.kb_total * L.plan.n_otiles * 2 * BWD_D_SLOT_BYTES;
     L.partial_bytes = (size_t)L.plan.splits * L.plan.slab_floats() * sizeof(float);
-    if (use_bwd2()) {
-        const Bwd2Plan p2 = plan_bwd2(s, has_base);
-        L.partial_bytes = (size_t)p2.splits * p2.slab_floats() * sizeof(float);
-    }
     return L;
 }
 
@@ -1913,32 +1885,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
-    if (need_param && use_bwd2()) {
-        const Bwd2Plan p2 = plan_bwd2(s, has_base);
-        const int64_t items = p2.n_items();
-        const int blocks = (int)(items < sm_count() ? items : sm_count());
-#define KAN_BWD2(NT, W)                                                                                        \
-    do {                                                                                                      \
-        e = ensure_dynamic_smem<tc_bwd_param2_kernel<NT, W>>((int)B2_SMEM_BYTES);                             \
-        if (e == cudaSuccess)                                                                                 \
-            tc_bwd_param2_kernel<NT, W><<<blocks, TC_THREADS, B2_SMEM_BYTES, st>>>(                           \
-                x, tab, dyimg, partial, status, s.N, s.I, s.O, p2, ti, vec_ok);                               \
-    } while (0)
-        if (ti.cpf == 1) {
-            if (split_terms == 3) KAN_BWD2(3, false); else KAN_BWD2(1, false);
-        } else {
-            if (split_terms == 3) KAN_BWD2(3, true); else KAN_BWD2(1, true);
-        }
-#undef KAN_BWD2
-        if (e != cudaSuccess) return e;
-        if ((e = cudaGetLastError()) != cudaSuccess) return e;
-        const int64_t total = (int64_t)((s.O + 3) / 4) * s.I;
-        int fblocks = (int)((total + 255) / 256 < (int64_t)sm_count() * 16 ? (total + 255) / 256
-                                                                           : (int64_t)sm_count() * 16);
-        finalize2_kernel<<<fblocks, 256, 0, st>>>(partial, p2, ti.cpf, sw, scaler, gsw, gscaler,
-                                                  has_base ? gbw : nullptr, s.O, s.I, s.R());
-        if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    } else if (need_param) {
+    if (need_param) {
         const int64_t items = L.plan.n_items();
         const int blocks = (int)(items < sm_count() ? items : sm_count());
 #define KAN_BWD(NT, W)                                                                                         \
