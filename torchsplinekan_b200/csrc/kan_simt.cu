@@ -221,7 +221,7 @@ __device__ __forceinline__ int basis_table_eval(const float* __restrict__ fcoef,
     return m - K;
 }
 
-__global__ void __launch_bounds__(BT_THREADS)
+__global__ void __launch_bounds__(BT_THREADS, 4)
 basis_table_kernel(const float* __restrict__ x, const float* __restrict__ tab, int fs, float* __restrict__ H,
                    int64_t N, int I, int G, int K, int64_t rows_per_block) {
     __shared__ __align__(16) float stab[BT_FEATURES * BT_STRIDE];
@@ -274,7 +274,7 @@ basis_table_kernel(const float* __restrict__ x, const float* __restrict__ tab, i
     }
 }
 
-__global__ void __launch_bounds__(BT_THREADS)
+__global__ void __launch_bounds__(BT_THREADS, 4)
 basis_grad_table_kernel(const float* __restrict__ x, const float* __restrict__ tab, int fs,
                         const float* __restrict__ gH, float* __restrict__ gx, int64_t N, int I, int G, int K,
                         int64_t rows_per_block) {
