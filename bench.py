@@ -339,7 +339,12 @@ def run_gpu_arm(args):
                          "achieved": achieved, "peak": bf16_peak, "unit": "TFLOP/s",
                          "frac": achieved / bf16_peak if achieved else None,
                          "frac_of_issued_mma": terms * achieved / bf16_peak if achieved else None,
-                         "peak_source": f"bf16 sustained, of {peak_src}", "traffic": None,
+                         "peak_source": f"bf16 sustained, of {peak_src}",
+                         # DRAM bytes per launch of the dominant kernel: ncu capture at 16 384 rows
+                         # (dram__bytes_read.sum + dram__bytes_write.sum), the part that grows with the
+                         # rows (x and the dY image / y) scaled to this run's rows, the rest (weight
+                         # image, tables, slab) kept
+                         "traffic": ncu_traffic_bytes(dom, rows),
                          "note": "flops counted once: 2*N*O*I*(R+1) per pass; the split mode issues 3 bf16 MMAs "
                                  "per product, so frac is capped at 1/3"},
             "clocks": clocks,
@@ -353,6 +358,18 @@ def run_gpu_arm(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def ncu_traffic_bytes(kernel, rows):
+    """DRAM traffic per launch of the two contraction kernels, from the ncu capture summarised in
+    profiles/tc_kernels_rows16384_full.md: forward 145.8 MB read + 41.5 MB written, parameter
+    backward 134.9 MB + 6.2 MB at 16 384 rows.  Of that, x, y and the dY image grow with the rows
+    (forward 67 + 67 MB, backward 67 + 67 MB at 16 384 rows); the remainder does not."""
+    if kernel not in ("forward", "backward"):
+        return None
+    total = {"forward": 187.3e6, "backward": 141.1e6}[kernel]
+    per_16k = 134.2e6
+    return per_16k * rows / 16384.0 + (total - per_16k)
 
 
 def run_micro(args):
