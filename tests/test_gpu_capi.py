@@ -230,8 +230,8 @@ def test_layer_golden_simt():
     dict(N=515, I=64, O=1, G=8, k=3),
     dict(N=1, I=300, O=37, G=5, k=3),                        # small-batch forward kernel: 1 row,
     dict(N=13, I=130, O=9, G=20, k=2, nonuniform=True),      # ragged rows / features / outputs,
-    dict(N=32, I=7, O=70, G=64, k=3, base=False),            # its largest batch, no base branch
-    dict(N=33, I=7, O=70, G=5, k=1, scaler=False),           # first batch of the tiled kernel
+    dict(N=255, I=7, O=70, G=64, k=3, base=False),           # its largest batch, no base branch
+    dict(N=256, I=7, O=70, G=5, k=1, scaler=False),          # first batch of the tiled kernel
 ])
 def test_layer_simt_vs_oracle(shape, dtype, tol):
     case = make_layer_case(dtype=dtype, seed=11, **shape)
