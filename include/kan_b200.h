@@ -197,10 +197,14 @@ KANB200_API int kanb200_backward_param_rows(int mode, const void* grad_out, cons
  * otherwise the owner of each slice loads it from every peer and stores the sum to every peer.
  * local_ranks > 1 runs ranks rank .. rank+local_ranks-1 of ONE device inside a single launch
  * (peer loads only) - the way to exercise the protocol on one GPU.  *status (device int) is set
- * to 1 when a bounded wait on another rank ran out; the pad must then be zeroed. */
+ * to 1 when a bounded wait on another rank ran out (kanb200_allreduce_set_wait_limit_ms); the pad
+ * must then be zeroed. */
 #define KANB200_MAX_RANKS 16
 #define KANB200_MAX_SEGMENTS 4
 KANB200_API size_t kanb200_allreduce_pad_bytes(int world, int blocks);
+/* How long a rank waits for another one inside the kernel before it gives up with *status = 1
+ * (process-wide; default 10 s). */
+KANB200_API int kanb200_allreduce_set_wait_limit_ms(int ms);
 KANB200_API int kanb200_allreduce_sum_f32(const void* const* peer_bases, void* multicast_base,
                                           size_t payload_offset, size_t pad_offset, size_t n_floats,
                                           int rank, int world, int local_ranks, int blocks, float scale,

@@ -60,6 +60,7 @@ SIGNATURES = {
                                                                           _c_i64, _c_i64, _c_void_p, _c_size,
                                                                           _c_void_p]),
     "kanb200_allreduce_pad_bytes": (_c_size, [_c_int, _c_int]),
+    "kanb200_allreduce_set_wait_limit_ms": (_c_int, [_c_int]),
     "kanb200_allreduce_sum_f32_ranges": (_c_int, [ctypes.POINTER(_c_void_p), _c_void_p, ctypes.POINTER(_c_size),
                                                   ctypes.POINTER(_c_size), _c_int, _c_size, _c_int, _c_int, _c_int,
                                                   _c_int, _c_int, ctypes.c_float, _c_void_p, _c_void_p]),
@@ -353,6 +354,10 @@ def check_status(ws: Optional[torch.Tensor]) -> None:
 # gradient all-reduce over symmetric memory
 # ---------------------------------------------------------------------------
 MAX_RANKS = 16
+
+
+def allreduce_set_wait_limit_ms(ms: int) -> None:
+    _check(lib().kanb200_allreduce_set_wait_limit_ms(int(ms)))
 
 
 def allreduce_pad_bytes(world: int, blocks: int) -> int:

@@ -394,6 +394,12 @@ KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const vo
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "umma_probe");
 }
 
+KANB200_API int kanb200_allreduce_set_wait_limit_ms(int ms) {
+    if (ms < 1 || ms > 600000) return fail(KANB200_EINVAL, "allreduce: wait limit must be between 1 ms and 10 min");
+    allreduce_set_wait_limit_ms((unsigned)ms);
+    return KANB200_OK;
+}
+
 KANB200_API size_t kanb200_allreduce_pad_bytes(int world, int blocks) {
     if (world < 1 || world > KANB200_MAX_RANKS || blocks < 1) return 0;
     return allreduce_pad_bytes(world, blocks);

@@ -13,7 +13,7 @@
 //
 // Block b of rank r only talks to block b of the other ranks: signal word [b][src] of a rank's
 // pad is raised by block b of rank src (CAS 0 -> 1) and lowered by the owner (CAS 1 -> 0), so
-// the pad needs no reset between calls.  Every spin has a time limit (two seconds); when it runs out
+// the pad needs no reset between calls.  Every spin has a time limit (ten seconds unless set otherwise); when it runs out
 // the kernel records kStatusTimeout in the caller's status word and returns (the pad is then
 // in an undefined state and must be zeroed before the next call).
 #include <cuda_runtime.h>
@@ -28,7 +28,9 @@ namespace {
 constexpr int AR_THREADS = 512;
 constexpr int AR_UNROLL = 8;
 constexpr int kArTimeout = 1;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;     // two seconds per wait
+// Limit of one wait on another rank.  Ranks of a job drift apart by much more than a kernel's
+// run time (first-call set-up, host scheduling), so the default is generous; it is still a bound.
+static unsigned long long g_wait_limit_ns = 10000000000ull;
 
 struct PeerTable {
     void* base[KANB200_MAX_RANKS];
@@ -55,7 +57,7 @@ __device__ __forceinline__ uint32_t cas_acquire_sys(uint32_t* addr, uint32_t exp
 
 // Block-level barrier with the same block of every other rank.  Returns false after a timeout.
 __device__ bool rank_barrier(const PeerTable& peers, size_t pad_off, int rank, int world, int block,
-                             int* status, int* abort_flag) {
+                             unsigned long long limit_ns, int* status, int* abort_flag) {
     __threadfence_system();                    // this thread's stores, visible to the peers
     __syncthreads();
     if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
@@ -69,13 +71,13 @@ __device__ bool rank_barrier(const PeerTable& peers, size_t pad_off, int rank, i
         do {
             if (cas_release_sys(remote, 0u, 1u) == 0u) { ok = true; break; }
             __nanosleep(64);
-        } while (global_timer_ns() - t0 < kWaitLimitNs);
+        } while (global_timer_ns() - t0 < limit_ns);
         if (ok) {
             ok = false;
             do {
                 if (cas_acquire_sys(local, 1u, 0u) == 1u) { ok = true; break; }
                 __nanosleep(64);
-            } while (global_timer_ns() - t0 < kWaitLimitNs);
+            } while (global_timer_ns() - t0 < limit_ns);
         }
         if (!ok) {
             atomicExch(status, kArTimeout);
@@ -120,13 +122,13 @@ struct Segments {
 template <bool MULTIMEM>
 __global__ void __launch_bounds__(AR_THREADS)
 allreduce_sum_kernel(PeerTable peers, char* mc_base, Segments segs, size_t pad_off,
-                     int rank0, int world, float scale, int* status) {
+                     int rank0, int world, float scale, unsigned long long limit_ns, int* status) {
     __shared__ int abort_flag;
     if (threadIdx.x == 0) abort_flag = 0;
     __syncthreads();
     const int rank = rank0 + blockIdx.y;
     const int block = blockIdx.x;
-    if (!rank_barrier(peers, pad_off, rank, world, block, status, &abort_flag)) return;
+    if (!rank_barrier(peers, pad_off, rank, world, block, limit_ns, status, &abort_flag)) return;
 
     for (int sg = 0; sg < segs.count; ++sg) {
         const size_t n4 = segs.n4[sg], payload_off = segs.off[sg];
@@ -172,10 +174,12 @@ allreduce_sum_kernel(PeerTable peers, char* mc_base, Segments segs, size_t pad_o
             }
         }
     }
-    rank_barrier(peers, pad_off, rank, world, block, status, &abort_flag);
+    rank_barrier(peers, pad_off, rank, world, block, limit_ns, status, &abort_flag);
 }
 
 }  // namespace
+
+void allreduce_set_wait_limit_ms(unsigned ms) { g_wait_limit_ns = (unsigned long long)ms * 1000000ull; }
 
 size_t allreduce_pad_bytes(int world, int blocks) {
     return ((size_t)world * blocks * sizeof(uint32_t) + 255) / 256 * 256;
@@ -195,9 +199,10 @@ cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, const s
     dim3 grid((unsigned)blocks, (unsigned)local_ranks);
     if (multicast_base)
         allreduce_sum_kernel<true><<<grid, threads, 0, st>>>(t, static_cast<char*>(multicast_base), segs, pad_off,
-                                                            rank, world, scale, status);
+                                                            rank, world, scale, g_wait_limit_ns, status);
     else
-        allreduce_sum_kernel<false><<<grid, threads, 0, st>>>(t, nullptr, segs, pad_off, rank, world, scale, status);
+        allreduce_sum_kernel<false><<<grid, threads, 0, st>>>(t, nullptr, segs, pad_off, rank, world, scale,
+                                                             g_wait_limit_ns, status);
     return cudaGetLastError();
 }
 

@@ -87,6 +87,7 @@ cudaError_t umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, u
 
 // Gradient all-reduce over symmetric memory (kan_collective.cu).
 size_t allreduce_pad_bytes(int world, int blocks);
+void allreduce_set_wait_limit_ms(unsigned ms);
 cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, const size_t* offsets, const size_t* n_floats,
                           int n_segments, size_t pad_off, int rank, int world, int local_ranks, int blocks,
                           int threads, float scale, int* status, cudaStream_t st);
