@@ -158,18 +158,13 @@ KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a,
                                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* Reads (and clears) the status word the tensor-core kernels keep at the start
- * of a workspace; synchronises the stream.  0 = every wait completed. */
+ * of a workspace; synchronises the stream.  0 = every wait completed.  The word
+ * is sticky: kernels only change it from 0 to a code and nothing but this call
+ * clears it, so a timed-out wait in one call is still reported after any number
+ * of later calls on the same workspace.  The caller zeroes the first 256 bytes
+ * of a workspace once, before its first use.  (No counterpart in the reference,
+ * whose kernels have no waits.) */
 KANB200_API int kanb200_check_status(void* workspace, void* stream);
-
-/* Layout self-test for the tensor-core operand formats: copies two byte images
- * into shared memory, issues `ksteps` tcgen05 MMAs (M = 128, N = ncols, K = 16
- * each, start addresses advanced by a_step / b_step bytes per step) with the
- * given matrix / instruction descriptors and writes the fp32 accumulator
- * D[128, ncols].  Has no counterpart in the reference; used by the tests to pin
- * the K-major and MN-major 128-byte-swizzle layouts the kernels rely on. */
-KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
-                       uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps,
-                       uint32_t a_step, uint32_t b_step, int ncols, float* D, int* status, void* stream);
 
 /* Parameter gradients of the output rows [o_begin, o_end) only (tensor-core modes, float32): the
  * pointers are those of the FULL tensors as in kanb200_backward; rows outside the range are not

@@ -37,4 +37,4 @@ def pytest_sessionstart(session):
     spec = importlib.util.spec_from_file_location("_kan_b200_build", os.path.join(ROOT, "torchsplinekan_b200", "build.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    mod.build_library()
+    mod.build_all()

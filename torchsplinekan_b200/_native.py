@@ -53,9 +53,6 @@ SIGNATURES = {
     "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                             _c_void_p, _c_size, _c_void_p]),
     "kanb200_check_status": (_c_int, [_c_void_p, _c_void_p]),
-    "kanb200_umma_probe": (_c_int, [_c_void_p, ctypes.c_uint32, _c_void_p, ctypes.c_uint32, ctypes.c_uint64,
-                                    ctypes.c_uint64, ctypes.c_uint32, _c_int, ctypes.c_uint32, ctypes.c_uint32,
-                                    _c_int, _c_void_p, _c_void_p, _c_void_p]),
     "kanb200_backward_param_rows": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                           _c_i64, _c_i64, _c_void_p, _c_size,
                                                                           _c_void_p]),

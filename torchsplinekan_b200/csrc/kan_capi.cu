@@ -146,7 +146,7 @@ KANB200_API int kanb200_basis_ws(int dtype, const void* x, const void* grid, voi
     if (!x || !grid || !H) return fail(KANB200_EINVAL, "kan_basis: NULL pointer");
     cudaStream_t st = (cudaStream_t)stream;
     float* tab = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWsHeader);
-    cudaError_t e = tc_build_table((const float*)grid, tab, reinterpret_cast<int*>(workspace), s, st);
+    cudaError_t e = tc_build_table((const float*)grid, tab, s, st);
     if (e == cudaSuccess) e = simt_basis_table((const float*)x, tab, tc_table_stride(s), (float*)H, s, st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis");
 }
@@ -164,7 +164,7 @@ KANB200_API int kanb200_basis_grad_ws(int dtype, const void* x, const void* grid
     if (!x || !grid || !gH || !gx) return fail(KANB200_EINVAL, "kan_basis_grad: NULL pointer");
     cudaStream_t st = (cudaStream_t)stream;
     float* tab = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWsHeader);
-    cudaError_t e = tc_build_table((const float*)grid, tab, reinterpret_cast<int*>(workspace), s, st);
+    cudaError_t e = tc_build_table((const float*)grid, tab, s, st);
     if (e == cudaSuccess)
         e = simt_basis_grad_table((const float*)x, tab, tc_table_stride(s), (const float*)gH, (float*)gx, s, st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_basis_grad");
@@ -382,16 +382,6 @@ KANB200_API int kanb200_check_status(void* workspace, void* stream) {
         return fail(KANB200_EDEVICE, "a tensor-core kernel gave up waiting (status %d)", code);
     }
     return KANB200_OK;
-}
-
-KANB200_API int kanb200_umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
-                       uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps,
-                       uint32_t a_step, uint32_t b_step, int ncols, float* D, int* status, void* stream) {
-    if (!a_img || !b_img || !D || !status || (a_bytes & 15) || (b_bytes & 15))
-        return fail(KANB200_EINVAL, "umma_probe: bad arguments");
-    cudaError_t e = umma_probe(a_img, a_bytes, b_img, b_bytes, a_desc, b_desc, idesc, ksteps, a_step, b_step,
-                               ncols, D, status, (cudaStream_t)stream);
-    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "umma_probe");
 }
 
 KANB200_API int kanb200_allreduce_set_wait_limit_ms(int ms) {

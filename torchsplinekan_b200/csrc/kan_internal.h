@@ -74,16 +74,10 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
                         const float* bw, const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
                         float* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st);
 
-// The per-span polynomial table on its own: bytes, floats per feature, and the kernel that fills it
-// (it also clears *status).
+// The per-span polynomial table on its own: bytes, floats per feature, and the kernel that fills it.
 size_t tc_table_bytes(const LayerShape& s);
 int tc_table_stride(const LayerShape& s);
-cudaError_t tc_build_table(const float* grid, float* tab, int* status, const LayerShape& s, cudaStream_t st);
-
-// Layout self-test (kan_probe.cu).
-cudaError_t umma_probe(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
-                       uint64_t a_desc, uint64_t b_desc, uint32_t idesc, int ksteps, uint32_t a_step,
-                       uint32_t b_step, int ncols, float* D, int* status, cudaStream_t st);
+cudaError_t tc_build_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st);
 
 // Gradient all-reduce over symmetric memory (kan_collective.cu).
 size_t allreduce_pad_bytes(int world, int blocks);
@@ -93,7 +87,8 @@ cudaError_t allreduce_sum(void* const* peer_bases, void* multicast_base, const s
                           int threads, float scale, int* status, cudaStream_t st);
 
 // Workspaces start with a 256-byte header whose first word is a status code
-// written by kernels whose bounded waits ran out.
+// written by kernels whose bounded waits ran out.  The word is sticky: kernels
+// only ever change it from 0 to a code, and only kanb200_check_status clears it.
 constexpr size_t kWsHeader = 256;
 
 }  // namespace kanb200

@@ -1,0 +1,106 @@
+// Self-test of the shared-memory operand layouts of tcgen05.mma.  Built into its own small library
+// (lib/libkan_b200_selftest.so) that only the test-suite loads; it is not part of the product ABI.
+//
+// One CTA copies two caller-built byte images (A: 128 x 64 bf16, B: 256 x 64 bf16) into shared
+// memory, issues the four K = 16 MMAs of one 64-wide block with the descriptors of the layout the
+// caller NAMES -- the same constexpr descriptor builders the production kernels use -- and writes
+// the fp32 accumulator D[128, 256] out.  The test builds the images for the K-major and MN-major
+// 128-byte-swizzle layouts and checks the product against numpy, so a wrong descriptor shows up
+// as a failed small test instead of a wrong large result.  Descriptors are never taken from the
+// caller.
+#include "kan_tc_ptx.cuh"
+
+#include <cuda_runtime.h>
+
+namespace kanb200 {
+
+namespace {
+using namespace ptx;
+
+constexpr int kLayoutKMajor = 0;     // rows x 128 B, K contiguous (forward: generated operand, weight image)
+constexpr int kLayoutMnMajor = 1;    // [64-wide MN group][8-row K group][8 rows][128 B] (backward operands)
+constexpr uint32_t kABytes = 128 * 64 * 2, kBBytes = 256 * 64 * 2;
+constexpr int kSteps = 4, kCols = 256;
+
+__global__ void __launch_bounds__(128, 1)
+umma_layout_kernel(const uint8_t* __restrict__ a_img, const uint8_t* __restrict__ b_img, int layout,
+                   float* __restrict__ D, int* __restrict__ status) {
+    const bool mn = layout == kLayoutMnMajor;
+    const uint32_t a_bytes = kABytes, b_bytes = kBBytes;
+    const uint64_t a_desc = mn ? make_sdesc_sw128(8192, 1024) : make_sdesc_sw128(16, 1024), b_desc = a_desc;
+    const uint32_t idesc = make_idesc_bf16(kCols, mn, mn);
+    const uint32_t a_step = mn ? 2048u : 32u, b_step = a_step;
+    const int ksteps = kSteps, ncols = kCols;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t done_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if ((sbase & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(status, 2);
+        return;
+    }
+    const uint32_t a_off = 0, b_off = (a_bytes + 1023u) & ~1023u;
+    for (uint32_t e = threadIdx.x * 16; e < a_bytes; e += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(smem + a_off + e) = *reinterpret_cast<const uint4*>(a_img + e);
+    for (uint32_t e = threadIdx.x * 16; e < b_bytes; e += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(smem + b_off + e) = *reinterpret_cast<const uint4*>(b_img + e);
+    fence_proxy_async_smem();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done_bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) {
+        for (int ks = 0; ks < ksteps; ++ks)
+            mma_f16_ss(tmem_base, sdesc_at(a_desc, sbase + a_off + ks * a_step),
+                       sdesc_at(b_desc, sbase + b_off + ks * b_step), idesc, ks > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&done_bar));
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(smem_u32(&done_bar), 0, &abort_flag);
+    tc_fence_after_sync();
+    if (ok) {
+        const int row = warp * 32 + lane;
+        for (int c = 0; c < ncols / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+            tmem_ld_wait();
+            for (int q = 0; q < 32; ++q) D[(size_t)row * ncols + c * 32 + q] = __uint_as_float(r[q]);
+        }
+    } else {
+        if (lane == 0) atomicExch(status, 1);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+}  // namespace
+}  // namespace kanb200
+
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_umma_layout(int layout, const void* a_img, const void* b_img, float* D, int* status,
+                                 void* stream) {
+    using namespace kanb200;
+    if ((layout != kLayoutKMajor && layout != kLayoutMnMajor) || !a_img || !b_img || !D || !status) return -1;
+    const int smem = (int)(kABytes + kBBytes);
+    cudaError_t e = cudaFuncSetAttribute(umma_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return -4;
+    umma_layout_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(reinterpret_cast<const uint8_t*>(a_img),
+                                                                reinterpret_cast<const uint8_t*>(b_img), layout, D,
+                                                                status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -29,8 +29,6 @@
 #include "kan_table.cuh"
 #include "kan_tc_ptx.cuh"
 
-#include <cstdlib>
-
 namespace kanb200 {
 
 namespace {
@@ -94,10 +92,9 @@ inline TabInfo make_tab_info(int G, int K) {
 }
 
 __global__ void build_poly_table_kernel(const float* __restrict__ grid, float* __restrict__ tab,
-                                        int* __restrict__ status, int I, int G, int K, TabInfo ti) {
+                                        int I, int G, int K, TabInfo ti) {
     const int nk = ti.nk, R = G + K;
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx == 0) *status = 0;                 // the contraction kernels that follow report into it
     if (idx >= I * (nk + 1)) return;
     const int f = idx / (nk + 1), e = idx - f * (nk + 1);
     const float* t = grid + (size_t)f * nk;
@@ -477,7 +474,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
     if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
-        if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
+        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -748,7 +745,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
 
     // ===== teardown =====
     if (*abort_flag) {
-        if (lane == 0) atomicExch(status, kStatusTimeout);
+        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
         __nanosleep(100000);                   // let copies / MMAs in flight land
     }
     tc_fence_before_sync();
@@ -820,7 +817,7 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     const int64_t n_items = plan.n_items();
 
     if ((sbase & 1023u) != 0) {
-        if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
+        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -1120,7 +1117,7 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 
     if (*abort_flag) {
-        if (lane == 0) atomicExch(status, kStatusTimeout);
+        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();
@@ -1195,7 +1192,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {
-        if (threadIdx.x == 0) atomicExch(status, kStatusBadSmem);
+        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -1544,7 +1541,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 
     if (*abort_flag) {
-        if (lane == 0) atomicExch(status, kStatusTimeout);
+        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();
@@ -1694,16 +1691,14 @@ inline int sm_count() {
 }
 
 // Chunk lengths (k-blocks accumulated in TMEM between drains).  Every tensor-core accumulation
-// truncates, so the error of a chain grows with its length; these defaults keep it below the
-// operand-split error.  KAN_B200_FWD_CHUNK / KAN_B200_BWD_CHUNK override them (tuning only).
-inline int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    if (!v || !*v) return dflt;
-    const int n = atoi(v);
-    return n > 0 ? n : dflt;
-}
-inline int fwd_chunk_kb() { static int c = env_int("KAN_B200_FWD_CHUNK", 144); return c; }
-inline int bwd_chunk_kb() { static int c = env_int("KAN_B200_BWD_CHUNK", 16); return c; }
+// truncates, so the error of a chain grows with its length; these lengths keep it below the
+// operand-split error (measured against float64: forward chains of 144 column blocks and backward
+// chains of 16 blocks of 64 samples stay within 1e-5 of max|result|; 32 / 64 sample blocks give
+// 8e-6 / 1.4e-5).  They are part of the numerical contract and therefore not tunable at run time.
+constexpr int kFwdChunkKb = 144;
+constexpr int kBwdChunkKb = 16;
+inline int fwd_chunk_kb() { return kFwdChunkKb; }
+inline int bwd_chunk_kb() { return kBwdChunkKb; }
 
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     BwdPlan p;
@@ -1728,11 +1723,10 @@ inline size_t table_bytes(const LayerShape& s) {
     return align256((size_t)s.I * make_tab_info(s.G, s.K).fs * sizeof(float));
 }
 
-inline cudaError_t launch_table(const float* grid, float* tab, int* status, const LayerShape& s,
-                                cudaStream_t st) {
+inline cudaError_t launch_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
     const TabInfo ti = make_tab_info(s.G, s.K);
     const int work = s.I * (ti.nk + 1);
-    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, status, s.I, s.G, s.K, ti);
+    build_poly_table_kernel<<<(work + 127) / 128, 128, 0, st>>>(grid, tab, s.I, s.G, s.K, ti);
     return cudaGetLastError();
 }
 
@@ -1778,8 +1772,8 @@ inline BwdLayout bwd_layout(const LayerShape& s, bool has_base) {
 
 size_t tc_table_bytes(const LayerShape& s) { return table_bytes(s); }
 int tc_table_stride(const LayerShape& s) { return make_tab_info(s.G, s.K).fs; }
-cudaError_t tc_build_table(const float* grid, float* tab, int* status, const LayerShape& s, cudaStream_t st) {
-    return launch_table(grid, tab, status, s, st);
+cudaError_t tc_build_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
+    return launch_table(grid, tab, s, st);
 }
 
 bool tc_supported(const LayerShape& s) {
@@ -1812,7 +1806,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     uint8_t* wimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
     const int kb_total = L.cs.kb_total();
     {
-        cudaError_t e0 = launch_table(grid, tab, status, s, st);
+        cudaError_t e0 = launch_table(grid, tab, s, st);
         if (e0 != cudaSuccess) return e0;
         const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
         int blocks = (int)((chunks + 255) / 256);
@@ -1875,7 +1869,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
     if (need_param) cursor += align256(L.partial_bytes);
     uint8_t* wimg = cursor;
 
-    if ((e = launch_table(grid, tab, status, s, st)) != cudaSuccess) return e;
+    if ((e = launch_table(grid, tab, s, st)) != cudaSuccess) return e;
     {
         const int64_t chunks = L.plan.kb_total * L.plan.n_otiles * 2 * 64 * 16;
         int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
