@@ -6,7 +6,8 @@ over the GPUs of one node with an NCCL all-reduce of the parameter gradients.
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
-    python bench.py --impl reference            # CPU arm: numpy port of the reference backend
+    python bench.py --impl reference            # CPU arm: the reference's own backend (baseline/_ref) on the host cores
+    python bench.py --impl reference-cuda       # informational: the reference's own CUDA backend on this GPU
 
 Prints ONE JSON line (rank 0).  `value` = samples/s with inputs resident in
 HBM; `e2e` = the same step through the public module API with the inputs
@@ -30,7 +31,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 IN_F, OUT_F, GRID, ORDER, BATCH = 1024, 1024, 5, 3, 65536
-CPU_SAMPLE_ROWS = 4096
 METRIC = "KANLinear fwd+bwd samples/s (1024->1024, G=5, k=3, fp32)"
 
 
@@ -50,50 +50,204 @@ def measured_peaks():
 
 
 # ---------------------------------------------------------------------------
-# CPU arm: the numpy oracle (a port of the reference's pure-PyTorch backend)
+# Reference arms.  They import the UNMODIFIED reference package from baseline/_ref (installed there by
+# __graft_entry__.build(); git-ignored) and never this repository's package: both register the
+# torch.ops namespace "spline_kan", so they cannot share a process.
 # ---------------------------------------------------------------------------
-def cpu_step(rows: int, reps: int, warmup: int):
-    """Median seconds of one forward + backward of sum(y^2) on `rows` rows, on the host cores, with
-    the multi-threaded PyTorch restatement of the reference's CPU path (oracle/kan_oracle_torch.py)."""
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+CPU_CHUNK_ROWS = 8192
+
+
+def _import_reference():
+    """The reference's `spline_kan` from baseline/_ref, or None when it is not installed."""
+    if not os.path.isdir(os.path.join(REF_DIR, "spline_kan")):
+        return None
+    if "torchsplinekan_b200" in sys.modules:
+        raise RuntimeError("the reference package cannot be imported beside torchsplinekan_b200")
+    sys.path.insert(0, REF_DIR)
+    import spline_kan                                   # noqa: F401  (the reference, not the alias of this repo)
+    assert os.path.realpath(os.path.dirname(spline_kan.__file__)).startswith(os.path.realpath(REF_DIR))
+    return spline_kan
+
+
+def _c1_batch(torch, rows=BATCH):
+    gen = torch.Generator().manual_seed(0)
+    return torch.randn(BATCH, IN_F, generator=gen).clamp_(-1, 1)[:rows].contiguous()
+
+
+def cpu_reference_step(chunks: int, reps: int, warmup: int, native: bool = False):
+    """Median seconds of forward + backward of sum(y^2) over `chunks` chunks of 8192 rows with
+    gradient accumulation, on the host cores: the reference's KANLinear(backend="reference") (pure
+    PyTorch), or with `native` its C++ CPU kernels (csrc/kan_cpu.cpp through _C.kan_apply on CPU
+    tensors).  Returns (seconds, kind) -- kind "port" when baseline/_ref is absent and the PyTorch
+    restatement under oracle/ is timed instead."""
     import torch
-    from oracle import kan_oracle as ko
-    from oracle import kan_oracle_torch as kt
     torch.set_num_threads(os.cpu_count() or 1)
-    g = torch.Generator().manual_seed(0)
-    x = torch.randn(rows, IN_F, generator=g).clamp_(-1, 1)
-    grid = torch.from_numpy(ko.uniform_grid(IN_F, GRID, ORDER))
-    R = GRID + ORDER
-    bw = (torch.rand(OUT_F, IN_F, generator=g) * 2 - 1) / IN_F ** 0.5
-    sw = (torch.rand(OUT_F, IN_F, R, generator=g) * 2 - 1) * 0.1 / R ** 0.5
-    sc = torch.ones(OUT_F, IN_F)
+    ref = _import_reference()
+    x = _c1_batch(torch, chunks * CPU_CHUNK_ROWS)
+    if ref is None:
+        if native:
+            return None, "unavailable"
+        from oracle import kan_oracle as ko
+        from oracle import kan_oracle_torch as kt
+        g = torch.Generator().manual_seed(0)
+        grid = torch.from_numpy(ko.uniform_grid(IN_F, GRID, ORDER))
+        R = GRID + ORDER
+        bw = (torch.rand(OUT_F, IN_F, generator=g) * 2 - 1) / IN_F ** 0.5
+        sw = (torch.rand(OUT_F, IN_F, R, generator=g) * 2 - 1) * 0.1 / R ** 0.5
+        sc = torch.ones(OUT_F, IN_F)
+
+        def step():
+            for c in range(chunks):
+                kt.layer_step_sum_sq(x[c * CPU_CHUNK_ROWS:(c + 1) * CPU_CHUNK_ROWS], grid, bw, sw, sc, ORDER,
+                                     need_x=False)
+        kind = "port"
+    else:
+        torch.manual_seed(0)
+        layer = ref.KANLinear(IN_F, OUT_F, grid_size=GRID, spline_order=ORDER, backend="reference")
+        if native:
+            from spline_kan import kan_linear as ref_kl
+            if not ref_kl._CUDA_EXT_LOADED:
+                return None, "unavailable"
+            ext = ref_kl._C
+
+            def fwd(xc):
+                return ext.kan_apply(xc, layer.grid, layer.base_weight, layer.spline_weight, layer.spline_scaler,
+                                     ORDER, True)
+        else:
+            fwd = layer
+
+        def step():
+            for p in layer.parameters():
+                p.grad = None
+            for c in range(chunks):
+                fwd(x[c * CPU_CHUNK_ROWS:(c + 1) * CPU_CHUNK_ROWS]).square().sum().backward()
+        kind = "reference"
     times = []
     for it in range(warmup + reps):
         t0 = time.perf_counter()
-        kt.layer_step_sum_sq(x, grid, bw, sw, sc, ORDER, need_x=False)
+        step()
         if it >= warmup:
             times.append(time.perf_counter() - t0)
-    return statistics.median(times)
+    return statistics.median(times), kind
+
+
+def cpu_baseline_record(chunks: int, reps: int, warmup: int):
+    """`cpu_baseline` object of the bench line (run in a child process: see _import_reference)."""
+    sec, kind = cpu_reference_step(chunks, reps, warmup)
+    rows = chunks * CPU_CHUNK_ROWS
+    what = ("the reference's KANLinear(backend='reference') on CPU tensors" if kind == "reference"
+            else "PyTorch-CPU restatement of the reference backend (oracle/kan_oracle_torch.py; baseline/_ref absent)")
+    rec = {"value": rows / sec, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": kind,
+           "sample": f"{chunks} chunk(s) of {CPU_CHUNK_ROWS} rows of the {BATCH}-row batch per step with gradient "
+                     f"accumulation, {what}, torch.set_num_threads({os.cpu_count()}), median of {reps} after "
+                     f"{warmup} warm-up"}
+    if kind == "reference":
+        sec2, kind2 = cpu_reference_step(1, max(1, min(reps, 2)), 1, native=True)
+        if sec2 is not None:
+            rec["kan_cpu_cpp"] = {"value": CPU_CHUNK_ROWS / sec2, "unit": "samples/s",
+                                  "sample": f"1 chunk of {CPU_CHUNK_ROWS} rows, the reference's C++ CPU kernels "
+                                            "(csrc/kan_cpu.cpp via _C.kan_apply on CPU tensors)"}
+    return rec, sec * (BATCH / rows)
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-    sec = cpu_step(CPU_SAMPLE_ROWS, steps, warmup)
-    val = CPU_SAMPLE_ROWS / sec
-    cores = os.cpu_count() or 1
-    sample = f"{CPU_SAMPLE_ROWS} rows of the {BATCH}-row batch per step, PyTorch-CPU restatement of the reference backend (oracle/kan_oracle_torch.py), median of {steps}"
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+    rec, sec_full = cpu_baseline_record(args.cpu_chunks, steps, warmup)
     line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": "samples/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": rec["value"], "unit": "samples/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec_full * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "KANLinear 1024->1024 G=5 k=3 fp32, fwd+bwd of sum(y^2), x without grad",
                    "global_batch": BATCH},
-        "cpu_baseline": {"value": val, "unit": "samples/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": rec,
+        "e2e": {"value": rec["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def run_reference_cuda_arm(args):
+    """Informational: the reference's OWN CUDA backend (csrc/kan_cuda.cu: SIMT basis kernels + cuBLAS;
+    csrc/kan_reg_cuda.cu) rebuilt for sm_100 in baseline/_ref, timed on this GPU at the benchmark's
+    configuration with TF32 matmul off (its published setting) and on, plus its fused regulariser on
+    the first layer of the 784-256-256-10 network."""
+    import torch
+    ref = _import_reference()
+    out = {"impl": "reference-cuda"}
+    if ref is None:
+        out["unavailable"] = "baseline/_ref is not installed"
+        print(json.dumps(out), flush=True)
+        return
+    from spline_kan import kan_linear as ref_kl
+    if not (ref_kl._CUDA_EXT_LOADED and torch.cuda.is_available()):
+        out["unavailable"] = "the reference's extension did not load or there is no GPU"
+        print(json.dumps(out), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    layer = ref.KANLinear(IN_F, OUT_F, grid_size=GRID, spline_order=ORDER, backend="cuda").to(dev)
+    x = _c1_batch(torch).to(dev)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    def step():
+        for p in layer.parameters():
+            p.grad = None
+        layer(x).square().sum().backward()
+
+    for tf32 in (False, True):
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        torch.backends.cudnn.allow_tf32 = tf32
+        ms = timed(step, max(3, min(args.steps, 10)))
+        out["c1_tf32_on" if tf32 else "c1_tf32_off"] = {"ms_per_step": ms, "samples_per_s": BATCH / ms * 1e3}
+    torch.backends.cuda.matmul.allow_tf32 = False
+    assert layer.last_backend == "cuda"
+    # fused regulariser, first layer of KAN[784,256,256,10], 8192 rows
+    torch.manual_seed(0)
+    l0 = ref.KANLinear(784, 256, grid_size=GRID, spline_order=ORDER, backend="cuda").to(dev)
+    x2 = (torch.rand(8192, 784, generator=torch.Generator().manual_seed(0)) * 2 - 1).to(dev)
+
+    def reg_step():
+        for p in l0.parameters():
+            p.grad = None
+        y, r = l0.forward_with_regularization(x2, 1e-2, 1e-2, reg_impl="fused")
+        (y.square().mean() + r).backward()
+    ms = timed(reg_step, max(3, min(args.steps, 10)))
+    out["c2_layer0_fwr_fused"] = {"ms_per_step": ms, "rows": 8192}
+    out["gpu"] = torch.cuda.get_device_name(0)
+    print(json.dumps(out), flush=True)
+
+
+def _child_json(argv, timeout):
+    """Runs this script with `argv` in a child process and returns the last JSON line it printed."""
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__)] + argv, capture_output=True, text=True,
+                           timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"timed out after {timeout} s"}
+    for row in reversed(r.stdout.splitlines()):
+        row = row.strip()
+        if row.startswith("{"):
+            try:
+                return json.loads(row)
+            except ValueError:
+                continue
+    return {"unavailable": f"exit code {r.returncode}: {r.stderr.strip()[-300:]}"}
 
 
 # ---------------------------------------------------------------------------
@@ -146,11 +300,37 @@ class ClockSampler:
         return out
 
 
+def multi_gpu_grad_check(torch, dist, layer, x, bucket, step, world):
+    """One extra step after the timed region: the bucket's all-reduced gradients against a plain NCCL
+    all-reduce of this rank's shard gradients (recomputed through autograd outside the bucket), and
+    whether every rank holds the same bits."""
+    from torchsplinekan_b200 import _C
+    step()
+    torch.cuda.synchronize()
+    reduced = torch.cat([b.detach().clone().flatten() for b in bucket.buckets])
+    params = [p for _, ps in bucket._buckets for p in ps]
+    with _C.no_grad_sinks():
+        grads = torch.autograd.grad(layer(x.detach()).square().sum(), params)
+    local = torch.cat([g.flatten() for g in grads])
+    dist.all_reduce(local, op=dist.ReduceOp.SUM)
+    den = float(local.abs().max())
+    max_rel = float((reduced - local).abs().max()) / max(den, 1e-30)
+    words = reduced.view(torch.int32).to(torch.int64)
+    weights = torch.arange(1, words.numel() + 1, device=words.device) % 65521
+    checksum = torch.stack([words.sum(), (words * weights).sum()])
+    gathered = [torch.empty_like(checksum) for _ in range(world)]
+    dist.all_gather(gathered, checksum)
+    identical = all(bool((g == gathered[0]).all()) for g in gathered)
+    return {"max_rel": max_rel, "ranks_bit_identical": identical, "ok": bool(max_rel < 1e-5 and identical),
+            "note": "bucket after the timed path's all-reduce vs NCCL all-reduce of the shard gradients recomputed "
+                    "outside the bucket; tolerance 1e-5 of max|gradient|; bit identity by checksums of the raw words"}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
     import torchsplinekan_b200 as sk
-    from torchsplinekan_b200 import _native, _C
+    from torchsplinekan_b200 import _C
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -205,13 +385,14 @@ def run_gpu_arm(args):
         return loss
 
     # End to end: every step copies one batch from pinned host memory (the next step's, on a side
-    # stream while this step computes) and reads the loss back.
+    # stream while this step computes) and copies its loss to pinned host memory.  The host reads the
+    # loss of step t only after it has queued step t+2 (three pinned slots), so it is always at least
+    # one full step ahead of the GPU and the device never waits for the host.
     prefetch = sk.HostBatchPrefetcher(x_host.shape, x_host.dtype, dev)
     prefetch.submit(x_host)
-    # the loss of every step is copied to pinned host memory; the host reads it one step later, so
-    # that it queues the next step while the GPU still works on this one
-    loss_host = [torch.zeros(1).pin_memory(), torch.zeros(1).pin_memory()]
-    loss_ready = [None, None]
+    LAG = 2
+    loss_host = [torch.zeros(1).pin_memory() for _ in range(LAG + 1)]
+    loss_ready = [None] * (LAG + 1)
     e2e_state = {"k": 0, "last": None}
 
     def read_loss(slot):
@@ -223,7 +404,6 @@ def run_gpu_arm(args):
     def step_e2e():
         k = e2e_state["k"]
         e2e_state["k"] = k + 1
-        read_loss((k + 1) % 2)                        # result of the previous step
         prefetch.submit(x_host)
         x_stage = prefetch.next()
         if args.need_x:
@@ -238,14 +418,17 @@ def run_gpu_arm(args):
         loss.backward()
         if bucket is not None:
             bucket.finish()
-        loss_host[k % 2].copy_(loss.detach().reshape(1), non_blocking=True)
+        slot = k % (LAG + 1)
+        loss_host[slot].copy_(loss.detach().reshape(1), non_blocking=True)
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream(dev))
-        loss_ready[k % 2] = ev
+        loss_ready[slot] = ev
+        read_loss((k + 1) % (LAG + 1))                # the slot step k+1 will write: result of step k-LAG
 
     def flush_e2e():
-        read_loss(0)
-        read_loss(1)
+        k = e2e_state["k"]
+        for j in range(LAG + 1):
+            read_loss((k + 1 + j) % (LAG + 1))        # oldest first
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -270,9 +453,11 @@ def run_gpu_arm(args):
     for _ in range(max(args.warmup, 3)):
         step_resident()
     step_e2e()
-    _native.EVENT_LOG = []
+    _C.take_event_log()
+    _C.set_event_log(True)
     ms_total = timed(step_resident, args.steps)
-    log, _native.EVENT_LOG = _native.EVENT_LOG, None
+    _C.set_event_log(False)
+    log = _C.take_event_log()
     # keep the same load running (untimed) until the clock sampler has seen about half a second
     # of it; the count is derived from the all-reduced time, so every rank does the same steps
     extra = int(min(2000, max(0, 500.0 / max(ms_total / args.steps, 1e-3) - args.steps)))
@@ -295,14 +480,14 @@ def run_gpu_arm(args):
     ms_e2e = float(ms_t.item())
     assert e2e_state["last"] is not None and math.isfinite(e2e_state["last"])
 
-    for buf in list(_native._ws_cache.values()):
-        _native.check_status(buf)
+    _C.check_status()
     if bucket is not None:
         bucket.check()
+    grad_check = multi_gpu_grad_check(torch, dist, layer, x_dev, bucket, step_resident, world) if world > 1 else None
 
     per = {}
-    for name, a, b in log:
-        per.setdefault(name, []).append(a.elapsed_time(b))
+    for name, ms in log:
+        per.setdefault(name, []).append(ms)
     kernel_ms = {k: sum(v) / len(v) for k, v in per.items()}
 
     # this library's kernels per step: forward = table + weight image + contraction; parameter
@@ -363,13 +548,21 @@ def run_gpu_arm(args):
                                  "per product, so frac is capped at 1/3"},
             "clocks": clocks,
         }
+        line["config"]["loss"] = ("sum(y^2) as one fused autograd function (one reduction pass forward, dY = 2 g y "
+                                  "backward) instead of the four elementwise passes of y.square().sum(); same maths")
+        if grad_check is not None:
+            line["grad_check"] = grad_check
         if world == 1 and not args.no_cpu_baseline:
-            sec = cpu_step(CPU_SAMPLE_ROWS, 3, 1)
-            line["cpu_baseline"] = {"value": CPU_SAMPLE_ROWS / sec, "unit": "samples/s",
-                                    "cores": os.cpu_count() or 1, "kind": "port",
-                                    "sample": f"{CPU_SAMPLE_ROWS} rows of the batch per step, PyTorch-CPU "
-                                              "restatement of the reference backend, all host threads, median of 3"}
+            # the reference itself, in child processes (it cannot be imported beside this package)
+            child = _child_json(["--impl", "reference", "--steps", "2", "--warmup", "1",
+                                 "--cpu-chunks", str(args.cpu_chunks)], timeout=900)
+            line["cpu_baseline"] = child.get("cpu_baseline") or {"unavailable": child.get("unavailable", "no output")}
+            line["reference_cuda"] = _child_json(["--impl", "reference-cuda", "--steps", "5"], timeout=600)
         print(json.dumps(line), flush=True)
+    if grad_check is not None and not grad_check["ok"]:
+        if world > 1:
+            dist.destroy_process_group()
+        raise SystemExit("bench.py: the all-reduced gradients differ from the sum of the shard gradients")
     if world > 1:
         dist.destroy_process_group()
 
@@ -416,8 +609,28 @@ def run_micro(args):
                         frac=bytes_ / ms / 1e6 / hbm_peak, peak_source=f"of {src}")
         if flops is not None:
             line.update(gflops=flops / ms / 1e6)
+            pk = extra.pop("fma_peak_tflops", None)
+            if pk:
+                line.update(fma_peak_tflops=pk, frac_of_fma_peak=flops / ms / 1e9 / pk)
         line.update(extra)
         print(json.dumps(line), flush=True)
+
+    # FMA-pipe peaks (register-only loop of 16 independent chains per thread, 148 * 8 blocks of 256)
+    import ctypes
+    from torchsplinekan_b200.build import SELFTEST_PATH
+    st_lib = ctypes.CDLL(SELFTEST_PATH)
+    st_lib.kanb200_selftest_fma_loop.restype = ctypes.c_int
+    st_lib.kanb200_selftest_fma_loop.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    fma_peak = {}
+    for code, name, dt, iters in ((0, "fp32", torch.float32, 1 << 16), (1, "fp64", torch.float64, 1 << 15)):
+        blocks = 148 * 8
+        buf = torch.empty(blocks * 256, dtype=dt, device=dev)
+        run = lambda: st_lib.kanb200_selftest_fma_loop(code, blocks, iters, ctypes.c_void_p(buf.data_ptr()),
+                                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        ms = timeit(run, reps=5)
+        fma_peak[name] = 2.0 * blocks * 256 * iters * 16 / ms / 1e9          # TFLOP/s
+        print(json.dumps({"kernel": f"fma_loop<{name}>", "ms": ms, "tflops": fma_peak[name],
+                          "note": "measured FMA-pipe peak (register-only loop)"}), flush=True)
 
     # standalone basis / basis gradient: N x I x (R+1) elements, fp32, c1 feature count
     N, I, G, k = args.micro_rows, 1024, 5, 3
@@ -441,11 +654,11 @@ def run_micro(args):
     ga = torch.rand(Oe, Ie, device=dev, generator=g)
     fl = 2.0 * Ne * Oe * Ie * (R + 1)
     ms = timeit(lambda: nat.edge_abs_mean(s, H, bw, W))
-    emit("edge_param_kernel<forward>", ms, flops=fl, bytes_moved_GB=4e-9 * (Ne * Ie * (R + 1) + Oe * Ie * (R + 2)))
+    emit("edge_param_kernel<forward>", ms, flops=fl, fma_peak_tflops=fma_peak["fp32"])
     ms = timeit(lambda: nat.edge_abs_mean_backward(ga, s, H, bw, W, False, False, True, True))
-    emit("edge_param_kernel<grad> + sum_slabs", ms, flops=2 * fl)
+    emit("edge_param_kernel<grad> + sum_slabs", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
     ms = timeit(lambda: nat.edge_abs_mean_backward(ga, s, H, bw, W, True, True, False, False))
-    emit("edge_input_kernel", ms, flops=2 * fl)
+    emit("edge_input_kernel", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
     del H, s, W
 
     # float64 SIMT layer (PINN-style 64 -> 64, G = 8)
@@ -457,10 +670,11 @@ def run_micro(args):
     swd = torch.randn(Od, Id, Gd + k, device=dev, dtype=torch.float64, generator=g)
     scd = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
     ms = timeit(lambda: nat.forward(xd, gd, bwd_, swd, scd, k, nat.MODE_SIMT))
-    emit("fwd_simt_kernel<double,3>", ms, flops=2.0 * Nd * Od * Id * (k + 2), note="useful flops: k+2 terms per edge")
+    emit("fwd_simt_kernel<double,3>", ms, flops=2.0 * Nd * Od * Id * (k + 2), note="useful flops: k+2 terms per edge",
+         fma_peak_tflops=fma_peak["fp64"])
     D = torch.randn(Nd, Od, device=dev, dtype=torch.float64, generator=g)
     ms = timeit(lambda: nat.backward(D, xd, gd, bwd_, swd, scd, k, True, True, True, True, nat.MODE_SIMT))
-    emit("bwd_simt (param + input)<double,3>", ms, flops=4.0 * Nd * Od * Id * (k + 2))
+    emit("bwd_simt (param + input)<double,3>", ms, flops=4.0 * Nd * Od * Id * (k + 2), fma_peak_tflops=fma_peak["fp64"])
 
 
 def run_config(args):
@@ -555,7 +769,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "reference-cuda"])
+    ap.add_argument("--cpu-chunks", type=int, default=8,
+                    help="chunks of 8192 rows per step of the CPU reference arm (8 = the whole 65536-row batch)")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--mode", default=None, choices=[None, "auto", "simt", "bf16x3", "bf16x1"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -571,6 +787,8 @@ def main():
         run_micro(args)
     elif args.impl == "reference":
         run_reference_arm(args)
+    elif args.impl == "reference-cuda":
+        run_reference_cuda_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -25,14 +25,6 @@ def _bf16_bits(a):
     return (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
 
 
-def _sdesc(lbo, sbo):
-    return ((lbo >> 4) & 0x3FFF) << 16 | ((sbo >> 4) & 0x3FFF) << 32 | 1 << 46 | 2 << 61
-
-
-def _idesc(n, a_mn, b_mn):
-    return (1 << 4) | (1 << 7) | (1 << 10) | (int(a_mn) << 15) | (int(b_mn) << 16) | ((n >> 3) << 17) | ((128 >> 4) << 24)
-
-
 def _img_kmajor(M):
     """[rows, 64] matrix -> K-major 128B-swizzled byte image (rows x 128 B), bf16."""
     return _img_kmajor_bits(_bf16_bits(M))
@@ -61,18 +53,27 @@ def _img_mnmajor(M):
     return img
 
 
-def _run_probe(a_img, b_img, a_desc, b_desc, idesc, ksteps, a_step, b_step, ncols):
+def _run_selftest(layout, a_img, b_img):
+    """Runs the operand-layout self-test kernel (its own small library, not part of the product ABI):
+    the caller names the layout (0 = K-major, 1 = MN-major); descriptors are built inside from the
+    same helpers the production kernels use."""
     import ctypes
+    import os
+    from torchsplinekan_b200.build import SELFTEST_PATH
+    assert os.path.exists(SELFTEST_PATH), "build the self-test library with torchsplinekan_b200/build.py"
+    lib = ctypes.CDLL(SELFTEST_PATH)
+    fn = lib.kanb200_selftest_umma_layout
+    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_int] + [ctypes.c_void_p] * 5
     a = torch.from_numpy(a_img.view(np.int16)).cuda()
     b = torch.from_numpy(b_img.view(np.int16)).cuda()
-    D = torch.zeros(128, ncols, dtype=torch.float32, device="cuda")
+    assert a.numel() == 128 * 64 and b.numel() == 256 * 64
+    D = torch.zeros(128, 256, dtype=torch.float32, device="cuda")
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
-    rc = nat.lib().kanb200_umma_probe(ctypes.c_void_p(a.data_ptr()), a.numel() * 2, ctypes.c_void_p(b.data_ptr()),
-                                      b.numel() * 2, a_desc, b_desc, idesc, ksteps, a_step, b_step, ncols,
-                                      ctypes.c_void_p(D.data_ptr()), ctypes.c_void_p(st.data_ptr()), None)
-    assert rc == 0, nat.last_error()
+    rc = fn(layout, ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(D.data_ptr()),
+            ctypes.c_void_p(st.data_ptr()), None)
+    assert rc == 0
     torch.cuda.synchronize()
-    assert int(st.item()) == 0, "probe kernel reported a timed-out wait"
+    assert int(st.item()) == 0, "self-test kernel reported a timed-out wait"
     return D.cpu().numpy()
 
 
@@ -83,16 +84,14 @@ def _small_int_matrix(rng, rows):
 def test_umma_layout_k_major():
     rng = np.random.default_rng(0)
     A, B = _small_int_matrix(rng, 128), _small_int_matrix(rng, 256)
-    D = _run_probe(_img_kmajor(A), _img_kmajor(B), _sdesc(16, 1024), _sdesc(16, 1024), _idesc(256, False, False),
-                   4, 32, 32, 256)
+    D = _run_selftest(0, _img_kmajor(A), _img_kmajor(B))
     assert np.array_equal(D, A @ B.T)
 
 
 def test_umma_layout_mn_major():
     rng = np.random.default_rng(1)
     A, B = _small_int_matrix(rng, 128), _small_int_matrix(rng, 256)
-    D = _run_probe(_img_mnmajor(A), _img_mnmajor(B), _sdesc(8192, 1024), _sdesc(8192, 1024),
-                   _idesc(256, True, True), 4, 2048, 2048, 256)
+    D = _run_selftest(1, _img_mnmajor(A), _img_mnmajor(B))
     assert np.array_equal(D, A @ B.T)
 
 

@@ -1,0 +1,333 @@
+"""Parity at the benchmark configurations' own sizes.
+
+The parity target is the dense PyTorch backend (the formulation of the reference's backend, pinned
+to the reference by the golden files in the CPU tests) evaluated in float64 ON THE GPU in row
+chunks; every tensor is compared with ``max|a - b| / max|b|``.  Tolerances: 1e-5 for float32 layers
+(the split-bf16 tensor-core arithmetic measures 4e-6 .. 7e-6), 1e-12 for float64; the deep float32
+network states its own bound below and says why.
+"""
+import math
+
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+sk = pytest.importorskip("torchsplinekan_b200")
+from torchsplinekan_b200 import _C, _native, dense_backend as db   # noqa: E402
+
+TOL32, TOL64 = 1e-5, 1e-12
+
+
+def _err(a, b):
+    return rel_err(a.detach().double().cpu().numpy(), b.detach().double().cpu().numpy())
+
+
+def _dense64_layer_step(x, grid, bw, sw, sc, k, dY, rows=2048):
+    """Float64 dense evaluation of y and, for the given dY, of all gradients, in row chunks."""
+    g64, bw64, sw64 = grid.double(), bw.double().requires_grad_(), sw.double().requires_grad_()
+    sc64 = sc.double().requires_grad_() if sc is not None else None
+    N, O = x.shape[0], sw.shape[0]
+    y = torch.empty(N, O, dtype=torch.float64, device=x.device)
+    gx = torch.empty(x.shape, dtype=torch.float64, device=x.device)
+    acc = [torch.zeros_like(p) for p in (bw64, sw64, sc64) if p is not None]
+    params = [p for p in (bw64, sw64, sc64) if p is not None]
+    for lo in range(0, N, rows):
+        xc = x[lo:lo + rows].double().requires_grad_()
+        H = db.compute_basis(xc, g64, k)
+        W = sw64 * sc64.unsqueeze(-1) if sc64 is not None else sw64
+        yc = torch.nn.functional.silu(xc) @ bw64.t() + H.reshape(xc.shape[0], -1) @ W.reshape(O, -1).t()
+        grads = torch.autograd.grad(yc, [xc] + params, grad_outputs=dY[lo:lo + rows].double())
+        y[lo:lo + rows] = yc.detach()
+        gx[lo:lo + rows] = grads[0]
+        for a, g in zip(acc, grads[1:]):
+            a += g
+    return y, gx, acc
+
+
+def test_config1_whole_batch_against_float64():
+    """KANLinear 1024 -> 1024, G = 5, k = 3, 65536 rows of N(0,1) clamped to [-1, 1] (a third of the
+    inputs sit exactly on the knots -1 and 1): y, dX and the three parameter gradients of the
+    tensor-core path against float64 for the WHOLE batch.  The backward is fed the kernel's own
+    dY = 2 y on both sides, so each tensor's error is that of the kernel that produced it."""
+    torch.manual_seed(0)
+    L = sk.KANLinear(1024, 1024, backend="cuda").cuda()
+    with torch.no_grad():
+        torch.nn.init.kaiming_uniform_(L.spline_scaler, a=math.sqrt(5))
+    x = torch.randn(65536, 1024, device="cuda", generator=torch.Generator(device="cuda").manual_seed(0)).clamp_(-1, 1)
+    args = (L.grid, L.base_weight.detach(), L.spline_weight.detach(), L.spline_scaler.detach())
+    assert _native.resolve_mode(_native.MODE_AUTO, torch.float32, 65536, 1024, 1024, 5, 3) == _native.MODE_TC_BF16X3
+    y = _native.forward(x, *args, 3, _native.MODE_AUTO)
+    dY = 2.0 * y
+    gx, gb, gs, gc = _native.backward(dY, x, *args, 3, True, True, True, True, _native.MODE_AUTO)
+    y64, gx64, (gb64, gs64, gc64) = _dense64_layer_step(x, *args, 3, dY)
+    errs = {"y": _err(y, y64), "dX": _err(gx, gx64), "d base_weight": _err(gb, gb64),
+            "d spline_weight": _err(gs, gs64), "d spline_scaler": _err(gc, gc64)}
+    print("config 1, 65536 rows, bf16x3 vs float64:", errs)
+    _native.check_all_workspaces()
+    _native.release_workspaces()
+    assert all(e < TOL32 for e in errs.values()), errs
+
+
+@pytest.mark.parametrize("I,O,N", [(4096, 512, 4096), (512, 4096, 4096)])
+def test_long_contractions_keep_the_float32_budget(I, O, N):
+    """A 4096-wide input (forward reduction over 4096 * 9 columns, chunked accumulation) and a
+    4096-wide output (the input-gradient kernel reduces over 4096 outputs): split-bf16 against
+    float64 stays within 1e-5."""
+    torch.manual_seed(1)
+    L = sk.KANLinear(I, O, backend="cuda").cuda()
+    with torch.no_grad():
+        torch.nn.init.kaiming_uniform_(L.spline_scaler, a=math.sqrt(5))
+        L.spline_weight.mul_(3.0)
+    x = torch.randn(N, I, device="cuda", generator=torch.Generator(device="cuda").manual_seed(2)).clamp_(-1, 1)
+    args = (L.grid, L.base_weight.detach(), L.spline_weight.detach(), L.spline_scaler.detach())
+    y = _native.forward(x, *args, 3, _native.MODE_TC_BF16X3)
+    dY = torch.randn(N, O, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    gx, gb, gs, gc = _native.backward(dY, x, *args, 3, True, True, True, True, _native.MODE_TC_BF16X3)
+    y64, gx64, (gb64, gs64, gc64) = _dense64_layer_step(x, *args, 3, dY, rows=512)
+    errs = {"y": _err(y, y64), "dX": _err(gx, gx64), "d base_weight": _err(gb, gb64),
+            "d spline_weight": _err(gs, gs64), "d spline_scaler": _err(gc, gc64)}
+    print(f"I={I} O={O} N={N}, bf16x3 vs float64:", errs)
+    _native.check_all_workspaces()
+    _native.release_workspaces()
+    assert all(e < TOL32 for e in errs.values()), errs
+
+
+@pytest.mark.parametrize("mode", ["auto", "simt"])
+def test_config3_wide_grid_full_size(mode):
+    """KANLinear 512 -> 512, G = 64, 16384 rows of the bimodal mixture, knots from update_grid on
+    that x: tensor-core path (auto) and gather path, against float64."""
+    torch.manual_seed(0)
+    ref = sk.KANLinear(512, 512, grid_size=64, backend="reference").to("cuda", torch.float64)
+    g = torch.Generator().manual_seed(0)
+    x = torch.where(torch.rand(16384, 512, generator=g) < 0.5, -0.5, 0.5) + 0.15 * torch.randn(16384, 512, generator=g)
+    x = x.clamp_(-1, 1).cuda()
+    ref.update_grid(x.double())
+    nat = sk.KANLinear(512, 512, grid_size=64, backend="cuda").cuda()
+    nat.load_state_dict({n: v.float() for n, v in ref.state_dict().items()})
+    args = (nat.grid, nat.base_weight.detach(), nat.spline_weight.detach(), nat.spline_scaler.detach())
+    m = _native.MODES[mode]
+    if mode == "auto":
+        assert _native.resolve_mode(m, torch.float32, 16384, 512, 512, 64, 3) == _native.MODE_TC_BF16X3
+    y = _native.forward(x, *args, 3, m)
+    dY = 2.0 * y
+    gx, gb, gs, gc = _native.backward(dY, x, *args, 3, True, True, True, True, m)
+    y64, gx64, (gb64, gs64, gc64) = _dense64_layer_step(x, *args, 3, dY, rows=512)
+    errs = {"y": _err(y, y64), "dX": _err(gx, gx64), "d base_weight": _err(gb, gb64),
+            "d spline_weight": _err(gs, gs64), "d spline_scaler": _err(gc, gc64)}
+    print(f"config 3 ({mode}) vs float64:", errs)
+    _native.check_all_workspaces()
+    _native.release_workspaces()
+    assert all(e < TOL32 for e in errs.values()), errs
+
+
+def test_config4_float64_pinn_full_size():
+    """KAN [2, 64, 64, 1], G = 8, float64, 131072 collocation points: first-order training step
+    on the native kernels and u_xx through create_graph=True on a 4096-row subset, both against
+    the dense backend to 1e-12."""
+    torch.manual_seed(0)
+    net = sk.KAN([2, 64, 64, 1], grid_size=8, backend="cuda").to("cuda", torch.float64)
+    ref = sk.KAN([2, 64, 64, 1], grid_size=8, backend="reference").to("cuda", torch.float64)
+    ref.load_state_dict(net.state_dict())
+    x = (torch.rand(131072, 2, dtype=torch.float64, generator=torch.Generator().manual_seed(0)) * 2 - 1).cuda()
+    target = torch.sin(math.pi * x[:, 0]) * torch.sin(math.pi * x[:, 1])
+
+    def step(model):
+        for p in model.parameters():
+            p.grad = None
+        u = model(x).squeeze(-1)
+        loss = (u - target).square().mean()
+        loss.backward()
+        return [u, loss] + [p.grad for p in model.parameters()]
+
+    got, want = step(net), step(ref)
+    assert all(l.last_backend == "cuda" for l in net.layers)
+    names = ["u", "loss"] + [n for n, _ in net.named_parameters()]
+    errs = {n: _err(a, b) for n, a, b in zip(names, got, want)}
+    print("config 4 first order:", errs)
+    assert all(e < TOL64 for e in errs.values()), errs
+
+    xs = x[:4096].clone().requires_grad_()
+
+    def second(model):
+        for p in model.parameters():
+            p.grad = None
+        u = model(xs)
+        (u_x,) = torch.autograd.grad(u.sum(), xs, create_graph=True)
+        (u_xx,) = torch.autograd.grad(u_x[:, 0].sum(), xs, create_graph=True)
+        res = (u_xx[:, 0] + math.pi ** 2 * torch.sin(math.pi * xs[:, 0])).square().mean()
+        res.backward()
+        return [u_x, u_xx] + [p.grad for p in model.parameters()]
+
+    got2, want2 = second(net), second(ref)
+    names2 = ["u_x", "u_xx"] + [n for n, _ in net.named_parameters()]
+    errs2 = {n: _err(a, b) for n, a, b in zip(names2, got2, want2)}
+    print("config 4 second order:", errs2)
+    assert all(e < TOL64 for e in errs2.values()), errs2
+    _C.check_status()
+
+
+def test_config2_full_size_training_step():
+    """KAN [784, 256, 256, 10], 8192 rows, update_grid on 4096 rows, cross-entropy plus the fused
+    activation regulariser (1e-2, 1e-2): native float32 against the dense backend in float64
+    (checkpointed evaluation of the same dense formulas, so that phi [N, O, I] is never held whole).
+
+    Bounds and why: y and the penalty are smooth in the rounding error and are held to 5e-5 after
+    three layers (each layer alone is within 1e-5, checked above and in test_gpu_capi).  The
+    penalty's gradient contains sign(phi): where |phi| is at rounding level, float32 and float64
+    disagree on the sign and single entries move by 2 ga / N -- the reference's own float32 test
+    of this path allows 5e-5 for one small layer (tests/test_fused_regularization.py:88-93).  The
+    native gradients must be as close to float64 as the dense FLOAT32 evaluation of the same
+    expression is (factor 3 of slack), and within 2e-4 in any case."""
+    torch.manual_seed(0)
+    net = sk.KAN([784, 256, 256, 10], backend="cuda").cuda()
+    g = torch.Generator().manual_seed(0)
+    x = (torch.rand(8192, 784, generator=g) * 2 - 1).cuda()
+    labels = torch.randint(0, 10, (8192,), generator=torch.Generator().manual_seed(1)).cuda()
+    net.update_grid(x[:4096])
+    ref = sk.KAN([784, 256, 256, 10], backend="reference").to("cuda", torch.float64)
+    ref.load_state_dict({n: v.double() for n, v in net.state_dict().items()})
+    ref32 = sk.KAN([784, 256, 256, 10], backend="reference").cuda()
+    ref32.load_state_dict(net.state_dict())
+
+    def run(model, xin, impl):
+        for p in model.parameters():
+            p.grad = None
+        y, r = model.forward_with_regularization(xin, 1e-2, 1e-2, reg_impl=impl, chunk_size=512)
+        (torch.nn.functional.cross_entropy(y, labels) + r).backward()
+        return [y, r] + [p.grad for p in model.parameters()]
+
+    got = run(net, x, "fused")
+    assert all(l.last_backend == "cuda" for l in net.layers)
+    want = run(ref, x.double(), "checkpoint")
+    want32 = run(ref32, x, "checkpoint")
+    names = ["y", "reg"] + [n for n, _ in net.named_parameters()]
+    errs = {n: _err(a, b) for n, a, b in zip(names, got, want)}
+    gap32 = {n: _err(a, b) for n, a, b in zip(names, want32, want)}
+    print("config 2 native32 vs dense64:", errs)
+    print("config 2 dense32 vs dense64:", gap32)
+    assert errs["y"] < 5e-5 and errs["reg"] < 5e-5, errs
+    for n in names:
+        assert errs[n] < min(2e-4, max(5e-5, 3.0 * gap32[n])), (n, errs[n], gap32[n])
+    _C.check_status()
+
+
+def _knots_with_zero_spans(I, G, k, kind, seed):
+    g = torch.Generator().manual_seed(seed)
+    n = G + 2 * k + 1
+    gaps = torch.rand(I, n - 1, generator=g, dtype=torch.float64) * 0.9 + 0.1
+    if kind == "interior":
+        gaps[:, k + G // 2] = 0.0                      # a zero-length interior span
+    elif kind == "last":
+        gaps[:, -1] = 0.0                              # the last span has zero length
+    elif kind == "double":
+        gaps[:, k + 1] = 0.0
+        gaps[:, k + 2] = 0.0                           # a triple knot
+    t = torch.cat([torch.zeros(I, 1, dtype=torch.float64), gaps.cumsum(1)], 1)
+    return t - t[:, k:k + 1] - 1.0
+
+
+@pytest.mark.parametrize("kind", ["interior", "last", "double"])
+@pytest.mark.parametrize("G,k", [(5, 3), (5, 2), (17, 3)])
+def test_repeated_knots_through_the_table_driven_paths(kind, G, k):
+    """Knot vectors with zero-length spans (the reference pins these for its basis kernels,
+    tests/test_local_basis.py:40-68) through the per-span polynomial table: the stand-alone basis
+    operators with scratch and the tensor-core layer kernels; inputs include every knot exactly
+    and out-of-range points."""
+    I, O = 32, 64
+    grid64 = _knots_with_zero_spans(I, G, k, kind, seed=G + k)
+    grid = grid64.float().cuda()
+    g = torch.Generator().manual_seed(7)
+    lo, hi = grid64[:, 0].min().item(), grid64[:, -1].max().item()
+    x = torch.rand(4096, I, generator=g, dtype=torch.float64) * 1.4 * (hi - lo) + lo - 0.2 * (hi - lo)
+    x = torch.cat([x, grid.double().cpu().t()], 0).float().cuda()          # + every (float32) knot exactly
+    N = x.shape[0]
+    H = _C.basis(x, grid, k)
+    H64 = db.compute_basis(x.double(), grid.double(), k)
+    assert _err(H, H64) < 2e-6
+    gH = torch.randn(N, I, G + k, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    gx = _C.basis_grad(x, grid, k, gH)
+    gx64 = (gH.double() * db.compute_basis_derivative(x.double(), grid.double(), k)).sum(-1)
+    assert _err(gx, gx64) < 1e-5
+    torch.manual_seed(3)
+    bw = torch.randn(O, I, device="cuda") / math.sqrt(I)
+    sw = torch.randn(O, I, G + k, device="cuda") * 0.3
+    sc = torch.rand(O, I, device="cuda") + 0.5
+    y = _native.forward(x, grid, bw, sw, sc, k, _native.MODE_TC_BF16X3)
+    dY = torch.randn(N, O, device="cuda", generator=torch.Generator(device="cuda").manual_seed(2))
+    got = _native.backward(dY, x, grid, bw, sw, sc, k, True, True, True, True, _native.MODE_TC_BF16X3)
+    y64, gx64, (gb64, gs64, gc64) = _dense64_layer_step(x, grid, bw, sw, sc, k, dY)
+    errs = {"y": _err(y, y64), "dX": _err(got[0], gx64), "d base_weight": _err(got[1], gb64),
+            "d spline_weight": _err(got[2], gs64), "d spline_scaler": _err(got[3], gc64)}
+    _native.check_all_workspaces()
+    assert all(e < TOL32 for e in errs.values()), errs
+
+
+def test_empty_batch_through_the_layer():
+    """A batch of zero rows gives an empty output and zero parameter gradients (the reference returns
+    early for B == 0, csrc/kan_cuda.cu:469-532)."""
+    L = sk.KANLinear(16, 8, backend="cuda").cuda()
+    x = torch.zeros(0, 16, device="cuda", requires_grad=True)
+    y = L(x)
+    assert y.shape == (0, 8)
+    y.sum().backward()
+    assert x.grad.shape == (0, 16)
+    for p in L.parameters():
+        assert p.grad is not None and float(p.grad.abs().sum()) == 0.0
+
+
+def test_status_word_is_sticky_across_calls():
+    """A status word set by an earlier kernel survives later calls on the same scratch buffer and
+    is raised by the next call or by check_status (it used to be cleared by every call)."""
+    L = sk.KANLinear(64, 64, backend="cuda").cuda()
+    x = torch.rand(512, 64, device="cuda") * 2 - 1
+    L(x)
+    _C.check_status()
+    _C._poke_status(0, 1)                       # forward scratch of the current stream: "a wait ran out"
+    L(x)                                        # runs (the word is mirrored to the host after the call) ...
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bounded wait|gave up"):
+        L(x)                                    # ... and the next call on that buffer reports it
+    _C.check_status()                           # cleared by the report
+    L(x)
+    _C.check_status()
+
+
+def test_prefetcher_never_overwrites_a_batch_that_is_still_read():
+    """submit() of batch t+1 comes before next() of batch t, as in the documented loop; a slow
+    consumer of batch t-1 (a long chain of matmuls queued behind a read of the buffer) must still
+    see its own batch."""
+    shape = (2048, 1024)
+    pre = sk.HostBatchPrefetcher(shape, torch.float32, torch.device("cuda"))
+    batches = [torch.full(shape, float(i)).pin_memory() for i in range(6)]
+    big = torch.randn(4096, 4096, device="cuda")
+    sums = []
+    pre.submit(batches[0])
+    for t in range(6):
+        if t + 1 < 6:
+            pre.submit(batches[t + 1])
+        xb = pre.next()
+        acc = big
+        for _ in range(12):                     # tens of milliseconds of work queued BEFORE the read
+            acc = acc @ big * 1e-3
+        sums.append(xb.sum() + 0.0 * acc[0, 0].nan_to_num())
+    torch.cuda.synchronize()
+    for t, s in enumerate(sums):
+        assert float(s) == float(t) * shape[0] * shape[1], (t, float(s))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.float64, 1e-9)])
+def test_update_grid_with_fewer_samples_than_coefficients(dtype, tol):
+    """update_grid on 4 samples with 8 coefficients per edge: the wide least-squares systems take
+    the minimum-norm solution on the GPU path as on the CPU path."""
+    torch.manual_seed(0)
+    a = sk.KANLinear(6, 5, backend="reference").to(dtype)
+    b = sk.KANLinear(6, 5, backend="reference").to("cuda", dtype)
+    b.load_state_dict(a.state_dict())
+    x = torch.rand(4, 6, dtype=dtype) * 2 - 1
+    a.update_grid(x)
+    b.update_grid(x.cuda())
+    assert _err(b.grid, a.grid) < 1e-6
+    assert _err(b.spline_weight, a.spline_weight) < tol

@@ -347,6 +347,12 @@ def check_status(ws: Optional[torch.Tensor]) -> None:
         _check(lib().kanb200_check_status(_p(ws), _stream(ws.device)))
 
 
+def check_all_workspaces() -> None:
+    """:func:`check_status` on every scratch buffer this module handed out."""
+    for buf in list(_ws_cache.values()):
+        check_status(buf)
+
+
 # ---------------------------------------------------------------------------
 # gradient all-reduce over symmetric memory
 # ---------------------------------------------------------------------------

@@ -1,6 +1,7 @@
-// Device-side building blocks shared by every kernel of the KANLinear path:
-// knot-span search, the k+1 non-zero B-spline values (and derivatives) of one
-// input, SiLU and its derivative.
+// Device-side building blocks of the gather (FMA-pipe) kernels: knot-span search, the k+1 non-zero
+// B-spline values (and derivatives) of one input evaluated in registers, SiLU and its derivative.
+// (The tensor-core kernels and the table-driven basis kernels evaluate the same functions from the
+// per-span polynomial table of kan_table.cuh instead.)
 //
 // Conventions (identical to the dense Cox-de Boor recurrence of the reference,
 // spline_kan/reference_backend.py:69-94):
@@ -17,77 +18,82 @@ namespace kanb200 {
 constexpr int kMaxOrder = 3;
 constexpr int kMaxKnots = 72;          // G + 2k + 1 <= 72  (G + 2k <= 71)
 
-// Index m in [0, nk-2] of the knot span that holds x, or -1 when x lies
-// outside the knot range (or is NaN).  x == t[nk-1] belongs to the last span.
+// Knot span of x: the largest m <= nk - 2 with t[m] <= x (so repeated knots select the span that
+// follows them, and x == t[nk-1] falls into the closed last span), or -1 when x lies outside
+// [t[0], t[nk-1]] or is NaN.  Descends over power-of-two strides: seven probes cover 72 knots, no
+// data-dependent loop count.
 template <typename T>
-__device__ __forceinline__ int find_span(const T* __restrict__ t, int nk, T x) {
-    if (!(x >= t[0]) || !(x <= t[nk - 1])) return -1;
-    if (x == t[nk - 1]) return nk - 2;
-    int lo = 0, hi = nk - 1;           // t[lo] <= x < t[hi]
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (t[mid] <= x) lo = mid; else hi = mid;
+__host__ __device__ __forceinline__ int locate_span(const T* __restrict__ t, int nk, T x) {
+    if (!(x >= t[0] && x <= t[nk - 1])) return -1;
+    int m = 0;
+#pragma unroll
+    for (int stride = 64; stride > 0; stride >>= 1) {
+        const int probe = m + stride;
+        if (probe <= nk - 2 && t[probe] <= x) m = probe;
     }
-    return lo;
+    return m;
 }
 
-// Quotient used inside the recurrence: IEEE division for double, the 2-ulp reciprocal-multiply
-// for float (the float kernels are compared at 1e-5, the double ones at 1e-12).
-template <typename T> __device__ __forceinline__ T ratio(T a, T b) { return a / b; }
-template <> __device__ __forceinline__ float ratio<float>(float a, float b) { return __fdividef(a, b); }
+// b / den with the "0 / 0 = 0" rule of the recurrence folded in by the caller.  IEEE division for
+// double; for float the 2-ulp fast division (the float kernels are compared at 1e-5, the double
+// ones at 1e-12).
+template <typename T> __host__ __device__ __forceinline__ T quotient(T b, T den) { return b / den; }
+template <> __host__ __device__ __forceinline__ float quotient<float>(float b, float den) {
+#ifdef __CUDA_ARCH__
+    return __fdividef(b, den);
+#else
+    return b / den;
+#endif
+}
 
-// The K+1 basis functions that can be non-zero on span m are B_{m-K+j,K},
-// j = 0..K.  val[j] receives their values at x; with DERIV, der[j] receives
-// d/dx.  Built bottom-up over the degree (triangular de Boor table); knot
-// reads beyond either end are clamped -- they only feed table entries that do
-// not correspond to a real basis function and are dropped by the caller.
+// Values (and, with DERIV, x-derivatives) of the K + 1 B-splines of degree K that can be non-zero
+// on span m: window slot j stands for basis index m - K + j.
+//
+// Degree by degree, the functions of degree d - 1 are first divided by the knot difference their
+// support spans,
+//        q_j = B_{m-d+1+j, d-1} / (t_{m+1+j} - t_{m+1+j-d}),        j = 0 .. d-1   (0 where the knots coincide)
+// which is the one quantity both terms of the Cox-de Boor step share:
+//        B_{m-d+j, d} = (x - t_{m-d+j}) q_{j-1} + (t_{m+1+j} - x) q_j.
+// At the last degree the same q give the derivative for free:
+//        d/dx B_{m-K+j, K} = K (q_{j-1} - q_j).
+// Knot reads beyond either end of the vector are clamped; they only reach slots whose basis
+// index lies outside [0, R), which the caller drops.
 template <int K, typename T, bool DERIV>
-__device__ __forceinline__ void local_basis(const T* __restrict__ t, int nk, int m, T x,
-                                            T (&val)[K + 1], T (&der)[K + 1]) {
-    auto knot = [&](int idx) -> T {
-        idx = idx < 0 ? 0 : (idx > nk - 1 ? nk - 1 : idx);
-        return t[idx];
-    };
-    T tk[2 * K];                        // t[m-K+1 .. m+K]
+__host__ __device__ __forceinline__ void window_values(const T* __restrict__ t, int nk, int m, T x,
+                                              T (&val)[K + 1], T (&der)[K + 1]) {
+    T kn[2 * K];                        // kn[K - 1 + e] = t[m + e],  e = 1-K .. K
 #pragma unroll
-    for (int q = 0; q < 2 * K; ++q) tk[q] = knot(m - K + 1 + q);
-    // tk index of knot t[m + d] is (K - 1 + d).
-    T nd[K + 1];
-    nd[0] = T(1);
+    for (int e = 0; e < 2 * K; ++e) {
+        int at = m - K + 1 + e;
+        at = at < 0 ? 0 : (at > nk - 1 ? nk - 1 : at);
+        kn[e] = t[at];
+    }
+    T b[K + 1];
+    b[0] = T(1);
 #pragma unroll
-    for (int j = 1; j <= K; ++j) nd[j] = T(0);
+    for (int j = 1; j <= K; ++j) b[j] = T(0);
 #pragma unroll
     for (int d = 1; d <= K; ++d) {
-        if (DERIV && d == K) {
-            // nd[0..K-1] hold the degree K-1 values B_{m-K+1+j, K-1}.
-#pragma unroll
-            for (int j = 0; j <= K; ++j) {
-                T a = T(0), b = T(0);
-                if (j >= 1) {           // B_{r,K-1}/(t_{r+K}-t_r), r = m-K+j
-                    const T den = tk[K - 1 + j] - tk[j - 1];
-                    if (den != T(0)) a = ratio<T>(nd[j - 1], den);
-                }
-                if (j <= K - 1) {       // B_{r+1,K-1}/(t_{r+K+1}-t_{r+1})
-                    const T den = tk[K + j] - tk[j];
-                    if (den != T(0)) b = ratio<T>(nd[j], den);
-                }
-                der[j] = T(K) * (a - b);
-            }
-        }
-        T carry = T(0);
+        T q[K + 1];
 #pragma unroll
         for (int j = 0; j < d; ++j) {
-            const T hi_k = tk[K + j];               // t[m + j + 1]
-            const T lo_k = tk[K - d + j];           // t[m + 1 - d + j]
-            const T den = hi_k - lo_k;
-            const T w = (den != T(0)) ? ratio<T>(nd[j], den) : T(0);
-            nd[j] = carry + (hi_k - x) * w;
-            carry = (x - lo_k) * w;
+            const T width = kn[K + j] - kn[K + j - d];
+            q[j] = (width != T(0)) ? quotient<T>(b[j], width) : T(0);
         }
-        nd[d] = carry;
+        if (DERIV && d == K) {
+#pragma unroll
+            for (int j = 0; j <= K; ++j)
+                der[j] = T(K) * ((j > 0 ? q[j - 1] : T(0)) - (j < K ? q[j] : T(0)));
+        }
+#pragma unroll
+        for (int j = d; j >= 0; --j) {
+            const T rising = (j > 0) ? (x - kn[K - 1 - d + j]) * q[j - 1] : T(0);
+            const T falling = (j < d) ? (kn[K + j] - x) * q[j] : T(0);
+            b[j] = rising + falling;
+        }
     }
 #pragma unroll
-    for (int j = 0; j <= K; ++j) val[j] = nd[j];
+    for (int j = 0; j <= K; ++j) val[j] = b[j];
 }
 
 // Places the K+1 local values of span m into a window of K+1 consecutive basis

@@ -88,8 +88,38 @@ umma_layout_kernel(const uint8_t* __restrict__ a_img, const uint8_t* __restrict_
         tmem_dealloc(tmem_base, 512);
     }
 }
+// Register-only FMA loop for measuring the FP32 / FP64 FMA-pipe peaks the gather kernels are
+// compared with: every thread runs `iters` rounds of 16 independent dependent-chain FMAs.
+template <typename T>
+__global__ void __launch_bounds__(256) fma_loop_kernel(T* __restrict__ out, int iters, T a, T b) {
+    T v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = T(threadIdx.x + j) * T(1e-3);
+#pragma unroll 1
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = fma(v[j], a, b);
+    }
+    T s = T(0);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) s += v[j];
+    out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
 }  // namespace
 }  // namespace kanb200
+
+// Launches blocks x 256 threads of the FMA loop (dtype 0 = float, 1 = double); the caller times it
+// with events.  FMAs executed: blocks * 256 * iters * 16.  `out` holds blocks * 256 elements.
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_fma_loop(int dtype, int blocks, int iters, void* out, void* stream) {
+    using namespace kanb200;
+    if (blocks < 1 || blocks > 65535 || iters < 1 || !out) return -1;
+    if (dtype == 0)
+        fma_loop_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)out, iters, 0.999f, 1e-3f);
+    else
+        fma_loop_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>((double*)out, iters, 0.999, 1e-3);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 extern "C" __attribute__((visibility("default")))
 int kanb200_selftest_umma_layout(int layout, const void* a_img, const void* b_img, float* D, int* status,

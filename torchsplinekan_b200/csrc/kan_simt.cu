@@ -34,10 +34,10 @@ __global__ void basis_kernel(const T* __restrict__ x, const T* __restrict__ grid
             const int i = (int)(idx % I);
             const T* t = grid + (size_t)i * nk;
             const T xv = x[idx];
-            const int m = find_span(t, nk, xv);
+            const int m = locate_span(t, nk, xv);
             if (m >= 0) {
                 T v[K + 1], d[K + 1];
-                local_basis<K, T, false>(t, nk, m, xv, v, d);
+                window_values<K, T, false>(t, nk, m, xv, v, d);
 #pragma unroll
                 for (int j = 0; j <= K; ++j) {
                     const int r = m - K + j;
@@ -72,10 +72,10 @@ basis_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid, flo
             const int i = (int)(idx % I);
             const float* t = grid + (size_t)i * nk;           // knot rows stay in L1
             const float xv = x[idx];
-            const int m = find_span<float>(t, nk, xv);
+            const int m = locate_span(t, nk, xv);
             if (m >= 0) {
                 float w[K + 1], d[K + 1];
-                local_basis<K, float, false>(t, nk, m, xv, w, d);
+                window_values<K, float, false>(t, nk, m, xv, w, d);
                 s = m - K;
 #pragma unroll
                 for (int j = 0; j <= K; ++j) v[j] = w[j];
@@ -121,11 +121,11 @@ basis_grad_r8_kernel(const float* __restrict__ x, const float* __restrict__ grid
         const float4 b = __ldg(reinterpret_cast<const float4*>(gH + idx * 8) + 1);
         const float g[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
         const float xv = x[idx];
-        const int m = find_span<float>(t, nk, xv);
+        const int m = locate_span(t, nk, xv);
         float acc = 0.f;
         if (m >= 0) {
             float v[K + 1], d[K + 1];
-            local_basis<K, float, true>(t, nk, m, xv, v, d);
+            window_values<K, float, true>(t, nk, m, xv, v, d);
 #pragma unroll
             for (int j = 0; j <= K; ++j) {
                 const int r = m - K + j;
@@ -331,11 +331,11 @@ __global__ void basis_grad_kernel(const T* __restrict__ x, const T* __restrict__
         const int i = (int)(idx % I);
         const T* t = grid + (size_t)i * nk;
         const T xv = x[idx];
-        const int m = find_span(t, nk, xv);
+        const int m = locate_span(t, nk, xv);
         T acc = T(0);
         if (m >= 0) {
             T v[K + 1], d[K + 1];
-            local_basis<K, T, true>(t, nk, m, xv, v, d);
+            window_values<K, T, true>(t, nk, m, xv, v, d);
             const T* g = gH + idx * R;
 #pragma unroll
             for (int j = 0; j <= K; ++j) {
@@ -422,10 +422,10 @@ fwd_simt_kernel(const T* __restrict__ x, const T* __restrict__ grid, const T* __
             if (n0 + n < N) {
                 const T xv = x[(size_t)(n0 + n) * I + (i0 + i)];
                 const T* t = knots + (size_t)i * nk;
-                const int m = find_span(t, nk, xv);
+                const int m = locate_span(t, nk, xv);
                 if (m >= 0) {
                     T v[K + 1], d[K + 1];
-                    local_basis<K, T, false>(t, nk, m, xv, v, d);
+                    window_values<K, T, false>(t, nk, m, xv, v, d);
                     s = window_in_range<K, T>(m, R, v, w);
                 }
                 sv = bw ? silu_t<T>(xv) : T(0);
@@ -509,10 +509,10 @@ bwd_param_simt_kernel(const T* __restrict__ dY, const T* __restrict__ x, const T
             for (int r = 0; r < RS; ++r) row[r] = T(0);
             if (nt + n < ne && i0 + i < I) {
                 const T xv = x[(size_t)(nt + n) * I + i0 + i];
-                const int m = find_span(&knots[i][0], nk, xv);
+                const int m = locate_span(&knots[i][0], nk, xv);
                 if (m >= 0) {
                     T v[K + 1], d[K + 1];
-                    local_basis<K, T, false>(&knots[i][0], nk, m, xv, v, d);
+                    window_values<K, T, false>(&knots[i][0], nk, m, xv, v, d);
 #pragma unroll
                     for (int j = 0; j <= K; ++j) {
                         const int r = m - K + j;
@@ -618,10 +618,10 @@ bwd_input_simt_kernel(const T* __restrict__ dY, const T* __restrict__ x, const T
     if (live) {
         const T xv = x[(size_t)n * I + i];
         const T* t = knots + (size_t)ti * nk;
-        const int m = find_span(t, nk, xv);
+        const int m = locate_span(t, nk, xv);
         if (m >= 0) {
             T v[K + 1], d[K + 1];
-            local_basis<K, T, true>(t, nk, m, xv, v, d);
+            window_values<K, T, true>(t, nk, m, xv, v, d);
             s = window_in_range<K, T>(m, R, d, dw);
         }
         if (bw) sg = silu_grad_t<T>(xv);
@@ -822,10 +822,10 @@ fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ grid, const T* __
             if (n0 + n < N) {
                 const T xv = x[(size_t)(n0 + n) * I + (i0 + i)];
                 const T* t = grid + (size_t)(i0 + i) * nk;
-                const int m = find_span(t, nk, xv);
+                const int m = locate_span(t, nk, xv);
                 if (m >= 0) {
                     T v[K + 1], d[K + 1];
-                    local_basis<K, T, false>(t, nk, m, xv, v, d);
+                    window_values<K, T, false>(t, nk, m, xv, v, d);
                     s = window_in_range<K, T>(m, R, v, w);
                 }
                 sv = bw ? silu_t<T>(xv) : T(0);

@@ -422,8 +422,10 @@ class HostBatchPrefetcher:
             x = pre.next()
             loss = step(x)
 
-    A buffer is reused only after the step that consumed it has finished on the compute stream
-    (an event recorded by the following ``next()``).
+    A staging buffer is overwritten only after everything that was queued on the compute stream
+    before the ``submit`` that reuses it has finished: ``submit`` records an event there and the copy
+    stream waits for it.  The last reader of the buffer (the step two batches back) was queued before
+    that point, however long it runs.
     """
 
     def __init__(self, shape, dtype: torch.dtype, device: torch.device) -> None:
@@ -433,7 +435,7 @@ class HostBatchPrefetcher:
         self.stream = torch.cuda.Stream(self.device)
         self._bufs = [torch.empty(shape, dtype=dtype, device=self.device) for _ in range(2)]
         self._ready = [torch.cuda.Event(), torch.cuda.Event()]
-        self._released = [None, None]
+        self._handed_out = [False, False]
         self._submitted = 0
         self._taken = 0
 
@@ -444,9 +446,13 @@ class HostBatchPrefetcher:
             raise ValueError(f"batch of shape {tuple(host_batch.shape)} / {host_batch.dtype} does not match the "
                              f"staging buffers {tuple(self._bufs[0].shape)} / {self._bufs[0].dtype}")
         i = self._submitted % 2
+        if self._handed_out[i]:
+            # the buffer's previous batch was given to the caller: its readers are on the compute
+            # stream, queued before this point
+            consumed = torch.cuda.Event()
+            consumed.record(torch.cuda.current_stream(self.device))
+            self.stream.wait_event(consumed)
         with torch.cuda.stream(self.stream):
-            if self._released[i] is not None:
-                self.stream.wait_event(self._released[i])
             self._bufs[i].copy_(host_batch, non_blocking=True)
             self._ready[i].record(self.stream)
         self._submitted += 1
@@ -454,14 +460,8 @@ class HostBatchPrefetcher:
     def next(self) -> torch.Tensor:
         if self._taken >= self._submitted:
             raise RuntimeError("next() without a submitted batch")
-        cur = torch.cuda.current_stream(self.device)
-        if self._taken > 0:
-            # everything queued so far on the compute stream used the previous buffer
-            j = (self._taken - 1) % 2
-            ev = torch.cuda.Event()
-            ev.record(cur)
-            self._released[j] = ev
         i = self._taken % 2
-        cur.wait_event(self._ready[i])
+        torch.cuda.current_stream(self.device).wait_event(self._ready[i])
+        self._handed_out[i] = True
         self._taken += 1
         return self._bufs[i]
