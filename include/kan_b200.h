@@ -58,6 +58,8 @@ extern "C" {
 #define KANB200_OP_EDGE_FWD 2
 #define KANB200_OP_EDGE_BWD 3
 #define KANB200_OP_BASIS    4  /* kanb200_basis_ws / kanb200_basis_grad_ws (O is ignored) */
+#define KANB200_OP_EDGE_X_FWD 5 /* kanb200_edge_abs_mean_x */
+#define KANB200_OP_EDGE_X_BWD 6 /* kanb200_edge_abs_mean_x_backward */
 
 KANB200_API const char* kanb200_last_error(void);
 KANB200_API int kanb200_version(void);
@@ -148,6 +150,20 @@ KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, c
 KANB200_API int kanb200_edge_abs_mean_noalloc(int dtype, const void* s, const void* H, const void* bw,
                                               const void* W, void* a,
                                               int64_t N, int64_t I, int64_t O, int R, void* stream);
+
+/* The same statistic evaluated straight from the layer input, the basis never stored:
+ *     a[o,i] = mean_n | s[n,i] bw[o,i] + sum_r B_r(x[n,i]) W[o,i,r] |
+ * with s = silu(x) when s is NULL (and bw given), or the caller's base values s [N,I] (layers with
+ * another base activation); bw NULL = no base term.  W [O,I,R] is the effective coefficient
+ * tensor (spline_weight * spline_scaler).  Replaces the pair kan_basis_cuda + edge_abs_mean_cuda
+ * of the reference's forward_with_regularization (spline_kan/kan_linear.py:381-416,
+ * csrc/kan_reg_cuda.cu:263-280) without the [N,I,R] intermediate.  float32 with G + k <= 8 runs
+ * on the tensor cores (one K = 16 MMA step per feature, |phi| summed from tensor memory); other
+ * shapes and float64 run on the FMA pipes.  mode as for kanb200_forward. */
+KANB200_API int kanb200_edge_abs_mean_x(int dtype, int mode, const void* x, const void* s, const void* grid,
+                                        const void* bw, const void* W, void* a,
+                                        int64_t N, int64_t I, int64_t O, int G, int k,
+                                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* Gradients of kanb200_edge_abs_mean; NULL output = not needed
  * (edge_abs_mean_backward_cuda, csrc/kan_reg_cuda.cu:284-312). */

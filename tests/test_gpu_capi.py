@@ -437,3 +437,32 @@ def test_allreduce_kernel_ranges_small_blocks_emulated_ranks():
     assert torch.equal(buf[:, :n], want)
     with pytest.raises(RuntimeError, match="between 1 and 4 ranges"):
         nat.allreduce_sum_ranges(ptrs, 0, ranges + ranges, pad_off, 0, world, status, local_ranks=world)
+
+
+# ---------------------------------------------------------------------------
+# edge statistic straight from x (tensor cores)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("N,I,O,G,k,base,custom_s", [
+    (4096, 64, 256, 5, 3, True, False), (1000, 37, 130, 5, 3, True, False), (2048, 16, 64, 4, 2, False, False),
+    (3000, 24, 300, 5, 3, True, True), (512, 8, 16, 7, 1, True, False)])
+def test_edge_abs_mean_from_x_tensor_cores(N, I, O, G, k, base, custom_s):
+    """a[o,i] from x (basis never stored) against the float64 dense evaluation; non-uniform knots,
+    a share of inputs exactly on knots and outside the knot range, ragged tiles."""
+    case = make_layer_case(N, I, O, G, k, np.float32, seed=N + I, nonuniform=True, base=base)
+    x, grid = dev(case["x"]), dev(case["grid"])
+    W = dev(case["sw"] * case["sc"][:, :, None])
+    bw = dev(case["bw"]) if base else None
+    s = torch.tanh(x) if custom_s else None
+    a = nat.edge_abs_mean_x(x, s, grid, bw, W, k, nat.MODE_TC_BF16X3)
+    torch.cuda.synchronize()
+    for key, buf in list(nat._ws_cache.items()):
+        if key[2] == "edge_x":
+            nat.check_status(buf)
+    x64 = case["x"].astype(np.float64)
+    H = ko.compute_basis(x64, case["grid"].astype(np.float64), k)
+    phi = np.einsum("nir,oir->noi", H, (case["sw"] * case["sc"][:, :, None]).astype(np.float64))
+    if base:
+        sv = np.tanh(x64) if custom_s else x64 / (1.0 + np.exp(-x64))
+        phi = phi + sv[:, None, :] * case["bw"].astype(np.float64)[None]
+    want = np.abs(phi).mean(0)
+    assert rel_err(a.cpu().numpy(), want) < TOL32

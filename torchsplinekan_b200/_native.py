@@ -19,7 +19,7 @@ from .build import LIB_PATH
 F32, F64 = 0, 1
 MODE_AUTO, MODE_SIMT, MODE_TC_BF16X3, MODE_TC_BF16X1 = 0, 1, 2, 3
 MODES = {"auto": MODE_AUTO, "simt": MODE_SIMT, "bf16x3": MODE_TC_BF16X3, "bf16x1": MODE_TC_BF16X1}
-OP_FORWARD, OP_BACKWARD, OP_EDGE_FWD, OP_EDGE_BWD, OP_BASIS = 0, 1, 2, 3, 4
+OP_FORWARD, OP_BACKWARD, OP_EDGE_FWD, OP_EDGE_BWD, OP_BASIS, OP_EDGE_X_FWD, OP_EDGE_X_BWD = 0, 1, 2, 3, 4, 5, 6
 EINVAL, EUNSUPPORTED, EWORKSPACE, ECUDA, EDEVICE = -1, -2, -3, -4, -5
 MAX_DEG0_BASIS = 71
 MAX_IN_FEATURES = 65535
@@ -49,6 +49,8 @@ SIGNATURES = {
                                                                        _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                    _c_void_p, _c_size, _c_void_p]),
+    "kanb200_edge_abs_mean_x": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
+                                                                             _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
     "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                             _c_void_p, _c_size, _c_void_p]),
@@ -318,6 +320,20 @@ def edge_abs_mean(s, H, bw, W) -> torch.Tensor:
         ws = workspace(dev, nb, "edge")
         _check(lib().kanb200_edge_abs_mean(_code(H.dtype), _p(s), _p(H), _p(bw), _p(W), _p(a), N, I, O, R,
                                            _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+    return a
+
+
+def edge_abs_mean_x(x, s, grid, bw, W, k: int, mode: int = MODE_AUTO) -> torch.Tensor:
+    """``a [O, I]`` straight from the layer input ``x`` (``s``: base values or None = SiLU of x)."""
+    dev = _need_cuda(x, grid, W)
+    N, I = x.shape
+    O = W.shape[0]
+    G = grid.shape[1] - 2 * k - 1
+    a = torch.empty((O, I), dtype=x.dtype, device=dev)
+    with _OnDevice(dev):
+        ws = workspace(dev, workspace_bytes(OP_EDGE_X_FWD, mode, x.dtype, N, I, O, G, k), "edge_x")
+        _check(lib().kanb200_edge_abs_mean_x(_code(x.dtype), mode, _p(x), _p(s), _p(grid), _p(bw), _p(W), _p(a),
+                                             N, I, O, G, k, _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return a
 
 

@@ -44,6 +44,13 @@ bool make_shape(int64_t N, int64_t I, int64_t O, int G, int k, LayerShape& s) {
     return true;
 }
 
+// Whether the from-x edge statistic takes the tensor-core kernel for this problem.
+bool edge_x_uses_tc(int mode, int dtype, const LayerShape& s) {
+    if (dtype != KANB200_F32 || mode == KANB200_MODE_SIMT || !tc_edge_supported(s)) return false;
+    if (mode == KANB200_MODE_AUTO) return s.N >= 256 && s.O >= 16;
+    return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -101,6 +108,11 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
     if (op == KANB200_OP_BASIS) {
         // the table-driven basis kernels; 0 = the recurrence kernels run and need nothing
         return dtype == KANB200_F32 && basis_table_supported(s) ? kWsHeader + tc_table_bytes(s) : 0;
+    }
+    if (op == KANB200_OP_EDGE_X_FWD) {
+        if (N < 1) return 0;
+        if (edge_x_uses_tc(mode, dtype, s)) return tc_edge_workspace(s);
+        return 0;
     }
     if (op == KANB200_OP_EDGE_FWD || op == KANB200_OP_EDGE_BWD) {
         const bool b = op == KANB200_OP_EDGE_BWD;
@@ -318,6 +330,30 @@ KANB200_API int kanb200_edge_abs_mean(int dtype, const void* s, const void* H, c
                                                     ws_body(workspace, workspace_bytes),
                                                     ws_body_bytes(workspace, workspace_bytes), st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean");
+}
+
+KANB200_API int kanb200_edge_abs_mean_x(int dtype, int mode, const void* x, const void* s_val, const void* grid,
+                                        const void* bw, const void* W, void* a,
+                                        int64_t N, int64_t I, int64_t O, int G, int k,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = kanb200_check_shapes(N, I, O, G, k, dtype);
+    if (rc) return rc;
+    if (N < 1) return fail(KANB200_EINVAL, "edge_abs_mean: need at least one sample");
+    if (!x || !grid || !W || !a) return fail(KANB200_EINVAL, "edge_abs_mean_x: NULL pointer");
+    if (s_val && !bw) return fail(KANB200_EINVAL, "edge_abs_mean_x: base values given without base_weight");
+    if (mode < KANB200_MODE_AUTO || mode > KANB200_MODE_TC_BF16X1) return fail(KANB200_EINVAL, "unknown mode %d", mode);
+    LayerShape s;
+    make_shape(N, I, O, G, k, s);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (edge_x_uses_tc(mode, dtype, s)) {
+        cudaError_t e = tc_edge_forward(mode == KANB200_MODE_TC_BF16X1 ? 1 : 3, (const float*)x, (const float*)s_val,
+                                        (const float*)grid, (const float*)bw, (const float*)W, (float*)a, s,
+                                        workspace, workspace_bytes, st);
+        return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x");
+    }
+    if (mode == KANB200_MODE_TC_BF16X3 || mode == KANB200_MODE_TC_BF16X1)
+        return fail(KANB200_EUNSUPPORTED, "edge_abs_mean_x: tensor-core modes need float32 and G + k <= 8");
+    return fail(KANB200_EUNSUPPORTED, "edge_abs_mean_x: this shape runs through kanb200_basis + kanb200_edge_abs_mean");
 }
 
 KANB200_API int kanb200_edge_abs_mean_noalloc(int dtype, const void* s, const void* H, const void* bw,

@@ -79,6 +79,14 @@ size_t tc_table_bytes(const LayerShape& s);
 int tc_table_stride(const LayerShape& s);
 cudaError_t tc_build_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st);
 
+// Edge statistic straight from x on the tensor cores (kan_tc_edge.cu): float32, G + k <= 8.
+// W is the effective coefficient tensor (scaler applied); s_val, when not NULL, replaces silu(x).
+bool tc_edge_supported(const LayerShape& s);
+size_t tc_edge_workspace(const LayerShape& s);
+cudaError_t tc_edge_forward(int split_terms, const float* x, const float* s_val, const float* grid, const float* bw,
+                            const float* W, float* a, const LayerShape& s, void* ws, size_t ws_bytes,
+                            cudaStream_t st);
+
 // Gradient all-reduce over symmetric memory (kan_collective.cu).
 size_t allreduce_pad_bytes(int world, int blocks);
 void allreduce_set_wait_limit_ms(unsigned ms);

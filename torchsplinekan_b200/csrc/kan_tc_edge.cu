@@ -1,0 +1,470 @@
+// Edge statistic of the activation regulariser on the tensor cores, straight from x:
+//
+//     a[o, i] = (1/N) sum_n | s(x[n,i]) bw[o,i] + sum_r B_r(x[n,i]) W[o,i,r] |
+//
+// For ONE input feature the inner expression is a small matrix product
+//     phi_i [outputs, samples] = Wop_i [outputs, 16] . Aop_i [samples, 16]^T
+// whose 16 columns are the feature's 8 spline slots, its base value s(x) and 7 zeros: exactly one
+// K = 16 step of tcgen05.mma.  The sample-side operand is evaluated from x by producer warps (the
+// same window evaluation and hi/lo bf16 split as the layer kernels, three MMAs per product), the
+// weight-side operand is a pre-swizzled image fetched by one bulk copy per work item, phi lands in
+// tensor memory with OUTPUTS on the lanes and SAMPLES on the columns, and the epilogue warps add up
+// |phi| along their own row: no shuffles, no atomics, phi and the basis are never stored.
+//
+// Work item = (group of 4 features, pair of 128-output tiles, range of samples).  Per 256-sample
+// tile the producers write one operand tile (256 rows x 4 features x 16 slots), the MMA thread
+// issues 4 features x 2 output tiles x 3 terms MMAs into two alternating 256-column accumulators,
+// and the epilogue threads keep one running sum per (output row, feature, output tile).  Partial
+// sums go to per-(sample range, column half) slabs that a second kernel adds in a fixed order.
+//
+// Limits: float32, G + k <= 8 (one 8-slot chunk per feature).  Every wait is bounded.
+#include "kan_tc_common.cuh"
+
+namespace kanb200 {
+
+namespace {
+
+constexpr int EDGE_PRODUCER_WARPS = 8, EDGE_EPILOGUE_WARPS = 8;
+constexpr int EDGE_PRODUCERS = EDGE_PRODUCER_WARPS * 32;          // one sample row each
+constexpr int EDGE_EPILOGUE = EDGE_EPILOGUE_WARPS * 32;           // 128 rows x 2 column halves
+constexpr int EDGE_MMA_WARP = EDGE_PRODUCER_WARPS + EDGE_EPILOGUE_WARPS;
+constexpr int EDGE_THREADS = (EDGE_MMA_WARP + 2) * 32;
+constexpr int EDGE_TN = 256;                                      // samples per tile = accumulator columns
+constexpr int EDGE_FQ = 4;                                        // features per operand tile (4 x 16 slots = 128 B)
+constexpr int EDGE_OT = 128;                                      // outputs per tile = accumulator rows
+constexpr int EDGE_MAX_OTILES = 2;                                // output tiles per work item
+
+constexpr uint32_t EDGE_A_TILE = EDGE_TN * 128;                   // 32 KB: 256 samples x 128 B
+constexpr uint32_t EDGE_A_STAGE = 2 * EDGE_A_TILE;                // hi + lo
+constexpr int EDGE_A_STAGES = 2;
+constexpr uint32_t EDGE_W_TILE = EDGE_OT * 128;                   // 16 KB: 128 outputs x 128 B
+constexpr uint32_t EDGE_W_SLOT = 2 * EDGE_W_TILE;                 // hi + lo of one output tile
+constexpr uint32_t EDGE_SMEM_A = 0;
+constexpr uint32_t EDGE_SMEM_W = EDGE_SMEM_A + EDGE_A_STAGES * EDGE_A_STAGE;
+constexpr uint32_t EDGE_SMEM_CTRL = EDGE_SMEM_W + EDGE_MAX_OTILES * EDGE_W_SLOT;
+constexpr uint32_t EDGE_SMEM_BYTES = EDGE_SMEM_CTRL + 256 + TAB_SMEM_FLOATS * 4;
+static_assert(EDGE_SMEM_BYTES <= 232448, "edge kernel shared memory exceeds 227 KB");
+
+struct EdgeCtrl {
+    uint64_t fullA[EDGE_A_STAGES], emptyA[EDGE_A_STAGES];
+    uint64_t fullW, emptyW;
+    uint64_t accFull[2], accEmpty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(EdgeCtrl) <= 256, "control block too large");
+
+struct EdgePlanTc {
+    int n_quads;           // groups of 4 features
+    int n_otiles;          // tiles of 128 outputs
+    int n_opairs;          // work-item groups of up to 2 output tiles
+    int splits;            // sample ranges
+    int64_t tiles_total;   // 256-sample tiles
+    int64_t tiles_per_split;
+    __host__ __device__ int64_t n_items() const { return (int64_t)n_quads * n_opairs * splits; }
+    __host__ __device__ int n_slabs() const { return splits * 2; }
+};
+
+// Weight-side operand image: for every (output tile of 128, group of 4 features) a hi tile and a lo
+// tile of 16 KB each, byte-for-byte the 128-byte-swizzled K-major shared-memory operand: row =
+// output, 128 B = 4 features x [8 spline slots | base weight, 7 zeros].
+__global__ void pack_edge_weights_kernel(const float* __restrict__ W, const float* __restrict__ bw,
+                                         uint8_t* __restrict__ img, int O, int I, int R, int n_quads, int n_otiles) {
+    const int64_t chunks = (int64_t)n_otiles * n_quads * EDGE_OT * 8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int cc = (int)(idx & 7);
+        int64_t rest = idx >> 3;
+        const int rr = (int)(rest % EDGE_OT);
+        rest /= EDGE_OT;
+        const int fq = (int)(rest % n_quads);
+        const int ot = (int)(rest / n_quads);
+        const int o = ot * EDGE_OT + rr, f = fq * EDGE_FQ + (cc >> 1);
+        float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (o < O && f < I) {
+            const size_t oi = (size_t)o * I + f;
+            if ((cc & 1) == 0) {
+                for (int e = 0; e < 8; ++e)
+                    if (e < R) w[e] = W[oi * R + e];
+            } else if (bw) {
+                w[0] = bw[oi];
+            }
+        }
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split2(w[2 * e], w[2 * e + 1], h[e], l[e]);
+        uint8_t* tile = img + ((size_t)ot * n_quads + fq) * (size_t)EDGE_W_SLOT;
+        const uint32_t off = sw128_chunk_offset((uint32_t)rr, (uint32_t)cc);
+        *reinterpret_cast<uint4*>(tile + off) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(tile + EDGE_W_TILE + off) = make_uint4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+template <int NTERMS>
+__global__ void __launch_bounds__(EDGE_THREADS, 1)
+tc_edge_fwd_kernel(const float* __restrict__ x, const float* __restrict__ sbase_val, const float* __restrict__ tab,
+                   const uint8_t* __restrict__ wimg, float* __restrict__ partial, int* __restrict__ status,
+                   int64_t N, int I, int O, int has_base, EdgePlanTc plan, TabInfo ti, int vec_x) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr bool SPLIT = (NTERMS == 3);
+    const uint32_t sbase = smem_u32(smem);
+    EdgeCtrl* ctrl = reinterpret_cast<EdgeCtrl*>(smem + EDGE_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + EDGE_SMEM_CTRL + 256);
+    volatile int* abort_flag = &ctrl->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool shared_grid = grid_is_shared(tab, I, ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
+
+    if ((sbase & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < EDGE_A_STAGES; ++s) {
+            mbar_init(smem_u32(&ctrl->fullA[s]), EDGE_PRODUCERS);
+            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->fullW), 1);
+        mbar_init(smem_u32(&ctrl->emptyW), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&ctrl->accFull[s]), 1);
+            mbar_init(smem_u32(&ctrl->accEmpty[s]), EDGE_EPILOGUE);
+        }
+        ctrl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == EDGE_MMA_WARP) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const int64_t n_items = plan.n_items();
+
+    // item -> (sample range, output pair, feature group); consecutive items share the samples
+    auto decode = [&](int64_t item, int& sp, int& op, int& fq) {
+        fq = (int)(item % plan.n_quads);
+        const int64_t rest = item / plan.n_quads;
+        op = (int)(rest % plan.n_opairs);
+        sp = (int)(rest / plan.n_opairs);
+    };
+    auto tile_range = [&](int sp, int64_t& t0, int64_t& t1) {
+        t0 = (int64_t)sp * plan.tiles_per_split;
+        t1 = t0 + plan.tiles_per_split;
+        if (t1 > plan.tiles_total) t1 = plan.tiles_total;
+    };
+    auto otiles_of = [&](int op) { return (plan.n_otiles - EDGE_MAX_OTILES * op) >= EDGE_MAX_OTILES ? EDGE_MAX_OTILES : 1; };
+
+    if (warp < EDGE_PRODUCER_WARPS) {
+        // ===== producers: thread = one sample row of the tile, 4 features each =====
+        const int row = threadIdx.x;                      // 0 .. 255
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            int sp, op, fq;
+            decode(item, sp, op, fq);
+            int64_t t0, t1;
+            tile_range(sp, t0, t1);
+            const int f0 = fq * EDGE_FQ;
+            for (int64_t t = t0; t < t1; ++t, ++it) {
+                const uint32_t stage = it % EDGE_A_STAGES;
+                const uint32_t a_hi = sbase + EDGE_SMEM_A + stage * EDGE_A_STAGE;
+                const uint32_t a_lo = a_hi + EDGE_A_TILE;
+                const int64_t n = t * EDGE_TN + row;
+                const bool row_ok = n < N;
+                float xv[EDGE_FQ] = {0.f, 0.f, 0.f, 0.f}, sv[EDGE_FQ] = {0.f, 0.f, 0.f, 0.f};
+                if (row_ok) {
+                    const float* xr = x + (size_t)n * I + f0;
+                    if (vec_x && f0 + EDGE_FQ <= I) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(xr));
+                        xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < EDGE_FQ; ++q)
+                            if (f0 + q < I) xv[q] = __ldg(xr + q);
+                    }
+                    if (has_base) {
+                        if (sbase_val) {
+                            const float* sr = sbase_val + (size_t)n * I + f0;
+#pragma unroll
+                            for (int q = 0; q < EDGE_FQ; ++q)
+                                if (f0 + q < I) sv[q] = __ldg(sr + q);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < EDGE_FQ; ++q) sv[q] = silu_fast(xv[q]);
+                        }
+                    }
+                }
+                uint4 hi[EDGE_FQ], lo[EDGE_FQ];
+                uint32_t bh[EDGE_FQ], bl[EDGE_FQ];
+#pragma unroll
+                for (int q = 0; q < EDGE_FQ; ++q) {
+                    const int f = f0 + q;
+                    const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
+                    const Window w = shared_grid ? eval_window<SPLIT, true, false>(stab, ti, xv[q])
+                                                 : eval_window<SPLIT, false, false>(ft, ti, xv[q]);
+                    place_window<SPLIT>(w, 0, hi[q], lo[q]);
+                    if (!(row_ok && f < I)) {
+                        hi[q] = make_uint4(0, 0, 0, 0);
+                        lo[q] = hi[q];
+                        sv[q] = 0.f;
+                    }
+                    uint32_t h2, l2;
+                    split2(sv[q], 0.0f, h2, l2);
+                    bh[q] = h2;
+                    bl[q] = SPLIT ? l2 : 0u;
+                }
+                if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / EDGE_A_STAGES) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+#pragma unroll
+                for (int q = 0; q < EDGE_FQ; ++q) {
+                    const uint32_t off0 = sw128_chunk_offset((uint32_t)row, (uint32_t)(2 * q));
+                    const uint32_t off1 = sw128_chunk_offset((uint32_t)row, (uint32_t)(2 * q + 1));
+                    st_shared_v4(a_hi + off0, hi[q]);
+                    st_shared_v4(a_hi + off1, make_uint4(bh[q], 0, 0, 0));
+                    if (SPLIT) {
+                        st_shared_v4(a_lo + off0, lo[q]);
+                        st_shared_v4(a_lo + off1, make_uint4(bl[q], 0, 0, 0));
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ctrl->fullA[stage]));
+            }
+        }
+    } else if (warp < EDGE_MMA_WARP) {
+        // ===== epilogue: thread = one output row of the accumulator, one half of its columns =====
+        const int e = warp - EDGE_PRODUCER_WARPS;          // 0 .. 7
+        const int quad = warp & 3;                         // TMEM lane quadrant of this warp
+        const int half = e >> 2;                           // columns [128 half, 128 half + 128)
+        const int orow = quad * 32 + lane;
+        uint32_t job = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            int sp, op, fq;
+            decode(item, sp, op, fq);
+            int64_t t0, t1;
+            tile_range(sp, t0, t1);
+            const int n_ot = otiles_of(op);
+            float total[EDGE_MAX_OTILES][EDGE_FQ];
+#pragma unroll
+            for (int j = 0; j < EDGE_MAX_OTILES; ++j)
+#pragma unroll
+                for (int q = 0; q < EDGE_FQ; ++q) total[j][q] = 0.f;
+            for (int64_t t = t0; t < t1 && ok; ++t) {
+#pragma unroll
+                for (int j = 0; j < EDGE_MAX_OTILES; ++j) {
+                    if (j >= n_ot) break;
+#pragma unroll
+                    for (int q = 0; q < EDGE_FQ; ++q, ++job) {
+                        const uint32_t buf = job & 1u;
+                        if (!mbar_wait(smem_u32(&ctrl->accFull[buf]), (job >> 1) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * EDGE_TN + half * 128 + c * 32, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int v = 0; v < 32; ++v) part[v & 3] += fabsf(__uint_as_float(r[v]));
+                        }
+                        total[j][q] += (part[0] + part[1]) + (part[2] + part[3]);
+                        tc_fence_before_sync();
+                        mbar_arrive(smem_u32(&ctrl->accEmpty[buf]));
+                    }
+                    if (!ok) break;
+                }
+            }
+            if (!ok) break;
+            // slab (sample range, column half) of the per-edge partial sums
+            float* slab = partial + ((size_t)sp * 2 + half) * ((size_t)O * I);
+#pragma unroll
+            for (int j = 0; j < EDGE_MAX_OTILES; ++j) {
+                if (j >= n_ot) break;
+                const int o = (op * EDGE_MAX_OTILES + j) * EDGE_OT + orow;
+                if (o >= O) continue;
+#pragma unroll
+                for (int q = 0; q < EDGE_FQ; ++q) {
+                    const int f = fq * EDGE_FQ + q;
+                    if (f < I) slab[(size_t)o * I + f] = total[j][q];
+                }
+            }
+        }
+    } else if (warp == EDGE_MMA_WARP) {
+        if (lane == 0) {
+            // ===== MMA issue: D[o, n] = Wop[o, 16] Aop[n, 16]^T per feature and output tile =====
+            constexpr uint32_t idesc = make_idesc_bf16(EDGE_TN, false, false);
+            constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
+            uint32_t it = 0, job = 0, n_item = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
+                int sp, op, fq;
+                decode(item, sp, op, fq);
+                int64_t t0, t1;
+                tile_range(sp, t0, t1);
+                const int n_ot = otiles_of(op);
+                if (!mbar_wait(smem_u32(&ctrl->fullW), n_item & 1u, abort_flag)) break;
+                tc_fence_after_sync();
+                for (int64_t t = t0; t < t1 && ok; ++t, ++it) {
+                    const uint32_t stage = it % EDGE_A_STAGES;
+                    const uint32_t a_hi = sbase + EDGE_SMEM_A + stage * EDGE_A_STAGE;
+                    const uint32_t a_lo = a_hi + EDGE_A_TILE;
+                    if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / EDGE_A_STAGES) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    for (int j = 0; j < n_ot && ok; ++j) {
+                        const uint32_t w_hi = sbase + EDGE_SMEM_W + j * EDGE_W_SLOT;
+                        const uint32_t w_lo = w_hi + EDGE_W_TILE;
+                        for (int q = 0; q < EDGE_FQ; ++q, ++job) {
+                            const uint32_t buf = job & 1u;
+                            if (!mbar_wait(smem_u32(&ctrl->accEmpty[buf]), ((job >> 1) & 1u) ^ 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t d_tmem = tmem_base + buf * EDGE_TN;
+                            mma_f16_ss(d_tmem, sdesc_at(dbase, w_hi + q * 32), sdesc_at(dbase, a_hi + q * 32), idesc, 0u);
+                            if (SPLIT) {
+                                mma_f16_ss(d_tmem, sdesc_at(dbase, w_lo + q * 32), sdesc_at(dbase, a_hi + q * 32), idesc, 1u);
+                                mma_f16_ss(d_tmem, sdesc_at(dbase, w_hi + q * 32), sdesc_at(dbase, a_lo + q * 32), idesc, 1u);
+                            }
+                            mma_commit(smem_u32(&ctrl->accFull[buf]));
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit(smem_u32(&ctrl->emptyA[stage]));
+                }
+                if (!ok) break;
+                mma_commit(smem_u32(&ctrl->emptyW));
+            }
+        }
+    } else {
+        if (lane == 0) {
+            // ===== bulk copies: the weight tiles of an item, once per item =====
+            uint32_t n_item = 0;
+            for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
+                int sp, op, fq;
+                decode(item, sp, op, fq);
+                const int n_ot = otiles_of(op);
+                if (!mbar_wait(smem_u32(&ctrl->emptyW), (n_item & 1u) ^ 1u, abort_flag)) break;
+                const uint32_t bar = smem_u32(&ctrl->fullW);
+                mbar_arrive_expect_tx(bar, (uint32_t)n_ot * EDGE_W_SLOT);
+                for (int j = 0; j < n_ot; ++j) {
+                    const int ot = op * EDGE_MAX_OTILES + j;
+                    const uint8_t* src = wimg + ((size_t)ot * plan.n_quads + fq) * (size_t)EDGE_W_SLOT;
+                    bulk_g2s(sbase + EDGE_SMEM_W + j * EDGE_W_SLOT, src, EDGE_W_SLOT, bar);
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == EDGE_MMA_WARP) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+__global__ void edge_sum_slabs_kernel(const float* __restrict__ partial, float* __restrict__ a, int64_t elems,
+                                      int slabs, float scale) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < elems;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < slabs; ++s) v += partial[(size_t)s * elems + e];
+        a[e] = v * scale;
+    }
+}
+
+EdgePlanTc plan_edge_tc(int64_t N, int I, int O) {
+    EdgePlanTc p;
+    p.n_quads = (I + EDGE_FQ - 1) / EDGE_FQ;
+    p.n_otiles = (O + EDGE_OT - 1) / EDGE_OT;
+    p.n_opairs = (p.n_otiles + EDGE_MAX_OTILES - 1) / EDGE_MAX_OTILES;
+    p.tiles_total = (N + EDGE_TN - 1) / EDGE_TN;
+    const int64_t base_items = (int64_t)p.n_quads * p.n_opairs;
+    // enough items for about four rounds of the persistent CTAs, at least two sample tiles each
+    int64_t splits = (4 * (int64_t)sm_count() + base_items - 1) / base_items;
+    const int64_t max_splits = (p.tiles_total + 1) / 2;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 64) splits = 64;
+    if (splits < 1) splits = 1;
+    p.tiles_per_split = (p.tiles_total + splits - 1) / splits;
+    p.splits = (int)((p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split);
+    return p;
+}
+
+}  // namespace
+
+bool tc_edge_supported(const LayerShape& s) {
+    return s.K >= 1 && s.K <= 3 && s.G >= 1 && s.R() <= 8 && s.N >= 1 && s.I >= 1 && s.O >= 1;
+}
+
+size_t tc_edge_workspace(const LayerShape& s) {
+    const EdgePlanTc p = plan_edge_tc(s.N, s.I, s.O);
+    return kWsHeader + tc_table_bytes(s) + align256((size_t)p.n_otiles * p.n_quads * EDGE_W_SLOT) +
+           align256((size_t)p.n_slabs() * s.O * s.I * sizeof(float));
+}
+
+// W is the effective coefficient tensor [O, I, R] (scaler already applied); s_val, when given,
+// replaces silu(x) as the base value (layers with another base activation); bw == NULL: no base term.
+cudaError_t tc_edge_forward(int split_terms, const float* x, const float* s_val, const float* grid, const float* bw,
+                            const float* W, float* a, const LayerShape& s, void* ws, size_t ws_bytes,
+                            cudaStream_t st) {
+    if (!ws || ws_bytes < tc_edge_workspace(s)) return cudaErrorMemoryAllocation;
+    const EdgePlanTc p = plan_edge_tc(s.N, s.I, s.O);
+    const TabInfo ti = make_tab_info(s.G, s.K);
+    int* status = reinterpret_cast<int*>(ws);
+    uint8_t* cur = reinterpret_cast<uint8_t*>(ws) + kWsHeader;
+    float* tab = reinterpret_cast<float*>(cur);
+    cur += tc_table_bytes(s);
+    uint8_t* wimg = cur;
+    cur += align256((size_t)p.n_otiles * p.n_quads * EDGE_W_SLOT);
+    float* partial = reinterpret_cast<float*>(cur);
+
+    cudaError_t e = tc_build_table(grid, tab, s, st);
+    if (e != cudaSuccess) return e;
+    {
+        const int64_t chunks = (int64_t)p.n_otiles * p.n_quads * EDGE_OT * 8;
+        int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
+                                                                            : (int64_t)sm_count() * 16);
+        pack_edge_weights_kernel<<<blocks, 256, 0, st>>>(W, bw, wimg, s.O, s.I, s.R(), p.n_quads, p.n_otiles);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    const int vec_x = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const int64_t items = p.n_items();
+    const int blocks = (int)(items < sm_count() ? items : sm_count());
+    if (split_terms == 3) {
+        e = ensure_dynamic_smem<tc_edge_fwd_kernel<3>>((int)EDGE_SMEM_BYTES);
+        if (e == cudaSuccess)
+            tc_edge_fwd_kernel<3><<<blocks, EDGE_THREADS, EDGE_SMEM_BYTES, st>>>(
+                x, s_val, tab, wimg, partial, status, s.N, s.I, s.O, bw ? 1 : 0, p, ti, vec_x);
+    } else {
+        e = ensure_dynamic_smem<tc_edge_fwd_kernel<1>>((int)EDGE_SMEM_BYTES);
+        if (e == cudaSuccess)
+            tc_edge_fwd_kernel<1><<<blocks, EDGE_THREADS, EDGE_SMEM_BYTES, st>>>(
+                x, s_val, tab, wimg, partial, status, s.N, s.I, s.O, bw ? 1 : 0, p, ti, vec_x);
+    }
+    if (e != cudaSuccess) return e;
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    const int64_t elems = (int64_t)s.O * s.I;
+    int rblocks = (int)((elems + 255) / 256 < (int64_t)sm_count() * 8 ? (elems + 255) / 256 : (int64_t)sm_count() * 8);
+    edge_sum_slabs_kernel<<<rblocks, 256, 0, st>>>(partial, a, elems, p.n_slabs(), 1.0f / (float)s.N);
+    return cudaGetLastError();
+}
+
+}  // namespace kanb200
