@@ -165,6 +165,18 @@ KANB200_API int kanb200_edge_abs_mean_x(int dtype, int mode, const void* x, cons
                                         int64_t N, int64_t I, int64_t O, int G, int k,
                                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* Gradients of kanb200_edge_abs_mean_x for the incoming grad_a [O,I]; NULL output = not needed:
+ *   gx [N,I]   input gradient through the basis (sum_r dH dB_r/dx), plus ds * silu'(x) when s is NULL;
+ *   ds [N,I]   gradient of the caller's base values (only when s is given);
+ *   dbw [O,I], dW [O,I,R]  parameter gradients (dW with respect to the effective coefficients).
+ * The [N,I,R] tensors H and dH of edge_abs_mean_backward_cuda + kan_basis_grad_cuda
+ * (csrc/kan_reg_cuda.cu:284-312, csrc/kan_cuda.cu:682-699) are never formed.  No atomics. */
+KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, const void* grad_a, const void* x, const void* s,
+                                                 const void* grid, const void* bw, const void* W,
+                                                 void* gx, void* ds, void* dbw, void* dW,
+                                                 int64_t N, int64_t I, int64_t O, int G, int k,
+                                                 void* workspace, size_t workspace_bytes, void* stream);
+
 /* Gradients of kanb200_edge_abs_mean; NULL output = not needed
  * (edge_abs_mean_backward_cuda, csrc/kan_reg_cuda.cu:284-312). */
 KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a,

@@ -176,11 +176,13 @@ def test_config2_full_size_training_step():
 
     Bounds and why: y and the penalty are smooth in the rounding error and are held to 5e-5 after
     three layers (each layer alone is within 1e-5, checked above and in test_gpu_capi).  The
-    penalty's gradient contains sign(phi): where |phi| is at rounding level, float32 and float64
-    disagree on the sign and single entries move by 2 ga / N -- the reference's own float32 test
-    of this path allows 5e-5 for one small layer (tests/test_fused_regularization.py:88-93).  The
-    native gradients must be as close to float64 as the dense FLOAT32 evaluation of the same
-    expression is (factor 3 of slack), and within 2e-4 in any case."""
+    penalty's gradient contains sign(phi): where |phi| is at rounding level, two evaluations
+    disagree on the sign and that edge's gradient entries move by 2 ga / N = 2.4e-4 of their largest
+    possible size, whatever the arithmetic -- float32 against float64 dense PyTorch shows it too.
+    Both are valid subgradients of |phi| at neighbouring points.  The native gradients must
+    therefore be as close to float64 in the max-norm as the dense FLOAT32 evaluation of the same
+    expression is (factor 3 of slack, never looser than 2e-3), and within 1e-3 in the relative
+    L2 norm, which single flipped entries hardly move but a wrong kernel would."""
     torch.manual_seed(0)
     net = sk.KAN([784, 256, 256, 10], backend="cuda").cuda()
     g = torch.Generator().manual_seed(0)
@@ -208,9 +210,12 @@ def test_config2_full_size_training_step():
     gap32 = {n: _err(a, b) for n, a, b in zip(names, want32, want)}
     print("config 2 native32 vs dense64:", errs)
     print("config 2 dense32 vs dense64:", gap32)
+    l2 = {n: float((a.double() - b).norm() / b.norm()) for n, a, b in zip(names, got, want)}
+    print("config 2 native32 vs dense64, relative L2:", l2)
     assert errs["y"] < 5e-5 and errs["reg"] < 5e-5, errs
     for n in names:
-        assert errs[n] < min(2e-4, max(5e-5, 3.0 * gap32[n])), (n, errs[n], gap32[n])
+        assert errs[n] < min(2e-3, max(5e-5, 3.0 * gap32[n])), (n, errs[n], gap32[n])
+        assert l2[n] < 1e-3, (n, l2[n])
     _C.check_status()
 
 

@@ -51,6 +51,8 @@ SIGNATURES = {
                                                                    _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_x": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                              _c_void_p, _c_size, _c_void_p]),
+    "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
+                                                                               _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
     "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                             _c_void_p, _c_size, _c_void_p]),
@@ -335,6 +337,25 @@ def edge_abs_mean_x(x, s, grid, bw, W, k: int, mode: int = MODE_AUTO) -> torch.T
         _check(lib().kanb200_edge_abs_mean_x(_code(x.dtype), mode, _p(x), _p(s), _p(grid), _p(bw), _p(W), _p(a),
                                              N, I, O, G, k, _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return a
+
+
+def edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k: int, need_x=True, need_s=True, need_bw=True, need_W=True):
+    """``(gx, ds, dbw, dW)`` of :func:`edge_abs_mean_x` (None where not needed / not applicable)."""
+    dev = _need_cuda(x, grid, W, ga)
+    N, I = x.shape
+    O, _, R = W.shape
+    G = grid.shape[1] - 2 * k - 1
+    has_base = bw is not None and bw.numel() > 0
+    gx = torch.empty_like(x) if need_x else None
+    ds = torch.empty_like(x) if (need_s and has_base and s is not None) else None
+    dbw = torch.empty((O, I), dtype=x.dtype, device=dev) if (need_bw and has_base) else None
+    dW = torch.empty_like(W) if need_W else None
+    with _OnDevice(dev):
+        ws = workspace(dev, workspace_bytes(OP_EDGE_X_BWD, MODE_AUTO, x.dtype, N, I, O, G, k), "edge_x")
+        _check(lib().kanb200_edge_abs_mean_x_backward(_code(x.dtype), _p(ga), _p(x), _p(s), _p(grid), _p(bw), _p(W),
+                                                      _p(gx), _p(ds), _p(dbw), _p(dW), N, I, O, G, k,
+                                                      _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
+    return gx, ds, dbw, dW
 
 
 def edge_abs_mean_backward(ga, s, H, bw, W, need_s, need_H, need_bw, need_W):

@@ -109,10 +109,12 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
         // the table-driven basis kernels; 0 = the recurrence kernels run and need nothing
         return dtype == KANB200_F32 && basis_table_supported(s) ? kWsHeader + tc_table_bytes(s) : 0;
     }
-    if (op == KANB200_OP_EDGE_X_FWD) {
+    if (op == KANB200_OP_EDGE_X_FWD || op == KANB200_OP_EDGE_X_BWD) {
         if (N < 1) return 0;
-        if (edge_x_uses_tc(mode, dtype, s)) return tc_edge_workspace(s);
-        return 0;
+        const bool b = op == KANB200_OP_EDGE_X_BWD;
+        if (!b && edge_x_uses_tc(mode, dtype, s)) return tc_edge_workspace(s);
+        return kWsHeader + (dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
+                                                 : edge_workspace<double>(N, s.I, s.O, s.R(), b));
     }
     if (op == KANB200_OP_EDGE_FWD || op == KANB200_OP_EDGE_BWD) {
         const bool b = op == KANB200_OP_EDGE_BWD;
@@ -353,7 +355,42 @@ KANB200_API int kanb200_edge_abs_mean_x(int dtype, int mode, const void* x, cons
     }
     if (mode == KANB200_MODE_TC_BF16X3 || mode == KANB200_MODE_TC_BF16X1)
         return fail(KANB200_EUNSUPPORTED, "edge_abs_mean_x: tensor-core modes need float32 and G + k <= 8");
-    return fail(KANB200_EUNSUPPORTED, "edge_abs_mean_x: this shape runs through kanb200_basis + kanb200_edge_abs_mean");
+    cudaError_t e =
+        dtype == KANB200_F32
+            ? edge_abs_mean_x_fwd<float>((const float*)x, (const float*)s_val, (const float*)grid, (const float*)bw,
+                                         (const float*)W, (float*)a, N, (int)I, (int)O, G + k, k,
+                                         ws_body(workspace, workspace_bytes), ws_body_bytes(workspace, workspace_bytes), st)
+            : edge_abs_mean_x_fwd<double>((const double*)x, (const double*)s_val, (const double*)grid,
+                                          (const double*)bw, (const double*)W, (double*)a, N, (int)I, (int)O, G + k, k,
+                                          ws_body(workspace, workspace_bytes), ws_body_bytes(workspace, workspace_bytes),
+                                          st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x");
+}
+
+KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, const void* grad_a, const void* x, const void* s_val,
+                                                 const void* grid, const void* bw, const void* W,
+                                                 void* gx, void* ds, void* dbw, void* dW,
+                                                 int64_t N, int64_t I, int64_t O, int G, int k,
+                                                 void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = kanb200_check_shapes(N, I, O, G, k, dtype);
+    if (rc) return rc;
+    if (N < 1) return fail(KANB200_EINVAL, "edge_abs_mean: need at least one sample");
+    if (!grad_a || !x || !grid || !W) return fail(KANB200_EINVAL, "edge_abs_mean_x_backward: NULL pointer");
+    if (s_val && !bw) return fail(KANB200_EINVAL, "edge_abs_mean_x_backward: base values given without base_weight");
+    if (ds && !s_val) return fail(KANB200_EINVAL, "edge_abs_mean_x_backward: ds requested without base values s");
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e =
+        dtype == KANB200_F32
+            ? edge_abs_mean_x_bwd<float>((const float*)grad_a, (const float*)x, (const float*)s_val, (const float*)grid,
+                                         (const float*)bw, (const float*)W, (float*)gx, (float*)ds, (float*)dbw,
+                                         (float*)dW, N, (int)I, (int)O, G + k, k, ws_body(workspace, workspace_bytes),
+                                         ws_body_bytes(workspace, workspace_bytes), st)
+            : edge_abs_mean_x_bwd<double>((const double*)grad_a, (const double*)x, (const double*)s_val,
+                                          (const double*)grid, (const double*)bw, (const double*)W, (double*)gx,
+                                          (double*)ds, (double*)dbw, (double*)dW, N, (int)I, (int)O, G + k, k,
+                                          ws_body(workspace, workspace_bytes), ws_body_bytes(workspace, workspace_bytes),
+                                          st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x_backward");
 }
 
 KANB200_API int kanb200_edge_abs_mean_noalloc(int dtype, const void* s, const void* H, const void* bw,

@@ -58,6 +58,16 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
                               T* ds, T* dH, T* dbw, T* dW,
                               int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// The same operators straight from the layer input x (no H, no dH): see kan_reg.cu.  Scratch as for
+// edge_abs_mean_fwd / _bwd.
+template <typename T>
+cudaError_t edge_abs_mean_x_fwd(const T* x, const T* s, const T* grid, const T* bw, const T* W, T* a,
+                                int64_t N, int I, int O, int R, int k, void* ws, size_t ws_bytes, cudaStream_t st);
+template <typename T>
+cudaError_t edge_abs_mean_x_bwd(const T* ga, const T* x, const T* s, const T* grid, const T* bw, const T* W,
+                                T* gx, T* ds, T* dbw, T* dW, int64_t N, int I, int O, int R, int k,
+                                void* ws, size_t ws_bytes, cudaStream_t st);
+
 // Fixed device scratch of the allocation-free edge statistic (kan_reg.cu).
 size_t edge_static_scratch_bytes();
 cudaError_t edge_static_scratch(void** ptr);

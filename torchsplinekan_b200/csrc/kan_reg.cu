@@ -6,6 +6,12 @@
 //             dbw[o,i] = sum_n g s      dW[o,i,r] = sum_n g H[n,i,r]
 //             ds[n,i]  = sum_o g bw     dH[n,i,r] = sum_o g W[o,i,r]
 //
+// Every kernel exists in two forms: from the materialised basis H [N,I,R] and base values s [N,I]
+// (the operator surface of the reference, csrc/kan_reg_cuda.cu) and -- template parameter K > 0 --
+// straight from the layer input x, where a block rebuilds the rows of H it needs in shared memory
+// (parameter kernels) or registers (input kernel), the input kernel contracts dH with dB/dx on the
+// spot, and neither H nor dH ever exists in memory.
+//
 // Bound by the FP32/FP64 FMA pipe (N O I (R+1) FMAs against N I (R+1) + O I (R+1)
 // input elements).  Sums over samples are split across blocks; each split
 // writes its own slab in the caller's workspace and a second kernel adds the
@@ -38,15 +44,20 @@ __device__ __forceinline__ void load_row16(const T* __restrict__ p, T (&out)[CNT
 
 // Thread = OPT outputs x one feature, W rows in registers; loops over the
 // samples of its split with H / s tiles staged in shared memory.
-template <typename T, int RMAX, int OPT, int TNS, bool GRAD>
+// K = 0: H and s are read from memory.  K = 1..3: H rows are evaluated from x on the knots `grid`
+// (spline order K), and the base value is s[n,i] when s is given, silu(x) otherwise.
+template <typename T, int RMAX, int OPT, int TNS, bool GRAD, int K>
 __global__ void __launch_bounds__(EA_THREADS)
 edge_param_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __restrict__ bw,
                   const T* __restrict__ W, const T* __restrict__ ga,
                   T* __restrict__ part_a, T* __restrict__ part_dbw, T* __restrict__ part_dW,
-                  int64_t N, int I, int O, int R, int64_t n_per_split) {
+                  int64_t N, int I, int O, int R, int64_t n_per_split,
+                  const T* __restrict__ x, const T* __restrict__ grid) {
     constexpr int TO = 32 * OPT;
     __shared__ __align__(16) T Hs[TNS][EA_TI][RMAX];
     __shared__ T ss[TNS][EA_TI];
+    __shared__ T knots[K > 0 ? EA_TI : 1][K > 0 ? kMaxKnots : 1];
+    const int nk = R + K + 1;
     const int tid = threadIdx.x;
     const int lane_o = tid & 31, ti = tid >> 5;
     const int o0 = blockIdx.x * TO, i0 = blockIdx.y * EA_TI;
@@ -76,19 +87,53 @@ edge_param_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
         }
     }
 
+    if constexpr (K > 0) {
+        for (int e = tid; e < EA_TI * nk; e += EA_THREADS) {
+            const int ii = e / nk, q = e - ii * nk;
+            knots[ii][q] = (i0 + ii < I) ? grid[(size_t)(i0 + ii) * nk + q] : T(0);
+        }
+    }
+
     for (int64_t nt = nb; nt < ne; nt += TNS) {
         __syncthreads();
-        for (int e = tid; e < TNS * EA_TI * RMAX; e += EA_THREADS) {
-            const int n = e / (EA_TI * RMAX);
-            const int rem = e - n * (EA_TI * RMAX);
-            const int ii = rem / RMAX, r = rem - ii * RMAX;
-            T v = T(0);
-            if (nt + n < ne && i0 + ii < I && r < R) v = H[((size_t)(nt + n) * I + i0 + ii) * R + r];
-            Hs[n][ii][r] = v;
-        }
-        for (int e = tid; e < TNS * EA_TI; e += EA_THREADS) {
-            const int n = e / EA_TI, ii = e - n * EA_TI;
-            ss[n][ii] = (has_base && nt + n < ne && i0 + ii < I) ? s[(size_t)(nt + n) * I + i0 + ii] : T(0);
+        if constexpr (K == 0) {
+            for (int e = tid; e < TNS * EA_TI * RMAX; e += EA_THREADS) {
+                const int n = e / (EA_TI * RMAX);
+                const int rem = e - n * (EA_TI * RMAX);
+                const int ii = rem / RMAX, r = rem - ii * RMAX;
+                T v = T(0);
+                if (nt + n < ne && i0 + ii < I && r < R) v = H[((size_t)(nt + n) * I + i0 + ii) * R + r];
+                Hs[n][ii][r] = v;
+            }
+            for (int e = tid; e < TNS * EA_TI; e += EA_THREADS) {
+                const int n = e / EA_TI, ii = e - n * EA_TI;
+                ss[n][ii] = (has_base && nt + n < ne && i0 + ii < I) ? s[(size_t)(nt + n) * I + i0 + ii] : T(0);
+            }
+        } else {
+            // one (sample, feature) pair per thread and round: its dense basis row and base value
+            for (int e = tid; e < TNS * EA_TI; e += EA_THREADS) {
+                const int n = e / EA_TI, ii = e - n * EA_TI;
+                T* row = &Hs[n][ii][0];
+#pragma unroll
+                for (int r = 0; r < RMAX; ++r) row[r] = T(0);
+                T sv = T(0);
+                if (nt + n < ne && i0 + ii < I) {
+                    const size_t at = (size_t)(nt + n) * I + i0 + ii;
+                    const T xv = x[at];
+                    const int m = locate_span(&knots[ii][0], nk, xv);
+                    if (m >= 0) {
+                        T v[K + 1], d[K + 1];
+                        window_values<K, T, false>(&knots[ii][0], nk, m, xv, v, d);
+#pragma unroll
+                        for (int j = 0; j <= K; ++j) {
+                            const int r = m - K + j;
+                            if (r >= 0 && r < R) row[r] = v[j];
+                        }
+                    }
+                    if (has_base) sv = s ? s[at] : silu_t<T>(xv);
+                }
+                ss[n][ii] = sv;
+            }
         }
         __syncthreads();
         const int lim = (int)((ne - nt < TNS) ? (ne - nt) : TNS);
@@ -169,14 +214,21 @@ __device__ __forceinline__ float signed_weight<float>(float c, float phi) {
 // tiles of outputs staged in shared memory (a weight row is read once per NPT samples).
 constexpr int EB_TI = 4, EB_TN = 32, EB_THREADS = 128;
 
-template <typename T, int RMAX, int TOC, int NPT>
+// K = 0: H rows are read, ds and dH are written.  K = 1..3: the rows are evaluated from x, dH is
+// contracted with dB/dx in registers and the kernel writes the input gradient
+//     gx[n,i] = sum_r dH[n,i,r] dB_r/dx (x[n,i])  ( + ds[n,i] silu'(x[n,i]) when s is NULL )
+// and, when the caller supplied its own base values s, ds [N,I] for them.
+template <typename T, int RMAX, int TOC, int NPT, int K>
 __global__ void __launch_bounds__(EB_THREADS)
 edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __restrict__ bw,
                   const T* __restrict__ W, const T* __restrict__ ga,
                   T* __restrict__ ds, T* __restrict__ dH,
-                  int64_t N, int I, int O, int R) {
+                  int64_t N, int I, int O, int R,
+                  const T* __restrict__ x, const T* __restrict__ grid, T* __restrict__ gx) {
     constexpr int WROW = RMAX + 16 / sizeof(T);   // 16-byte aligned rows: [RMAX] = bw, [RMAX+1] = ga/N
     __shared__ __align__(16) T Ws[TOC][EB_TI][WROW];
+    __shared__ T knots[K > 0 ? EB_TI : 1][K > 0 ? kMaxKnots : 1];
+    const int nk = R + K + 1;
     const int tid = threadIdx.x;
     const int ti = tid & (EB_TI - 1), tn = tid / EB_TI;
     const int i0 = blockIdx.y * EB_TI;
@@ -186,18 +238,53 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
     const T invN = T(1) / T(N);
 
     T h[NPT][RMAX], dh[NPT][RMAX], sv[NPT], dsv[NPT];
+    T der[K > 0 ? NPT : 1][K + 1], xq[K > 0 ? NPT : 1];
+    int first[K > 0 ? NPT : 1];          // basis index of window slot 0 (may be negative)
     bool live[NPT];
+    if constexpr (K > 0) {
+        for (int e = tid; e < EB_TI * nk; e += EB_THREADS) {
+            const int ii = e / nk, q = e - ii * nk;
+            knots[ii][q] = (i0 + ii < I) ? grid[(size_t)(i0 + ii) * nk + q] : T(0);
+        }
+        __syncthreads();
+    }
 #pragma unroll
     for (int q = 0; q < NPT; ++q) {
         const int64_t n = nbase + (int64_t)q * EB_TN;
         live[q] = (i < I) && (n < N);
-#pragma unroll
-        for (int r = 0; r < RMAX; ++r) {
-            h[q][r] = (live[q] && r < R) ? H[((size_t)n * I + i) * R + r] : T(0);
-            dh[q][r] = T(0);
-        }
-        sv[q] = (live[q] && has_base) ? s[(size_t)n * I + i] : T(0);
         dsv[q] = T(0);
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) dh[q][r] = T(0);
+        if constexpr (K == 0) {
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) h[q][r] = (live[q] && r < R) ? H[((size_t)n * I + i) * R + r] : T(0);
+            sv[q] = (live[q] && has_base) ? s[(size_t)n * I + i] : T(0);
+        } else {
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r) h[q][r] = T(0);
+#pragma unroll
+            for (int j = 0; j <= K; ++j) der[q][j] = T(0);
+            sv[q] = T(0);
+            xq[q] = T(0);
+            first[q] = 0;
+            if (live[q]) {
+                const T xv = x[(size_t)n * I + i];
+                xq[q] = xv;
+                const int m = locate_span(&knots[ti][0], nk, xv);
+                if (m >= 0) {
+                    T v[K + 1];
+                    window_values<K, T, true>(&knots[ti][0], nk, m, xv, v, der[q]);
+                    first[q] = m - K;
+                    // registers cannot be indexed by m: every slot picks its value by comparison
+#pragma unroll
+                    for (int r = 0; r < RMAX; ++r) {
+#pragma unroll
+                        for (int j = 0; j <= K; ++j) h[q][r] = (r == m - K + j && r < R) ? v[j] : h[q][r];
+                    }
+                }
+                if (has_base) sv[q] = s ? s[(size_t)n * I + i] : silu_t<T>(xv);
+            }
+        }
     }
 
     for (int oc = 0; oc < O; oc += TOC) {
@@ -241,10 +328,24 @@ edge_input_kernel(const T* __restrict__ s, const T* __restrict__ H, const T* __r
         if (!live[q]) continue;
         const int64_t n = nbase + (int64_t)q * EB_TN;
         if (ds) ds[(size_t)n * I + i] = dsv[q];
-        if (dH) {
+        if constexpr (K == 0) {
+            if (dH) {
 #pragma unroll
-            for (int r = 0; r < RMAX; ++r)
-                if (r < R) dH[((size_t)n * I + i) * R + r] = dh[q][r];
+                for (int r = 0; r < RMAX; ++r)
+                    if (r < R) dH[((size_t)n * I + i) * R + r] = dh[q][r];
+            }
+        } else {
+            if (gx) {
+                T g = (has_base && !s) ? dsv[q] * silu_grad_t<T>(xq[q]) : T(0);
+#pragma unroll
+                for (int r = 0; r < RMAX; ++r) {
+                    T d = T(0);
+#pragma unroll
+                    for (int j = 0; j <= K; ++j) d = (r == first[q] + j && r < R) ? der[q][j] : d;
+                    g += dh[q][r] * d;
+                }
+                gx[(size_t)n * I + i] = g;
+            }
         }
     }
 }
@@ -264,13 +365,13 @@ int edge_param_blocks_per_sm(int rmax) {
     int n = 0;
     cudaError_t e;
     if (rmax == 8)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 8, 4, 32, GRAD>, EA_THREADS, 0);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 8, 4, 32, GRAD, 0>, EA_THREADS, 0);
     else if (rmax == 16)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 16, 2, 32, GRAD>, EA_THREADS, 0);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 16, 2, 32, GRAD, 0>, EA_THREADS, 0);
     else if (rmax == 32)
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 32, 1, 8, GRAD>, EA_THREADS, 0);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 32, 1, 8, GRAD, 0>, EA_THREADS, 0);
     else
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 72, 1, 8, GRAD>, EA_THREADS, 0);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, edge_param_kernel<T, 72, 1, 8, GRAD, 0>, EA_THREADS, 0);
     if (e != cudaSuccess || n < 1) {
         cudaGetLastError();
         return GRAD ? 2 : 4;            // not cached: a later call with a device asks again
@@ -327,13 +428,15 @@ EdgePlan plan_edge(int64_t N, int I, int O, int R) {
     return p;
 }
 
-template <typename T, bool GRAD>
+// K = 0: from H / s.  K > 0: from x on the knots `grid`.
+template <typename T, bool GRAD, int K>
 cudaError_t launch_edge_param(const EdgePlan& p, const T* s, const T* H, const T* bw, const T* W, const T* ga,
-                              T* pa, T* pdbw, T* pdW, int64_t N, int I, int O, int R, cudaStream_t st) {
+                              T* pa, T* pdbw, T* pdW, int64_t N, int I, int O, int R, cudaStream_t st,
+                              const T* x = nullptr, const T* grid = nullptr) {
     dim3 g((O + p.to - 1) / p.to, (I + EA_TI - 1) / EA_TI, p.splits);
-#define KAN_EP(RM, OP, TN)                                                                           \
-    edge_param_kernel<T, RM, OP, TN, GRAD><<<g, EA_THREADS, 0, st>>>(s, H, bw, W, ga, pa, pdbw, pdW, \
-                                                                     N, I, O, R, p.n_per_split)
+#define KAN_EP(RM, OP, TN)                                                                              \
+    edge_param_kernel<T, RM, OP, TN, GRAD, K><<<g, EA_THREADS, 0, st>>>(s, H, bw, W, ga, pa, pdbw, pdW, \
+                                                                        N, I, O, R, p.n_per_split, x, grid)
     if (p.rmax == 8) KAN_EP(8, 4, 32);
     else if (p.rmax == 16) KAN_EP(16, 2, 32);
     else if (p.rmax == 32) KAN_EP(32, 1, 8);
@@ -341,6 +444,27 @@ cudaError_t launch_edge_param(const EdgePlan& p, const T* s, const T* H, const T
 #undef KAN_EP
     return cudaGetLastError();
 }
+
+template <typename T, int K>
+cudaError_t launch_edge_input(const T* s, const T* H, const T* bw, const T* W, const T* ga, T* ds, T* dH,
+                              int64_t N, int I, int O, int R, cudaStream_t st,
+                              const T* x = nullptr, const T* grid = nullptr, T* gx = nullptr) {
+    const int rmax = R <= 8 ? 8 : (R <= 16 ? 16 : (R <= 32 ? 32 : 72));
+    const int npt = rmax == 8 ? 4 : (rmax == 16 ? 2 : 1);   // samples per thread
+    dim3 g((unsigned)((N + EB_TN * npt - 1) / (EB_TN * npt)), (I + EB_TI - 1) / EB_TI);
+    if (rmax == 8) edge_input_kernel<T, 8, 32, 4, K><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, ds, dH, N, I, O, R, x, grid, gx);
+    else if (rmax == 16) edge_input_kernel<T, 16, 32, 2, K><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, ds, dH, N, I, O, R, x, grid, gx);
+    else if (rmax == 32) edge_input_kernel<T, 32, 16, 1, K><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, ds, dH, N, I, O, R, x, grid, gx);
+    else edge_input_kernel<T, 72, 8, 1, K><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, ds, dH, N, I, O, R, x, grid, gx);
+    return cudaGetLastError();
+}
+
+#define KAN_EDGE_K(Kval, ...)                                      \
+    switch (Kval) {                                                \
+        case 1: { constexpr int KK = 1; __VA_ARGS__; break; }      \
+        case 2: { constexpr int KK = 2; __VA_ARGS__; break; }      \
+        default: { constexpr int KK = 3; __VA_ARGS__; break; }     \
+    }
 
 inline int grid_1d(int64_t work, int threads, int cap = 148 * 32) {
     int64_t b = (work + threads - 1) / threads;
@@ -365,7 +489,7 @@ cudaError_t edge_abs_mean_fwd(const T* s, const T* H, const T* bw, const T* W, T
     const size_t oi = (size_t)O * I;
     if (!ws || ws_bytes < (size_t)p.splits * oi * sizeof(T)) return cudaErrorMemoryAllocation;
     T* pa = reinterpret_cast<T*>(ws);
-    cudaError_t e = launch_edge_param<T, false>(p, s, H, bw, W, nullptr, pa, nullptr, nullptr, N, I, O, R, st);
+    cudaError_t e = launch_edge_param<T, false, 0>(p, s, H, bw, W, nullptr, pa, nullptr, nullptr, N, I, O, R, st);
     if (e != cudaSuccess) return e;
     sum_slabs_kernel<T><<<grid_1d((int64_t)oi, 256), 256, 0, st>>>(pa, a, (int64_t)oi, p.splits, T(1) / T(N));
     return cudaGetLastError();
@@ -382,8 +506,8 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
         if (!ws || ws_bytes < (size_t)p.splits * oi * (R + 1) * sizeof(T)) return cudaErrorMemoryAllocation;
         T* pdW = reinterpret_cast<T*>(ws);
         T* pdbw = pdW + (size_t)p.splits * oi * R;
-        e = launch_edge_param<T, true>(p, s, H, bw, W, ga, nullptr, (dbw && bw) ? pdbw : nullptr,
-                                       dW ? pdW : nullptr, N, I, O, R, st);
+        e = launch_edge_param<T, true, 0>(p, s, H, bw, W, ga, nullptr, (dbw && bw) ? pdbw : nullptr,
+                                          dW ? pdW : nullptr, N, I, O, R, st);
         if (e != cudaSuccess) return e;
         if (dW) {
             sum_slabs_kernel<T><<<grid_1d((int64_t)oi * R, 256), 256, 0, st>>>(pdW, dW, (int64_t)oi * R, p.splits, T(1));
@@ -394,16 +518,57 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
             if ((e = cudaGetLastError()) != cudaSuccess) return e;
         }
     }
-    if ((ds && bw) || dH) {
-        const int rmax = R <= 8 ? 8 : (R <= 16 ? 16 : (R <= 32 ? 32 : 72));
-        const int npt = rmax == 8 ? 4 : (rmax == 16 ? 2 : 1);   // samples per thread
-        dim3 g((unsigned)((N + EB_TN * npt - 1) / (EB_TN * npt)), (I + EB_TI - 1) / EB_TI);
-        T* dsp = (ds && bw) ? ds : nullptr;
-        if (rmax == 8) edge_input_kernel<T, 8, 32, 4><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        else if (rmax == 16) edge_input_kernel<T, 16, 32, 2><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        else if (rmax == 32) edge_input_kernel<T, 32, 16, 1><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        else edge_input_kernel<T, 72, 8, 1><<<g, EB_THREADS, 0, st>>>(s, H, bw, W, ga, dsp, dH, N, I, O, R);
-        e = cudaGetLastError();
+    if ((ds && bw) || dH) e = launch_edge_input<T, 0>(s, H, bw, W, ga, (ds && bw) ? ds : nullptr, dH, N, I, O, R, st);
+    return e;
+}
+
+// ---------------------------------------------------------------------------
+// The same operators straight from the layer input x (spline order k, knots grid [I, R + k + 1])
+// ---------------------------------------------------------------------------
+template <typename T>
+cudaError_t edge_abs_mean_x_fwd(const T* x, const T* s, const T* grid, const T* bw, const T* W, T* a,
+                                int64_t N, int I, int O, int R, int k, void* ws, size_t ws_bytes, cudaStream_t st) {
+    EdgePlan p = plan_edge<T, false>(N, I, O, R);
+    const size_t oi = (size_t)O * I;
+    if (!ws || ws_bytes < (size_t)p.splits * oi * sizeof(T)) return cudaErrorMemoryAllocation;
+    T* pa = reinterpret_cast<T*>(ws);
+    cudaError_t e = cudaSuccess;
+    KAN_EDGE_K(k, (e = launch_edge_param<T, false, KK>(p, s, nullptr, bw, W, nullptr, pa, nullptr, nullptr, N, I, O, R,
+                                                       st, x, grid)));
+    if (e != cudaSuccess) return e;
+    sum_slabs_kernel<T><<<grid_1d((int64_t)oi, 256), 256, 0, st>>>(pa, a, (int64_t)oi, p.splits, T(1) / T(N));
+    return cudaGetLastError();
+}
+
+// gx: input gradient through the basis (and through silu when s is NULL); ds: gradient of the
+// caller's base values (only with s); dbw, dW: parameter gradients.  NULL = not needed.
+template <typename T>
+cudaError_t edge_abs_mean_x_bwd(const T* ga, const T* x, const T* s, const T* grid, const T* bw, const T* W,
+                                T* gx, T* ds, T* dbw, T* dW, int64_t N, int I, int O, int R, int k,
+                                void* ws, size_t ws_bytes, cudaStream_t st) {
+    cudaError_t e = cudaSuccess;
+    const size_t oi = (size_t)O * I;
+    if ((dbw && bw) || dW) {
+        EdgePlan p = plan_edge<T, true>(N, I, O, R);
+        if (!ws || ws_bytes < (size_t)p.splits * oi * (R + 1) * sizeof(T)) return cudaErrorMemoryAllocation;
+        T* pdW = reinterpret_cast<T*>(ws);
+        T* pdbw = pdW + (size_t)p.splits * oi * R;
+        KAN_EDGE_K(k, (e = launch_edge_param<T, true, KK>(p, s, nullptr, bw, W, ga, nullptr,
+                                                          (dbw && bw) ? pdbw : nullptr, dW ? pdW : nullptr, N, I, O,
+                                                          R, st, x, grid)));
+        if (e != cudaSuccess) return e;
+        if (dW) {
+            sum_slabs_kernel<T><<<grid_1d((int64_t)oi * R, 256), 256, 0, st>>>(pdW, dW, (int64_t)oi * R, p.splits, T(1));
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
+        if (dbw && bw) {
+            sum_slabs_kernel<T><<<grid_1d((int64_t)oi, 256), 256, 0, st>>>(pdbw, dbw, (int64_t)oi, p.splits, T(1));
+            if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        }
+    }
+    if (gx || (ds && s && bw)) {
+        KAN_EDGE_K(k, (e = launch_edge_input<T, KK>(s, nullptr, bw, W, ga, (ds && s && bw) ? ds : nullptr, nullptr, N, I,
+                                                    O, R, st, x, grid, gx)));
     }
     return e;
 }
@@ -442,7 +607,11 @@ cudaError_t edge_static_scratch(void** ptr) {
     template cudaError_t edge_abs_mean_fwd<T>(const T*, const T*, const T*, const T*, T*, int64_t, int,  \
                                               int, int, void*, size_t, cudaStream_t);                    \
     template cudaError_t edge_abs_mean_bwd<T>(const T*, const T*, const T*, const T*, const T*, T*, T*,  \
-                                              T*, T*, int64_t, int, int, int, void*, size_t, cudaStream_t);
+                                              T*, T*, int64_t, int, int, int, void*, size_t, cudaStream_t); \
+    template cudaError_t edge_abs_mean_x_fwd<T>(const T*, const T*, const T*, const T*, const T*, T*, int64_t, \
+                                                int, int, int, int, void*, size_t, cudaStream_t);         \
+    template cudaError_t edge_abs_mean_x_bwd<T>(const T*, const T*, const T*, const T*, const T*, const T*, T*, \
+                                                T*, T*, T*, int64_t, int, int, int, int, void*, size_t, cudaStream_t);
 KAN_INSTANTIATE(float)
 KAN_INSTANTIATE(double)
 

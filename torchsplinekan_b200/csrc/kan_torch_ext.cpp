@@ -74,7 +74,7 @@ const char* mode_name(int m) {
 // every call that may write it the word is copied (asynchronously, 4 bytes) into a pinned host word
 // that the next call on the same buffer looks at without synchronising.
 // ------------------------------------------------------------------------------------------------
-enum Purpose { WS_FWD = 0, WS_BWD = 1, WS_BASIS = 2, WS_EDGE = 3 };
+enum Purpose { WS_FWD = 0, WS_BWD = 1, WS_BASIS = 2, WS_EDGE = 3, WS_EDGE_X = 4 };
 
 struct Scratch {
     Tensor buf;
@@ -434,6 +434,82 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> edge_abs_mean_backward(const Tensor& 
 }
 
 // ------------------------------------------------------------------------------------------------
+// edge statistic straight from the layer input (no counterpart among the reference's operators:
+// it fuses kan_basis_cuda + edge_abs_mean_cuda, and in backward edge_abs_mean_backward_cuda +
+// kan_basis_grad_cuda, so that H [N,I,R] and dH never exist).  s: the caller's base values [N,I],
+// or an empty tensor = silu(x); base_weight empty = no base term; W = effective coefficients.
+// ------------------------------------------------------------------------------------------------
+int check_edge_x(const Tensor& x, const Tensor& s, const Tensor& grid, const Tensor& bw, const Tensor& W, int64_t k) {
+    const int G = check_basis_args(x, grid, k);
+    TORCH_CHECK(W.is_cuda() && W.dim() == 3 && W.size(1) == x.size(1) && W.size(2) == G + k,
+                "edge_abs_mean_x: W must be a CUDA tensor [O, I, G+k]");
+    TORCH_CHECK(W.scalar_type() == x.scalar_type(), "edge_abs_mean_x: dtype mismatch");
+    TORCH_CHECK(x.size(0) >= 1, "edge_abs_mean: need at least one sample");
+    if (has(bw))
+        TORCH_CHECK(bw.dim() == 2 && bw.size(0) == W.size(0) && bw.size(1) == W.size(1) &&
+                        bw.scalar_type() == x.scalar_type(),
+                    "edge_abs_mean_x: base_weight must be [O, I]");
+    if (has(s))
+        TORCH_CHECK(has(bw) && s.dim() == 2 && s.size(0) == x.size(0) && s.size(1) == x.size(1) &&
+                        s.scalar_type() == x.scalar_type(),
+                    "edge_abs_mean_x: s must be [N, I] and needs base_weight");
+    return G;
+}
+
+Tensor edge_abs_mean_x(const Tensor& x, const Tensor& s, const Tensor& grid, const Tensor& base_weight, const Tensor& W,
+                       int64_t k) {
+    const int G = check_edge_x(x, s, grid, base_weight, W, k);
+    c10::cuda::CUDAGuard guard(x.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const int64_t N = x.size(0), I = x.size(1), O = W.size(0);
+    Tensor a = at::empty({O, I}, x.options());
+    const Tensor xc = x.contiguous(), sc = contig_or_absent(s), gc = grid.contiguous(),
+                 bw = contig_or_absent(base_weight), Wc = W.contiguous();
+    const int code = dtype_code(x), mode = g_mode.load();
+    Scratch* ws = scratch(x.device(), st, WS_EDGE_X,
+                          kanb200_workspace_bytes(KANB200_OP_EDGE_X_FWD, mode, code, N, I, O, G, (int)k, 0, 0));
+    {
+        ScopedTimer timer("edge_forward", st);
+        check_rc(kanb200_edge_abs_mean_x(code, mode, xc.data_ptr(), cptr(sc), gc.data_ptr(), cptr(bw), Wc.data_ptr(),
+                                         a.data_ptr(), N, I, O, G, (int)k, ws ? ws->buf.data_ptr() : nullptr,
+                                         ws ? (size_t)ws->buf.numel() : 0, st));
+    }
+    mirror_status(ws, st);
+    return a;
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor> edge_abs_mean_x_backward(const Tensor& grad_a, const Tensor& x, const Tensor& s,
+                                                                    const Tensor& grid, const Tensor& base_weight,
+                                                                    const Tensor& W, int64_t k, bool need_x, bool need_s,
+                                                                    bool need_bw, bool need_W) {
+    const int G = check_edge_x(x, s, grid, base_weight, W, k);
+    TORCH_CHECK(grad_a.dim() == 2 && grad_a.size(0) == W.size(0) && grad_a.size(1) == W.size(1),
+                "edge_abs_mean_x_backward: grad shape");
+    c10::cuda::CUDAGuard guard(x.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const int64_t N = x.size(0), I = x.size(1), O = W.size(0), R = W.size(2);
+    const bool has_base = has(base_weight);
+    Tensor gx, ds, dbw, dW;
+    if (need_x) gx = at::empty({N, I}, x.options());
+    if (need_s && has_base && has(s)) ds = at::empty({N, I}, x.options());
+    if (need_bw && has_base) dbw = at::empty({O, I}, x.options());
+    if (need_W) dW = at::empty({O, I, R}, x.options());
+    const Tensor ga = grad_a.to(x.scalar_type()).contiguous(), xc = x.contiguous(), sc = contig_or_absent(s),
+                 gc = grid.contiguous(), bw = contig_or_absent(base_weight), Wc = W.contiguous();
+    const int code = dtype_code(x);
+    Scratch* ws = scratch(x.device(), st, WS_EDGE_X,
+                          kanb200_workspace_bytes(KANB200_OP_EDGE_X_BWD, KANB200_MODE_AUTO, code, N, I, O, G, (int)k, 0, 0));
+    {
+        ScopedTimer timer("edge_backward", st);
+        check_rc(kanb200_edge_abs_mean_x_backward(code, ga.data_ptr(), xc.data_ptr(), cptr(sc), gc.data_ptr(), cptr(bw),
+                                                  Wc.data_ptr(), mptr(gx), mptr(ds), mptr(dbw), mptr(dW), N, I, O, G,
+                                                  (int)k, ws ? ws->buf.data_ptr() : nullptr,
+                                                  ws ? (size_t)ws->buf.numel() : 0, st));
+    }
+    return std::make_tuple(gx, ds, dbw, dW);
+}
+
+// ------------------------------------------------------------------------------------------------
 // dense differentiable formulas (any device): used while a backward pass is itself being recorded,
 // so that higher-order derivatives are exact (kan_backward_composite, csrc/kan_cpu.cpp:301-345)
 // ------------------------------------------------------------------------------------------------
@@ -768,6 +844,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           },
           py::arg("grad_a"), py::arg("s"), py::arg("H"), py::arg("base_weight"), py::arg("W"), py::arg("need_s"),
           py::arg("need_H"), py::arg("need_bw"), py::arg("need_W"), "(ds|None, dH|None, dbw|None, dW|None)");
+    m.def("edge_abs_mean_x", &edge_abs_mean_x, py::arg("x"), py::arg("s"), py::arg("grid"), py::arg("base_weight"),
+          py::arg("W"), py::arg("spline_order"),
+          "a[o,i] = mean_n |s bw + <B(x), W>| straight from x; s empty = silu(x)");
+    m.def("edge_abs_mean_x_backward",
+          [](const Tensor& ga, const Tensor& x, const Tensor& s, const Tensor& grid, const Tensor& bw, const Tensor& W,
+             int64_t k, bool need_x, bool need_s, bool need_bw, bool need_W) {
+              Tensor gx, ds, dbw, dW;
+              std::tie(gx, ds, dbw, dW) = edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k, need_x, need_s, need_bw, need_W);
+              auto opt = [](const Tensor& t) -> py::object { return t.defined() ? py::cast(t) : py::none(); };
+              return py::make_tuple(opt(gx), opt(ds), opt(dbw), opt(dW));
+          },
+          py::arg("grad_a"), py::arg("x"), py::arg("s"), py::arg("grid"), py::arg("base_weight"), py::arg("W"),
+          py::arg("spline_order"), py::arg("need_x"), py::arg("need_s"), py::arg("need_bw"), py::arg("need_W"),
+          "(gx|None, ds|None, dbw|None, dW|None)");
     m.def("set_basis_impl", [](int impl) { check_rc(kanb200_set_basis_impl(impl)); }, py::arg("impl"));
     m.def("get_basis_impl", []() { return kanb200_get_basis_impl(); });
 

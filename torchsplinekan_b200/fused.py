@@ -73,6 +73,56 @@ class EdgeAbsMean(torch.autograd.Function):
                 dbw if need_bw and has_base else None, dW if need_W else None)
 
 
+class EdgeAbsMeanX(torch.autograd.Function):
+    """Per-edge mean |phi| straight from the layer input: ``a = mean_n |s bw + <B(x), W>|`` with
+    neither phi [N, O, I] nor the basis [N, I, R] stored, forward or backward (the reference builds
+    it from NativeBasis + EdgeAbsMean, spline_kan/kan_linear.py:381-416, and keeps H for backward).
+
+    ``s``: the layer's base values ``base_activation(x)`` as a tensor, or None when the activation
+    is SiLU (the kernels then evaluate it, and its derivative, themselves).
+    """
+
+    @staticmethod
+    def forward(ctx, x, s, grid, k, bw, W):
+        none = x.new_empty(0)
+        ctx.k, ctx.has_s, ctx.has_base = int(k), s is not None, bw is not None
+        ctx.save_for_backward(x, s if s is not None else none, grid, bw if bw is not None else none, W)
+        return _C.edge_abs_mean_x(x, s if s is not None else none, grid, bw if bw is not None else none, W, int(k))
+
+    @staticmethod
+    def backward(ctx, ga):
+        x, s, grid, bw, W = ctx.saved_tensors
+        need_x, need_s, _, _, need_bw, need_W = ctx.needs_input_grad
+        has_s, has_base = ctx.has_s, ctx.has_base
+        if torch.is_grad_enabled():
+            # dense differentiable formulas in the saved inputs themselves (create_graph=True)
+            H = compute_basis(x, grid, ctx.k)
+            sv = (s if has_s else torch.nn.functional.silu(x)) if has_base else None
+            phi = torch.einsum("oir,nir->noi", W, H)
+            if has_base:
+                phi = sv.unsqueeze(1) * bw.unsqueeze(0) + phi
+            g = phi.sign() * ga.unsqueeze(0) / x.shape[0]
+            gx = gs = None
+            if need_x:
+                gx = (torch.einsum("noi,oir->nir", g, W) * compute_basis_derivative(x, grid, ctx.k)).sum(-1)
+                if has_base and not has_s:
+                    sig = torch.sigmoid(x)
+                    gx = gx + (g * bw.unsqueeze(0)).sum(1) * (sig * (1.0 + x * (1.0 - sig)))
+            if need_s and has_s:
+                gs = (g * bw.unsqueeze(0)).sum(1)
+            return (gx, gs, None, None, (g * sv.unsqueeze(1)).sum(0) if need_bw and has_base else None,
+                    torch.einsum("noi,nir->oir", g, H) if need_W else None)
+        gx, ds, dbw, dW = _C.edge_abs_mean_x_backward(ga, x, s, grid, bw, W, ctx.k, bool(need_x),
+                                                      bool(need_s and has_s), bool(need_bw and has_base), bool(need_W))
+        return (gx if need_x else None, ds if (need_s and has_s) else None, None, None,
+                dbw if (need_bw and has_base) else None, dW if need_W else None)
+
+
+def edge_abs_mean_from_input(x: torch.Tensor, s: Optional[torch.Tensor], grid: torch.Tensor, k: int,
+                             bw: Optional[torch.Tensor], W: torch.Tensor) -> torch.Tensor:
+    return EdgeAbsMeanX.apply(x, s, grid, k, bw, W)
+
+
 def native_basis(x: torch.Tensor, grid: torch.Tensor, k: int) -> torch.Tensor:
     return NativeBasis.apply(x, grid, k)
 

@@ -150,8 +150,10 @@ class KANLinear(nn.Module):
         if x is None:
             return self._ref.regularization_loss(reg_act, reg_entropy, x=None)     # canonical error
         xf = x.reshape(-1, self.in_features)
-        s = self._ref.base_activation(xf)
         impl = self._resolve_reg_impl(reg_impl, xf)
+        if impl == "fused":
+            return regularization_from_edge_means(self._edge_abs_mean_from_input(xf), reg_act, reg_entropy)
+        s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         a = self._edge_abs_mean(xf, s, H, self._ref.effective_spline_weight(), impl, chunk_size)
         return regularization_from_edge_means(a, reg_act, reg_entropy)
@@ -178,15 +180,21 @@ class KANLinear(nn.Module):
         lead = x.shape[:-1]
         xf = x.reshape(-1, self.in_features)
         impl = self._resolve_reg_impl(reg_impl, xf)
+        if impl == "fused":
+            # One evaluation of x feeds two native operators and nothing of size [N, I, R] or
+            # [N, O, I] is ever stored: y from the layer kernels (kan_apply), the edge statistic
+            # from the from-x edge kernels.  The parameters receive gradients from both terms, so a
+            # data-parallel gradient sink must not take over the layer's backward.
+            with _C.no_grad_sinks():
+                y = self._cuda_forward(xf)
+            self.last_backend = "cuda"
+            a = self._edge_abs_mean_from_input(xf)
+            return y.reshape(lead + (self.out_features,)), regularization_from_edge_means(a, reg_act, reg_entropy)
         s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         W = self._ref.effective_spline_weight()
-        # y is formed from the same H that feeds the edge statistic, in full float32 like the
-        # reference: with the split-bf16 layer kernels the hidden activations of a deep net move by
-        # a few 1e-5, which flips sign(phi) of near-zero edges in the following layers and shows up
-        # as 5e-4 differences in the penalty's gradient (measured on the 784-256-256-10 net).
         y = F.linear(s, self.base_weight) + F.linear(H.reshape(xf.shape[0], -1), W.reshape(self.out_features, -1))
-        self.last_backend = "cuda" if impl == "fused" else "reference"
+        self.last_backend = "reference"
         a = self._edge_abs_mean(xf, s, H, W, impl, chunk_size)
         return y.reshape(lead + (self.out_features,)), regularization_from_edge_means(a, reg_act, reg_entropy)
 
@@ -202,14 +210,18 @@ class KANLinear(nn.Module):
                                "'checkpoint' instead.")
         return reg_impl
 
+    def _edge_abs_mean_from_input(self, x_flat: torch.Tensor) -> torch.Tensor:
+        """``a [O, I]`` from the native from-x edge kernels.  With SiLU the kernels evaluate the base
+        value (and its derivative) themselves; any other activation is evaluated by PyTorch and its
+        values are handed over, so autograd carries the gradient through it."""
+        s = None if self._native_fuses_base else self._ref.base_activation(x_flat)
+        return _fused.edge_abs_mean_from_input(x_flat, s, self.grid, self.spline_order, self.base_weight,
+                                               self._ref.effective_spline_weight())
+
     def _basis(self, x_flat: torch.Tensor, impl: str) -> torch.Tensor:
-        if impl == "fused":
-            return _fused.native_basis(x_flat, self.grid, self.spline_order)
         return compute_basis(x_flat, self.grid, self.spline_order)
 
     def _edge_abs_mean(self, x_flat, s, H, W, impl, chunk_size):
-        if impl == "fused":
-            return _fused.edge_abs_mean(s, H, self.base_weight, W)
         if impl == "checkpoint":
             if chunk_size < 1:
                 raise ValueError(f"chunk_size must be >= 1, got {chunk_size}")
@@ -222,6 +234,8 @@ class KANLinear(nn.Module):
         """Per-edge L1 norm ``mean_n |phi_{o,i}(x_n)|`` -> [O, I] (kan_linear.py:451-458)."""
         xf = x.reshape(-1, self.in_features)
         impl = self._resolve_reg_impl("auto", xf)
+        if impl == "fused":
+            return self._edge_abs_mean_from_input(xf)       # no basis tensor, nothing saved (no_grad)
         s = self._ref.base_activation(xf)
         return self._edge_abs_mean(xf, s, self._basis(xf, impl), self._ref.effective_spline_weight(), impl, 1024)
 
