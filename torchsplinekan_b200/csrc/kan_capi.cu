@@ -67,6 +67,13 @@ KANB200_API int kanb200_set_basis_impl(int impl) {
 
 KANB200_API int kanb200_get_basis_impl(void) { return g_basis_impl; }
 
+KANB200_API int kanb200_set_accumulation_chunks(int forward_blocks, int param_blocks, int input_blocks) {
+    if (forward_blocks < 0 || param_blocks < 0 || input_blocks < 0)
+        return fail(KANB200_EINVAL, "accumulation chunk lengths must not be negative");
+    tc_set_chunks(forward_blocks, param_blocks, input_blocks);
+    return KANB200_OK;
+}
+
 KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int k, int dtype) {
     if (dtype != KANB200_F32 && dtype != KANB200_F64)
         return fail(KANB200_EINVAL, "only FP32 and FP64 inputs are supported");
@@ -103,6 +110,7 @@ KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, 
 KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k,
                                int need_x, int need_param) {
     if (kanb200_check_shapes(N, I, O, G, k, dtype) != KANB200_OK) return 0;
+    if (N == 0) return 0;                       // an empty batch launches nothing that needs scratch
     LayerShape s;
     make_shape(N, I, O, G, k, s);
     if (op == KANB200_OP_BASIS) {

@@ -84,6 +84,10 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
                         const float* bw, const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,
                         float* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// Shortens the accumulation chains of the tensor-core kernels (values above the built-in lengths
+// are clamped to them; 0 keeps the current value).
+void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb);
+
 // The per-span polynomial table on its own: bytes, floats per feature, and the kernel that fills it.
 size_t tc_table_bytes(const LayerShape& s);
 int tc_table_stride(const LayerShape& s);

@@ -722,6 +722,7 @@ ParamPlan<T> plan_param(const LayerShape& s) {
     if (splits < 1) splits = 1;
     p.n_per_split = (s.N + splits - 1) / splits;
     p.n_per_split = (p.n_per_split + p.tns - 1) / p.tns * p.tns;
+    if (p.n_per_split < p.tns) p.n_per_split = p.tns;          // empty batch: one (empty) split
     p.splits = (int)((s.N + p.n_per_split - 1) / p.n_per_split);
     if (p.splits < 1) p.splits = 1;
     return p;

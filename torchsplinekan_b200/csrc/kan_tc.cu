@@ -939,6 +939,7 @@ struct DxParams {
     int n_ohalves;                 // 128-output groups of the dY image
     int64_t n_blocks64;            // 64-sample blocks of the dY image
     int kb_o;                      // 64-output k-blocks
+    int kb_o_chunk;                // k-blocks accumulated in TMEM before the epilogue adds them to gx
     int n_fgroups;                 // groups of 256 features
     int has_base;
     int64_t n_items;
@@ -996,6 +997,9 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     const int cpf = WIDE ? P.ti.cpf : 1;
     const int sub_spline = 8 * cpf;
     const int n_sub = sub_spline + (P.has_base ? 1 : 0);    // sub-tiles per item
+    // The reduction over the outputs is cut into chunks of kb_o_chunk k-blocks: an item runs its
+    // sub-tiles once per chunk, and every pass after the first adds to gx.
+    const int n_oc = (P.kb_o + P.kb_o_chunk - 1) / P.kb_o_chunk;
     // sub-tile j of feature group fg -> first column block of the weight image, and whether it is
     // the base sub-tile
     auto sub_info = [&](int fg, int j, bool& is_base, int& cb0) {
@@ -1018,7 +1022,8 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
             float* grow = gx + (size_t)(row_ok ? n : 0) * P.I;
             bool ok = true;
-            for (int j = 0; j < n_sub; ++j, ++sub) {
+            for (int pass = 0; pass < n_oc * n_sub; ++pass, ++sub) {
+                const int oc = pass / n_sub, j = pass - oc * n_sub;
                 bool is_base;
                 int cb0;
                 sub_info(fg, j, is_base, cb0);
@@ -1118,10 +1123,15 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
 #pragma unroll
                             for (int e = 0; e < 4; ++e) o[e] = __uint_as_float(r[4 * q + e]) * silu_grad_fast(xv[e]);
                             if (P.vec_ok && f + 4 <= P.I) {
-                                *reinterpret_cast<float4*>(grow + f) = make_float4(o[0], o[1], o[2], o[3]);
+                                float4* dst = reinterpret_cast<float4*>(grow + f);
+                                if (oc > 0) {
+                                    const float4 old = *dst;
+                                    o[0] += old.x; o[1] += old.y; o[2] += old.z; o[3] += old.w;
+                                }
+                                *dst = make_float4(o[0], o[1], o[2], o[3]);
                             } else {
                                 for (int e = 0; e < 4; ++e)
-                                    if (f + e < P.I) grow[f + e] = o[e];
+                                    if (f + e < P.I) grow[f + e] = oc > 0 ? grow[f + e] + o[e] : o[e];
                             }
                         }
                     } else {
@@ -1160,14 +1170,14 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                         }
                         if (P.vec_ok && f0 + 4 <= P.I) {
                             float4* dst = reinterpret_cast<float4*>(grow + f0);
-                            if (P.has_base) {
+                            if (P.has_base || oc > 0) {
                                 const float4 old = *dst;
                                 o[0] += old.x; o[1] += old.y; o[2] += old.z; o[3] += old.w;
                             }
                             *dst = make_float4(o[0], o[1], o[2], o[3]);
                         } else {
                             for (int e = 0; e < 4; ++e)
-                                if (f0 + e < P.I) grow[f0 + e] = P.has_base ? grow[f0 + e] + o[e] : o[e];
+                                if (f0 + e < P.I) grow[f0 + e] = (P.has_base || oc > 0) ? grow[f0 + e] + o[e] : o[e];
                         }
                     }
                 }
@@ -1186,7 +1196,9 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             uint32_t it = 0, bslot = 0, sub = 0;
             bool ok = true;
             for (int64_t item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
-                for (int j = 0; j < n_sub && ok; ++j, ++sub) {
+                for (int pass = 0; pass < n_oc * n_sub && ok; ++pass, ++sub) {
+                    const int oc = pass / n_sub;
+                    const int ko0 = oc * P.kb_o_chunk, ko1 = (ko0 + P.kb_o_chunk < P.kb_o) ? ko0 + P.kb_o_chunk : P.kb_o;
                     const uint32_t buf = sub & 1u;
                     if (!mbar_wait(smem_u32(&ctrl->accEmpty[buf]), ((sub >> 1) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
@@ -1194,7 +1206,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                     }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
-                    for (int ko = 0; ko < P.kb_o; ++ko, ++it) {
+                    for (int ko = ko0; ko < ko1; ++ko, ++it) {
                         const uint32_t stage = it % DX_A_STAGES;
                         const uint32_t a_hi = sbase + DX_SMEM_A + stage * DX_A_STAGE_BYTES;
                         const uint32_t a_lo = a_hi + TILE_A_BYTES;
@@ -1209,7 +1221,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
 #pragma unroll
                         for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
                             mma_f16_ss(d_tmem, sdesc_at(da, a_hi + ks * 32), sdesc_at(db, b_hi + ks * 2048), idesc,
-                                       (ko > 0 || ks > 0) ? 1u : 0u);
+                                       (ko > ko0 || ks > 0) ? 1u : 0u);
                         if (SPLIT) {
 #pragma unroll
                             for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
@@ -1247,11 +1259,13 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             for (int64_t item = blockIdx.x; item < P.n_items && ok; item += gridDim.x) {
                 const int64_t mt = item / P.n_fgroups;
                 const int fg = (int)(item - mt * P.n_fgroups);
-                for (int j = 0; j < n_sub && ok; ++j) {
+                for (int pass = 0; pass < n_oc * n_sub && ok; ++pass) {
+                    const int oc = pass / n_sub, j = pass - oc * n_sub;
+                    const int ko0 = oc * P.kb_o_chunk, ko1 = (ko0 + P.kb_o_chunk < P.kb_o) ? ko0 + P.kb_o_chunk : P.kb_o;
                     bool is_base;
                     int cb0;
                     sub_info(fg, j, is_base, cb0);
-                    for (int ko = 0; ko < P.kb_o && ok; ++ko, ++it) {
+                    for (int ko = ko0; ko < ko1 && ok; ++ko, ++it) {
                         // A: 128 samples x 64 outputs = two 64-sample blocks of the dY image
                         const uint32_t stage = it % DX_A_STAGES;
                         if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / DX_A_STAGES) & 1u) ^ 1u, abort_flag)) {
@@ -1452,10 +1466,13 @@ finalize_wide_kernel(const float* __restrict__ partial, BwdPlan plan, int cpf,
 // operand-split error (measured against float64: forward chains of 144 column blocks and backward
 // chains of 16 blocks of 64 samples stay within 1e-5 of max|result|; 32 / 64 sample blocks give
 // 8e-6 / 1.4e-5).  They are part of the numerical contract and therefore not tunable at run time.
-constexpr int kFwdChunkKb = 144;
-constexpr int kBwdChunkKb = 16;
-inline int fwd_chunk_kb() { return kFwdChunkKb; }
-inline int bwd_chunk_kb() { return kBwdChunkKb; }
+constexpr int kFwdChunkKb = 144;      // forward: 64-column blocks per chain
+constexpr int kBwdChunkKb = 16;       // parameter gradients: 64-sample blocks per chain
+constexpr int kDxChunkKb = 32;        // input gradient: 64-output blocks per chain
+int g_fwd_chunk = kFwdChunkKb, g_bwd_chunk = kBwdChunkKb, g_dx_chunk = kDxChunkKb;
+inline int fwd_chunk_kb() { return g_fwd_chunk; }
+inline int bwd_chunk_kb() { return g_bwd_chunk; }
+inline int dx_chunk_kb() { return g_dx_chunk; }
 
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     BwdPlan p;
@@ -1516,6 +1533,15 @@ size_t tc_table_bytes(const LayerShape& s) { return table_bytes(s); }
 int tc_table_stride(const LayerShape& s) { return make_tab_info(s.G, s.K).fs; }
 cudaError_t tc_build_table(const float* grid, float* tab, const LayerShape& s, cudaStream_t st) {
     return launch_table(grid, tab, s, st);
+}
+
+// Shorter accumulation chains (never longer than the built-in lengths, so the stated tolerance
+// always holds); 0 keeps a value.
+void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb) {
+    auto clamp = [](int v, int cur, int max) { return v <= 0 ? cur : (v < 1 ? 1 : (v > max ? max : v)); };
+    g_fwd_chunk = clamp(fwd_kb, g_fwd_chunk, kFwdChunkKb);
+    g_bwd_chunk = clamp(bwd_kb, g_bwd_chunk, kBwdChunkKb);
+    g_dx_chunk = clamp(dx_kb, g_dx_chunk, kDxChunkKb);
 }
 
 bool tc_supported(const LayerShape& s) {
@@ -1668,6 +1694,7 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
         P.n_otiles = F.n_otiles; P.n_ohalves = L.plan.n_otiles * 2;
         P.n_blocks64 = L.plan.kb_total;
         P.kb_o = (s.O + BLOCK_K - 1) / BLOCK_K;
+        P.kb_o_chunk = dx_chunk_kb();
         P.n_fgroups = (s.I + 255) / 256;
         P.has_base = has_base ? 1 : 0;
         P.n_items = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_fgroups;
