@@ -528,6 +528,378 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
 }
 
 // ---------------------------------------------------------------------------
+// Forward kernel on CTA pairs:  y[n, o] = sum_c A[n, c] W[o, c]
+// ---------------------------------------------------------------------------
+// Two CTAs of a cluster run every MMA together (tcgen05 cta_group::2): the pair's tile is 256
+// samples x up to 512 outputs, each CTA generates the A tile of its own 128 samples and stages
+// HALF of every weight tile (128 of the 256 output rows), so per MMA a CTA's tensor core reads
+// 4 KB + 4 KB of shared memory instead of 4 KB + 8 KB and the bulk-copy traffic per CTA halves:
+// the single-CTA kernel spends more shared-memory bandwidth on operand reads and tile writes per
+// k-block (448 KB) than its MMAs take time for (3072 cycles x 128 B).  The even CTA (leader) issues
+// the MMAs; the odd CTA's MMA warp instead forwards "my A stage / B slot is ready" to the leader's
+// barriers; tcgen05.commit releases stages and slots in both CTAs at once.
+constexpr int PF_A_STAGES = 3, PF_B_SLOTS = 8;
+constexpr uint32_t PF_B_SLOT_BYTES = TILE_B_BYTES / 2;                     // 128 output rows x 128 B
+constexpr uint32_t PF_SMEM_A = 0;
+constexpr uint32_t PF_SMEM_B = PF_SMEM_A + PF_A_STAGES * FWD_A_STAGE_BYTES;
+constexpr uint32_t PF_SMEM_CTRL = PF_SMEM_B + PF_B_SLOTS * PF_B_SLOT_BYTES;
+constexpr uint32_t PF_CTRL_BYTES = 512 + TAB_SMEM_FLOATS * 4;
+constexpr uint32_t PF_SMEM_BYTES = PF_SMEM_CTRL + PF_CTRL_BYTES;
+static_assert(PF_SMEM_BYTES <= 232448, "pair forward kernel shared memory exceeds 227 KB");
+
+struct PairFwdCtrl {
+    uint64_t fullA[PF_A_STAGES], emptyA[PF_A_STAGES], peerA[PF_A_STAGES];
+    uint64_t fullB[PF_B_SLOTS], emptyB[PF_B_SLOTS], peerB[PF_B_SLOTS];
+    uint64_t chunkFull, drained, peerDrained;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(PairFwdCtrl) <= 512, "control block too large");
+
+template <int NTERMS, bool WIDE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
+                       float* __restrict__ y, int* __restrict__ status, const FwdParams P) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr bool SPLIT = (NTERMS == 3);
+    const uint32_t sbase = smem_u32(smem);
+    PairFwdCtrl* ctrl = reinterpret_cast<PairFwdCtrl*>(smem + PF_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + PF_SMEM_CTRL + 512);
+    volatile int* abort_flag = &ctrl->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();              // 0 = leader (issues the MMAs), 1 = peer
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const bool shared_grid = grid_is_shared(tab, P.I, P.ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
+
+    const bool bad_smem = (sbase & 1023u) != 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PF_A_STAGES; ++s) {
+            mbar_init(smem_u32(&ctrl->fullA[s]), WORKER_THREADS);
+            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
+            mbar_init(smem_u32(&ctrl->peerA[s]), 1);
+        }
+        for (int s = 0; s < PF_B_SLOTS; ++s) {
+            mbar_init(smem_u32(&ctrl->fullB[s]), 1);
+            mbar_init(smem_u32(&ctrl->emptyB[s]), 1);
+            mbar_init(smem_u32(&ctrl->peerB[s]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->chunkFull), 1);
+        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
+        mbar_init(smem_u32(&ctrl->peerDrained), 1);
+        ctrl->abort_flag = bad_smem ? 1 : 0;
+        fence_mbar_init();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc_pair(smem_u32(&ctrl->tmem_base), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                     // both CTAs' barriers exist before anyone arrives remotely
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    if (bad_smem && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+
+    // pair tile -> (256-sample tile, pair of 256-output tiles)
+    const int64_t n_ptiles = ((P.N + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * P.n_opairs;
+
+    if (warp < WORKER_WARPS) {
+        // ===== workers: x -> basis / silu -> swizzled A tile of this CTA's 128 samples; drains =====
+        const int quad = warp & 3;
+        const int part = warp >> 2;
+        const int row = quad * 32 + lane;
+        uint32_t it = 0, n_drained = 0;
+        bool ok = !bad_smem;
+        bool pend = false, pend_first = false;
+        int64_t pend_mt = 0;
+        int pend_op = 0;
+
+        auto drain = [&]() -> bool {
+            if (!mbar_wait_cluster(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
+            ++n_drained;
+            tc_fence_after_sync();
+            const int64_t n = pend_mt * (2 * BLOCK_M) + rank * BLOCK_M + row;
+            const int nsub = (P.n_otiles - 2 * pend_op) >= 2 ? 2 : 1;
+#pragma unroll 1
+            for (int c = part; c < nsub * (BLOCK_N / 32); c += 4) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = pend_op * 2 * BLOCK_N + c * 32;
+                if (n < P.N && col0 < P.O)
+                    drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
+            }
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctrl->drained));
+            pend = false;
+            return true;
+        };
+
+        for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
+            const int64_t mt = tile / P.n_opairs;
+            const int op = (int)(tile - mt * P.n_opairs);
+            const int64_t n = mt * (2 * BLOCK_M) + rank * BLOCK_M + row;
+            const bool row_ok = n < P.N;
+            const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
+            const int cpf = WIDE ? P.ti.cpf : 1;
+            float nx0 = 0.f, nx1 = 0.f;
+            auto chunk_pair = [&](int kb, int& f0, int& cw0, int& f1, int& cw1) {
+                const int g0 = kb * 8 + part * 2;
+                if (!WIDE) {
+                    f0 = g0; cw0 = 0; f1 = g0 + 1; cw1 = 0;
+                } else {
+                    f0 = g0 / cpf; cw0 = g0 - f0 * cpf;
+                    f1 = f0; cw1 = cw0 + 1;
+                    if (cw1 == cpf) { f1 = f0 + 1; cw1 = 0; }
+                }
+            };
+            auto prefetch_spline = [&](int kb) {
+                int f0, cw0, f1, cw1;
+                chunk_pair(kb, f0, cw0, f1, cw1);
+                if (!WIDE && P.vec_x2 && row_ok && f0 + 1 < P.I) {
+                    const float2 v = __ldg(reinterpret_cast<const float2*>(xrow + f0));
+                    nx0 = v.x;
+                    nx1 = v.y;
+                } else {
+                    nx0 = (row_ok && f0 < P.I) ? __ldg(xrow + f0) : 0.f;
+                    nx1 = (row_ok && f1 < P.I) ? __ldg(xrow + f1) : 0.f;
+                }
+            };
+            if (P.kb_spline > 0) prefetch_spline(0);
+            for (int kb = 0; kb < P.kb_total; ++kb, ++it) {
+                const uint32_t stage = it % PF_A_STAGES;
+                const uint32_t a_hi = sbase + PF_SMEM_A + stage * FWD_A_STAGE_BYTES;
+                const uint32_t a_lo = a_hi + TILE_A_BYTES;
+                const bool chunk_start = (kb % P.chunk_kb) == 0;
+                const uint32_t empty_parity = ((it / PF_A_STAGES) & 1u) ^ 1u;
+                if (kb < P.kb_spline) {
+                    int f0, cw0, f1, cw1;
+                    chunk_pair(kb, f0, cw0, f1, cw1);
+                    const float x0 = nx0, x1 = nx1;
+                    if (kb + 1 < P.kb_spline) prefetch_spline(kb + 1);
+                    const bool ok0 = row_ok && f0 < P.I, ok1 = row_ok && f1 < P.I;
+                    const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * P.ti.fs;
+                    const float* t1 = tab + (size_t)(f1 < P.I ? f1 : P.I - 1) * P.ti.fs;
+                    uint4 hi0, lo0, hi1, lo1;
+                    Window w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x0)
+                                           : eval_window<SPLIT, false, WIDE>(t0, P.ti, x0);
+                    place_window<SPLIT>(w, cw0, hi0, lo0);
+                    if (!WIDE || f1 != f0)
+                        w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x1)
+                                        : eval_window<SPLIT, false, WIDE>(t1, P.ti, x1);
+                    place_window<SPLIT>(w, cw1, hi1, lo1);
+                    if (!mbar_wait_cluster(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint4 zero = make_uint4(0, 0, 0, 0);
+                    const uint32_t off0 = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2));
+                    const uint32_t off1 = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2 + 1));
+                    st_shared_v4(a_hi + off0, ok0 ? hi0 : zero);
+                    st_shared_v4(a_hi + off1, ok1 ? hi1 : zero);
+                    if (SPLIT) {
+                        st_shared_v4(a_lo + off0, ok0 ? lo0 : zero);
+                        st_shared_v4(a_lo + off1, ok1 ? lo1 : zero);
+                    }
+                } else {
+                    const int f0 = (kb - P.kb_spline) * 64 + part * 16;
+                    float xv[2][8];
+                    load_x8(x, n, row_ok, P.I, f0, P.vec_x != 0, xv[0]);
+                    load_x8(x, n, row_ok, P.I, f0 + 8, P.vec_x != 0, xv[1]);
+                    if (!mbar_wait_cluster(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint4 hi, lo;
+                        silu_chunk<SPLIT>(xv[c], hi, lo);
+                        const uint32_t off = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2 + c));
+                        st_shared_v4(a_hi + off, hi);
+                        if (SPLIT) st_shared_v4(a_lo + off, lo);
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ctrl->fullA[stage]));
+                if (pend && chunk_start) {
+                    if (!drain()) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                    pend = true;
+                    pend_first = kb < P.chunk_kb;
+                    pend_mt = mt;
+                    pend_op = op;
+                }
+            }
+        }
+        if (ok && pend) drain();
+    } else if (warp == MMA_WARP) {
+        if (lane == 0 && !bad_smem) {
+            if (rank == 0) {
+                // ===== leader: MMA issue for the pair =====
+                constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, false, false, 2 * BLOCK_M);
+                constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
+                uint32_t it = 0, bslot = 0, n_chunks = 0;
+                bool ok = true;
+                auto wait_b = [&](uint32_t slot, uint32_t parity) -> bool {
+                    return mbar_wait(smem_u32(&ctrl->fullB[slot]), parity, abort_flag) &&
+                           mbar_wait_cluster(smem_u32(&ctrl->peerB[slot]), parity, abort_flag);
+                };
+                for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
+                    const int op = (int)(tile % P.n_opairs);
+                    const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
+                    for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
+                        const uint32_t stage = it % PF_A_STAGES;
+                        const uint32_t a_hi = sbase + PF_SMEM_A + stage * FWD_A_STAGE_BYTES;
+                        const uint32_t a_lo = a_hi + TILE_A_BYTES;
+                        const bool chunk_start = (kb % P.chunk_kb) == 0;
+                        if (chunk_start && n_chunks > 0) {
+                            // both CTAs must have drained their half of the accumulator
+                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag) ||
+                                !mbar_wait_cluster(smem_u32(&ctrl->peerDrained), (n_chunks - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                        }
+                        const uint32_t a_parity = (it / PF_A_STAGES) & 1u;
+                        if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), a_parity, abort_flag) ||
+                            !mbar_wait_cluster(smem_u32(&ctrl->peerA[stage]), a_parity, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        for (int j = 0; j < nsub && ok; ++j) {
+                            const uint32_t d_tmem = tmem_base + j * BLOCK_N;
+                            const uint32_t slot_h = bslot % PF_B_SLOTS;
+                            if (!wait_b(slot_h, (bslot / PF_B_SLOTS) & 1u)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t b_hi = sbase + PF_SMEM_B + slot_h * PF_B_SLOT_BYTES;
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ss_pair(d_tmem, sdesc_at(dbase, a_hi + ks * 32), sdesc_at(dbase, b_hi + ks * 32),
+                                                idesc, (!chunk_start || ks > 0) ? 1u : 0u);
+                            if (SPLIT) {
+#pragma unroll
+                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, a_lo + ks * 32),
+                                                    sdesc_at(dbase, b_hi + ks * 32), idesc, 1u);
+                            }
+                            mma_commit_pair(smem_u32(&ctrl->emptyB[slot_h]));
+                            ++bslot;
+                            if (SPLIT) {
+                                const uint32_t slot_l = bslot % PF_B_SLOTS;
+                                if (!wait_b(slot_l, (bslot / PF_B_SLOTS) & 1u)) {
+                                    ok = false;
+                                    break;
+                                }
+                                tc_fence_after_sync();
+                                const uint32_t b_lo = sbase + PF_SMEM_B + slot_l * PF_B_SLOT_BYTES;
+#pragma unroll
+                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, a_hi + ks * 32),
+                                                    sdesc_at(dbase, b_lo + ks * 32), idesc, 1u);
+                                mma_commit_pair(smem_u32(&ctrl->emptyB[slot_l]));
+                                ++bslot;
+                            }
+                        }
+                        if (!ok) break;
+                        mma_commit_pair(smem_u32(&ctrl->emptyA[stage]));
+                        if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                            mma_commit_pair(smem_u32(&ctrl->chunkFull));
+                            ++n_chunks;
+                        }
+                    }
+                }
+            } else {
+                // ===== peer: forwards the readiness of its own stages / slots / drains to the leader,
+                // in the order the leader consumes them =====
+                const uint32_t l_peerDrained = map_to_cta(smem_u32(&ctrl->peerDrained), 0);
+                uint32_t it = 0, bslot = 0, n_chunks = 0;
+                bool ok = true;
+                for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
+                    const int op = (int)(tile % P.n_opairs);
+                    const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
+                    for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
+                        const uint32_t stage = it % PF_A_STAGES;
+                        const bool chunk_start = (kb % P.chunk_kb) == 0;
+                        if (chunk_start && n_chunks > 0) {
+                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_remote(l_peerDrained);
+                        }
+                        if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / PF_A_STAGES) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerA[stage]), 0));
+                        for (int s = 0; s < nsub * (SPLIT ? 2 : 1); ++s, ++bslot) {
+                            const uint32_t slot = bslot % PF_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->fullB[slot]), (bslot / PF_B_SLOTS) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerB[slot]), 0));
+                        }
+                        if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) ++n_chunks;
+                    }
+                }
+            }
+        }
+    } else {
+        if (lane == 0 && !bad_smem) {
+            // ===== bulk copies: this CTA's half (128 output rows) of every weight tile =====
+            uint32_t bslot = 0;
+            bool ok = true;
+            for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
+                const int op = (int)(tile % P.n_opairs);
+                const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
+                for (int kb = 0; kb < P.kb_total && ok; ++kb) {
+                    for (int j = 0; j < nsub && ok; ++j) {
+                        const uint8_t* src = wimg + ((size_t)(2 * op + j) * P.kb_total + kb) * (2 * (size_t)TILE_B_BYTES) +
+                                             (size_t)rank * PF_B_SLOT_BYTES;
+                        for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
+                            const uint32_t slot = bslot % PF_B_SLOTS;
+                            if (!mbar_wait_cluster(smem_u32(&ctrl->emptyB[slot]), ((bslot / PF_B_SLOTS) & 1u) ^ 1u,
+                                                   abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
+                            mbar_arrive_expect_tx(bar, PF_B_SLOT_BYTES);
+                            bulk_g2s(sbase + PF_SMEM_B + slot * PF_B_SLOT_BYTES, src + (size_t)term * TILE_B_BYTES,
+                                     PF_B_SLOT_BYTES, bar);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ===== teardown: neither CTA may leave while the other can still signal its barriers =====
+    if (*abort_flag && !bad_smem) {
+        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Parameter-gradient kernel:  D[o, c] = sum_n dY[n, o] A[n, c]
 // ---------------------------------------------------------------------------
 // Work item = (output tile of 256, column tile of 256, sample split).  The
@@ -1463,16 +1835,56 @@ finalize_wide_kernel(const float* __restrict__ partial, BwdPlan plan, int cpf,
 
 // Chunk lengths (k-blocks accumulated in TMEM between drains).  Every tensor-core accumulation
 // truncates, so the error of a chain grows with its length; these lengths keep it below the
-// operand-split error (measured against float64: forward chains of 144 column blocks and backward
-// chains of 16 blocks of 64 samples stay within 1e-5 of max|result|; 32 / 64 sample blocks give
-// 8e-6 / 1.4e-5).  They are part of the numerical contract and therefore not tunable at run time.
-constexpr int kFwdChunkKb = 144;      // forward: 64-column blocks per chain
+// operand-split error.  Measured against float64 (max-norm relative):
+//   forward, 1024 features (144 column blocks, one chain): 5.4e-6;  4096 features (576 blocks):
+//     chains of 144 / 72 / 48 / 36 / 24 blocks give 1.55e-5 / 1.5e-5 / 9.8e-6 / 8.5e-6 / 5.4e-6, at
+//     0 / 6 / 13 / 19 / 33 % more time -> layers beyond 144 blocks use chains of 36;
+//   parameter gradients, 65536 samples: chains of 16 / 32 / 64 blocks of 64 samples give 5.4e-6 /
+//     8.4e-6 / 1.4e-5;
+//   input gradient, 4096 outputs (64 blocks): one chain 1.5e-5, chains of 32 / 24 / 16 / 8 blocks
+//     8.5e-6 / 6.3e-6 / 6.7e-6 / 4.7e-6 (1024 outputs, 16 blocks: 5.9e-6, unaffected).
+// They are part of the numerical contract; kanb200_set_accumulation_chunks can only shorten them.
+constexpr int kFwdChunkKb = 144;      // forward: 64-column blocks per chain (layers of up to 144 blocks)
+constexpr int kFwdChunkWideKb = 36;   // forward: layers with more than 144 column blocks
 constexpr int kBwdChunkKb = 16;       // parameter gradients: 64-sample blocks per chain
-constexpr int kDxChunkKb = 32;        // input gradient: 64-output blocks per chain
+constexpr int kDxChunkKb = 24;        // input gradient: 64-output blocks per chain
 int g_fwd_chunk = kFwdChunkKb, g_bwd_chunk = kBwdChunkKb, g_dx_chunk = kDxChunkKb;
-inline int fwd_chunk_kb() { return g_fwd_chunk; }
+inline int fwd_chunk_kb(int kb_total) {
+    const int wide = g_fwd_chunk < kFwdChunkWideKb ? g_fwd_chunk : kFwdChunkWideKb;
+    return kb_total <= kFwdChunkKb ? g_fwd_chunk : wide;
+}
 inline int bwd_chunk_kb() { return g_bwd_chunk; }
 inline int dx_chunk_kb() { return g_dx_chunk; }
+
+// 1 = the kernels that run on CTA pairs (clusters of two, tcgen05 cta_group::2) where they exist.
+int g_pair_kernels = 1;
+
+// Launches `kernel` as clusters of two CTAs: min(items, co-resident clusters) of them.
+// cudaErrorNotSupported when not even one cluster fits (the caller falls back to single CTAs).
+template <typename Kernel, typename... Args>
+cudaError_t launch_pairs(Kernel kernel, int64_t items, uint32_t smem_bytes, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cfg.gridDim = dim3(2);
+    int max_clusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+    if (e != cudaSuccess || max_clusters < 1) {
+        cudaGetLastError();
+        return cudaErrorNotSupported;
+    }
+    const int64_t pairs = items < max_clusters ? items : max_clusters;
+    cfg.gridDim = dim3((unsigned)(2 * pairs));
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
 
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     BwdPlan p;
@@ -1544,6 +1956,9 @@ void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb) {
     g_dx_chunk = clamp(dx_kb, g_dx_chunk, kDxChunkKb);
 }
 
+void tc_set_pair_kernels(int on) { g_pair_kernels = on ? 1 : 0; }
+int tc_get_pair_kernels() { return g_pair_kernels; }
+
 bool tc_supported(const LayerShape& s) {
     // any grid the layer accepts (G + 2 K <= 71); the window of k + 1 <= 4 values is what the
     // table entries hold
@@ -1589,13 +2004,32 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     P.kb_spline = L.cs.kb_spline; P.kb_total = kb_total;
     P.n_otiles = L.n_otiles; P.n_opairs = (L.n_otiles + 1) / 2;
     P.n_tiles = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_opairs;
-    P.chunk_kb = fwd_chunk_kb();
+    P.chunk_kb = fwd_chunk_kb(kb_total);
     P.vec_x = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     P.vec_x2 = ((s.I & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 7) == 0);
     P.vec_y = ((s.O & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
     P.ti = ti;
-    const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
     cudaError_t e = cudaSuccess;
+    if (g_pair_kernels) {
+        // CTA pairs: tile = 256 samples x 512 outputs, one cluster of two CTAs each
+        const int64_t n_ptiles = ((s.N + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * P.n_opairs;
+#define KAN_FWD_PAIR(NT, W)                                                                                   \
+    do {                                                                                                      \
+        e = ensure_dynamic_smem<tc_forward_pair_kernel<NT, W>>((int)PF_SMEM_BYTES);                           \
+        if (e == cudaSuccess)                                                                                 \
+            e = launch_pairs(tc_forward_pair_kernel<NT, W>, n_ptiles, PF_SMEM_BYTES, st, x,                   \
+                             (const float*)tab, (const uint8_t*)wimg, y, status, P);                          \
+    } while (0)
+        if (ti.cpf == 1) {
+            if (split_terms == 3) KAN_FWD_PAIR(3, false); else KAN_FWD_PAIR(1, false);
+        } else {
+            if (split_terms == 3) KAN_FWD_PAIR(3, true); else KAN_FWD_PAIR(1, true);
+        }
+#undef KAN_FWD_PAIR
+        if (e != cudaErrorNotSupported) return e != cudaSuccess ? e : cudaGetLastError();
+        e = cudaSuccess;                 // no room for a single cluster: the single-CTA kernel runs
+    }
+    const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
 #define KAN_FWD(NT, W)                                                                                         \
     do {                                                                                                      \
         e = ensure_dynamic_smem<tc_forward_kernel<NT, W>>((int)FWD_SMEM_BYTES);                               \

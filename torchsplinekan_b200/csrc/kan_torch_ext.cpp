@@ -14,6 +14,10 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda_runtime.h>
 
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
 #include <atomic>
 #include <cstdlib>
 #include <map>
@@ -84,33 +88,48 @@ struct Scratch {
 std::mutex g_ws_mutex;
 std::map<std::tuple<int, int64_t, int>, Scratch> g_ws;
 
-void raise_if_reported(Scratch& s, cudaStream_t st) {
+// True when the pinned copy of the status word shows that an earlier kernel on this buffer gave up
+// a bounded wait; the pinned copy is reset (the device word is cleared by the caller's check).
+bool reported(Scratch& s) {
     if (s.mirror && *reinterpret_cast<volatile int*>(s.mirror) != 0) {
         *s.mirror = 0;
-        const int rc = kanb200_check_status(s.buf.data_ptr(), st);     // synchronises, clears the device word
-        if (rc != KANB200_OK) check_rc(rc);
-        TORCH_CHECK(false, "kan_b200: an earlier tensor-core kernel on this stream gave up a bounded wait; "
-                           "its outputs are incomplete");
+        return true;
     }
+    return false;
 }
 
+// Never throws while the registry lock is held: a pending report comes back in `pending`.
 Scratch* scratch(const c10::Device& dev, cudaStream_t st, int purpose, size_t bytes) {
     if (bytes == 0) return nullptr;
-    std::lock_guard<std::mutex> lock(g_ws_mutex);
-    auto key = std::make_tuple((int)dev.index(), (int64_t)reinterpret_cast<intptr_t>(st), purpose);
-    Scratch& s = g_ws[key];
-    if (!s.buf.defined() || (size_t)s.buf.numel() < bytes) {
-        if (s.buf.defined()) raise_if_reported(s, st);
-        s.buf = at::empty({(int64_t)bytes + 256}, at::TensorOptions().dtype(at::kByte).device(dev));
-        C10_CUDA_CHECK(cudaMemsetAsync(s.buf.data_ptr(), 0, 256, st));
-        if (!s.mirror) {
-            C10_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&s.mirror), sizeof(int), cudaHostAllocDefault));
-            *s.mirror = 0;
+    Scratch* out = nullptr;
+    bool pending = false;
+    void* old_buf = nullptr;
+    Tensor keep_alive;
+    {
+        std::lock_guard<std::mutex> lock(g_ws_mutex);
+        auto key = std::make_tuple((int)dev.index(), (int64_t)reinterpret_cast<intptr_t>(st), purpose);
+        Scratch& s = g_ws[key];
+        if (s.buf.defined()) pending = reported(s);
+        if (pending) {
+            keep_alive = s.buf;
+            old_buf = s.buf.data_ptr();
         }
-    } else {
-        raise_if_reported(s, st);
+        if (!s.buf.defined() || (size_t)s.buf.numel() < bytes) {
+            s.buf = at::empty({(int64_t)bytes + 256}, at::TensorOptions().dtype(at::kByte).device(dev));
+            C10_CUDA_CHECK(cudaMemsetAsync(s.buf.data_ptr(), 0, 256, st));
+            if (!s.mirror) {
+                C10_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&s.mirror), sizeof(int), cudaHostAllocDefault));
+                *s.mirror = 0;
+            }
+        }
+        out = &s;
     }
-    return &s;
+    if (pending) {
+        kanb200_check_status(old_buf, st);          // synchronises and clears the device word
+        TORCH_CHECK(false, "kan_b200: an earlier tensor-core kernel on this stream gave up a bounded wait "
+                           "(its outputs are incomplete); the status has been cleared");
+    }
+    return out;
 }
 
 inline void mirror_status(Scratch* s, cudaStream_t st) {
@@ -145,6 +164,22 @@ void poke_status(int purpose, int code) {
     TORCH_CHECK(it != g_ws.end() && it->second.buf.defined(), "no such workspace yet");
     C10_CUDA_CHECK(cudaMemcpyAsync(it->second.buf.data_ptr(), &code, sizeof(int), cudaMemcpyHostToDevice, st));
     C10_CUDA_CHECK(cudaStreamSynchronize(st));
+}
+
+// Debugging aid (environment variable KAN_B200_BACKTRACE): native frames on a fatal signal.
+void backtrace_on_signal(int sig) {
+    void* frames[64];
+    const int n = backtrace(frames, 64);
+    const char msg[] = "kan_b200: fatal signal, native frames:\n";
+    if (write(2, msg, sizeof(msg) - 1) < 0) {}
+    backtrace_symbols_fd(frames, n, 2);
+    signal(sig, SIG_DFL);
+    raise(sig);
+}
+void install_backtrace_handler() {
+    signal(SIGSEGV, backtrace_on_signal);
+    signal(SIGFPE, backtrace_on_signal);
+    signal(SIGABRT, backtrace_on_signal);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -798,6 +833,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.attr("CUDA_MAX_IN_FEATURES") = KANB200_MAX_IN_FEATURES;
     m.attr("HAS_FUSED_KERNELS") = true;
     m.attr("TORCH_OPS_REGISTERED") = true;
+    if (std::getenv("KAN_B200_BACKTRACE")) install_backtrace_handler();
     if (const char* env = std::getenv("KAN_B200_MODE")) {
         const int mode = mode_from_name(env);
         if (mode >= 0) g_mode.store(mode);
