@@ -73,8 +73,8 @@ KANB200_API int kanb200_get_basis_impl(void);
 
 /* The tensor-core accumulator truncates on every accumulation, so long reductions are cut into
  * chains whose partial results are added in float32 with round-to-nearest.  The built-in chain
- * lengths (forward: 144 blocks of 64 columns, 36 for layers wider than that; parameter gradients:
- * 16 blocks of 64 samples; input gradient: 24 blocks of 64 outputs) hold the stated 1e-5 tolerance.  This call can only SHORTEN
+ * lengths (forward: 24 blocks of 64 columns; parameter gradients: 16 blocks of 64 samples; input
+ * gradient: 24 blocks of 64 outputs) hold the stated 1e-5 tolerance.  This call can only SHORTEN
  * them (larger values are clamped, 0 keeps a value): more accurate, slightly slower.  Process-wide.
  * No counterpart in the reference (its GEMMs are cuBLAS calls). */
 KANB200_API int kanb200_set_accumulation_chunks(int forward_blocks, int param_blocks, int input_blocks);

@@ -210,12 +210,16 @@ def test_mnist_shaped_step_with_updated_grid():
     print("dense32 vs dense64", dense_gap)
     # y and the penalty itself are smooth in the rounding error.
     assert errs["y"] < 5e-5 and errs["reg"] < 5e-5, errs
-    # The penalty's gradient contains sign(phi): where |phi| is at rounding level two float32
-    # evaluations (or float32 and float64) disagree on the sign, which moves single entries by
-    # 2 ga / N.  The native result must therefore be as close to float64 as the dense float32
-    # evaluation of the same expression is (factor 3 of slack), not closer than rounding allows.
-    for n in names:
-        assert errs[n] < max(5e-5, 3.0 * dense_gap[n]), (n, errs[n], dense_gap[n])
+    # The penalty's gradient contains sign(phi): where |phi| is at rounding level two evaluations
+    # disagree on the sign, and every such flip moves the entries of one edge by up to 2 ga / N --
+    # 2e-3 of the largest possible entry at 1024 rows, whatever the arithmetic (float32 against
+    # float64 dense PyTorch shows the same).  Flips are discrete, so the max-norm is held to the
+    # dense float32 gap with slack OR a few flips' worth, and the relative L2 norm (which single
+    # entries hardly move, but a wrong kernel would) to 2e-3.
+    n_rows = x.shape[0]
+    for n, a, b in zip(names, got, want):
+        assert errs[n] < max(5e-5, 3.0 * dense_gap[n], 5.0 / n_rows), (n, errs[n], dense_gap[n])
+        assert float((a.double() - b).norm() / b.norm()) < 2e-3, n
     # plain forward/backward goes through kan_apply (tensor cores for the two wide layers)
     for p in net.parameters():
         p.grad = None

@@ -63,6 +63,14 @@ def test_mode_resolution_and_workspace_sizes():
     assert _native.workspace_bytes(_native.OP_EDGE_BWD, _native.MODE_SIMT, f64, 1024, 16, 8, 7, 1) > 0
 
 
+def test_operator_errors_carry_numbers():
+    """Messages built from numbers (sizes, limits) come out of the compiled operator layer intact
+    -- a module linked against a foreign C++ runtime crashes exactly there."""
+    z = torch.zeros
+    with pytest.raises(RuntimeError, match=r"spline_weight.size\(2\)=7 but grid implies R=G\+k=8"):
+        _C.kan_forward(z(4, 3), z(3, 12), z(5, 3), z(5, 3, 7), z(5, 3), 3, True)
+
+
 def test_cpu_tensors_are_rejected_not_emulated():
     L = sk.KANLinear(4, 3, backend="cuda")
     with pytest.raises(RuntimeError, match="CPU tensor"):

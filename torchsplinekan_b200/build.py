@@ -81,7 +81,11 @@ def build_extension(force: bool = False) -> str:
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     cudart = ["-L" + cudart_dir, "-l:libcudart.so.12", "-Wl,-rpath," + os.path.abspath(cudart_dir)] \
         if os.path.exists(os.path.join(cudart_dir, "libcudart.so.12")) else ["-L" + os.path.join(cuda_home, "lib64"), "-lcudart"]
-    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+    # The system compiler, whatever $CXX says: the extension must use the same libstdc++ as the
+    # interpreter's other extension modules (a toolchain that links its own copy statically breaks
+    # stream formatting inside the module).
+    cxx = shutil.which("g++", path="/usr/bin:/usr/local/bin:/bin") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
            "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
            f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
            *["-I" + p for p in ce.include_paths()], "-I" + sysconfig.get_paths()["include"],

@@ -169,24 +169,30 @@ constexpr int WORKER_THREADS = WORKER_WARPS * 32;
 constexpr int TC_THREADS = (WORKER_WARPS + 2) * 32;    // + MMA warp + bulk-copy warp
 constexpr int MMA_WARP = WORKER_WARPS;              // warp MMA_WARP + 1 issues the bulk copies
 
+// Fire-and-forget float32 add of four consecutive values, performed in L2 (IEEE round-to-nearest).
+// The running result is never read back by the SM, so a drain costs no load latency.  An element
+// is only ever touched by ONE thread, in program order (a store for the first chunk, then adds), so
+// the sum is the same bits on every run.
+__device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
 // Adds (or, for the first chunk, stores) 32 accumulator columns of one row.
 __device__ __forceinline__ void drain_row32(float* __restrict__ dst, const uint32_t (&r)[32], bool first,
                                             int valid, bool vec) {
     if (vec && valid >= 32) {
-        float4* d4 = reinterpret_cast<float4*>(dst);
         if (first) {
+            float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
             for (int q = 0; q < 8; ++q)
                 d4[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
         } else {
-            float4 old[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) old[q] = d4[q];
 #pragma unroll
             for (int q = 0; q < 8; ++q)
-                d4[q] = make_float4(old[q].x + __uint_as_float(r[4 * q]), old[q].y + __uint_as_float(r[4 * q + 1]),
-                                    old[q].z + __uint_as_float(r[4 * q + 2]), old[q].w + __uint_as_float(r[4 * q + 3]));
+                red_add_v4(dst + 4 * q, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
         }
     } else {
 #pragma unroll
@@ -616,7 +622,7 @@ tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ ta
         int pend_op = 0;
 
         auto drain = [&]() -> bool {
-            if (!mbar_wait_cluster(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
+            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
             ++n_drained;
             tc_fence_after_sync();
             const int64_t n = pend_mt * (2 * BLOCK_M) + rank * BLOCK_M + row;
@@ -689,7 +695,7 @@ tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ ta
                         w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x1)
                                         : eval_window<SPLIT, false, WIDE>(t1, P.ti, x1);
                     place_window<SPLIT>(w, cw1, hi1, lo1);
-                    if (!mbar_wait_cluster(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
+                    if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
                         ok = false;
                         break;
                     }
@@ -707,7 +713,7 @@ tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ ta
                     float xv[2][8];
                     load_x8(x, n, row_ok, P.I, f0, P.vec_x != 0, xv[0]);
                     load_x8(x, n, row_ok, P.I, f0 + 8, P.vec_x != 0, xv[1]);
-                    if (!mbar_wait_cluster(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
+                    if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
                         ok = false;
                         break;
                     }
@@ -868,7 +874,7 @@ tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ ta
                                              (size_t)rank * PF_B_SLOT_BYTES;
                         for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
                             const uint32_t slot = bslot % PF_B_SLOTS;
-                            if (!mbar_wait_cluster(smem_u32(&ctrl->emptyB[slot]), ((bslot / PF_B_SLOTS) & 1u) ^ 1u,
+                            if (!mbar_wait(smem_u32(&ctrl->emptyB[slot]), ((bslot / PF_B_SLOTS) & 1u) ^ 1u,
                                                    abort_flag)) {
                                 ok = false;
                                 break;
@@ -1024,22 +1030,18 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
 #pragma unroll 1
                 for (int c = part; c < BLOCK_N / 32; c += 4) {
                     float4* dst = tile + ((size_t)h * 64 + c * 8) * 128 + row;
-                    float4 old[8];
-                    if (!pend_first) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) old[q] = dst[(size_t)q * 128];
-                    }
                     uint32_t r[32];
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + h * BLOCK_N + c * 32, r);
                     tmem_ld_wait();
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                        if (!pend_first) {
-                            v.x += old[q].x; v.y += old[q].y; v.z += old[q].z; v.w += old[q].w;
-                        }
-                        dst[(size_t)q * 128] = v;
+                        if (pend_first)
+                            dst[(size_t)q * 128] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        else
+                            red_add_v4(reinterpret_cast<float*>(dst + (size_t)q * 128), __uint_as_float(r[4 * q]),
+                                       __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                       __uint_as_float(r[4 * q + 3]));
                     }
                 }
             }
@@ -1268,6 +1270,418 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     if (warp == MMA_WARP) {
         __syncwarp();
         tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Parameter-gradient kernel on CTA pairs:  D[o, c] = sum_n dY[n, o] A[n, c]
+// ---------------------------------------------------------------------------
+// Work item of a pair = (group of 512 outputs, column tile of 256, sample split).  Every MMA has
+// M = 256 outputs (128 per CTA, each CTA loads the dY tiles of its own rows) and N = 256 columns of
+// which each CTA GENERATES ONLY 128: the operand producers -- the resource that bounds the
+// single-CTA kernel (measured: with a third of the MMAs it is hardly faster) -- do half the work
+// per flop.  Two accumulators (two 256-output halves of the group) fill the 512 TMEM columns of
+// each CTA.  Slab layout and finalize kernels are those of the single-CTA kernel.
+constexpr int PB_G_STAGES = 4, PB_D_SLOTS = 3;
+constexpr uint32_t PB_G_HALF_BYTES = TILE_B_BYTES / 2;                    // 128 columns x 64 samples, bf16
+constexpr uint32_t PB_G_STAGE_BYTES = 2 * PB_G_HALF_BYTES;                // hi + lo
+constexpr uint32_t PB_SMEM_G = 0;
+constexpr uint32_t PB_SMEM_D = PB_SMEM_G + PB_G_STAGES * PB_G_STAGE_BYTES;
+constexpr uint32_t PB_SMEM_CTRL = PB_SMEM_D + PB_D_SLOTS * BWD_D_SLOT_BYTES;
+constexpr uint32_t PB_CTRL_BYTES = 512 + TAB_SMEM_FLOATS * 4;
+constexpr uint32_t PB_SMEM_BYTES = PB_SMEM_CTRL + PB_CTRL_BYTES;
+static_assert(PB_SMEM_BYTES <= 232448, "pair backward kernel shared memory exceeds 227 KB");
+
+struct PairBwdCtrl {
+    uint64_t fullG[PB_G_STAGES], emptyG[PB_G_STAGES], peerG[PB_G_STAGES];
+    uint64_t fullD[PB_D_SLOTS], emptyD[PB_D_SLOTS], peerD[PB_D_SLOTS];
+    uint64_t chunkFull, drained, peerDrained;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(PairBwdCtrl) <= 512, "control block too large");
+
+// plan.splits / kb_per_split are those of the PAIR decomposition: items = n_ogroups * n_ctiles * splits
+template <int NTERMS, bool WIDE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_bwd_param_pair_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ dyimg,
+                         float* __restrict__ partial, int* __restrict__ status,
+                         int64_t N, int I, int O, BwdPlan plan, TabInfo ti, int vec_ok) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr bool SPLIT = (NTERMS == 3);
+    const uint32_t sbase = smem_u32(smem);
+    PairBwdCtrl* ctrl = reinterpret_cast<PairBwdCtrl*>(smem + PB_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + PB_SMEM_CTRL + 512);
+    volatile int* abort_flag = &ctrl->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const bool shared_grid = grid_is_shared(tab, I, ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
+    const int n_ohalves = plan.n_otiles * 2;
+    const int n_ctiles = plan.n_ctiles();
+    const int n_ogroups = (plan.n_otiles + 1) / 2;
+    const int64_t n_items = (int64_t)n_ogroups * n_ctiles * plan.splits;
+
+    const bool bad_smem = (sbase & 1023u) != 0;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PB_G_STAGES; ++s) {
+            mbar_init(smem_u32(&ctrl->fullG[s]), WORKER_THREADS);
+            mbar_init(smem_u32(&ctrl->emptyG[s]), 1);
+            mbar_init(smem_u32(&ctrl->peerG[s]), 1);
+        }
+        for (int s = 0; s < PB_D_SLOTS; ++s) {
+            mbar_init(smem_u32(&ctrl->fullD[s]), 1);
+            mbar_init(smem_u32(&ctrl->emptyD[s]), 1);
+            mbar_init(smem_u32(&ctrl->peerD[s]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->chunkFull), 1);
+        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
+        mbar_init(smem_u32(&ctrl->peerDrained), 1);
+        ctrl->abort_flag = bad_smem ? 1 : 0;
+        fence_mbar_init();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc_pair(smem_u32(&ctrl->tmem_base), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    if (bad_smem && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+
+    // item -> (split, output group of 512, column tile); consecutive items share the output group
+    auto decode = [&](int64_t item, int& sp, int& og, int& ct) {
+        ct = (int)(item % n_ctiles);
+        const int64_t rest = item / n_ctiles;
+        og = (int)(rest % n_ogroups);
+        sp = (int)(rest / n_ogroups);
+    };
+    auto k_range = [&](int sp, int64_t& kb0, int64_t& kb1) {
+        kb0 = (int64_t)sp * plan.kb_per_split;
+        kb1 = kb0 + plan.kb_per_split;
+        if (kb1 > plan.kb_total) kb1 = plan.kb_total;
+    };
+    auto halves_of = [&](int og) { return (plan.n_otiles - 2 * og) >= 2 ? 2 : 1; };
+
+    if (warp < WORKER_WARPS) {
+        // ===== workers: this CTA's 128 columns x 64 samples per block, MN-major; drains =====
+        const int quad = warp & 3, part = warp >> 2;
+        // spline tiles: thread = (sample, 2 chunks); base tiles: thread = (2 samples, 8 features)
+        const int n_loc = (warp & 1) * 32 + lane;       // sample within the block (spline tiles)
+        const int fq = warp >> 1;                       // pair of chunks (spline tiles), 0..7
+        const int kg = warp >> 1;                       // group of 8 samples (base tiles)
+        const int r0 = (warp & 1) * 4 + (lane >> 4) * 2; // first of this thread's 2 rows in the group
+        const int bch = lane & 15;                      // chunk of 8 base features within the half tile
+        uint32_t it = 0, n_drained = 0;
+        bool ok = !bad_smem;
+        bool pend = false, pend_first = false;
+        int pend_sp = 0, pend_og = 0, pend_ct = 0;
+        auto drain = [&]() -> bool {
+            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
+            ++n_drained;
+            tc_fence_after_sync();
+            const int row = quad * 32 + lane;
+            const int nh = halves_of(pend_og);
+#pragma unroll 1
+            for (int h = 0; h < nh; ++h) {
+                // accumulator h = output tile 2 og + h; this CTA holds its rows [128 rank, 128 rank + 128)
+                float4* tile = reinterpret_cast<float4*>(partial) +
+                               ((((size_t)pend_sp * plan.n_otiles + (pend_og * 2 + h)) * n_ctiles + pend_ct) * 2 + rank) *
+                                   (size_t)(64 * 128);
+#pragma unroll 1
+                for (int c = part; c < BLOCK_N / 32; c += 4) {
+                    float4* dst = tile + ((size_t)c * 8) * 128 + row;
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + h * BLOCK_N + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (pend_first)
+                            dst[(size_t)q * 128] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        else
+                            red_add_v4(reinterpret_cast<float*>(dst + (size_t)q * 128), __uint_as_float(r[4 * q]),
+                                       __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                       __uint_as_float(r[4 * q + 3]));
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctrl->drained));
+            pend = false;
+            return true;
+        };
+
+        for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
+            int sp, og, ct;
+            decode(item, sp, og, ct);
+            const bool spline = ct < plan.ct_spline;
+            const int f_tile0 = spline ? 0 : (ct - plan.ct_spline) * 256 + (int)rank * 128;
+            int64_t kb0, kb1;
+            k_range(sp, kb0, kb1);
+            // spline tiles: chunk g = 32 ct + 16 rank + 2 fq + q belongs to feature g / cpf and holds its
+            // slots 8 (g % cpf) ..; the inputs of the next block of samples are loaded one iteration ahead
+            int cf[2], ccw[2];
+            {
+                const int g0 = ct * 32 + (int)rank * 16 + fq * 2;
+                const int cpf = WIDE ? ti.cpf : 1;
+                cf[0] = g0 / cpf;
+                ccw[0] = g0 - cf[0] * cpf;
+                cf[1] = cf[0];
+                ccw[1] = ccw[0] + 1;
+                if (ccw[1] == cpf) { cf[1] += 1; ccw[1] = 0; }
+            }
+            const int f_sp = cf[0];
+            float nx[2] = {0.f, 0.f};
+            auto prefetch_spline = [&](int64_t kb) {
+                const int64_t n = kb * BLOCK_K + n_loc;
+                nx[0] = 0.f;
+                nx[1] = 0.f;
+                if (n < N && f_sp < I) {
+                    const float* xr = x + (size_t)n * I;
+                    if (!WIDE && vec_ok && f_sp + 2 <= I) {
+                        const float2 v = __ldg(reinterpret_cast<const float2*>(xr + f_sp));
+                        nx[0] = v.x; nx[1] = v.y;
+                    } else {
+                        nx[0] = __ldg(xr + cf[0]);
+                        if (cf[1] < I) nx[1] = (cf[1] == cf[0]) ? nx[0] : __ldg(xr + cf[1]);
+                    }
+                }
+            };
+            if (spline) prefetch_spline(kb0);
+            for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
+                const uint32_t stage = it % PB_G_STAGES;
+                const uint32_t g_hi = sbase + PB_SMEM_G + stage * PB_G_STAGE_BYTES;
+                const uint32_t g_lo = g_hi + PB_G_HALF_BYTES;
+                const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
+                const uint32_t empty_parity = ((it / PB_G_STAGES) & 1u) ^ 1u;
+                if (spline) {
+                    const float xv[2] = {nx[0], nx[1]};
+                    if (kb + 1 < kb1) prefetch_spline(kb + 1);
+                    const bool n_ok = kb * BLOCK_K + n_loc < N;
+                    const int kk = n_loc & 7;
+                    Window w;
+                    uint4 hi[2], lo[2];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int f = cf[q];
+                        if (!WIDE || q == 0 || f != cf[q - 1]) {    // uniform over the warp
+                            if (shared_grid)
+                                w = eval_window<SPLIT, true, WIDE>(stab, ti, xv[q]);
+                            else
+                                w = eval_window<SPLIT, false, WIDE>(tab + (size_t)(f < I ? f : I - 1) * ti.fs, ti,
+                                                                    xv[q]);
+                        }
+                        place_window<SPLIT>(w, ccw[q], hi[q], lo[q]);
+                        if (!(n_ok && f < I)) {
+                            hi[q] = make_uint4(0, 0, 0, 0);
+                            lo[q] = hi[q];
+                        }
+                    }
+                    if (!mbar_wait(smem_u32(&ctrl->emptyG[stage]), empty_parity, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int fl = fq * 2 + q;                       // chunk within the half tile, 0..15
+                        const uint32_t off = (uint32_t)((fl >> 3) * 8 + (n_loc >> 3)) * 1024u + (uint32_t)kk * 128u +
+                                             (uint32_t)(((fl & 7) ^ kk) << 4);
+                        st_shared_v4(g_hi + off, hi[q]);
+                        if (SPLIT) st_shared_v4(g_lo + off, lo[q]);
+                    }
+                } else {
+                    // lane & 15 = chunk of 8 base features of this CTA's 128; two sample rows per thread
+                    const int64_t nrow0 = kb * BLOCK_K + kg * 8 + r0;
+                    const uint32_t atom = (uint32_t)((bch >> 3) * 8 + kg) * 1024u;   // [col group][sample group]
+                    const int f0 = f_tile0 + bch * 8;
+                    float xv[2][8];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) load_x8(x, nrow0 + q, nrow0 + q < N, I, f0, vec_ok != 0, xv[q]);
+                    if (!mbar_wait(smem_u32(&ctrl->emptyG[stage]), empty_parity, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        uint4 hi, lo;
+                        silu_chunk<SPLIT>(xv[q], hi, lo);
+                        const int rr = r0 + q;
+                        const uint32_t off = atom + (uint32_t)rr * 128u + (uint32_t)(((bch & 7) ^ rr) << 4);
+                        st_shared_v4(g_hi + off, hi);
+                        if (SPLIT) st_shared_v4(g_lo + off, lo);
+                    }
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ctrl->fullG[stage]));
+                if (pend && chunk_start) {
+                    if (!drain()) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
+                    pend = true;
+                    pend_first = (kb - kb0) < plan.chunk_kb;
+                    pend_sp = sp;
+                    pend_og = og;
+                    pend_ct = ct;
+                }
+            }
+        }
+        if (ok && pend) drain();
+    } else if (warp == MMA_WARP) {
+        if (lane == 0 && !bad_smem) {
+            if (rank == 0) {
+                // ===== leader: MMA issue =====
+                constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, true, true, 2 * BLOCK_M);
+                constexpr uint64_t dbase = make_sdesc_sw128(8192, 1024);
+                uint32_t it = 0, dslot = 0, n_chunks = 0;
+                bool ok = true;
+                for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
+                    int sp, og, ct;
+                    decode(item, sp, og, ct);
+                    const int nh = halves_of(og);
+                    int64_t kb0, kb1;
+                    k_range(sp, kb0, kb1);
+                    for (int64_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+                        const uint32_t stage = it % PB_G_STAGES;
+                        const uint32_t g_hi = sbase + PB_SMEM_G + stage * PB_G_STAGE_BYTES;
+                        const uint32_t g_lo = g_hi + PB_G_HALF_BYTES;
+                        const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
+                        if (chunk_start && n_chunks > 0) {
+                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag) ||
+                                !mbar_wait_cluster(smem_u32(&ctrl->peerDrained), (n_chunks - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                        }
+                        const uint32_t g_parity = (it / PB_G_STAGES) & 1u;
+                        if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), g_parity, abort_flag) ||
+                            !mbar_wait_cluster(smem_u32(&ctrl->peerG[stage]), g_parity, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        for (int h = 0; h < nh; ++h, ++dslot) {
+                            const uint32_t slot = dslot % PB_D_SLOTS;
+                            const uint32_t d_parity = (dslot / PB_D_SLOTS) & 1u;
+                            if (!mbar_wait(smem_u32(&ctrl->fullD[slot]), d_parity, abort_flag) ||
+                                !mbar_wait_cluster(smem_u32(&ctrl->peerD[slot]), d_parity, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t d_hi = sbase + PB_SMEM_D + slot * BWD_D_SLOT_BYTES;
+                            const uint32_t d_lo = d_hi + TILE_A_BYTES;
+                            const uint32_t d_tmem = tmem_base + h * BLOCK_N;
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ss_pair(d_tmem, sdesc_at(dbase, d_hi + ks * 2048),
+                                                sdesc_at(dbase, g_hi + ks * 2048), idesc, (!chunk_start || ks > 0) ? 1u : 0u);
+                            if (SPLIT) {
+#pragma unroll
+                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, d_lo + ks * 2048),
+                                                    sdesc_at(dbase, g_hi + ks * 2048), idesc, 1u);
+#pragma unroll
+                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, d_hi + ks * 2048),
+                                                    sdesc_at(dbase, g_lo + ks * 2048), idesc, 1u);
+                            }
+                            mma_commit_pair(smem_u32(&ctrl->emptyD[slot]));
+                        }
+                        if (!ok) break;
+                        mma_commit_pair(smem_u32(&ctrl->emptyG[stage]));
+                        if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
+                            mma_commit_pair(smem_u32(&ctrl->chunkFull));
+                            ++n_chunks;
+                        }
+                    }
+                }
+            } else {
+                // ===== peer: forwards the readiness of its own stages / slots / drains to the leader =====
+                const uint32_t l_peerDrained = map_to_cta(smem_u32(&ctrl->peerDrained), 0);
+                uint32_t it = 0, dslot = 0, n_chunks = 0;
+                bool ok = true;
+                for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
+                    int sp, og, ct;
+                    decode(item, sp, og, ct);
+                    const int nh = halves_of(og);
+                    int64_t kb0, kb1;
+                    k_range(sp, kb0, kb1);
+                    for (int64_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
+                        const uint32_t stage = it % PB_G_STAGES;
+                        const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
+                        if (chunk_start && n_chunks > 0) {
+                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_remote(l_peerDrained);
+                        }
+                        if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), (it / PB_G_STAGES) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerG[stage]), 0));
+                        for (int h = 0; h < nh; ++h, ++dslot) {
+                            const uint32_t slot = dslot % PB_D_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->fullD[slot]), (dslot / PB_D_SLOTS) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerD[slot]), 0));
+                        }
+                        if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) ++n_chunks;
+                    }
+                }
+            }
+        }
+    } else {
+        if (lane == 0 && !bad_smem) {
+            // ===== bulk copies: the dY tiles of this CTA's own 128 output rows =====
+            uint32_t dslot = 0;
+            bool ok = true;
+            for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
+                int sp, og, ct;
+                decode(item, sp, og, ct);
+                const int nh = halves_of(og);
+                int64_t kb0, kb1;
+                k_range(sp, kb0, kb1);
+                for (int64_t kb = kb0; kb < kb1 && ok; ++kb) {
+                    for (int h = 0; h < nh; ++h, ++dslot) {
+                        const uint32_t slot = dslot % PB_D_SLOTS;
+                        if (!mbar_wait(smem_u32(&ctrl->emptyD[slot]), ((dslot / PB_D_SLOTS) & 1u) ^ 1u,
+                                               abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        const size_t ohalf = (size_t)(og * 2 + h) * 2 + rank;
+                        const uint8_t* src = dyimg + ((size_t)kb * n_ohalves + ohalf) * BWD_D_SLOT_BYTES;
+                        const uint32_t bytes = SPLIT ? BWD_D_SLOT_BYTES : TILE_A_BYTES;
+                        const uint32_t bar = smem_u32(&ctrl->fullD[slot]);
+                        mbar_arrive_expect_tx(bar, bytes);
+                        bulk_g2s(sbase + PB_SMEM_D + slot * BWD_D_SLOT_BYTES, src, bytes, bar);
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag && !bad_smem) {
+        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -1834,25 +2248,26 @@ finalize_wide_kernel(const float* __restrict__ partial, BwdPlan plan, int cpf,
 }
 
 // Chunk lengths (k-blocks accumulated in TMEM between drains).  Every tensor-core accumulation
-// truncates, so the error of a chain grows with its length; these lengths keep it below the
-// operand-split error.  Measured against float64 (max-norm relative):
-//   forward, 1024 features (144 column blocks, one chain): 5.4e-6;  4096 features (576 blocks):
-//     chains of 144 / 72 / 48 / 36 / 24 blocks give 1.55e-5 / 1.5e-5 / 9.8e-6 / 8.5e-6 / 5.4e-6, at
-//     0 / 6 / 13 / 19 / 33 % more time -> layers beyond 144 blocks use chains of 36;
+// truncates toward zero, i.e. shrinks the running sum by a fraction of an ulp; over a chain the
+// error grows like (number of accumulations) x |partial sums| and is systematic.  A drain adds the
+// chain's result to the running total in float32 with round-to-nearest (in L2, red.global.add) and
+// restarts the chain at zero.  Measured against float64 (max-norm relative), 12 accumulations per
+// block of 64:
+//   forward, spline-dominated weights, 1024 features (144 blocks): one chain 3.2e-5; the error is
+//     proportional to the chain length, chains of 24 blocks stay at the operand-split floor
+//     (5e-6 .. 7e-6).  (With the reference's initialisation the base branch dominates y and even
+//     one chain of 144 blocks measures 5.4e-6, which is why only general weights show it.)
+//     4096 features: chains of 144 / 48 / 36 / 24 blocks give 1.55e-5 / 9.8e-6 / 8.5e-6 / 5.4e-6;
 //   parameter gradients, 65536 samples: chains of 16 / 32 / 64 blocks of 64 samples give 5.4e-6 /
 //     8.4e-6 / 1.4e-5;
 //   input gradient, 4096 outputs (64 blocks): one chain 1.5e-5, chains of 32 / 24 / 16 / 8 blocks
 //     8.5e-6 / 6.3e-6 / 6.7e-6 / 4.7e-6 (1024 outputs, 16 blocks: 5.9e-6, unaffected).
 // They are part of the numerical contract; kanb200_set_accumulation_chunks can only shorten them.
-constexpr int kFwdChunkKb = 144;      // forward: 64-column blocks per chain (layers of up to 144 blocks)
-constexpr int kFwdChunkWideKb = 36;   // forward: layers with more than 144 column blocks
+constexpr int kFwdChunkKb = 24;       // forward: 64-column blocks per chain
 constexpr int kBwdChunkKb = 16;       // parameter gradients: 64-sample blocks per chain
 constexpr int kDxChunkKb = 24;        // input gradient: 64-output blocks per chain
 int g_fwd_chunk = kFwdChunkKb, g_bwd_chunk = kBwdChunkKb, g_dx_chunk = kDxChunkKb;
-inline int fwd_chunk_kb(int kb_total) {
-    const int wide = g_fwd_chunk < kFwdChunkWideKb ? g_fwd_chunk : kFwdChunkWideKb;
-    return kb_total <= kFwdChunkKb ? g_fwd_chunk : wide;
-}
+inline int fwd_chunk_kb(int) { return g_fwd_chunk; }
 inline int bwd_chunk_kb() { return g_bwd_chunk; }
 inline int dx_chunk_kb() { return g_dx_chunk; }
 
@@ -2082,6 +2497,27 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
     }
     const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (need_param) {
+        bool launched = false;
+        if (g_pair_kernels) {
+            const int64_t pair_items = (int64_t)((L.plan.n_otiles + 1) / 2) * L.plan.n_ctiles() * L.plan.splits;
+#define KAN_BWD_PAIR(NT, W)                                                                                   \
+    do {                                                                                                      \
+        e = ensure_dynamic_smem<tc_bwd_param_pair_kernel<NT, W>>((int)PB_SMEM_BYTES);                         \
+        if (e == cudaSuccess)                                                                                 \
+            e = launch_pairs(tc_bwd_param_pair_kernel<NT, W>, pair_items, PB_SMEM_BYTES, st, x,               \
+                             (const float*)tab, (const uint8_t*)dyimg, partial, status, (int64_t)s.N, s.I,    \
+                             s.O, L.plan, ti, vec_ok);                                                        \
+    } while (0)
+            if (ti.cpf == 1) {
+                if (split_terms == 3) KAN_BWD_PAIR(3, false); else KAN_BWD_PAIR(1, false);
+            } else {
+                if (split_terms == 3) KAN_BWD_PAIR(3, true); else KAN_BWD_PAIR(1, true);
+            }
+#undef KAN_BWD_PAIR
+            if (e == cudaSuccess) launched = true;
+            else if (e != cudaErrorNotSupported) return e;
+            e = cudaSuccess;
+        }
         const int64_t items = L.plan.n_items();
         const int blocks = (int)(items < sm_count() ? items : sm_count());
 #define KAN_BWD(NT, W)                                                                                         \
@@ -2091,10 +2527,12 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
             tc_bwd_param_kernel<NT, W><<<blocks, TC_THREADS, BWD_SMEM_BYTES, st>>>(                           \
                 x, tab, dyimg, partial, status, s.N, s.I, s.O, L.plan, ti, vec_ok);                           \
     } while (0)
-        if (ti.cpf == 1) {
-            if (split_terms == 3) KAN_BWD(3, false); else KAN_BWD(1, false);
-        } else {
-            if (split_terms == 3) KAN_BWD(3, true); else KAN_BWD(1, true);
+        if (!launched) {
+            if (ti.cpf == 1) {
+                if (split_terms == 3) KAN_BWD(3, false); else KAN_BWD(1, false);
+            } else {
+                if (split_terms == 3) KAN_BWD(3, true); else KAN_BWD(1, true);
+            }
         }
 #undef KAN_BWD
         if (e != cudaSuccess) return e;
