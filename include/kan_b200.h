@@ -200,13 +200,31 @@ KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a,
                                    int64_t N, int64_t I, int64_t O, int R,
                                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Coefficient refit after the knots of a layer moved: the least-squares part of update_grid
+ * (ReferenceKANLayer.update_grid + curve2coeff, spline_kan/reference_backend.py:218-265, 442-493, where
+ * every old curve is sampled at every input into an [O, B, I] tensor and one system per feature is
+ * solved on the CPU).  For samples x [N,I] and knot rows grid_old / grid_new [I, G+2k+1] it returns, per
+ * input feature, the float64 matrix  transfer[i] = G_i^-1 M_i  [R, R]  with
+ *     G_i = sum_n b_new(x[n,i]) b_new(x[n,i])^T,   M_i = sum_n b_new(x[n,i]) b_old(x[n,i])^T,
+ * so that the refitted coefficients of EVERY output are  c_new[o,i,:] = transfer[i] c_old[o,i,:]
+ * (the normal equations of fitting the new basis to the old curve at the samples; the curves
+ * themselves are never formed).  gram [I,R,R] receives the Cholesky factors (scratch).  info[i] != 0
+ * marks a feature whose G_i is not safely positive definite (a pivot below 1e-10 of its largest
+ * diagonal entry: too few distinct samples for some basis function); its transfer matrix is not
+ * valid and the caller refits that feature by a minimum-norm solver.  All device pointers. */
+KANB200_API int kanb200_refit_transfer(int dtype, const void* x, const void* grid_old, const void* grid_new,
+                                       double* gram, double* transfer, int* info,
+                                       int64_t N, int64_t I, int G, int k, void* stream);
+
 /* Reads (and clears) the status word the tensor-core kernels keep at the start
  * of a workspace; synchronises the stream.  0 = every wait completed.  The word
  * is sticky: kernels only change it from 0 to a code and nothing but this call
  * clears it, so a timed-out wait in one call is still reported after any number
  * of later calls on the same workspace.  The caller zeroes the first 256 bytes
- * of a workspace once, before its first use.  (No counterpart in the reference,
- * whose kernels have no waits.) */
+ * of a workspace once, before its first use.  Bytes 8..15 of that header may hold a
+ * device-accessible pointer to an int (e.g. in mapped pinned host memory) that a reporting kernel
+ * also sets, so that a host can notice a report without synchronising; NULL (the zeroed header) =
+ * none.  (No counterpart in the reference, whose kernels have no waits.) */
 KANB200_API int kanb200_check_status(void* workspace, void* stream);
 
 /* Parameter gradients of the output rows [o_begin, o_end) only (tensor-core modes, float32): the

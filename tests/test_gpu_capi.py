@@ -280,7 +280,8 @@ def test_auto_mode_resolution():
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 65536, 1024, 1024, 5, 3) == nat.MODE_TC_BF16X3
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float64, 65536, 1024, 1024, 5, 3) == nat.MODE_SIMT
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 16384, 512, 512, 64, 3) == nat.MODE_TC_BF16X3
-    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 16, 32, 5, 3) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 256, 256, 5, 3) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 16, 32, 5, 3) == nat.MODE_SIMT      # too little work
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 128, 16, 32, 5, 3) == nat.MODE_SIMT
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 32, 8, 5, 3) == nat.MODE_SIMT
 

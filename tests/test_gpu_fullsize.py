@@ -284,18 +284,23 @@ def test_empty_batch_through_the_layer():
 
 
 def test_status_word_is_sticky_across_calls():
-    """A status word set by an earlier kernel survives later calls on the same scratch buffer and
-    is raised by the next call or by check_status (it used to be cleared by every call)."""
-    L = sk.KANLinear(64, 64, backend="cuda").cuda()
-    x = torch.rand(512, 64, device="cuda") * 2 - 1
+    """A status word set by an earlier kernel survives later calls on the same scratch buffer (it
+    used to be cleared by every call) and check_status still raises; and a report that reached the
+    host-visible int makes the very next call on that buffer raise without any synchronisation."""
+    L = sk.KANLinear(256, 256, backend="cuda").cuda()
+    x = torch.rand(512, 256, device="cuda") * 2 - 1
     L(x)
     _C.check_status()
-    _C._poke_status(0, 1)                       # forward scratch of the current stream: "a wait ran out"
-    L(x)                                        # runs (the word is mirrored to the host after the call) ...
-    torch.cuda.synchronize()
-    with pytest.raises(RuntimeError, match="bounded wait|gave up"):
-        L(x)                                    # ... and the next call on that buffer reports it
+    _C._poke_status(0, 1, False)                # device word only: "a wait ran out", nobody noticed yet
+    L(x)
+    L(x)                                        # two more calls on the same scratch buffer ...
+    with pytest.raises(RuntimeError, match="gave up"):
+        _C.check_status()                       # ... and the word is still there
     _C.check_status()                           # cleared by the report
+    _C._poke_status(0, 1, True)                 # as a kernel reports it: device word + host-visible int
+    with pytest.raises(RuntimeError, match="gave up a bounded wait"):
+        L(x)
+    _C.check_status()
     L(x)
     _C.check_status()
 

@@ -59,6 +59,7 @@ SIGNATURES = {
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
     "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
                                                                             _c_void_p, _c_size, _c_void_p]),
+    "kanb200_refit_transfer": (_c_int, [_c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_int, _c_int, _c_void_p]),
     "kanb200_check_status": (_c_int, [_c_void_p, _c_void_p]),
     "kanb200_backward_param_rows": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                           _c_i64, _c_i64, _c_void_p, _c_size,
@@ -377,6 +378,24 @@ def edge_abs_mean_backward(ga, s, H, bw, W, need_s, need_H, need_bw, need_W):
                                                     _p(ds), _p(dH), _p(dbw), _p(dW), N, I, O, R,
                                                     _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return ds, dH, dbw, dW
+
+
+def refit_transfer(x: torch.Tensor, grid_old: torch.Tensor, grid_new: torch.Tensor, k: int):
+    """``(transfer [I, R, R] float64, info [I] int32)``: per input feature the matrix that maps old
+    spline coefficients to the least-squares refit on the new knots at the samples ``x``; ``info != 0``
+    marks features whose normal equations are not safely positive definite."""
+    dev = _need_cuda(x, grid_old, grid_new)
+    N, I = x.shape
+    G = grid_old.shape[1] - 2 * k - 1
+    R = G + k
+    gram = torch.empty((I, R, R), dtype=torch.float64, device=dev)
+    transfer = torch.empty((I, R, R), dtype=torch.float64, device=dev)
+    info = torch.empty((I,), dtype=torch.int32, device=dev)
+    with _OnDevice(dev):
+        _check(lib().kanb200_refit_transfer(_code(x.dtype), _p(x.contiguous()), _p(grid_old.contiguous()),
+                                            _p(grid_new.contiguous()), _p(gram), _p(transfer), _p(info), N, I, G, k,
+                                            _stream(dev)))
+    return transfer, info
 
 
 def check_status(ws: Optional[torch.Tensor]) -> None:

@@ -17,7 +17,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libkan_b200.so")
-SOURCES = ["kan_capi.cu", "kan_simt.cu", "kan_reg.cu", "kan_tc.cu", "kan_tc_edge.cu", "kan_collective.cu"]
+SOURCES = ["kan_capi.cu", "kan_simt.cu", "kan_reg.cu", "kan_tc.cu", "kan_tc_edge.cu", "kan_refit.cu", "kan_collective.cu"]
 # test-only library (operand-layout self-test); never loaded by the package
 SELFTEST_SOURCE = "kan_selftest.cu"
 SELFTEST_PATH = os.path.join(LIB_DIR, "libkan_b200_selftest.so")

@@ -103,9 +103,10 @@ KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, 
     make_shape(N, I, O, G, k, s);
     const bool tc_ok = dtype == KANB200_F32 && tc_supported(s);
     if (mode == KANB200_MODE_AUTO) {
-        // The tensor-core kernels handle ragged tiles; below a few hundred rows the gather
-        // kernels have less fixed cost.
-        if (tc_ok && N >= 256 && O >= 16 && I >= 8) return KANB200_MODE_TC_BF16X3;
+        // The tensor-core kernels handle ragged tiles, but a call costs three to six launches (table,
+        // operand images, contraction, finalize) against one to three for the gather kernels: they
+        // pay from about 2^24 edge-samples (N I O) on.
+        if (tc_ok && N >= 256 && O >= 16 && I >= 8 && N * I * O >= ((int64_t)1 << 24)) return KANB200_MODE_TC_BF16X3;
         return KANB200_MODE_SIMT;
     }
     if (mode == KANB200_MODE_SIMT) return mode;
@@ -456,6 +457,25 @@ KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a, co
                                         (int)I, (int)O, R, ws_body(workspace, workspace_bytes),
                                         ws_body_bytes(workspace, workspace_bytes), st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_backward");
+}
+
+KANB200_API int kanb200_refit_transfer(int dtype, const void* x, const void* grid_old, const void* grid_new,
+                                       double* gram, double* transfer, int* info,
+                                       int64_t N, int64_t I, int G, int k, void* stream) {
+    int rc = kanb200_check_shapes(N, I, 1, G, k, dtype);
+    if (rc) return rc;
+    if (N < 1) return fail(KANB200_EINVAL, "refit_transfer: need at least one sample");
+    if (!x || !grid_old || !grid_new || !gram || !transfer || !info)
+        return fail(KANB200_EINVAL, "refit_transfer: NULL pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int R = G + k;
+    cudaError_t e = dtype == KANB200_F32
+                        ? refit_moments<float>((const float*)x, (const float*)grid_old, (const float*)grid_new, gram,
+                                               transfer, N, (int)I, R, k, st)
+                        : refit_moments<double>((const double*)x, (const double*)grid_old, (const double*)grid_new,
+                                                gram, transfer, N, (int)I, R, k, st);
+    if (e == cudaSuccess) e = refit_solve(gram, transfer, info, (int)I, R, st);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "refit_transfer");
 }
 
 KANB200_API int kanb200_check_status(void* workspace, void* stream) {

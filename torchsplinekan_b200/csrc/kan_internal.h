@@ -105,6 +105,13 @@ cudaError_t tc_edge_forward(int split_terms, const float* x, const float* s_val,
                             const float* W, float* a, const LayerShape& s, void* ws, size_t ws_bytes,
                             cudaStream_t st);
 
+// Coefficient refit after a knot update (kan_refit.cu): per-feature moment matrices
+// G = sum b_new b_new^T, M = sum b_new b_old^T (float64 [I, R, R]) and the in-place solve X = G^-1 M.
+template <typename T>
+cudaError_t refit_moments(const T* x, const T* grid_old, const T* grid_new, double* Gm, double* Mm, int64_t N, int I,
+                          int R, int k, cudaStream_t st);
+cudaError_t refit_solve(double* Gm, double* Mm, int* info, int I, int R, cudaStream_t st);
+
 // Gradient all-reduce over symmetric memory (kan_collective.cu).
 size_t allreduce_pad_bytes(int world, int blocks);
 void allreduce_set_wait_limit_ms(unsigned ms);

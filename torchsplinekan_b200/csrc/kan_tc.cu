@@ -250,7 +250,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
     if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
-        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+        if (threadIdx.x == 0) report_status(status, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -521,7 +521,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
 
     // ===== teardown =====
     if (*abort_flag) {
-        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        if (lane == 0) report_status(status, kStatusTimeout);
         __nanosleep(100000);                   // let copies / MMAs in flight land
     }
     tc_fence_before_sync();
@@ -605,7 +605,7 @@ tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ ta
     cluster_sync_all();                     // both CTAs' barriers exist before anyone arrives remotely
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
-    if (bad_smem && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+    if (bad_smem && threadIdx.x == 0) report_status(status, kStatusBadSmem);
 
     // pair tile -> (256-sample tile, pair of 256-output tiles)
     const int64_t n_ptiles = ((P.N + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * P.n_opairs;
@@ -892,7 +892,7 @@ tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ ta
 
     // ===== teardown: neither CTA may leave while the other can still signal its barriers =====
     if (*abort_flag && !bad_smem) {
-        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        if (lane == 0) report_status(status, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();
@@ -965,7 +965,7 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     const int64_t n_items = plan.n_items();
 
     if ((sbase & 1023u) != 0) {
-        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+        if (threadIdx.x == 0) report_status(status, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -1261,7 +1261,7 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 
     if (*abort_flag) {
-        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        if (lane == 0) report_status(status, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();
@@ -1350,7 +1350,7 @@ tc_bwd_param_pair_kernel(const float* __restrict__ x, const float* __restrict__ 
     cluster_sync_all();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
-    if (bad_smem && threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+    if (bad_smem && threadIdx.x == 0) report_status(status, kStatusBadSmem);
 
     // item -> (split, output group of 512, column tile); consecutive items share the output group
     auto decode = [&](int64_t item, int& sp, int& og, int& ct) {
@@ -1672,7 +1672,7 @@ tc_bwd_param_pair_kernel(const float* __restrict__ x, const float* __restrict__ 
     }
 
     if (*abort_flag && !bad_smem) {
-        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        if (lane == 0) report_status(status, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();
@@ -1749,7 +1749,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {
-        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+        if (threadIdx.x == 0) report_status(status, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -2111,7 +2111,7 @@ tc_bwd_input_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     }
 
     if (*abort_flag) {
-        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        if (lane == 0) report_status(status, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();

@@ -239,6 +239,19 @@ __device__ __forceinline__ void load_x8(const float* __restrict__ x, int64_t row
     }
 }
 
+// Records that a bounded wait ran out (or that the kernel could not start): the workspace's status
+// word takes the code if it is still 0 (it is sticky), and when the caller stored a pointer at byte
+// 8 of the workspace header -- an int the host can read without synchronising, e.g. in mapped
+// pinned memory -- that int receives the code too.
+__device__ __forceinline__ void report_status(int* status, int code) {
+    atomicCAS(status, 0, code);
+    int* mirror = *reinterpret_cast<int* volatile*>(status + 2);
+    if (mirror != nullptr) {
+        *reinterpret_cast<volatile int*>(mirror) = code;
+        __threadfence_system();
+    }
+}
+
 inline int sm_count() {
     static int cached = 0;
     if (cached == 0) {

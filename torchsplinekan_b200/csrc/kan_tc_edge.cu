@@ -116,7 +116,7 @@ tc_edge_fwd_kernel(const float* __restrict__ x, const float* __restrict__ sbase_
     if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
     if ((sbase & 1023u) != 0) {
-        if (threadIdx.x == 0) atomicCAS(status, 0, kStatusBadSmem);
+        if (threadIdx.x == 0) report_status(status, kStatusBadSmem);
         return;
     }
     if (threadIdx.x == 0) {
@@ -368,7 +368,7 @@ tc_edge_fwd_kernel(const float* __restrict__ x, const float* __restrict__ sbase_
     }
 
     if (*abort_flag) {
-        if (lane == 0) atomicCAS(status, 0, kStatusTimeout);
+        if (lane == 0) report_status(status, kStatusTimeout);
         __nanosleep(100000);
     }
     tc_fence_before_sync();

@@ -74,15 +74,16 @@ const char* mode_name(int m) {
 
 // ------------------------------------------------------------------------------------------------
 // scratch memory: one buffer per (device, stream, purpose), grown on demand, from the caching
-// allocator.  The first word of a buffer is the sticky status word of the tensor-core kernels; after
-// every call that may write it the word is copied (asynchronously, 4 bytes) into a pinned host word
-// that the next call on the same buffer looks at without synchronising.
+// allocator.  The first word of a buffer is the sticky status word of the tensor-core kernels; the
+// header also carries a pointer to one int of mapped pinned host memory that a reporting kernel sets
+// as well, and every later call on the same buffer looks at that int without synchronising.
 // ------------------------------------------------------------------------------------------------
 enum Purpose { WS_FWD = 0, WS_BWD = 1, WS_BASIS = 2, WS_EDGE = 3, WS_EDGE_X = 4 };
 
 struct Scratch {
     Tensor buf;
-    int* mirror = nullptr;       // pinned host copy of the status word
+    int* mirror = nullptr;       // mapped pinned host int that a reporting kernel sets
+    void* mirror_dev = nullptr;  // its device address, stored at byte 8 of the buffer's header
 };
 
 std::mutex g_ws_mutex;
@@ -118,9 +119,15 @@ Scratch* scratch(const c10::Device& dev, cudaStream_t st, int purpose, size_t by
             s.buf = at::empty({(int64_t)bytes + 256}, at::TensorOptions().dtype(at::kByte).device(dev));
             C10_CUDA_CHECK(cudaMemsetAsync(s.buf.data_ptr(), 0, 256, st));
             if (!s.mirror) {
-                C10_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&s.mirror), sizeof(int), cudaHostAllocDefault));
+                C10_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&s.mirror), sizeof(int), cudaHostAllocMapped));
                 *s.mirror = 0;
             }
+            void* mirror_dev = nullptr;
+            C10_CUDA_CHECK(cudaHostGetDevicePointer(&mirror_dev, s.mirror, 0));
+            s.mirror_dev = mirror_dev;
+            // the 8-byte source of this copy must outlive the call: it lives in the registry entry
+            C10_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(s.buf.data_ptr()) + 8, &s.mirror_dev, sizeof(void*),
+                                           cudaMemcpyHostToDevice, st));
         }
         out = &s;
     }
@@ -130,10 +137,6 @@ Scratch* scratch(const c10::Device& dev, cudaStream_t st, int purpose, size_t by
                            "(its outputs are incomplete); the status has been cleared");
     }
     return out;
-}
-
-inline void mirror_status(Scratch* s, cudaStream_t st) {
-    if (s) C10_CUDA_CHECK(cudaMemcpyAsync(s->mirror, s->buf.data_ptr(), sizeof(int), cudaMemcpyDeviceToHost, st));
 }
 
 void check_status_all() {
@@ -155,8 +158,9 @@ void release_workspaces() {
     g_ws.clear();
 }
 
-// Test hook: presets the status word of the (current device, current stream, purpose) buffer.
-void poke_status(int purpose, int code) {
+// Test hook: presets the status word of the (current device, current stream, purpose) buffer, and with
+// `as_kernel` also the host-visible int, as a reporting kernel would.
+void poke_status(int purpose, int code, bool as_kernel) {
     const auto dev = c10::Device(c10::kCUDA, (c10::DeviceIndex)at::cuda::current_device());
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
     std::lock_guard<std::mutex> lock(g_ws_mutex);
@@ -164,6 +168,7 @@ void poke_status(int purpose, int code) {
     TORCH_CHECK(it != g_ws.end() && it->second.buf.defined(), "no such workspace yet");
     C10_CUDA_CHECK(cudaMemcpyAsync(it->second.buf.data_ptr(), &code, sizeof(int), cudaMemcpyHostToDevice, st));
     C10_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (as_kernel && it->second.mirror) *it->second.mirror = code;
 }
 
 // Debugging aid (environment variable KAN_B200_BACKTRACE): native frames on a fatal signal.
@@ -307,7 +312,6 @@ Tensor forward_impl(const Tensor& x, const Tensor& grid, const Tensor& base_weig
                                  y.data_ptr(), d.N, d.I, d.O, d.G, d.k, ws ? ws->buf.data_ptr() : nullptr,
                                  ws ? (size_t)ws->buf.numel() : 0, st));
     }
-    mirror_status(ws, st);
     return y;
 }
 
@@ -344,7 +348,6 @@ Grads backward_impl(const Tensor& grad_output, const Tensor& x, const Tensor& gr
                                   mptr(g.gx), mptr(g.gb), mptr(g.gs), mptr(g.gc), d.N, d.I, d.O, d.G, d.k,
                                   ws ? ws->buf.data_ptr() : nullptr, ws ? (size_t)ws->buf.numel() : 0, st));
     }
-    mirror_status(ws, st);
     return g;
 }
 
@@ -509,7 +512,6 @@ Tensor edge_abs_mean_x(const Tensor& x, const Tensor& s, const Tensor& grid, con
                                          a.data_ptr(), N, I, O, G, (int)k, ws ? ws->buf.data_ptr() : nullptr,
                                          ws ? (size_t)ws->buf.numel() : 0, st));
     }
-    mirror_status(ws, st);
     return a;
 }
 
@@ -690,7 +692,6 @@ bool sink_backward(bool need_x, bool need_base, bool need_spline, bool need_scal
                                                  d.O, d.G, d.k, r.first, r.second, ws->buf.data_ptr(),
                                                  (size_t)ws->buf.numel(), st));
         }
-        mirror_status(ws, st);
         sink.attr("rows_done")(r.first, r.second);
     }
     if (need_x)
@@ -916,7 +917,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("check_status", &check_status_all,
           "synchronises and raises if a tensor-core kernel reported a timed-out wait on any scratch buffer");
     m.def("release_workspaces", &release_workspaces);
-    m.def("_poke_status", &poke_status);
+    m.def("_poke_status", &poke_status, py::arg("purpose"), py::arg("code"), py::arg("as_kernel") = true);
     m.def("set_event_log", &set_event_log);
     m.def("take_event_log", &take_event_log);
 }

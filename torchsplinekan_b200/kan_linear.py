@@ -14,7 +14,7 @@ import torch.nn.functional as F
 
 from . import _C
 from . import fused as _fused
-from .dense_backend import (ReferenceKANLayer, compute_basis, edge_abs_mean_dense, fit_spline_coeffs,
+from .dense_backend import (ReferenceKANLayer, compute_basis, curve2coeff, edge_abs_mean_dense, fit_spline_coeffs,
                             regularization_from_edge_means)
 
 _CUDA_EXT_LOADED: bool = True            # importing ._C raises when the library is missing
@@ -131,10 +131,42 @@ class KANLinear(nn.Module):
     # -- knots from data ---------------------------------------------------
     def update_grid(self, x: torch.Tensor, margin: float = 0.01) -> None:
         """Moves the knots to the distribution of ``x`` and refits ``spline_weight``
-        (see :meth:`ReferenceKANLayer.update_grid`)."""
-        self._ref.update_grid(x, margin=margin)
+        (see :meth:`ReferenceKANLayer.update_grid`).
+
+        For CUDA inputs on the native backend the refit stays on the device: per input feature two
+        [R, R] moment matrices of the new and old basis at the samples give the matrix that maps old
+        coefficients to refitted ones (``kanb200_refit_transfer``), so neither the sampled curves
+        [O, B, I] nor a system per (feature, output) is ever formed; only features whose normal
+        equations are not safely positive definite (too few distinct samples) take the
+        minimum-norm path of the dense backend."""
+        xf = x.reshape(-1, self.in_features)
+        if not (xf.is_cuda and self.backend_for(xf) == "cuda"):
+            self._ref.update_grid(x, margin=margin)
+            with torch.no_grad():
+                self.grid.copy_(self._ref.grid)
+            return
+        ref = self._ref
+        if margin <= 0:
+            raise ValueError(f"margin must be positive, got {margin}")
+        if not (0.0 < ref.grid_eps < 1.0):
+            raise ValueError(f"grid_eps must be in (0, 1), got {ref.grid_eps}")
+        if xf.shape[0] < 2:
+            raise ValueError(f"update_grid requires at least 2 samples, got {xf.shape[0]}")
+        from . import _native
         with torch.no_grad():
-            self.grid.copy_(self._ref.grid)
+            xs = xf.to(self.grid.dtype)
+            knots = ref.grid_from_samples(xs, self.grid_size, margin)
+            transfer, info = _native.refit_transfer(xs, self.grid, knots, self.spline_order)
+            coeffs = torch.einsum("irs,ois->oir", transfer, self.spline_weight.double())
+            weak = torch.nonzero(info != 0).flatten()
+            if weak.numel() > 0:
+                # minimum-norm refit of the few rank-deficient features, as the dense backend does
+                cols = weak.tolist()
+                curve = torch.einsum("oir,bir->obi", self.spline_weight[:, cols],
+                                     compute_basis(xs[:, cols], self.grid[cols], self.spline_order))
+                coeffs[:, cols] = curve2coeff(xs[:, cols], curve, knots[cols], self.spline_order).double()
+            self._copy_grid_(knots)
+            self.spline_weight.copy_(coeffs.to(self.spline_weight.dtype))
 
     # -- regularisation ----------------------------------------------------
     def regularization_loss(self, reg_act: float = 1.0, reg_entropy: float = 1.0, *,
