@@ -659,7 +659,22 @@ def run_micro(args):
     emit("edge_param_kernel<grad> + sum_slabs", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
     ms = timeit(lambda: nat.edge_abs_mean_backward(ga, s, H, bw, W, True, True, False, False))
     emit("edge_input_kernel", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
-    del H, s, W
+    del H
+
+    # the same statistic straight from x (basis never stored): tensor-core forward, FMA-pipe backward
+    xe = torch.rand(Ne, Ie, device=dev, generator=g) * 2 - 1
+    ge = ((torch.arange(G + 2 * k + 1, device=dev, dtype=torch.float32) - k) * (2.0 / G) - 1.0)[None] \
+        .expand(Ie, -1).contiguous()
+    ms = timeit(lambda: nat.edge_abs_mean_x(xe, None, ge, bw, W, k, nat.MODE_TC_BF16X3))
+    emit("tc_edge_fwd_kernel (from x, tensor cores)", ms, flops=fl, note="2 N O I (R+1) flops counted once; 3 bf16 MMAs per product",
+         tflops_counted_once=fl / ms / 1e9)
+    ms = timeit(lambda: nat.edge_abs_mean_x(xe, None, ge, bw, W, k, nat.MODE_SIMT))
+    emit("edge_param_kernel<forward, from x>", ms, flops=fl, fma_peak_tflops=fma_peak["fp32"])
+    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, False, False, True, True))
+    emit("edge_param_kernel<grad, from x> + sum_slabs", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
+    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, True, False, False, False))
+    emit("edge_input_kernel<from x>", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
+    del s, W, xe
 
     # float64 SIMT layer (PINN-style 64 -> 64, G = 8)
     Nd, Id, Od, Gd = 131072, 64, 64, 8

@@ -79,13 +79,6 @@ KANB200_API int kanb200_get_basis_impl(void);
  * No counterpart in the reference (its GEMMs are cuBLAS calls). */
 KANB200_API int kanb200_set_accumulation_chunks(int forward_blocks, int param_blocks, int input_blocks);
 
-/* The tensor-core contractions exist in two forms with bit-identical results: on pairs of CTAs
- * (thread-block clusters of two sharing every MMA, tcgen05 cta_group::2; default) and on single
- * CTAs (used automatically where no cluster fits).  0 selects the single-CTA kernels everywhere,
- * e.g. to compare the two.  Process-wide.  No counterpart in the reference. */
-KANB200_API int kanb200_set_pair_kernels(int on);
-KANB200_API int kanb200_get_pair_kernels(void);
-
 /* Shape / limit validation run by every entry point before any launch
  * (kan_check_inputs, csrc/kan_ops.h:27-78). */
 KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int k, int dtype);

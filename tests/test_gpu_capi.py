@@ -510,23 +510,9 @@ def test_edge_abs_mean_from_x_fma_kernels_and_backward(N, I, O, G, k, base, cust
 
 
 @pytest.mark.parametrize("shape", [
-    dict(N=1024, I=64, O=256, G=5, k=3), dict(N=777, I=100, O=300, G=5, k=3, scaler=False),
-    dict(N=130, I=40, O=1024, G=5, k=3, nonuniform=True), dict(N=3000, I=24, O=520, G=20, k=2, nonuniform=True),
-    dict(N=257, I=1024, O=64, G=5, k=3)])
-def test_cta_pair_kernels_match_single_cta_kernels_bit_for_bit(shape):
-    """The contractions on CTA pairs (clusters of two sharing every MMA) run the same MMAs in the
-    same order per output element as the single-CTA kernels: identical bits, and both within the
-    tolerance of the oracle."""
-    case = make_layer_case(dtype=np.float32, seed=11, **shape)
-    out = {}
-    try:
-        for on in (0, 1):
-            assert nat.lib().kanb200_set_pair_kernels(on) == 0
-            out[on] = _run_layer(case, nat.MODE_TC_BF16X3)
-    finally:
-        nat.lib().kanb200_set_pair_kernels(1)
-    names = ["y", "dY", "gx", "g_base", "g_spline", "g_scaler"]
-    for name, a, b in zip(names, out[0], out[1]):
-        if a is not None:
-            assert np.array_equal(a, b), name
-    _compare_layer(case, nat.MODE_TC_BF16X3, TOL32)
+    dict(N=257, I=1024, O=64, G=5, k=3), dict(N=3000, I=24, O=520, G=20, k=2, nonuniform=True),
+    dict(N=130, I=40, O=1024, G=5, k=3, nonuniform=True)])
+def test_layer_tensor_core_general_weights(shape):
+    """Spline-dominated weights (the reference's initialisation makes the base branch dominate y and
+    hides accumulation error): 1024 features in one tile, a wide grid, many outputs."""
+    _compare_layer(make_layer_case(dtype=np.float32, seed=11, **shape), nat.MODE_TC_BF16X3, TOL32)

@@ -277,7 +277,9 @@ def test_torch_ops_surface():
 
 
 def test_virtual_shards_sum_to_full_batch_gradient():
-    """Eight row shards processed one after the other give the unsharded gradients (1e-6)."""
+    """Eight row shards processed one after the other give the unsharded gradients, within the
+    tolerance of the arithmetic (the full batch runs on the tensor cores, the small shards on the
+    gather kernels)."""
     nat, _ = _pair(64, 96)
     x = torch.rand(4096, 64, device="cuda") * 2 - 1
     full = _step(nat, x)[2:]
@@ -287,7 +289,7 @@ def test_virtual_shards_sum_to_full_batch_gradient():
         for s, g in zip(acc, _step(nat, x[a:b])[2:]):
             s += g
     for s, g in zip(acc, full):
-        assert _err(s, g) < 1e-6
+        assert _err(s, g) < TOL32
 
 
 def test_full_size_layer_properties():

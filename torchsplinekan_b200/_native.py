@@ -33,8 +33,6 @@ SIGNATURES = {
     "kanb200_set_basis_impl": (_c_int, [_c_int]),
     "kanb200_get_basis_impl": (_c_int, []),
     "kanb200_set_accumulation_chunks": (_c_int, [_c_int, _c_int, _c_int]),
-    "kanb200_set_pair_kernels": (_c_int, [_c_int]),
-    "kanb200_get_pair_kernels": (_c_int, []),
     "kanb200_check_shapes": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int]),
     "kanb200_resolve_mode": (_c_int, [_c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
     "kanb200_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int,

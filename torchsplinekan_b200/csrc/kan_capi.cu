@@ -74,13 +74,6 @@ KANB200_API int kanb200_set_accumulation_chunks(int forward_blocks, int param_bl
     return KANB200_OK;
 }
 
-KANB200_API int kanb200_set_pair_kernels(int on) {
-    tc_set_pair_kernels(on);
-    return KANB200_OK;
-}
-
-KANB200_API int kanb200_get_pair_kernels(void) { return tc_get_pair_kernels(); }
-
 KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int k, int dtype) {
     if (dtype != KANB200_F32 && dtype != KANB200_F64)
         return fail(KANB200_EINVAL, "only FP32 and FP64 inputs are supported");

@@ -88,10 +88,6 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
 // are clamped to them; 0 keeps the current value).
 void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb);
 
-// Selects between the kernels that run on CTA pairs (1, default) and the single-CTA kernels (0).
-void tc_set_pair_kernels(int on);
-int tc_get_pair_kernels();
-
 // The per-span polynomial table on its own: bytes, floats per feature, and the kernel that fills it.
 size_t tc_table_bytes(const LayerShape& s);
 int tc_table_stride(const LayerShape& s);

@@ -534,378 +534,6 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
 }
 
 // ---------------------------------------------------------------------------
-// Forward kernel on CTA pairs:  y[n, o] = sum_c A[n, c] W[o, c]
-// ---------------------------------------------------------------------------
-// Two CTAs of a cluster run every MMA together (tcgen05 cta_group::2): the pair's tile is 256
-// samples x up to 512 outputs, each CTA generates the A tile of its own 128 samples and stages
-// HALF of every weight tile (128 of the 256 output rows), so per MMA a CTA's tensor core reads
-// 4 KB + 4 KB of shared memory instead of 4 KB + 8 KB and the bulk-copy traffic per CTA halves:
-// the single-CTA kernel spends more shared-memory bandwidth on operand reads and tile writes per
-// k-block (448 KB) than its MMAs take time for (3072 cycles x 128 B).  The even CTA (leader) issues
-// the MMAs; the odd CTA's MMA warp instead forwards "my A stage / B slot is ready" to the leader's
-// barriers; tcgen05.commit releases stages and slots in both CTAs at once.
-constexpr int PF_A_STAGES = 3, PF_B_SLOTS = 8;
-constexpr uint32_t PF_B_SLOT_BYTES = TILE_B_BYTES / 2;                     // 128 output rows x 128 B
-constexpr uint32_t PF_SMEM_A = 0;
-constexpr uint32_t PF_SMEM_B = PF_SMEM_A + PF_A_STAGES * FWD_A_STAGE_BYTES;
-constexpr uint32_t PF_SMEM_CTRL = PF_SMEM_B + PF_B_SLOTS * PF_B_SLOT_BYTES;
-constexpr uint32_t PF_CTRL_BYTES = 512 + TAB_SMEM_FLOATS * 4;
-constexpr uint32_t PF_SMEM_BYTES = PF_SMEM_CTRL + PF_CTRL_BYTES;
-static_assert(PF_SMEM_BYTES <= 232448, "pair forward kernel shared memory exceeds 227 KB");
-
-struct PairFwdCtrl {
-    uint64_t fullA[PF_A_STAGES], emptyA[PF_A_STAGES], peerA[PF_A_STAGES];
-    uint64_t fullB[PF_B_SLOTS], emptyB[PF_B_SLOTS], peerB[PF_B_SLOTS];
-    uint64_t chunkFull, drained, peerDrained;
-    uint32_t tmem_base;
-    int abort_flag;
-};
-static_assert(sizeof(PairFwdCtrl) <= 512, "control block too large");
-
-template <int NTERMS, bool WIDE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-tc_forward_pair_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
-                       float* __restrict__ y, int* __restrict__ status, const FwdParams P) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr bool SPLIT = (NTERMS == 3);
-    const uint32_t sbase = smem_u32(smem);
-    PairFwdCtrl* ctrl = reinterpret_cast<PairFwdCtrl*>(smem + PF_SMEM_CTRL);
-    float* stab = reinterpret_cast<float*>(smem + PF_SMEM_CTRL + 512);
-    volatile int* abort_flag = &ctrl->abort_flag;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();              // 0 = leader (issues the MMAs), 1 = peer
-    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const bool shared_grid = grid_is_shared(tab, P.I, P.ti);
-    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
-
-    const bool bad_smem = (sbase & 1023u) != 0;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < PF_A_STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->fullA[s]), WORKER_THREADS);
-            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
-            mbar_init(smem_u32(&ctrl->peerA[s]), 1);
-        }
-        for (int s = 0; s < PF_B_SLOTS; ++s) {
-            mbar_init(smem_u32(&ctrl->fullB[s]), 1);
-            mbar_init(smem_u32(&ctrl->emptyB[s]), 1);
-            mbar_init(smem_u32(&ctrl->peerB[s]), 1);
-        }
-        mbar_init(smem_u32(&ctrl->chunkFull), 1);
-        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
-        mbar_init(smem_u32(&ctrl->peerDrained), 1);
-        ctrl->abort_flag = bad_smem ? 1 : 0;
-        fence_mbar_init();
-    }
-    if (warp == MMA_WARP) {
-        tmem_alloc_pair(smem_u32(&ctrl->tmem_base), 512);
-        tmem_relinquish_pair();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();                     // both CTAs' barriers exist before anyone arrives remotely
-    tc_fence_after_sync();
-    const uint32_t tmem_base = ctrl->tmem_base;
-    if (bad_smem && threadIdx.x == 0) report_status(status, kStatusBadSmem);
-
-    // pair tile -> (256-sample tile, pair of 256-output tiles)
-    const int64_t n_ptiles = ((P.N + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * P.n_opairs;
-
-    if (warp < WORKER_WARPS) {
-        // ===== workers: x -> basis / silu -> swizzled A tile of this CTA's 128 samples; drains =====
-        const int quad = warp & 3;
-        const int part = warp >> 2;
-        const int row = quad * 32 + lane;
-        uint32_t it = 0, n_drained = 0;
-        bool ok = !bad_smem;
-        bool pend = false, pend_first = false;
-        int64_t pend_mt = 0;
-        int pend_op = 0;
-
-        auto drain = [&]() -> bool {
-            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
-            ++n_drained;
-            tc_fence_after_sync();
-            const int64_t n = pend_mt * (2 * BLOCK_M) + rank * BLOCK_M + row;
-            const int nsub = (P.n_otiles - 2 * pend_op) >= 2 ? 2 : 1;
-#pragma unroll 1
-            for (int c = part; c < nsub * (BLOCK_N / 32); c += 4) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, r);
-                tmem_ld_wait();
-                const int col0 = pend_op * 2 * BLOCK_N + c * 32;
-                if (n < P.N && col0 < P.O)
-                    drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
-            }
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->drained));
-            pend = false;
-            return true;
-        };
-
-        for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
-            const int64_t mt = tile / P.n_opairs;
-            const int op = (int)(tile - mt * P.n_opairs);
-            const int64_t n = mt * (2 * BLOCK_M) + rank * BLOCK_M + row;
-            const bool row_ok = n < P.N;
-            const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
-            const int cpf = WIDE ? P.ti.cpf : 1;
-            float nx0 = 0.f, nx1 = 0.f;
-            auto chunk_pair = [&](int kb, int& f0, int& cw0, int& f1, int& cw1) {
-                const int g0 = kb * 8 + part * 2;
-                if (!WIDE) {
-                    f0 = g0; cw0 = 0; f1 = g0 + 1; cw1 = 0;
-                } else {
-                    f0 = g0 / cpf; cw0 = g0 - f0 * cpf;
-                    f1 = f0; cw1 = cw0 + 1;
-                    if (cw1 == cpf) { f1 = f0 + 1; cw1 = 0; }
-                }
-            };
-            auto prefetch_spline = [&](int kb) {
-                int f0, cw0, f1, cw1;
-                chunk_pair(kb, f0, cw0, f1, cw1);
-                if (!WIDE && P.vec_x2 && row_ok && f0 + 1 < P.I) {
-                    const float2 v = __ldg(reinterpret_cast<const float2*>(xrow + f0));
-                    nx0 = v.x;
-                    nx1 = v.y;
-                } else {
-                    nx0 = (row_ok && f0 < P.I) ? __ldg(xrow + f0) : 0.f;
-                    nx1 = (row_ok && f1 < P.I) ? __ldg(xrow + f1) : 0.f;
-                }
-            };
-            if (P.kb_spline > 0) prefetch_spline(0);
-            for (int kb = 0; kb < P.kb_total; ++kb, ++it) {
-                const uint32_t stage = it % PF_A_STAGES;
-                const uint32_t a_hi = sbase + PF_SMEM_A + stage * FWD_A_STAGE_BYTES;
-                const uint32_t a_lo = a_hi + TILE_A_BYTES;
-                const bool chunk_start = (kb % P.chunk_kb) == 0;
-                const uint32_t empty_parity = ((it / PF_A_STAGES) & 1u) ^ 1u;
-                if (kb < P.kb_spline) {
-                    int f0, cw0, f1, cw1;
-                    chunk_pair(kb, f0, cw0, f1, cw1);
-                    const float x0 = nx0, x1 = nx1;
-                    if (kb + 1 < P.kb_spline) prefetch_spline(kb + 1);
-                    const bool ok0 = row_ok && f0 < P.I, ok1 = row_ok && f1 < P.I;
-                    const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * P.ti.fs;
-                    const float* t1 = tab + (size_t)(f1 < P.I ? f1 : P.I - 1) * P.ti.fs;
-                    uint4 hi0, lo0, hi1, lo1;
-                    Window w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x0)
-                                           : eval_window<SPLIT, false, WIDE>(t0, P.ti, x0);
-                    place_window<SPLIT>(w, cw0, hi0, lo0);
-                    if (!WIDE || f1 != f0)
-                        w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x1)
-                                        : eval_window<SPLIT, false, WIDE>(t1, P.ti, x1);
-                    place_window<SPLIT>(w, cw1, hi1, lo1);
-                    if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint4 zero = make_uint4(0, 0, 0, 0);
-                    const uint32_t off0 = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2));
-                    const uint32_t off1 = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2 + 1));
-                    st_shared_v4(a_hi + off0, ok0 ? hi0 : zero);
-                    st_shared_v4(a_hi + off1, ok1 ? hi1 : zero);
-                    if (SPLIT) {
-                        st_shared_v4(a_lo + off0, ok0 ? lo0 : zero);
-                        st_shared_v4(a_lo + off1, ok1 ? lo1 : zero);
-                    }
-                } else {
-                    const int f0 = (kb - P.kb_spline) * 64 + part * 16;
-                    float xv[2][8];
-                    load_x8(x, n, row_ok, P.I, f0, P.vec_x != 0, xv[0]);
-                    load_x8(x, n, row_ok, P.I, f0 + 8, P.vec_x != 0, xv[1]);
-                    if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), empty_parity, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint4 hi, lo;
-                        silu_chunk<SPLIT>(xv[c], hi, lo);
-                        const uint32_t off = sw128_chunk_offset((uint32_t)row, (uint32_t)(part * 2 + c));
-                        st_shared_v4(a_hi + off, hi);
-                        if (SPLIT) st_shared_v4(a_lo + off, lo);
-                    }
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->fullA[stage]));
-                if (pend && chunk_start) {
-                    if (!drain()) {
-                        ok = false;
-                        break;
-                    }
-                }
-                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
-                    pend = true;
-                    pend_first = kb < P.chunk_kb;
-                    pend_mt = mt;
-                    pend_op = op;
-                }
-            }
-        }
-        if (ok && pend) drain();
-    } else if (warp == MMA_WARP) {
-        if (lane == 0 && !bad_smem) {
-            if (rank == 0) {
-                // ===== leader: MMA issue for the pair =====
-                constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, false, false, 2 * BLOCK_M);
-                constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
-                uint32_t it = 0, bslot = 0, n_chunks = 0;
-                bool ok = true;
-                auto wait_b = [&](uint32_t slot, uint32_t parity) -> bool {
-                    return mbar_wait(smem_u32(&ctrl->fullB[slot]), parity, abort_flag) &&
-                           mbar_wait_cluster(smem_u32(&ctrl->peerB[slot]), parity, abort_flag);
-                };
-                for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
-                    const int op = (int)(tile % P.n_opairs);
-                    const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
-                    for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
-                        const uint32_t stage = it % PF_A_STAGES;
-                        const uint32_t a_hi = sbase + PF_SMEM_A + stage * FWD_A_STAGE_BYTES;
-                        const uint32_t a_lo = a_hi + TILE_A_BYTES;
-                        const bool chunk_start = (kb % P.chunk_kb) == 0;
-                        if (chunk_start && n_chunks > 0) {
-                            // both CTAs must have drained their half of the accumulator
-                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag) ||
-                                !mbar_wait_cluster(smem_u32(&ctrl->peerDrained), (n_chunks - 1) & 1u, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                        }
-                        const uint32_t a_parity = (it / PF_A_STAGES) & 1u;
-                        if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), a_parity, abort_flag) ||
-                            !mbar_wait_cluster(smem_u32(&ctrl->peerA[stage]), a_parity, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        for (int j = 0; j < nsub && ok; ++j) {
-                            const uint32_t d_tmem = tmem_base + j * BLOCK_N;
-                            const uint32_t slot_h = bslot % PF_B_SLOTS;
-                            if (!wait_b(slot_h, (bslot / PF_B_SLOTS) & 1u)) {
-                                ok = false;
-                                break;
-                            }
-                            tc_fence_after_sync();
-                            const uint32_t b_hi = sbase + PF_SMEM_B + slot_h * PF_B_SLOT_BYTES;
-#pragma unroll
-                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                                mma_f16_ss_pair(d_tmem, sdesc_at(dbase, a_hi + ks * 32), sdesc_at(dbase, b_hi + ks * 32),
-                                                idesc, (!chunk_start || ks > 0) ? 1u : 0u);
-                            if (SPLIT) {
-#pragma unroll
-                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, a_lo + ks * 32),
-                                                    sdesc_at(dbase, b_hi + ks * 32), idesc, 1u);
-                            }
-                            mma_commit_pair(smem_u32(&ctrl->emptyB[slot_h]));
-                            ++bslot;
-                            if (SPLIT) {
-                                const uint32_t slot_l = bslot % PF_B_SLOTS;
-                                if (!wait_b(slot_l, (bslot / PF_B_SLOTS) & 1u)) {
-                                    ok = false;
-                                    break;
-                                }
-                                tc_fence_after_sync();
-                                const uint32_t b_lo = sbase + PF_SMEM_B + slot_l * PF_B_SLOT_BYTES;
-#pragma unroll
-                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, a_hi + ks * 32),
-                                                    sdesc_at(dbase, b_lo + ks * 32), idesc, 1u);
-                                mma_commit_pair(smem_u32(&ctrl->emptyB[slot_l]));
-                                ++bslot;
-                            }
-                        }
-                        if (!ok) break;
-                        mma_commit_pair(smem_u32(&ctrl->emptyA[stage]));
-                        if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
-                            mma_commit_pair(smem_u32(&ctrl->chunkFull));
-                            ++n_chunks;
-                        }
-                    }
-                }
-            } else {
-                // ===== peer: forwards the readiness of its own stages / slots / drains to the leader,
-                // in the order the leader consumes them =====
-                const uint32_t l_peerDrained = map_to_cta(smem_u32(&ctrl->peerDrained), 0);
-                uint32_t it = 0, bslot = 0, n_chunks = 0;
-                bool ok = true;
-                for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
-                    const int op = (int)(tile % P.n_opairs);
-                    const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
-                    for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
-                        const uint32_t stage = it % PF_A_STAGES;
-                        const bool chunk_start = (kb % P.chunk_kb) == 0;
-                        if (chunk_start && n_chunks > 0) {
-                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                            mbar_arrive_remote(l_peerDrained);
-                        }
-                        if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / PF_A_STAGES) & 1u, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerA[stage]), 0));
-                        for (int s = 0; s < nsub * (SPLIT ? 2 : 1); ++s, ++bslot) {
-                            const uint32_t slot = bslot % PF_B_SLOTS;
-                            if (!mbar_wait(smem_u32(&ctrl->fullB[slot]), (bslot / PF_B_SLOTS) & 1u, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                            mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerB[slot]), 0));
-                        }
-                        if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) ++n_chunks;
-                    }
-                }
-            }
-        }
-    } else {
-        if (lane == 0 && !bad_smem) {
-            // ===== bulk copies: this CTA's half (128 output rows) of every weight tile =====
-            uint32_t bslot = 0;
-            bool ok = true;
-            for (int64_t tile = pair; tile < n_ptiles && ok; tile += n_pairs) {
-                const int op = (int)(tile % P.n_opairs);
-                const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
-                for (int kb = 0; kb < P.kb_total && ok; ++kb) {
-                    for (int j = 0; j < nsub && ok; ++j) {
-                        const uint8_t* src = wimg + ((size_t)(2 * op + j) * P.kb_total + kb) * (2 * (size_t)TILE_B_BYTES) +
-                                             (size_t)rank * PF_B_SLOT_BYTES;
-                        for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
-                            const uint32_t slot = bslot % PF_B_SLOTS;
-                            if (!mbar_wait(smem_u32(&ctrl->emptyB[slot]), ((bslot / PF_B_SLOTS) & 1u) ^ 1u,
-                                                   abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                            const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
-                            mbar_arrive_expect_tx(bar, PF_B_SLOT_BYTES);
-                            bulk_g2s(sbase + PF_SMEM_B + slot * PF_B_SLOT_BYTES, src + (size_t)term * TILE_B_BYTES,
-                                     PF_B_SLOT_BYTES, bar);
-                        }
-                    }
-                }
-            }
-        }
-    }
-
-    // ===== teardown: neither CTA may leave while the other can still signal its barriers =====
-    if (*abort_flag && !bad_smem) {
-        if (lane == 0) report_status(status, kStatusTimeout);
-        __nanosleep(100000);
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();
-    tc_fence_after_sync();
-    if (warp == MMA_WARP) {
-        __syncwarp();
-        tmem_dealloc_pair(tmem_base, 512);
-    }
-}
-
-// ---------------------------------------------------------------------------
 // Parameter-gradient kernel:  D[o, c] = sum_n dY[n, o] A[n, c]
 // ---------------------------------------------------------------------------
 // Work item = (output tile of 256, column tile of 256, sample split).  The
@@ -1270,418 +898,6 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
     if (warp == MMA_WARP) {
         __syncwarp();
         tmem_dealloc(tmem_base, 512);
-    }
-}
-
-// ---------------------------------------------------------------------------
-// Parameter-gradient kernel on CTA pairs:  D[o, c] = sum_n dY[n, o] A[n, c]
-// ---------------------------------------------------------------------------
-// Work item of a pair = (group of 512 outputs, column tile of 256, sample split).  Every MMA has
-// M = 256 outputs (128 per CTA, each CTA loads the dY tiles of its own rows) and N = 256 columns of
-// which each CTA GENERATES ONLY 128: the operand producers -- the resource that bounds the
-// single-CTA kernel (measured: with a third of the MMAs it is hardly faster) -- do half the work
-// per flop.  Two accumulators (two 256-output halves of the group) fill the 512 TMEM columns of
-// each CTA.  Slab layout and finalize kernels are those of the single-CTA kernel.
-constexpr int PB_G_STAGES = 4, PB_D_SLOTS = 3;
-constexpr uint32_t PB_G_HALF_BYTES = TILE_B_BYTES / 2;                    // 128 columns x 64 samples, bf16
-constexpr uint32_t PB_G_STAGE_BYTES = 2 * PB_G_HALF_BYTES;                // hi + lo
-constexpr uint32_t PB_SMEM_G = 0;
-constexpr uint32_t PB_SMEM_D = PB_SMEM_G + PB_G_STAGES * PB_G_STAGE_BYTES;
-constexpr uint32_t PB_SMEM_CTRL = PB_SMEM_D + PB_D_SLOTS * BWD_D_SLOT_BYTES;
-constexpr uint32_t PB_CTRL_BYTES = 512 + TAB_SMEM_FLOATS * 4;
-constexpr uint32_t PB_SMEM_BYTES = PB_SMEM_CTRL + PB_CTRL_BYTES;
-static_assert(PB_SMEM_BYTES <= 232448, "pair backward kernel shared memory exceeds 227 KB");
-
-struct PairBwdCtrl {
-    uint64_t fullG[PB_G_STAGES], emptyG[PB_G_STAGES], peerG[PB_G_STAGES];
-    uint64_t fullD[PB_D_SLOTS], emptyD[PB_D_SLOTS], peerD[PB_D_SLOTS];
-    uint64_t chunkFull, drained, peerDrained;
-    uint32_t tmem_base;
-    int abort_flag;
-};
-static_assert(sizeof(PairBwdCtrl) <= 512, "control block too large");
-
-// plan.splits / kb_per_split are those of the PAIR decomposition: items = n_ogroups * n_ctiles * splits
-template <int NTERMS, bool WIDE>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-tc_bwd_param_pair_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ dyimg,
-                         float* __restrict__ partial, int* __restrict__ status,
-                         int64_t N, int I, int O, BwdPlan plan, TabInfo ti, int vec_ok) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr bool SPLIT = (NTERMS == 3);
-    const uint32_t sbase = smem_u32(smem);
-    PairBwdCtrl* ctrl = reinterpret_cast<PairBwdCtrl*>(smem + PB_SMEM_CTRL);
-    float* stab = reinterpret_cast<float*>(smem + PB_SMEM_CTRL + 512);
-    volatile int* abort_flag = &ctrl->abort_flag;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();
-    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const bool shared_grid = grid_is_shared(tab, I, ti);
-    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
-    const int n_ohalves = plan.n_otiles * 2;
-    const int n_ctiles = plan.n_ctiles();
-    const int n_ogroups = (plan.n_otiles + 1) / 2;
-    const int64_t n_items = (int64_t)n_ogroups * n_ctiles * plan.splits;
-
-    const bool bad_smem = (sbase & 1023u) != 0;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < PB_G_STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->fullG[s]), WORKER_THREADS);
-            mbar_init(smem_u32(&ctrl->emptyG[s]), 1);
-            mbar_init(smem_u32(&ctrl->peerG[s]), 1);
-        }
-        for (int s = 0; s < PB_D_SLOTS; ++s) {
-            mbar_init(smem_u32(&ctrl->fullD[s]), 1);
-            mbar_init(smem_u32(&ctrl->emptyD[s]), 1);
-            mbar_init(smem_u32(&ctrl->peerD[s]), 1);
-        }
-        mbar_init(smem_u32(&ctrl->chunkFull), 1);
-        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
-        mbar_init(smem_u32(&ctrl->peerDrained), 1);
-        ctrl->abort_flag = bad_smem ? 1 : 0;
-        fence_mbar_init();
-    }
-    if (warp == MMA_WARP) {
-        tmem_alloc_pair(smem_u32(&ctrl->tmem_base), 512);
-        tmem_relinquish_pair();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = ctrl->tmem_base;
-    if (bad_smem && threadIdx.x == 0) report_status(status, kStatusBadSmem);
-
-    // item -> (split, output group of 512, column tile); consecutive items share the output group
-    auto decode = [&](int64_t item, int& sp, int& og, int& ct) {
-        ct = (int)(item % n_ctiles);
-        const int64_t rest = item / n_ctiles;
-        og = (int)(rest % n_ogroups);
-        sp = (int)(rest / n_ogroups);
-    };
-    auto k_range = [&](int sp, int64_t& kb0, int64_t& kb1) {
-        kb0 = (int64_t)sp * plan.kb_per_split;
-        kb1 = kb0 + plan.kb_per_split;
-        if (kb1 > plan.kb_total) kb1 = plan.kb_total;
-    };
-    auto halves_of = [&](int og) { return (plan.n_otiles - 2 * og) >= 2 ? 2 : 1; };
-
-    if (warp < WORKER_WARPS) {
-        // ===== workers: this CTA's 128 columns x 64 samples per block, MN-major; drains =====
-        const int quad = warp & 3, part = warp >> 2;
-        // spline tiles: thread = (sample, 2 chunks); base tiles: thread = (2 samples, 8 features)
-        const int n_loc = (warp & 1) * 32 + lane;       // sample within the block (spline tiles)
-        const int fq = warp >> 1;                       // pair of chunks (spline tiles), 0..7
-        const int kg = warp >> 1;                       // group of 8 samples (base tiles)
-        const int r0 = (warp & 1) * 4 + (lane >> 4) * 2; // first of this thread's 2 rows in the group
-        const int bch = lane & 15;                      // chunk of 8 base features within the half tile
-        uint32_t it = 0, n_drained = 0;
-        bool ok = !bad_smem;
-        bool pend = false, pend_first = false;
-        int pend_sp = 0, pend_og = 0, pend_ct = 0;
-        auto drain = [&]() -> bool {
-            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
-            ++n_drained;
-            tc_fence_after_sync();
-            const int row = quad * 32 + lane;
-            const int nh = halves_of(pend_og);
-#pragma unroll 1
-            for (int h = 0; h < nh; ++h) {
-                // accumulator h = output tile 2 og + h; this CTA holds its rows [128 rank, 128 rank + 128)
-                float4* tile = reinterpret_cast<float4*>(partial) +
-                               ((((size_t)pend_sp * plan.n_otiles + (pend_og * 2 + h)) * n_ctiles + pend_ct) * 2 + rank) *
-                                   (size_t)(64 * 128);
-#pragma unroll 1
-                for (int c = part; c < BLOCK_N / 32; c += 4) {
-                    float4* dst = tile + ((size_t)c * 8) * 128 + row;
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + h * BLOCK_N + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        if (pend_first)
-                            dst[(size_t)q * 128] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                        else
-                            red_add_v4(reinterpret_cast<float*>(dst + (size_t)q * 128), __uint_as_float(r[4 * q]),
-                                       __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
-                                       __uint_as_float(r[4 * q + 3]));
-                    }
-                }
-            }
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->drained));
-            pend = false;
-            return true;
-        };
-
-        for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
-            int sp, og, ct;
-            decode(item, sp, og, ct);
-            const bool spline = ct < plan.ct_spline;
-            const int f_tile0 = spline ? 0 : (ct - plan.ct_spline) * 256 + (int)rank * 128;
-            int64_t kb0, kb1;
-            k_range(sp, kb0, kb1);
-            // spline tiles: chunk g = 32 ct + 16 rank + 2 fq + q belongs to feature g / cpf and holds its
-            // slots 8 (g % cpf) ..; the inputs of the next block of samples are loaded one iteration ahead
-            int cf[2], ccw[2];
-            {
-                const int g0 = ct * 32 + (int)rank * 16 + fq * 2;
-                const int cpf = WIDE ? ti.cpf : 1;
-                cf[0] = g0 / cpf;
-                ccw[0] = g0 - cf[0] * cpf;
-                cf[1] = cf[0];
-                ccw[1] = ccw[0] + 1;
-                if (ccw[1] == cpf) { cf[1] += 1; ccw[1] = 0; }
-            }
-            const int f_sp = cf[0];
-            float nx[2] = {0.f, 0.f};
-            auto prefetch_spline = [&](int64_t kb) {
-                const int64_t n = kb * BLOCK_K + n_loc;
-                nx[0] = 0.f;
-                nx[1] = 0.f;
-                if (n < N && f_sp < I) {
-                    const float* xr = x + (size_t)n * I;
-                    if (!WIDE && vec_ok && f_sp + 2 <= I) {
-                        const float2 v = __ldg(reinterpret_cast<const float2*>(xr + f_sp));
-                        nx[0] = v.x; nx[1] = v.y;
-                    } else {
-                        nx[0] = __ldg(xr + cf[0]);
-                        if (cf[1] < I) nx[1] = (cf[1] == cf[0]) ? nx[0] : __ldg(xr + cf[1]);
-                    }
-                }
-            };
-            if (spline) prefetch_spline(kb0);
-            for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
-                const uint32_t stage = it % PB_G_STAGES;
-                const uint32_t g_hi = sbase + PB_SMEM_G + stage * PB_G_STAGE_BYTES;
-                const uint32_t g_lo = g_hi + PB_G_HALF_BYTES;
-                const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
-                const uint32_t empty_parity = ((it / PB_G_STAGES) & 1u) ^ 1u;
-                if (spline) {
-                    const float xv[2] = {nx[0], nx[1]};
-                    if (kb + 1 < kb1) prefetch_spline(kb + 1);
-                    const bool n_ok = kb * BLOCK_K + n_loc < N;
-                    const int kk = n_loc & 7;
-                    Window w;
-                    uint4 hi[2], lo[2];
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        const int f = cf[q];
-                        if (!WIDE || q == 0 || f != cf[q - 1]) {    // uniform over the warp
-                            if (shared_grid)
-                                w = eval_window<SPLIT, true, WIDE>(stab, ti, xv[q]);
-                            else
-                                w = eval_window<SPLIT, false, WIDE>(tab + (size_t)(f < I ? f : I - 1) * ti.fs, ti,
-                                                                    xv[q]);
-                        }
-                        place_window<SPLIT>(w, ccw[q], hi[q], lo[q]);
-                        if (!(n_ok && f < I)) {
-                            hi[q] = make_uint4(0, 0, 0, 0);
-                            lo[q] = hi[q];
-                        }
-                    }
-                    if (!mbar_wait(smem_u32(&ctrl->emptyG[stage]), empty_parity, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        const int fl = fq * 2 + q;                       // chunk within the half tile, 0..15
-                        const uint32_t off = (uint32_t)((fl >> 3) * 8 + (n_loc >> 3)) * 1024u + (uint32_t)kk * 128u +
-                                             (uint32_t)(((fl & 7) ^ kk) << 4);
-                        st_shared_v4(g_hi + off, hi[q]);
-                        if (SPLIT) st_shared_v4(g_lo + off, lo[q]);
-                    }
-                } else {
-                    // lane & 15 = chunk of 8 base features of this CTA's 128; two sample rows per thread
-                    const int64_t nrow0 = kb * BLOCK_K + kg * 8 + r0;
-                    const uint32_t atom = (uint32_t)((bch >> 3) * 8 + kg) * 1024u;   // [col group][sample group]
-                    const int f0 = f_tile0 + bch * 8;
-                    float xv[2][8];
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) load_x8(x, nrow0 + q, nrow0 + q < N, I, f0, vec_ok != 0, xv[q]);
-                    if (!mbar_wait(smem_u32(&ctrl->emptyG[stage]), empty_parity, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-#pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        uint4 hi, lo;
-                        silu_chunk<SPLIT>(xv[q], hi, lo);
-                        const int rr = r0 + q;
-                        const uint32_t off = atom + (uint32_t)rr * 128u + (uint32_t)(((bch & 7) ^ rr) << 4);
-                        st_shared_v4(g_hi + off, hi);
-                        if (SPLIT) st_shared_v4(g_lo + off, lo);
-                    }
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->fullG[stage]));
-                if (pend && chunk_start) {
-                    if (!drain()) {
-                        ok = false;
-                        break;
-                    }
-                }
-                if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
-                    pend = true;
-                    pend_first = (kb - kb0) < plan.chunk_kb;
-                    pend_sp = sp;
-                    pend_og = og;
-                    pend_ct = ct;
-                }
-            }
-        }
-        if (ok && pend) drain();
-    } else if (warp == MMA_WARP) {
-        if (lane == 0 && !bad_smem) {
-            if (rank == 0) {
-                // ===== leader: MMA issue =====
-                constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, true, true, 2 * BLOCK_M);
-                constexpr uint64_t dbase = make_sdesc_sw128(8192, 1024);
-                uint32_t it = 0, dslot = 0, n_chunks = 0;
-                bool ok = true;
-                for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
-                    int sp, og, ct;
-                    decode(item, sp, og, ct);
-                    const int nh = halves_of(og);
-                    int64_t kb0, kb1;
-                    k_range(sp, kb0, kb1);
-                    for (int64_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-                        const uint32_t stage = it % PB_G_STAGES;
-                        const uint32_t g_hi = sbase + PB_SMEM_G + stage * PB_G_STAGE_BYTES;
-                        const uint32_t g_lo = g_hi + PB_G_HALF_BYTES;
-                        const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
-                        if (chunk_start && n_chunks > 0) {
-                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag) ||
-                                !mbar_wait_cluster(smem_u32(&ctrl->peerDrained), (n_chunks - 1) & 1u, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                        }
-                        const uint32_t g_parity = (it / PB_G_STAGES) & 1u;
-                        if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), g_parity, abort_flag) ||
-                            !mbar_wait_cluster(smem_u32(&ctrl->peerG[stage]), g_parity, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        for (int h = 0; h < nh; ++h, ++dslot) {
-                            const uint32_t slot = dslot % PB_D_SLOTS;
-                            const uint32_t d_parity = (dslot / PB_D_SLOTS) & 1u;
-                            if (!mbar_wait(smem_u32(&ctrl->fullD[slot]), d_parity, abort_flag) ||
-                                !mbar_wait_cluster(smem_u32(&ctrl->peerD[slot]), d_parity, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                            tc_fence_after_sync();
-                            const uint32_t d_hi = sbase + PB_SMEM_D + slot * BWD_D_SLOT_BYTES;
-                            const uint32_t d_lo = d_hi + TILE_A_BYTES;
-                            const uint32_t d_tmem = tmem_base + h * BLOCK_N;
-#pragma unroll
-                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                                mma_f16_ss_pair(d_tmem, sdesc_at(dbase, d_hi + ks * 2048),
-                                                sdesc_at(dbase, g_hi + ks * 2048), idesc, (!chunk_start || ks > 0) ? 1u : 0u);
-                            if (SPLIT) {
-#pragma unroll
-                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, d_lo + ks * 2048),
-                                                    sdesc_at(dbase, g_hi + ks * 2048), idesc, 1u);
-#pragma unroll
-                                for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
-                                    mma_f16_ss_pair(d_tmem, sdesc_at(dbase, d_hi + ks * 2048),
-                                                    sdesc_at(dbase, g_lo + ks * 2048), idesc, 1u);
-                            }
-                            mma_commit_pair(smem_u32(&ctrl->emptyD[slot]));
-                        }
-                        if (!ok) break;
-                        mma_commit_pair(smem_u32(&ctrl->emptyG[stage]));
-                        if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
-                            mma_commit_pair(smem_u32(&ctrl->chunkFull));
-                            ++n_chunks;
-                        }
-                    }
-                }
-            } else {
-                // ===== peer: forwards the readiness of its own stages / slots / drains to the leader =====
-                const uint32_t l_peerDrained = map_to_cta(smem_u32(&ctrl->peerDrained), 0);
-                uint32_t it = 0, dslot = 0, n_chunks = 0;
-                bool ok = true;
-                for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
-                    int sp, og, ct;
-                    decode(item, sp, og, ct);
-                    const int nh = halves_of(og);
-                    int64_t kb0, kb1;
-                    k_range(sp, kb0, kb1);
-                    for (int64_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
-                        const uint32_t stage = it % PB_G_STAGES;
-                        const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
-                        if (chunk_start && n_chunks > 0) {
-                            if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                            mbar_arrive_remote(l_peerDrained);
-                        }
-                        if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), (it / PB_G_STAGES) & 1u, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerG[stage]), 0));
-                        for (int h = 0; h < nh; ++h, ++dslot) {
-                            const uint32_t slot = dslot % PB_D_SLOTS;
-                            if (!mbar_wait(smem_u32(&ctrl->fullD[slot]), (dslot / PB_D_SLOTS) & 1u, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
-                            mbar_arrive_remote(map_to_cta(smem_u32(&ctrl->peerD[slot]), 0));
-                        }
-                        if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) ++n_chunks;
-                    }
-                }
-            }
-        }
-    } else {
-        if (lane == 0 && !bad_smem) {
-            // ===== bulk copies: the dY tiles of this CTA's own 128 output rows =====
-            uint32_t dslot = 0;
-            bool ok = true;
-            for (int64_t item = pair; item < n_items && ok; item += n_pairs) {
-                int sp, og, ct;
-                decode(item, sp, og, ct);
-                const int nh = halves_of(og);
-                int64_t kb0, kb1;
-                k_range(sp, kb0, kb1);
-                for (int64_t kb = kb0; kb < kb1 && ok; ++kb) {
-                    for (int h = 0; h < nh; ++h, ++dslot) {
-                        const uint32_t slot = dslot % PB_D_SLOTS;
-                        if (!mbar_wait(smem_u32(&ctrl->emptyD[slot]), ((dslot / PB_D_SLOTS) & 1u) ^ 1u,
-                                               abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        const size_t ohalf = (size_t)(og * 2 + h) * 2 + rank;
-                        const uint8_t* src = dyimg + ((size_t)kb * n_ohalves + ohalf) * BWD_D_SLOT_BYTES;
-                        const uint32_t bytes = SPLIT ? BWD_D_SLOT_BYTES : TILE_A_BYTES;
-                        const uint32_t bar = smem_u32(&ctrl->fullD[slot]);
-                        mbar_arrive_expect_tx(bar, bytes);
-                        bulk_g2s(sbase + PB_SMEM_D + slot * BWD_D_SLOT_BYTES, src, bytes, bar);
-                    }
-                }
-            }
-        }
-    }
-
-    if (*abort_flag && !bad_smem) {
-        if (lane == 0) report_status(status, kStatusTimeout);
-        __nanosleep(100000);
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();
-    tc_fence_after_sync();
-    if (warp == MMA_WARP) {
-        __syncwarp();
-        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -2271,36 +1487,6 @@ inline int fwd_chunk_kb(int) { return g_fwd_chunk; }
 inline int bwd_chunk_kb() { return g_bwd_chunk; }
 inline int dx_chunk_kb() { return g_dx_chunk; }
 
-// 1 = the kernels that run on CTA pairs (clusters of two, tcgen05 cta_group::2) where they exist.
-int g_pair_kernels = 1;
-
-// Launches `kernel` as clusters of two CTAs: min(items, co-resident clusters) of them.
-// cudaErrorNotSupported when not even one cluster fits (the caller falls back to single CTAs).
-template <typename Kernel, typename... Args>
-cudaError_t launch_pairs(Kernel kernel, int64_t items, uint32_t smem_bytes, cudaStream_t st, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = st;
-    cfg.gridDim = dim3(2);
-    int max_clusters = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
-    if (e != cudaSuccess || max_clusters < 1) {
-        cudaGetLastError();
-        return cudaErrorNotSupported;
-    }
-    const int64_t pairs = items < max_clusters ? items : max_clusters;
-    cfg.gridDim = dim3((unsigned)(2 * pairs));
-    return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
 inline BwdPlan plan_bwd(const LayerShape& s, bool has_base) {
     BwdPlan p;
     p.n_otiles = (s.O + BLOCK_N - 1) / BLOCK_N;
@@ -2371,9 +1557,6 @@ void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb) {
     g_dx_chunk = clamp(dx_kb, g_dx_chunk, kDxChunkKb);
 }
 
-void tc_set_pair_kernels(int on) { g_pair_kernels = on ? 1 : 0; }
-int tc_get_pair_kernels() { return g_pair_kernels; }
-
 bool tc_supported(const LayerShape& s) {
     // any grid the layer accepts (G + 2 K <= 71); the window of k + 1 <= 4 values is what the
     // table entries hold
@@ -2425,25 +1608,6 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     P.vec_y = ((s.O & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
     P.ti = ti;
     cudaError_t e = cudaSuccess;
-    if (g_pair_kernels) {
-        // CTA pairs: tile = 256 samples x 512 outputs, one cluster of two CTAs each
-        const int64_t n_ptiles = ((s.N + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * P.n_opairs;
-#define KAN_FWD_PAIR(NT, W)                                                                                   \
-    do {                                                                                                      \
-        e = ensure_dynamic_smem<tc_forward_pair_kernel<NT, W>>((int)PF_SMEM_BYTES);                           \
-        if (e == cudaSuccess)                                                                                 \
-            e = launch_pairs(tc_forward_pair_kernel<NT, W>, n_ptiles, PF_SMEM_BYTES, st, x,                   \
-                             (const float*)tab, (const uint8_t*)wimg, y, status, P);                          \
-    } while (0)
-        if (ti.cpf == 1) {
-            if (split_terms == 3) KAN_FWD_PAIR(3, false); else KAN_FWD_PAIR(1, false);
-        } else {
-            if (split_terms == 3) KAN_FWD_PAIR(3, true); else KAN_FWD_PAIR(1, true);
-        }
-#undef KAN_FWD_PAIR
-        if (e != cudaErrorNotSupported) return e != cudaSuccess ? e : cudaGetLastError();
-        e = cudaSuccess;                 // no room for a single cluster: the single-CTA kernel runs
-    }
     const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
 #define KAN_FWD(NT, W)                                                                                         \
     do {                                                                                                      \
@@ -2497,27 +1661,6 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
     }
     const int vec_ok = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     if (need_param) {
-        bool launched = false;
-        if (g_pair_kernels) {
-            const int64_t pair_items = (int64_t)((L.plan.n_otiles + 1) / 2) * L.plan.n_ctiles() * L.plan.splits;
-#define KAN_BWD_PAIR(NT, W)                                                                                   \
-    do {                                                                                                      \
-        e = ensure_dynamic_smem<tc_bwd_param_pair_kernel<NT, W>>((int)PB_SMEM_BYTES);                         \
-        if (e == cudaSuccess)                                                                                 \
-            e = launch_pairs(tc_bwd_param_pair_kernel<NT, W>, pair_items, PB_SMEM_BYTES, st, x,               \
-                             (const float*)tab, (const uint8_t*)dyimg, partial, status, (int64_t)s.N, s.I,    \
-                             s.O, L.plan, ti, vec_ok);                                                        \
-    } while (0)
-            if (ti.cpf == 1) {
-                if (split_terms == 3) KAN_BWD_PAIR(3, false); else KAN_BWD_PAIR(1, false);
-            } else {
-                if (split_terms == 3) KAN_BWD_PAIR(3, true); else KAN_BWD_PAIR(1, true);
-            }
-#undef KAN_BWD_PAIR
-            if (e == cudaSuccess) launched = true;
-            else if (e != cudaErrorNotSupported) return e;
-            e = cudaSuccess;
-        }
         const int64_t items = L.plan.n_items();
         const int blocks = (int)(items < sm_count() ? items : sm_count());
 #define KAN_BWD(NT, W)                                                                                         \
@@ -2527,12 +1670,10 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
             tc_bwd_param_kernel<NT, W><<<blocks, TC_THREADS, BWD_SMEM_BYTES, st>>>(                           \
                 x, tab, dyimg, partial, status, s.N, s.I, s.O, L.plan, ti, vec_ok);                           \
     } while (0)
-        if (!launched) {
-            if (ti.cpf == 1) {
-                if (split_terms == 3) KAN_BWD(3, false); else KAN_BWD(1, false);
-            } else {
-                if (split_terms == 3) KAN_BWD(3, true); else KAN_BWD(1, true);
-            }
+        if (ti.cpf == 1) {
+            if (split_terms == 3) KAN_BWD(3, false); else KAN_BWD(1, false);
+        } else {
+            if (split_terms == 3) KAN_BWD(3, true); else KAN_BWD(1, true);
         }
 #undef KAN_BWD
         if (e != cudaSuccess) return e;

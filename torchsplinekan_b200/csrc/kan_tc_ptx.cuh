@@ -135,94 +135,14 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---- CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) ----------------------------
-// The two CTAs of a pair run one MMA together: M = 256 accumulator rows (128 per CTA, each CTA
-// supplies its own A rows) and each CTA supplies HALF of the B rows, so a CTA stages and reads half
-// of the B operand a single CTA would.  One thread of the even CTA (the leader) issues the MMAs;
-// shared-memory descriptors hold CTA-local offsets that both CTAs resolve in their own memory.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address of the same shared-memory location in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait on a barrier that the other CTA of the pair arrives on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#pragma unroll 1
-    for (int it = 0; it < 128; ++it)
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-#pragma unroll 1
-    while (true) {
-#pragma unroll 1
-        for (int it = 0; it < 512; ++it)
-            if (mbar_try_wait_cluster(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish_pair() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Arrives, once every MMA issued so far is done, on the barrier at this shared-memory offset in
-// BOTH CTAs of the pair.
-__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
-    const uint16_t both = 3;
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(bar), "h"(both)
-        : "memory");
-}
-
 // ---- descriptors ------------------------------------------------------------
 // Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, M = 128.
 // Bit layout: [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B
 // format, 15 A major, 16 B major (0 = K-major, 1 = MN-major), [17,23) N >> 3,
 // [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int n, bool a_mn_major, bool b_mn_major, int m = 128) {
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int n, bool a_mn_major, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
-           ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+           ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 // Shared-memory matrix descriptor, 128-byte swizzle.  Bit layout: [0,14) start
 // address >> 4, [16,30) leading-dimension byte offset >> 4, [32,46) stride-

@@ -118,16 +118,23 @@ Scratch* scratch(const c10::Device& dev, cudaStream_t st, int purpose, size_t by
         if (!s.buf.defined() || (size_t)s.buf.numel() < bytes) {
             s.buf = at::empty({(int64_t)bytes + 256}, at::TensorOptions().dtype(at::kByte).device(dev));
             C10_CUDA_CHECK(cudaMemsetAsync(s.buf.data_ptr(), 0, 256, st));
-            if (!s.mirror) {
-                C10_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&s.mirror), sizeof(int), cudaHostAllocMapped));
-                *s.mirror = 0;
+            // Host allocations and copies from pageable memory are not allowed while the stream is
+            // being captured into a graph: a buffer first created there gets no host-visible int
+            // (its device word still works, check_status reads it).
+            cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+            C10_CUDA_CHECK(cudaStreamIsCapturing(st, &capturing));
+            if (capturing == cudaStreamCaptureStatusNone) {
+                if (!s.mirror) {
+                    C10_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&s.mirror), sizeof(int), cudaHostAllocMapped));
+                    *s.mirror = 0;
+                }
+                void* mirror_dev = nullptr;
+                C10_CUDA_CHECK(cudaHostGetDevicePointer(&mirror_dev, s.mirror, 0));
+                s.mirror_dev = mirror_dev;
+                // the 8-byte source of this copy must outlive the call: it lives in the registry entry
+                C10_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(s.buf.data_ptr()) + 8, &s.mirror_dev,
+                                               sizeof(void*), cudaMemcpyHostToDevice, st));
             }
-            void* mirror_dev = nullptr;
-            C10_CUDA_CHECK(cudaHostGetDevicePointer(&mirror_dev, s.mirror, 0));
-            s.mirror_dev = mirror_dev;
-            // the 8-byte source of this copy must outlive the call: it lives in the registry entry
-            C10_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(s.buf.data_ptr()) + 8, &s.mirror_dev, sizeof(void*),
-                                           cudaMemcpyHostToDevice, st));
         }
         out = &s;
     }
