@@ -218,7 +218,9 @@ static_assert(FWD_SMEM_BYTES <= 232448, "forward kernel shared memory exceeds 22
 struct FwdCtrl {
     uint64_t fullA[FWD_A_STAGES], emptyA[FWD_A_STAGES];
     uint64_t fullB[FWD_B_SLOTS], emptyB[FWD_B_SLOTS];
-    uint64_t chunkFull, drained;
+    // per 256-column accumulator: its chain is complete / its columns have been drained.  Kept apart
+    // so that one accumulator is drained while the MMAs of the other run.
+    uint64_t chunkFull[2], drained[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -262,8 +264,10 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
             mbar_init(smem_u32(&ctrl->fullB[s]), 1);
             mbar_init(smem_u32(&ctrl->emptyB[s]), 1);
         }
-        mbar_init(smem_u32(&ctrl->chunkFull), 1);
-        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
+        for (int j = 0; j < 2; ++j) {
+            mbar_init(smem_u32(&ctrl->chunkFull[j]), 1);
+            mbar_init(smem_u32(&ctrl->drained[j]), WORKER_THREADS);
+        }
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
@@ -281,7 +285,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
         const int quad = warp & 3;                        // TMEM lane quadrant = row group
         const int part = warp >> 2;                       // which quarter of the k-block / column groups
         const int row = quad * 32 + lane;
-        uint32_t it = 0, n_drained = 0;
+        uint32_t it = 0, n_drained[2] = {0, 0};
         bool ok = true;
         // drain bookkeeping: the chunk that ended most recently and is not yet added to y
         bool pend = false, pend_first = false;
@@ -289,22 +293,25 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
         int pend_op = 0;
 
         auto drain = [&]() -> bool {
-            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
-            ++n_drained;
-            tc_fence_after_sync();
             const int64_t n = pend_mt * BLOCK_M + row;
             const int nsub = (P.n_otiles - 2 * pend_op) >= 2 ? 2 : 1;
 #pragma unroll 1
-            for (int c = part; c < nsub * (BLOCK_N / 32); c += 4) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, r);
-                tmem_ld_wait();
-                const int col0 = pend_op * 2 * BLOCK_N + c * 32;
-                if (n < P.N && col0 < P.O)
-                    drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
+            for (int j = 0; j < nsub; ++j) {
+                if (!mbar_wait(smem_u32(&ctrl->chunkFull[j]), n_drained[j] & 1u, abort_flag)) return false;
+                ++n_drained[j];
+                tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = part; c < BLOCK_N / 32; c += 4) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + j * BLOCK_N + c * 32, r);
+                    tmem_ld_wait();
+                    const int col0 = (pend_op * 2 + j) * BLOCK_N + c * 32;
+                    if (n < P.N && col0 < P.O)
+                        drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->drained[j]));
             }
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->drained));
             pend = false;
             return true;
         };
@@ -420,7 +427,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
             // ===== MMA issue =====
             constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, false, false);
             constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
-            uint32_t it = 0, bslot = 0, n_chunks = 0;
+            uint32_t it = 0, bslot = 0, n_chunks[2] = {0, 0};
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
                 const int64_t mt = tile / P.n_opairs;
@@ -431,13 +438,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                     const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                     const uint32_t a_lo = a_hi + TILE_A_BYTES;
                     const bool chunk_start = (kb % P.chunk_kb) == 0;
-                    if (chunk_start && n_chunks > 0) {
-                        // the accumulator may be overwritten only after the workers have drained it
-                        if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                    }
+                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total;
                     if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FWD_A_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -445,6 +446,14 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                     tc_fence_after_sync();
                     for (int j = 0; j < nsub && ok; ++j) {
                         const uint32_t d_tmem = tmem_base + j * BLOCK_N;
+                        if (chunk_start && n_chunks[j] > 0) {
+                            // this accumulator may be overwritten only after the workers have drained it
+                            if (!mbar_wait(smem_u32(&ctrl->drained[j]), (n_chunks[j] - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                        }
                         const uint32_t slot_h = bslot % FWD_B_SLOTS;
                         if (!mbar_wait(smem_u32(&ctrl->fullB[slot_h]), (bslot / FWD_B_SLOTS) & 1u, abort_flag)) {
                             ok = false;
@@ -479,13 +488,14 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                             mma_commit(smem_u32(&ctrl->emptyB[slot_l]));
                             ++bslot;
                         }
+                        if (chunk_end) {
+                            // this accumulator's chain is complete: its drain overlaps the MMAs of the other
+                            mma_commit(smem_u32(&ctrl->chunkFull[j]));
+                            ++n_chunks[j];
+                        }
                     }
                     if (!ok) break;
                     mma_commit(smem_u32(&ctrl->emptyA[stage]));
-                    if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
-                        mma_commit(smem_u32(&ctrl->chunkFull));
-                        ++n_chunks;
-                    }
                 }
             }
         }
@@ -554,7 +564,7 @@ static_assert(BWD_SMEM_BYTES <= 232448, "backward kernel shared memory exceeds 2
 struct BwdCtrl {
     uint64_t fullG[BWD_G_STAGES], emptyG[BWD_G_STAGES];
     uint64_t fullD[BWD_D_SLOTS], emptyD[BWD_D_SLOTS];
-    uint64_t chunkFull, drained;
+    uint64_t chunkFull[2], drained[2];     // per 128-row half of the accumulator (see FwdCtrl)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -605,8 +615,10 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             mbar_init(smem_u32(&ctrl->fullD[s]), 1);
             mbar_init(smem_u32(&ctrl->emptyD[s]), 1);
         }
-        mbar_init(smem_u32(&ctrl->chunkFull), 1);
-        mbar_init(smem_u32(&ctrl->drained), WORKER_THREADS);
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(smem_u32(&ctrl->chunkFull[h]), 1);
+            mbar_init(smem_u32(&ctrl->drained[h]), WORKER_THREADS);
+        }
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
@@ -645,9 +657,6 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
         bool pend = false, pend_first = false;
         int pend_sp = 0, pend_ot = 0, pend_ct = 0;
         auto drain = [&]() -> bool {
-            if (!mbar_wait(smem_u32(&ctrl->chunkFull), n_drained & 1u, abort_flag)) return false;
-            ++n_drained;
-            tc_fence_after_sync();
             // Partial sums live in a blocked layout so that a warp (32 consecutive rows) touches
             // contiguous memory: tile (split, o-tile, c-tile) -> [half][column / 4][row][4 floats].
             float4* tile = reinterpret_cast<float4*>(partial) +
@@ -655,6 +664,8 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
             const int row = quad * 32 + lane;
 #pragma unroll 1
             for (int h = 0; h < 2; ++h) {
+                if (!mbar_wait(smem_u32(&ctrl->chunkFull[h]), n_drained & 1u, abort_flag)) return false;
+                tc_fence_after_sync();
 #pragma unroll 1
                 for (int c = part; c < BLOCK_N / 32; c += 4) {
                     float4* dst = tile + ((size_t)h * 64 + c * 8) * 128 + row;
@@ -672,9 +683,10 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                                        __uint_as_float(r[4 * q + 3]));
                     }
                 }
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->drained[h]));
             }
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->drained));
+            ++n_drained;
             pend = false;
             return true;
         };
@@ -816,17 +828,19 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                     const uint32_t g_hi = sbase + BWD_SMEM_G + stage * BWD_G_STAGE_BYTES;
                     const uint32_t g_lo = g_hi + TILE_B_BYTES;
                     const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
-                    if (chunk_start && n_chunks > 0) {
-                        if (!mbar_wait(smem_u32(&ctrl->drained), (n_chunks - 1) & 1u, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                    }
+                    const bool chunk_end = ((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1;
                     if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), (it / BWD_G_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
                     for (int h = 0; h < 2; ++h, ++dslot) {
+                        if (chunk_start && n_chunks > 0) {
+                            // half h may be overwritten only after the workers have drained it
+                            if (!mbar_wait(smem_u32(&ctrl->drained[h]), (n_chunks - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                        }
                         const uint32_t slot = dslot % BWD_D_SLOTS;
                         if (!mbar_wait(smem_u32(&ctrl->fullD[slot]), (dslot / BWD_D_SLOTS) & 1u, abort_flag)) {
                             ok = false;
@@ -851,13 +865,12 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                                            sdesc_at(dbase, g_lo + ks * 2048), idesc, 1u);
                         }
                         mma_commit(smem_u32(&ctrl->emptyD[slot]));
+                        // the half's chain is complete: its drain overlaps the MMAs of the other half
+                        if (chunk_end) mma_commit(smem_u32(&ctrl->chunkFull[h]));
                     }
                     if (!ok) break;
                     mma_commit(smem_u32(&ctrl->emptyG[stage]));
-                    if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
-                        mma_commit(smem_u32(&ctrl->chunkFull));
-                        ++n_chunks;
-                    }
+                    if (chunk_end) ++n_chunks;
                 }
             }
         }

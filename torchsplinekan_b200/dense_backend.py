@@ -145,10 +145,14 @@ def curve2coeff(x_samples: torch.Tensor, y_samples: torch.Tensor, grid: torch.Te
         return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype)
     n_feat, n_samp, n_coef = A.shape
     n_out = y_samples.shape[0]
-    # reduced QR: Q [I, B, m], Rm [I, m, R] with m = min(B, R) (fewer samples than coefficients
-    # leave a wide system, whose minimum-norm solution the solver below still returns)
-    Q, Rm = torch.linalg.qr(A.to(torch.float64))
-    Z = torch.empty((n_feat, Rm.shape[1], n_out), dtype=torch.float64, device=A.device)
+    if n_samp < n_coef:
+        # fewer samples than coefficients: nothing to reduce, and the rank decisions of the
+        # minimum-norm solver should be taken on the very matrix the CPU path hands it
+        Y = y_samples.permute(2, 1, 0).contiguous().to(torch.float64)
+        sol = torch.linalg.lstsq(A.to(torch.float64).cpu(), Y.cpu()).solution
+        return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype, device=x_samples.device)
+    Q, Rm = torch.linalg.qr(A.to(torch.float64))                                           # [I, B, R], [I, R, R]
+    Z = torch.empty((n_feat, n_coef, n_out), dtype=torch.float64, device=A.device)
     # Q^T Y in slabs of features, so that the float64 copy of Y stays below ~512 MB
     step = max(1, int((1 << 26) // max(1, n_samp * n_out)))
     for lo in range(0, n_feat, step):
