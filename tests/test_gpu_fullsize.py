@@ -331,14 +331,18 @@ def test_prefetcher_never_overwrites_a_batch_that_is_still_read():
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.float64, 1e-9)])
 def test_update_grid_with_fewer_samples_than_coefficients(dtype, tol):
-    """update_grid on 4 samples with 8 coefficients per edge: the wide least-squares systems take
-    the minimum-norm solution on the GPU path as on the CPU path."""
+    """update_grid on 4 samples with 8 coefficients per edge (used to raise a shape error on CUDA
+    samples): the wide systems get the minimum-norm solution, which interpolates the old curves
+    at the samples, on the GPU path as on the CPU path."""
     torch.manual_seed(0)
     a = sk.KANLinear(6, 5, backend="reference").to(dtype)
     b = sk.KANLinear(6, 5, backend="reference").to("cuda", dtype)
     b.load_state_dict(a.state_dict())
     x = torch.rand(4, 6, dtype=dtype) * 2 - 1
+    before = torch.einsum("oir,bir->obi", a.spline_weight, db.compute_basis(x, a.grid, 3)).detach()
     a.update_grid(x)
     b.update_grid(x.cuda())
     assert _err(b.grid, a.grid) < 1e-6
     assert _err(b.spline_weight, a.spline_weight) < tol
+    after = torch.einsum("oir,bir->obi", b.spline_weight.cpu(), db.compute_basis(x, b.grid.cpu(), 3)).detach()
+    assert _err(after, before) < (1e-4 if dtype == torch.float32 else 1e-10)

@@ -139,18 +139,21 @@ def curve2coeff(x_samples: torch.Tensor, y_samples: torch.Tensor, grid: torch.Te
     CPU give the same minimum-norm solution while ``B / R`` times fewer bytes cross the bus.
     """
     A = compute_basis(x_samples, grid, k).permute(1, 0, 2).contiguous()                   # [I, B, R]
+    n_feat, n_samp, n_coef = A.shape
+    n_out = y_samples.shape[0]
+    if n_samp < n_coef:
+        # Fewer samples than coefficients: a wide system with many exact zeros.  LAPACK's default
+        # driver (pivoted QR, the one the reference calls) misjudges the rank of such matrices and
+        # returns vectors that do not even satisfy the equations (checked: residual of order one on a
+        # block-structured 4 x 8 system that the SVD driver solves to 1e-15), so the SVD-based
+        # minimum-norm driver is used here, on the CPU, for CPU and CUDA samples alike.
+        Y = y_samples.permute(2, 1, 0).contiguous().to(torch.float64)
+        sol = torch.linalg.lstsq(A.to(torch.float64).cpu(), Y.cpu(), driver="gelsd").solution
+        return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype, device=x_samples.device)
     if not A.is_cuda:
         Y = y_samples.permute(2, 1, 0).contiguous().to(torch.float64)                      # [I, B, O]
         sol = torch.linalg.lstsq(A.to(torch.float64), Y).solution                          # [I, R, O]
         return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype)
-    n_feat, n_samp, n_coef = A.shape
-    n_out = y_samples.shape[0]
-    if n_samp < n_coef:
-        # fewer samples than coefficients: nothing to reduce, and the rank decisions of the
-        # minimum-norm solver should be taken on the very matrix the CPU path hands it
-        Y = y_samples.permute(2, 1, 0).contiguous().to(torch.float64)
-        sol = torch.linalg.lstsq(A.to(torch.float64).cpu(), Y.cpu()).solution
-        return sol.permute(2, 0, 1).contiguous().to(dtype=x_samples.dtype, device=x_samples.device)
     Q, Rm = torch.linalg.qr(A.to(torch.float64))                                           # [I, B, R], [I, R, R]
     Z = torch.empty((n_feat, n_coef, n_out), dtype=torch.float64, device=A.device)
     # Q^T Y in slabs of features, so that the float64 copy of Y stays below ~512 MB
