@@ -632,6 +632,19 @@ def run_micro(args):
         print(json.dumps({"kernel": f"fma_loop<{name}>", "ms": ms, "tflops": fma_peak[name],
                           "note": "measured FMA-pipe peak (register-only loop)"}), flush=True)
 
+    # FP64 matrix-instruction peak (mma.sync f64; 8 independent accumulator tiles per warp)
+    st_lib.kanb200_selftest_dmma_loop.restype = ctypes.c_int
+    st_lib.kanb200_selftest_dmma_loop.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    for shape, name, per in ((0, "m8n8k4", 256), (1, "m16n8k8", 1024)):
+        blocks, iters = 148 * 8, 1 << 13
+        buf = torch.empty(blocks * 256, dtype=torch.float64, device=dev)
+        run = lambda: st_lib.kanb200_selftest_dmma_loop(shape, blocks, iters, ctypes.c_void_p(buf.data_ptr()),
+                                                         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        ms = timeit(run, reps=5)
+        fma_peak["dmma_" + name] = 2.0 * blocks * 8 * iters * 8 * per / ms / 1e9
+        print(json.dumps({"kernel": f"dmma_loop<{name}>", "ms": ms, "tflops": fma_peak["dmma_" + name],
+                          "note": "measured FP64 matrix-instruction peak (register-only loop)"}), flush=True)
+
     # standalone basis / basis gradient: N x I x (R+1) elements, fp32, c1 feature count
     N, I, G, k = args.micro_rows, 1024, 5, 3
     R = G + k
@@ -739,7 +752,7 @@ def run_config(args):
         x = (torch.rand(131072, 2, generator=g, dtype=torch.float64) * 2 - 1).to(dev)
         ref = torch.sin(math.pi * x[:, 0]) * torch.sin(math.pi * x[:, 1])
         loss_fn = lambda: (net(x).squeeze(-1) - ref).square().mean()
-        name, rows = "c4 KAN[2,64,64,1] G=8 N=131072 fp64 PINN loss (SIMT kernels)", 131072
+        name, rows = "c4 KAN[2,64,64,1] G=8 N=131072 fp64 PINN loss (FP64 matrix-instruction kernels)", 131072
     else:
         raise SystemExit("--config must be 0, 2, 3 or 4 (1 is the default benchmark)")
 

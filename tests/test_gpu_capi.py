@@ -238,6 +238,45 @@ def test_layer_simt_vs_oracle(shape, dtype, tol):
 
 
 @pytest.mark.parametrize("shape", [
+    dict(N=512, I=2, O=64, G=8, k=3),                         # the three layers of the PINN-style network
+    dict(N=1000, I=64, O=64, G=8, k=3),
+    dict(N=700, I=64, O=1, G=8, k=3),
+    dict(N=1111, I=70, O=130, G=20, k=2, nonuniform=True),    # ragged in rows, features, outputs
+    dict(N=513, I=9, O=8, G=5, k=3, scaler=False),            # R + 1 odd, the 8-output tile
+    dict(N=640, I=33, O=9, G=5, k=1, base=False, nonuniform=True),
+    dict(N=900, I=5, O=200, G=60, k=3, nonuniform=True),      # one feature per chunk
+    dict(N=2048, I=130, O=70, G=11, k=3),                     # 12 columns of padding in the last chunk
+])
+def test_layer_float64_matrix_kernels_vs_oracle(shape):
+    """float64 from 512 rows on runs on the FP64 matrix instruction (dense formulation)."""
+    case = make_layer_case(dtype=np.float64, seed=23, **shape)
+    errs = _compare_layer(case, nat.MODE_SIMT, TOL64)
+    print("dense64", shape, errs)
+    _compare_layer(case, nat.MODE_AUTO, TOL64, need_x=False)
+
+
+def test_fp64_matrix_instruction_fragments():
+    """The fragment layout kan_dmma.cuh documents for mma.sync m8n8k4 f64, stated in numpy."""
+    import ctypes
+    from torchsplinekan_b200.build import SELFTEST_PATH
+    lib = ctypes.CDLL(SELFTEST_PATH)
+    fn = lib.kanb200_selftest_dmma_fragments
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 4
+    rng = np.random.default_rng(0)
+    A, B = rng.standard_normal((8, 4)), rng.standard_normal((4, 8))
+    lanes = np.arange(32)
+    g, t = lanes // 4, lanes % 4
+    a, b = dev(A[g, t].copy()), dev(B[t, g].copy())
+    c = torch.zeros(32, 4, dtype=torch.float64, device="cuda")
+    assert fn(0, a.data_ptr(), b.data_ptr(), c.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    C = A @ B
+    got = c.cpu().numpy()
+    assert np.abs(got[:, 0] - C[g, 2 * t]).max() < 1e-14 and np.abs(got[:, 1] - C[g, 2 * t + 1]).max() < 1e-14
+
+
+@pytest.mark.parametrize("shape", [
     dict(N=128, I=8, O=256, G=5, k=3),
     dict(N=300, I=40, O=70, G=5, k=3, nonuniform=True),
     dict(N=1024, I=64, O=256, G=5, k=3),
@@ -245,6 +284,9 @@ def test_layer_simt_vs_oracle(shape, dtype, tol):
     dict(N=640, I=72, O=128, G=4, k=2, nonuniform=True),
     dict(N=513, I=33, O=65, G=3, k=1, base=False),
     dict(N=2048, I=256, O=512, G=5, k=3, nonuniform=True),
+    dict(N=2048, I=256, O=10, G=5, k=3),                      # narrow layers: a handful of outputs
+    dict(N=1500, I=64, O=1, G=5, k=3, nonuniform=True),
+    dict(N=777, I=40, O=4, G=8, k=2, scaler=False),
 ])
 def test_layer_tensor_core_bf16x3_vs_oracle(shape):
     case = make_layer_case(dtype=np.float32, seed=5, **shape)
@@ -284,6 +326,10 @@ def test_auto_mode_resolution():
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 16, 32, 5, 3) == nat.MODE_SIMT      # too little work
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 128, 16, 32, 5, 3) == nat.MODE_SIMT
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 32, 8, 5, 3) == nat.MODE_SIMT
+    # narrow layers over long batches: the cost follows N I (outputs are padded to one tile)
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 8192, 256, 10, 5, 3) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 8192, 64, 4, 5, 3) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 8192, 4, 64, 5, 3) == nat.MODE_SIMT       # I < 8
 
 
 def test_backward_skips_unrequested_outputs():

@@ -59,7 +59,10 @@ def test_mode_resolution_and_workspace_sizes():
     assert fw == 256 + 1024 * 1024 + 4 * 144 * 2 * 32768
     bw = _native.workspace_bytes(_native.OP_BACKWARD, _native.MODE_AUTO, f32, 65536, 1024, 1024, 5, 3, False, True)
     assert bw > 65536 * 1024 * 4          # bf16 hi/lo image of dY plus the partial slab
-    assert _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_SIMT, f64, 1024, 16, 8, 5, 3) == 0
+    # float64 from 512 rows on: the weight image of the matrix-instruction kernels, 8 * 16 * 9 doubles
+    assert _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_SIMT, f64, 1024, 16, 8, 5, 3) == 256 + 9216
+    assert _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_SIMT, f64, 511, 16, 8, 5, 3) == 0
+    assert _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_SIMT, f32, 1024, 16, 8, 5, 3) == 0
     assert _native.workspace_bytes(_native.OP_EDGE_BWD, _native.MODE_SIMT, f64, 1024, 16, 8, 7, 1) > 0
 
 

@@ -17,13 +17,13 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libkan_b200.so")
-SOURCES = ["kan_capi.cu", "kan_simt.cu", "kan_reg.cu", "kan_tc.cu", "kan_tc_edge.cu", "kan_refit.cu", "kan_collective.cu"]
+SOURCES = ["kan_capi.cu", "kan_simt.cu", "kan_reg.cu", "kan_dense64.cu", "kan_tc.cu", "kan_tc_edge.cu", "kan_refit.cu", "kan_collective.cu"]
 # test-only library (operand-layout self-test); never loaded by the package
 SELFTEST_SOURCE = "kan_selftest.cu"
 SELFTEST_PATH = os.path.join(LIB_DIR, "libkan_b200_selftest.so")
 # PyTorch operator layer (TORCH_LIBRARY + pybind + autograd node), host C++ only
 EXT_SOURCE = "kan_torch_ext.cpp"
-HEADERS = ["kan_device.cuh", "kan_internal.h", "kan_table.cuh", "kan_tc_ptx.cuh", "kan_tc_common.cuh", os.path.join("..", "..", "include", "kan_b200.h")]
+HEADERS = ["kan_device.cuh", "kan_dmma.cuh", "kan_internal.h", "kan_table.cuh", "kan_tc_ptx.cuh", "kan_tc_common.cuh", os.path.join("..", "..", "include", "kan_b200.h")]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
@@ -55,7 +55,7 @@ def ext_path() -> str:
 def build_selftest(force: bool = False) -> str:
     """The operand-layout self-test kernel as a library of its own (loaded by the tests only)."""
     src = os.path.join(CSRC, SELFTEST_SOURCE)
-    if not force and not _older_than(SELFTEST_PATH, [src, os.path.join(CSRC, "kan_tc_ptx.cuh")]):
+    if not force and not _older_than(SELFTEST_PATH, [src, os.path.join(CSRC, "kan_tc_ptx.cuh"), os.path.join(CSRC, "kan_dmma.cuh")]):
         return SELFTEST_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
     cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-shared", src, "-o", SELFTEST_PATH + ".tmp"]

@@ -97,9 +97,14 @@ KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, 
     const bool tc_ok = dtype == KANB200_F32 && tc_supported(s);
     if (mode == KANB200_MODE_AUTO) {
         // The tensor-core kernels handle ragged tiles, but a call costs three to six launches (table,
-        // operand images, contraction, finalize) against one to three for the gather kernels: they
-        // pay from about 2^24 edge-samples (N I O) on.
-        if (tc_ok && N >= 256 && O >= 16 && I >= 8 && N * I * O >= ((int64_t)1 << 24)) return KANB200_MODE_TC_BF16X3;
+        // operand images, contraction, finalize) against one to three for the gather kernels, about
+        // 35 us in all: they pay from about 2^24 edge-samples (N I O) on, and for narrow layers (whose
+        // outputs are padded to a 256-wide tile, so the cost follows N I) from 2^19 input values on
+        // (measured, 8192 rows: 256 -> 10 forward 0.085 against 0.305 ms, 64 -> 4 0.038 against 0.078 ms;
+        // 1024 rows, 32 -> 8: 0.034 against 0.033 ms).
+        if (tc_ok && N >= 256 && I >= 8 &&
+            (N * I * O >= ((int64_t)1 << 24) || N * I >= ((int64_t)1 << 19)))
+            return KANB200_MODE_TC_BF16X3;
         return KANB200_MODE_SIMT;
     }
     if (mode == KANB200_MODE_SIMT) return mode;
@@ -134,6 +139,9 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
     const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
     if (m < 0) return 0;
     if (m == KANB200_MODE_SIMT) {
+        if (dtype == KANB200_F64 && dense64_supported(s)) {
+            return dense64_workspace(op == KANB200_OP_FORWARD, s, need_x != 0, need_param != 0);
+        }
         if (op == KANB200_OP_FORWARD) return 0;
         const size_t b = dtype == KANB200_F32 ? simt_backward_workspace<float>(s, need_param != 0)
                                               : simt_backward_workspace<double>(s, need_param != 0);
@@ -223,7 +231,11 @@ KANB200_API int kanb200_forward(int dtype, int mode, const void* x, const void* 
     make_shape(N, I, O, G, k, s);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (m == KANB200_MODE_SIMT) {
+    if (m == KANB200_MODE_SIMT && dtype == KANB200_F64 && dense64_supported(s)) {
+        e = dense64_forward((const double*)x, (const double*)grid, (const double*)base_weight,
+                            (const double*)spline_weight, (const double*)spline_scaler, (double*)y, s,
+                            workspace, workspace_bytes, st);
+    } else if (m == KANB200_MODE_SIMT) {
         e = dtype == KANB200_F32
                 ? simt_forward<float>((const float*)x, (const float*)grid, (const float*)base_weight,
                                       (const float*)spline_weight, (const float*)spline_scaler, (float*)y, s, st)
@@ -255,7 +267,12 @@ KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out, cons
     make_shape(N, I, O, G, k, s);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (m == KANB200_MODE_SIMT) {
+    if (m == KANB200_MODE_SIMT && dtype == KANB200_F64 && dense64_supported(s)) {
+        e = dense64_backward((const double*)grad_out, (const double*)x, (const double*)grid,
+                             (const double*)base_weight, (const double*)spline_weight, (const double*)spline_scaler,
+                             (double*)grad_x, (double*)grad_base_weight, (double*)grad_spline_weight,
+                             (double*)grad_spline_scaler, s, workspace, workspace_bytes, st);
+    } else if (m == KANB200_MODE_SIMT) {
         e = dtype == KANB200_F32
                 ? simt_backward<float>((const float*)grad_out, (const float*)x, (const float*)grid,
                                        (const float*)base_weight, (const float*)spline_weight,

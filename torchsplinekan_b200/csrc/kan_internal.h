@@ -39,6 +39,18 @@ cudaError_t finalize_param_grads(const T* partial, int splits, int64_t split_str
                                  const T* sw, const T* scaler, T* gsw, T* gscaler, T* gbw,
                                  int O, int I, int R, cudaStream_t st);
 
+// ---- float64 layers on the FP64 matrix instruction (kan_dense64.cu) ----------
+// From 512 rows on; workspace = status header, the weight image (forward, input gradient) and the
+// per-split slabs of the parameter gradients, in that order.
+bool dense64_supported(const LayerShape& s);
+size_t dense64_workspace(bool forward, const LayerShape& s, bool need_x, bool need_param);
+cudaError_t dense64_forward(const double* x, const double* grid, const double* bw, const double* sw,
+                            const double* scaler, double* y, const LayerShape& s, void* ws, size_t ws_bytes,
+                            cudaStream_t st);
+cudaError_t dense64_backward(const double* dY, const double* x, const double* grid, const double* bw,
+                             const double* sw, const double* scaler, double* gx, double* gbw, double* gsw,
+                             double* gscaler, const LayerShape& s, void* ws, size_t ws_bytes, cudaStream_t st);
+
 // Table-driven dense basis / basis gradient (float, R == 8, at most 12 knots, N >= 256, N I >= 2^21): `tab` is
 // the polynomial table built by tc_build_table, `fs` its floats per feature.
 bool basis_table_supported(const LayerShape& s);

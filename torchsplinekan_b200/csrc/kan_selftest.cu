@@ -8,6 +8,7 @@
 // 128-byte-swizzle layouts and checks the product against numpy, so a wrong descriptor shows up
 // as a failed small test instead of a wrong large result.  Descriptors are never taken from the
 // caller.
+#include "kan_dmma.cuh"
 #include "kan_tc_ptx.cuh"
 
 #include <cuda_runtime.h>
@@ -105,8 +106,75 @@ __global__ void __launch_bounds__(256) fma_loop_kernel(T* __restrict__ out, int 
     for (int j = 0; j < 16; ++j) s += v[j];
     out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
 }
+
+// The same for the FP64 tensor-core instruction (mma.sync, the only FP64 matrix instruction the
+// part has): every warp runs `iters` rounds of 8 independent accumulator tiles.
+template <int SHAPE>
+__global__ void __launch_bounds__(256) dmma_loop_kernel(double* __restrict__ out, int iters) {
+    double c[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) c[j][q] = 0.0;
+    double a[4], b[2];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) a[q] = 1e-3 * (threadIdx.x + q);
+    b[0] = 0.5, b[1] = 0.25;
+#pragma unroll 1
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (SHAPE == 0) dmma::m8n8k4(c[j][0], c[j][1], a[0], b[0]);
+            else dmma::m16n8k8(c[j], a, b);
+        }
+    }
+    double s = 0.0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) s += c[j][q];
+    out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+
+// One warp, one instruction: the caller provides every lane's operand registers and reads every
+// lane's accumulator registers, so a test can state the fragment layout it relies on in numpy.
+__global__ void dmma_fragment_kernel(int shape, const double* __restrict__ a, const double* __restrict__ b,
+                                     double* __restrict__ c) {
+    const int lane = threadIdx.x;
+    double cr[4] = {0.0, 0.0, 0.0, 0.0};
+    if (shape == 0) {
+        dmma::m8n8k4(cr[0], cr[1], a[lane], b[lane]);
+    } else {
+        double ar[4], br[2];
+        for (int q = 0; q < 4; ++q) ar[q] = a[lane * 4 + q];
+        for (int q = 0; q < 2; ++q) br[q] = b[lane * 2 + q];
+        dmma::m16n8k8(cr, ar, br);
+    }
+    for (int q = 0; q < 4; ++q) c[lane * 4 + q] = cr[q];
+}
 }  // namespace
 }  // namespace kanb200
+
+// FP64 matrix-instruction loop: shape 0 = m8n8k4 (256 FMAs per warp instruction), 1 = m16n8k8
+// (1024).  Executed FMAs: blocks * 8 warps * iters * 8 * that.  `out` holds blocks * 256 doubles.
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_dmma_loop(int shape, int blocks, int iters, void* out, void* stream) {
+    using namespace kanb200;
+    if (blocks < 1 || blocks > 65535 || iters < 1 || !out || shape < 0 || shape > 1) return -1;
+    if (shape == 0) dmma_loop_kernel<0><<<blocks, 256, 0, (cudaStream_t)stream>>>((double*)out, iters);
+    else dmma_loop_kernel<1><<<blocks, 256, 0, (cudaStream_t)stream>>>((double*)out, iters);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// One warp-wide FP64 matrix instruction on caller-provided fragments: a holds 32 x (1 | 4) doubles,
+// b 32 x (1 | 2), c receives 32 x 4 (shape 0 fills the first two of each lane).
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_dmma_fragments(int shape, const double* a, const double* b, double* c, void* stream) {
+    using namespace kanb200;
+    if (shape < 0 || shape > 1 || !a || !b || !c) return -1;
+    dmma_fragment_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(shape, a, b, c);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 // Launches blocks x 256 threads of the FMA loop (dtype 0 = float, 1 = double); the caller times it
 // with events.  FMAs executed: blocks * 256 * iters * 16.  `out` holds blocks * 256 elements.

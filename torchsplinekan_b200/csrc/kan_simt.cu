@@ -582,6 +582,40 @@ __global__ void finalize_param_kernel(const T* __restrict__ partial, int splits,
     }
 }
 
+// The same sums with one warp per (o, i): the lanes stride over the slabs and a butterfly adds
+// them up, for plans with many row splits (small layers over long batches).
+template <typename T>
+__global__ void finalize_param_wide_kernel(const T* __restrict__ partial, int splits, int64_t split_stride,
+                                           int64_t ldo, int sI, int64_t boff, int sB,
+                                           const T* __restrict__ sw, const T* __restrict__ scaler,
+                                           T* __restrict__ gsw, T* __restrict__ gscaler, T* __restrict__ gbw,
+                                           int O, int I, int R) {
+    const int lane = threadIdx.x & 31;
+    const int64_t total = (int64_t)O * I;
+    const int64_t warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t oi = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; oi < total; oi += warps) {
+        const int o = (int)(oi / I), i = (int)(oi - (int64_t)o * I);
+        const T* p0 = partial + (size_t)o * ldo;
+        const T sc = scaler ? scaler[oi] : T(1);
+        T gs = T(0);
+        const int last = gbw ? R : R - 1;
+        for (int r = (gsw || gscaler) ? 0 : R; r <= last; ++r) {
+            const T* src = p0 + (r < R ? (size_t)i * sI + r : (size_t)boff + (size_t)i * sB);
+            T d = T(0);
+            for (int s = lane; s < splits; s += 32) d += src[(size_t)s * split_stride];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+            if (r < R) {
+                if (gsw && lane == 0) gsw[(size_t)oi * R + r] = scaler ? sc * d : d;
+                if (gscaler) gs += sw[(size_t)oi * R + r] * d;
+            } else if (lane == 0) {
+                gbw[oi] = d;
+            }
+        }
+        if (gscaler && lane == 0) gscaler[oi] = gs;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Backward, input:  gx[n,i] = sum_j der_j (sum_o dY[n,o] W_eff[o,i,s+j]) + silu'(x) sum_o dY[n,o] bw[o,i]
 // ---------------------------------------------------------------------------
@@ -716,7 +750,7 @@ ParamPlan<T> plan_param(const LayerShape& s) {
     p.to = 32 * p.opt;
     const int64_t bxy = (int64_t)((s.O + p.to - 1) / p.to) * ((s.I + BP_TI - 1) / BP_TI);
     int64_t splits = (4 * 148 + bxy - 1) / bxy;
-    const int64_t max_splits = (s.N + 255) / 256;
+    const int64_t max_splits = (s.N + 63) / 64;
     if (splits > max_splits) splits = max_splits;
     if (splits > 64) splits = 64;
     if (splits < 1) splits = 1;
@@ -928,6 +962,12 @@ cudaError_t finalize_param_grads(const T* partial, int splits, int64_t split_str
                                  int64_t ldo, int sI, int64_t boff, int sB,
                                  const T* sw, const T* scaler, T* gsw, T* gscaler, T* gbw,
                                  int O, int I, int R, cudaStream_t st) {
+    if (splits >= 8) {
+        const int blocks = grid_1d((int64_t)O * I * 32, 256);
+        finalize_param_wide_kernel<T><<<blocks, 256, 0, st>>>(partial, splits, split_stride, ldo, sI, boff, sB,
+                                                             sw, scaler, gsw, gscaler, gbw, O, I, R);
+        return cudaGetLastError();
+    }
     const int blocks = grid_1d((int64_t)O * I, 128);
     finalize_param_kernel<T><<<blocks, 128, 0, st>>>(partial, splits, split_stride, ldo, sI, boff, sB,
                                                     sw, scaler, gsw, gscaler, gbw, O, I, R);
