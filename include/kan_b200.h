@@ -178,8 +178,13 @@ KANB200_API int kanb200_edge_abs_mean_x(int dtype, int mode, const void* x, cons
  *   ds [N,I]   gradient of the caller's base values (only when s is given);
  *   dbw [O,I], dW [O,I,R]  parameter gradients (dW with respect to the effective coefficients).
  * The [N,I,R] tensors H and dH of edge_abs_mean_backward_cuda + kan_basis_grad_cuda
- * (csrc/kan_reg_cuda.cu:284-312, csrc/kan_cuda.cu:682-699) are never formed.  No atomics. */
-KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, const void* grad_a, const void* x, const void* s,
+ * (csrc/kan_reg_cuda.cu:284-312, csrc/kan_cuda.cu:682-699) are never formed.  No atomics.
+ * float32 with G + k <= 8, at most 256 outputs and s == NULL runs on the tensor cores: sign(phi) is
+ * written to shared memory as an exact bf16 operand and both gradients are two more small matrix
+ * products per feature, chained behind the one that forms phi.  Other cases run on the FMA pipes.
+ * mode as for kanb200_forward (the two tensor-core modes select the same kernel here: the sign of
+ * phi is always taken from the three-term product). */
+KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void* grad_a, const void* x, const void* s,
                                                  const void* grid, const void* bw, const void* W,
                                                  void* gx, void* ds, void* dbw, void* dW,
                                                  int64_t N, int64_t I, int64_t O, int G, int k,

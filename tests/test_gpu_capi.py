@@ -540,7 +540,7 @@ def test_edge_abs_mean_from_x_fma_kernels_and_backward(N, I, O, G, k, base, cust
         sig = torch.sigmoid(x)
         gx_ref = gx_ref + ds_ref * (sig * (1 + x * (1 - sig)))
     a = nat.edge_abs_mean_x(x, s_custom, grid, bw, W, k, nat.MODE_SIMT)
-    gx, ds, dbw, dW = nat.edge_abs_mean_x_backward(ga, x, s_custom, grid, bw, W, k)
+    gx, ds, dbw, dW = nat.edge_abs_mean_x_backward(ga, x, s_custom, grid, bw, W, k, mode=nat.MODE_SIMT)
     torch.cuda.synchronize()
     f = lambda t: t.double().cpu().numpy()
     assert rel_err(f(a), f(a_ref)) < tol
@@ -553,6 +553,95 @@ def test_edge_abs_mean_from_x_fma_kernels_and_backward(N, I, O, G, k, base, cust
     else:
         assert ds is None
     assert x.dtype == tdt
+
+
+def _edge_backward_dense64(case, ga, base):
+    """float64 dense evaluation of the edge statistic's gradients: (phi, gx, dbw, dW)."""
+    k = case["k"]
+    x = case["x"].astype(np.float64)
+    g64 = case["grid"].astype(np.float64)
+    W = (case["sw"] * case["sc"][:, :, None]).astype(np.float64)
+    H = ko.compute_basis(x, g64, k)
+    dHdx = ko.compute_basis_derivative(x, g64, k)
+    phi = np.einsum("nir,oir->noi", H, W)
+    sig = 1.0 / (1.0 + np.exp(-x))
+    if base:
+        bw = case["bw"].astype(np.float64)
+        phi = phi + (x * sig)[:, None, :] * bw[None]
+    sg = np.sign(phi) * (ga.astype(np.float64) / x.shape[0])[None]
+    dW = np.einsum("noi,nir->oir", sg, H)
+    gx = np.einsum("noi,oir,nir->ni", sg, W, dHdx)
+    dbw = None
+    if base:
+        dbw = np.einsum("noi,ni->oi", sg, x * sig)
+        gx = gx + np.einsum("noi,oi->ni", sg, bw) * (sig * (1 + x * (1 - sig)))
+    return phi, gx, dbw, dW
+
+
+@pytest.mark.parametrize("N,I,O,G,k,base", [
+    (1024, 16, 256, 5, 3, True), (777, 37, 130, 5, 3, True), (2048, 8, 64, 4, 2, False), (300, 5, 16, 7, 1, True),
+    (4096, 64, 256, 5, 3, True)])
+def test_edge_backward_tensor_cores_fixed_signs(N, I, O, G, k, base):
+    """Gradients of the from-x edge statistic on the tensor cores where the sign of every phi is
+    beyond doubt (coefficients and base weights of one sign per output, inputs in (0, 1) so that
+    SiLU is positive): sign tile, both chained products, scaling and the ragged edges are checked
+    at float32 accuracy against the float64 dense evaluation."""
+    case = make_layer_case(N, I, O, G, k, np.float32, seed=N + O, nonuniform=True, base=base)
+    rng = np.random.default_rng(N)
+    flip = np.where(np.arange(O) % 3 == 0, -1.0, 1.0).astype(np.float32)
+    case["x"] = rng.uniform(0.02, 0.98, size=case["x"].shape).astype(np.float32)
+    case["sw"] = (np.abs(case["sw"]) + 0.05) * flip[:, None, None]
+    case["sc"] = np.abs(case["sc"]) + 0.05
+    if base:
+        case["bw"] = (np.abs(case["bw"]) + 0.05) * flip[:, None]
+    ga = rng.uniform(0.1, 1.0, size=(O, I)).astype(np.float32)
+    phi, gx_ref, dbw_ref, dW_ref = _edge_backward_dense64(case, ga, base)
+    assert np.abs(phi).min() > 1e-4
+    x, grid = dev(case["x"]), dev(case["grid"])
+    W = dev(case["sw"] * case["sc"][:, :, None])
+    bw = dev(case["bw"]) if base else None
+    gx, ds, dbw, dW = nat.edge_abs_mean_x_backward(dev(ga), x, None, grid, bw, W, k, mode=nat.MODE_TC_BF16X3)
+    torch.cuda.synchronize()
+    for key, buf in list(nat._ws_cache.items()):
+        if key[2] == "edge_x":
+            nat.check_status(buf)
+    f = lambda t: t.double().cpu().numpy()
+    errs = {"dW": rel_err(f(dW), dW_ref), "gx": rel_err(f(gx), gx_ref)}
+    if base:
+        errs["dbw"] = rel_err(f(dbw), dbw_ref)
+    print("edge backward (tensor cores)", (N, I, O), errs)
+    assert all(e < 2e-5 for e in errs.values()), errs
+    # parameter gradients alone (no input gradient: the third product is skipped)
+    _, _, dbw2, dW2 = nat.edge_abs_mean_x_backward(dev(ga), x, None, grid, bw, W, k, need_x=False,
+                                                   mode=nat.MODE_TC_BF16X3)
+    assert torch.equal(dW2, dW) and (not base or torch.equal(dbw2, dbw))
+
+
+@pytest.mark.parametrize("N,I,O", [(2048, 32, 256), (1500, 20, 70)])
+def test_edge_backward_tensor_cores_random_signs(N, I, O):
+    """Random coefficients: phi changes sign from sample to sample.  Where |phi| is at rounding level
+    two evaluations may disagree on the sign, and each such sample moves an entry by 2 ga / N times a
+    basis value, so the comparison is in the relative L2 norm and in the share of entries that agree.
+    The tensor-core kernel takes the sign from the split-bf16 product (phi to about 5e-6 of its
+    terms), the FMA kernels from float32 arithmetic: a few more samples near phi = 0 fall on the other
+    side (measured: relative L2 7e-5 / 3e-5 / 2e-4 for dW / dbw / gx, 99.9 % of entries within 2e-5)."""
+    G, k = 5, 3
+    case = make_layer_case(N, I, O, G, k, np.float32, seed=3 * N + O, nonuniform=True, base=True)
+    rng = np.random.default_rng(O)
+    ga = rng.uniform(0.1, 1.0, size=(O, I)).astype(np.float32)
+    _, gx_ref, dbw_ref, dW_ref = _edge_backward_dense64(case, ga, True)
+    x, grid = dev(case["x"]), dev(case["grid"])
+    W, bw = dev(case["sw"] * case["sc"][:, :, None]), dev(case["bw"])
+    gx, ds, dbw, dW = nat.edge_abs_mean_x_backward(dev(ga), x, None, grid, bw, W, k, mode=nat.MODE_TC_BF16X3)
+    gx_f, _, dbw_f, dW_f = nat.edge_abs_mean_x_backward(dev(ga), x, None, grid, bw, W, k, mode=nat.MODE_SIMT)
+    torch.cuda.synchronize()
+    f = lambda t: t.double().cpu().numpy()
+    for name, got, fma, want in (("dW", dW, dW_f, dW_ref), ("dbw", dbw, dbw_f, dbw_ref), ("gx", gx, gx_f, gx_ref)):
+        l2 = np.linalg.norm(f(got) - want) / np.linalg.norm(want)
+        l2_fma = np.linalg.norm(f(fma) - want) / np.linalg.norm(want)
+        close = np.mean(np.abs(f(got) - want) <= 2e-5 * np.abs(want).max())
+        print(f"edge backward random signs {name}: rel L2 {l2:.2e} (FMA kernels {l2_fma:.2e}), entries within 2e-5: {close:.4f}")
+        assert l2 < max(5e-4, 3 * l2_fma) and close > 0.995
 
 
 @pytest.mark.parametrize("shape", [

@@ -179,11 +179,13 @@ def test_config2_full_size_training_step():
     penalty's gradient contains sign(phi): where |phi| is at rounding level, two evaluations
     disagree on the sign and that edge's gradient entries move by 2 ga / N = 2.4e-4 of their largest
     possible size, whatever the arithmetic -- float32 against float64 dense PyTorch shows it too.
-    Both are valid subgradients of |phi| at neighbouring points.  The native gradients must
-    therefore be as close to float64 in the max-norm as the dense FLOAT32 evaluation of the same
-    expression is (factor 3 of slack) or within a few flips' worth (5 / N; flips are discrete events),
-    and within 1e-3 in the relative L2 norm, which single flipped entries hardly move but a wrong
-    kernel would."""
+    Both are valid subgradients of |phi| at neighbouring points.  The native backward takes the
+    signs from the split-bf16 tensor-core product (phi to about 5e-6 of its terms), so a few more
+    samples fall on the other side than in float32 arithmetic.  The native gradients must therefore
+    be as close to float64 in the max-norm as the dense FLOAT32 evaluation of the same expression
+    is (factor 3 of slack) or within a few flips' worth (10 / N; flips are discrete events), and
+    within 1e-3 in the relative L2 norm (measured: 7e-5), which single flipped entries hardly move
+    but a wrong kernel would."""
     torch.manual_seed(0)
     net = sk.KAN([784, 256, 256, 10], backend="cuda").cuda()
     g = torch.Generator().manual_seed(0)
@@ -215,7 +217,7 @@ def test_config2_full_size_training_step():
     print("config 2 native32 vs dense64, relative L2:", l2)
     assert errs["y"] < 5e-5 and errs["reg"] < 5e-5, errs
     for n in names:
-        assert errs[n] < max(5e-5, 3.0 * gap32[n], 5.0 / x.shape[0]), (n, errs[n], gap32[n])
+        assert errs[n] < max(5e-5, 3.0 * gap32[n], 10.0 / x.shape[0]), (n, errs[n], gap32[n])
         assert l2[n] < 1e-3, (n, l2[n])
     _C.check_status()
 

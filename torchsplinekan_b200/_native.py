@@ -52,7 +52,7 @@ SIGNATURES = {
                                                                    _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_x": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                              _c_void_p, _c_size, _c_void_p]),
-    "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
+    "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                                _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
     "kanb200_edge_abs_mean_backward": (_c_int, [_c_int] + [_c_void_p] * 9 + [_c_i64, _c_i64, _c_i64, _c_int,
@@ -341,7 +341,8 @@ def edge_abs_mean_x(x, s, grid, bw, W, k: int, mode: int = MODE_AUTO) -> torch.T
     return a
 
 
-def edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k: int, need_x=True, need_s=True, need_bw=True, need_W=True):
+def edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k: int, need_x=True, need_s=True, need_bw=True, need_W=True,
+                             mode: int = MODE_AUTO):
     """``(gx, ds, dbw, dW)`` of :func:`edge_abs_mean_x` (None where not needed / not applicable)."""
     dev = _need_cuda(x, grid, W, ga)
     N, I = x.shape
@@ -353,8 +354,8 @@ def edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k: int, need_x=True, need_s=
     dbw = torch.empty((O, I), dtype=x.dtype, device=dev) if (need_bw and has_base) else None
     dW = torch.empty_like(W) if need_W else None
     with _OnDevice(dev):
-        ws = workspace(dev, workspace_bytes(OP_EDGE_X_BWD, MODE_AUTO, x.dtype, N, I, O, G, k), "edge_x")
-        _check(lib().kanb200_edge_abs_mean_x_backward(_code(x.dtype), _p(ga), _p(x), _p(s), _p(grid), _p(bw), _p(W),
+        ws = workspace(dev, workspace_bytes(OP_EDGE_X_BWD, mode, x.dtype, N, I, O, G, k), "edge_x")
+        _check(lib().kanb200_edge_abs_mean_x_backward(_code(x.dtype), mode, _p(ga), _p(x), _p(s), _p(grid), _p(bw), _p(W),
                                                       _p(gx), _p(ds), _p(dbw), _p(dW), N, I, O, G, k,
                                                       _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return gx, ds, dbw, dW

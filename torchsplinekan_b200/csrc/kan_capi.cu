@@ -51,6 +51,13 @@ bool edge_x_uses_tc(int mode, int dtype, const LayerShape& s) {
     return true;
 }
 
+// The same for its backward (needs the SiLU / no-base form: no caller-provided base values).
+bool edge_x_bwd_uses_tc(int mode, int dtype, const LayerShape& s, bool custom_base) {
+    if (dtype != KANB200_F32 || mode == KANB200_MODE_SIMT || custom_base || !tc_edge_bwd_supported(s)) return false;
+    if (mode == KANB200_MODE_AUTO) return s.N >= 256 && s.O >= 16;
+    return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -127,6 +134,11 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
         if (N < 1) return 0;
         const bool b = op == KANB200_OP_EDGE_X_BWD;
         if (!b && edge_x_uses_tc(mode, dtype, s)) return tc_edge_workspace(s);
+        size_t tc_bytes = 0;
+        if (b && edge_x_bwd_uses_tc(mode, dtype, s, false)) tc_bytes = tc_edge_bwd_workspace(s, true);
+        const size_t fma_bytes = kWsHeader + (dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
+                                                                     : edge_workspace<double>(N, s.I, s.O, s.R(), b));
+        if (b) return tc_bytes > fma_bytes ? tc_bytes : fma_bytes;      // a call with base values takes the FMA path
         return kWsHeader + (dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
                                                  : edge_workspace<double>(N, s.I, s.O, s.R(), b));
     }
@@ -393,7 +405,8 @@ KANB200_API int kanb200_edge_abs_mean_x(int dtype, int mode, const void* x, cons
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x");
 }
 
-KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, const void* grad_a, const void* x, const void* s_val,
+KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void* grad_a, const void* x,
+                                                 const void* s_val,
                                                  const void* grid, const void* bw, const void* W,
                                                  void* gx, void* ds, void* dbw, void* dW,
                                                  int64_t N, int64_t I, int64_t O, int G, int k,
@@ -404,7 +417,19 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, const void* grad_a, 
     if (!grad_a || !x || !grid || !W) return fail(KANB200_EINVAL, "edge_abs_mean_x_backward: NULL pointer");
     if (s_val && !bw) return fail(KANB200_EINVAL, "edge_abs_mean_x_backward: base values given without base_weight");
     if (ds && !s_val) return fail(KANB200_EINVAL, "edge_abs_mean_x_backward: ds requested without base values s");
+    if (mode < KANB200_MODE_AUTO || mode > KANB200_MODE_TC_BF16X1) return fail(KANB200_EINVAL, "unknown mode %d", mode);
     cudaStream_t st = (cudaStream_t)stream;
+    LayerShape shape;
+    make_shape(N, I, O, G, k, shape);
+    if (edge_x_bwd_uses_tc(mode, dtype, shape, s_val != nullptr)) {
+        cudaError_t e = tc_edge_backward((const float*)grad_a, (const float*)x, (const float*)grid, (const float*)bw,
+                                         (const float*)W, (float*)gx, (float*)dbw, (float*)dW, shape, workspace,
+                                         workspace_bytes, st);
+        return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x_backward");
+    }
+    if (mode == KANB200_MODE_TC_BF16X3 || mode == KANB200_MODE_TC_BF16X1)
+        return fail(KANB200_EUNSUPPORTED, "edge_abs_mean_x_backward: tensor-core modes need float32, G + k <= 8, "
+                                          "at most 256 outputs and no caller-provided base values");
     cudaError_t e =
         dtype == KANB200_F32
             ? edge_abs_mean_x_bwd<float>((const float*)grad_a, (const float*)x, (const float*)s_val, (const float*)grid,

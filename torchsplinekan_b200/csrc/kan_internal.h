@@ -113,6 +113,14 @@ cudaError_t tc_edge_forward(int split_terms, const float* x, const float* s_val,
                             const float* W, float* a, const LayerShape& s, void* ws, size_t ws_bytes,
                             cudaStream_t st);
 
+// Backward of the same statistic on the tensor cores: float32, G + k <= 8, at most 256 outputs,
+// SiLU or no base branch.  gx, dbw, dW may be NULL.
+bool tc_edge_bwd_supported(const LayerShape& s);
+size_t tc_edge_bwd_workspace(const LayerShape& s, bool need_x);
+cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid, const float* bw, const float* W,
+                             float* gx, float* dbw, float* dW, const LayerShape& s, void* ws, size_t ws_bytes,
+                             cudaStream_t st);
+
 // Coefficient refit after a knot update (kan_refit.cu): per-feature moment matrices
 // G = sum b_new b_new^T, M = sum b_new b_old^T (float64 [I, R, R]) and the in-place solve X = G^-1 M.
 template <typename T>

@@ -89,6 +89,81 @@ umma_layout_kernel(const uint8_t* __restrict__ a_img, const uint8_t* __restrict_
         tmem_dealloc(tmem_base, 512);
     }
 }
+// The same with every layout parameter named by the caller (strides in bytes, all fed through the
+// production descriptor builder): operands of up to 32 KB each, `ksteps` K = 16 steps, N columns.
+// Used to pin down the readings of ONE shared tile by two different products, e.g. a K-major
+// [rows][64] tile read as an MN-major operand whose 16 columns start 32 q bytes into every row.
+struct GeneralLayout {
+    uint32_t a_bytes, b_bytes;
+    uint32_t a_mn, b_mn;             // 1 = MN-major
+    uint32_t a_lbo, a_sbo, a_step, a_off;
+    uint32_t b_lbo, b_sbo, b_step, b_off;
+    uint32_t n, ksteps;
+};
+
+__global__ void __launch_bounds__(128, 1)
+umma_general_kernel(const uint8_t* __restrict__ a_img, const uint8_t* __restrict__ b_img, GeneralLayout L,
+                    float* __restrict__ D, int* __restrict__ status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t done_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if ((sbase & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(status, 2);
+        return;
+    }
+    const uint32_t a_base = 0, b_base = 32768;
+    for (uint32_t e = threadIdx.x * 16; e < L.a_bytes; e += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(smem + a_base + e) = *reinterpret_cast<const uint4*>(a_img + e);
+    for (uint32_t e = threadIdx.x * 16; e < L.b_bytes; e += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(smem + b_base + e) = *reinterpret_cast<const uint4*>(b_img + e);
+    fence_proxy_async_smem();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done_bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) {
+        const uint64_t a_desc = make_sdesc_sw128(L.a_lbo, L.a_sbo), b_desc = make_sdesc_sw128(L.b_lbo, L.b_sbo);
+        const uint32_t idesc = make_idesc_bf16((int)L.n, L.a_mn != 0, L.b_mn != 0);
+        for (uint32_t ks = 0; ks < L.ksteps; ++ks)
+            mma_f16_ss(tmem_base, sdesc_at(a_desc, sbase + a_base + L.a_off + ks * L.a_step),
+                       sdesc_at(b_desc, sbase + b_base + L.b_off + ks * L.b_step), idesc, ks > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&done_bar));
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(smem_u32(&done_bar), 0, &abort_flag);
+    tc_fence_after_sync();
+    if (ok) {
+        const int row = warp * 32 + lane;
+        for (uint32_t c = 0; c < (L.n + 31) / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + c * 32, r);
+            tmem_ld_wait();
+            for (uint32_t q = 0; q < 32 && c * 32 + q < L.n; ++q) D[(size_t)row * L.n + c * 32 + q] = __uint_as_float(r[q]);
+        }
+    } else {
+        if (lane == 0) atomicExch(status, 1);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // Register-only FMA loop for measuring the FP32 / FP64 FMA-pipe peaks the gather kernels are
 // compared with: every thread runs `iters` rounds of 16 independent dependent-chain FMAs.
 template <typename T>
@@ -200,5 +275,31 @@ int kanb200_selftest_umma_layout(int layout, const void* a_img, const void* b_im
     umma_layout_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(reinterpret_cast<const uint8_t*>(a_img),
                                                                 reinterpret_cast<const uint8_t*>(b_img), layout, D,
                                                                 status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// D[128, n] of `ksteps` K = 16 steps with caller-named layout parameters (16 integers in the order
+// of GeneralLayout); operands at most 32 KB each, n a multiple of 16 up to 256.
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_umma_general(const void* a_img, const void* b_img, const unsigned* params, float* D,
+                                  int* status, void* stream) {
+    using namespace kanb200;
+    if (!a_img || !b_img || !params || !D || !status) return -1;
+    GeneralLayout L;
+    L.a_bytes = params[0]; L.b_bytes = params[1]; L.a_mn = params[2]; L.b_mn = params[3];
+    L.a_lbo = params[4]; L.a_sbo = params[5]; L.a_step = params[6]; L.a_off = params[7];
+    L.b_lbo = params[8]; L.b_sbo = params[9]; L.b_step = params[10]; L.b_off = params[11];
+    L.n = params[12]; L.ksteps = params[13];
+    if (L.a_bytes > 32768 || L.b_bytes > 32768 || (L.a_bytes & 15) || (L.b_bytes & 15) || L.n < 16 || L.n > 256 ||
+        (L.n & 15) || L.ksteps < 1 || L.ksteps > 16)
+        return -1;
+    const uint64_t a_last = (uint64_t)L.a_off + (uint64_t)(L.ksteps - 1) * L.a_step;
+    const uint64_t b_last = (uint64_t)L.b_off + (uint64_t)(L.ksteps - 1) * L.b_step;
+    if (a_last >= 32768 || b_last >= 32768) return -1;
+    const int smem = 65536;
+    cudaError_t e = cudaFuncSetAttribute(umma_general_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return -4;
+    umma_general_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(reinterpret_cast<const uint8_t*>(a_img),
+                                                                 reinterpret_cast<const uint8_t*>(b_img), L, D, status);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -69,6 +69,7 @@ struct EdgePlanTc {
 // tile of 16 KB each, byte-for-byte the 128-byte-swizzled K-major shared-memory operand: row =
 // output, 128 B = 4 features x [8 spline slots | base weight, 7 zeros].
 __global__ void pack_edge_weights_kernel(const float* __restrict__ W, const float* __restrict__ bw,
+                                         const float* __restrict__ edge_scale, float scale,
                                          uint8_t* __restrict__ img, int O, int I, int R, int n_quads, int n_otiles) {
     const int64_t chunks = (int64_t)n_otiles * n_quads * EDGE_OT * 8;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < chunks;
@@ -88,6 +89,11 @@ __global__ void pack_edge_weights_kernel(const float* __restrict__ W, const floa
                     if (e < R) w[e] = W[oi * R + e];
             } else if (bw) {
                 w[0] = bw[oi];
+            }
+            if (edge_scale) {
+                const float sc = edge_scale[oi] * scale;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) w[e] *= sc;
             }
         }
         uint32_t h[4], l[4];
@@ -408,6 +414,507 @@ EdgePlanTc plan_edge_tc(int64_t N, int I, int O) {
     return p;
 }
 
+
+// ===========================================================================================
+// Backward of the edge statistic on the tensor cores.
+//
+// With phi_i[o, n] as above and S_i = sign(phi_i) (exact in bf16: -1, 0, +1),
+//     dW[o,i,r']  = (ga[o,i] / N) sum_n S_i[o,n] A_i[n,r']          r' = 8 spline slots | base value
+//     gx[n,i]     = sum_r' dA_i[n,r'] sum_o S_i[o,n] (ga[o,i] / N) W[o,i,r']
+// are two more small products per feature, chained behind the first through shared memory:
+//     GEMM1  phi [o 128, n 128] = Wop [o,16] Aop[n,16]^T            three terms (hi/lo split of both)
+//     sign   8 warps read phi from tensor memory and write S as a bf16 tile [o][n]
+//     GEMM2  G   [o 128, r' 16] += S[o, n] Aop[n, r']               S K-major, the SAME sample tile read
+//                                                                   MN-major, 16 columns at 32 q bytes
+//     GEMM3  D3  [n 128, r' 16] += S^T[n, o] Wg[o, r']              the S tile read MN-major, Wg = ga W / N
+// G stays in tensor memory over all sample tiles of a work item (at most 8 tiles = 1024 samples per
+// accumulation chain), D3 over the output tiles of one sample tile.  At the end of an item the sign
+// warps scale G into per-split slabs; per sample tile four more warps contract D3 with the basis
+// derivatives of x (from the polynomial table) into gx.  Nothing of size [N, O, I] or [N, I, R] is
+// ever stored.  Up to 256 outputs (both output tiles in one item, so gx needs no second pass).
+// ===========================================================================================
+constexpr int EB_TN = 128;                                        // samples per tile
+constexpr int EB_PRODUCER_WARPS = 8, EB_SIGN_WARPS = 8, EB_GX_WARPS = 4;
+constexpr int EB_PRODUCERS = EB_PRODUCER_WARPS * 32, EB_SIGNERS = EB_SIGN_WARPS * 32, EB_GXERS = EB_GX_WARPS * 32;
+constexpr int EB_MMA_WARP = EB_PRODUCER_WARPS + EB_SIGN_WARPS + EB_GX_WARPS;
+constexpr int EB_THREADS = (EB_MMA_WARP + 2) * 32;
+constexpr int EB_MAX_CHAIN_TILES = 8;
+constexpr uint32_t EB_A_TILE = EB_TN * 128;                       // 16 KB
+constexpr uint32_t EB_A_STAGE = 2 * EB_A_TILE;
+constexpr uint32_t EB_S_BLOCK = EDGE_OT * 128;                    // 16 KB: 128 outputs x 64 samples
+constexpr uint32_t EB_SMEM_A = 0;
+constexpr uint32_t EB_SMEM_S = EB_SMEM_A + 2 * EB_A_STAGE;
+constexpr uint32_t EB_SMEM_W = EB_SMEM_S + 2 * EB_S_BLOCK;
+constexpr uint32_t EB_SMEM_WG = EB_SMEM_W + EDGE_MAX_OTILES * EDGE_W_SLOT;
+constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WG + EDGE_MAX_OTILES * EDGE_W_SLOT;
+constexpr uint32_t EB_SMEM_BYTES = EB_SMEM_CTRL + 256 + TAB_SMEM_FLOATS * 4;
+static_assert(EB_SMEM_BYTES <= 232448, "edge backward kernel shared memory exceeds 227 KB");
+constexpr uint32_t EB_TMEM_G = 256, EB_TMEM_D3 = 384;
+
+struct EdgeBwdCtrl {
+    uint64_t fullA[2], emptyA[2];
+    uint64_t fullW, emptyW;
+    uint64_t phiFull[2], phiEmpty[2];
+    uint64_t sFull, sEmpty;
+    uint64_t gFull, gEmpty;
+    uint64_t d3Full[2], d3Empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(EdgeBwdCtrl) <= 256, "control block too large");
+
+struct EdgeBwdPlan {
+    int n_quads, n_otiles, splits;
+    int64_t tiles_total, tiles_per_split;
+    __host__ __device__ int64_t n_items() const { return (int64_t)n_quads * splits; }
+};
+
+__global__ void __launch_bounds__(EB_THREADS, 1)
+tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
+                   const uint8_t* __restrict__ wgimg, const float* __restrict__ ga, float* __restrict__ slabs,
+                   float* __restrict__ gx, int* __restrict__ status, int64_t N, int I, int O, int has_base,
+                   EdgeBwdPlan plan, TabInfo ti, int vec_x) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t sbase = smem_u32(smem);
+    EdgeBwdCtrl* ctrl = reinterpret_cast<EdgeBwdCtrl*>(smem + EB_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + EB_SMEM_CTRL + 256);
+    volatile int* abort_flag = &ctrl->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool need_gx = gx != nullptr;
+    const bool shared_grid = grid_is_shared(tab, I, ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
+
+    if ((sbase & 1023u) != 0) {
+        if (threadIdx.x == 0) report_status(status, kStatusBadSmem);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&ctrl->fullA[s]), EB_PRODUCERS);
+            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
+            mbar_init(smem_u32(&ctrl->phiFull[s]), 1);
+            mbar_init(smem_u32(&ctrl->phiEmpty[s]), EB_SIGNERS);
+            mbar_init(smem_u32(&ctrl->d3Full[s]), 1);
+            mbar_init(smem_u32(&ctrl->d3Empty[s]), EB_GXERS);
+        }
+        mbar_init(smem_u32(&ctrl->fullW), 1);
+        mbar_init(smem_u32(&ctrl->emptyW), 1);
+        mbar_init(smem_u32(&ctrl->sFull), EB_SIGNERS);
+        mbar_init(smem_u32(&ctrl->sEmpty), 1);
+        mbar_init(smem_u32(&ctrl->gFull), 1);
+        mbar_init(smem_u32(&ctrl->gEmpty), EB_SIGNERS);
+        ctrl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == EB_MMA_WARP) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const int64_t n_items = plan.n_items();
+    const int n_ot = plan.n_otiles;                     // 1 or 2
+
+    // item -> (sample range, feature group); consecutive items share the samples
+    auto decode = [&](int64_t item, int& sp, int& fq) {
+        fq = (int)(item % plan.n_quads);
+        sp = (int)(item / plan.n_quads);
+    };
+    auto tile_range = [&](int sp, int64_t& t0, int64_t& t1) {
+        t0 = (int64_t)sp * plan.tiles_per_split;
+        t1 = t0 + plan.tiles_per_split;
+        if (t1 > plan.tiles_total) t1 = plan.tiles_total;
+    };
+
+    if (warp < EB_PRODUCER_WARPS) {
+        // ===== producers: thread = (sample row, pair of features) =====
+        const int row = threadIdx.x & (EB_TN - 1), pr = threadIdx.x >> 7;      // pr = 0, 1
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            int sp, fq;
+            decode(item, sp, fq);
+            int64_t t0, t1;
+            tile_range(sp, t0, t1);
+            const int f0 = fq * EDGE_FQ + 2 * pr;
+            for (int64_t t = t0; t < t1; ++t, ++it) {
+                const uint32_t stage = it & 1u;
+                const uint32_t a_hi = sbase + EB_SMEM_A + stage * EB_A_STAGE;
+                const uint32_t a_lo = a_hi + EB_A_TILE;
+                const int64_t n = t * EB_TN + row;
+                const bool row_ok = n < N;
+                float xv[2] = {0.f, 0.f};
+                if (row_ok) {
+                    const float* xr = x + (size_t)n * I + f0;
+                    if (vec_x && f0 + 2 <= I) {
+                        const float2 v = __ldg(reinterpret_cast<const float2*>(xr));
+                        xv[0] = v.x; xv[1] = v.y;
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 2; ++q)
+                            if (f0 + q < I) xv[q] = __ldg(xr + q);
+                    }
+                }
+                uint4 hi[2], lo[2];
+                uint32_t bh[2], bl[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int f = f0 + q;
+                    const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
+                    const Window w = shared_grid ? eval_window<true, true, false>(stab, ti, xv[q])
+                                                 : eval_window<true, false, false>(ft, ti, xv[q]);
+                    place_window<true>(w, 0, hi[q], lo[q]);
+                    float sv = has_base ? silu_fast(xv[q]) : 0.f;
+                    if (!(row_ok && f < I)) {
+                        hi[q] = make_uint4(0, 0, 0, 0);
+                        lo[q] = hi[q];
+                        sv = 0.f;
+                    }
+                    split2(sv, 0.0f, bh[q], bl[q]);
+                }
+                if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const uint32_t c0 = (uint32_t)(2 * (2 * pr + q));
+                    const uint32_t off0 = sw128_chunk_offset((uint32_t)row, c0);
+                    const uint32_t off1 = sw128_chunk_offset((uint32_t)row, c0 + 1);
+                    st_shared_v4(a_hi + off0, hi[q]);
+                    st_shared_v4(a_hi + off1, make_uint4(bh[q], 0, 0, 0));
+                    st_shared_v4(a_lo + off0, lo[q]);
+                    st_shared_v4(a_lo + off1, make_uint4(bl[q], 0, 0, 0));
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ctrl->fullA[stage]));
+            }
+        }
+    } else if (warp < EB_PRODUCER_WARPS + EB_SIGN_WARPS) {
+        // ===== sign warps: thread = one output row, one half (64) of the sample columns =====
+        const int e = warp - EB_PRODUCER_WARPS;            // 0 .. 7
+        const int quad = warp & 3;
+        const int half = e >> 2;
+        const int orow = quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const float inv_n = 1.0f / (float)N;
+        uint32_t job = 0, n_item = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
+            int sp, fq;
+            decode(item, sp, fq);
+            int64_t t0, t1;
+            tile_range(sp, t0, t1);
+            const int64_t units = (t1 - t0) * n_ot * EDGE_FQ;
+            for (int64_t u = 0; u < units; ++u, ++job) {
+                const uint32_t buf = job & 1u;
+                if (!mbar_wait(smem_u32(&ctrl->phiFull[buf]), (job >> 1) & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(lane_addr + buf * EB_TN + half * 64, r0);
+                tmem_ld_32x32(lane_addr + buf * EB_TN + half * 64 + 32, r1);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->phiEmpty[buf]));
+                // sign as bf16: +1 = 0x3F80, -1 = 0xBF80, 0 = 0x0000
+                auto sgn = [](uint32_t bits) -> uint32_t {
+                    return (bits & 0x7FFFFFFFu) ? (((bits >> 16) & 0x8000u) | 0x3F80u) : 0u;
+                };
+                if (!mbar_wait(smem_u32(&ctrl->sEmpty), (job & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t s_blk = sbase + EB_SMEM_S + (uint32_t)half * EB_S_BLOCK;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint4 v;
+                    v.x = sgn(r0[8 * c + 0]) | (sgn(r0[8 * c + 1]) << 16);
+                    v.y = sgn(r0[8 * c + 2]) | (sgn(r0[8 * c + 3]) << 16);
+                    v.z = sgn(r0[8 * c + 4]) | (sgn(r0[8 * c + 5]) << 16);
+                    v.w = sgn(r0[8 * c + 6]) | (sgn(r0[8 * c + 7]) << 16);
+                    st_shared_v4(s_blk + sw128_chunk_offset((uint32_t)orow, (uint32_t)c), v);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint4 v;
+                    v.x = sgn(r1[8 * c + 0]) | (sgn(r1[8 * c + 1]) << 16);
+                    v.y = sgn(r1[8 * c + 2]) | (sgn(r1[8 * c + 3]) << 16);
+                    v.z = sgn(r1[8 * c + 4]) | (sgn(r1[8 * c + 5]) << 16);
+                    v.w = sgn(r1[8 * c + 6]) | (sgn(r1[8 * c + 7]) << 16);
+                    st_shared_v4(s_blk + sw128_chunk_offset((uint32_t)orow, (uint32_t)(4 + c)), v);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(smem_u32(&ctrl->sFull));
+            }
+            if (!ok) break;
+            // the item's parameter-gradient sums: this thread writes features 2 half, 2 half + 1
+            if (!mbar_wait(smem_u32(&ctrl->gFull), n_item & 1u, abort_flag)) break;
+            tc_fence_after_sync();
+            float* slab = slabs + (size_t)sp * ((size_t)O * I * 9);
+            for (int j = 0; j < n_ot; ++j) {
+                const int o = j * EDGE_OT + orow;
+#pragma unroll
+                for (int qq = 0; qq < 2; ++qq) {
+                    const int q = 2 * half + qq, f = fq * EDGE_FQ + q;
+                    uint32_t r[16];
+                    tmem_ld_32x16(lane_addr + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 16, r);
+                    tmem_ld_wait();
+                    if (o < O && f < I) {
+                        const float sc = __ldg(ga + (size_t)o * I + f) * inv_n;
+                        float* out = slab + ((size_t)o * I + f) * 9;
+#pragma unroll
+                        for (int c = 0; c < 9; ++c) out[c] = sc * __uint_as_float(r[c]);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctrl->gEmpty));
+        }
+    } else if (warp < EB_MMA_WARP) {
+        // ===== input-gradient warps: thread = one sample row of the tile =====
+        if (need_gx) {
+            const int quad = warp & 3;
+            const int row = quad * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                int sp, fq;
+                decode(item, sp, fq);
+                int64_t t0, t1;
+                tile_range(sp, t0, t1);
+                const int f0 = fq * EDGE_FQ;
+                for (int64_t t = t0; t < t1; ++t, ++it) {
+                    const uint32_t tb = it & 1u;
+                    const int64_t n = t * EB_TN + row;
+                    const bool row_ok = n < N;
+                    float xv[EDGE_FQ] = {0.f, 0.f, 0.f, 0.f};
+                    if (row_ok) {
+                        const float* xr = x + (size_t)n * I + f0;
+                        if (vec_x && f0 + EDGE_FQ <= I && (I & 3) == 0) {
+                            const float4 v = __ldg(reinterpret_cast<const float4*>(xr));
+                            xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < EDGE_FQ; ++q)
+                                if (f0 + q < I) xv[q] = __ldg(xr + q);
+                        }
+                    }
+                    float dcoef[EDGE_FQ][9];
+#pragma unroll
+                    for (int q = 0; q < EDGE_FQ; ++q) {
+                        const int f = f0 + q;
+                        const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
+                        float d[4];
+                        const int s0 = shared_grid ? eval_feature_deriv<true, false>(stab, ti, xv[q], d)
+                                                   : eval_feature_deriv<false, false>(ft, ti, xv[q], d);
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const int jj = c - s0;
+                            dcoef[q][c] = jj == 0 ? d[0] : (jj == 1 ? d[1] : (jj == 2 ? d[2] : (jj == 3 ? d[3] : 0.f)));
+                        }
+                        dcoef[q][8] = has_base ? silu_grad_fast(xv[q]) : 0.f;
+                    }
+                    if (!mbar_wait(smem_u32(&ctrl->d3Full[tb]), (it >> 1) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    float g[EDGE_FQ];
+#pragma unroll
+                    for (int q = 0; q < EDGE_FQ; ++q) {
+                        uint32_t r[16];
+                        tmem_ld_32x16(lane_addr + EB_TMEM_D3 + tb * 64 + (uint32_t)q * 16, r);
+                        tmem_ld_wait();
+                        float acc = 0.f;
+#pragma unroll
+                        for (int c = 0; c < 9; ++c) acc = fmaf(__uint_as_float(r[c]), dcoef[q][c], acc);
+                        g[q] = acc;
+                    }
+                    tc_fence_before_sync();
+                    mbar_arrive(smem_u32(&ctrl->d3Empty[tb]));
+                    if (row_ok) {
+                        float* out = gx + (size_t)n * I + f0;
+                        if (vec_x && f0 + EDGE_FQ <= I && (I & 3) == 0) {
+                            *reinterpret_cast<float4*>(out) = make_float4(g[0], g[1], g[2], g[3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < EDGE_FQ; ++q)
+                                if (f0 + q < I) out[q] = g[q];
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == EB_MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t idesc1 = make_idesc_bf16(EB_TN, false, false);
+            constexpr uint32_t idesc2 = make_idesc_bf16(16, false, true);
+            constexpr uint32_t idesc3 = make_idesc_bf16(16, true, true);
+            constexpr uint64_t d_k = make_sdesc_sw128(16, 1024);          // K-major rows of 128 B
+            constexpr uint64_t d_mn16 = make_sdesc_sw128(8192, 1024);     // MN-major, one group of columns
+            constexpr uint64_t d_mnS = make_sdesc_sw128(EB_S_BLOCK, 1024);  // MN-major, two groups of 64 samples
+            uint32_t it = 0, job = 0, n_item = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
+                int sp, fq;
+                decode(item, sp, fq);
+                int64_t t0, t1;
+                tile_range(sp, t0, t1);
+                if (!mbar_wait(smem_u32(&ctrl->fullW), n_item & 1u, abort_flag)) break;
+                if (!mbar_wait(smem_u32(&ctrl->gEmpty), (n_item & 1u) ^ 1u, abort_flag)) break;
+                tc_fence_after_sync();
+                auto stage_ready = [&](uint32_t tile_it) -> bool {
+                    if (!mbar_wait(smem_u32(&ctrl->fullA[tile_it & 1u]), (tile_it >> 1) & 1u, abort_flag)) return false;
+                    if (need_gx &&
+                        !mbar_wait(smem_u32(&ctrl->d3Empty[tile_it & 1u]), ((tile_it >> 1) & 1u) ^ 1u, abort_flag))
+                        return false;
+                    tc_fence_after_sync();
+                    return true;
+                };
+                auto gemm1 = [&](uint32_t tile_it, int j, int q, uint32_t jb) -> bool {
+                    const uint32_t buf = jb & 1u;
+                    if (!mbar_wait(smem_u32(&ctrl->phiEmpty[buf]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) return false;
+                    tc_fence_after_sync();
+                    const uint32_t a_hi = sbase + EB_SMEM_A + (tile_it & 1u) * EB_A_STAGE, a_lo = a_hi + EB_A_TILE;
+                    const uint32_t w_hi = sbase + EB_SMEM_W + j * EDGE_W_SLOT, w_lo = w_hi + EDGE_W_TILE;
+                    const uint32_t d = tmem_base + buf * EB_TN;
+                    mma_f16_ss(d, sdesc_at(d_k, w_hi + q * 32), sdesc_at(d_k, a_hi + q * 32), idesc1, 0u);
+                    mma_f16_ss(d, sdesc_at(d_k, w_lo + q * 32), sdesc_at(d_k, a_hi + q * 32), idesc1, 1u);
+                    mma_f16_ss(d, sdesc_at(d_k, w_hi + q * 32), sdesc_at(d_k, a_lo + q * 32), idesc1, 1u);
+                    mma_commit(smem_u32(&ctrl->phiFull[buf]));
+                    return true;
+                };
+                // units of the item in order (tile, output tile, feature); GEMM1 runs one unit ahead
+                int64_t t = t0;
+                int j = 0, q = 0;
+                uint32_t cur_it = it;
+                if (!stage_ready(cur_it) || !gemm1(cur_it, 0, 0, job)) break;
+                while (true) {
+                    int64_t nt = t;
+                    int nj = j, nq = q + 1;
+                    if (nq == EDGE_FQ) { nq = 0; ++nj; }
+                    if (nj == n_ot) { nj = 0; ++nt; }
+                    const bool has_next = nt < t1;
+                    const uint32_t next_it = cur_it + (nt != t ? 1u : 0u);
+                    if (has_next) {
+                        if (nt != t && !stage_ready(next_it)) { ok = false; break; }
+                        if (!gemm1(next_it, nj, nq, job + 1)) { ok = false; break; }
+                    }
+                    if (!mbar_wait(smem_u32(&ctrl->sFull), job & 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_hi = sbase + EB_SMEM_A + (cur_it & 1u) * EB_A_STAGE, a_lo = a_hi + EB_A_TILE;
+                    const uint32_t s_t = sbase + EB_SMEM_S;
+                    {   // GEMM2: G[j][q] (+)= S[o, n] A[n, r']
+                        const uint32_t d = tmem_base + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 16;
+                        uint32_t acc = t > t0 ? 1u : 0u;
+#pragma unroll 1
+                        for (int ks = 0; ks < 8; ++ks) {
+                            const uint32_t sa = s_t + (uint32_t)(ks >> 2) * EB_S_BLOCK + (uint32_t)(ks & 3) * 32;
+                            mma_f16_ss(d, sdesc_at(d_k, sa), sdesc_at(d_mn16, a_hi + q * 32 + ks * 2048), idesc2, acc);
+                            mma_f16_ss(d, sdesc_at(d_k, sa), sdesc_at(d_mn16, a_lo + q * 32 + ks * 2048), idesc2, 1u);
+                            acc = 1u;
+                        }
+                    }
+                    if (need_gx) {   // GEMM3: D3[q] (+)= S^T[n, o] Wg[o, r']
+                        const uint32_t wg_hi = sbase + EB_SMEM_WG + j * EDGE_W_SLOT, wg_lo = wg_hi + EDGE_W_TILE;
+                        const uint32_t d = tmem_base + EB_TMEM_D3 + (cur_it & 1u) * 64 + (uint32_t)q * 16;
+                        uint32_t acc = j > 0 ? 1u : 0u;
+#pragma unroll 1
+                        for (int ks = 0; ks < 8; ++ks) {
+                            mma_f16_ss(d, sdesc_at(d_mnS, s_t + ks * 2048), sdesc_at(d_mn16, wg_hi + q * 32 + ks * 2048),
+                                       idesc3, acc);
+                            mma_f16_ss(d, sdesc_at(d_mnS, s_t + ks * 2048), sdesc_at(d_mn16, wg_lo + q * 32 + ks * 2048),
+                                       idesc3, 1u);
+                            acc = 1u;
+                        }
+                    }
+                    mma_commit(smem_u32(&ctrl->sEmpty));
+                    if (!has_next || nt != t) {
+                        mma_commit(smem_u32(&ctrl->emptyA[cur_it & 1u]));
+                        if (need_gx) mma_commit(smem_u32(&ctrl->d3Full[cur_it & 1u]));
+                    }
+                    ++job;
+                    if (!has_next) break;
+                    t = nt; j = nj; q = nq; cur_it = next_it;
+                }
+                if (!ok) break;
+                it = cur_it + 1;
+                mma_commit(smem_u32(&ctrl->gFull));
+                mma_commit(smem_u32(&ctrl->emptyW));
+            }
+        }
+    } else {
+        if (lane == 0) {
+            // ===== bulk copies: the weight tiles of an item (and their ga-scaled twins), once per item =====
+            uint32_t n_item = 0;
+            for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
+                int sp, fq;
+                decode(item, sp, fq);
+                if (!mbar_wait(smem_u32(&ctrl->emptyW), (n_item & 1u) ^ 1u, abort_flag)) break;
+                const uint32_t bar = smem_u32(&ctrl->fullW);
+                mbar_arrive_expect_tx(bar, (uint32_t)n_ot * EDGE_W_SLOT * (need_gx ? 2u : 1u));
+                for (int j = 0; j < n_ot; ++j) {
+                    const size_t off = ((size_t)j * plan.n_quads + fq) * (size_t)EDGE_W_SLOT;
+                    bulk_g2s(sbase + EB_SMEM_W + j * EDGE_W_SLOT, wimg + off, EDGE_W_SLOT, bar);
+                    if (need_gx) bulk_g2s(sbase + EB_SMEM_WG + j * EDGE_W_SLOT, wgimg + off, EDGE_W_SLOT, bar);
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        if (lane == 0) report_status(status, kStatusTimeout);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == EB_MMA_WARP) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// dW[o,i,r] = sum over the sample ranges of slab[.][o][i][r], dbw[o,i] the same of slot 8.
+__global__ void edge_bwd_finalize_kernel(const float* __restrict__ slabs, int splits, float* __restrict__ dW,
+                                         float* __restrict__ dbw, int64_t pairs, int R) {
+    const int64_t total = pairs * 9;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t oi = e / 9;
+        const int c = (int)(e - oi * 9);
+        const bool wanted = c < R ? dW != nullptr : (c == 8 && dbw != nullptr);
+        if (!wanted) continue;
+        float v = 0.f;
+        for (int s = 0; s < splits; ++s) v += slabs[(size_t)s * total + e];
+        if (c < R) dW[oi * R + c] = v;
+        else dbw[oi] = v;
+    }
+}
+
+EdgeBwdPlan plan_edge_bwd(int64_t N, int I, int O) {
+    EdgeBwdPlan p;
+    p.n_quads = (I + EDGE_FQ - 1) / EDGE_FQ;
+    p.n_otiles = (O + EDGE_OT - 1) / EDGE_OT;
+    p.tiles_total = (N + EB_TN - 1) / EB_TN;
+    // chains of at most EB_MAX_CHAIN_TILES sample tiles per accumulator, and about four rounds of
+    // work items for the persistent blocks
+    int64_t splits = (p.tiles_total + EB_MAX_CHAIN_TILES - 1) / EB_MAX_CHAIN_TILES;
+    const int64_t for_balance = (4 * (int64_t)sm_count() + p.n_quads - 1) / p.n_quads;
+    if (splits < for_balance) splits = for_balance;
+    if (splits > p.tiles_total) splits = p.tiles_total;
+    if (splits < 1) splits = 1;
+    p.tiles_per_split = (p.tiles_total + splits - 1) / splits;
+    p.splits = (int)((p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split);
+    return p;
+}
+
 }  // namespace
 
 bool tc_edge_supported(const LayerShape& s) {
@@ -442,7 +949,8 @@ cudaError_t tc_edge_forward(int split_terms, const float* x, const float* s_val,
         const int64_t chunks = (int64_t)p.n_otiles * p.n_quads * EDGE_OT * 8;
         int blocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
                                                                             : (int64_t)sm_count() * 16);
-        pack_edge_weights_kernel<<<blocks, 256, 0, st>>>(W, bw, wimg, s.O, s.I, s.R(), p.n_quads, p.n_otiles);
+        pack_edge_weights_kernel<<<blocks, 256, 0, st>>>(W, bw, nullptr, 1.0f, wimg, s.O, s.I, s.R(), p.n_quads,
+                                                         p.n_otiles);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     const int vec_x = ((s.I & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
@@ -465,6 +973,70 @@ cudaError_t tc_edge_forward(int split_terms, const float* x, const float* s_val,
     int rblocks = (int)((elems + 255) / 256 < (int64_t)sm_count() * 8 ? (elems + 255) / 256 : (int64_t)sm_count() * 8);
     edge_sum_slabs_kernel<<<rblocks, 256, 0, st>>>(partial, a, elems, p.n_slabs(), 1.0f / (float)s.N);
     return cudaGetLastError();
+}
+
+// Backward on the tensor cores: float32, G + k <= 8, up to 256 outputs, SiLU (or no) base branch.
+bool tc_edge_bwd_supported(const LayerShape& s) {
+    return tc_edge_supported(s) && s.O <= EDGE_OT * EDGE_MAX_OTILES && s.N >= 1;
+}
+
+size_t tc_edge_bwd_workspace(const LayerShape& s, bool need_x) {
+    const EdgeBwdPlan p = plan_edge_bwd(s.N, s.I, s.O);
+    const size_t img = align256((size_t)p.n_otiles * p.n_quads * EDGE_W_SLOT);
+    return kWsHeader + tc_table_bytes(s) + img * (need_x ? 2 : 1) +
+           align256((size_t)p.splits * s.O * s.I * 9 * sizeof(float));
+}
+
+// ga = gradient of the loss with respect to a [O, I]; W the effective coefficients; gx, dbw, dW may be NULL.
+cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid, const float* bw, const float* W,
+                             float* gx, float* dbw, float* dW, const LayerShape& s, void* ws, size_t ws_bytes,
+                             cudaStream_t st) {
+    const bool need_x = gx != nullptr;
+    if (!ws || ws_bytes < tc_edge_bwd_workspace(s, need_x)) return cudaErrorMemoryAllocation;
+    const EdgeBwdPlan p = plan_edge_bwd(s.N, s.I, s.O);
+    const TabInfo ti = make_tab_info(s.G, s.K);
+    int* status = reinterpret_cast<int*>(ws);
+    uint8_t* cur = reinterpret_cast<uint8_t*>(ws) + kWsHeader;
+    float* tab = reinterpret_cast<float*>(cur);
+    cur += tc_table_bytes(s);
+    const size_t img = align256((size_t)p.n_otiles * p.n_quads * EDGE_W_SLOT);
+    uint8_t* wimg = cur;
+    cur += img;
+    uint8_t* wgimg = need_x ? cur : nullptr;
+    if (need_x) cur += img;
+    float* slabs = reinterpret_cast<float*>(cur);
+
+    cudaError_t e = tc_build_table(grid, tab, s, st);
+    if (e != cudaSuccess) return e;
+    const int64_t chunks = (int64_t)p.n_otiles * p.n_quads * EDGE_OT * 8;
+    const int pblocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
+                                                                              : (int64_t)sm_count() * 16);
+    pack_edge_weights_kernel<<<pblocks, 256, 0, st>>>(W, bw, nullptr, 1.0f, wimg, s.O, s.I, s.R(), p.n_quads,
+                                                      p.n_otiles);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    if (need_x) {
+        pack_edge_weights_kernel<<<pblocks, 256, 0, st>>>(W, bw, ga, 1.0f / (float)s.N, wgimg, s.O, s.I, s.R(),
+                                                          p.n_quads, p.n_otiles);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    const int vec_x = ((s.I & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                      (!gx || (reinterpret_cast<uintptr_t>(gx) & 15) == 0);
+    const int64_t items = p.n_items();
+    const int blocks = (int)(items < sm_count() ? items : sm_count());
+    e = ensure_dynamic_smem<tc_edge_bwd_kernel>((int)EB_SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    tc_edge_bwd_kernel<<<blocks, EB_THREADS, EB_SMEM_BYTES, st>>>(x, tab, wimg, wgimg, ga, slabs, gx, status, s.N, s.I,
+                                                                  s.O, bw ? 1 : 0, p, ti, vec_x);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    if (dW || (dbw && bw)) {
+        const int64_t total = (int64_t)s.O * s.I * 9;
+        const int fblocks = (int)((total + 255) / 256 < (int64_t)sm_count() * 8 ? (total + 255) / 256
+                                                                                : (int64_t)sm_count() * 8);
+        edge_bwd_finalize_kernel<<<fblocks, 256, 0, st>>>(slabs, p.splits, dW, bw ? dbw : nullptr, (int64_t)s.O * s.I,
+                                                          s.R());
+        e = cudaGetLastError();
+    }
+    return e;
 }
 
 }  // namespace kanb200

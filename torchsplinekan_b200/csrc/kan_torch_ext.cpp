@@ -540,12 +540,12 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> edge_abs_mean_x_backward(const Tensor
     if (need_W) dW = at::empty({O, I, R}, x.options());
     const Tensor ga = grad_a.to(x.scalar_type()).contiguous(), xc = x.contiguous(), sc = contig_or_absent(s),
                  gc = grid.contiguous(), bw = contig_or_absent(base_weight), Wc = W.contiguous();
-    const int code = dtype_code(x);
+    const int code = dtype_code(x), mode = g_mode.load();
     Scratch* ws = scratch(x.device(), st, WS_EDGE_X,
-                          kanb200_workspace_bytes(KANB200_OP_EDGE_X_BWD, KANB200_MODE_AUTO, code, N, I, O, G, (int)k, 0, 0));
+                          kanb200_workspace_bytes(KANB200_OP_EDGE_X_BWD, mode, code, N, I, O, G, (int)k, 0, 0));
     {
         ScopedTimer timer("edge_backward", st);
-        check_rc(kanb200_edge_abs_mean_x_backward(code, ga.data_ptr(), xc.data_ptr(), cptr(sc), gc.data_ptr(), cptr(bw),
+        check_rc(kanb200_edge_abs_mean_x_backward(code, mode, ga.data_ptr(), xc.data_ptr(), cptr(sc), gc.data_ptr(), cptr(bw),
                                                   Wc.data_ptr(), mptr(gx), mptr(ds), mptr(dbw), mptr(dW), N, I, O, G,
                                                   (int)k, ws ? ws->buf.data_ptr() : nullptr,
                                                   ws ? (size_t)ws->buf.numel() : 0, st));
