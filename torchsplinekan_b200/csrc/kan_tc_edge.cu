@@ -442,9 +442,10 @@ constexpr int EB_MAX_CHAIN_TILES = 8;
 constexpr uint32_t EB_A_TILE = EB_TN * 128;                       // 16 KB
 constexpr uint32_t EB_A_STAGE = 2 * EB_A_TILE;
 constexpr uint32_t EB_S_BLOCK = EDGE_OT * 128;                    // 16 KB: 128 outputs x 64 samples
-constexpr uint32_t EB_SMEM_A = 0;
-constexpr uint32_t EB_SMEM_S = EB_SMEM_A + 2 * EB_A_STAGE;
-constexpr uint32_t EB_SMEM_W = EB_SMEM_S + 2 * EB_S_BLOCK;
+constexpr uint32_t EB_S_TILE = 2 * EB_S_BLOCK;                    // 32 KB: 128 outputs x 128 samples
+constexpr uint32_t EB_SMEM_A = 0;                                 // one stage: the producers refill it at tile ends
+constexpr uint32_t EB_SMEM_S = EB_SMEM_A + EB_A_STAGE;            // two sign tiles: conversion runs one unit ahead
+constexpr uint32_t EB_SMEM_W = EB_SMEM_S + 2 * EB_S_TILE;
 constexpr uint32_t EB_SMEM_WG = EB_SMEM_W + EDGE_MAX_OTILES * EDGE_W_SLOT;
 constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WG + EDGE_MAX_OTILES * EDGE_W_SLOT;
 constexpr uint32_t EB_SMEM_BYTES = EB_SMEM_CTRL + 256 + TAB_SMEM_FLOATS * 4;
@@ -452,10 +453,10 @@ static_assert(EB_SMEM_BYTES <= 232448, "edge backward kernel shared memory excee
 constexpr uint32_t EB_TMEM_G = 256, EB_TMEM_D3 = 384;
 
 struct EdgeBwdCtrl {
-    uint64_t fullA[2], emptyA[2];
+    uint64_t fullA, emptyA;
     uint64_t fullW, emptyW;
     uint64_t phiFull[2], phiEmpty[2];
-    uint64_t sFull, sEmpty;
+    uint64_t sFull[2], sEmpty[2];
     uint64_t gFull, gEmpty;
     uint64_t d3Full[2], d3Empty[2];
     uint32_t tmem_base;
@@ -490,17 +491,17 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&ctrl->fullA[s]), EB_PRODUCERS);
-            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
             mbar_init(smem_u32(&ctrl->phiFull[s]), 1);
             mbar_init(smem_u32(&ctrl->phiEmpty[s]), EB_SIGNERS);
+            mbar_init(smem_u32(&ctrl->sFull[s]), EB_SIGNERS);
+            mbar_init(smem_u32(&ctrl->sEmpty[s]), 1);
             mbar_init(smem_u32(&ctrl->d3Full[s]), 1);
             mbar_init(smem_u32(&ctrl->d3Empty[s]), EB_GXERS);
         }
+        mbar_init(smem_u32(&ctrl->fullA), EB_PRODUCERS);
+        mbar_init(smem_u32(&ctrl->emptyA), 1);
         mbar_init(smem_u32(&ctrl->fullW), 1);
         mbar_init(smem_u32(&ctrl->emptyW), 1);
-        mbar_init(smem_u32(&ctrl->sFull), EB_SIGNERS);
-        mbar_init(smem_u32(&ctrl->sEmpty), 1);
         mbar_init(smem_u32(&ctrl->gFull), 1);
         mbar_init(smem_u32(&ctrl->gEmpty), EB_SIGNERS);
         ctrl->abort_flag = 0;
@@ -540,8 +541,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             tile_range(sp, t0, t1);
             const int f0 = fq * EDGE_FQ + 2 * pr;
             for (int64_t t = t0; t < t1; ++t, ++it) {
-                const uint32_t stage = it & 1u;
-                const uint32_t a_hi = sbase + EB_SMEM_A + stage * EB_A_STAGE;
+                const uint32_t a_hi = sbase + EB_SMEM_A;
                 const uint32_t a_lo = a_hi + EB_A_TILE;
                 const int64_t n = t * EB_TN + row;
                 const bool row_ok = n < N;
@@ -574,7 +574,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     }
                     split2(sv, 0.0f, bh[q], bl[q]);
                 }
-                if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                if (!mbar_wait(smem_u32(&ctrl->emptyA), (it & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
@@ -589,7 +589,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     st_shared_v4(a_lo + off1, make_uint4(bl[q], 0, 0, 0));
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->fullA[stage]));
+                mbar_arrive(smem_u32(&ctrl->fullA));
             }
         }
     } else if (warp < EB_PRODUCER_WARPS + EB_SIGN_WARPS) {
@@ -621,35 +621,38 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&ctrl->phiEmpty[buf]));
-                // sign as bf16: +1 = 0x3F80, -1 = 0xBF80, 0 = 0x0000
-                auto sgn = [](uint32_t bits) -> uint32_t {
-                    return (bits & 0x7FFFFFFFu) ? (((bits >> 16) & 0x8000u) | 0x3F80u) : 0u;
+                // signs of two neighbouring samples as a pair of bf16 (+1 = 0x3F80, -1 = 0xBF80, 0 = 0)
+                auto sgn2 = [](uint32_t a, uint32_t b) -> uint32_t {
+                    const uint32_t t = (__byte_perm(a, b, 0x7632) & 0x80008000u) | 0x3F803F80u;
+                    const uint32_t keep = ((a << 1) ? 0x0000FFFFu : 0u) | ((b << 1) ? 0xFFFF0000u : 0u);
+                    return t & keep;
                 };
-                if (!mbar_wait(smem_u32(&ctrl->sEmpty), (job & 1u) ^ 1u, abort_flag)) {
+                const uint32_t sb = job & 1u;
+                if (!mbar_wait(smem_u32(&ctrl->sEmpty[sb]), ((job >> 1) & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
-                const uint32_t s_blk = sbase + EB_SMEM_S + (uint32_t)half * EB_S_BLOCK;
+                const uint32_t s_blk = sbase + EB_SMEM_S + sb * EB_S_TILE + (uint32_t)half * EB_S_BLOCK;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint4 v;
-                    v.x = sgn(r0[8 * c + 0]) | (sgn(r0[8 * c + 1]) << 16);
-                    v.y = sgn(r0[8 * c + 2]) | (sgn(r0[8 * c + 3]) << 16);
-                    v.z = sgn(r0[8 * c + 4]) | (sgn(r0[8 * c + 5]) << 16);
-                    v.w = sgn(r0[8 * c + 6]) | (sgn(r0[8 * c + 7]) << 16);
+                    v.x = sgn2(r0[8 * c + 0], r0[8 * c + 1]);
+                    v.y = sgn2(r0[8 * c + 2], r0[8 * c + 3]);
+                    v.z = sgn2(r0[8 * c + 4], r0[8 * c + 5]);
+                    v.w = sgn2(r0[8 * c + 6], r0[8 * c + 7]);
                     st_shared_v4(s_blk + sw128_chunk_offset((uint32_t)orow, (uint32_t)c), v);
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint4 v;
-                    v.x = sgn(r1[8 * c + 0]) | (sgn(r1[8 * c + 1]) << 16);
-                    v.y = sgn(r1[8 * c + 2]) | (sgn(r1[8 * c + 3]) << 16);
-                    v.z = sgn(r1[8 * c + 4]) | (sgn(r1[8 * c + 5]) << 16);
-                    v.w = sgn(r1[8 * c + 6]) | (sgn(r1[8 * c + 7]) << 16);
+                    v.x = sgn2(r1[8 * c + 0], r1[8 * c + 1]);
+                    v.y = sgn2(r1[8 * c + 2], r1[8 * c + 3]);
+                    v.z = sgn2(r1[8 * c + 4], r1[8 * c + 5]);
+                    v.w = sgn2(r1[8 * c + 6], r1[8 * c + 7]);
                     st_shared_v4(s_blk + sw128_chunk_offset((uint32_t)orow, (uint32_t)(4 + c)), v);
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->sFull));
+                mbar_arrive(smem_u32(&ctrl->sFull[sb]));
             }
             if (!ok) break;
             // the item's parameter-gradient sums: this thread writes features 2 half, 2 half + 1
@@ -769,79 +772,81 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 if (!mbar_wait(smem_u32(&ctrl->fullW), n_item & 1u, abort_flag)) break;
                 if (!mbar_wait(smem_u32(&ctrl->gEmpty), (n_item & 1u) ^ 1u, abort_flag)) break;
                 tc_fence_after_sync();
+                const uint32_t a_hi = sbase + EB_SMEM_A, a_lo = a_hi + EB_A_TILE;
                 auto stage_ready = [&](uint32_t tile_it) -> bool {
-                    if (!mbar_wait(smem_u32(&ctrl->fullA[tile_it & 1u]), (tile_it >> 1) & 1u, abort_flag)) return false;
+                    if (!mbar_wait(smem_u32(&ctrl->fullA), tile_it & 1u, abort_flag)) return false;
                     if (need_gx &&
                         !mbar_wait(smem_u32(&ctrl->d3Empty[tile_it & 1u]), ((tile_it >> 1) & 1u) ^ 1u, abort_flag))
                         return false;
                     tc_fence_after_sync();
                     return true;
                 };
-                auto gemm1 = [&](uint32_t tile_it, int j, int q, uint32_t jb) -> bool {
+                auto gemm1 = [&](int j, int q, uint32_t jb) -> bool {
                     const uint32_t buf = jb & 1u;
                     if (!mbar_wait(smem_u32(&ctrl->phiEmpty[buf]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) return false;
                     tc_fence_after_sync();
-                    const uint32_t a_hi = sbase + EB_SMEM_A + (tile_it & 1u) * EB_A_STAGE, a_lo = a_hi + EB_A_TILE;
-                    const uint32_t w_hi = sbase + EB_SMEM_W + j * EDGE_W_SLOT, w_lo = w_hi + EDGE_W_TILE;
+                    const uint32_t w_hi = sbase + EB_SMEM_W + j * EDGE_W_SLOT + q * 32;
+                    const uint64_t dw_hi = sdesc_at(d_k, w_hi), dw_lo = sdesc_at(d_k, w_hi + EDGE_W_TILE);
+                    const uint64_t da_hi = sdesc_at(d_k, a_hi + q * 32), da_lo = sdesc_at(d_k, a_lo + q * 32);
                     const uint32_t d = tmem_base + buf * EB_TN;
-                    mma_f16_ss(d, sdesc_at(d_k, w_hi + q * 32), sdesc_at(d_k, a_hi + q * 32), idesc1, 0u);
-                    mma_f16_ss(d, sdesc_at(d_k, w_lo + q * 32), sdesc_at(d_k, a_hi + q * 32), idesc1, 1u);
-                    mma_f16_ss(d, sdesc_at(d_k, w_hi + q * 32), sdesc_at(d_k, a_lo + q * 32), idesc1, 1u);
+                    mma_f16_ss(d, dw_hi, da_hi, idesc1, 0u);
+                    mma_f16_ss(d, dw_lo, da_hi, idesc1, 1u);
+                    mma_f16_ss(d, dw_hi, da_lo, idesc1, 1u);
                     mma_commit(smem_u32(&ctrl->phiFull[buf]));
                     return true;
                 };
-                // units of the item in order (tile, output tile, feature); GEMM1 runs one unit ahead
+                // units of the item in order (tile, output tile, feature); within a tile GEMM1 runs one
+                // unit ahead of the two products that consume the sign tile
                 int64_t t = t0;
                 int j = 0, q = 0;
                 uint32_t cur_it = it;
-                if (!stage_ready(cur_it) || !gemm1(cur_it, 0, 0, job)) break;
+                if (!stage_ready(cur_it) || !gemm1(0, 0, job)) break;
                 while (true) {
                     int64_t nt = t;
                     int nj = j, nq = q + 1;
                     if (nq == EDGE_FQ) { nq = 0; ++nj; }
                     if (nj == n_ot) { nj = 0; ++nt; }
-                    const bool has_next = nt < t1;
-                    const uint32_t next_it = cur_it + (nt != t ? 1u : 0u);
-                    if (has_next) {
-                        if (nt != t && !stage_ready(next_it)) { ok = false; break; }
-                        if (!gemm1(next_it, nj, nq, job + 1)) { ok = false; break; }
-                    }
-                    if (!mbar_wait(smem_u32(&ctrl->sFull), job & 1u, abort_flag)) { ok = false; break; }
+                    const bool has_next = nt < t1, same_tile = nt == t;
+                    if (has_next && same_tile && !gemm1(nj, nq, job + 1)) { ok = false; break; }
+                    const uint32_t sb = job & 1u;
+                    if (!mbar_wait(smem_u32(&ctrl->sFull[sb]), (job >> 1) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t a_hi = sbase + EB_SMEM_A + (cur_it & 1u) * EB_A_STAGE, a_lo = a_hi + EB_A_TILE;
-                    const uint32_t s_t = sbase + EB_SMEM_S;
-                    {   // GEMM2: G[j][q] (+)= S[o, n] A[n, r']
+                    const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
+                    {   // GEMM2: G[j][q] (+)= S[o, n] A[n, r']; descriptor addresses advance in 16-byte units
                         const uint32_t d = tmem_base + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 16;
-                        uint32_t acc = t > t0 ? 1u : 0u;
-#pragma unroll 1
+                        const uint64_t ds0 = sdesc_at(d_k, s_t), ds1 = sdesc_at(d_k, s_t + EB_S_BLOCK);
+                        const uint64_t dh = sdesc_at(d_mn16, a_hi + q * 32), dl = sdesc_at(d_mn16, a_lo + q * 32);
+                        const uint32_t first = t > t0 ? 1u : 0u;
+#pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
-                            const uint32_t sa = s_t + (uint32_t)(ks >> 2) * EB_S_BLOCK + (uint32_t)(ks & 3) * 32;
-                            mma_f16_ss(d, sdesc_at(d_k, sa), sdesc_at(d_mn16, a_hi + q * 32 + ks * 2048), idesc2, acc);
-                            mma_f16_ss(d, sdesc_at(d_k, sa), sdesc_at(d_mn16, a_lo + q * 32 + ks * 2048), idesc2, 1u);
-                            acc = 1u;
+                            const uint64_t sa = (ks < 4 ? ds0 : ds1) + (uint64_t)((ks & 3) * 2);
+                            mma_f16_ss(d, sa, dh + (uint64_t)(ks * 128), idesc2, ks == 0 ? first : 1u);
+                            mma_f16_ss(d, sa, dl + (uint64_t)(ks * 128), idesc2, 1u);
                         }
                     }
                     if (need_gx) {   // GEMM3: D3[q] (+)= S^T[n, o] Wg[o, r']
-                        const uint32_t wg_hi = sbase + EB_SMEM_WG + j * EDGE_W_SLOT, wg_lo = wg_hi + EDGE_W_TILE;
+                        const uint32_t wg_hi = sbase + EB_SMEM_WG + j * EDGE_W_SLOT + q * 32;
                         const uint32_t d = tmem_base + EB_TMEM_D3 + (cur_it & 1u) * 64 + (uint32_t)q * 16;
-                        uint32_t acc = j > 0 ? 1u : 0u;
-#pragma unroll 1
+                        const uint64_t dsT = sdesc_at(d_mnS, s_t);
+                        const uint64_t dh = sdesc_at(d_mn16, wg_hi), dl = sdesc_at(d_mn16, wg_hi + EDGE_W_TILE);
+                        const uint32_t first = j > 0 ? 1u : 0u;
+#pragma unroll
                         for (int ks = 0; ks < 8; ++ks) {
-                            mma_f16_ss(d, sdesc_at(d_mnS, s_t + ks * 2048), sdesc_at(d_mn16, wg_hi + q * 32 + ks * 2048),
-                                       idesc3, acc);
-                            mma_f16_ss(d, sdesc_at(d_mnS, s_t + ks * 2048), sdesc_at(d_mn16, wg_lo + q * 32 + ks * 2048),
-                                       idesc3, 1u);
-                            acc = 1u;
+                            mma_f16_ss(d, dsT + (uint64_t)(ks * 128), dh + (uint64_t)(ks * 128), idesc3,
+                                       ks == 0 ? first : 1u);
+                            mma_f16_ss(d, dsT + (uint64_t)(ks * 128), dl + (uint64_t)(ks * 128), idesc3, 1u);
                         }
                     }
-                    mma_commit(smem_u32(&ctrl->sEmpty));
-                    if (!has_next || nt != t) {
-                        mma_commit(smem_u32(&ctrl->emptyA[cur_it & 1u]));
-                        if (need_gx) mma_commit(smem_u32(&ctrl->d3Full[cur_it & 1u]));
-                    }
+                    mma_commit(smem_u32(&ctrl->sEmpty[sb]));
                     ++job;
-                    if (!has_next) break;
-                    t = nt; j = nj; q = nq; cur_it = next_it;
+                    if (!has_next || !same_tile) {
+                        mma_commit(smem_u32(&ctrl->emptyA));
+                        if (need_gx) mma_commit(smem_u32(&ctrl->d3Full[cur_it & 1u]));
+                        if (!has_next) break;
+                        ++cur_it;
+                        if (!stage_ready(cur_it) || !gemm1(nj, nq, job)) { ok = false; break; }
+                    }
+                    t = nt; j = nj; q = nq;
                 }
                 if (!ok) break;
                 it = cur_it + 1;
