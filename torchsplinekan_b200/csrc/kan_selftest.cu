@@ -164,6 +164,60 @@ umma_general_kernel(const uint8_t* __restrict__ a_img, const uint8_t* __restrict
     }
 }
 
+// Issue and completion cost of small MMAs: one or two threads (of different warps) each issue `reps`
+// K = 16 MMAs with N columns (operands: zero-filled 128-byte-swizzled K-major tiles, the same for
+// every MMA; accumulators: separate tensor-memory columns per thread) and commit.  Reports clock
+// cycles: [0] issue loop of thread 0, [1] until thread 0's MMAs completed, [2], [3] the same for
+// thread 1.
+__global__ void __launch_bounds__(128, 1)
+umma_rate_kernel(int n, int reps, int threads, int same_acc, long long* __restrict__ out, int* __restrict__ status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t done_bar[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t e = threadIdx.x * 16; e < 65536; e += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(smem + e) = make_uint4(0, 0, 0, 0);
+    fence_proxy_async_smem();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done_bar[0]), 1);
+        mbar_init(smem_u32(&done_bar[1]), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+    if (lane == 0 && warp < threads) {
+        const uint64_t desc = make_sdesc_sw128(16, 1024);
+        const uint32_t idesc = make_idesc_bf16(n, false, false);
+        const uint64_t a = sdesc_at(desc, sbase + warp * 16384), b = sdesc_at(desc, sbase + 32768);
+        const long long t0 = clock64();
+        for (int r = 0; r < reps; ++r)
+            mma_f16_ss(tmem_base + warp * 256 + (same_acc ? 0 : (r & 7) * 32 * (n > 32 ? 0 : 1)), a + (uint64_t)((r & 3) * 2),
+                       b + (uint64_t)((r & 3) * 2), idesc, 1u);
+        mma_commit(smem_u32(&done_bar[warp]));
+        const long long t1 = clock64();
+        const bool ok = mbar_wait(smem_u32(&done_bar[warp]), 0, &abort_flag);
+        const long long t2 = clock64();
+        out[2 * warp] = t1 - t0;
+        out[2 * warp + 1] = t2 - t0;
+        if (!ok) atomicExch(status, 1);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // Register-only FMA loop for measuring the FP32 / FP64 FMA-pipe peaks the gather kernels are
 // compared with: every thread runs `iters` rounds of 16 independent dependent-chain FMAs.
 template <typename T>
@@ -301,5 +355,18 @@ int kanb200_selftest_umma_general(const void* a_img, const void* b_img, const un
     if (e != cudaSuccess) return -4;
     umma_general_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(reinterpret_cast<const uint8_t*>(a_img),
                                                                  reinterpret_cast<const uint8_t*>(b_img), L, D, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// See umma_rate_kernel: n columns (16 .. 256), reps MMAs per thread, 1 or 2 issuing threads,
+// same_acc = every MMA of a thread accumulates into the same columns.  out receives 4 cycle counts.
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_umma_rate(int n, int reps, int threads, int same_acc, long long* out, int* status, void* stream) {
+    using namespace kanb200;
+    if (n < 16 || n > 256 || (n & 15) || reps < 1 || reps > 4096 || threads < 1 || threads > 2 || !out || !status) return -1;
+    const int smem = 65536;
+    cudaError_t e = cudaFuncSetAttribute(umma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return -4;
+    umma_rate_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(n, reps, threads, same_acc, out, status);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

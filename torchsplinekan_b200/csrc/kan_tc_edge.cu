@@ -434,7 +434,7 @@ EdgePlanTc plan_edge_tc(int64_t N, int I, int O) {
 // ever stored.  Up to 256 outputs (both output tiles in one item, so gx needs no second pass).
 // ===========================================================================================
 constexpr int EB_TN = 128;                                        // samples per tile
-constexpr int EB_PRODUCER_WARPS = 8, EB_SIGN_WARPS = 8, EB_GX_WARPS = 4;
+constexpr int EB_PRODUCER_WARPS = 4, EB_SIGN_WARPS = 16, EB_GX_WARPS = 4;
 constexpr int EB_PRODUCERS = EB_PRODUCER_WARPS * 32, EB_SIGNERS = EB_SIGN_WARPS * 32, EB_GXERS = EB_GX_WARPS * 32;
 constexpr int EB_MMA_WARP = EB_PRODUCER_WARPS + EB_SIGN_WARPS + EB_GX_WARPS;
 constexpr int EB_THREADS = (EB_MMA_WARP + 2) * 32;
@@ -492,8 +492,8 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&ctrl->phiFull[s]), 1);
-            mbar_init(smem_u32(&ctrl->phiEmpty[s]), EB_SIGNERS);
-            mbar_init(smem_u32(&ctrl->sFull[s]), EB_SIGNERS);
+            mbar_init(smem_u32(&ctrl->phiEmpty[s]), EB_SIGNERS / 2);      // one group of sign warps each
+            mbar_init(smem_u32(&ctrl->sFull[s]), EB_SIGNERS / 2);
             mbar_init(smem_u32(&ctrl->sEmpty[s]), 1);
             mbar_init(smem_u32(&ctrl->d3Full[s]), 1);
             mbar_init(smem_u32(&ctrl->d3Empty[s]), EB_GXERS);
@@ -530,8 +530,8 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
     };
 
     if (warp < EB_PRODUCER_WARPS) {
-        // ===== producers: thread = (sample row, pair of features) =====
-        const int row = threadIdx.x & (EB_TN - 1), pr = threadIdx.x >> 7;      // pr = 0, 1
+        // ===== producers: thread = one sample row, its four features in two passes =====
+        const int row = threadIdx.x;                                            // 0 .. 127
         uint32_t it = 0;
         bool ok = true;
         for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
@@ -539,12 +539,15 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             decode(item, sp, fq);
             int64_t t0, t1;
             tile_range(sp, t0, t1);
-            const int f0 = fq * EDGE_FQ + 2 * pr;
             for (int64_t t = t0; t < t1; ++t, ++it) {
                 const uint32_t a_hi = sbase + EB_SMEM_A;
                 const uint32_t a_lo = a_hi + EB_A_TILE;
                 const int64_t n = t * EB_TN + row;
                 const bool row_ok = n < N;
+                bool waited = false;
+#pragma unroll 1
+                for (int pr = 0; pr < 2; ++pr) {
+                const int f0 = fq * EDGE_FQ + 2 * pr;
                 float xv[2] = {0.f, 0.f};
                 if (row_ok) {
                     const float* xr = x + (size_t)n * I + f0;
@@ -574,10 +577,11 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     }
                     split2(sv, 0.0f, bh[q], bl[q]);
                 }
-                if (!mbar_wait(smem_u32(&ctrl->emptyA), (it & 1u) ^ 1u, abort_flag)) {
+                if (!waited && !mbar_wait(smem_u32(&ctrl->emptyA), (it & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
+                waited = true;
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
                     const uint32_t c0 = (uint32_t)(2 * (2 * pr + q));
@@ -588,82 +592,79 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     st_shared_v4(a_lo + off0, lo[q]);
                     st_shared_v4(a_lo + off1, make_uint4(bl[q], 0, 0, 0));
                 }
+                }
+                if (!ok) break;
                 fence_proxy_async_smem();
                 mbar_arrive(smem_u32(&ctrl->fullA));
             }
         }
     } else if (warp < EB_PRODUCER_WARPS + EB_SIGN_WARPS) {
-        // ===== sign warps: thread = one output row, one half (64) of the sample columns =====
-        const int e = warp - EB_PRODUCER_WARPS;            // 0 .. 7
+        // ===== sign warps: two groups of eight; group g converts the units with job parity g (accumulator
+        // g -> sign tile g), so two conversions are in flight; thread = one output row, 64 samples.
+        // sign(phi) as bf16 is the float's sign bit over the pattern of 1.0 (0x3F80); an exact zero
+        // counts as +1, which only matters for edges whose weights are all zero (the finalize kernel
+        // writes their gradients as zero, and their scaled weights contribute nothing to gx) =====
+        const int e = warp - EB_PRODUCER_WARPS;            // 0 .. 15
         const int quad = warp & 3;
-        const int half = e >> 2;
+        const int half = e >> 3;                           // the group
+        const int ch = (e >> 2) & 1;                       // samples [64 ch, 64 ch + 64)
         const int orow = quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const uint32_t row_off = (uint32_t)(orow >> 3) * 1024u + (uint32_t)(orow & 7) * 128u, x7 = (uint32_t)(orow & 7);
         const float inv_n = 1.0f / (float)N;
         uint32_t job = 0, n_item = 0;
         bool ok = true;
+        auto sgn2 = [](uint32_t a, uint32_t b) -> uint32_t {
+            return (__byte_perm(a, b, 0x7632) & 0x80008000u) | 0x3F803F80u;
+        };
         for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
             int sp, fq;
             decode(item, sp, fq);
             int64_t t0, t1;
             tile_range(sp, t0, t1);
-            const int64_t units = (t1 - t0) * n_ot * EDGE_FQ;
-            for (int64_t u = 0; u < units; ++u, ++job) {
-                const uint32_t buf = job & 1u;
-                if (!mbar_wait(smem_u32(&ctrl->phiFull[buf]), (job >> 1) & 1u, abort_flag)) {
+            const int64_t units = (t1 - t0) * n_ot * EDGE_FQ;          // a multiple of 4: job stays even at item starts
+            for (int64_t u = half; u < units && ok; u += 2) {
+                const uint32_t jb = job + (uint32_t)u;
+                const uint32_t buf = (uint32_t)half;                    // == jb & 1
+                if (!mbar_wait(smem_u32(&ctrl->phiFull[buf]), (jb >> 1) & 1u, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (!mbar_wait(smem_u32(&ctrl->sEmpty[buf]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                uint32_t r0[32], r1[32];
-                tmem_ld_32x32(lane_addr + buf * EB_TN + half * 64, r0);
-                tmem_ld_32x32(lane_addr + buf * EB_TN + half * 64 + 32, r1);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                mbar_arrive(smem_u32(&ctrl->phiEmpty[buf]));
-                // signs of two neighbouring samples as a pair of bf16 (+1 = 0x3F80, -1 = 0xBF80, 0 = 0)
-                auto sgn2 = [](uint32_t a, uint32_t b) -> uint32_t {
-                    const uint32_t t = (__byte_perm(a, b, 0x7632) & 0x80008000u) | 0x3F803F80u;
-                    const uint32_t keep = ((a << 1) ? 0x0000FFFFu : 0u) | ((b << 1) ? 0xFFFF0000u : 0u);
-                    return t & keep;
-                };
-                const uint32_t sb = job & 1u;
-                if (!mbar_wait(smem_u32(&ctrl->sEmpty[sb]), ((job >> 1) & 1u) ^ 1u, abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                const uint32_t s_blk = sbase + EB_SMEM_S + sb * EB_S_TILE + (uint32_t)half * EB_S_BLOCK;
+                const uint32_t s_blk = sbase + EB_SMEM_S + buf * EB_S_TILE + (uint32_t)ch * EB_S_BLOCK + row_off;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint4 v;
-                    v.x = sgn2(r0[8 * c + 0], r0[8 * c + 1]);
-                    v.y = sgn2(r0[8 * c + 2], r0[8 * c + 3]);
-                    v.z = sgn2(r0[8 * c + 4], r0[8 * c + 5]);
-                    v.w = sgn2(r0[8 * c + 6], r0[8 * c + 7]);
-                    st_shared_v4(s_blk + sw128_chunk_offset((uint32_t)orow, (uint32_t)c), v);
-                }
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(lane_addr + buf * EB_TN + ch * 64 + h2 * 32, r);
+                    tmem_ld_wait();
+                    if (h2 == 1) {
+                        tc_fence_before_sync();
+                        mbar_arrive(smem_u32(&ctrl->phiEmpty[buf]));
+                    }
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint4 v;
-                    v.x = sgn2(r1[8 * c + 0], r1[8 * c + 1]);
-                    v.y = sgn2(r1[8 * c + 2], r1[8 * c + 3]);
-                    v.z = sgn2(r1[8 * c + 4], r1[8 * c + 5]);
-                    v.w = sgn2(r1[8 * c + 6], r1[8 * c + 7]);
-                    st_shared_v4(s_blk + sw128_chunk_offset((uint32_t)orow, (uint32_t)(4 + c)), v);
+                    for (int c = 0; c < 4; ++c)
+                        st_shared_v4(s_blk + (((uint32_t)(4 * h2 + c) ^ x7) << 4),
+                                     make_uint4(sgn2(r[8 * c], r[8 * c + 1]), sgn2(r[8 * c + 2], r[8 * c + 3]),
+                                                sgn2(r[8 * c + 4], r[8 * c + 5]), sgn2(r[8 * c + 6], r[8 * c + 7])));
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->sFull[sb]));
+                mbar_arrive(smem_u32(&ctrl->sFull[buf]));
             }
+            job += (uint32_t)units;
             if (!ok) break;
-            // the item's parameter-gradient sums: this thread writes features 2 half, 2 half + 1
+            // the item's parameter-gradient sums: this thread writes output tile `half`, features 2 ch, 2 ch + 1
             if (!mbar_wait(smem_u32(&ctrl->gFull), n_item & 1u, abort_flag)) break;
             tc_fence_after_sync();
             float* slab = slabs + (size_t)sp * ((size_t)O * I * 9);
-            for (int j = 0; j < n_ot; ++j) {
+            for (int j = half; j < n_ot; j += 2) {
                 const int o = j * EDGE_OT + orow;
 #pragma unroll
                 for (int qq = 0; qq < 2; ++qq) {
-                    const int q = 2 * half + qq, f = fq * EDGE_FQ + q;
+                    const int q = 2 * ch + qq, f = fq * EDGE_FQ + q;
                     uint32_t r[16];
                     tmem_ld_32x16(lane_addr + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 16, r);
                     tmem_ld_wait();
@@ -708,21 +709,6 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                                 if (f0 + q < I) xv[q] = __ldg(xr + q);
                         }
                     }
-                    float dcoef[EDGE_FQ][9];
-#pragma unroll
-                    for (int q = 0; q < EDGE_FQ; ++q) {
-                        const int f = f0 + q;
-                        const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
-                        float d[4];
-                        const int s0 = shared_grid ? eval_feature_deriv<true, false>(stab, ti, xv[q], d)
-                                                   : eval_feature_deriv<false, false>(ft, ti, xv[q], d);
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const int jj = c - s0;
-                            dcoef[q][c] = jj == 0 ? d[0] : (jj == 1 ? d[1] : (jj == 2 ? d[2] : (jj == 3 ? d[3] : 0.f)));
-                        }
-                        dcoef[q][8] = has_base ? silu_grad_fast(xv[q]) : 0.f;
-                    }
                     if (!mbar_wait(smem_u32(&ctrl->d3Full[tb]), (it >> 1) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -731,12 +717,21 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     float g[EDGE_FQ];
 #pragma unroll
                     for (int q = 0; q < EDGE_FQ; ++q) {
+                        const int f = f0 + q;
+                        const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
+                        float d[4];
+                        const int s0 = shared_grid ? eval_feature_deriv<true, false>(stab, ti, xv[q], d)
+                                                   : eval_feature_deriv<false, false>(ft, ti, xv[q], d);
                         uint32_t r[16];
                         tmem_ld_32x16(lane_addr + EB_TMEM_D3 + tb * 64 + (uint32_t)q * 16, r);
                         tmem_ld_wait();
-                        float acc = 0.f;
+                        float acc = has_base ? __uint_as_float(r[8]) * silu_grad_fast(xv[q]) : 0.f;
 #pragma unroll
-                        for (int c = 0; c < 9; ++c) acc = fmaf(__uint_as_float(r[c]), dcoef[q][c], acc);
+                        for (int c = 0; c < 8; ++c) {
+                            const int jj = c - s0;
+                            const float dc = jj == 0 ? d[0] : (jj == 1 ? d[1] : (jj == 2 ? d[2] : (jj == 3 ? d[3] : 0.f)));
+                            acc = fmaf(__uint_as_float(r[c]), dc, acc);
+                        }
                         g[q] = acc;
                     }
                     tc_fence_before_sync();
@@ -887,7 +882,10 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
 }
 
 // dW[o,i,r] = sum over the sample ranges of slab[.][o][i][r], dbw[o,i] the same of slot 8.
-__global__ void edge_bwd_finalize_kernel(const float* __restrict__ slabs, int splits, float* __restrict__ dW,
+// An edge whose coefficients and base weight are all zero has phi == 0 for every sample, hence
+// sign(phi) == 0 and zero gradients (the kernel above counts an exact zero as +1).
+__global__ void edge_bwd_finalize_kernel(const float* __restrict__ slabs, int splits, const float* __restrict__ W,
+                                         const float* __restrict__ bw, float* __restrict__ dW,
                                          float* __restrict__ dbw, int64_t pairs, int R) {
     const int64_t total = pairs * 9;
     for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
@@ -896,8 +894,11 @@ __global__ void edge_bwd_finalize_kernel(const float* __restrict__ slabs, int sp
         const int c = (int)(e - oi * 9);
         const bool wanted = c < R ? dW != nullptr : (c == 8 && dbw != nullptr);
         if (!wanted) continue;
+        bool live = bw != nullptr && bw[oi] != 0.0f;
+        for (int r = 0; r < R && !live; ++r) live = W[oi * R + r] != 0.0f;
         float v = 0.f;
-        for (int s = 0; s < splits; ++s) v += slabs[(size_t)s * total + e];
+        if (live)
+            for (int s = 0; s < splits; ++s) v += slabs[(size_t)s * total + e];
         if (c < R) dW[oi * R + c] = v;
         else dbw[oi] = v;
     }
@@ -1037,7 +1038,7 @@ cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid,
         const int64_t total = (int64_t)s.O * s.I * 9;
         const int fblocks = (int)((total + 255) / 256 < (int64_t)sm_count() * 8 ? (total + 255) / 256
                                                                                 : (int64_t)sm_count() * 8);
-        edge_bwd_finalize_kernel<<<fblocks, 256, 0, st>>>(slabs, p.splits, dW, bw ? dbw : nullptr, (int64_t)s.O * s.I,
+        edge_bwd_finalize_kernel<<<fblocks, 256, 0, st>>>(slabs, p.splits, W, bw, dW, bw ? dbw : nullptr, (int64_t)s.O * s.I,
                                                           s.R());
         e = cudaGetLastError();
     }
