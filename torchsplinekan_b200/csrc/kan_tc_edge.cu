@@ -418,29 +418,35 @@ EdgePlanTc plan_edge_tc(int64_t N, int I, int O) {
 // ===========================================================================================
 // Backward of the edge statistic on the tensor cores.
 //
-// With phi_i[o, n] as above and S_i = sign(phi_i) (exact in bf16: -1, 0, +1),
+// With phi_i[o, n] as above and S_i = sign(phi_i) (exact in bf16: -1, +1),
 //     dW[o,i,r']  = (ga[o,i] / N) sum_n S_i[o,n] A_i[n,r']          r' = 8 spline slots | base value
 //     gx[n,i]     = sum_r' dA_i[n,r'] sum_o S_i[o,n] (ga[o,i] / N) W[o,i,r']
 // are two more small products per feature, chained behind the first through shared memory:
 //     GEMM1  phi [o 128, n 128] = Wop [o,16] Aop[n,16]^T            three terms (hi/lo split of both)
-//     sign   8 warps read phi from tensor memory and write S as a bf16 tile [o][n]
-//     GEMM2  G   [o 128, r' 16] += S[o, n] Aop[n, r']               S K-major, the SAME sample tile read
-//                                                                   MN-major, 16 columns at 32 q bytes
-//     GEMM3  D3  [n 128, r' 16] += S^T[n, o] Wg[o, r']              the S tile read MN-major, Wg = ga W / N
+//     sign   16 warps read phi from tensor memory and write S as a bf16 tile [o][n]
+//     GEMM2  G   [o 128, 32]    += S[o, n] [A_hi | A_lo][n, 32]     S K-major; the SAME sample tile read
+//                                                                   MN-major, 32 columns per feature
+//     GEMM3  D3  [n 128, 32]    += S^T[n, o] [Wg_hi | Wg_lo][o, 32] the S tile read MN-major, Wg = ga W / N
+// An MMA instruction costs its issuing thread about 64 cycles however few columns it has (measured,
+// kanb200_selftest_umma_rate), so the hi and lo parts of an operand sit side by side in the
+// 128-byte rows (a row = 2 features x [16 hi | 16 lo]) and one N = 32 instruction serves both; the
+// epilogues add the two halves.  GEMM1 / GEMM2 and GEMM3 are issued by two different threads.
 // G stays in tensor memory over all sample tiles of a work item (at most 8 tiles = 1024 samples per
 // accumulation chain), D3 over the output tiles of one sample tile.  At the end of an item the sign
 // warps scale G into per-split slabs; per sample tile four more warps contract D3 with the basis
 // derivatives of x (from the polynomial table) into gx.  Nothing of size [N, O, I] or [N, I, R] is
 // ever stored.  Up to 256 outputs (both output tiles in one item, so gx needs no second pass).
+// Tensor memory: phi 128 columns, G 2 x 4 x 32, D3 4 x 32.
 // ===========================================================================================
 constexpr int EB_TN = 128;                                        // samples per tile
 constexpr int EB_PRODUCER_WARPS = 4, EB_SIGN_WARPS = 16, EB_GX_WARPS = 4;
 constexpr int EB_PRODUCERS = EB_PRODUCER_WARPS * 32, EB_SIGNERS = EB_SIGN_WARPS * 32, EB_GXERS = EB_GX_WARPS * 32;
-constexpr int EB_MMA_WARP = EB_PRODUCER_WARPS + EB_SIGN_WARPS + EB_GX_WARPS;
-constexpr int EB_THREADS = (EB_MMA_WARP + 2) * 32;
+constexpr int EB_MMA_WARP = EB_PRODUCER_WARPS + EB_SIGN_WARPS + EB_GX_WARPS;      // GEMM1, GEMM2
+constexpr int EB_MMA3_WARP = EB_MMA_WARP + 1;                                     // GEMM3
+constexpr int EB_THREADS = (EB_MMA_WARP + 3) * 32;
 constexpr int EB_MAX_CHAIN_TILES = 8;
-constexpr uint32_t EB_A_TILE = EB_TN * 128;                       // 16 KB
-constexpr uint32_t EB_A_STAGE = 2 * EB_A_TILE;
+constexpr uint32_t EB_A_TILE = EB_TN * 128;                       // 16 KB: 128 samples x 2 features x [hi | lo]
+constexpr uint32_t EB_A_STAGE = 2 * EB_A_TILE;                    // features 0-1, features 2-3
 constexpr uint32_t EB_S_BLOCK = EDGE_OT * 128;                    // 16 KB: 128 outputs x 64 samples
 constexpr uint32_t EB_S_TILE = 2 * EB_S_BLOCK;                    // 32 KB: 128 outputs x 128 samples
 constexpr uint32_t EB_SMEM_A = 0;                                 // one stage: the producers refill it at tile ends
@@ -450,15 +456,17 @@ constexpr uint32_t EB_SMEM_WG = EB_SMEM_W + EDGE_MAX_OTILES * EDGE_W_SLOT;
 constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WG + EDGE_MAX_OTILES * EDGE_W_SLOT;
 constexpr uint32_t EB_SMEM_BYTES = EB_SMEM_CTRL + 256 + TAB_SMEM_FLOATS * 4;
 static_assert(EB_SMEM_BYTES <= 232448, "edge backward kernel shared memory exceeds 227 KB");
-constexpr uint32_t EB_TMEM_G = 256, EB_TMEM_D3 = 384;
+constexpr uint32_t EB_TMEM_G = 128, EB_TMEM_D3 = 384;
 
 struct EdgeBwdCtrl {
     uint64_t fullA, emptyA;
     uint64_t fullW, emptyW;
-    uint64_t phiFull[2], phiEmpty[2];
+    uint64_t phiFull[2], phiEmpty;        // one accumulator; a 'full' barrier per sign group (a group
+                                          // that polled every other phase of a shared one would see the
+                                          // phase before its own as complete)
     uint64_t sFull[2], sEmpty[2];
     uint64_t gFull, gEmpty;
-    uint64_t d3Full[2], d3Empty[2];
+    uint64_t d3Full, d3Empty;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -469,6 +477,46 @@ struct EdgeBwdPlan {
     int64_t tiles_total, tiles_per_split;
     __host__ __device__ int64_t n_items() const { return (int64_t)n_quads * splits; }
 };
+
+// Weight-side operand image of the backward kernel: per (output tile of 128, group of 4 features) two
+// tiles of 16 KB (features 0-1, features 2-3), rows of 128 B = 2 features x [hi: 8 spline slots,
+// base weight, 7 zeros | lo: the same], 128-byte-swizzled.  edge_scale (ga) and scale (1 / N), when
+// given, are folded in (the operand of GEMM3).
+__global__ void pack_edge_weights_pairs_kernel(const float* __restrict__ W, const float* __restrict__ bw,
+                                               const float* __restrict__ edge_scale, float scale,
+                                               uint8_t* __restrict__ img, int O, int I, int R, int n_quads,
+                                               int n_otiles) {
+    const int64_t units = (int64_t)n_otiles * n_quads * EDGE_OT * EDGE_FQ;      // (tile, group, row, feature)
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < units;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int q = (int)(idx & 3);
+        int64_t rest = idx >> 2;
+        const int rr = (int)(rest % EDGE_OT);
+        rest /= EDGE_OT;
+        const int fq = (int)(rest % n_quads);
+        const int ot = (int)(rest / n_quads);
+        const int o = ot * EDGE_OT + rr, f = fq * EDGE_FQ + q;
+        float w[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float b = 0.f;
+        if (o < O && f < I) {
+            const size_t oi = (size_t)o * I + f;
+            const float sc = edge_scale ? edge_scale[oi] * scale : 1.0f;
+            for (int e = 0; e < 8; ++e)
+                if (e < R) w[e] = W[oi * R + e] * sc;
+            if (bw) b = bw[oi] * sc;
+        }
+        uint32_t h[4], l[4], bh, bl;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split2(w[2 * e], w[2 * e + 1], h[e], l[e]);
+        split2(b, 0.0f, bh, bl);
+        uint8_t* tile = img + ((size_t)ot * n_quads + fq) * (size_t)EDGE_W_SLOT + (size_t)(q >> 1) * EDGE_W_TILE;
+        const uint32_t c0 = (uint32_t)(4 * (q & 1));
+        *reinterpret_cast<uint4*>(tile + sw128_chunk_offset((uint32_t)rr, c0)) = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(tile + sw128_chunk_offset((uint32_t)rr, c0 + 1)) = make_uint4(bh, 0, 0, 0);
+        *reinterpret_cast<uint4*>(tile + sw128_chunk_offset((uint32_t)rr, c0 + 2)) = make_uint4(l[0], l[1], l[2], l[3]);
+        *reinterpret_cast<uint4*>(tile + sw128_chunk_offset((uint32_t)rr, c0 + 3)) = make_uint4(bl, 0, 0, 0);
+    }
+}
 
 __global__ void __launch_bounds__(EB_THREADS, 1)
 tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
@@ -490,18 +538,20 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         return;
     }
     if (threadIdx.x == 0) {
+        const uint32_t issuers = need_gx ? 2u : 1u;                      // threads whose MMAs read S and W
         for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&ctrl->phiFull[s]), 1);
-            mbar_init(smem_u32(&ctrl->phiEmpty[s]), EB_SIGNERS / 2);      // one group of sign warps each
-            mbar_init(smem_u32(&ctrl->sFull[s]), EB_SIGNERS / 2);
-            mbar_init(smem_u32(&ctrl->sEmpty[s]), 1);
-            mbar_init(smem_u32(&ctrl->d3Full[s]), 1);
-            mbar_init(smem_u32(&ctrl->d3Empty[s]), EB_GXERS);
+            mbar_init(smem_u32(&ctrl->sFull[s]), EB_SIGNERS / 2);      // one group of sign warps each
+            mbar_init(smem_u32(&ctrl->sEmpty[s]), issuers);
         }
+        mbar_init(smem_u32(&ctrl->phiFull[0]), 1);
+        mbar_init(smem_u32(&ctrl->phiFull[1]), 1);
+        mbar_init(smem_u32(&ctrl->phiEmpty), EB_SIGNERS / 2);
+        mbar_init(smem_u32(&ctrl->d3Full), 1);
+        mbar_init(smem_u32(&ctrl->d3Empty), EB_GXERS);
         mbar_init(smem_u32(&ctrl->fullA), EB_PRODUCERS);
         mbar_init(smem_u32(&ctrl->emptyA), 1);
         mbar_init(smem_u32(&ctrl->fullW), 1);
-        mbar_init(smem_u32(&ctrl->emptyW), 1);
+        mbar_init(smem_u32(&ctrl->emptyW), issuers);
         mbar_init(smem_u32(&ctrl->gFull), 1);
         mbar_init(smem_u32(&ctrl->gEmpty), EB_SIGNERS);
         ctrl->abort_flag = 0;
@@ -528,6 +578,10 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         t1 = t0 + plan.tiles_per_split;
         if (t1 > plan.tiles_total) t1 = plan.tiles_total;
     };
+    // shared-memory address of feature q's [hi | lo] columns inside a tile pair that starts at `base`
+    auto pair_addr = [](uint32_t base, uint32_t tile_bytes, int q) -> uint32_t {
+        return base + (uint32_t)(q >> 1) * tile_bytes + (uint32_t)(q & 1) * 64u;
+    };
 
     if (warp < EB_PRODUCER_WARPS) {
         // ===== producers: thread = one sample row, its four features in two passes =====
@@ -540,58 +594,55 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             int64_t t0, t1;
             tile_range(sp, t0, t1);
             for (int64_t t = t0; t < t1; ++t, ++it) {
-                const uint32_t a_hi = sbase + EB_SMEM_A;
-                const uint32_t a_lo = a_hi + EB_A_TILE;
                 const int64_t n = t * EB_TN + row;
                 const bool row_ok = n < N;
                 bool waited = false;
 #pragma unroll 1
                 for (int pr = 0; pr < 2; ++pr) {
-                const int f0 = fq * EDGE_FQ + 2 * pr;
-                float xv[2] = {0.f, 0.f};
-                if (row_ok) {
-                    const float* xr = x + (size_t)n * I + f0;
-                    if (vec_x && f0 + 2 <= I) {
-                        const float2 v = __ldg(reinterpret_cast<const float2*>(xr));
-                        xv[0] = v.x; xv[1] = v.y;
-                    } else {
+                    const uint32_t a_tile = sbase + EB_SMEM_A + (uint32_t)pr * EB_A_TILE;
+                    const int f0 = fq * EDGE_FQ + 2 * pr;
+                    float xv[2] = {0.f, 0.f};
+                    if (row_ok) {
+                        const float* xr = x + (size_t)n * I + f0;
+                        if (vec_x && f0 + 2 <= I) {
+                            const float2 v = __ldg(reinterpret_cast<const float2*>(xr));
+                            xv[0] = v.x; xv[1] = v.y;
+                        } else {
 #pragma unroll
-                        for (int q = 0; q < 2; ++q)
-                            if (f0 + q < I) xv[q] = __ldg(xr + q);
+                            for (int q = 0; q < 2; ++q)
+                                if (f0 + q < I) xv[q] = __ldg(xr + q);
+                        }
                     }
-                }
-                uint4 hi[2], lo[2];
-                uint32_t bh[2], bl[2];
+                    uint4 hi[2], lo[2];
+                    uint32_t bh[2], bl[2];
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int f = f0 + q;
-                    const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
-                    const Window w = shared_grid ? eval_window<true, true, false>(stab, ti, xv[q])
-                                                 : eval_window<true, false, false>(ft, ti, xv[q]);
-                    place_window<true>(w, 0, hi[q], lo[q]);
-                    float sv = has_base ? silu_fast(xv[q]) : 0.f;
-                    if (!(row_ok && f < I)) {
-                        hi[q] = make_uint4(0, 0, 0, 0);
-                        lo[q] = hi[q];
-                        sv = 0.f;
+                    for (int q = 0; q < 2; ++q) {
+                        const int f = f0 + q;
+                        const float* ft = tab + (size_t)(f < I ? f : I - 1) * ti.fs;
+                        const Window w = shared_grid ? eval_window<true, true, false>(stab, ti, xv[q])
+                                                     : eval_window<true, false, false>(ft, ti, xv[q]);
+                        place_window<true>(w, 0, hi[q], lo[q]);
+                        float sv = has_base ? silu_fast(xv[q]) : 0.f;
+                        if (!(row_ok && f < I)) {
+                            hi[q] = make_uint4(0, 0, 0, 0);
+                            lo[q] = hi[q];
+                            sv = 0.f;
+                        }
+                        split2(sv, 0.0f, bh[q], bl[q]);
                     }
-                    split2(sv, 0.0f, bh[q], bl[q]);
-                }
-                if (!waited && !mbar_wait(smem_u32(&ctrl->emptyA), (it & 1u) ^ 1u, abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                waited = true;
+                    if (!waited && !mbar_wait(smem_u32(&ctrl->emptyA), (it & 1u) ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    waited = true;
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const uint32_t c0 = (uint32_t)(2 * (2 * pr + q));
-                    const uint32_t off0 = sw128_chunk_offset((uint32_t)row, c0);
-                    const uint32_t off1 = sw128_chunk_offset((uint32_t)row, c0 + 1);
-                    st_shared_v4(a_hi + off0, hi[q]);
-                    st_shared_v4(a_hi + off1, make_uint4(bh[q], 0, 0, 0));
-                    st_shared_v4(a_lo + off0, lo[q]);
-                    st_shared_v4(a_lo + off1, make_uint4(bl[q], 0, 0, 0));
-                }
+                    for (int q = 0; q < 2; ++q) {
+                        const uint32_t c0 = (uint32_t)(4 * q);
+                        st_shared_v4(a_tile + sw128_chunk_offset((uint32_t)row, c0), hi[q]);
+                        st_shared_v4(a_tile + sw128_chunk_offset((uint32_t)row, c0 + 1), make_uint4(bh[q], 0, 0, 0));
+                        st_shared_v4(a_tile + sw128_chunk_offset((uint32_t)row, c0 + 2), lo[q]);
+                        st_shared_v4(a_tile + sw128_chunk_offset((uint32_t)row, c0 + 3), make_uint4(bl[q], 0, 0, 0));
+                    }
                 }
                 if (!ok) break;
                 fence_proxy_async_smem();
@@ -599,11 +650,11 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             }
         }
     } else if (warp < EB_PRODUCER_WARPS + EB_SIGN_WARPS) {
-        // ===== sign warps: two groups of eight; group g converts the units with job parity g (accumulator
-        // g -> sign tile g), so two conversions are in flight; thread = one output row, 64 samples.
-        // sign(phi) as bf16 is the float's sign bit over the pattern of 1.0 (0x3F80); an exact zero
-        // counts as +1, which only matters for edges whose weights are all zero (the finalize kernel
-        // writes their gradients as zero, and their scaled weights contribute nothing to gx) =====
+        // ===== sign warps: two groups of eight; group g converts the units with job parity g into sign
+        // tile g, so one conversion overlaps the products that read the other tile; thread = one output
+        // row, 64 samples.  sign(phi) as bf16 is the float's sign bit over the pattern of 1.0 (0x3F80);
+        // an exact zero counts as +1, which only matters for edges whose weights are all zero (the
+        // finalize kernel writes their gradients as zero, and their scaled weights add nothing to gx) =====
         const int e = warp - EB_PRODUCER_WARPS;            // 0 .. 15
         const int quad = warp & 3;
         const int half = e >> 3;                           // the group
@@ -625,25 +676,25 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             const int64_t units = (t1 - t0) * n_ot * EDGE_FQ;          // a multiple of 4: job stays even at item starts
             for (int64_t u = half; u < units && ok; u += 2) {
                 const uint32_t jb = job + (uint32_t)u;
-                const uint32_t buf = (uint32_t)half;                    // == jb & 1
-                if (!mbar_wait(smem_u32(&ctrl->phiFull[buf]), (jb >> 1) & 1u, abort_flag)) {
+                const uint32_t sb = (uint32_t)half;                     // == jb & 1
+                if (!mbar_wait(smem_u32(&ctrl->phiFull[sb]), (jb >> 1) & 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
-                if (!mbar_wait(smem_u32(&ctrl->sEmpty[buf]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) {
+                if (!mbar_wait(smem_u32(&ctrl->sEmpty[sb]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t s_blk = sbase + EB_SMEM_S + buf * EB_S_TILE + (uint32_t)ch * EB_S_BLOCK + row_off;
+                const uint32_t s_blk = sbase + EB_SMEM_S + sb * EB_S_TILE + (uint32_t)ch * EB_S_BLOCK + row_off;
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2) {
                     uint32_t r[32];
-                    tmem_ld_32x32(lane_addr + buf * EB_TN + ch * 64 + h2 * 32, r);
+                    tmem_ld_32x32(lane_addr + ch * 64 + h2 * 32, r);
                     tmem_ld_wait();
                     if (h2 == 1) {
                         tc_fence_before_sync();
-                        mbar_arrive(smem_u32(&ctrl->phiEmpty[buf]));
+                        mbar_arrive(smem_u32(&ctrl->phiEmpty));
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -652,7 +703,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                                                 sgn2(r[8 * c + 4], r[8 * c + 5]), sgn2(r[8 * c + 6], r[8 * c + 7])));
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->sFull[buf]));
+                mbar_arrive(smem_u32(&ctrl->sFull[sb]));
             }
             job += (uint32_t)units;
             if (!ok) break;
@@ -665,14 +716,14 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
 #pragma unroll
                 for (int qq = 0; qq < 2; ++qq) {
                     const int q = 2 * ch + qq, f = fq * EDGE_FQ + q;
-                    uint32_t r[16];
-                    tmem_ld_32x16(lane_addr + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 16, r);
+                    uint32_t r[32];
+                    tmem_ld_32x32(lane_addr + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 32, r);
                     tmem_ld_wait();
                     if (o < O && f < I) {
                         const float sc = __ldg(ga + (size_t)o * I + f) * inv_n;
                         float* out = slab + ((size_t)o * I + f) * 9;
 #pragma unroll
-                        for (int c = 0; c < 9; ++c) out[c] = sc * __uint_as_float(r[c]);
+                        for (int c = 0; c < 9; ++c) out[c] = sc * (__uint_as_float(r[c]) + __uint_as_float(r[16 + c]));
                     }
                 }
             }
@@ -694,7 +745,6 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 tile_range(sp, t0, t1);
                 const int f0 = fq * EDGE_FQ;
                 for (int64_t t = t0; t < t1; ++t, ++it) {
-                    const uint32_t tb = it & 1u;
                     const int64_t n = t * EB_TN + row;
                     const bool row_ok = n < N;
                     float xv[EDGE_FQ] = {0.f, 0.f, 0.f, 0.f};
@@ -709,7 +759,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                                 if (f0 + q < I) xv[q] = __ldg(xr + q);
                         }
                     }
-                    if (!mbar_wait(smem_u32(&ctrl->d3Full[tb]), (it >> 1) & 1u, abort_flag)) {
+                    if (!mbar_wait(smem_u32(&ctrl->d3Full), it & 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
@@ -722,20 +772,20 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                         float d[4];
                         const int s0 = shared_grid ? eval_feature_deriv<true, false>(stab, ti, xv[q], d)
                                                    : eval_feature_deriv<false, false>(ft, ti, xv[q], d);
-                        uint32_t r[16];
-                        tmem_ld_32x16(lane_addr + EB_TMEM_D3 + tb * 64 + (uint32_t)q * 16, r);
+                        uint32_t r[32];
+                        tmem_ld_32x32(lane_addr + EB_TMEM_D3 + (uint32_t)q * 32, r);
                         tmem_ld_wait();
-                        float acc = has_base ? __uint_as_float(r[8]) * silu_grad_fast(xv[q]) : 0.f;
+                        float acc = has_base ? (__uint_as_float(r[8]) + __uint_as_float(r[24])) * silu_grad_fast(xv[q]) : 0.f;
 #pragma unroll
                         for (int c = 0; c < 8; ++c) {
                             const int jj = c - s0;
                             const float dc = jj == 0 ? d[0] : (jj == 1 ? d[1] : (jj == 2 ? d[2] : (jj == 3 ? d[3] : 0.f)));
-                            acc = fmaf(__uint_as_float(r[c]), dc, acc);
+                            acc = fmaf(__uint_as_float(r[c]) + __uint_as_float(r[16 + c]), dc, acc);
                         }
                         g[q] = acc;
                     }
                     tc_fence_before_sync();
-                    mbar_arrive(smem_u32(&ctrl->d3Empty[tb]));
+                    mbar_arrive(smem_u32(&ctrl->d3Empty));
                     if (row_ok) {
                         float* out = gx + (size_t)n * I + f0;
                         if (vec_x && f0 + EDGE_FQ <= I && (I & 3) == 0) {
@@ -751,12 +801,11 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         }
     } else if (warp == EB_MMA_WARP) {
         if (lane == 0) {
+            // ===== issuer of GEMM1 and GEMM2 =====
             constexpr uint32_t idesc1 = make_idesc_bf16(EB_TN, false, false);
-            constexpr uint32_t idesc2 = make_idesc_bf16(16, false, true);
-            constexpr uint32_t idesc3 = make_idesc_bf16(16, true, true);
+            constexpr uint32_t idesc2 = make_idesc_bf16(32, false, true);
             constexpr uint64_t d_k = make_sdesc_sw128(16, 1024);          // K-major rows of 128 B
-            constexpr uint64_t d_mn16 = make_sdesc_sw128(8192, 1024);     // MN-major, one group of columns
-            constexpr uint64_t d_mnS = make_sdesc_sw128(EB_S_BLOCK, 1024);  // MN-major, two groups of 64 samples
+            constexpr uint64_t d_mn = make_sdesc_sw128(8192, 1024);       // MN-major, one group of columns
             uint32_t it = 0, job = 0, n_item = 0;
             bool ok = true;
             for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
@@ -767,31 +816,25 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 if (!mbar_wait(smem_u32(&ctrl->fullW), n_item & 1u, abort_flag)) break;
                 if (!mbar_wait(smem_u32(&ctrl->gEmpty), (n_item & 1u) ^ 1u, abort_flag)) break;
                 tc_fence_after_sync();
-                const uint32_t a_hi = sbase + EB_SMEM_A, a_lo = a_hi + EB_A_TILE;
                 auto stage_ready = [&](uint32_t tile_it) -> bool {
                     if (!mbar_wait(smem_u32(&ctrl->fullA), tile_it & 1u, abort_flag)) return false;
-                    if (need_gx &&
-                        !mbar_wait(smem_u32(&ctrl->d3Empty[tile_it & 1u]), ((tile_it >> 1) & 1u) ^ 1u, abort_flag))
-                        return false;
                     tc_fence_after_sync();
                     return true;
                 };
                 auto gemm1 = [&](int j, int q, uint32_t jb) -> bool {
-                    const uint32_t buf = jb & 1u;
-                    if (!mbar_wait(smem_u32(&ctrl->phiEmpty[buf]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) return false;
+                    if (!mbar_wait(smem_u32(&ctrl->phiEmpty), (jb & 1u) ^ 1u, abort_flag)) return false;
                     tc_fence_after_sync();
-                    const uint32_t w_hi = sbase + EB_SMEM_W + j * EDGE_W_SLOT + q * 32;
-                    const uint64_t dw_hi = sdesc_at(d_k, w_hi), dw_lo = sdesc_at(d_k, w_hi + EDGE_W_TILE);
-                    const uint64_t da_hi = sdesc_at(d_k, a_hi + q * 32), da_lo = sdesc_at(d_k, a_lo + q * 32);
-                    const uint32_t d = tmem_base + buf * EB_TN;
-                    mma_f16_ss(d, dw_hi, da_hi, idesc1, 0u);
-                    mma_f16_ss(d, dw_lo, da_hi, idesc1, 1u);
-                    mma_f16_ss(d, dw_hi, da_lo, idesc1, 1u);
-                    mma_commit(smem_u32(&ctrl->phiFull[buf]));
+                    const uint32_t w = pair_addr(sbase + EB_SMEM_W + j * EDGE_W_SLOT, EDGE_W_TILE, q);
+                    const uint32_t a = pair_addr(sbase + EB_SMEM_A, EB_A_TILE, q);
+                    const uint64_t dw_hi = sdesc_at(d_k, w), da_hi = sdesc_at(d_k, a);
+                    mma_f16_ss(tmem_base, dw_hi, da_hi, idesc1, 0u);
+                    mma_f16_ss(tmem_base, dw_hi + 2u, da_hi, idesc1, 1u);          // lo part: 32 bytes on
+                    mma_f16_ss(tmem_base, dw_hi, da_hi + 2u, idesc1, 1u);
+                    mma_commit(smem_u32(&ctrl->phiFull[jb & 1u]));
                     return true;
                 };
                 // units of the item in order (tile, output tile, feature); within a tile GEMM1 runs one
-                // unit ahead of the two products that consume the sign tile
+                // unit ahead of the products that consume the sign tile
                 int64_t t = t0;
                 int j = 0, q = 0;
                 uint32_t cur_it = it;
@@ -802,41 +845,26 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     if (nq == EDGE_FQ) { nq = 0; ++nj; }
                     if (nj == n_ot) { nj = 0; ++nt; }
                     const bool has_next = nt < t1, same_tile = nt == t;
-                    if (has_next && same_tile && !gemm1(nj, nq, job + 1)) { ok = false; break; }
                     const uint32_t sb = job & 1u;
                     if (!mbar_wait(smem_u32(&ctrl->sFull[sb]), (job >> 1) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
-                    {   // GEMM2: G[j][q] (+)= S[o, n] A[n, r']; descriptor addresses advance in 16-byte units
-                        const uint32_t d = tmem_base + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 16;
+                    // the sign warps have read phi(job): the next unit's phi may overwrite it
+                    if (has_next && same_tile && !gemm1(nj, nq, job + 1)) { ok = false; break; }
+                    {   // GEMM2: G[j][q] (+)= S[o, n] [A_hi | A_lo][n, 32]; addresses advance in 16-byte units
+                        const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
+                        const uint32_t d = tmem_base + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 32;
                         const uint64_t ds0 = sdesc_at(d_k, s_t), ds1 = sdesc_at(d_k, s_t + EB_S_BLOCK);
-                        const uint64_t dh = sdesc_at(d_mn16, a_hi + q * 32), dl = sdesc_at(d_mn16, a_lo + q * 32);
+                        const uint64_t db = sdesc_at(d_mn, pair_addr(sbase + EB_SMEM_A, EB_A_TILE, q));
                         const uint32_t first = t > t0 ? 1u : 0u;
 #pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            const uint64_t sa = (ks < 4 ? ds0 : ds1) + (uint64_t)((ks & 3) * 2);
-                            mma_f16_ss(d, sa, dh + (uint64_t)(ks * 128), idesc2, ks == 0 ? first : 1u);
-                            mma_f16_ss(d, sa, dl + (uint64_t)(ks * 128), idesc2, 1u);
-                        }
-                    }
-                    if (need_gx) {   // GEMM3: D3[q] (+)= S^T[n, o] Wg[o, r']
-                        const uint32_t wg_hi = sbase + EB_SMEM_WG + j * EDGE_W_SLOT + q * 32;
-                        const uint32_t d = tmem_base + EB_TMEM_D3 + (cur_it & 1u) * 64 + (uint32_t)q * 16;
-                        const uint64_t dsT = sdesc_at(d_mnS, s_t);
-                        const uint64_t dh = sdesc_at(d_mn16, wg_hi), dl = sdesc_at(d_mn16, wg_hi + EDGE_W_TILE);
-                        const uint32_t first = j > 0 ? 1u : 0u;
-#pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            mma_f16_ss(d, dsT + (uint64_t)(ks * 128), dh + (uint64_t)(ks * 128), idesc3,
+                        for (int ks = 0; ks < 8; ++ks)
+                            mma_f16_ss(d, (ks < 4 ? ds0 : ds1) + (uint64_t)((ks & 3) * 2), db + (uint64_t)(ks * 128), idesc2,
                                        ks == 0 ? first : 1u);
-                            mma_f16_ss(d, dsT + (uint64_t)(ks * 128), dl + (uint64_t)(ks * 128), idesc3, 1u);
-                        }
                     }
                     mma_commit(smem_u32(&ctrl->sEmpty[sb]));
                     ++job;
                     if (!has_next || !same_tile) {
                         mma_commit(smem_u32(&ctrl->emptyA));
-                        if (need_gx) mma_commit(smem_u32(&ctrl->d3Full[cur_it & 1u]));
                         if (!has_next) break;
                         ++cur_it;
                         if (!stage_ready(cur_it) || !gemm1(nj, nq, job)) { ok = false; break; }
@@ -846,6 +874,47 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 if (!ok) break;
                 it = cur_it + 1;
                 mma_commit(smem_u32(&ctrl->gFull));
+                mma_commit(smem_u32(&ctrl->emptyW));
+            }
+        }
+    } else if (warp == EB_MMA3_WARP) {
+        if (lane == 0 && need_gx) {
+            // ===== issuer of GEMM3: D3[q] (+)= S^T[n, o] [Wg_hi | Wg_lo][o, 32] =====
+            constexpr uint32_t idesc3 = make_idesc_bf16(32, true, true);
+            constexpr uint64_t d_mn = make_sdesc_sw128(8192, 1024);
+            constexpr uint64_t d_mnS = make_sdesc_sw128(EB_S_BLOCK, 1024);  // MN-major, two groups of 64 samples
+            uint32_t it = 0, job = 0, n_item = 0;
+            bool ok = true;
+            for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
+                int sp, fq;
+                decode(item, sp, fq);
+                int64_t t0, t1;
+                tile_range(sp, t0, t1);
+                if (!mbar_wait(smem_u32(&ctrl->fullW), n_item & 1u, abort_flag)) break;
+                tc_fence_after_sync();
+                for (int64_t t = t0; t < t1 && ok; ++t, ++it) {
+                    if (!mbar_wait(smem_u32(&ctrl->d3Empty), (it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    for (int j = 0; j < n_ot && ok; ++j) {
+                        for (int q = 0; q < EDGE_FQ; ++q, ++job) {
+                            const uint32_t sb = job & 1u;
+                            if (!mbar_wait(smem_u32(&ctrl->sFull[sb]), (job >> 1) & 1u, abort_flag)) { ok = false; break; }
+                            tc_fence_after_sync();
+                            const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
+                            const uint32_t d = tmem_base + EB_TMEM_D3 + (uint32_t)q * 32;
+                            const uint64_t dsT = sdesc_at(d_mnS, s_t);
+                            const uint64_t db = sdesc_at(d_mn, pair_addr(sbase + EB_SMEM_WG + j * EDGE_W_SLOT, EDGE_W_TILE, q));
+                            const uint32_t first = j > 0 ? 1u : 0u;
+#pragma unroll
+                            for (int ks = 0; ks < 8; ++ks)
+                                mma_f16_ss(d, dsT + (uint64_t)(ks * 128), db + (uint64_t)(ks * 128), idesc3,
+                                           ks == 0 ? first : 1u);
+                            mma_commit(smem_u32(&ctrl->sEmpty[sb]));
+                        }
+                    }
+                    if (ok) mma_commit(smem_u32(&ctrl->d3Full));
+                }
+                if (!ok) break;
                 mma_commit(smem_u32(&ctrl->emptyW));
             }
         }
@@ -881,7 +950,6 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
     }
 }
 
-// dW[o,i,r] = sum over the sample ranges of slab[.][o][i][r], dbw[o,i] the same of slot 8.
 // An edge whose coefficients and base weight are all zero has phi == 0 for every sample, hence
 // sign(phi) == 0 and zero gradients (the kernel above counts an exact zero as +1).
 __global__ void edge_bwd_finalize_kernel(const float* __restrict__ slabs, int splits, const float* __restrict__ W,
@@ -1014,15 +1082,15 @@ cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid,
 
     cudaError_t e = tc_build_table(grid, tab, s, st);
     if (e != cudaSuccess) return e;
-    const int64_t chunks = (int64_t)p.n_otiles * p.n_quads * EDGE_OT * 8;
+    const int64_t chunks = (int64_t)p.n_otiles * p.n_quads * EDGE_OT * EDGE_FQ;
     const int pblocks = (int)((chunks + 255) / 256 < (int64_t)sm_count() * 16 ? (chunks + 255) / 256
                                                                               : (int64_t)sm_count() * 16);
-    pack_edge_weights_kernel<<<pblocks, 256, 0, st>>>(W, bw, nullptr, 1.0f, wimg, s.O, s.I, s.R(), p.n_quads,
-                                                      p.n_otiles);
+    pack_edge_weights_pairs_kernel<<<pblocks, 256, 0, st>>>(W, bw, nullptr, 1.0f, wimg, s.O, s.I, s.R(), p.n_quads,
+                                                            p.n_otiles);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     if (need_x) {
-        pack_edge_weights_kernel<<<pblocks, 256, 0, st>>>(W, bw, ga, 1.0f / (float)s.N, wgimg, s.O, s.I, s.R(),
-                                                          p.n_quads, p.n_otiles);
+        pack_edge_weights_pairs_kernel<<<pblocks, 256, 0, st>>>(W, bw, ga, 1.0f / (float)s.N, wgimg, s.O, s.I, s.R(),
+                                                                p.n_quads, p.n_otiles);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
     }
     const int vec_x = ((s.I & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
