@@ -435,8 +435,10 @@ EdgePlanTc plan_edge_tc(int64_t N, int I, int O) {
 // accumulation chain), D3 over the output tiles of one sample tile.  At the end of an item the sign
 // warps scale G into per-split slabs; per sample tile four more warps contract D3 with the basis
 // derivatives of x (from the polynomial table) into gx.  Nothing of size [N, O, I] or [N, I, R] is
-// ever stored.  Up to 256 outputs (both output tiles in one item, so gx needs no second pass).
-// Tensor memory: phi 128 columns, G 2 x 4 x 32, D3 4 x 32.
+// ever stored.  A work item = (range of samples, group of 4 features, tile of 128 outputs); with two
+// output tiles (129 .. 256 outputs) the two items of a sample tile each add their share to a
+// zero-filled gx (red.add of exactly two terms: the result does not depend on the order).
+// Tensor memory: phi 2 x 128 columns, G 4 x 32, D3 4 x 32.
 // ===========================================================================================
 constexpr int EB_TN = 128;                                        // samples per tile
 constexpr int EB_PRODUCER_WARPS = 4, EB_SIGN_WARPS = 16, EB_GX_WARPS = 4;
@@ -449,21 +451,19 @@ constexpr uint32_t EB_A_TILE = EB_TN * 128;                       // 16 KB: 128 
 constexpr uint32_t EB_A_STAGE = 2 * EB_A_TILE;                    // features 0-1, features 2-3
 constexpr uint32_t EB_S_BLOCK = EDGE_OT * 128;                    // 16 KB: 128 outputs x 64 samples
 constexpr uint32_t EB_S_TILE = 2 * EB_S_BLOCK;                    // 32 KB: 128 outputs x 128 samples
-constexpr uint32_t EB_SMEM_A = 0;                                 // one stage: the producers refill it at tile ends
-constexpr uint32_t EB_SMEM_S = EB_SMEM_A + EB_A_STAGE;            // two sign tiles: conversion runs one unit ahead
+constexpr uint32_t EB_SMEM_A = 0;                                 // two stages of the sample-side operand
+constexpr uint32_t EB_SMEM_S = EB_SMEM_A + 2 * EB_A_STAGE;        // two sign tiles: conversion runs one unit ahead
 constexpr uint32_t EB_SMEM_W = EB_SMEM_S + 2 * EB_S_TILE;
-constexpr uint32_t EB_SMEM_WG = EB_SMEM_W + EDGE_MAX_OTILES * EDGE_W_SLOT;
-constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WG + EDGE_MAX_OTILES * EDGE_W_SLOT;
+constexpr uint32_t EB_SMEM_WG = EB_SMEM_W + EDGE_W_SLOT;
+constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WG + EDGE_W_SLOT;
 constexpr uint32_t EB_SMEM_BYTES = EB_SMEM_CTRL + 256 + TAB_SMEM_FLOATS * 4;
 static_assert(EB_SMEM_BYTES <= 232448, "edge backward kernel shared memory exceeds 227 KB");
-constexpr uint32_t EB_TMEM_G = 128, EB_TMEM_D3 = 384;
+constexpr uint32_t EB_TMEM_G = 256, EB_TMEM_D3 = 384;
 
 struct EdgeBwdCtrl {
-    uint64_t fullA, emptyA;
+    uint64_t fullA[2], emptyA[2];
     uint64_t fullW, emptyW;
-    uint64_t phiFull[2], phiEmpty;        // one accumulator; a 'full' barrier per sign group (a group
-                                          // that polled every other phase of a shared one would see the
-                                          // phase before its own as complete)
+    uint64_t phiFull[2], phiEmpty[2];     // accumulator b, sign tile b and sign group b belong together
     uint64_t sFull[2], sEmpty[2];
     uint64_t gFull, gEmpty;
     uint64_t d3Full, d3Empty;
@@ -475,7 +475,7 @@ static_assert(sizeof(EdgeBwdCtrl) <= 256, "control block too large");
 struct EdgeBwdPlan {
     int n_quads, n_otiles, splits;
     int64_t tiles_total, tiles_per_split;
-    __host__ __device__ int64_t n_items() const { return (int64_t)n_quads * splits; }
+    __host__ __device__ int64_t n_items() const { return (int64_t)n_quads * n_otiles * splits; }
 };
 
 // Weight-side operand image of the backward kernel: per (output tile of 128, group of 4 features) two
@@ -542,14 +542,13 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&ctrl->sFull[s]), EB_SIGNERS / 2);      // one group of sign warps each
             mbar_init(smem_u32(&ctrl->sEmpty[s]), issuers);
+            mbar_init(smem_u32(&ctrl->phiFull[s]), 1);
+            mbar_init(smem_u32(&ctrl->phiEmpty[s]), EB_SIGNERS / 2);
+            mbar_init(smem_u32(&ctrl->fullA[s]), EB_PRODUCERS);
+            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
         }
-        mbar_init(smem_u32(&ctrl->phiFull[0]), 1);
-        mbar_init(smem_u32(&ctrl->phiFull[1]), 1);
-        mbar_init(smem_u32(&ctrl->phiEmpty), EB_SIGNERS / 2);
         mbar_init(smem_u32(&ctrl->d3Full), 1);
         mbar_init(smem_u32(&ctrl->d3Empty), EB_GXERS);
-        mbar_init(smem_u32(&ctrl->fullA), EB_PRODUCERS);
-        mbar_init(smem_u32(&ctrl->emptyA), 1);
         mbar_init(smem_u32(&ctrl->fullW), 1);
         mbar_init(smem_u32(&ctrl->emptyW), issuers);
         mbar_init(smem_u32(&ctrl->gFull), 1);
@@ -566,12 +565,18 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
     const int64_t n_items = plan.n_items();
-    const int n_ot = plan.n_otiles;                     // 1 or 2
+    const bool add_gx = plan.n_otiles > 1;              // two items contribute to every gx entry
 
-    // item -> (sample range, feature group); consecutive items share the samples
-    auto decode = [&](int64_t item, int& sp, int& fq) {
+    // item -> (sample range, output tile, feature group); consecutive items share the samples
+    auto decode3 = [&](int64_t item, int& sp, int& ot, int& fq) {
         fq = (int)(item % plan.n_quads);
-        sp = (int)(item / plan.n_quads);
+        const int64_t rest = item / plan.n_quads;
+        ot = (int)(rest % plan.n_otiles);
+        sp = (int)(rest / plan.n_otiles);
+    };
+    auto decode = [&](int64_t item, int& sp, int& fq) {
+        int ot;
+        decode3(item, sp, ot, fq);
     };
     auto tile_range = [&](int sp, int64_t& t0, int64_t& t1) {
         t0 = (int64_t)sp * plan.tiles_per_split;
@@ -599,7 +604,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 bool waited = false;
 #pragma unroll 1
                 for (int pr = 0; pr < 2; ++pr) {
-                    const uint32_t a_tile = sbase + EB_SMEM_A + (uint32_t)pr * EB_A_TILE;
+                    const uint32_t a_tile = sbase + EB_SMEM_A + (it & 1u) * EB_A_STAGE + (uint32_t)pr * EB_A_TILE;
                     const int f0 = fq * EDGE_FQ + 2 * pr;
                     float xv[2] = {0.f, 0.f};
                     if (row_ok) {
@@ -630,7 +635,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                         }
                         split2(sv, 0.0f, bh[q], bl[q]);
                     }
-                    if (!waited && !mbar_wait(smem_u32(&ctrl->emptyA), (it & 1u) ^ 1u, abort_flag)) {
+                    if (!waited && !mbar_wait(smem_u32(&ctrl->emptyA[it & 1u]), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
                         ok = false;
                         break;
                     }
@@ -646,7 +651,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 }
                 if (!ok) break;
                 fence_proxy_async_smem();
-                mbar_arrive(smem_u32(&ctrl->fullA));
+                mbar_arrive(smem_u32(&ctrl->fullA[it & 1u]));
             }
         }
     } else if (warp < EB_PRODUCER_WARPS + EB_SIGN_WARPS) {
@@ -669,11 +674,11 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             return (__byte_perm(a, b, 0x7632) & 0x80008000u) | 0x3F803F80u;
         };
         for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++n_item) {
-            int sp, fq;
-            decode(item, sp, fq);
+            int sp, ot, fq;
+            decode3(item, sp, ot, fq);
             int64_t t0, t1;
             tile_range(sp, t0, t1);
-            const int64_t units = (t1 - t0) * n_ot * EDGE_FQ;          // a multiple of 4: job stays even at item starts
+            const int64_t units = (t1 - t0) * EDGE_FQ;                 // a multiple of 4: job stays even at item starts
             for (int64_t u = half; u < units && ok; u += 2) {
                 const uint32_t jb = job + (uint32_t)u;
                 const uint32_t sb = (uint32_t)half;                     // == jb & 1
@@ -690,11 +695,11 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2) {
                     uint32_t r[32];
-                    tmem_ld_32x32(lane_addr + ch * 64 + h2 * 32, r);
+                    tmem_ld_32x32(lane_addr + sb * EB_TN + ch * 64 + h2 * 32, r);
                     tmem_ld_wait();
                     if (h2 == 1) {
                         tc_fence_before_sync();
-                        mbar_arrive(smem_u32(&ctrl->phiEmpty));
+                        mbar_arrive(smem_u32(&ctrl->phiEmpty[sb]));
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
@@ -707,24 +712,21 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             }
             job += (uint32_t)units;
             if (!ok) break;
-            // the item's parameter-gradient sums: this thread writes output tile `half`, features 2 ch, 2 ch + 1
+            // the item's parameter-gradient sums: this thread writes feature 2 ch + half of its output row
             if (!mbar_wait(smem_u32(&ctrl->gFull), n_item & 1u, abort_flag)) break;
             tc_fence_after_sync();
-            float* slab = slabs + (size_t)sp * ((size_t)O * I * 9);
-            for (int j = half; j < n_ot; j += 2) {
-                const int o = j * EDGE_OT + orow;
+            {
+                float* slab = slabs + (size_t)sp * ((size_t)O * I * 9);
+                const int o = ot * EDGE_OT + orow;
+                const int q = 2 * ch + half, f = fq * EDGE_FQ + q;
+                uint32_t r[32];
+                tmem_ld_32x32(lane_addr + EB_TMEM_G + (uint32_t)q * 32, r);
+                tmem_ld_wait();
+                if (o < O && f < I) {
+                    const float sc = __ldg(ga + (size_t)o * I + f) * inv_n;
+                    float* out = slab + ((size_t)o * I + f) * 9;
 #pragma unroll
-                for (int qq = 0; qq < 2; ++qq) {
-                    const int q = 2 * ch + qq, f = fq * EDGE_FQ + q;
-                    uint32_t r[32];
-                    tmem_ld_32x32(lane_addr + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 32, r);
-                    tmem_ld_wait();
-                    if (o < O && f < I) {
-                        const float sc = __ldg(ga + (size_t)o * I + f) * inv_n;
-                        float* out = slab + ((size_t)o * I + f) * 9;
-#pragma unroll
-                        for (int c = 0; c < 9; ++c) out[c] = sc * (__uint_as_float(r[c]) + __uint_as_float(r[16 + c]));
-                    }
+                    for (int c = 0; c < 9; ++c) out[c] = sc * (__uint_as_float(r[c]) + __uint_as_float(r[16 + c]));
                 }
             }
             tc_fence_before_sync();
@@ -786,7 +788,12 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     }
                     tc_fence_before_sync();
                     mbar_arrive(smem_u32(&ctrl->d3Empty));
-                    if (row_ok) {
+                    if (row_ok && add_gx) {
+                        float* out = gx + (size_t)n * I + f0;
+#pragma unroll
+                        for (int q = 0; q < EDGE_FQ; ++q)
+                            if (f0 + q < I) atomicAdd(out + q, g[q]);
+                    } else if (row_ok) {
                         float* out = gx + (size_t)n * I + f0;
                         if (vec_x && f0 + EDGE_FQ <= I && (I & 3) == 0) {
                             *reinterpret_cast<float4*>(out) = make_float4(g[0], g[1], g[2], g[3]);
@@ -817,44 +824,49 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 if (!mbar_wait(smem_u32(&ctrl->gEmpty), (n_item & 1u) ^ 1u, abort_flag)) break;
                 tc_fence_after_sync();
                 auto stage_ready = [&](uint32_t tile_it) -> bool {
-                    if (!mbar_wait(smem_u32(&ctrl->fullA), tile_it & 1u, abort_flag)) return false;
+                    if (!mbar_wait(smem_u32(&ctrl->fullA[tile_it & 1u]), (tile_it >> 1) & 1u, abort_flag)) return false;
                     tc_fence_after_sync();
                     return true;
                 };
-                auto gemm1 = [&](int j, int q, uint32_t jb) -> bool {
-                    if (!mbar_wait(smem_u32(&ctrl->phiEmpty), (jb & 1u) ^ 1u, abort_flag)) return false;
+                auto gemm1 = [&](uint32_t tile_it, int q, uint32_t jb) -> bool {
+                    const uint32_t buf = jb & 1u;
+                    if (!mbar_wait(smem_u32(&ctrl->phiEmpty[buf]), ((jb >> 1) & 1u) ^ 1u, abort_flag)) return false;
                     tc_fence_after_sync();
-                    const uint32_t w = pair_addr(sbase + EB_SMEM_W + j * EDGE_W_SLOT, EDGE_W_TILE, q);
-                    const uint32_t a = pair_addr(sbase + EB_SMEM_A, EB_A_TILE, q);
+                    const uint32_t w = pair_addr(sbase + EB_SMEM_W, EDGE_W_TILE, q);
+                    const uint32_t a = pair_addr(sbase + EB_SMEM_A + (tile_it & 1u) * EB_A_STAGE, EB_A_TILE, q);
                     const uint64_t dw_hi = sdesc_at(d_k, w), da_hi = sdesc_at(d_k, a);
-                    mma_f16_ss(tmem_base, dw_hi, da_hi, idesc1, 0u);
-                    mma_f16_ss(tmem_base, dw_hi + 2u, da_hi, idesc1, 1u);          // lo part: 32 bytes on
-                    mma_f16_ss(tmem_base, dw_hi, da_hi + 2u, idesc1, 1u);
-                    mma_commit(smem_u32(&ctrl->phiFull[jb & 1u]));
+                    const uint32_t d = tmem_base + buf * EB_TN;
+                    mma_f16_ss(d, dw_hi, da_hi, idesc1, 0u);
+                    mma_f16_ss(d, dw_hi + 2u, da_hi, idesc1, 1u);                  // lo part: 32 bytes on
+                    mma_f16_ss(d, dw_hi, da_hi + 2u, idesc1, 1u);
+                    mma_commit(smem_u32(&ctrl->phiFull[buf]));
                     return true;
                 };
-                // units of the item in order (tile, output tile, feature); within a tile GEMM1 runs one
-                // unit ahead of the products that consume the sign tile
+                // units of the item in order (tile, feature); GEMM1 runs one unit ahead of the products
+                // that consume the sign tile
                 int64_t t = t0;
-                int j = 0, q = 0;
+                int q = 0;
                 uint32_t cur_it = it;
-                if (!stage_ready(cur_it) || !gemm1(0, 0, job)) break;
+                if (!stage_ready(cur_it) || !gemm1(cur_it, 0, job)) break;
                 while (true) {
                     int64_t nt = t;
-                    int nj = j, nq = q + 1;
-                    if (nq == EDGE_FQ) { nq = 0; ++nj; }
-                    if (nj == n_ot) { nj = 0; ++nt; }
+                    int nq = q + 1;
+                    if (nq == EDGE_FQ) { nq = 0; ++nt; }
                     const bool has_next = nt < t1, same_tile = nt == t;
+                    const uint32_t next_it = cur_it + (same_tile ? 0u : 1u);
+                    if (has_next) {
+                        if (!same_tile && !stage_ready(next_it)) { ok = false; break; }
+                        if (!gemm1(next_it, nq, job + 1)) { ok = false; break; }
+                    }
                     const uint32_t sb = job & 1u;
                     if (!mbar_wait(smem_u32(&ctrl->sFull[sb]), (job >> 1) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    // the sign warps have read phi(job): the next unit's phi may overwrite it
-                    if (has_next && same_tile && !gemm1(nj, nq, job + 1)) { ok = false; break; }
-                    {   // GEMM2: G[j][q] (+)= S[o, n] [A_hi | A_lo][n, 32]; addresses advance in 16-byte units
+                    {   // GEMM2: G[q] (+)= S[o, n] [A_hi | A_lo][n, 32]; addresses advance in 16-byte units
                         const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
-                        const uint32_t d = tmem_base + EB_TMEM_G + (uint32_t)(j * EDGE_FQ + q) * 32;
+                        const uint32_t d = tmem_base + EB_TMEM_G + (uint32_t)q * 32;
                         const uint64_t ds0 = sdesc_at(d_k, s_t), ds1 = sdesc_at(d_k, s_t + EB_S_BLOCK);
-                        const uint64_t db = sdesc_at(d_mn, pair_addr(sbase + EB_SMEM_A, EB_A_TILE, q));
+                        const uint64_t db =
+                            sdesc_at(d_mn, pair_addr(sbase + EB_SMEM_A + (cur_it & 1u) * EB_A_STAGE, EB_A_TILE, q));
                         const uint32_t first = t > t0 ? 1u : 0u;
 #pragma unroll
                         for (int ks = 0; ks < 8; ++ks)
@@ -863,13 +875,9 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                     }
                     mma_commit(smem_u32(&ctrl->sEmpty[sb]));
                     ++job;
-                    if (!has_next || !same_tile) {
-                        mma_commit(smem_u32(&ctrl->emptyA));
-                        if (!has_next) break;
-                        ++cur_it;
-                        if (!stage_ready(cur_it) || !gemm1(nj, nq, job)) { ok = false; break; }
-                    }
-                    t = nt; j = nj; q = nq;
+                    if (!has_next || !same_tile) mma_commit(smem_u32(&ctrl->emptyA[cur_it & 1u]));
+                    if (!has_next) break;
+                    t = nt; q = nq; cur_it = next_it;
                 }
                 if (!ok) break;
                 it = cur_it + 1;
@@ -895,22 +903,18 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 for (int64_t t = t0; t < t1 && ok; ++t, ++it) {
                     if (!mbar_wait(smem_u32(&ctrl->d3Empty), (it & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    for (int j = 0; j < n_ot && ok; ++j) {
-                        for (int q = 0; q < EDGE_FQ; ++q, ++job) {
-                            const uint32_t sb = job & 1u;
-                            if (!mbar_wait(smem_u32(&ctrl->sFull[sb]), (job >> 1) & 1u, abort_flag)) { ok = false; break; }
-                            tc_fence_after_sync();
-                            const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
-                            const uint32_t d = tmem_base + EB_TMEM_D3 + (uint32_t)q * 32;
-                            const uint64_t dsT = sdesc_at(d_mnS, s_t);
-                            const uint64_t db = sdesc_at(d_mn, pair_addr(sbase + EB_SMEM_WG + j * EDGE_W_SLOT, EDGE_W_TILE, q));
-                            const uint32_t first = j > 0 ? 1u : 0u;
+                    for (int q = 0; q < EDGE_FQ; ++q, ++job) {
+                        const uint32_t sb = job & 1u;
+                        if (!mbar_wait(smem_u32(&ctrl->sFull[sb]), (job >> 1) & 1u, abort_flag)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t s_t = sbase + EB_SMEM_S + sb * EB_S_TILE;
+                        const uint32_t d = tmem_base + EB_TMEM_D3 + (uint32_t)q * 32;
+                        const uint64_t dsT = sdesc_at(d_mnS, s_t);
+                        const uint64_t db = sdesc_at(d_mn, pair_addr(sbase + EB_SMEM_WG, EDGE_W_TILE, q));
 #pragma unroll
-                            for (int ks = 0; ks < 8; ++ks)
-                                mma_f16_ss(d, dsT + (uint64_t)(ks * 128), db + (uint64_t)(ks * 128), idesc3,
-                                           ks == 0 ? first : 1u);
-                            mma_commit(smem_u32(&ctrl->sEmpty[sb]));
-                        }
+                        for (int ks = 0; ks < 8; ++ks)
+                            mma_f16_ss(d, dsT + (uint64_t)(ks * 128), db + (uint64_t)(ks * 128), idesc3, ks == 0 ? 0u : 1u);
+                        mma_commit(smem_u32(&ctrl->sEmpty[sb]));
                     }
                     if (ok) mma_commit(smem_u32(&ctrl->d3Full));
                 }
@@ -923,16 +927,14 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             // ===== bulk copies: the weight tiles of an item (and their ga-scaled twins), once per item =====
             uint32_t n_item = 0;
             for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x, ++n_item) {
-                int sp, fq;
-                decode(item, sp, fq);
+                int sp, ot, fq;
+                decode3(item, sp, ot, fq);
                 if (!mbar_wait(smem_u32(&ctrl->emptyW), (n_item & 1u) ^ 1u, abort_flag)) break;
                 const uint32_t bar = smem_u32(&ctrl->fullW);
-                mbar_arrive_expect_tx(bar, (uint32_t)n_ot * EDGE_W_SLOT * (need_gx ? 2u : 1u));
-                for (int j = 0; j < n_ot; ++j) {
-                    const size_t off = ((size_t)j * plan.n_quads + fq) * (size_t)EDGE_W_SLOT;
-                    bulk_g2s(sbase + EB_SMEM_W + j * EDGE_W_SLOT, wimg + off, EDGE_W_SLOT, bar);
-                    if (need_gx) bulk_g2s(sbase + EB_SMEM_WG + j * EDGE_W_SLOT, wgimg + off, EDGE_W_SLOT, bar);
-                }
+                mbar_arrive_expect_tx(bar, EDGE_W_SLOT * (need_gx ? 2u : 1u));
+                const size_t off = ((size_t)ot * plan.n_quads + fq) * (size_t)EDGE_W_SLOT;
+                bulk_g2s(sbase + EB_SMEM_W, wimg + off, EDGE_W_SLOT, bar);
+                if (need_gx) bulk_g2s(sbase + EB_SMEM_WG, wgimg + off, EDGE_W_SLOT, bar);
             }
         }
     }
@@ -980,7 +982,8 @@ EdgeBwdPlan plan_edge_bwd(int64_t N, int I, int O) {
     // chains of at most EB_MAX_CHAIN_TILES sample tiles per accumulator, and about four rounds of
     // work items for the persistent blocks
     int64_t splits = (p.tiles_total + EB_MAX_CHAIN_TILES - 1) / EB_MAX_CHAIN_TILES;
-    const int64_t for_balance = (4 * (int64_t)sm_count() + p.n_quads - 1) / p.n_quads;
+    const int64_t base_items = (int64_t)p.n_quads * p.n_otiles;
+    const int64_t for_balance = (4 * (int64_t)sm_count() + base_items - 1) / base_items;
     if (splits < for_balance) splits = for_balance;
     if (splits > p.tiles_total) splits = p.tiles_total;
     if (splits < 1) splits = 1;
@@ -1092,6 +1095,10 @@ cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid,
         pack_edge_weights_pairs_kernel<<<pblocks, 256, 0, st>>>(W, bw, ga, 1.0f / (float)s.N, wgimg, s.O, s.I, s.R(),
                                                                 p.n_quads, p.n_otiles);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    if (need_x && p.n_otiles > 1) {
+        e = cudaMemsetAsync(gx, 0, (size_t)s.N * s.I * sizeof(float), st);
+        if (e != cudaSuccess) return e;
     }
     const int vec_x = ((s.I & 1) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                       (!gx || (reinterpret_cast<uintptr_t>(gx) & 15) == 0);
