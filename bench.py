@@ -674,7 +674,7 @@ def run_micro(args):
     emit("edge_input_kernel", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
     del H
 
-    # the same statistic straight from x (basis never stored): tensor-core forward, FMA-pipe backward
+    # the same statistic straight from x (basis never stored), on the tensor cores and on the FMA pipes
     xe = torch.rand(Ne, Ie, device=dev, generator=g) * 2 - 1
     ge = ((torch.arange(G + 2 * k + 1, device=dev, dtype=torch.float32) - k) * (2.0 / G) - 1.0)[None] \
         .expand(Ie, -1).contiguous()
@@ -683,26 +683,55 @@ def run_micro(args):
          tflops_counted_once=fl / ms / 1e9)
     ms = timeit(lambda: nat.edge_abs_mean_x(xe, None, ge, bw, W, k, nat.MODE_SIMT))
     emit("edge_param_kernel<forward, from x>", ms, flops=fl, fma_peak_tflops=fma_peak["fp32"])
-    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, False, False, True, True))
+    simt = nat.MODE_SIMT
+    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, False, False, True, True, mode=simt))
     emit("edge_param_kernel<grad, from x> + sum_slabs", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
-    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, True, False, False, False))
+    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, True, False, False, False, mode=simt))
     emit("edge_input_kernel<from x>", ms, flops=2 * fl, fma_peak_tflops=fma_peak["fp32"])
+    tc = nat.MODE_TC_BF16X3
+    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, False, False, True, True, mode=tc))
+    emit("tc_edge_bwd_kernel (parameter gradients, tensor cores)", ms, flops=2 * fl,
+         note="phi + sign(phi)^T A: 4 N O I (R+1) flops counted once", tflops_counted_once=2 * fl / ms / 1e9)
+    ms = timeit(lambda: nat.edge_abs_mean_x_backward(ga, xe, None, ge, bw, W, k, True, False, True, True, mode=tc))
+    emit("tc_edge_bwd_kernel (parameter + input gradients, tensor cores)", ms, flops=3 * fl,
+         note="6 N O I (R+1) flops counted once", tflops_counted_once=3 * fl / ms / 1e9)
     del s, W, xe
 
-    # float64 SIMT layer (PINN-style 64 -> 64, G = 8)
-    Nd, Id, Od, Gd = 131072, 64, 64, 8
-    xd = torch.rand(Nd, Id, device=dev, dtype=torch.float64, generator=g) * 2 - 1
-    gd = ((torch.arange(Gd + 2 * k + 1, device=dev, dtype=torch.float64) - k) * (2.0 / Gd) - 1.0)[None] \
-        .expand(Id, -1).contiguous()
-    bwd_ = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
-    swd = torch.randn(Od, Id, Gd + k, device=dev, dtype=torch.float64, generator=g)
-    scd = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
-    ms = timeit(lambda: nat.forward(xd, gd, bwd_, swd, scd, k, nat.MODE_SIMT))
-    emit("fwd_simt_kernel<double,3>", ms, flops=2.0 * Nd * Od * Id * (k + 2), note="useful flops: k+2 terms per edge",
-         fma_peak_tflops=fma_peak["fp64"])
-    D = torch.randn(Nd, Od, device=dev, dtype=torch.float64, generator=g)
-    ms = timeit(lambda: nat.backward(D, xd, gd, bwd_, swd, scd, k, True, True, True, True, nat.MODE_SIMT))
-    emit("bwd_simt (param + input)<double,3>", ms, flops=4.0 * Nd * Od * Id * (k + 2), fma_peak_tflops=fma_peak["fp64"])
+    # MMA issue cost: cycles per tcgen05.mma (K = 16) for one issuing thread, by accumulator width
+    st_lib.kanb200_selftest_umma_rate.restype = ctypes.c_int
+    st_lib.kanb200_selftest_umma_rate.argtypes = [ctypes.c_int] * 4 + [ctypes.c_void_p] * 3
+    cyc = torch.zeros(4, dtype=torch.int64, device=dev)
+    stat = torch.zeros(1, dtype=torch.int32, device=dev)
+    for n_cols in (16, 32, 128, 256):
+        for threads in (1, 2):
+            for _ in range(2):
+                st_lib.kanb200_selftest_umma_rate(n_cols, 512, threads, 1, ctypes.c_void_p(cyc.data_ptr()),
+                                                  ctypes.c_void_p(stat.data_ptr()), None)
+                torch.cuda.synchronize()
+            print(json.dumps({"kernel": f"umma_rate<N={n_cols}, issuing threads={threads}>",
+                              "cycles_per_mma_per_thread": cyc[1].item() / 512.0,
+                              "note": "M = 128, K = 16, bf16; 512 instructions per thread, until completion"}),
+                  flush=True)
+
+    # float64 layers of the PINN-style network on the FP64 matrix instruction (131072 rows, G = 8)
+    Nd, Gd = 131072, 8
+    for Id, Od in ((2, 64), (64, 64), (64, 1)):
+        xd = torch.rand(Nd, Id, device=dev, dtype=torch.float64, generator=g) * 2 - 1
+        gd = ((torch.arange(Gd + 2 * k + 1, device=dev, dtype=torch.float64) - k) * (2.0 / Gd) - 1.0)[None] \
+            .expand(Id, -1).contiguous()
+        bwd_ = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
+        swd = torch.randn(Od, Id, Gd + k, device=dev, dtype=torch.float64, generator=g)
+        scd = torch.randn(Od, Id, device=dev, dtype=torch.float64, generator=g)
+        D = torch.randn(Nd, Od, device=dev, dtype=torch.float64, generator=g)
+        dense = 2.0 * Nd * Od * Id * (Gd + k + 1)
+        pk = fma_peak["dmma_m8n8k4"]
+        ms = timeit(lambda: nat.forward(xd, gd, bwd_, swd, scd, k, nat.MODE_SIMT))
+        emit(f"dm_forward_kernel<double> {Id}->{Od}", ms, flops=dense, fma_peak_tflops=pk,
+             note="dense flops 2 N O I (R+1) against the measured FP64 matrix-instruction peak")
+        ms = timeit(lambda: nat.backward(D, xd, gd, bwd_, swd, scd, k, False, True, True, True, nat.MODE_SIMT))
+        emit(f"dm_bwd_param_kernel<double> {Id}->{Od}", ms, flops=dense, fma_peak_tflops=pk)
+        ms = timeit(lambda: nat.backward(D, xd, gd, bwd_, swd, scd, k, True, False, False, False, nat.MODE_SIMT))
+        emit(f"dm_bwd_input_kernel<double> {Id}->{Od}", ms, flops=dense, fma_peak_tflops=pk)
 
 
 def run_config(args):

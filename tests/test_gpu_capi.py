@@ -95,6 +95,47 @@ def test_umma_layout_mn_major():
     assert np.array_equal(D, A @ B.T)
 
 
+def _run_selftest_general(a_img, b_img, params, n):
+    import ctypes
+    from torchsplinekan_b200.build import SELFTEST_PATH
+    lib = ctypes.CDLL(SELFTEST_PATH)
+    fn = lib.kanb200_selftest_umma_general
+    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_void_p] * 6
+    a = torch.from_numpy(a_img.view(np.int16)).cuda()
+    b = torch.from_numpy(b_img.view(np.int16)).cuda()
+    D = torch.zeros(128, n, dtype=torch.float32, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    p = (ctypes.c_uint * 16)(*params, 0, 0)
+    assert fn(a.data_ptr(), b.data_ptr(), ctypes.cast(p, ctypes.c_void_p), D.data_ptr(), st.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    return D.cpu().numpy()
+
+
+@pytest.mark.parametrize("q", [0, 1])
+def test_umma_one_tile_read_by_two_products(q):
+    """The operand readings the edge-statistic backward kernel relies on: ONE 128-byte-swizzled tile of
+    rows [k][64 values] is the K-major operand of one product and, read MN-major with 32 columns that
+    start 64 q bytes into every row, the operand of the next; and a sign tile stored as two K-major
+    blocks of 64 samples is read MN-major (two groups of 64, 16 KB apart) by the third."""
+    rng = np.random.default_rng(7 + q)
+    # params: a_bytes, b_bytes, a_mn, b_mn, a_lbo, a_sbo, a_step, a_off, b_lbo, b_sbo, b_step, b_off, n, ksteps
+    A = rng.integers(-4, 5, (128, 64)).astype(np.float32)
+    B = rng.integers(-4, 5, (64, 64)).astype(np.float32)
+    D = _run_selftest_general(_img_kmajor(A), _img_kmajor(B),
+                              [16384, 8192, 0, 1, 16, 1024, 32, 0, 8192, 1024, 2048, 64 * q, 32, 4], 32)
+    assert np.array_equal(D, A @ B[:, 32 * q:32 * q + 32])
+    S = rng.integers(-1, 2, (128, 128)).astype(np.float32)
+    W = rng.integers(-4, 5, (128, 64)).astype(np.float32)
+    s_img = np.concatenate([_img_kmajor(S[:, :64]), _img_kmajor(S[:, 64:])])
+    D = _run_selftest_general(s_img, _img_kmajor(W),
+                              [32768, 16384, 1, 1, 16384, 1024, 2048, 0, 8192, 1024, 2048, 64 * q, 32, 8], 32)
+    assert np.array_equal(D, S.T @ W[:, 32 * q:32 * q + 32])
+    D = _run_selftest_general(s_img, _img_kmajor(B),
+                              [32768, 8192, 0, 1, 16, 1024, 32, 16384, 8192, 1024, 2048, 64 * q, 32, 4], 32)
+    assert np.array_equal(D, S[:, 64:] @ B[:, 32 * q:32 * q + 32])
+
+
 # ---------------------------------------------------------------------------
 # basis / basis gradient
 # ---------------------------------------------------------------------------
