@@ -190,6 +190,14 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void
                                                  int64_t N, int64_t I, int64_t O, int G, int k,
                                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* The tensor-core backward takes sign(phi) from a split-bf16 product, which gives phi to about 5e-6 of
+ * its terms.  With the re-check on (the default) a phi below 2e-5 of a bound on its terms is evaluated
+ * again in float32 before its sign is taken, so the gradients are those of a float32 evaluation
+ * (relative L2 error against float64 3e-7 instead of 7e-5 .. 2e-4); switching it off makes the kernel
+ * about a third faster.  Process-wide; returns KANB200_OK. */
+KANB200_API int kanb200_set_edge_sign_recheck(int on);
+KANB200_API int kanb200_get_edge_sign_recheck(void);
+
 /* Gradients of kanb200_edge_abs_mean; NULL output = not needed
  * (edge_abs_mean_backward_cuda, csrc/kan_reg_cuda.cu:284-312). */
 KANB200_API int kanb200_edge_abs_mean_backward(int dtype, const void* grad_a,

@@ -179,13 +179,12 @@ def test_config2_full_size_training_step():
     penalty's gradient contains sign(phi): where |phi| is at rounding level, two evaluations
     disagree on the sign and that edge's gradient entries move by 2 ga / N = 2.4e-4 of their largest
     possible size, whatever the arithmetic -- float32 against float64 dense PyTorch shows it too.
-    Both are valid subgradients of |phi| at neighbouring points.  The native backward takes the
-    signs from the split-bf16 tensor-core product (phi to about 5e-6 of its terms), so a few more
-    samples fall on the other side than in float32 arithmetic.  The native gradients must therefore
-    be as close to float64 in the max-norm as the dense FLOAT32 evaluation of the same expression
-    is (factor 3 of slack) or within a few flips' worth (10 / N; flips are discrete events), and
-    within 1e-3 in the relative L2 norm (measured: 7e-5), which single flipped entries hardly move
-    but a wrong kernel would."""
+    Both are valid subgradients of |phi| at neighbouring points.  (The tensor-core backward evaluates
+    phi values at rounding level again in float32 before taking their sign, so its sign decisions are
+    those of float32 arithmetic.)  The native gradients must therefore be as close to float64 in the
+    max-norm as the dense FLOAT32 evaluation of the same expression is (factor 3 of slack) or within
+    a few flips' worth (10 / N; flips are discrete events), and within 1e-3 in the relative L2 norm
+    (measured: 6e-5), which single flipped entries hardly move but a wrong kernel would."""
     torch.manual_seed(0)
     net = sk.KAN([784, 256, 256, 10], backend="cuda").cuda()
     g = torch.Generator().manual_seed(0)

@@ -52,6 +52,8 @@ SIGNATURES = {
                                                                    _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_x": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                              _c_void_p, _c_size, _c_void_p]),
+    "kanb200_set_edge_sign_recheck": (_c_int, [_c_int]),
+    "kanb200_get_edge_sign_recheck": (_c_int, []),
     "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                                _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
@@ -359,6 +361,16 @@ def edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k: int, need_x=True, need_s=
                                                       _p(gx), _p(ds), _p(dbw), _p(dW), N, I, O, G, k,
                                                       _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return gx, ds, dbw, dW
+
+
+def set_edge_sign_recheck(on: bool) -> None:
+    """Whether the tensor-core backward of the edge statistic evaluates near-zero phi again in float32
+    before taking their sign (default on; off is about a third faster, signs at split-bf16 accuracy)."""
+    _check(lib().kanb200_set_edge_sign_recheck(1 if on else 0))
+
+
+def get_edge_sign_recheck() -> bool:
+    return bool(lib().kanb200_get_edge_sign_recheck())
 
 
 def edge_abs_mean_backward(ga, s, H, bw, W, need_s, need_H, need_bw, need_W):

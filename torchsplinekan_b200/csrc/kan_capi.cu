@@ -54,7 +54,9 @@ bool edge_x_uses_tc(int mode, int dtype, const LayerShape& s) {
 // The same for its backward (needs the SiLU / no-base form: no caller-provided base values).
 bool edge_x_bwd_uses_tc(int mode, int dtype, const LayerShape& s, bool custom_base) {
     if (dtype != KANB200_F32 || mode == KANB200_MODE_SIMT || custom_base || !tc_edge_bwd_supported(s)) return false;
-    if (mode == KANB200_MODE_AUTO) return s.N >= 256 && s.O >= 16;
+    // from about 2^23 edge-samples on: below, the table, the two weight images and the finalize pass
+    // cost more than the FMA kernels need for the whole job
+    if (mode == KANB200_MODE_AUTO) return s.N >= 256 && s.O >= 16 && s.N * s.I * s.O >= ((int64_t)1 << 23);
     return true;
 }
 
@@ -443,6 +445,13 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void
                                           st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x_backward");
 }
+
+KANB200_API int kanb200_set_edge_sign_recheck(int on) {
+    tc_edge_set_sign_recheck(on != 0);
+    return KANB200_OK;
+}
+
+KANB200_API int kanb200_get_edge_sign_recheck(void) { return tc_edge_get_sign_recheck() ? 1 : 0; }
 
 KANB200_API int kanb200_edge_abs_mean_noalloc(int dtype, const void* s, const void* H, const void* bw,
                                                const void* W, void* a, int64_t N, int64_t I, int64_t O, int R,

@@ -121,6 +121,11 @@ cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid,
                              float* gx, float* dbw, float* dW, const LayerShape& s, void* ws, size_t ws_bytes,
                              cudaStream_t st);
 
+// Whether the backward kernel evaluates a phi whose tensor-core value is at rounding level again in
+// float32 before taking its sign (default: yes).
+void tc_edge_set_sign_recheck(bool on);
+bool tc_edge_get_sign_recheck();
+
 // Coefficient refit after a knot update (kan_refit.cu): per-feature moment matrices
 // G = sum b_new b_new^T, M = sum b_new b_old^T (float64 [I, R, R]) and the in-place solve X = G^-1 M.
 template <typename T>

@@ -189,6 +189,22 @@ __device__ __forceinline__ int eval_feature_deriv(const float* __restrict__ ftab
     return __float_as_int(meta.y);
 }
 
+// Values of the window functions of one input in float32 (no bf16 split); returns the window start.
+template <bool SMEM_TAB, bool WIDE>
+__device__ __forceinline__ int eval_feature_values(const float* __restrict__ ftab, const TabInfo& ti, float xv,
+                                                   float (&v)[4]) {
+    auto ld4 = [](const float4* p) -> float4 { return SMEM_TAB ? *p : __ldg(p); };
+    const int m = table_entry_index<SMEM_TAB, WIDE>(ftab, ti, xv);
+    const float4* ent = reinterpret_cast<const float4*>(ftab + ti.es + m * TAB_ENTRY_FLOATS);
+    const float4 c0 = ld4(ent), c1 = ld4(ent + 1), c2 = ld4(ent + 2), c3 = ld4(ent + 3), meta = ld4(ent + 4);
+    const float u = xv - meta.x;
+    v[0] = fmaf(fmaf(fmaf(c0.w, u, c0.z), u, c0.y), u, c0.x);
+    v[1] = fmaf(fmaf(fmaf(c1.w, u, c1.z), u, c1.y), u, c1.x);
+    v[2] = fmaf(fmaf(fmaf(c2.w, u, c2.z), u, c2.y), u, c2.x);
+    v[3] = fmaf(fmaf(fmaf(c3.w, u, c3.z), u, c3.y), u, c3.x);
+    return __float_as_int(meta.y);
+}
+
 // sigma(x) (1 + x (1 - sigma(x)))
 __device__ __forceinline__ float silu_grad_fast(float x) {
     const float sg = __fdividef(1.0f, 1.0f + __expf(-x));

@@ -455,7 +455,10 @@ constexpr uint32_t EB_SMEM_A = 0;                                 // two stages 
 constexpr uint32_t EB_SMEM_S = EB_SMEM_A + 2 * EB_A_STAGE;        // two sign tiles: conversion runs one unit ahead
 constexpr uint32_t EB_SMEM_W = EB_SMEM_S + 2 * EB_S_TILE;
 constexpr uint32_t EB_SMEM_WG = EB_SMEM_W + EDGE_W_SLOT;
-constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WG + EDGE_W_SLOT;
+constexpr uint32_t EB_SMEM_XS = EB_SMEM_WG + EDGE_W_SLOT;          // float32 x of the two operand stages: [2][128][4]
+constexpr uint32_t EB_SMEM_WROWS = EB_SMEM_XS + 2 * EB_TN * EDGE_FQ * 4;   // float32 weights of the item: [128][4][12]
+constexpr uint32_t EB_WROW_FLOATS = 12;                           // 8 coefficients, base weight, re-check bound, 2 unused
+constexpr uint32_t EB_SMEM_CTRL = EB_SMEM_WROWS + EDGE_OT * EDGE_FQ * EB_WROW_FLOATS * 4;
 constexpr uint32_t EB_SMEM_BYTES = EB_SMEM_CTRL + 256 + TAB_SMEM_FLOATS * 4;
 static_assert(EB_SMEM_BYTES <= 232448, "edge backward kernel shared memory exceeds 227 KB");
 constexpr uint32_t EB_TMEM_G = 256, EB_TMEM_D3 = 384;
@@ -467,6 +470,7 @@ struct EdgeBwdCtrl {
     uint64_t sFull[2], sEmpty[2];
     uint64_t gFull, gEmpty;
     uint64_t d3Full, d3Empty;
+    uint64_t wrFull, wrFree;              // float32 weight rows of the item (sign warps among themselves)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -520,9 +524,10 @@ __global__ void pack_edge_weights_pairs_kernel(const float* __restrict__ W, cons
 
 __global__ void __launch_bounds__(EB_THREADS, 1)
 tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
-                   const uint8_t* __restrict__ wgimg, const float* __restrict__ ga, float* __restrict__ slabs,
-                   float* __restrict__ gx, int* __restrict__ status, int64_t N, int I, int O, int has_base,
-                   EdgeBwdPlan plan, TabInfo ti, int vec_x) {
+                   const uint8_t* __restrict__ wgimg, const float* __restrict__ ga, const float* __restrict__ Wf,
+                   const float* __restrict__ bwf, float* __restrict__ slabs, float* __restrict__ gx,
+                   int* __restrict__ status, int64_t N, int I, int O, int R, EdgeBwdPlan plan, TabInfo ti,
+                   int vec_x, int recheck) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     EdgeBwdCtrl* ctrl = reinterpret_cast<EdgeBwdCtrl*>(smem + EB_SMEM_CTRL);
@@ -530,6 +535,9 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
     volatile int* abort_flag = &ctrl->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool need_gx = gx != nullptr;
+    const int has_base = bwf != nullptr;
+    float* xs = reinterpret_cast<float*>(smem + EB_SMEM_XS);
+    float* wrows = reinterpret_cast<float*>(smem + EB_SMEM_WROWS);
     const bool shared_grid = grid_is_shared(tab, I, ti);
     if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
 
@@ -549,6 +557,8 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         }
         mbar_init(smem_u32(&ctrl->d3Full), 1);
         mbar_init(smem_u32(&ctrl->d3Empty), EB_GXERS);
+        mbar_init(smem_u32(&ctrl->wrFull), EB_SIGNERS);
+        mbar_init(smem_u32(&ctrl->wrFree), EB_SIGNERS);
         mbar_init(smem_u32(&ctrl->fullW), 1);
         mbar_init(smem_u32(&ctrl->emptyW), issuers);
         mbar_init(smem_u32(&ctrl->gFull), 1);
@@ -640,6 +650,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                         break;
                     }
                     waited = true;
+                    *reinterpret_cast<float2*>(xs + ((it & 1u) * EB_TN + row) * EDGE_FQ + 2 * pr) = make_float2(xv[0], xv[1]);
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
                         const uint32_t c0 = (uint32_t)(4 * q);
@@ -659,7 +670,12 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         // tile g, so one conversion overlaps the products that read the other tile; thread = one output
         // row, 64 samples.  sign(phi) as bf16 is the float's sign bit over the pattern of 1.0 (0x3F80);
         // an exact zero counts as +1, which only matters for edges whose weights are all zero (the
-        // finalize kernel writes their gradients as zero, and their scaled weights add nothing to gx) =====
+        // finalize kernel writes their gradients as zero, and their scaled weights add nothing to gx).
+        // The split-bf16 product gives phi to about 2^-17 of its terms (measured: 4e-6 .. 7e-6 of the
+        // largest); with `recheck`, where |phi| is below 2e-5 of a bound on them, max_r |W_r| + 2 |bw|, the
+        // thread evaluates that one phi again in float32 -- x of the tile and the item's weight rows are
+        // kept in shared memory for that -- so the signs are those of a float32 evaluation (some tens of
+        // values per million take this path) =====
         const int e = warp - EB_PRODUCER_WARPS;            // 0 .. 15
         const int quad = warp & 3;
         const int half = e >> 3;                           // the group
@@ -668,7 +684,7 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
         const uint32_t row_off = (uint32_t)(orow >> 3) * 1024u + (uint32_t)(orow & 7) * 128u, x7 = (uint32_t)(orow & 7);
         const float inv_n = 1.0f / (float)N;
-        uint32_t job = 0, n_item = 0;
+        uint32_t job = 0, n_item = 0, tile_it = 0;
         bool ok = true;
         auto sgn2 = [](uint32_t a, uint32_t b) -> uint32_t {
             return (__byte_perm(a, b, 0x7632) & 0x80008000u) | 0x3F803F80u;
@@ -679,9 +695,36 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
             int64_t t0, t1;
             tile_range(sp, t0, t1);
             const int64_t units = (t1 - t0) * EDGE_FQ;                 // a multiple of 4: job stays even at item starts
+            const int o_glob = ot * EDGE_OT + orow;
+            float tau2[2] = {0.f, 0.f};                                // this group sees features half, half + 2
+            if (recheck) {
+                // the item's float32 weight rows: thread (row, column half ch, group) loads feature 2 ch + group
+                if (!mbar_wait(smem_u32(&ctrl->wrFree), (n_item & 1u) ^ 1u, abort_flag)) break;   // last item's readers
+                {
+                    const int q = 2 * ch + half, f = fq * EDGE_FQ + q;
+                    float* dst = wrows + ((size_t)orow * EDGE_FQ + q) * EB_WROW_FLOATS;
+                    float m = 0.f, b = 0.f;
+                    const bool live = o_glob < O && f < I;
+                    for (int r = 0; r < 8; ++r) {
+                        const float w = (live && r < R) ? __ldg(Wf + ((size_t)o_glob * I + f) * R + r) : 0.f;
+                        dst[r] = w;
+                        m = fmaxf(m, fabsf(w));
+                    }
+                    if (live && has_base) b = __ldg(bwf + (size_t)o_glob * I + f);
+                    dst[8] = b;
+                    dst[9] = (m + 2.0f * fabsf(b)) * 2.0e-5f;
+                }
+                mbar_arrive(smem_u32(&ctrl->wrFull));
+                if (!mbar_wait(smem_u32(&ctrl->wrFull), n_item & 1u, abort_flag)) break;
+                tau2[0] = wrows[((size_t)orow * EDGE_FQ + half) * EB_WROW_FLOATS + 9];
+                tau2[1] = wrows[((size_t)orow * EDGE_FQ + half + 2) * EB_WROW_FLOATS + 9];
+            }
+            const uint32_t it0 = tile_it;
             for (int64_t u = half; u < units && ok; u += 2) {
                 const uint32_t jb = job + (uint32_t)u;
                 const uint32_t sb = (uint32_t)half;                     // == jb & 1
+                const int qu = (int)(u & 3);
+                const float tau = (qu >> 1) ? tau2[1] : tau2[0];
                 if (!mbar_wait(smem_u32(&ctrl->phiFull[sb]), (jb >> 1) & 1u, abort_flag)) {
                     ok = false;
                     break;
@@ -701,6 +744,35 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                         tc_fence_before_sync();
                         mbar_arrive(smem_u32(&ctrl->phiEmpty[sb]));
                     }
+                    if (recheck) {
+                        float l4[4] = {3.0e38f, 3.0e38f, 3.0e38f, 3.0e38f};  // smallest |phi| of the 32 values
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) l4[c & 3] = fminf(l4[c & 3], fabsf(__uint_as_float(r[c])));
+                        if (fminf(fminf(l4[0], l4[1]), fminf(l4[2], l4[3])) < tau) {   // rare
+                            const float* wrow = wrows + ((size_t)orow * EDGE_FQ + qu) * EB_WROW_FLOATS;
+                            const uint32_t stage = (it0 + (uint32_t)(u >> 2)) & 1u;
+                            const float* ftab = tab + (size_t)min(fq * EDGE_FQ + qu, I - 1) * ti.fs;
+                            uint32_t small = 0u;
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) small |= (fabsf(__uint_as_float(r[c])) < tau) ? (1u << c) : 0u;
+                            while (small) {
+                                const int c = __ffs(small) - 1;
+                                small &= small - 1u;
+                                const float xv = xs[(stage * EB_TN + ch * 64 + h2 * 32 + c) * EDGE_FQ + qu];
+                                float v[4];
+                                const int s0 = shared_grid ? eval_feature_values<true, false>(stab, ti, xv, v)
+                                                           : eval_feature_values<false, false>(ftab, ti, xv, v);
+                                float phi = has_base ? silu_fast(xv) * wrow[8] : 0.f;
+#pragma unroll
+                                for (int jj = 0; jj < 4; ++jj)
+                                    if (s0 + jj >= 0 && s0 + jj < 8) phi = fmaf(v[jj], wrow[s0 + jj], phi);
+                                const uint32_t bits = __float_as_uint(phi);
+#pragma unroll
+                                for (int cc = 0; cc < 32; ++cc)
+                                    if (cc == c) r[cc] = bits;
+                            }
+                        }
+                    }
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
                         st_shared_v4(s_blk + (((uint32_t)(4 * h2 + c) ^ x7) << 4),
@@ -711,7 +783,9 @@ tc_edge_bwd_kernel(const float* __restrict__ x, const float* __restrict__ tab, c
                 mbar_arrive(smem_u32(&ctrl->sFull[sb]));
             }
             job += (uint32_t)units;
+            tile_it += (uint32_t)(t1 - t0);
             if (!ok) break;
+            if (recheck) mbar_arrive(smem_u32(&ctrl->wrFree));
             // the item's parameter-gradient sums: this thread writes feature 2 ch + half of its output row
             if (!mbar_wait(smem_u32(&ctrl->gFull), n_item & 1u, abort_flag)) break;
             tc_fence_after_sync();
@@ -974,6 +1048,8 @@ __global__ void edge_bwd_finalize_kernel(const float* __restrict__ slabs, int sp
     }
 }
 
+bool g_sign_recheck = true;
+
 EdgeBwdPlan plan_edge_bwd(int64_t N, int I, int O) {
     EdgeBwdPlan p;
     p.n_quads = (I + EDGE_FQ - 1) / EDGE_FQ;
@@ -1106,8 +1182,8 @@ cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid,
     const int blocks = (int)(items < sm_count() ? items : sm_count());
     e = ensure_dynamic_smem<tc_edge_bwd_kernel>((int)EB_SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    tc_edge_bwd_kernel<<<blocks, EB_THREADS, EB_SMEM_BYTES, st>>>(x, tab, wimg, wgimg, ga, slabs, gx, status, s.N, s.I,
-                                                                  s.O, bw ? 1 : 0, p, ti, vec_x);
+    tc_edge_bwd_kernel<<<blocks, EB_THREADS, EB_SMEM_BYTES, st>>>(x, tab, wimg, wgimg, ga, W, bw, slabs, gx, status, s.N,
+                                                                  s.I, s.O, s.R(), p, ti, vec_x, g_sign_recheck ? 1 : 0);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     if (dW || (dbw && bw)) {
         const int64_t total = (int64_t)s.O * s.I * 9;
@@ -1119,5 +1195,8 @@ cudaError_t tc_edge_backward(const float* ga, const float* x, const float* grid,
     }
     return e;
 }
+
+void tc_edge_set_sign_recheck(bool on) { g_sign_recheck = on; }
+bool tc_edge_get_sign_recheck() { return g_sign_recheck; }
 
 }  // namespace kanb200
