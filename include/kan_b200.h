@@ -196,6 +196,13 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void
  * (relative L2 error against float64 3e-7 instead of 7e-5 .. 2e-4); switching it off makes the kernel
  * about a third faster.  Process-wide; returns KANB200_OK. */
 KANB200_API int kanb200_set_edge_sign_recheck(int on);
+
+/* Which tensor-core forward kernel runs (same results): 1 = the generated operand is stored in tensor
+ * memory and the MMA reads it from there (shared memory only carries the weight tiles; one
+ * 256-output tile per generated tile), 0 = generated operand in shared memory, two 256-output
+ * sub-tiles per generated tile, -1 (default) = by shape: tensor memory for up to 256 outputs.
+ * Process-wide. */
+KANB200_API int kanb200_set_forward_variant(int variant);
 KANB200_API int kanb200_get_edge_sign_recheck(void);
 
 /* Gradients of kanb200_edge_abs_mean; NULL output = not needed

@@ -333,6 +333,13 @@ def test_layer_tensor_core_bf16x3_vs_oracle(shape):
     case = make_layer_case(dtype=np.float32, seed=5, **shape)
     errs = _compare_layer(case, nat.MODE_TC_BF16X3, TOL32)
     print("bf16x3", shape, errs)
+    # both forward kernels (generated operand in shared / in tensor memory) whatever the shape picks
+    try:
+        for variant in (0, 1):
+            nat.lib().kanb200_set_forward_variant(variant)
+            _compare_layer(case, nat.MODE_TC_BF16X3, TOL32, need_x=False)
+    finally:
+        nat.lib().kanb200_set_forward_variant(-1)
 
 
 @pytest.mark.parametrize("shape", [

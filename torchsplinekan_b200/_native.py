@@ -52,6 +52,7 @@ SIGNATURES = {
                                                                    _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_x": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                              _c_void_p, _c_size, _c_void_p]),
+    "kanb200_set_forward_variant": (_c_int, [_c_int]),
     "kanb200_set_edge_sign_recheck": (_c_int, [_c_int]),
     "kanb200_get_edge_sign_recheck": (_c_int, []),
     "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
@@ -95,6 +96,9 @@ def lib() -> ctypes.CDLL:
                     fn = getattr(handle, name)
                     fn.restype, fn.argtypes = res, args
                 _lib = handle
+                variant = os.environ.get("KAN_B200_FORWARD_VARIANT")     # "tmem" | "smem": see kanb200_set_forward_variant
+                if variant in ("tmem", "smem"):
+                    handle.kanb200_set_forward_variant(1 if variant == "tmem" else 0)
     return _lib
 
 

@@ -446,6 +446,11 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x_backward");
 }
 
+KANB200_API int kanb200_set_forward_variant(int variant) {
+    tc_set_forward_variant(variant);
+    return KANB200_OK;
+}
+
 KANB200_API int kanb200_set_edge_sign_recheck(int on) {
     tc_edge_set_sign_recheck(on != 0);
     return KANB200_OK;

@@ -100,6 +100,10 @@ cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const flo
 // are clamped to them; 0 keeps the current value).
 void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb);
 
+// Forward kernel variant: -1 = chosen by shape (tensor-memory operand for up to 256 outputs), 0 = generated
+// operand in shared memory, 1 = in tensor memory.
+void tc_set_forward_variant(int v);
+
 // The per-span polynomial table on its own: bytes, floats per feature, and the kernel that fills it.
 size_t tc_table_bytes(const LayerShape& s);
 int tc_table_stride(const LayerShape& s);

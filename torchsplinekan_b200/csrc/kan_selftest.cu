@@ -164,6 +164,75 @@ umma_general_kernel(const uint8_t* __restrict__ a_img, const uint8_t* __restrict
     }
 }
 
+// A operand from tensor memory: 128 threads (thread = row) write A[128][64] (bf16 pairs, as 32 words
+// per row) into tensor-memory columns [256, 288) with tcgen05.st, one thread issues the four K = 16
+// steps against a K-major shared-memory B tile [256][64], and D[128, 256] is read back.  `a_words` is
+// [128][32] uint32: word w of a row = elements 2w (low half) and 2w + 1 (high half).
+__global__ void __launch_bounds__(128, 1)
+umma_tmem_a_kernel(const uint32_t* __restrict__ a_words, const uint8_t* __restrict__ b_img, float* __restrict__ D,
+                   int* __restrict__ status) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ uint64_t done_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t e = threadIdx.x * 16; e < kBBytes; e += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(smem + e) = *reinterpret_cast<const uint4*>(b_img + e);
+    fence_proxy_async_smem();
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done_bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_slot;
+    const int row = warp * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    for (int c = 0; c < 4; ++c) {
+        uint32_t r[8];
+        for (int q = 0; q < 8; ++q) r[q] = a_words[row * 32 + c * 8 + q];
+        tmem_st_32x8(lane_addr + 256 + c * 8, r);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (threadIdx.x == 0) {
+        const uint64_t b_desc = make_sdesc_sw128(16, 1024);
+        const uint32_t idesc = make_idesc_bf16(256, false, false);
+        for (int ks = 0; ks < 4; ++ks)
+            mma_f16_ts(tmem_base, tmem_base + 256 + ks * 8, sdesc_at(b_desc, sbase + ks * 32), idesc, ks > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&done_bar));
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(smem_u32(&done_bar), 0, &abort_flag);
+    tc_fence_after_sync();
+    if (ok) {
+        for (int c = 0; c < 8; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(lane_addr + c * 32, r);
+            tmem_ld_wait();
+            for (int q = 0; q < 32; ++q) D[(size_t)row * 256 + c * 32 + q] = __uint_as_float(r[q]);
+        }
+    } else {
+        if (lane == 0) atomicExch(status, 1);
+        __nanosleep(100000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // Issue and completion cost of small MMAs: one or two threads (of different warps) each issue `reps`
 // K = 16 MMAs with N columns (operands: zero-filled 128-byte-swizzled K-major tiles, the same for
 // every MMA; accumulators: separate tensor-memory columns per thread) and commit.  Reports clock
@@ -368,5 +437,18 @@ int kanb200_selftest_umma_rate(int n, int reps, int threads, int same_acc, long 
     cudaError_t e = cudaFuncSetAttribute(umma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return -4;
     umma_rate_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(n, reps, threads, same_acc, out, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// See umma_tmem_a_kernel: a_words [128][32] uint32 (bf16 pairs), b_img the K-major image of B [256][64].
+extern "C" __attribute__((visibility("default")))
+int kanb200_selftest_umma_tmem_a(const void* a_words, const void* b_img, float* D, int* status, void* stream) {
+    using namespace kanb200;
+    if (!a_words || !b_img || !D || !status) return -1;
+    const int smem = (int)kBBytes;
+    cudaError_t e = cudaFuncSetAttribute(umma_tmem_a_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return -4;
+    umma_tmem_a_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(reinterpret_cast<const uint32_t*>(a_words),
+                                                                reinterpret_cast<const uint8_t*>(b_img), D, status);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

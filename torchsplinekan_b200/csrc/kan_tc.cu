@@ -216,8 +216,8 @@ constexpr uint32_t FWD_SMEM_BYTES = FWD_SMEM_CTRL + FWD_CTRL_BYTES;
 static_assert(FWD_SMEM_BYTES <= 232448, "forward kernel shared memory exceeds 227 KB");
 
 struct FwdCtrl {
-    uint64_t fullA[FWD_A_STAGES], emptyA[FWD_A_STAGES];
-    uint64_t fullB[FWD_B_SLOTS], emptyB[FWD_B_SLOTS];
+    uint64_t fullA[5], emptyA[5];          // sized for both forward kernels
+    uint64_t fullB[6], emptyB[6];
     // per 256-column accumulator: its chain is complete / its columns have been drained.  Kept apart
     // so that one accumulator is drained while the MMAs of the other run.
     uint64_t chunkFull[2], drained[2];
@@ -521,6 +521,335 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                             const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
                             mbar_arrive_expect_tx(bar, TILE_B_BYTES);
                             bulk_g2s(sbase + FWD_SMEM_B + slot * TILE_B_BYTES, src + (size_t)term * TILE_B_BYTES,
+                                     TILE_B_BYTES, bar);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ===== teardown =====
+    if (*abort_flag) {
+        if (lane == 0) report_status(status, kStatusTimeout);
+        __nanosleep(100000);                   // let copies / MMAs in flight land
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    if (warp == MMA_WARP) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Forward kernel with the generated operand in TENSOR MEMORY.
+// The workers store their rows of A straight into tensor memory (tcgen05.st; lane = sample row, one
+// 32-bit column = two consecutive K elements), the MMA takes A from there (no shared-memory read
+// for it), and shared memory only carries the weight tiles.  Tile = 128 samples x 256 outputs (one
+// accumulator of 256 columns; four operand stages of 64 columns fill the rest), so every generated
+// tile serves 256 outputs instead of the 512 of the kernel above: it is the faster kernel for
+// layers of up to 256 outputs (measured, 8192 rows: 784 -> 256 0.216 against 0.229 ms, 256 -> 10
+// 0.077 against 0.087 ms) and the slower one beyond (1024 -> 1024 at 65536 rows: 3.9 against 2.9 ms:
+// twice the operand production and twice the weight-tile traffic per output).
+// ---------------------------------------------------------------------------
+constexpr int FTS_A_STAGES = 4, FTS_B_SLOTS = 6;                 // one operand stage per group of 4 worker warps
+static_assert(FTS_A_STAGES * 4 == WORKER_WARPS, "one operand stage per worker group");
+constexpr uint32_t FTS_TMEM_A = 256;
+constexpr uint32_t FTS_SMEM_B = 0;
+constexpr uint32_t FTS_SMEM_CTRL = FTS_SMEM_B + FTS_B_SLOTS * TILE_B_BYTES;
+constexpr uint32_t FTS_SMEM_BYTES = FTS_SMEM_CTRL + FWD_CTRL_BYTES;
+static_assert(FTS_SMEM_BYTES <= 232448, "forward kernel shared memory exceeds 227 KB");
+
+template <int NTERMS, bool WIDE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab, const uint8_t* __restrict__ wimg,
+                  float* __restrict__ y, int* __restrict__ status, const FwdParams P) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr bool SPLIT = (NTERMS == 3);
+    const uint32_t sbase = smem_u32(smem);
+    FwdCtrl* ctrl = reinterpret_cast<FwdCtrl*>(smem + FTS_SMEM_CTRL);
+    float* stab = reinterpret_cast<float*>(smem + FTS_SMEM_CTRL + 256);
+    volatile int* abort_flag = &ctrl->abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool shared_grid = grid_is_shared(tab, P.I, P.ti);
+    if (shared_grid && threadIdx.x < TAB_SMEM_FLOATS && threadIdx.x < P.ti.fs) stab[threadIdx.x] = tab[threadIdx.x];
+
+    if ((sbase & 1023u) != 0) {                 // swizzled tiles need 1024-byte alignment
+        if (threadIdx.x == 0) report_status(status, kStatusBadSmem);
+        return;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < FTS_A_STAGES; ++s) {
+            mbar_init(smem_u32(&ctrl->fullA[s]), WORKER_THREADS / FTS_A_STAGES);     // one group of worker warps
+            mbar_init(smem_u32(&ctrl->emptyA[s]), 1);
+        }
+        for (int s = 0; s < FTS_B_SLOTS; ++s) {
+            mbar_init(smem_u32(&ctrl->fullB[s]), 1);
+            mbar_init(smem_u32(&ctrl->emptyB[s]), 1);
+        }
+        for (int j = 0; j < 2; ++j) {
+            mbar_init(smem_u32(&ctrl->chunkFull[j]), 1);
+            mbar_init(smem_u32(&ctrl->drained[j]), WORKER_THREADS);
+        }
+        ctrl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    if (warp < WORKER_WARPS) {
+        // ===== workers: x -> basis / silu -> swizzled A tile; drain between chunks =====
+        const int quad = warp & 3;                        // TMEM lane quadrant = row group
+        const int part = warp >> 2;                       // which quarter of the k-block / column groups
+        const int row = quad * 32 + lane;
+        uint32_t it = 0, n_drained[2] = {0, 0};
+        bool ok = true;
+        // drain bookkeeping: the chunk that ended most recently and is not yet added to y
+        bool pend = false, pend_first = false;
+        int64_t pend_mt = 0;
+        int pend_op = 0;
+
+        auto drain = [&]() -> bool {
+            const int64_t n = pend_mt * BLOCK_M + row;
+#pragma unroll 1
+            for (int j = 0; j < 1; ++j) {
+                if (!mbar_wait(smem_u32(&ctrl->chunkFull[j]), n_drained[j] & 1u, abort_flag)) return false;
+                ++n_drained[j];
+                tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = part; c < BLOCK_N / 32; c += 4) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + j * BLOCK_N + c * 32, r);
+                    tmem_ld_wait();
+                    const int col0 = pend_op * BLOCK_N + c * 32;
+                    if (n < P.N && col0 < P.O)
+                        drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
+                }
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->drained[j]));
+            }
+            pend = false;
+            return true;
+        };
+
+        for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+            const int64_t mt = tile / P.n_otiles;
+            const int op = (int)(tile - mt * P.n_otiles);          // the 256-output tile
+            const int64_t n = mt * BLOCK_M + row;
+            const bool row_ok = n < P.N;
+            const float* xrow = x + (size_t)(row_ok ? n : 0) * P.I;
+            // The four groups of four worker warps take the k-blocks in turn: group g fills operand stage
+            // g with every fourth block (block counter it = g mod 4), a thread = one row of it, all eight
+            // chunks (chunk c of block kb is global chunk g = 8 kb + c; it belongs to feature g / cpf and
+            // holds its slots 8 (g % cpf) ..).  Four blocks are therefore in production at any time, and a
+            // thread has eight independent window evaluations to overlap.
+            const int cpf = WIDE ? P.ti.cpf : 1;
+            auto chunk_pair = [&](int kb, int p, int& f0, int& cw0, int& f1, int& cw1) {
+                const int g0 = kb * 8 + p * 2;
+                if (!WIDE) {
+                    f0 = g0; cw0 = 0; f1 = g0 + 1; cw1 = 0;
+                } else {
+                    f0 = g0 / cpf; cw0 = g0 - f0 * cpf;
+                    f1 = f0; cw1 = cw0 + 1;
+                    if (cw1 == cpf) { f1 = f0 + 1; cw1 = 0; }
+                }
+            };
+            for (int kb = 0; kb < P.kb_total; ++kb, ++it) {
+                const uint32_t stage = it % FTS_A_STAGES;
+                const bool chunk_start = (kb % P.chunk_kb) == 0;
+                if ((int)stage == part) {
+                    // operand stage in tensor memory: 32 columns of bf16 pairs (hi), then 32 (lo)
+                    const uint32_t a_hi = tmem_base + ((uint32_t)(quad * 32) << 16) + FTS_TMEM_A + stage * 64;
+                    const uint32_t a_lo = a_hi + 32;
+                    float xb[8];
+                    if (kb < P.kb_spline && !WIDE) load_x8(x, n, row_ok, P.I, kb * 8, P.vec_x != 0, xb);
+                    if (!mbar_wait(smem_u32(&ctrl->emptyA[stage]), ((it / FTS_A_STAGES) & 1u) ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    if (kb < P.kb_spline) {
+#pragma unroll
+                        for (int p = 0; p < 4; ++p) {
+                            int f0, cw0, f1, cw1;
+                            chunk_pair(kb, p, f0, cw0, f1, cw1);
+                            float x0, x1;
+                            if (!WIDE) {
+                                x0 = xb[2 * p];
+                                x1 = xb[2 * p + 1];
+                            } else {
+                                x0 = (row_ok && f0 < P.I) ? __ldg(xrow + f0) : 0.f;
+                                x1 = (row_ok && f1 < P.I) ? __ldg(xrow + f1) : 0.f;
+                            }
+                            const bool ok0 = row_ok && f0 < P.I, ok1 = row_ok && f1 < P.I;
+                            // features beyond I read the last feature's table; their rows are zeroed below
+                            const float* t0 = tab + (size_t)(f0 < P.I ? f0 : P.I - 1) * P.ti.fs;
+                            const float* t1 = tab + (size_t)(f1 < P.I ? f1 : P.I - 1) * P.ti.fs;
+                            uint4 hi0, lo0, hi1, lo1;
+                            Window w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x0)
+                                                   : eval_window<SPLIT, false, WIDE>(t0, P.ti, x0);
+                            place_window<SPLIT>(w, cw0, hi0, lo0);
+                            if (!WIDE || f1 != f0)                 // uniform over the warp
+                                w = shared_grid ? eval_window<SPLIT, true, WIDE>(stab, P.ti, x1)
+                                                : eval_window<SPLIT, false, WIDE>(t1, P.ti, x1);
+                            place_window<SPLIT>(w, cw1, hi1, lo1);
+                            const uint4 zero = make_uint4(0, 0, 0, 0);
+                            if (!ok0) { hi0 = zero; lo0 = zero; }
+                            if (!ok1) { hi1 = zero; lo1 = zero; }
+                            {
+                                const uint32_t wd[8] = {hi0.x, hi0.y, hi0.z, hi0.w, hi1.x, hi1.y, hi1.z, hi1.w};
+                                tmem_st_32x8(a_hi + p * 8, wd);
+                            }
+                            if (SPLIT) {
+                                const uint32_t wd[8] = {lo0.x, lo0.y, lo0.z, lo0.w, lo1.x, lo1.y, lo1.z, lo1.w};
+                                tmem_st_32x8(a_lo + p * 8, wd);
+                            }
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int p = 0; p < 4; ++p) {
+                            const int f0 = (kb - P.kb_spline) * 64 + p * 16;
+                            float xv[2][8];
+                            load_x8(x, n, row_ok, P.I, f0, P.vec_x != 0, xv[0]);
+                            load_x8(x, n, row_ok, P.I, f0 + 8, P.vec_x != 0, xv[1]);
+                            uint4 hi[2], lo[2];
+                            silu_chunk<SPLIT>(xv[0], hi[0], lo[0]);
+                            silu_chunk<SPLIT>(xv[1], hi[1], lo[1]);
+                            {
+                                const uint32_t wd[8] = {hi[0].x, hi[0].y, hi[0].z, hi[0].w,
+                                                        hi[1].x, hi[1].y, hi[1].z, hi[1].w};
+                                tmem_st_32x8(a_hi + p * 8, wd);
+                            }
+                            if (SPLIT) {
+                                const uint32_t wd[8] = {lo[0].x, lo[0].y, lo[0].z, lo[0].w,
+                                                        lo[1].x, lo[1].y, lo[1].z, lo[1].w};
+                                tmem_st_32x8(a_lo + p * 8, wd);
+                            }
+                        }
+                    }
+                    tmem_st_wait();
+                    tc_fence_before_sync();
+                    mbar_arrive(smem_u32(&ctrl->fullA[stage]));
+                }
+                // The previous chunk is drained only after the first k-block of the next one has
+                // been produced, so the MMA pipe restarts without waiting for the producers.
+                if (pend && chunk_start) {
+                    if (!drain()) {
+                        ok = false;
+                        break;
+                    }
+                }
+                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                    pend = true;
+                    pend_first = kb < P.chunk_kb;
+                    pend_mt = mt;
+                    pend_op = op;
+                }
+            }
+        }
+        if (ok && pend) drain();
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            // ===== MMA issue =====
+            constexpr uint32_t idesc = make_idesc_bf16(BLOCK_N, false, false);
+            constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
+            uint32_t it = 0, bslot = 0, n_chunks[2] = {0, 0};
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+                const int nsub = 1;
+                for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
+                    const uint32_t stage = it % FTS_A_STAGES;
+                    const uint32_t a_hi = tmem_base + FTS_TMEM_A + stage * 64;
+                    const uint32_t a_lo = a_hi + 32;
+                    const bool chunk_start = (kb % P.chunk_kb) == 0;
+                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total;
+                    if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FTS_A_STAGES) & 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    for (int j = 0; j < nsub && ok; ++j) {
+                        const uint32_t d_tmem = tmem_base + j * BLOCK_N;
+                        if (chunk_start && n_chunks[j] > 0) {
+                            // this accumulator may be overwritten only after the workers have drained it
+                            if (!mbar_wait(smem_u32(&ctrl->drained[j]), (n_chunks[j] - 1) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                        }
+                        const uint32_t slot_h = bslot % FTS_B_SLOTS;
+                        if (!mbar_wait(smem_u32(&ctrl->fullB[slot_h]), (bslot / FTS_B_SLOTS) & 1u, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t b_hi = sbase + FTS_SMEM_B + slot_h * TILE_B_BYTES;
+#pragma unroll
+                        for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                            mma_f16_ts(d_tmem, a_hi + ks * 8, sdesc_at(dbase, b_hi + ks * 32), idesc,
+                                       (!chunk_start || ks > 0) ? 1u : 0u);
+                        if (SPLIT) {
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ts(d_tmem, a_lo + ks * 8, sdesc_at(dbase, b_hi + ks * 32), idesc, 1u);
+                        }
+                        mma_commit(smem_u32(&ctrl->emptyB[slot_h]));
+                        ++bslot;
+                        if (SPLIT) {
+                            const uint32_t slot_l = bslot % FTS_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->fullB[slot_l]), (bslot / FTS_B_SLOTS) & 1u, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t b_lo = sbase + FTS_SMEM_B + slot_l * TILE_B_BYTES;
+#pragma unroll
+                            for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks)
+                                mma_f16_ts(d_tmem, a_hi + ks * 8, sdesc_at(dbase, b_lo + ks * 32), idesc, 1u);
+                            mma_commit(smem_u32(&ctrl->emptyB[slot_l]));
+                            ++bslot;
+                        }
+                        if (chunk_end) {
+                            // this accumulator's chain is complete: its drain overlaps the MMAs of the other
+                            mma_commit(smem_u32(&ctrl->chunkFull[j]));
+                            ++n_chunks[j];
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit(smem_u32(&ctrl->emptyA[stage]));
+                }
+            }
+        }
+    } else {
+        if (lane == 0) {
+            // ===== bulk-copy producer for weight tiles =====
+            uint32_t bslot = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+                const int64_t mt = tile / P.n_otiles;
+                const int op = (int)(tile - mt * P.n_otiles);
+                for (int kb = 0; kb < P.kb_total && ok; ++kb) {
+                    {
+                        const uint8_t* src = wimg + ((size_t)op * P.kb_total + kb) * (2 * (size_t)TILE_B_BYTES);
+                        for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
+                            const uint32_t slot = bslot % FTS_B_SLOTS;
+                            if (!mbar_wait(smem_u32(&ctrl->emptyB[slot]), ((bslot / FTS_B_SLOTS) & 1u) ^ 1u,
+                                           abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            const uint32_t bar = smem_u32(&ctrl->fullB[slot]);
+                            mbar_arrive_expect_tx(bar, TILE_B_BYTES);
+                            bulk_g2s(sbase + FTS_SMEM_B + slot * TILE_B_BYTES, src + (size_t)term * TILE_B_BYTES,
                                      TILE_B_BYTES, bar);
                         }
                     }
@@ -1563,6 +1892,10 @@ cudaError_t tc_build_table(const float* grid, float* tab, const LayerShape& s, c
 
 // Shorter accumulation chains (never longer than the built-in lengths, so the stated tolerance
 // always holds); 0 keeps a value.
+// Which forward kernel runs: -1 = by shape, 0 = generated operand in shared memory, 1 = in tensor memory.
+int g_fwd_variant = -1;
+void tc_set_forward_variant(int v) { g_fwd_variant = v < 0 ? -1 : (v > 0 ? 1 : 0); }
+
 void tc_set_chunks(int fwd_kb, int bwd_kb, int dx_kb) {
     auto clamp = [](int v, int cur, int max) { return v <= 0 ? cur : (v < 1 ? 1 : (v > max ? max : v)); };
     g_fwd_chunk = clamp(fwd_kb, g_fwd_chunk, kFwdChunkKb);
@@ -1621,9 +1954,20 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     P.vec_y = ((s.O & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
     P.ti = ti;
     cudaError_t e = cudaSuccess;
+    // layers of up to 256 outputs (a single output tile) gain from the tensor-memory operand: the generated
+    // tile serves one accumulator either way, and shared memory is left to the weight tiles
+    const bool operand_in_tmem = g_fwd_variant < 0 ? P.n_otiles == 1 : g_fwd_variant == 1;
+    if (operand_in_tmem) P.n_tiles = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_otiles;      // one 256-output tile each
     const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
 #define KAN_FWD(NT, W)                                                                                         \
     do {                                                                                                      \
+        if (operand_in_tmem) {                                                                                \
+            e = ensure_dynamic_smem<tc_forward_ts_kernel<NT, W>>((int)FTS_SMEM_BYTES);                        \
+            if (e == cudaSuccess)                                                                             \
+                tc_forward_ts_kernel<NT, W><<<blocks, TC_THREADS, FTS_SMEM_BYTES, st>>>(x, tab, wimg, y,      \
+                                                                                         status, P);         \
+            break;                                                                                            \
+        }                                                                                                     \
         e = ensure_dynamic_smem<tc_forward_kernel<NT, W>>((int)FWD_SMEM_BYTES);                               \
         if (e == cudaSuccess)                                                                                 \
             tc_forward_kernel<NT, W><<<blocks, TC_THREADS, FWD_SMEM_BYTES, st>>>(x, tab, wimg, y, status, P); \
