@@ -290,3 +290,29 @@ def test_data_parallel_entry_points_validate_before_any_launch():
     assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f64, 65536, 1024, 1, 5, 3) == 0
     assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f32, 65536, 1024, 1, 8, 3) == 0
     assert _native.workspace_bytes(_native.OP_BASIS, _native.MODE_AUTO, f32, 1024, 64, 1, 5, 3) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+def test_penalty_head_closed_form_matches_dense_formulation(dtype):
+    """The scalar head of the activation regulariser with its gradient in closed form against
+    autograd through the dense formulation (reference_backend.py:149-170): generic edge means,
+    some exactly zero, all zero; and second derivatives through the function."""
+    from torchsplinekan_b200 import fused
+    from torchsplinekan_b200.dense_backend import regularization_from_edge_means
+    torch.manual_seed(0)
+    cases = [torch.rand(5, 7, dtype=dtype) + 0.01,
+             torch.cat([torch.zeros(2, 7, dtype=dtype), torch.rand(3, 7, dtype=dtype)]),
+             torch.zeros(3, 4, dtype=dtype)]
+    tol = 1e-14 if dtype == torch.float64 else 1e-6
+    for a0 in cases:
+        a = a0.clone().requires_grad_()
+        (want,) = torch.autograd.grad(regularization_from_edge_means(a, 0.7, 1.3) * 2.0, a)
+        b = a0.clone().requires_grad_()
+        out = fused.penalty_from_edge_means(b, 0.7, 1.3)
+        (got,) = torch.autograd.grad(out * 2.0, b)
+        assert float((out.detach() - regularization_from_edge_means(a0, 0.7, 1.3)).abs()) <= tol
+        assert float((got - want).abs().max()) <= tol
+    if dtype == torch.float64:
+        a = (torch.rand(4, 3, dtype=dtype) + 0.05).requires_grad_()
+        f = lambda t: fused.penalty_from_edge_means(t, 0.7, 1.3)
+        assert torch.autograd.gradcheck(f, (a,)) and torch.autograd.gradgradcheck(f, (a,))

@@ -118,6 +118,56 @@ class EdgeAbsMeanX(torch.autograd.Function):
                 dbw if (need_bw and has_base) else None, dW if need_W else None)
 
 
+class PenaltyFromEdgeMeans(torch.autograd.Function):
+    """``mu1 * A + mu2 * S`` with ``A = sum a``, ``p = a / A``, ``S = -sum p log p`` (the scalar head of the
+    activation regulariser, reference_backend.py:149-170) with its gradient in closed form,
+    ``d/da_j = mu1 - mu2 (log p_j + S) / A``: a handful of small kernels instead of the twenty the chain rule
+    through clamp / div / log / mul / sum launches.  The backward is written with differentiable
+    operations, so higher-order derivatives work.  Same clamps as the dense formulation: ``A`` and
+    ``p`` at the dtype's smallest normal (entries clamped there get no entropy gradient)."""
+
+    @staticmethod
+    def forward(ctx, a, mu1, mu2):
+        tiny = torch.finfo(a.dtype).tiny
+        total = a.sum()
+        p = (a / total.clamp(min=tiny)).clamp(min=tiny)
+        logp = p.log()
+        entropy = -(p * logp).sum()
+        ctx.save_for_backward(a)
+        ctx.mu = (float(mu1), float(mu2))
+        return mu1 * total + mu2 * entropy
+
+    @staticmethod
+    def backward(ctx, g):
+        (a,) = ctx.saved_tensors
+        mu1, mu2 = ctx.mu
+        if torch.is_grad_enabled():                       # create_graph: let autograd differentiate the plain formula
+            with torch.enable_grad():
+                a_ = a.detach().requires_grad_(True) if not a.requires_grad else a
+                tiny = torch.finfo(a.dtype).tiny
+                total = a_.sum()
+                p = (a_ / total.clamp(min=tiny)).clamp(min=tiny)
+                val = mu1 * total + mu2 * (-(p * p.log()).sum())
+                (ga,) = torch.autograd.grad(val, a_, g, create_graph=True)
+            return ga, None, None
+        tiny = torch.finfo(a.dtype).tiny
+        total = a.sum()
+        safe = total.clamp(min=tiny)
+        q = a / safe
+        p = q.clamp(min=tiny)
+        logp = p.log()
+        entropy = -(p * logp).sum()
+        # entries clamped at `tiny` only feel the entropy through A: mu2 (1 - S) / A; with A itself
+        # clamped (an all-zero layer) nothing but mu1 is left
+        dead = mu1 + mu2 * (1.0 - entropy) / safe * (total >= tiny)
+        ga = torch.where(q >= tiny, mu1 - mu2 * (logp + entropy) / safe, dead)
+        return g * ga, None, None
+
+
+def penalty_from_edge_means(a: torch.Tensor, mu1: float, mu2: float) -> torch.Tensor:
+    return PenaltyFromEdgeMeans.apply(a, mu1, mu2)
+
+
 def edge_abs_mean_from_input(x: torch.Tensor, s: Optional[torch.Tensor], grid: torch.Tensor, k: int,
                              bw: Optional[torch.Tensor], W: torch.Tensor) -> torch.Tensor:
     return EdgeAbsMeanX.apply(x, s, grid, k, bw, W)

@@ -184,7 +184,7 @@ class KANLinear(nn.Module):
         xf = x.reshape(-1, self.in_features)
         impl = self._resolve_reg_impl(reg_impl, xf)
         if impl == "fused":
-            return regularization_from_edge_means(self._edge_abs_mean_from_input(xf), reg_act, reg_entropy)
+            return _fused.penalty_from_edge_means(self._edge_abs_mean_from_input(xf), reg_act, reg_entropy)
         s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         a = self._edge_abs_mean(xf, s, H, self._ref.effective_spline_weight(), impl, chunk_size)
@@ -221,7 +221,7 @@ class KANLinear(nn.Module):
                 y = self._cuda_forward(xf)
             self.last_backend = "cuda"
             a = self._edge_abs_mean_from_input(xf)
-            return y.reshape(lead + (self.out_features,)), regularization_from_edge_means(a, reg_act, reg_entropy)
+            return y.reshape(lead + (self.out_features,)), _fused.penalty_from_edge_means(a, reg_act, reg_entropy)
         s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         W = self._ref.effective_spline_weight()
