@@ -489,6 +489,27 @@ def run_gpu_arm(args):
     ms_e2e = float(ms_t.item())
     assert e2e_state["last"] is not None and math.isfinite(e2e_state["last"])
 
+    # the same resident step with single bf16 operands (one MMA per product instead of three): a
+    # second, lower-precision data point beside the headline
+    x1_line = None
+    if world == 1 and not args.mode:
+        with torch.no_grad():
+            y3 = layer(x_dev)
+        prev_mode = _C.get_mma_mode()
+        _C.set_mma_mode("bf16x1")
+        try:
+            for _ in range(3):
+                step_resident()
+            n1 = min(args.steps, 10)
+            ms1 = timed(step_resident, n1) / n1
+            with torch.no_grad():
+                y1 = layer(x_dev)
+            x1_line = {"value": args.batch / (ms1 * 1e-3), "unit": "samples/s", "ms_per_step": ms1,
+                       "stated_tolerance": 1e-2,
+                       "max_error_vs_bf16x3_rel_to_max": float((y1 - y3).abs().max() / y3.abs().max())}
+        finally:
+            _C.set_mma_mode(prev_mode)
+
     _C.check_status()
     if bucket is not None:
         bucket.check()
@@ -563,6 +584,8 @@ def run_gpu_arm(args):
                                   "backward) instead of the four elementwise passes of y.square().sum(); same maths")
         if grad_check is not None:
             line["grad_check"] = grad_check
+        if x1_line is not None:
+            line["bf16x1"] = x1_line
         if world == 1 and not args.no_cpu_baseline:
             # the reference itself, in child processes (it cannot be imported beside this package)
             child = _child_json(["--impl", "reference", "--steps", "2", "--warmup", "1",
