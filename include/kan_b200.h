@@ -197,6 +197,15 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void
  * about a third faster.  Process-wide; returns KANB200_OK. */
 KANB200_API int kanb200_set_edge_sign_recheck(int on);
 
+/* Scalar head of the activation regulariser from the per-edge statistic a (n = O*I entries, any shape):
+ *   value[0] = mu1 * A + mu2 * S,  A = sum a,  p = max(a / max(A, tiny), tiny),  S = -sum p log p,
+ *   grad[j]  = d value / d a_j = mu1 - mu2 (log p_j + S) / A   (NULL = not needed)
+ * (regularization_from_edge_means, spline_kan/reference_backend.py:149-170, which the reference
+ * evaluates as a chain of tensor operations and differentiates through autograd).  One launch,
+ * sums in float64; tiny = the dtype's smallest normal, as in the reference's clamps. */
+KANB200_API int kanb200_edge_penalty(int dtype, const void* a, int64_t n, double mu1, double mu2, void* value,
+                                     void* grad, void* stream);
+
 /* Which tensor-core forward kernel runs (same results): 1 = the generated operand is stored in tensor
  * memory and the MMA reads it from there (shared memory only carries the weight tiles; one
  * 256-output tile per generated tile), 0 = generated operand in shared memory, two 256-output

@@ -626,6 +626,42 @@ def _edge_backward_dense64(case, ga, base):
     return phi, gx, dbw, dW
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_edge_penalty_one_launch_matches_dense_formulation(dtype):
+    """kanb200_edge_penalty (value and closed-form gradient of the regulariser's scalar head in one
+    launch) against autograd through the dense tensor formulation (reference_backend.py:149-170):
+    generic edge means, some exactly zero, all zero, a statistic of a realistic size; and the
+    autograd function that uses it."""
+    from torchsplinekan_b200 import _native as nat, fused
+    from torchsplinekan_b200.dense_backend import regularization_from_edge_means
+    torch.manual_seed(0)
+    cases = [torch.rand(5, 7, dtype=dtype) + 0.01,
+             torch.cat([torch.zeros(2, 7, dtype=dtype), torch.rand(3, 7, dtype=dtype)]),
+             torch.zeros(3, 4, dtype=dtype),
+             torch.rand(256, 784, dtype=dtype) * 0.05]
+    tol = 1e-13 if dtype == torch.float64 else 2e-6
+    for a0 in cases:
+        a = a0.clone().requires_grad_()
+        want_v = regularization_from_edge_means(a, 0.7, 1.3)
+        (want_g,) = torch.autograd.grad(want_v, a)
+        got_v, got_g = nat.edge_penalty(a0.cuda(), 0.7, 1.3)
+        scale = max(1.0, float(want_v.detach().abs()))
+        assert abs(float(got_v) - float(want_v)) <= tol * scale
+        gscale = max(1.0, float(want_g.abs().max()))
+        assert float((got_g.cpu() - want_g).abs().max()) <= tol * gscale * 4
+        only_v, none_g = nat.edge_penalty(a0.cuda(), 0.7, 1.3, need_grad=False)
+        assert none_g is None and float(only_v) == float(got_v)
+        b = a0.cuda().requires_grad_()
+        out = fused.penalty_from_edge_means(b, 0.7, 1.3)
+        (gb,) = torch.autograd.grad(out * 2.0, b)
+        assert float((gb.cpu() - 2.0 * want_g).abs().max()) <= tol * gscale * 8
+    if dtype == torch.float64:
+        a = (torch.rand(4, 3, dtype=dtype, device="cuda") + 0.05).requires_grad_()
+        f = lambda t: fused.penalty_from_edge_means(t, 0.7, 1.3)
+        assert torch.autograd.gradcheck(f, (a,)) and torch.autograd.gradgradcheck(f, (a,))
+
+
 @pytest.mark.parametrize("N,I,O,G,k,base", [
     (1024, 16, 256, 5, 3, True), (777, 37, 130, 5, 3, True), (2048, 8, 64, 4, 2, False), (300, 5, 16, 7, 1, True),
     (4096, 64, 256, 5, 3, True)])

@@ -55,6 +55,8 @@ SIGNATURES = {
     "kanb200_set_forward_variant": (_c_int, [_c_int]),
     "kanb200_set_edge_sign_recheck": (_c_int, [_c_int]),
     "kanb200_get_edge_sign_recheck": (_c_int, []),
+    "kanb200_edge_penalty": (_c_int, [_c_int, _c_void_p, _c_i64, ctypes.c_double, ctypes.c_double, _c_void_p, _c_void_p,
+                                      _c_void_p]),
     "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                                _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
@@ -345,6 +347,18 @@ def edge_abs_mean_x(x, s, grid, bw, W, k: int, mode: int = MODE_AUTO) -> torch.T
         _check(lib().kanb200_edge_abs_mean_x(_code(x.dtype), mode, _p(x), _p(s), _p(grid), _p(bw), _p(W), _p(a),
                                              N, I, O, G, k, _p(ws), 0 if ws is None else ws.numel(), _stream(dev)))
     return a
+
+
+def edge_penalty(a: torch.Tensor, mu1: float, mu2: float, need_grad: bool = True):
+    """``(mu1 sum(a) + mu2 entropy(a / sum(a)), d/da)`` from one launch (gradient None when not needed)."""
+    dev = _need_cuda(a)
+    a = a.contiguous()
+    value = torch.empty((), dtype=a.dtype, device=dev)
+    grad = torch.empty_like(a) if need_grad else None
+    with _OnDevice(dev):
+        _check(lib().kanb200_edge_penalty(_code(a.dtype), _p(a), a.numel(), float(mu1), float(mu2), _p(value),
+                                          _p(grad), _stream(dev)))
+    return value, grad
 
 
 def edge_abs_mean_x_backward(ga, x, s, grid, bw, W, k: int, need_x=True, need_s=True, need_bw=True, need_W=True,

@@ -70,6 +70,11 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
                               T* ds, T* dH, T* dbw, T* dW,
                               int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// value = mu1 sum(a) + mu2 entropy(a / sum(a)) and its gradient with respect to a (NULL = not needed):
+// the scalar head of the activation regulariser in one launch.
+template <typename T>
+cudaError_t edge_penalty(const T* a, int64_t n, double mu1, double mu2, T* value, T* grad, cudaStream_t st);
+
 // The same operators straight from the layer input x (no H, no dH): see kan_reg.cu.  Scratch as for
 // edge_abs_mean_fwd / _bwd.
 template <typename T>

@@ -602,6 +602,64 @@ cudaError_t edge_static_scratch(void** ptr) {
     return cudaSuccess;
 }
 
+// ---------------------------------------------------------------------------
+// Scalar head of the activation regulariser (reference: regularization_from_edge_means,
+// spline_kan/reference_backend.py:149-170):
+//   value = mu1 A + mu2 S,   A = sum a,   p = max(a / max(A, tiny), tiny),   S = -sum p log p
+// and its gradient in closed form,  d value / d a_j = mu1 - mu2 (log p_j + S) / A  (entries clamped at
+// `tiny` only feel the entropy through A: mu1 + mu2 (1 - S) / A; with A itself clamped nothing but mu1
+// is left).  One block, three passes over a (the statistic has O x I entries: at most a few million),
+// sums in float64: one launch instead of the twenty-odd elementwise / reduction launches of the
+// tensor formulation.
+// ---------------------------------------------------------------------------
+constexpr int PEN_THREADS = 1024;
+
+__device__ __forceinline__ double block_sum(double v, double* red) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();                       // red may still be read from the previous call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int w = 0; w < PEN_THREADS / 32; ++w) t += red[w];    // same order in every thread
+    return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PEN_THREADS)
+edge_penalty_kernel(const T* __restrict__ a, int64_t n, double mu1, double mu2, T tiny, T* __restrict__ value,
+                    T* __restrict__ grad) {
+    __shared__ double red[PEN_THREADS / 32];
+    double part = 0.0;
+    for (int64_t j = threadIdx.x; j < n; j += PEN_THREADS) part += (double)a[j];
+    const T total = (T)block_sum(part, red);
+    const T safe = total > tiny ? total : tiny;
+    part = 0.0;
+    for (int64_t j = threadIdx.x; j < n; j += PEN_THREADS) {
+        const T q = a[j] / safe;
+        const T pj = q > tiny ? q : tiny;
+        part += (double)(pj * log(pj));
+    }
+    const T entropy = (T)(-block_sum(part, red));
+    if (threadIdx.x == 0) *value = (T)(mu1 * (double)total + mu2 * (double)entropy);
+    if (!grad) return;
+    const T m1 = (T)mu1, m2 = (T)mu2;
+    const T dead = m1 + (total >= tiny ? m2 * ((T)1 - entropy) / safe : (T)0);
+    for (int64_t j = threadIdx.x; j < n; j += PEN_THREADS) {
+        const T q = a[j] / safe;
+        grad[j] = q >= tiny ? m1 - m2 * (log(q) + entropy) / safe : dead;
+    }
+}
+
+template <typename T>
+cudaError_t edge_penalty(const T* a, int64_t n, double mu1, double mu2, T* value, T* grad, cudaStream_t st) {
+    const T tiny = sizeof(T) == 4 ? (T)1.17549435e-38 : (T)2.2250738585072014e-308;
+    edge_penalty_kernel<T><<<1, PEN_THREADS, 0, st>>>(a, n, mu1, mu2, tiny, value, grad);
+    return cudaGetLastError();
+}
+template cudaError_t edge_penalty<float>(const float*, int64_t, double, double, float*, float*, cudaStream_t);
+template cudaError_t edge_penalty<double>(const double*, int64_t, double, double, double*, double*, cudaStream_t);
+
 #define KAN_INSTANTIATE(T)                                                                               \
     template size_t edge_workspace<T>(int64_t, int, int, int, bool);                                     \
     template cudaError_t edge_abs_mean_fwd<T>(const T*, const T*, const T*, const T*, T*, int64_t, int,  \

@@ -522,6 +522,19 @@ Tensor edge_abs_mean_x(const Tensor& x, const Tensor& s, const Tensor& grid, con
     return a;
 }
 
+// Scalar head of the activation regulariser and its gradient with respect to the edge statistic, in one
+// launch (kanb200_edge_penalty).
+std::tuple<Tensor, Tensor> edge_penalty(const Tensor& a, double mu1, double mu2) {
+    TORCH_CHECK(a.is_cuda() && a.numel() > 0, "edge_penalty: a must be a non-empty CUDA tensor");
+    c10::cuda::CUDAGuard guard(a.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const Tensor ac = a.contiguous();
+    Tensor value = at::empty({}, a.options()), grad = at::empty_like(ac);
+    check_rc(kanb200_edge_penalty(dtype_code(a), ac.data_ptr(), ac.numel(), mu1, mu2, value.data_ptr(),
+                                  grad.data_ptr(), st));
+    return {value, grad.view(a.sizes())};
+}
+
 std::tuple<Tensor, Tensor, Tensor, Tensor> edge_abs_mean_x_backward(const Tensor& grad_a, const Tensor& x, const Tensor& s,
                                                                     const Tensor& grid, const Tensor& base_weight,
                                                                     const Tensor& W, int64_t k, bool need_x, bool need_s,
@@ -891,6 +904,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("edge_abs_mean_x", &edge_abs_mean_x, py::arg("x"), py::arg("s"), py::arg("grid"), py::arg("base_weight"),
           py::arg("W"), py::arg("spline_order"),
           "a[o,i] = mean_n |s bw + <B(x), W>| straight from x; s empty = silu(x)");
+    m.def("edge_penalty", &edge_penalty, py::arg("a"), py::arg("mu1"), py::arg("mu2"),
+          "(mu1 sum(a) + mu2 entropy(a / sum(a)), its gradient with respect to a) in one launch");
     m.def("edge_abs_mean_x_backward",
           [](const Tensor& ga, const Tensor& x, const Tensor& s, const Tensor& grid, const Tensor& bw, const Tensor& W,
              int64_t k, bool need_x, bool need_s, bool need_bw, bool need_W) {
