@@ -849,8 +849,18 @@ def run_config(args):
         b.record()
         torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
-    ms = statistics.median(times)
-    print(json.dumps({"config": name, "ms_per_step": ms, "samples_per_s": rows / ms * 1e3, "steps": args.steps,
+    ms_synced = statistics.median(times)
+    # the same steps back to back, as a training loop issues them (no host synchronisation between steps):
+    # for the small configurations the host's launch work of step t+1 then overlaps the kernels of step t
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    print(json.dumps({"config": name, "ms_per_step": ms, "ms_per_step_synchronised": ms_synced,
+                      "samples_per_s": rows / ms * 1e3, "steps": args.steps,
                       "backends": [getattr(l, "last_backend", None) for l in getattr(net, "layers", [net])]}),
           flush=True)
 

@@ -201,6 +201,44 @@ __device__ __forceinline__ void drain_row32(float* __restrict__ dst, const uint3
     }
 }
 
+// The same for the 32 rows of a warp at once, with full 128-byte lines per request: after a load of
+// tensor memory lane l holds 32 columns of row l, so a store or reduction per lane touches 16 bytes in
+// each of 32 rows.  Three butterfly exchanges (lane bit 2 + t <-> slot bit t) re-sort the 8 groups of 4
+// columns so that slot q of lane 4 b + a holds columns 4b .. 4b+3 of row 4 q + a; every instruction then
+// covers four rows with 128 contiguous bytes each (measured on the whole y of 65536 x 1024: 2.36 against
+// 1.32 TB/s of reductions).  All 32 rows and columns must be valid and 16-byte aligned.
+__device__ __forceinline__ void drain_rows32_warp(float* __restrict__ warp_dst, size_t ld, uint32_t (&r)[32], int lane,
+                                                  bool first) {
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const int lane_bit = 4 << t, slot_bit = 1 << t;
+        const bool up = (lane & lane_bit) != 0;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s & slot_bit) continue;
+            const int s2 = s | slot_bit;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t send = up ? r[4 * s + w] : r[4 * s2 + w];
+                const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, lane_bit);
+                if (up) r[4 * s + w] = recv;
+                else r[4 * s2 + w] = recv;
+            }
+        }
+    }
+    float* dst = warp_dst + (size_t)(lane & 3) * ld + 4 * (lane >> 2);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        float* d = dst + (size_t)(4 * q) * ld;
+        if (first)
+            *reinterpret_cast<float4*>(d) = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+        else
+            red_add_v4(d, __uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                       __uint_as_float(r[4 * q + 3]));
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Forward kernel:  y[n, o] = sum_c A[n, c] W[o, c]
 // ---------------------------------------------------------------------------
@@ -306,7 +344,10 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + j * BLOCK_N + c * 32, r);
                     tmem_ld_wait();
                     const int col0 = (pend_op * 2 + j) * BLOCK_N + c * 32;
-                    if (n < P.N && col0 < P.O)
+                    const int64_t n0 = n - lane;                   // first of the warp's 32 rows
+                    if (P.vec_y && n0 + 32 <= P.N && col0 + 32 <= P.O)        // uniform over the warp
+                        drain_rows32_warp(y + (size_t)n0 * P.O + col0, (size_t)P.O, r, lane, pend_first);
+                    else if (n < P.N && col0 < P.O)
                         drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
                 }
                 tc_fence_before_sync();
@@ -630,7 +671,10 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                     tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + j * BLOCK_N + c * 32, r);
                     tmem_ld_wait();
                     const int col0 = pend_op * BLOCK_N + c * 32;
-                    if (n < P.N && col0 < P.O)
+                    const int64_t n0 = n - lane;                   // first of the warp's 32 rows
+                    if (P.vec_y && n0 + 32 <= P.N && col0 + 32 <= P.O)        // uniform over the warp
+                        drain_rows32_warp(y + (size_t)n0 * P.O + col0, (size_t)P.O, r, lane, pend_first);
+                    else if (n < P.N && col0 < P.O)
                         drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
                 }
                 tc_fence_before_sync();
