@@ -20,10 +20,10 @@ except ImportError as exc:            # no fallback: say how to build and stop
         f"This package has no fallback implementation.  [{exc}]") from exc
 from .kan_linear import KANLinear
 from .kan import KAN
-from .data_parallel import GradientBucket, HostBatchPrefetcher, shard_rows
+from .data_parallel import GradientBucket, HostBatchPrefetcher, global_edge_means, shard_rows
 from .pruning import PruneResult, prune_nodes
 
 __version__ = "0.1.0"
 
-__all__ = ["KANLinear", "KAN", "PruneResult", "prune_nodes", "GradientBucket", "HostBatchPrefetcher", "shard_rows",
+__all__ = ["KANLinear", "KAN", "PruneResult", "prune_nodes", "GradientBucket", "HostBatchPrefetcher", "shard_rows", "global_edge_means",
            "__version__"]

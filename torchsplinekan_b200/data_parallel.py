@@ -35,6 +35,62 @@ def shard_rows(n_rows: int, world_size: int, rank: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
+class _ScaleThenAllReduce(torch.autograd.Function):
+    """``out = all_reduce_sum(weight * t)`` (weight: this rank's own scalar).  Its adjoint is
+    :class:`_AllReduceThenScale` and vice versa, so derivatives of any order go through the
+    collective."""
+
+    @staticmethod
+    def forward(ctx, t, weight, group):
+        ctx.group = group
+        ctx.save_for_backward(weight)
+        out = (t * weight).contiguous()
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (weight,) = ctx.saved_tensors
+        return _AllReduceThenScale.apply(g, weight, ctx.group), None, None
+
+
+class _AllReduceThenScale(torch.autograd.Function):
+    """``out = weight * all_reduce_sum(t)``: the adjoint of :class:`_ScaleThenAllReduce`."""
+
+    @staticmethod
+    def forward(ctx, t, weight, group):
+        ctx.group = group
+        ctx.save_for_backward(weight)
+        out = t.contiguous().clone()
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+        return out * weight
+
+    @staticmethod
+    def backward(ctx, g):
+        (weight,) = ctx.saved_tensors
+        return _ScaleThenAllReduce.apply(g, weight, ctx.group), None, None
+
+
+def global_edge_means(a_local: torch.Tensor, n_local_rows: int,
+                      group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Per-edge mean |phi| of the GLOBAL batch from each rank's statistic of its own rows:
+    ``a[o, i] = sum_r (N_r / N) a_r[o, i]`` (one all-reduce of ``[O, I]`` values; the row counts
+    travel in a second, one-element all-reduce, so ragged shards are weighted correctly).
+
+    With gradient all-reduce alone every rank evaluates the regulariser on its shard, and because
+    the entropy term is not linear in ``a`` the sum of those penalties is not the penalty of the
+    whole batch.  Feeding the result of this function to the penalty instead makes every rank
+    evaluate the whole-batch penalty; its backward all-reduces the incoming gradient and scales it by
+    ``N_r / N``, so summing (or averaging) the ranks' parameter gradients afterwards gives exactly
+    the gradient of (the sum, or the average, over ranks of) the per-rank losses.  A rank that adds
+    the penalty to a loss whose gradients are SUMMED over ``P`` ranks scales it by ``1 / P``."""
+    count = torch.tensor([float(n_local_rows)], dtype=torch.float64, device=a_local.device)
+    total = count.clone()
+    dist.all_reduce(total, op=dist.ReduceOp.SUM, group=group)
+    weight = (count / total).to(a_local.dtype)              # stays on the device: no host synchronisation
+    return _ScaleThenAllReduce.apply(a_local, weight, group)
+
+
 def _layer_params(layer: nn.Module) -> List[nn.Parameter]:
     seen, out = set(), []
     for p in layer.parameters():

@@ -171,9 +171,10 @@ class KANLinear(nn.Module):
     # -- regularisation ----------------------------------------------------
     def regularization_loss(self, reg_act: float = 1.0, reg_entropy: float = 1.0, *,
                             x: Optional[torch.Tensor] = None, mode: str = "activation",
-                            reg_impl: str = "auto", chunk_size: int = 1024) -> torch.Tensor:
+                            reg_impl: str = "auto", chunk_size: int = 1024, reg_group=None) -> torch.Tensor:
         """Scalar sparsity penalty (kan_linear.py:275-334).  ``mode="activation"`` needs ``x``;
-        ``reg_impl`` selects how mean|phi| is evaluated (see :meth:`forward_with_regularization`)."""
+        ``reg_impl`` selects how mean|phi| is evaluated and ``reg_group`` whether the statistic is
+        taken over the global batch (see :meth:`forward_with_regularization`)."""
         if mode not in ("activation", "coefficient"):
             raise ValueError(f"mode must be 'activation' or 'coefficient', got {mode!r}")
         if mode == "coefficient":
@@ -184,15 +185,25 @@ class KANLinear(nn.Module):
         xf = x.reshape(-1, self.in_features)
         impl = self._resolve_reg_impl(reg_impl, xf)
         if impl == "fused":
-            return _fused.penalty_from_edge_means(self._edge_abs_mean_from_input(xf), reg_act, reg_entropy)
+            a = self._across_ranks(self._edge_abs_mean_from_input(xf), xf, reg_group)
+            return _fused.penalty_from_edge_means(a, reg_act, reg_entropy)
         s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         a = self._edge_abs_mean(xf, s, H, self._ref.effective_spline_weight(), impl, chunk_size)
-        return regularization_from_edge_means(a, reg_act, reg_entropy)
+        return regularization_from_edge_means(self._across_ranks(a, xf, reg_group), reg_act, reg_entropy)
+
+    @staticmethod
+    def _across_ranks(a: torch.Tensor, x_flat: torch.Tensor, reg_group) -> torch.Tensor:
+        """The edge statistic of the global batch when a process group is given (one all-reduce of
+        ``[O, I]`` values, weighted by the ranks' row counts), else ``a`` itself."""
+        if reg_group is None:
+            return a
+        from .data_parallel import global_edge_means
+        return global_edge_means(a, x_flat.shape[0], None if reg_group is True else reg_group)
 
     def forward_with_regularization(self, x: torch.Tensor, reg_act: float = 1.0, reg_entropy: float = 1.0, *,
-                                    mode: str = "activation", reg_impl: str = "auto", chunk_size: int = 1024
-                                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+                                    mode: str = "activation", reg_impl: str = "auto", chunk_size: int = 1024,
+                                    reg_group=None) -> Tuple[torch.Tensor, torch.Tensor]:
         """``(self(x), self.regularization_loss(reg_act, reg_entropy, x=x))`` from one evaluation of the
         base activation and the basis (kan_linear.py:340-389).
 
@@ -200,6 +211,14 @@ class KANLinear(nn.Module):
         (phi [N,O,I] in PyTorch), "fused" (native kernel, phi never stored, recomputed in backward)
         or "checkpoint" (chunked PyTorch with activation checkpointing).  All give the same value
         and gradients up to rounding and keep the full graph to ``x`` and the parameters.
+
+        ``reg_group`` (no counterpart in the reference, which has no multi-device code): None = the
+        statistic of the rows this process holds (with data parallelism every rank then penalises
+        its own shard); a ``torch.distributed`` process group, or True for the default group = the
+        statistic of the GLOBAL batch, from one all-reduce of ``mean|phi| [O, I]`` weighted by the
+        ranks' row counts (:func:`torchsplinekan_b200.global_edge_means`), so that every rank
+        evaluates the whole-batch penalty and the reduced parameter gradients are those of the
+        unsharded batch.
         """
         if mode == "coefficient":
             # the parameters get gradients from both terms: a data-parallel gradient sink must not
@@ -220,14 +239,14 @@ class KANLinear(nn.Module):
             with _C.no_grad_sinks():
                 y = self._cuda_forward(xf)
             self.last_backend = "cuda"
-            a = self._edge_abs_mean_from_input(xf)
+            a = self._across_ranks(self._edge_abs_mean_from_input(xf), xf, reg_group)
             return y.reshape(lead + (self.out_features,)), _fused.penalty_from_edge_means(a, reg_act, reg_entropy)
         s = self._ref.base_activation(xf)
         H = self._basis(xf, impl)
         W = self._ref.effective_spline_weight()
         y = F.linear(s, self.base_weight) + F.linear(H.reshape(xf.shape[0], -1), W.reshape(self.out_features, -1))
         self.last_backend = "reference"
-        a = self._edge_abs_mean(xf, s, H, W, impl, chunk_size)
+        a = self._across_ranks(self._edge_abs_mean(xf, s, H, W, impl, chunk_size), xf, reg_group)
         return y.reshape(lead + (self.out_features,)), regularization_from_edge_means(a, reg_act, reg_entropy)
 
     def _resolve_reg_impl(self, reg_impl: str, x_flat: torch.Tensor) -> str:
