@@ -83,7 +83,11 @@ KANB200_API int kanb200_set_accumulation_chunks(int forward_blocks, int param_bl
  * (kan_check_inputs, csrc/kan_ops.h:27-78). */
 KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int k, int dtype);
 
-/* The mode KANB200_MODE_AUTO resolves to for this problem. */
+/* The kernel family a call takes: what KANB200_MODE_AUTO resolves to for this problem (a given mode is
+ * only validated).  The rule differs by direction -- op = KANB200_OP_FORWARD or KANB200_OP_BACKWARD --
+ * because the gather forward loses to the tensor cores on much smaller problems than the gather
+ * backward does.  kanb200_resolve_mode is the backward rule (kept for existing callers). */
+KANB200_API int kanb200_resolve_mode_for(int op, int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k);
 KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k);
 
 /* Bytes of caller-provided scratch the given op needs (0 = none). */
@@ -119,6 +123,27 @@ KANB200_API int kanb200_forward(int dtype, int mode,
                     const void* spline_weight, const void* spline_scaler,
                     void* y, int64_t N, int64_t I, int64_t O, int G, int k,
                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Inference with fixed parameters (the use export_inference serves, spline_kan/kan_linear.py:471-496:
+ * the scaler folded into the coefficients once).  Here everything that depends on the parameters
+ * only -- the per-span polynomial table of the knots and the bf16 hi/lo image of the effective
+ * weights (base_weight columns included) -- is built ONCE into a caller-owned device buffer and every
+ * later call runs the contraction alone: one launch per layer instead of three.
+ *   kanb200_prepared_bytes    size of that buffer; 0 = no prepared form for this configuration
+ *                             (float64, k > 3): use kanb200_forward
+ *   kanb200_prepare_forward   fills it (base_weight / spline_scaler may be NULL as in kanb200_forward)
+ *   kanb200_forward_prepared  y = layer(x) from x and the buffer; has_base must repeat whether
+ *                             base_weight was given; mode AUTO / TC_BF16X3 / TC_BF16X1; workspace: at
+ *                             least 256 bytes (the status header).  Same results as kanb200_forward
+ *                             in the same tensor-core mode, bit for bit. */
+KANB200_API size_t kanb200_prepared_bytes(int dtype, int64_t I, int64_t O, int G, int k, int has_base);
+KANB200_API int kanb200_prepare_forward(int dtype, const void* grid, const void* base_weight,
+                                        const void* spline_weight, const void* spline_scaler, int64_t I, int64_t O,
+                                        int G, int k, void* prepared, size_t prepared_bytes, void* stream);
+KANB200_API int kanb200_forward_prepared(int dtype, int mode, const void* x, const void* prepared,
+                                         size_t prepared_bytes, int has_base, void* y, int64_t N, int64_t I,
+                                         int64_t O, int G, int k, void* workspace, size_t workspace_bytes,
+                                         void* stream);
 
 /* First-order backward; any of the four outputs may be NULL = not needed
  * (kan_backward_cuda_ex, csrc/kan_cuda.cu:537-630).  The basis is recomputed

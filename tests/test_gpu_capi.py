@@ -378,6 +378,12 @@ def test_auto_mode_resolution():
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 8192, 256, 10, 5, 3) == nat.MODE_TC_BF16X3
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 8192, 64, 4, 5, 3) == nat.MODE_TC_BF16X3
     assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 8192, 4, 64, 5, 3) == nat.MODE_SIMT       # I < 8
+    # the forward alone moves to the tensor cores earlier than the backward (the gather forward walks every feature)
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 256, 10, 5, 3) == nat.MODE_SIMT
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 256, 10, 5, 3, nat.OP_FORWARD) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 64, 64, 5, 3, nat.OP_FORWARD) == nat.MODE_TC_BF16X3
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 1024, 32, 8, 5, 3, nat.OP_FORWARD) == nat.MODE_SIMT
+    assert nat.resolve_mode(nat.MODE_AUTO, torch.float32, 128, 784, 256, 5, 3, nat.OP_FORWARD) == nat.MODE_SIMT   # N < 256
 
 
 def test_backward_skips_unrequested_outputs():
@@ -744,3 +750,34 @@ def test_layer_tensor_core_general_weights(shape):
     """Spline-dominated weights (the reference's initialisation makes the base branch dominate y and
     hides accumulation error): 1024 features in one tile, a wide grid, many outputs."""
     _compare_layer(make_layer_case(dtype=np.float32, seed=11, **shape), nat.MODE_TC_BF16X3, TOL32)
+
+
+@pytest.mark.parametrize("N,I,O,G,k,base,scaler", [
+    (1024, 64, 640, 5, 3, True, True),      # two output tiles + remainder: shared-memory operand kernel
+    (777, 37, 130, 5, 3, True, False),      # one output tile: tensor-memory operand kernel, ragged everything
+    (512, 24, 300, 4, 2, False, True),      # no base branch
+    (2048, 16, 64, 20, 3, True, True),      # wide grid: three chunks per feature
+])
+def test_forward_prepared_equals_forward_bit_for_bit(N, I, O, G, k, base, scaler):
+    """kanb200_prepare_forward + kanb200_forward_prepared (knot table and weight image built once,
+    contraction alone per call: the form export_inference's frozen layers use,
+    spline_kan/kan_linear.py:471-496) against kanb200_forward in the same tensor-core mode: identical
+    bits, for several calls on one prepared buffer and for both MMA modes."""
+    from torchsplinekan_b200 import _native as nat
+    case = make_layer_case(N, I, O, G, k, np.float32, seed=31, nonuniform=True, scaler=scaler, base=base)
+    x, grid, sw = dev(case["x"]), dev(case["grid"]), dev(case["sw"])
+    bw, sc = dev(case["bw"]), dev(case["sc"])
+    prepared = nat.prepare_forward(grid, bw, sw, sc, k)
+    assert prepared is not None and prepared.dtype == torch.uint8
+    for mode in (nat.MODE_TC_BF16X3, nat.MODE_TC_BF16X1):
+        want = nat.forward(x, grid, bw, sw, sc, k, mode)
+        for _ in range(2):
+            got = nat.forward_prepared(x, prepared, O, G, k, base, mode)
+            assert torch.equal(got, want)
+    half = nat.forward_prepared(x[: N // 2 + 3], prepared, O, G, k, base, nat.MODE_TC_BF16X3)
+    assert torch.equal(half, nat.forward(x[: N // 2 + 3].contiguous(), grid, bw, sw, sc, k, nat.MODE_TC_BF16X3))
+    # float64 has no prepared form
+    assert nat.prepare_forward(grid.double(), None if bw is None else bw.double(), sw.double(),
+                               None if sc is None else sc.double(), k) is None
+    with pytest.raises(RuntimeError):
+        nat.forward_prepared(x, prepared[: prepared.numel() // 2].contiguous(), O, G, k, base, nat.MODE_TC_BF16X3)

@@ -445,3 +445,68 @@ def test_update_grid_on_gpu_matches_cpu_solve(dtype, tol):
     assert _err(gpu(probe.cuda()).cpu(), cpu(probe)) < tol
     keep = [i for i in range(24) if i != 3]
     assert _err(gpu.spline_weight[:, keep].cpu(), cpu.spline_weight[:, keep]) < tol
+
+
+@pytest.mark.parametrize("act", [torch.nn.SiLU, torch.nn.Tanh])
+def test_export_inference_caches_the_operand_images(act):
+    """export_inference() (kan_linear.py:471-496) returns a frozen layer whose native forward builds the
+    knot table and the weight image once and reuses them: same values as the trained layer, identical
+    bits from call to call, and a rebuild as soon as a parameter or the knots change in place, are
+    replaced by load_state_dict, or gradients are wanted again."""
+    layer, _ = _pair(64, 300, act=act)
+    x = (torch.rand(2048, 64, device="cuda") * 2 - 1)
+    twin = layer.export_inference()
+    assert twin.cache_operands and not layer.cache_operands and twin._operands is None
+    with torch.no_grad():
+        want = layer(x)
+    got = twin(x)
+    assert twin._operands is not None and twin._operands[1] is not None     # the tensor-core path took it
+    assert twin.last_backend == "cuda" and not got.requires_grad
+    assert _err(got, want) < 1e-6
+    buf = twin._operands[1]
+    assert torch.equal(twin(x), got) and twin._operands[1] is buf           # reused, not rebuilt
+    assert torch.equal(twin(x[:1000]), got[:1000])
+    # in-place change of a parameter: the cache notices (version counter) and the values follow
+    with torch.no_grad():
+        twin.spline_weight.mul_(2.0)
+        twin.base_weight.zero_()
+        layer.spline_weight.mul_(2.0)
+        layer.base_weight.zero_()
+        want2 = layer(x)
+    got2 = twin(x)
+    assert twin._operands[1] is not buf and _err(got2, want2) < 1e-6
+    # new knots
+    twin.update_grid(x[:512])
+    layer_knots = twin.grid.clone()
+    got3 = twin(x)
+    plain = twin.make_like()
+    plain.load_state_dict(twin.state_dict())
+    assert not plain.cache_operands and torch.equal(plain.grid, layer_knots)
+    with torch.no_grad():
+        assert torch.equal(plain(x), got3)
+    # gradients wanted again: the ordinary operator runs (and differentiates)
+    xg = x[:300].clone().requires_grad_(True)
+    twin(xg).sum().backward()
+    assert xg.grad is not None and torch.isfinite(xg.grad).all()
+    # a small call stays on the gather kernels and leaves the cache alone
+    key = twin._operands[0]
+    twin(x[:8])
+    assert twin._operands[0] == key
+    # float64 twin: no prepared form, ordinary path
+    t64 = layer.double().export_inference()
+    y64 = t64(x.double())
+    assert t64._operands is None and y64.dtype == torch.float64
+
+
+def test_export_inference_network_matches():
+    """KAN.export_inference: every layer of the frozen network runs from its cached operands."""
+    torch.manual_seed(0)
+    net = sk.KAN([64, 256, 20], backend="cuda").to("cuda")          # both layers large enough for the tensor cores
+    x = torch.rand(8192, 64, device="cuda") * 2 - 1
+    frozen = net.export_inference()
+    with torch.no_grad():
+        want = net(x)
+    got = frozen(x)
+    assert all(l.cache_operands and l._operands is not None for l in frozen.layers)
+    assert _err(got, want) < 1e-6
+    assert torch.equal(frozen(x), got)

@@ -35,6 +35,7 @@ SIGNATURES = {
     "kanb200_set_accumulation_chunks": (_c_int, [_c_int, _c_int, _c_int]),
     "kanb200_check_shapes": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int, _c_int, _c_int]),
     "kanb200_resolve_mode": (_c_int, [_c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
+    "kanb200_resolve_mode_for": (_c_int, [_c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
     "kanb200_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                           _c_int, _c_int]),
     "kanb200_basis": (_c_int, [_c_int, _c_void_p, _c_void_p, _c_void_p, _c_i64, _c_i64, _c_int, _c_int, _c_void_p]),
@@ -55,6 +56,11 @@ SIGNATURES = {
     "kanb200_set_forward_variant": (_c_int, [_c_int]),
     "kanb200_set_edge_sign_recheck": (_c_int, [_c_int]),
     "kanb200_get_edge_sign_recheck": (_c_int, []),
+    "kanb200_prepared_bytes": (_c_size, [_c_int, _c_i64, _c_i64, _c_int, _c_int, _c_int]),
+    "kanb200_prepare_forward": (_c_int, [_c_int] + [_c_void_p] * 4 + [_c_i64, _c_i64, _c_int, _c_int, _c_void_p, _c_size,
+                                         _c_void_p]),
+    "kanb200_forward_prepared": (_c_int, [_c_int, _c_int, _c_void_p, _c_void_p, _c_size, _c_int, _c_void_p, _c_i64, _c_i64,
+                                          _c_i64, _c_int, _c_int, _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_penalty": (_c_int, [_c_int, _c_void_p, _c_i64, ctypes.c_double, ctypes.c_double, _c_void_p, _c_void_p,
                                       _c_void_p]),
     "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
@@ -193,8 +199,9 @@ def release_workspaces() -> None:
     _ws_cache.clear()
 
 
-def resolve_mode(mode: int, dtype: torch.dtype, N: int, I: int, O: int, G: int, k: int) -> int:
-    m = lib().kanb200_resolve_mode(mode, _code(dtype), N, I, O, G, k)
+def resolve_mode(mode: int, dtype: torch.dtype, N: int, I: int, O: int, G: int, k: int, op: int = None) -> int:
+    """Kernel family of a call (``op``: OP_FORWARD or OP_BACKWARD, the default)."""
+    m = lib().kanb200_resolve_mode_for(OP_BACKWARD if op is None else op, mode, _code(dtype), N, I, O, G, k)
     if m < 0:
         _check(m)
     return m
@@ -269,6 +276,37 @@ def forward(x, grid, base_weight, spline_weight, spline_scaler, k: int, mode: in
             _check(lib().kanb200_forward(_code(x.dtype), mode, _p(x), _p(grid), _p(base_weight),
                                          _p(spline_weight), _p(spline_scaler), _p(y), N, I, O, G, k, _p(ws),
                                          0 if ws is None else ws.numel(), _stream(dev)))
+    return y
+
+
+def prepare_forward(grid, base_weight, spline_weight, spline_scaler, k: int) -> Optional[torch.Tensor]:
+    """Table + weight image of a layer with fixed parameters (bytes on the device), or None when the
+    configuration has no prepared form (float64, k > 3)."""
+    dev = _need_cuda(grid, spline_weight)
+    O, I, _ = spline_weight.shape
+    G = grid.shape[1] - 2 * k - 1
+    has_base = base_weight is not None and base_weight.numel() > 0
+    nb = lib().kanb200_prepared_bytes(_code(spline_weight.dtype), I, O, G, k, int(has_base))
+    if nb == 0:
+        return None
+    buf = torch.empty(nb, dtype=torch.uint8, device=dev)
+    with _OnDevice(dev):
+        _check(lib().kanb200_prepare_forward(_code(spline_weight.dtype), _p(grid), _p(base_weight if has_base else None),
+                                             _p(spline_weight), _p(spline_scaler), I, O, G, k, _p(buf), nb,
+                                             _stream(dev)))
+    return buf
+
+
+def forward_prepared(x, prepared: torch.Tensor, O: int, G: int, k: int, has_base: bool,
+                     mode: int = MODE_AUTO) -> torch.Tensor:
+    """``y = layer(x)`` from x and the buffer of :func:`prepare_forward`: the contraction alone."""
+    dev = _need_cuda(x, prepared)
+    N, I = x.shape
+    y = torch.empty((N, O), dtype=x.dtype, device=dev)
+    with _OnDevice(dev):
+        ws = workspace(dev, 256, "fwd_prepared")
+        _check(lib().kanb200_forward_prepared(_code(x.dtype), mode, _p(x), _p(prepared), prepared.numel(), int(has_base),
+                                              _p(y), N, I, O, G, k, _p(ws), ws.numel(), _stream(dev)))
     return y
 
 

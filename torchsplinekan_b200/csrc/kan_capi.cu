@@ -104,26 +104,35 @@ KANB200_API int kanb200_check_shapes(int64_t N, int64_t I, int64_t O, int G, int
     return KANB200_OK;
 }
 
-KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k) {
+KANB200_API int kanb200_resolve_mode_for(int op, int mode, int dtype, int64_t N, int64_t I, int64_t O, int G,
+                                         int k) {
     LayerShape s;
     make_shape(N, I, O, G, k, s);
     const bool tc_ok = dtype == KANB200_F32 && tc_supported(s);
     if (mode == KANB200_MODE_AUTO) {
+        if (!tc_ok || N < 256 || I < 8) return KANB200_MODE_SIMT;
         // The tensor-core kernels handle ragged tiles, but a call costs three to six launches (table,
         // operand images, contraction, finalize) against one to three for the gather kernels, about
-        // 35 us in all: they pay from about 2^24 edge-samples (N I O) on, and for narrow layers (whose
+        // 35 us in all.
+        // Backward: they pay from about 2^24 edge-samples (N I O) on, and for narrow layers (whose
         // outputs are padded to a 256-wide tile, so the cost follows N I) from 2^19 input values on
-        // (measured, 8192 rows: 256 -> 10 forward 0.085 against 0.305 ms, 64 -> 4 0.038 against 0.078 ms;
-        // 1024 rows, 32 -> 8: 0.034 against 0.033 ms).
-        if (tc_ok && N >= 256 && I >= 8 &&
-            (N * I * O >= ((int64_t)1 << 24) || N * I >= ((int64_t)1 << 19)))
-            return KANB200_MODE_TC_BF16X3;
+        // (measured, us, gather / tensor cores: 256 -> 10 at 1024 rows 68 / 112, at 4096 rows 182 / 122;
+        // 64 -> 64 at 1024 rows 56 / 71, at 4096 rows 109 / 82; 256 -> 256 at 1024 rows 250 / 124).
+        // Forward: the gather kernel walks every input feature per output tile and loses much earlier
+        // (256 -> 10 at 256 .. 4096 rows 241 / 76; 64 -> 64 84 / 35; 784 -> 256 at 256 rows 988 / 202;
+        // 32 -> 8 at 1024 rows 33 / 34): from 2^16 input values on.
+        const int64_t narrow = op == KANB200_OP_FORWARD ? ((int64_t)1 << 16) : ((int64_t)1 << 19);
+        if (N * I * O >= ((int64_t)1 << 24) || N * I >= narrow) return KANB200_MODE_TC_BF16X3;
         return KANB200_MODE_SIMT;
     }
     if (mode == KANB200_MODE_SIMT) return mode;
     if (mode == KANB200_MODE_TC_BF16X3 || mode == KANB200_MODE_TC_BF16X1)
         return tc_ok ? mode : fail(KANB200_EUNSUPPORTED, "tensor-core modes need float32 and spline order k <= 3");
     return fail(KANB200_EINVAL, "unknown mode %d", mode);
+}
+
+KANB200_API int kanb200_resolve_mode(int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k) {
+    return kanb200_resolve_mode_for(KANB200_OP_BACKWARD, mode, dtype, N, I, O, G, k);
 }
 
 KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t N, int64_t I, int64_t O, int G, int k,
@@ -154,7 +163,8 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
         return kWsHeader + (dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
                                                  : edge_workspace<double>(N, s.I, s.O, s.R(), b));
     }
-    const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
+    const int m = kanb200_resolve_mode_for(op == KANB200_OP_FORWARD ? KANB200_OP_FORWARD : KANB200_OP_BACKWARD, mode,
+                                           dtype, N, I, O, G, k);
     if (m < 0) return 0;
     if (m == KANB200_MODE_SIMT) {
         if (dtype == KANB200_F64 && dense64_supported(s)) {
@@ -243,7 +253,7 @@ KANB200_API int kanb200_forward(int dtype, int mode, const void* x, const void* 
     if (rc) return rc;
     if (N == 0) return KANB200_OK;
     if (!x || !grid || !spline_weight || !y) return fail(KANB200_EINVAL, "kan_forward: NULL pointer");
-    const int m = kanb200_resolve_mode(mode, dtype, N, I, O, G, k);
+    const int m = kanb200_resolve_mode_for(KANB200_OP_FORWARD, mode, dtype, N, I, O, G, k);
     if (m < 0) return m;
     LayerShape s;
     make_shape(N, I, O, G, k, s);
@@ -265,6 +275,50 @@ KANB200_API int kanb200_forward(int dtype, int mode, const void* x, const void* 
                        (float*)y, s, workspace, workspace_bytes, st);
     }
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "kan_forward");
+}
+
+KANB200_API size_t kanb200_prepared_bytes(int dtype, int64_t I, int64_t O, int G, int k, int has_base) {
+    LayerShape s;
+    make_shape(1, I, O, G, k, s);
+    if (dtype != KANB200_F32 || kanb200_check_shapes(1, I, O, G, k, dtype) != KANB200_OK || !tc_supported(s)) return 0;
+    return tc_prepared_bytes(s, has_base != 0);
+}
+
+KANB200_API int kanb200_prepare_forward(int dtype, const void* grid, const void* base_weight,
+                                        const void* spline_weight, const void* spline_scaler, int64_t I, int64_t O,
+                                        int G, int k, void* prepared, size_t prepared_bytes, void* stream) {
+    int rc = kanb200_check_shapes(1, I, O, G, k, dtype);
+    if (rc) return rc;
+    if (!grid || !spline_weight || !prepared) return fail(KANB200_EINVAL, "prepare_forward: NULL pointer");
+    LayerShape s;
+    make_shape(1, I, O, G, k, s);
+    if (dtype != KANB200_F32 || !tc_supported(s))
+        return fail(KANB200_EUNSUPPORTED, "prepare_forward: the prepared form needs float32 and spline order k <= 3");
+    cudaError_t e = tc_prepare_forward((const float*)grid, (const float*)base_weight, (const float*)spline_weight,
+                                       (const float*)spline_scaler, s, prepared, prepared_bytes,
+                                       (cudaStream_t)stream);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "prepare_forward");
+}
+
+KANB200_API int kanb200_forward_prepared(int dtype, int mode, const void* x, const void* prepared,
+                                         size_t prepared_bytes, int has_base, void* y, int64_t N, int64_t I,
+                                         int64_t O, int G, int k, void* workspace, size_t workspace_bytes,
+                                         void* stream) {
+    int rc = kanb200_check_shapes(N, I, O, G, k, dtype);
+    if (rc) return rc;
+    if (N == 0) return KANB200_OK;
+    if (!x || !prepared || !y) return fail(KANB200_EINVAL, "forward_prepared: NULL pointer");
+    LayerShape s;
+    make_shape(N, I, O, G, k, s);
+    if (dtype != KANB200_F32 || !tc_supported(s))
+        return fail(KANB200_EUNSUPPORTED, "forward_prepared: the prepared form needs float32 and spline order k <= 3");
+    if (mode == KANB200_MODE_SIMT) return fail(KANB200_EINVAL, "forward_prepared: runs on the tensor cores only");
+    if (mode != KANB200_MODE_AUTO && mode != KANB200_MODE_TC_BF16X3 && mode != KANB200_MODE_TC_BF16X1)
+        return fail(KANB200_EINVAL, "unknown mode %d", mode);
+    cudaError_t e = tc_forward_prepared(mode == KANB200_MODE_TC_BF16X1 ? 1 : 3, (const float*)x, prepared,
+                                        prepared_bytes, has_base != 0, (float*)y, s, workspace, workspace_bytes,
+                                        (cudaStream_t)stream);
+    return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "forward_prepared");
 }
 
 KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out, const void* x, const void* grid,

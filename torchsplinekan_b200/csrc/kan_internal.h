@@ -92,6 +92,14 @@ cudaError_t edge_static_scratch(void** ptr);
 // ---- tensor-core path (kan_tc.cu), fp32 I/O ---------------------------------
 bool tc_supported(const LayerShape& s);
 size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param);
+// Inference with fixed parameters: table + weight image built once into a caller-owned buffer
+// (tc_prepare_forward), then only the contraction per call (tc_forward_prepared; ws = status header).
+size_t tc_prepared_bytes(const LayerShape& s, bool has_base);
+cudaError_t tc_prepare_forward(const float* grid, const float* bw, const float* sw, const float* scaler,
+                               const LayerShape& s, void* prepared, size_t prepared_bytes, cudaStream_t st);
+cudaError_t tc_forward_prepared(int split_terms, const float* x, const void* prepared, size_t prepared_bytes,
+                                bool has_base, float* y, const LayerShape& s, void* ws, size_t ws_bytes,
+                                cudaStream_t st);
 cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const float* bw, const float* sw,
                        const float* scaler, float* y, const LayerShape& s,
                        void* ws, size_t ws_bytes, cudaStream_t st);

@@ -1964,29 +1964,72 @@ size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param) {
     return b;
 }
 
+// Table of the knots and bf16 image of the effective weights: everything the forward kernels need
+// besides x.  They depend on the parameters only, so inference with fixed parameters builds them once
+// (tc_prepare_forward) and every later call runs the contraction alone (tc_forward_prepared).
+namespace {
+cudaError_t build_forward_operands(const float* grid, const float* bw, const float* sw, const float* scaler,
+                                   float* tab, uint8_t* wimg, const LayerShape& s, cudaStream_t st) {
+    const FwdLayout L = fwd_layout(s, bw != nullptr);
+    const TabInfo ti = make_tab_info(s.G, s.K);
+    const int kb_total = L.cs.kb_total();
+    cudaError_t e0 = launch_table(grid, tab, s, st);
+    if (e0 != cudaSuccess) return e0;
+    const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
+    int blocks = (int)((chunks + 255) / 256);
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), ti.cpf, L.cs.kb_spline,
+                                                kb_total, L.n_otiles);
+    return cudaGetLastError();
+}
+cudaError_t run_forward(int split_terms, const float* x, const float* tab, const uint8_t* wimg, float* y,
+                        int* status, const LayerShape& s, bool has_base, cudaStream_t st);
+}  // namespace
+
+size_t tc_prepared_bytes(const LayerShape& s, bool has_base) {
+    return table_bytes(s) + align256(fwd_layout(s, has_base).wimg_bytes);
+}
+
+cudaError_t tc_prepare_forward(const float* grid, const float* bw, const float* sw, const float* scaler,
+                               const LayerShape& s, void* prepared, size_t prepared_bytes, cudaStream_t st) {
+    if (!prepared || prepared_bytes < tc_prepared_bytes(s, bw != nullptr)) return cudaErrorMemoryAllocation;
+    float* tab = reinterpret_cast<float*>(prepared);
+    uint8_t* wimg = reinterpret_cast<uint8_t*>(prepared) + table_bytes(s);
+    return build_forward_operands(grid, bw, sw, scaler, tab, wimg, s, st);
+}
+
+cudaError_t tc_forward_prepared(int split_terms, const float* x, const void* prepared, size_t prepared_bytes,
+                                bool has_base, float* y, const LayerShape& s, void* ws, size_t ws_bytes,
+                                cudaStream_t st) {
+    if (s.N == 0) return cudaSuccess;
+    if (!prepared || prepared_bytes < tc_prepared_bytes(s, has_base)) return cudaErrorMemoryAllocation;
+    if (!ws || ws_bytes < kWsHeader) return cudaErrorMemoryAllocation;
+    const float* tab = reinterpret_cast<const float*>(prepared);
+    const uint8_t* wimg = reinterpret_cast<const uint8_t*>(prepared) + table_bytes(s);
+    return run_forward(split_terms, x, tab, wimg, y, reinterpret_cast<int*>(ws), s, has_base, st);
+}
+
 cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const float* bw, const float* sw,
                        const float* scaler, float* y, const LayerShape& s,
                        void* ws, size_t ws_bytes, cudaStream_t st) {
     if (s.N == 0) return cudaSuccess;
     const bool has_base = bw != nullptr;
     FwdLayout L = fwd_layout(s, has_base);
-    const TabInfo ti = make_tab_info(s.G, s.K);
     if (!ws || ws_bytes < kWsHeader + table_bytes(s) + L.wimg_bytes) return cudaErrorMemoryAllocation;
     int* status = reinterpret_cast<int*>(ws);
     float* tab = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + kWsHeader);
     uint8_t* wimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
+    cudaError_t e = build_forward_operands(grid, bw, sw, scaler, tab, wimg, s, st);
+    if (e != cudaSuccess) return e;
+    return run_forward(split_terms, x, tab, wimg, y, status, s, has_base, st);
+}
+
+namespace {
+cudaError_t run_forward(int split_terms, const float* x, const float* tab, const uint8_t* wimg, float* y,
+                        int* status, const LayerShape& s, bool has_base, cudaStream_t st) {
+    const FwdLayout L = fwd_layout(s, has_base);
+    const TabInfo ti = make_tab_info(s.G, s.K);
     const int kb_total = L.cs.kb_total();
-    {
-        cudaError_t e0 = launch_table(grid, tab, s, st);
-        if (e0 != cudaSuccess) return e0;
-        const int64_t chunks = (int64_t)L.n_otiles * kb_total * BLOCK_N * 8;
-        int blocks = (int)((chunks + 255) / 256);
-        if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-        pack_weights_kernel<<<blocks, 256, 0, st>>>(sw, scaler, bw, wimg, s.O, s.I, s.R(), ti.cpf, L.cs.kb_spline,
-                                                    kb_total, L.n_otiles);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-    }
     FwdParams P;
     P.N = s.N; P.I = s.I; P.O = s.O; P.G = s.G;
     P.kb_spline = L.cs.kb_spline; P.kb_total = kb_total;
@@ -2025,6 +2068,7 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
+}  // namespace
 
 cudaError_t tc_backward(int split_terms, const float* dY, int64_t ldy, const float* x, const float* grid,
                         const float* bw, const float* sw, const float* scaler, float* gx, float* gbw, float* gsw,

@@ -322,6 +322,55 @@ Tensor forward_impl(const Tensor& x, const Tensor& grid, const Tensor& base_weig
     return y;
 }
 
+// Inference with fixed parameters: table + weight image built once (prepare_forward), contraction
+// alone per call (forward_prepared).  An empty result of prepare_forward means "no prepared form".
+Tensor prepare_forward(const Tensor& grid, const Tensor& base_weight, const Tensor& spline_weight,
+                       const Tensor& spline_scaler, int64_t spline_order, bool has_scaler) {
+    TORCH_CHECK(spline_weight.is_cuda() && spline_weight.dim() == 3, "prepare_forward: spline_weight must be a CUDA "
+                "tensor [O, I, G+k]");
+    TORCH_CHECK(grid.is_cuda() && grid.dim() == 2, "prepare_forward: grid must be a CUDA tensor [I, G+2k+1]");
+    const int64_t O = spline_weight.size(0), I = spline_weight.size(1);
+    const int64_t G = grid.size(1) - 2 * spline_order - 1;
+    TORCH_CHECK(grid.size(0) == I && spline_weight.size(2) == G + spline_order, "prepare_forward: shapes do not agree");
+    const bool has_base = has(base_weight);
+    const int code = dtype_code(spline_weight);
+    const size_t bytes = kanb200_prepared_bytes(code, I, O, (int)G, (int)spline_order, has_base ? 1 : 0);
+    Tensor buf = at::empty({(int64_t)bytes}, spline_weight.options().dtype(at::kByte));
+    if (bytes == 0) return buf;
+    c10::cuda::CUDAGuard guard(spline_weight.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const Tensor gc = grid.contiguous(), bw = contig_or_absent(base_weight), sw = spline_weight.contiguous(),
+                 sc = has_scaler ? contig_or_absent(spline_scaler) : Tensor();
+    check_rc(kanb200_prepare_forward(code, gc.data_ptr(), cptr(bw), sw.data_ptr(), cptr(sc), I, O, (int)G,
+                                     (int)spline_order, buf.data_ptr(), bytes, st));
+    return buf;
+}
+
+Tensor forward_prepared(const Tensor& x, const Tensor& prepared, int64_t O, int64_t G, int64_t spline_order,
+                        bool has_base) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kFloat,
+                "forward_prepared: x must be a float32 CUDA tensor [B, I]");
+    TORCH_CHECK(prepared.is_cuda() && prepared.scalar_type() == at::kByte && prepared.is_contiguous() &&
+                    prepared.device() == x.device(),
+                "forward_prepared: prepared must be the buffer of prepare_forward on x's device");
+    c10::cuda::CUDAGuard guard(x.device());
+    cudaStream_t st = at::cuda::getCurrentCUDAStream();
+    const int64_t N = x.size(0), I = x.size(1);
+    Tensor y = at::empty({N, O}, x.options());
+    if (N == 0) return y;
+    const Tensor xc = x.contiguous();
+    int mode = g_mode.load();
+    if (mode == KANB200_MODE_SIMT) mode = KANB200_MODE_AUTO;     // the prepared form exists on the tensor cores only
+    Scratch* ws = scratch(x.device(), st, WS_FWD, 256);
+    {
+        ScopedTimer timer("forward", st);
+        check_rc(kanb200_forward_prepared(dtype_code(x), mode, xc.data_ptr(), prepared.data_ptr(),
+                                          (size_t)prepared.numel(), has_base ? 1 : 0, y.data_ptr(), N, I, O, (int)G,
+                                          (int)spline_order, ws->buf.data_ptr(), (size_t)ws->buf.numel(), st));
+    }
+    return y;
+}
+
 struct Grads {
     Tensor gx, gb, gs, gc;
 };
@@ -904,6 +953,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("edge_abs_mean_x", &edge_abs_mean_x, py::arg("x"), py::arg("s"), py::arg("grid"), py::arg("base_weight"),
           py::arg("W"), py::arg("spline_order"),
           "a[o,i] = mean_n |s bw + <B(x), W>| straight from x; s empty = silu(x)");
+    m.def("prepare_forward", &prepare_forward, py::arg("grid"), py::arg("base_weight"), py::arg("spline_weight"),
+          py::arg("spline_scaler"), py::arg("spline_order"), py::arg("has_scaler"),
+          "table + weight image of a layer with fixed parameters (empty = no prepared form)");
+    m.def("forward_prepared", &forward_prepared, py::arg("x"), py::arg("prepared"), py::arg("out_features"),
+          py::arg("grid_size"), py::arg("spline_order"), py::arg("has_base"),
+          "layer(x) from x and the buffer of prepare_forward: the contraction alone");
+    m.def("resolve_mode",
+          [](int64_t N, int64_t I, int64_t O, int64_t G, int64_t k, bool f64) {
+              return kanb200_resolve_mode_for(KANB200_OP_FORWARD, g_mode.load(), f64 ? KANB200_F64 : KANB200_F32, N, I, O,
+                                              (int)G, (int)k);
+          },
+          "the kernel family (KANB200_MODE_*) a forward call of this shape takes in the current mode");
     m.def("edge_penalty", &edge_penalty, py::arg("a"), py::arg("mu1"), py::arg("mu2"),
           "(mu1 sum(a) + mu2 entropy(a / sum(a)), its gradient with respect to a) in one launch");
     m.def("edge_abs_mean_x_backward",

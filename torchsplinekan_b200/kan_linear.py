@@ -69,6 +69,10 @@ class KANLinear(nn.Module):
             self._use_cuda = native_ok
         self.backend = backend
         self.last_backend: Optional[str] = None      # plain string: cannot keep a graph alive
+        # Inference with fixed parameters (export_inference): the knot table and the weight image of
+        # the native kernels are then built once and reused while the parameters stay as they are.
+        self.cache_operands = False
+        self._operands = None                        # (key, device buffer)
 
         # The dense layer owns parameters and buffers; they are aliased here so
         # that state dicts carry both key sets, as the reference's do.
@@ -122,11 +126,39 @@ class KANLinear(nn.Module):
         absent = xf.new_empty(0)
         has_scaler = self.enable_standalone_scale_spline
         fuse_base = self._native_fuses_base
+        prepared = self._prepared_operands(xf, fuse_base, has_scaler) if self.cache_operands else None
+        if prepared is not None:
+            out = _C.forward_prepared(xf, prepared, self.out_features, self.grid_size, self.spline_order, fuse_base)
+            if not fuse_base:
+                out = out + F.linear(self._ref.base_activation(xf), self.base_weight)
+            return out.reshape(lead + (self.out_features,))
         out = _C.kan_apply(xf, self.grid, self.base_weight if fuse_base else absent, self.spline_weight,
                            self.spline_scaler if has_scaler else absent, self.spline_order, has_scaler)
         if not fuse_base:
             out = out + F.linear(self._ref.base_activation(xf), self.base_weight)
         return out.reshape(lead + (self.out_features,))
+
+    def _prepared_operands(self, xf: torch.Tensor, fuse_base: bool, has_scaler: bool):
+        """The buffer of ``_C.prepare_forward`` for the current parameters, or None when this call
+        cannot use it: gradients are wanted, the dtype is not float32, or a call of this shape does not
+        run on the tensor cores.  The buffer is rebuilt when a parameter or the knots were modified in
+        place (their version counters), replaced, or moved."""
+        params = [self.grid, self.spline_weight] + ([self.base_weight] if fuse_base else []) + \
+                 ([self.spline_scaler] if has_scaler else [])
+        if xf.dtype != torch.float32 or xf.shape[0] == 0:
+            return None
+        if torch.is_grad_enabled() and (xf.requires_grad or any(p.requires_grad for p in params)):
+            return None
+        if _C.resolve_mode(xf.shape[0], self.in_features, self.out_features, self.grid_size, self.spline_order,
+                           False) not in (2, 3):                 # KANB200_MODE_TC_BF16X3 / _BF16X1
+            return None
+        key = tuple((p.data_ptr(), p._version, p.device) for p in params)
+        if self._operands is None or self._operands[0] != key:
+            absent = xf.new_empty(0)
+            buf = _C.prepare_forward(self.grid, self.base_weight if fuse_base else absent, self.spline_weight,
+                                     self.spline_scaler if has_scaler else absent, self.spline_order, has_scaler)
+            self._operands = (key, buf if buf.numel() > 0 else None)
+        return self._operands[1]
 
     # -- knots from data ---------------------------------------------------
     def update_grid(self, x: torch.Tensor, margin: float = 0.01) -> None:
@@ -324,6 +356,9 @@ class KANLinear(nn.Module):
             out.spline_weight.copy_(self._ref.effective_spline_weight())
             out._copy_grid_(self.grid)
         out.requires_grad_(requires_grad)
+        # frozen parameters: the native kernels' knot table and weight image are built at the first
+        # call and reused (one launch per layer and call instead of three)
+        out.cache_operands = not requires_grad
         return out.train(self.training and requires_grad)
 
     @torch.no_grad()
