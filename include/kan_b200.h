@@ -133,9 +133,12 @@ KANB200_API int kanb200_forward(int dtype, int mode,
  *                             (float64, k > 3): use kanb200_forward
  *   kanb200_prepare_forward   fills it (base_weight / spline_scaler may be NULL as in kanb200_forward)
  *   kanb200_forward_prepared  y = layer(x) from x and the buffer; has_base must repeat whether
- *                             base_weight was given; mode AUTO / TC_BF16X3 / TC_BF16X1; workspace: at
- *                             least 256 bytes (the status header).  Same results as kanb200_forward
- *                             in the same tensor-core mode, bit for bit. */
+ *                             base_weight was given; mode AUTO / TC_BF16X3 / TC_BF16X1; workspace:
+ *                             kanb200_workspace_bytes(KANB200_OP_FORWARD, KANB200_MODE_TC_BF16X3, ...)
+ *                             bytes, at least the 256-byte status header (with less than that figure a
+ *                             small batch runs the chains of a tile one after the other instead of
+ *                             side by side).  Same results as kanb200_forward in the same
+ *                             tensor-core mode and with the same workspace size, bit for bit. */
 KANB200_API size_t kanb200_prepared_bytes(int dtype, int64_t I, int64_t O, int G, int k, int has_base);
 KANB200_API int kanb200_prepare_forward(int dtype, const void* grid, const void* base_weight,
                                         const void* spline_weight, const void* spline_scaler, int64_t I, int64_t O,

@@ -781,3 +781,35 @@ def test_forward_prepared_equals_forward_bit_for_bit(N, I, O, G, k, base, scaler
                                None if sc is None else sc.double(), k) is None
     with pytest.raises(RuntimeError):
         nat.forward_prepared(x, prepared[: prepared.numel() // 2].contiguous(), O, G, k, base, nat.MODE_TC_BF16X3)
+
+
+@pytest.mark.parametrize("N,I,O,G,k", [
+    (300, 256, 40, 5, 3),        # 36 column blocks = 2 chains, tensor-memory operand kernel, ragged rows
+    (130, 784, 300, 5, 3),       # 111 blocks = 5 chains, shared-memory operand kernel (two output tiles)
+    (1000, 200, 520, 4, 2),      # 3 output tiles (a pair and a single one), 2 chains
+    (256, 24, 64, 64, 3),        # wide grid: 9 chunks per feature
+])
+def test_forward_small_batch_chains_as_work_items(N, I, O, G, k):
+    """Small batches: the chains of 24 column blocks of a tile run as separate work items whose partial
+    results are added in fixed order by a second kernel.  Against the float64 oracle (stated 1e-5),
+    and bit-identical to the same call with a workspace too small for the partial results, where a
+    tile's chains run one after the other inside one work item."""
+    from torchsplinekan_b200 import _native as nat
+    case = make_layer_case(N, I, O, G, k, np.float32, seed=41, nonuniform=True)
+    x, grid, bw, sw, sc = dev(case["x"]), dev(case["grid"]), dev(case["bw"]), dev(case["sw"]), dev(case["sc"])
+    y = nat.forward(x, grid, bw, sw, sc, k, nat.MODE_TC_BF16X3)
+    want = oracle_step(case, need_x=False)[0]
+    assert rel_err(y.cpu().numpy().astype(np.float64), want) < 1e-5
+    full = nat.workspace_bytes(nat.OP_FORWARD, nat.MODE_TC_BF16X3, torch.float32, N, I, O, G, k)
+    prepared = nat.prepare_forward(grid, bw, sw, sc, k)
+    assert full > 256 + prepared.numel()                      # room for the partial results was asked for
+    y2 = torch.empty_like(y)
+    small = torch.zeros(256, dtype=torch.uint8, device=x.device)
+    lib = nat.lib()
+    rc = lib.kanb200_forward_prepared(0, nat.MODE_TC_BF16X3, x.data_ptr(), prepared.data_ptr(), prepared.numel(), 1,
+                                      y2.data_ptr(), N, I, O, G, k, small.data_ptr(), small.numel(),
+                                      torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    assert torch.equal(nat.forward(x, grid, bw, sw, sc, k, nat.MODE_TC_BF16X3), y)      # and from run to run

@@ -304,7 +304,7 @@ def forward_prepared(x, prepared: torch.Tensor, O: int, G: int, k: int, has_base
     N, I = x.shape
     y = torch.empty((N, O), dtype=x.dtype, device=dev)
     with _OnDevice(dev):
-        ws = workspace(dev, 256, "fwd_prepared")
+        ws = workspace(dev, max(256, workspace_bytes(OP_FORWARD, MODE_TC_BF16X3, x.dtype, N, I, O, G, k)), "fwd")
         _check(lib().kanb200_forward_prepared(_code(x.dtype), mode, _p(x), _p(prepared), prepared.numel(), int(has_base),
                                               _p(y), N, I, O, G, k, _p(ws), ws.numel(), _stream(dev)))
     return y

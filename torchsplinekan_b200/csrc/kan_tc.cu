@@ -272,8 +272,31 @@ struct FwdParams {
     int64_t n_tiles;
     int chunk_kb;          // k-blocks accumulated in TMEM between drains
     int vec_x, vec_x2, vec_y;
+    // Few row tiles (small batches): every chain of chunk_kb blocks is a work item of its own
+    // (item = tile * n_ksplit + chain) and stores its result in slab[chain][N][O]; a second kernel adds
+    // the slabs in fixed order.  n_ksplit == 1: an item is a whole tile and accumulates in y itself.
+    int n_ksplit;
+    float* slab;
     TabInfo ti;
+    __host__ __device__ int64_t n_items() const { return n_tiles * n_ksplit; }
 };
+
+// item -> tile, blocks [kb0, kb1) and destination of the item's result
+__device__ __forceinline__ void fwd_item(const FwdParams& P, int64_t item, float* y, int64_t& tile, int& kb0, int& kb1,
+                                         float*& dst) {
+    if (P.n_ksplit > 1) {
+        tile = item / P.n_ksplit;
+        const int chain = (int)(item - tile * P.n_ksplit);
+        kb0 = chain * P.chunk_kb;
+        kb1 = kb0 + P.chunk_kb < P.kb_total ? kb0 + P.chunk_kb : P.kb_total;
+        dst = P.slab + (size_t)chain * (size_t)P.N * P.O;
+    } else {
+        tile = item;
+        kb0 = 0;
+        kb1 = P.kb_total;
+        dst = y;
+    }
+}
 
 template <int NTERMS, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -329,6 +352,7 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
         bool pend = false, pend_first = false;
         int64_t pend_mt = 0;
         int pend_op = 0;
+        float* pend_dst = y;
 
         auto drain = [&]() -> bool {
             const int64_t n = pend_mt * BLOCK_M + row;
@@ -346,9 +370,9 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                     const int col0 = (pend_op * 2 + j) * BLOCK_N + c * 32;
                     const int64_t n0 = n - lane;                   // first of the warp's 32 rows
                     if (P.vec_y && n0 + 32 <= P.N && col0 + 32 <= P.O)        // uniform over the warp
-                        drain_rows32_warp(y + (size_t)n0 * P.O + col0, (size_t)P.O, r, lane, pend_first);
+                        drain_rows32_warp(pend_dst + (size_t)n0 * P.O + col0, (size_t)P.O, r, lane, pend_first);
                     else if (n < P.N && col0 < P.O)
-                        drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
+                        drain_row32(pend_dst + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
                 }
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&ctrl->drained[j]));
@@ -357,7 +381,11 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
             return true;
         };
 
-        for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+        for (int64_t item = blockIdx.x; item < P.n_items() && ok; item += gridDim.x) {
+            int64_t tile;
+            int kb0, kb1;
+            float* dst;
+            fwd_item(P, item, y, tile, kb0, kb1, dst);
             const int64_t mt = tile / P.n_opairs;
             const int op = (int)(tile - mt * P.n_opairs);
             const int64_t n = mt * BLOCK_M + row;
@@ -390,8 +418,8 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                     nx1 = (row_ok && f1 < P.I) ? __ldg(xrow + f1) : 0.f;
                 }
             };
-            if (P.kb_spline > 0) prefetch_spline(0);
-            for (int kb = 0; kb < P.kb_total; ++kb, ++it) {
+            if (kb0 < P.kb_spline) prefetch_spline(kb0);
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t stage = it % FWD_A_STAGES;
                 const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                 const uint32_t a_lo = a_hi + TILE_A_BYTES;
@@ -454,11 +482,12 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                         break;
                     }
                 }
-                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1) {
                     pend = true;
-                    pend_first = kb < P.chunk_kb;
+                    pend_first = P.n_ksplit > 1 || kb < P.chunk_kb;
                     pend_mt = mt;
                     pend_op = op;
+                    pend_dst = dst;
                 }
             }
         }
@@ -470,16 +499,20 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
             constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
             uint32_t it = 0, bslot = 0, n_chunks[2] = {0, 0};
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+            for (int64_t item = blockIdx.x; item < P.n_items() && ok; item += gridDim.x) {
+                int64_t tile;
+                int kb0, kb1;
+                float* dst;
+                fwd_item(P, item, y, tile, kb0, kb1, dst);
                 const int64_t mt = tile / P.n_opairs;
                 const int op = (int)(tile - mt * P.n_opairs);
                 const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
-                for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
                     const uint32_t stage = it % FWD_A_STAGES;
                     const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                     const uint32_t a_lo = a_hi + TILE_A_BYTES;
                     const bool chunk_start = (kb % P.chunk_kb) == 0;
-                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total;
+                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1;
                     if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FWD_A_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -545,11 +578,15 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
             // ===== bulk-copy producer for weight tiles =====
             uint32_t bslot = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+            for (int64_t item = blockIdx.x; item < P.n_items() && ok; item += gridDim.x) {
+                int64_t tile;
+                int kb0, kb1;
+                float* dst;
+                fwd_item(P, item, y, tile, kb0, kb1, dst);
                 const int64_t mt = tile / P.n_opairs;
                 const int op = (int)(tile - mt * P.n_opairs);
                 const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
-                for (int kb = 0; kb < P.kb_total && ok; ++kb) {
+                for (int kb = kb0; kb < kb1 && ok; ++kb) {
                     for (int j = 0; j < nsub && ok; ++j) {
                         const uint8_t* src = wimg + ((size_t)(2 * op + j) * P.kb_total + kb) * (2 * (size_t)TILE_B_BYTES);
                         for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
@@ -657,6 +694,7 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
         bool pend = false, pend_first = false;
         int64_t pend_mt = 0;
         int pend_op = 0;
+        float* pend_dst = y;
 
         auto drain = [&]() -> bool {
             const int64_t n = pend_mt * BLOCK_M + row;
@@ -673,9 +711,9 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                     const int col0 = pend_op * BLOCK_N + c * 32;
                     const int64_t n0 = n - lane;                   // first of the warp's 32 rows
                     if (P.vec_y && n0 + 32 <= P.N && col0 + 32 <= P.O)        // uniform over the warp
-                        drain_rows32_warp(y + (size_t)n0 * P.O + col0, (size_t)P.O, r, lane, pend_first);
+                        drain_rows32_warp(pend_dst + (size_t)n0 * P.O + col0, (size_t)P.O, r, lane, pend_first);
                     else if (n < P.N && col0 < P.O)
-                        drain_row32(y + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
+                        drain_row32(pend_dst + (size_t)n * P.O + col0, r, pend_first, P.O - col0, P.vec_y != 0);
                 }
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&ctrl->drained[j]));
@@ -684,7 +722,11 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
             return true;
         };
 
-        for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+        for (int64_t item = blockIdx.x; item < P.n_items() && ok; item += gridDim.x) {
+            int64_t tile;
+            int kb0, kb1;
+            float* dst;
+            fwd_item(P, item, y, tile, kb0, kb1, dst);
             const int64_t mt = tile / P.n_otiles;
             const int op = (int)(tile - mt * P.n_otiles);          // the 256-output tile
             const int64_t n = mt * BLOCK_M + row;
@@ -706,7 +748,7 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                     if (cw1 == cpf) { f1 = f0 + 1; cw1 = 0; }
                 }
             };
-            for (int kb = 0; kb < P.kb_total; ++kb, ++it) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t stage = it % FTS_A_STAGES;
                 const bool chunk_start = (kb % P.chunk_kb) == 0;
                 if ((int)stage == part) {
@@ -791,11 +833,12 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                         break;
                     }
                 }
-                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total) {
+                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1) {
                     pend = true;
-                    pend_first = kb < P.chunk_kb;
+                    pend_first = P.n_ksplit > 1 || kb < P.chunk_kb;
                     pend_mt = mt;
                     pend_op = op;
+                    pend_dst = dst;
                 }
             }
         }
@@ -807,14 +850,18 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
             constexpr uint64_t dbase = make_sdesc_sw128(16, 1024);
             uint32_t it = 0, bslot = 0, n_chunks[2] = {0, 0};
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+            for (int64_t item = blockIdx.x; item < P.n_items() && ok; item += gridDim.x) {
+                int64_t tile;
+                int kb0, kb1;
+                float* dst;
+                fwd_item(P, item, y, tile, kb0, kb1, dst);
                 const int nsub = 1;
-                for (int kb = 0; kb < P.kb_total && ok; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
                     const uint32_t stage = it % FTS_A_STAGES;
                     const uint32_t a_hi = tmem_base + FTS_TMEM_A + stage * 64;
                     const uint32_t a_lo = a_hi + 32;
                     const bool chunk_start = (kb % P.chunk_kb) == 0;
-                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == P.kb_total;
+                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1;
                     if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FTS_A_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -878,10 +925,14 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
             // ===== bulk-copy producer for weight tiles =====
             uint32_t bslot = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < P.n_tiles && ok; tile += gridDim.x) {
+            for (int64_t item = blockIdx.x; item < P.n_items() && ok; item += gridDim.x) {
+                int64_t tile;
+                int kb0, kb1;
+                float* dst;
+                fwd_item(P, item, y, tile, kb0, kb1, dst);
                 const int64_t mt = tile / P.n_otiles;
                 const int op = (int)(tile - mt * P.n_otiles);
-                for (int kb = 0; kb < P.kb_total && ok; ++kb) {
+                for (int kb = kb0; kb < kb1 && ok; ++kb) {
                     {
                         const uint8_t* src = wimg + ((size_t)op * P.kb_total + kb) * (2 * (size_t)TILE_B_BYTES);
                         for (int term = 0; term < (SPLIT ? 2 : 1); ++term, ++bslot) {
@@ -1914,6 +1965,22 @@ inline FwdLayout fwd_layout(const LayerShape& s, bool has_base) {
     return L;
 }
 
+// Number of separately stored chains the forward would split a tile into for this batch (1 = no
+// split): a tile's chain over the columns is serial, so a batch of few row tiles leaves most SMs idle
+// unless the chains of chunk_kb blocks -- which are drained separately anyway -- become work items.
+inline int forward_ksplit(const LayerShape& s, bool has_base, int64_t n_tiles) {
+    const int kb_total = fwd_layout(s, has_base).cs.kb_total();
+    const int chains = (kb_total + fwd_chunk_kb(kb_total) - 1) / fwd_chunk_kb(kb_total);
+    return (chains > 1 && n_tiles * 2 <= sm_count()) ? chains : 1;
+}
+// Bytes of the partial results for the most finely split case of this shape.
+inline size_t forward_slab_bytes(const LayerShape& s, bool has_base) {
+    const FwdLayout L = fwd_layout(s, has_base);
+    const int64_t row_tiles = (s.N + BLOCK_M - 1) / BLOCK_M;
+    const int k = forward_ksplit(s, has_base, row_tiles * ((L.n_otiles + 1) / 2));     // the smaller tile count
+    return k > 1 ? align256((size_t)k * (size_t)s.N * s.O * sizeof(float)) : 0;
+}
+
 struct BwdLayout {
     BwdPlan plan;
     size_t dyimg_bytes, partial_bytes;
@@ -1955,13 +2022,39 @@ bool tc_supported(const LayerShape& s) {
 
 size_t tc_workspace(int op, const LayerShape& s, bool need_x, bool need_param) {
     // Sized for a layer with a base branch (the larger case).
-    if (op == 0) return kWsHeader + table_bytes(s) + align256(fwd_layout(s, true).wimg_bytes);
+    if (op == 0)
+        return kWsHeader + table_bytes(s) + align256(fwd_layout(s, true).wimg_bytes) + forward_slab_bytes(s, true);
     size_t b = kWsHeader + table_bytes(s);
     BwdLayout L = bwd_layout(s, true);
     if (need_param || need_x) b += align256(L.dyimg_bytes);
     if (need_param) b += align256(L.partial_bytes);
     if (need_x) b += align256(fwd_layout(s, true).wimg_bytes);
     return b;
+}
+
+// y = slab[0] + slab[1] + ... in that order (the forward's per-chain partial results, small batches).
+__global__ void sum_forward_slabs_kernel(const float* __restrict__ slab, float* __restrict__ y, int64_t count,
+                                         int n_slabs, int vec) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    if (vec) {
+        const float4* s4 = reinterpret_cast<const float4*>(slab);
+        float4* y4 = reinterpret_cast<float4*>(y);
+        const int64_t c4 = count / 4;
+        for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < c4; e += stride) {
+            float4 a = s4[e];
+            for (int c = 1; c < n_slabs; ++c) {
+                const float4 b = s4[(size_t)c * c4 + e];
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            }
+            y4[e] = a;
+        }
+    } else {
+        for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += stride) {
+            float a = slab[e];
+            for (int c = 1; c < n_slabs; ++c) a += slab[(size_t)c * count + e];
+            y[e] = a;
+        }
+    }
 }
 
 // Table of the knots and bf16 image of the effective weights: everything the forward kernels need
@@ -1983,7 +2076,8 @@ cudaError_t build_forward_operands(const float* grid, const float* bw, const flo
     return cudaGetLastError();
 }
 cudaError_t run_forward(int split_terms, const float* x, const float* tab, const uint8_t* wimg, float* y,
-                        int* status, const LayerShape& s, bool has_base, cudaStream_t st);
+                        int* status, void* slab, size_t slab_bytes, const LayerShape& s, bool has_base,
+                        cudaStream_t st);
 }  // namespace
 
 size_t tc_prepared_bytes(const LayerShape& s, bool has_base) {
@@ -2006,7 +2100,8 @@ cudaError_t tc_forward_prepared(int split_terms, const float* x, const void* pre
     if (!ws || ws_bytes < kWsHeader) return cudaErrorMemoryAllocation;
     const float* tab = reinterpret_cast<const float*>(prepared);
     const uint8_t* wimg = reinterpret_cast<const uint8_t*>(prepared) + table_bytes(s);
-    return run_forward(split_terms, x, tab, wimg, y, reinterpret_cast<int*>(ws), s, has_base, st);
+    return run_forward(split_terms, x, tab, wimg, y, reinterpret_cast<int*>(ws),
+                       reinterpret_cast<uint8_t*>(ws) + kWsHeader, ws_bytes - kWsHeader, s, has_base, st);
 }
 
 cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const float* bw, const float* sw,
@@ -2021,12 +2116,15 @@ cudaError_t tc_forward(int split_terms, const float* x, const float* grid, const
     uint8_t* wimg = reinterpret_cast<uint8_t*>(ws) + kWsHeader + table_bytes(s);
     cudaError_t e = build_forward_operands(grid, bw, sw, scaler, tab, wimg, s, st);
     if (e != cudaSuccess) return e;
-    return run_forward(split_terms, x, tab, wimg, y, status, s, has_base, st);
+    const size_t used = kWsHeader + table_bytes(s) + align256(L.wimg_bytes);
+    return run_forward(split_terms, x, tab, wimg, y, status, reinterpret_cast<uint8_t*>(ws) + used,
+                       ws_bytes > used ? ws_bytes - used : 0, s, has_base, st);
 }
 
 namespace {
 cudaError_t run_forward(int split_terms, const float* x, const float* tab, const uint8_t* wimg, float* y,
-                        int* status, const LayerShape& s, bool has_base, cudaStream_t st) {
+                        int* status, void* slab, size_t slab_bytes, const LayerShape& s, bool has_base,
+                        cudaStream_t st) {
     const FwdLayout L = fwd_layout(s, has_base);
     const TabInfo ti = make_tab_info(s.G, s.K);
     const int kb_total = L.cs.kb_total();
@@ -2045,7 +2143,12 @@ cudaError_t run_forward(int split_terms, const float* x, const float* tab, const
     // tile serves one accumulator either way, and shared memory is left to the weight tiles
     const bool operand_in_tmem = g_fwd_variant < 0 ? P.n_otiles == 1 : g_fwd_variant == 1;
     if (operand_in_tmem) P.n_tiles = ((s.N + BLOCK_M - 1) / BLOCK_M) * P.n_otiles;      // one 256-output tile each
-    const int blocks = (int)(P.n_tiles < sm_count() ? P.n_tiles : sm_count());
+    // small batches: one work item per chain, partial results in the workspace (when it has the room)
+    P.n_ksplit = forward_ksplit(s, has_base, P.n_tiles);
+    if (P.n_ksplit > 1 && (!slab || slab_bytes < (size_t)P.n_ksplit * (size_t)s.N * s.O * sizeof(float))) P.n_ksplit = 1;
+    P.slab = reinterpret_cast<float*>(slab);
+    const int64_t n_items = P.n_items();
+    const int blocks = (int)(n_items < sm_count() ? n_items : sm_count());
 #define KAN_FWD(NT, W)                                                                                         \
     do {                                                                                                      \
         if (operand_in_tmem) {                                                                                \
@@ -2066,7 +2169,16 @@ cudaError_t run_forward(int split_terms, const float* x, const float* tab, const
     }
 #undef KAN_FWD
     if (e != cudaSuccess) return e;
-    return cudaGetLastError();
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    if (P.n_ksplit > 1) {
+        const int64_t count = s.N * (int64_t)s.O;
+        const int vec = (count % 4 == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+        const int64_t work = vec ? count / 4 : count;
+        int rblocks = (int)((work + 255) / 256 < (int64_t)sm_count() * 8 ? (work + 255) / 256 : (int64_t)sm_count() * 8);
+        sum_forward_slabs_kernel<<<rblocks, 256, 0, st>>>(P.slab, y, count, P.n_ksplit, vec);
+        e = cudaGetLastError();
+    }
+    return e;
 }
 }  // namespace
 

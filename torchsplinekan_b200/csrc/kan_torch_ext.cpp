@@ -361,7 +361,9 @@ Tensor forward_prepared(const Tensor& x, const Tensor& prepared, int64_t O, int6
     const Tensor xc = x.contiguous();
     int mode = g_mode.load();
     if (mode == KANB200_MODE_SIMT) mode = KANB200_MODE_AUTO;     // the prepared form exists on the tensor cores only
-    Scratch* ws = scratch(x.device(), st, WS_FWD, 256);
+    size_t bytes = kanb200_workspace_bytes(KANB200_OP_FORWARD, KANB200_MODE_TC_BF16X3, dtype_code(x), N, I, O, (int)G,
+                                           (int)spline_order, 1, 1);
+    Scratch* ws = scratch(x.device(), st, WS_FWD, bytes < 256 ? 256 : bytes);
     {
         ScopedTimer timer("forward", st);
         check_rc(kanb200_forward_prepared(dtype_code(x), mode, xc.data_ptr(), prepared.data_ptr(),
