@@ -47,9 +47,9 @@ bool make_shape(int64_t N, int64_t I, int64_t O, int G, int k, LayerShape& s) {
 // Whether the from-x edge statistic takes the tensor-core kernel for this problem.
 bool edge_x_uses_tc(int mode, int dtype, const LayerShape& s) {
     if (dtype != KANB200_F32 || mode == KANB200_MODE_SIMT || !tc_edge_supported(s)) return false;
-    // (measured at 8192 rows, 256 features: 10 or 4 outputs 0.07 against 0.145 ms -- the FMA kernels tile 32
-    // outputs and cost the same for fewer)
-    if (mode == KANB200_MODE_AUTO) return s.N >= 256;
+    // layers of at most 16 outputs have a kernel of their own on the FMA pipes (the tensor-core tile
+    // is 128 outputs wide whatever the layer has)
+    if (mode == KANB200_MODE_AUTO) return s.N >= 256 && s.O > 16;
     return true;
 }
 
@@ -60,7 +60,7 @@ bool edge_x_bwd_uses_tc(int mode, int dtype, const LayerShape& s, bool custom_ba
     // cost more than the FMA kernels need for the whole job
     // (outputs are padded to a tile of 128, so the cost follows N I max(O, 128))
     if (mode == KANB200_MODE_AUTO)
-        return s.N >= 256 && s.N * s.I * (int64_t)(s.O > 128 ? s.O : 128) >= ((int64_t)1 << 23);
+        return s.N >= 256 && s.O > 16 && s.N * s.I * (int64_t)(s.O > 128 ? s.O : 128) >= ((int64_t)1 << 23);
     return true;
 }
 
