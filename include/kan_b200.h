@@ -229,10 +229,14 @@ KANB200_API int kanb200_set_edge_sign_recheck(int on);
  *   value[0] = mu1 * A + mu2 * S,  A = sum a,  p = max(a / max(A, tiny), tiny),  S = -sum p log p,
  *   grad[j]  = d value / d a_j = mu1 - mu2 (log p_j + S) / A   (NULL = not needed)
  * (regularization_from_edge_means, spline_kan/reference_backend.py:149-170, which the reference
- * evaluates as a chain of tensor operations and differentiates through autograd).  One launch,
- * sums in float64; tiny = the dtype's smallest normal, as in the reference's clamps. */
+ * evaluates as a chain of tensor operations and differentiates through autograd).  Sums in float64;
+ * tiny = the dtype's smallest normal, as in the reference's clamps.  With a workspace of
+ * kanb200_edge_penalty_workspace_bytes() bytes (plain scratch, no status header) two launches share
+ * the work over the whole GPU; with workspace == NULL, or fewer than 4096 entries, one block does it
+ * all in one launch. */
+KANB200_API size_t kanb200_edge_penalty_workspace_bytes(void);
 KANB200_API int kanb200_edge_penalty(int dtype, const void* a, int64_t n, double mu1, double mu2, void* value,
-                                     void* grad, void* stream);
+                                     void* grad, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Which tensor-core forward kernel runs (same results): 1 = the generated operand is stored in tensor
  * memory and the MMA reads it from there (shared memory only carries the weight tiles; one

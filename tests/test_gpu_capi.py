@@ -645,7 +645,8 @@ def test_edge_penalty_one_launch_matches_dense_formulation(dtype):
     cases = [torch.rand(5, 7, dtype=dtype) + 0.01,
              torch.cat([torch.zeros(2, 7, dtype=dtype), torch.rand(3, 7, dtype=dtype)]),
              torch.zeros(3, 4, dtype=dtype),
-             torch.rand(256, 784, dtype=dtype) * 0.05]
+             torch.rand(256, 784, dtype=dtype) * 0.05,
+             torch.cat([torch.zeros(40, 300, dtype=dtype), torch.rand(60, 300, dtype=dtype)])]     # two-launch form with dead entries
     tol = 1e-13 if dtype == torch.float64 else 2e-6
     for a0 in cases:
         a = a0.clone().requires_grad_()
@@ -658,6 +659,10 @@ def test_edge_penalty_one_launch_matches_dense_formulation(dtype):
         assert float((got_g.cpu() - want_g).abs().max()) <= tol * gscale * 4
         only_v, none_g = nat.edge_penalty(a0.cuda(), 0.7, 1.3, need_grad=False)
         assert none_g is None and float(only_v) == float(got_v)
+        # the single-block form (no workspace) and the two-launch form agree
+        one_v, one_g = nat.edge_penalty(a0.cuda(), 0.7, 1.3, scratch=False)
+        assert abs(float(one_v) - float(want_v)) <= tol * scale
+        assert float((one_g.cpu() - want_g).abs().max()) <= tol * gscale * 4
         b = a0.cuda().requires_grad_()
         out = fused.penalty_from_edge_means(b, 0.7, 1.3)
         (gb,) = torch.autograd.grad(out * 2.0, b)

@@ -61,8 +61,9 @@ SIGNATURES = {
                                          _c_void_p]),
     "kanb200_forward_prepared": (_c_int, [_c_int, _c_int, _c_void_p, _c_void_p, _c_size, _c_int, _c_void_p, _c_i64, _c_i64,
                                           _c_i64, _c_int, _c_int, _c_void_p, _c_size, _c_void_p]),
+    "kanb200_edge_penalty_workspace_bytes": (_c_size, []),
     "kanb200_edge_penalty": (_c_int, [_c_int, _c_void_p, _c_i64, ctypes.c_double, ctypes.c_double, _c_void_p, _c_void_p,
-                                      _c_void_p]),
+                                      _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_x_backward": (_c_int, [_c_int, _c_int] + [_c_void_p] * 10 + [_c_i64, _c_i64, _c_i64, _c_int, _c_int,
                                                                                _c_void_p, _c_size, _c_void_p]),
     "kanb200_edge_abs_mean_noalloc": (_c_int, [_c_int] + [_c_void_p] * 5 + [_c_i64, _c_i64, _c_i64, _c_int, _c_void_p]),
@@ -387,15 +388,18 @@ def edge_abs_mean_x(x, s, grid, bw, W, k: int, mode: int = MODE_AUTO) -> torch.T
     return a
 
 
-def edge_penalty(a: torch.Tensor, mu1: float, mu2: float, need_grad: bool = True):
-    """``(mu1 sum(a) + mu2 entropy(a / sum(a)), d/da)`` from one launch (gradient None when not needed)."""
+def edge_penalty(a: torch.Tensor, mu1: float, mu2: float, need_grad: bool = True, scratch: bool = True):
+    """``(mu1 sum(a) + mu2 entropy(a / sum(a)), d/da)`` (gradient None when not needed); ``scratch=False``
+    withholds the workspace, i.e. forces the single-block form."""
     dev = _need_cuda(a)
     a = a.contiguous()
     value = torch.empty((), dtype=a.dtype, device=dev)
     grad = torch.empty_like(a) if need_grad else None
+    nb = int(lib().kanb200_edge_penalty_workspace_bytes()) if scratch else 0
+    ws = torch.empty(nb, dtype=torch.uint8, device=dev) if nb else None
     with _OnDevice(dev):
         _check(lib().kanb200_edge_penalty(_code(a.dtype), _p(a), a.numel(), float(mu1), float(mu2), _p(value),
-                                          _p(grad), _stream(dev)))
+                                          _p(grad), _p(ws), nb, _stream(dev)))
     return value, grad
 
 

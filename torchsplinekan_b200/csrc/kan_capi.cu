@@ -504,14 +504,18 @@ KANB200_API int kanb200_edge_abs_mean_x_backward(int dtype, int mode, const void
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_abs_mean_x_backward");
 }
 
+KANB200_API size_t kanb200_edge_penalty_workspace_bytes(void) { return edge_penalty_workspace_bytes(); }
+
 KANB200_API int kanb200_edge_penalty(int dtype, const void* a, int64_t n, double mu1, double mu2, void* value,
-                                     void* grad, void* stream) {
+                                     void* grad, void* workspace, size_t workspace_bytes, void* stream) {
     if (dtype != KANB200_F32 && dtype != KANB200_F64) return fail(KANB200_EINVAL, "edge_penalty: bad dtype");
     if (!a || !value || n < 1) return fail(KANB200_EINVAL, "edge_penalty: NULL pointer or no entries");
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e = dtype == KANB200_F32
-                        ? edge_penalty<float>((const float*)a, n, mu1, mu2, (float*)value, (float*)grad, st)
-                        : edge_penalty<double>((const double*)a, n, mu1, mu2, (double*)value, (double*)grad, st);
+                        ? edge_penalty<float>((const float*)a, n, mu1, mu2, (float*)value, (float*)grad, workspace,
+                                              workspace_bytes, st)
+                        : edge_penalty<double>((const double*)a, n, mu1, mu2, (double*)value, (double*)grad, workspace,
+                                               workspace_bytes, st);
     return e == cudaSuccess ? KANB200_OK : cuda_fail(e, "edge_penalty");
 }
 

@@ -73,7 +73,9 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
 // value = mu1 sum(a) + mu2 entropy(a / sum(a)) and its gradient with respect to a (NULL = not needed):
 // the scalar head of the activation regulariser in one launch.
 template <typename T>
-cudaError_t edge_penalty(const T* a, int64_t n, double mu1, double mu2, T* value, T* grad, cudaStream_t st);
+cudaError_t edge_penalty(const T* a, int64_t n, double mu1, double mu2, T* value, T* grad, void* ws, size_t ws_bytes,
+                         cudaStream_t st);
+size_t edge_penalty_workspace_bytes();      // scratch of the two-launch form (without it: one block)
 
 // The same operators straight from the layer input x (no H, no dH): see kan_reg.cu.  Scratch as for
 // edge_abs_mean_fwd / _bwd.

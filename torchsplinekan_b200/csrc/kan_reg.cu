@@ -877,14 +877,100 @@ edge_penalty_kernel(const T* __restrict__ a, int64_t n, double mu1, double mu2, 
     }
 }
 
+// The same in two launches that use the whole GPU (a statistic of 200 000 entries keeps the single block
+// above busy for 60 us).  With q = a / A,  sum q log q = (sum a log a - log A sum a) / A, so ONE pass
+// gives A and the entropy: every block leaves (sum a, sum a log a, number of zero entries) in the
+// workspace; the second kernel's blocks each add those partial sums in the same fixed order, block 0
+// writes the value and all of them write their share of the gradient, with the clamps decided per
+// element as above.  (An entry below tiny * A but above zero -- a denormal next to normal entries --
+// enters the entropy with its own q log q instead of tiny log tiny: a difference of 1e-36.)
+constexpr int PEN2_THREADS = 256, PEN2_MAX_BLOCKS = 256;
+constexpr size_t kPenaltyWorkspaceBytes = (size_t)PEN2_MAX_BLOCKS * 3 * sizeof(double);
+
+template <int THREADS>
+__device__ __forceinline__ void block_sum3(double (&v)[3], double (*red)[3]) {
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+        for (int o = 16; o > 0; o >>= 1) v[c] += __shfl_xor_sync(0xffffffffu, v[c], o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0)
+        for (int c = 0; c < 3; ++c) red[warp][c] = v[c];
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 3; ++c) {
+        double t = 0.0;
+        for (int w = 0; w < THREADS / 32; ++w) t += red[w][c];
+        v[c] = t;
+    }
+}
+
 template <typename T>
-cudaError_t edge_penalty(const T* a, int64_t n, double mu1, double mu2, T* value, T* grad, cudaStream_t st) {
+__global__ void __launch_bounds__(PEN2_THREADS)
+edge_penalty_partial_kernel(const T* __restrict__ a, int64_t n, double* __restrict__ partial) {
+    __shared__ double red[PEN2_THREADS / 32][3];
+    double v[3] = {0.0, 0.0, 0.0};
+    for (int64_t j = (int64_t)blockIdx.x * PEN2_THREADS + threadIdx.x; j < n; j += (int64_t)gridDim.x * PEN2_THREADS) {
+        const T aj = a[j];
+        if (aj > T(0)) {
+            v[0] += (double)aj;
+            v[1] += (double)(aj * log(aj));
+        } else {
+            v[2] += 1.0;
+        }
+    }
+    block_sum3<PEN2_THREADS>(v, red);
+    if (threadIdx.x == 0)
+        for (int c = 0; c < 3; ++c) partial[(size_t)blockIdx.x * 3 + c] = v[c];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(PEN2_THREADS)
+edge_penalty_finish_kernel(const T* __restrict__ a, int64_t n, const double* __restrict__ partial, int n_partial,
+                           double mu1, double mu2, T tiny, T* __restrict__ value, T* __restrict__ grad) {
+    __shared__ double red[PEN2_THREADS / 32][3];
+    double v[3] = {0.0, 0.0, 0.0};
+    for (int b = threadIdx.x; b < n_partial; b += PEN2_THREADS)          // same order in every block
+        for (int c = 0; c < 3; ++c) v[c] += partial[(size_t)b * 3 + c];
+    block_sum3<PEN2_THREADS>(v, red);
+    const T total = (T)v[0];
+    const T safe = total > tiny ? total : tiny;
+    // -sum p log p: entries above zero with their own q log q, zero entries clamped at tiny
+    const double ent = -((v[1] - log((double)safe) * v[0]) / (double)safe) - v[2] * ((double)tiny * log((double)tiny));
+    const T entropy = (T)ent;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *value = (T)(mu1 * (double)total + mu2 * (double)entropy);
+    if (!grad) return;
+    const T m1 = (T)mu1, m2 = (T)mu2;
+    const T dead = m1 + (total >= tiny ? m2 * ((T)1 - entropy) / safe : (T)0);
+    for (int64_t j = (int64_t)blockIdx.x * PEN2_THREADS + threadIdx.x; j < n; j += (int64_t)gridDim.x * PEN2_THREADS) {
+        const T q = a[j] / safe;
+        grad[j] = q >= tiny ? m1 - m2 * (log(q) + entropy) / safe : dead;
+    }
+}
+
+size_t edge_penalty_workspace_bytes() { return kPenaltyWorkspaceBytes; }
+
+template <typename T>
+cudaError_t edge_penalty(const T* a, int64_t n, double mu1, double mu2, T* value, T* grad, void* ws, size_t ws_bytes,
+                         cudaStream_t st) {
     const T tiny = sizeof(T) == 4 ? (T)1.17549435e-38 : (T)2.2250738585072014e-308;
-    edge_penalty_kernel<T><<<1, PEN_THREADS, 0, st>>>(a, n, mu1, mu2, tiny, value, grad);
+    if (!ws || ws_bytes < kPenaltyWorkspaceBytes || n < 4096) {
+        edge_penalty_kernel<T><<<1, PEN_THREADS, 0, st>>>(a, n, mu1, mu2, tiny, value, grad);
+        return cudaGetLastError();
+    }
+    int64_t blocks = (n + 4 * PEN2_THREADS - 1) / (4 * PEN2_THREADS);
+    if (blocks > PEN2_MAX_BLOCKS) blocks = PEN2_MAX_BLOCKS;
+    double* partial = reinterpret_cast<double*>(ws);
+    edge_penalty_partial_kernel<T><<<(int)blocks, PEN2_THREADS, 0, st>>>(a, n, partial);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    edge_penalty_finish_kernel<T><<<(int)blocks, PEN2_THREADS, 0, st>>>(a, n, partial, (int)blocks, mu1, mu2, tiny, value,
+                                                                          grad);
     return cudaGetLastError();
 }
-template cudaError_t edge_penalty<float>(const float*, int64_t, double, double, float*, float*, cudaStream_t);
-template cudaError_t edge_penalty<double>(const double*, int64_t, double, double, double*, double*, cudaStream_t);
+template cudaError_t edge_penalty<float>(const float*, int64_t, double, double, float*, float*, void*, size_t,
+                                         cudaStream_t);
+template cudaError_t edge_penalty<double>(const double*, int64_t, double, double, double*, double*, void*, size_t,
+                                          cudaStream_t);
 
 #define KAN_INSTANTIATE(T)                                                                               \
     template size_t edge_workspace<T>(int64_t, int, int, int, bool);                                     \

@@ -581,8 +581,10 @@ std::tuple<Tensor, Tensor> edge_penalty(const Tensor& a, double mu1, double mu2)
     cudaStream_t st = at::cuda::getCurrentCUDAStream();
     const Tensor ac = a.contiguous();
     Tensor value = at::empty({}, a.options()), grad = at::empty_like(ac);
+    const size_t ws_bytes = kanb200_edge_penalty_workspace_bytes();
+    Tensor ws = at::empty({(int64_t)ws_bytes}, a.options().dtype(at::kByte));
     check_rc(kanb200_edge_penalty(dtype_code(a), ac.data_ptr(), ac.numel(), mu1, mu2, value.data_ptr(),
-                                  grad.data_ptr(), st));
+                                  grad.data_ptr(), ws.data_ptr(), ws_bytes, st));
     return {value, grad.view(a.sizes())};
 }
 
