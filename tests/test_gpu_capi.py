@@ -818,3 +818,35 @@ def test_forward_small_batch_chains_as_work_items(N, I, O, G, k):
     torch.cuda.synchronize()
     assert torch.equal(y, y2)
     assert torch.equal(nat.forward(x, grid, bw, sw, sc, k, nat.MODE_TC_BF16X3), y)      # and from run to run
+
+
+@pytest.mark.parametrize("N,I,O,G,k,dtype,tol", [
+    (32768, 24, 1, 8, 3, np.float64, TOL64),      # scalar output, eleven basis functions (16-slot variant)
+    (40000, 9, 4, 5, 3, np.float32, TOL32),       # four outputs, ragged last block
+    (32768, 17, 3, 4, 2, np.float64, TOL64),
+    (33000, 6, 2, 12, 1, np.float32, TOL32),
+])
+def test_narrow_layer_kernels(N, I, O, G, k, dtype, tol):
+    """Layers with a handful of outputs and many samples (scalar heads: KAN[2,64,64,1]'s last layer) take
+    the narrow-layer kernels in AUTO mode: forward and all gradients against the float64 oracle on a
+    slice of the rows and against the gather kernels on all of them."""
+    from torchsplinekan_b200 import _native as nat
+    case = make_layer_case(N, I, O, G, k, dtype, seed=51, nonuniform=True)
+    x, grid, bw, sw, sc = dev(case["x"]), dev(case["grid"]), dev(case["bw"]), dev(case["sw"]), dev(case["sc"])
+    y = nat.forward(x, grid, bw, sw, sc, k, nat.MODE_AUTO)
+    D = 2.0 * y
+    got = nat.backward(D, x, grid, bw, sw, sc, k, True, True, True, True, nat.MODE_AUTO)
+    ys = nat.forward(x, grid, bw, sw, sc, k, nat.MODE_SIMT)
+    want = nat.backward(D, x, grid, bw, sw, sc, k, True, True, True, True, nat.MODE_SIMT)
+    f = lambda t: t.double().cpu().numpy()
+    assert rel_err(f(y), f(ys)) < tol
+    for a, b in zip(got, want):
+        assert rel_err(f(a), f(b)) < tol * 4
+    # oracle on the first 512 rows (forward and input gradient are row-wise)
+    sub = {n: (v[:512] if n == "x" else v) for n, v in case.items()}
+    yo, Do, gxo = oracle_step(sub)[:3]
+    assert rel_err(f(y[:512]), yo) < tol
+    assert rel_err(f(got[0][:512]), gxo) < tol * 4
+    # without parameter gradients no workspace is needed
+    gx_only = nat.backward(D, x, grid, bw, sw, sc, k, True, False, False, False, nat.MODE_AUTO)
+    assert torch.equal(gx_only[0], got[0]) and gx_only[1] is None

@@ -44,6 +44,18 @@ bool make_shape(int64_t N, int64_t I, int64_t O, int G, int k, LayerShape& s) {
     return true;
 }
 
+// Whether a layer call takes the narrow-layer kernels (AUTO only): a handful of outputs, where the
+// 256-output tile of the tensor-core kernels and the 64-wide tiles of the float64 matrix-instruction
+// kernels mostly compute padding, and enough samples to fill the GPU with blocks of 64.  Measured
+// (us, forward / backward, narrow against the kernels it replaces): 64 -> 1 at 131072 rows float32
+// 156 / 464 against 288 / 1018, float64 242 / 799 against 279 / 874; where they lose -- 256 -> 10 at
+// 8192 rows 278 / 260 against 74 / 156, float64 64 -> 16 at 4096 rows 162 / 172 against 64 / 116 --
+// they are not chosen.
+bool layer_uses_narrow(int mode, int dtype, const LayerShape& s) {
+    if (mode != KANB200_MODE_AUTO || !narrow_layer_supported(s.O, s.R(), s.K)) return false;
+    return s.O <= 4 && s.N >= 32768 && (dtype == KANB200_F64 || dtype == KANB200_F32);
+}
+
 // Whether the from-x edge statistic takes the tensor-core kernel for this problem.
 bool edge_x_uses_tc(int mode, int dtype, const LayerShape& s) {
     if (dtype != KANB200_F32 || mode == KANB200_MODE_SIMT || !tc_edge_supported(s)) return false;
@@ -163,6 +175,11 @@ KANB200_API size_t kanb200_workspace_bytes(int op, int mode, int dtype, int64_t 
         return kWsHeader + (dtype == KANB200_F32 ? edge_workspace<float>(N, s.I, s.O, s.R(), b)
                                                  : edge_workspace<double>(N, s.I, s.O, s.R(), b));
     }
+    if (layer_uses_narrow(mode, dtype, s)) {
+        if (op == KANB200_OP_FORWARD || !need_param) return 0;
+        return kWsHeader + (dtype == KANB200_F32 ? narrow_layer_workspace<float>(N, s.I, s.O, s.R())
+                                                 : narrow_layer_workspace<double>(N, s.I, s.O, s.R()));
+    }
     const int m = kanb200_resolve_mode_for(op == KANB200_OP_FORWARD ? KANB200_OP_FORWARD : KANB200_OP_BACKWARD, mode,
                                            dtype, N, I, O, G, k);
     if (m < 0) return 0;
@@ -259,7 +276,15 @@ KANB200_API int kanb200_forward(int dtype, int mode, const void* x, const void* 
     make_shape(N, I, O, G, k, s);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (m == KANB200_MODE_SIMT && dtype == KANB200_F64 && dense64_supported(s)) {
+    if (layer_uses_narrow(mode, dtype, s)) {
+        e = dtype == KANB200_F32
+                ? narrow_layer_forward<float>((const float*)x, (const float*)grid, (const float*)base_weight,
+                                              (const float*)spline_weight, (const float*)spline_scaler, (float*)y, N,
+                                              s.I, s.O, s.R(), k, st)
+                : narrow_layer_forward<double>((const double*)x, (const double*)grid, (const double*)base_weight,
+                                               (const double*)spline_weight, (const double*)spline_scaler, (double*)y,
+                                               N, s.I, s.O, s.R(), k, st);
+    } else if (m == KANB200_MODE_SIMT && dtype == KANB200_F64 && dense64_supported(s)) {
         e = dense64_forward((const double*)x, (const double*)grid, (const double*)base_weight,
                             (const double*)spline_weight, (const double*)spline_scaler, (double*)y, s,
                             workspace, workspace_bytes, st);
@@ -339,7 +364,22 @@ KANB200_API int kanb200_backward(int dtype, int mode, const void* grad_out, cons
     make_shape(N, I, O, G, k, s);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (m == KANB200_MODE_SIMT && dtype == KANB200_F64 && dense64_supported(s)) {
+    if (layer_uses_narrow(mode, dtype, s)) {
+        void* body = ws_body(workspace, workspace_bytes);
+        const size_t body_bytes = ws_body_bytes(workspace, workspace_bytes);
+        e = dtype == KANB200_F32
+                ? narrow_layer_backward<float>((const float*)grad_out, (const float*)x, (const float*)grid,
+                                               (const float*)base_weight, (const float*)spline_weight,
+                                               (const float*)spline_scaler, (float*)grad_x, (float*)grad_base_weight,
+                                               (float*)grad_spline_weight, (float*)grad_spline_scaler, N, s.I, s.O,
+                                               s.R(), k, body, body_bytes, st)
+                : narrow_layer_backward<double>((const double*)grad_out, (const double*)x, (const double*)grid,
+                                                (const double*)base_weight, (const double*)spline_weight,
+                                                (const double*)spline_scaler, (double*)grad_x,
+                                                (double*)grad_base_weight, (double*)grad_spline_weight,
+                                                (double*)grad_spline_scaler, N, s.I, s.O, s.R(), k, body, body_bytes,
+                                                st);
+    } else if (m == KANB200_MODE_SIMT && dtype == KANB200_F64 && dense64_supported(s)) {
         e = dense64_backward((const double*)grad_out, (const double*)x, (const double*)grid,
                              (const double*)base_weight, (const double*)spline_weight, (const double*)spline_scaler,
                              (double*)grad_x, (double*)grad_base_weight, (double*)grad_spline_weight,

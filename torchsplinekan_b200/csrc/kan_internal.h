@@ -70,6 +70,20 @@ cudaError_t edge_abs_mean_bwd(const T* ga, const T* s, const T* H, const T* bw, 
                               T* ds, T* dH, T* dbw, T* dW,
                               int64_t N, int I, int O, int R, void* ws, size_t ws_bytes, cudaStream_t st);
 
+// Layers of at most 16 outputs (classifier heads, scalar outputs) on the FMA pipes: one kernel for the
+// forward; one kernel for all gradients plus a small pass for the scaler algebra (per-split slabs, no
+// atomics).  Any float type, k <= 3, at most 16 basis functions per feature.
+bool narrow_layer_supported(int O, int R, int k);
+template <typename T>
+size_t narrow_layer_workspace(int64_t N, int I, int O, int R);
+template <typename T>
+cudaError_t narrow_layer_forward(const T* x, const T* grid, const T* bw, const T* sw, const T* scaler, T* y, int64_t N,
+                                 int I, int O, int R, int k, cudaStream_t st);
+template <typename T>
+cudaError_t narrow_layer_backward(const T* dY, const T* x, const T* grid, const T* bw, const T* sw, const T* scaler,
+                                  T* gx, T* gbw, T* gsw, T* gscaler, int64_t N, int I, int O, int R, int k, void* ws,
+                                  size_t ws_bytes, cudaStream_t st);
+
 // value = mu1 sum(a) + mu2 entropy(a / sum(a)) and its gradient with respect to a (NULL = not needed):
 // the scalar head of the activation regulariser in one launch.
 template <typename T>

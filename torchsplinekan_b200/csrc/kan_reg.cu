@@ -488,19 +488,23 @@ inline int grid_1d(int64_t work, int threads, int cap = 148 * 32) {
 // slabs, summed in fixed order: no atomics.  Measured, 8192 rows, statistic / all gradients in us:
 // 256 -> 10: 68 / 172 (tensor-core kernels 69 / 283, the 32-output FMA kernels 145 / 580), 256 -> 4:
 // 49 / 105, 64 -> 16: 29 / 68 (37 / 110); 65536 rows, 64 -> 1: 90 / 195 (101 / 496).
-constexpr int EN_THREADS = 128, EN_R = 8;
+constexpr int EN_THREADS = 128, EN_R = 8;            // EN_R: slots per feature of the edge kernels (R <= 8)
 constexpr int kNarrowMaxO = 16;
 
-template <typename T, int K, int OT, bool GRAD>
+// RM = slots kept per feature (8 or 16).  LAYER = false: the edge statistic (g = sign(phi) ga / N).
+// LAYER = true: the backward of the layer itself, y = sum_i phi: g = dY[n, o] (passed as `ga`, [N, O]),
+// phi is not needed, and `W` are the raw coefficients that `scaler` (may be NULL) multiplies.
+template <typename T, int K, int OT, bool GRAD, int RM = EN_R, bool LAYER = false>
 __global__ void __launch_bounds__(EN_THREADS)
 edge_narrow_kernel(const T* __restrict__ x, const T* __restrict__ s, const T* __restrict__ grid,
                    const T* __restrict__ bw, const T* __restrict__ W, const T* __restrict__ ga,
                    T* __restrict__ pa, T* __restrict__ pdW, T* __restrict__ pdbw, T* __restrict__ gx,
-                   T* __restrict__ ds, int64_t N, int I, int O, int R, int64_t rows_per_split) {
+                   T* __restrict__ ds, int64_t N, int I, int O, int R, int64_t rows_per_split,
+                   const T* __restrict__ scaler = nullptr) {
     __shared__ T knots[kMaxKnots];
-    constexpr int WROW = EN_R + 4;                       // rows start on 16-byte boundaries
+    constexpr int WROW = RM + 4;                       // rows start on 16-byte boundaries
     __shared__ __align__(16) T Ws[OT][WROW];             // [r < 8] weights, [8] base weight, [9] ga / N
-    __shared__ T red[EN_THREADS / 32][OT * (EN_R + 1)];
+    __shared__ T red[EN_THREADS / 32][OT * (RM + 1)];
     const int i = blockIdx.x, split = blockIdx.y, tid = threadIdx.x;
     const int nk = R + K + 1;
     const bool has_base = bw != nullptr;
@@ -517,18 +521,18 @@ edge_narrow_kernel(const T* __restrict__ x, const T* __restrict__ s, const T* __
             T v = T(0);
             if (o0 + o < O) {
                 const size_t oi = (size_t)(o0 + o) * I + i;
-                if (r < EN_R) v = r < R ? W[oi * R + r] : T(0);
-                else if (r == EN_R) v = has_base ? bw[oi] : T(0);
-                else if (r == EN_R + 1) v = (GRAD && ga) ? ga[oi] * invN : T(0);
+                if (r < RM) v = r < R ? W[oi * R + r] * ((LAYER && scaler) ? scaler[oi] : T(1)) : T(0);
+                else if (r == RM) v = has_base ? bw[oi] : T(0);
+                else if (r == RM + 1) v = (GRAD && !LAYER && ga) ? ga[oi] * invN : T(0);
             }
             Ws[o][r] = v;
         }
         __syncthreads();
-        T acc[OT][GRAD ? EN_R + 1 : 1];
+        T acc[OT][GRAD ? RM + 1 : 1];
 #pragma unroll
         for (int o = 0; o < OT; ++o)
 #pragma unroll
-            for (int r = 0; r < (GRAD ? EN_R + 1 : 1); ++r) acc[o][r] = T(0);
+            for (int r = 0; r < (GRAD ? RM + 1 : 1); ++r) acc[o][r] = T(0);
 
         // the next sample's input (and base value) is loaded while this one is processed
         T x_next = n_begin + tid < n_end ? x[(size_t)(n_begin + tid) * I + i] : T(0);
@@ -539,16 +543,16 @@ edge_narrow_kernel(const T* __restrict__ x, const T* __restrict__ s, const T* __
                 x_next = x[(size_t)(n + EN_THREADS) * I + i];
                 if (s && has_base) s_next = s[(size_t)(n + EN_THREADS) * I + i];
             }
-            T A[EN_R], dA[EN_R];
+            T A[RM], dA[RM];
 #pragma unroll
-            for (int r = 0; r < EN_R; ++r) { A[r] = T(0); dA[r] = T(0); }
+            for (int r = 0; r < RM; ++r) { A[r] = T(0); dA[r] = T(0); }
             const int m = locate_span(knots, nk, xv);
             if (m >= 0) {
                 T v[K + 1], d[K + 1];
                 window_values<K, T, true>(knots, nk, m, xv, v, d);
                 // registers cannot be indexed by m: every slot picks its value by comparison
 #pragma unroll
-                for (int r = 0; r < EN_R; ++r) {
+                for (int r = 0; r < RM; ++r) {
 #pragma unroll
                     for (int j = 0; j <= K; ++j) {
                         const bool hit = (r == m - K + j) && r < R;
@@ -562,34 +566,38 @@ edge_narrow_kernel(const T* __restrict__ x, const T* __restrict__ s, const T* __
 #pragma unroll
             for (int o = 0; o < OT; ++o) {
                 // the row of weights in 16-byte pieces (broadcast reads), used for phi and for dphi/dx
-                T w[EN_R];
+                T w[RM];
                 {
                     using V = typename std::conditional<sizeof(T) == 4, float4, double2>::type;
                     constexpr int PER = 16 / sizeof(T);
                     const V* src = reinterpret_cast<const V*>(&Ws[o][0]);
 #pragma unroll
-                    for (int q = 0; q < EN_R / PER; ++q) {
+                    for (int q = 0; q < RM / PER; ++q) {
                         const V v = src[q];
                         const T* pv = reinterpret_cast<const T*>(&v);
 #pragma unroll
                         for (int e = 0; e < PER; ++e) w[q * PER + e] = pv[e];
                     }
                 }
-                T phi = Ws[o][EN_R] * sv;
+                T phi = T(0);
+                if (!LAYER) {
+                    phi = Ws[o][RM] * sv;
 #pragma unroll
-                for (int r = 0; r < EN_R; ++r) phi = fma(w[r], A[r], phi);
+                    for (int r = 0; r < RM; ++r) phi = fma(w[r], A[r], phi);
+                }
                 if (!GRAD) {
                     acc[o][0] += fabs(phi);
                 } else {
-                    const T g = signed_weight<T>(Ws[o][EN_R + 1], phi);
+                    const T g = LAYER ? (o0 + o < O ? ga[(size_t)n * O + o0 + o] : T(0))
+                                      : signed_weight<T>(Ws[o][RM + 1], phi);
 #pragma unroll
-                    for (int r = 0; r < EN_R; ++r) acc[o][r] = fma(g, A[r], acc[o][r]);
-                    acc[o][GRAD ? EN_R : 0] = fma(g, sv, acc[o][GRAD ? EN_R : 0]);
+                    for (int r = 0; r < RM; ++r) acc[o][r] = fma(g, A[r], acc[o][r]);
+                    acc[o][GRAD ? RM : 0] = fma(g, sv, acc[o][GRAD ? RM : 0]);
                     T dphi = T(0);
 #pragma unroll
-                    for (int r = 0; r < EN_R; ++r) dphi = fma(w[r], dA[r], dphi);
+                    for (int r = 0; r < RM; ++r) dphi = fma(w[r], dA[r], dphi);
                     g_basis = fma(g, dphi, g_basis);
-                    g_base = fma(g, Ws[o][EN_R], g_base);
+                    g_base = fma(g, Ws[o][RM], g_base);
                 }
             }
             if (GRAD) {
@@ -609,7 +617,7 @@ edge_narrow_kernel(const T* __restrict__ x, const T* __restrict__ s, const T* __
         }
 
         // block sum of the accumulators: shuffles inside a warp, shared memory across the four warps
-        constexpr int CNT = GRAD ? EN_R + 1 : 1;
+        constexpr int CNT = GRAD ? RM + 1 : 1;
 #pragma unroll
         for (int o = 0; o < OT; ++o)
 #pragma unroll
@@ -627,11 +635,124 @@ edge_narrow_kernel(const T* __restrict__ x, const T* __restrict__ s, const T* __
             const size_t oi = (size_t)(o0 + o) * I + i;
             if (!GRAD) {
                 pa[(size_t)split * oi_all + oi] = v;
-            } else if (r < EN_R) {
+            } else if (r < RM) {
                 if (pdW && r < R) pdW[((size_t)split * oi_all + oi) * R + r] = v;
             } else if (pdbw) {
                 pdbw[(size_t)split * oi_all + oi] = v;
             }
+        }
+    }
+}
+
+// Layer forward for at most 16 outputs:  y[n, o] = sum_i ( bw[o,i] silu(x[n,i]) + sum_r W[o,i,r] scaler[o,i] B_r(x[n,i]) ).
+// A block owns 64 samples; its 128 threads are 64 samples x 2 halves that take alternate chunks of
+// eight features (knots and effective weights of a chunk staged in shared memory); a thread
+// evaluates the k+1 non-zero basis values of its sample and gathers the matching coefficients.
+constexpr int NF_FC = 8, NF_ROWS = 64;
+template <typename T, int K, int OT>
+__global__ void __launch_bounds__(EN_THREADS)
+narrow_layer_forward_kernel(const T* __restrict__ x, const T* __restrict__ grid, const T* __restrict__ bw,
+                            const T* __restrict__ sw, const T* __restrict__ scaler, T* __restrict__ y, int64_t N, int I,
+                            int O, int R) {
+    constexpr int RW = 20;                                   // R + 1 <= 17 values per (feature, output)
+    __shared__ T knots[2][NF_FC][kMaxKnots];
+    __shared__ T Ws[2][NF_FC][OT][RW];
+    __shared__ T ysum[NF_ROWS][OT + 1];
+    const int tid = threadIdx.x, half = tid >> 6, nl = tid & (NF_ROWS - 1);
+    const int nk = R + K + 1;
+    const int64_t n = (int64_t)blockIdx.x * NF_ROWS + nl;
+    const bool row_ok = n < N;
+    const bool has_base = bw != nullptr;
+    const int n_chunks = (I + NF_FC - 1) / NF_FC;
+    for (int o0 = 0; o0 < O; o0 += OT) {
+        T acc[OT];
+#pragma unroll
+        for (int o = 0; o < OT; ++o) acc[o] = T(0);
+        // both halves walk ceil(n_chunks / 2) rounds together (block barriers inside)
+        for (int c0 = 0; c0 < n_chunks; c0 += 2) {
+            __syncthreads();
+            for (int e = tid; e < 2 * NF_FC * nk; e += EN_THREADS) {
+                const int h = e / (NF_FC * nk), rem = e - h * (NF_FC * nk);
+                const int fi = rem / nk, q = rem - fi * nk;
+                const int i = (c0 + h) * NF_FC + fi;
+                knots[h][fi][q] = i < I ? grid[(size_t)i * nk + q] : T(0);
+            }
+            for (int e = tid; e < 2 * NF_FC * OT * (R + 1); e += EN_THREADS) {
+                const int h = e / (NF_FC * OT * (R + 1));
+                int rem = e - h * (NF_FC * OT * (R + 1));
+                const int fi = rem / (OT * (R + 1));
+                rem -= fi * (OT * (R + 1));
+                const int o = rem / (R + 1), r = rem - o * (R + 1);
+                const int i = (c0 + h) * NF_FC + fi;
+                T v = T(0);
+                if (i < I && o0 + o < O) {
+                    const size_t oi = (size_t)(o0 + o) * I + i;
+                    if (r < R) v = sw[oi * R + r] * (scaler ? scaler[oi] : T(1));
+                    else v = has_base ? bw[oi] : T(0);
+                }
+                Ws[h][fi][o][r] = v;
+            }
+            __syncthreads();
+            const int i_first = (c0 + half) * NF_FC;
+            if (row_ok && i_first < I) {
+#pragma unroll 1
+                for (int fi = 0; fi < NF_FC; ++fi) {
+                    const int i = i_first + fi;
+                    if (i >= I) break;
+                    const T xv = x[(size_t)n * I + i];
+                    const T sv = has_base ? silu_t<T>(xv) : T(0);
+                    const int m = locate_span(&knots[half][fi][0], nk, xv);
+                    T v[K + 1], unused[K + 1], w[K + 1];
+                    if (m >= 0) window_values<K, T, false>(&knots[half][fi][0], nk, m, xv, v, unused);
+                    const int first = window_in_range<K, T>(m, R, v, w);
+#pragma unroll
+                    for (int o = 0; o < OT; ++o) {
+                        const T* wr = &Ws[half][fi][o][0];
+                        T a = wr[R] * sv;
+#pragma unroll
+                        for (int j = 0; j <= K; ++j) a = fma(wr[first + j], w[j], a);
+                        acc[o] += a;
+                    }
+                }
+            }
+        }
+        // the two halves of a sample add up through shared memory
+        __syncthreads();
+        if (half == 1)
+#pragma unroll
+            for (int o = 0; o < OT; ++o) ysum[nl][o] = acc[o];
+        __syncthreads();
+        if (half == 0 && row_ok)
+#pragma unroll
+            for (int o = 0; o < OT; ++o)
+                if (o0 + o < O) y[(size_t)n * O + o0 + o] = acc[o] + ysum[nl][o];
+    }
+}
+
+// Parameter gradients of the narrow layer from the per-split slabs of edge_narrow_kernel<..., LAYER = true>:
+// dW_eff = sum of the slabs; gsw = scaler dW_eff, gscaler = sum_r sw dW_eff, gbw = sum of its slabs.
+template <typename T>
+__global__ void narrow_layer_finalize_kernel(const T* __restrict__ pdW, const T* __restrict__ pdbw,
+                                             const T* __restrict__ sw, const T* __restrict__ scaler,
+                                             T* __restrict__ gsw, T* __restrict__ gscaler, T* __restrict__ gbw,
+                                             int64_t oi_count, int R, int splits) {
+    for (int64_t oi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; oi < oi_count;
+         oi += (int64_t)gridDim.x * blockDim.x) {
+        if (gsw || gscaler) {
+            const T sc = scaler ? scaler[oi] : T(1);
+            T gs = T(0);
+            for (int r = 0; r < R; ++r) {
+                T d = T(0);
+                for (int sp = 0; sp < splits; ++sp) d += pdW[((size_t)sp * oi_count + oi) * R + r];
+                if (gsw) gsw[oi * R + r] = sc * d;
+                if (gscaler) gs += sw[oi * R + r] * d;
+            }
+            if (gscaler) gscaler[oi] = gs;
+        }
+        if (gbw) {
+            T d = T(0);
+            for (int sp = 0; sp < splits; ++sp) d += pdbw[(size_t)sp * oi_count + oi];
+            gbw[oi] = d;
         }
     }
 }
@@ -972,6 +1093,65 @@ template cudaError_t edge_penalty<float>(const float*, int64_t, double, double, 
 template cudaError_t edge_penalty<double>(const double*, int64_t, double, double, double*, double*, void*, size_t,
                                           cudaStream_t);
 
+// ---------------------------------------------------------------------------
+// Layer forward / backward for at most 16 outputs (any float type, k <= 3, R <= 16)
+// ---------------------------------------------------------------------------
+bool narrow_layer_supported(int O, int R, int k) { return O >= 1 && O <= kNarrowMaxO && R <= 16 && k >= 1 && k <= 3; }
+
+template <typename T>
+size_t narrow_layer_workspace(int64_t N, int I, int O, int R) {
+    return (size_t)narrow_splits(N, I) * (size_t)O * I * (size_t)(R + 1) * sizeof(T);
+}
+
+template <typename T>
+cudaError_t narrow_layer_forward(const T* x, const T* grid, const T* bw, const T* sw, const T* scaler, T* y, int64_t N,
+                                 int I, int O, int R, int k, cudaStream_t st) {
+    if (N < 1) return cudaSuccess;
+    const int blocks = (int)((N + NF_ROWS - 1) / NF_ROWS);
+    constexpr int OT = sizeof(T) == 4 ? 16 : 8;
+    if (O <= 4) {
+        KAN_EDGE_K(k, (narrow_layer_forward_kernel<T, KK, 4><<<blocks, EN_THREADS, 0, st>>>(x, grid, bw, sw, scaler, y, N,
+                                                                                           I, O, R)));
+    } else {
+        KAN_EDGE_K(k, (narrow_layer_forward_kernel<T, KK, OT><<<blocks, EN_THREADS, 0, st>>>(x, grid, bw, sw, scaler, y,
+                                                                                            N, I, O, R)));
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t narrow_layer_backward(const T* dY, const T* x, const T* grid, const T* bw, const T* sw, const T* scaler,
+                                  T* gx, T* gbw, T* gsw, T* gscaler, int64_t N, int I, int O, int R, int k, void* ws,
+                                  size_t ws_bytes, cudaStream_t st) {
+    if (N < 1) return cudaSuccess;
+    const bool want_param = gsw || gscaler || (gbw && bw);
+    const int splits = narrow_splits(N, I);
+    const size_t oi = (size_t)O * I;
+    if (want_param && (!ws || ws_bytes < narrow_layer_workspace<T>(N, I, O, R))) return cudaErrorMemoryAllocation;
+    T* pdW = reinterpret_cast<T*>(ws);
+    T* pdbw = want_param ? pdW + (size_t)splits * oi * R : nullptr;
+    const int64_t rows = (N + splits - 1) / splits;
+    const dim3 blocks(I, splits);
+    T* pw = (gsw || gscaler) ? pdW : nullptr;
+    T* pb = (gbw && bw) ? pdbw : nullptr;
+    // accumulators per thread: outputs x (slots + 1); float 8 x 9 or 4 x 17, double 4 x 9 or 2 x 17
+    if (R <= EN_R) {
+        constexpr int OT = sizeof(T) == 4 ? 8 : 4;
+        KAN_EDGE_K(k, (edge_narrow_kernel<T, KK, OT, true, EN_R, true><<<blocks, EN_THREADS, 0, st>>>(
+                          x, nullptr, grid, bw, sw, dY, nullptr, pw, pb, gx, nullptr, N, I, O, R, rows, scaler)));
+    } else {
+        constexpr int OT = sizeof(T) == 4 ? 4 : 2;
+        KAN_EDGE_K(k, (edge_narrow_kernel<T, KK, OT, true, 16, true><<<blocks, EN_THREADS, 0, st>>>(
+                          x, nullptr, grid, bw, sw, dY, nullptr, pw, pb, gx, nullptr, N, I, O, R, rows, scaler)));
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess || !want_param) return e;
+    narrow_layer_finalize_kernel<T><<<grid_1d((int64_t)oi, 256), 256, 0, st>>>(pdW, pdbw, sw, scaler, gsw, gscaler,
+                                                                              (gbw && bw) ? gbw : nullptr, (int64_t)oi, R,
+                                                                              splits);
+    return cudaGetLastError();
+}
+
 #define KAN_INSTANTIATE(T)                                                                               \
     template size_t edge_workspace<T>(int64_t, int, int, int, bool);                                     \
     template cudaError_t edge_abs_mean_fwd<T>(const T*, const T*, const T*, const T*, T*, int64_t, int,  \
@@ -984,5 +1164,13 @@ template cudaError_t edge_penalty<double>(const double*, int64_t, double, double
                                                 T*, T*, T*, int64_t, int, int, int, int, void*, size_t, cudaStream_t);
 KAN_INSTANTIATE(float)
 KAN_INSTANTIATE(double)
+#define KAN_INSTANTIATE_NARROW(T)                                                                              \
+    template size_t narrow_layer_workspace<T>(int64_t, int, int, int);                                         \
+    template cudaError_t narrow_layer_forward<T>(const T*, const T*, const T*, const T*, const T*, T*, int64_t, int,  \
+                                                 int, int, int, cudaStream_t);                                 \
+    template cudaError_t narrow_layer_backward<T>(const T*, const T*, const T*, const T*, const T*, const T*, T*, T*, \
+                                                  T*, T*, int64_t, int, int, int, int, void*, size_t, cudaStream_t);
+KAN_INSTANTIATE_NARROW(float)
+KAN_INSTANTIATE_NARROW(double)
 
 }  // namespace kanb200
