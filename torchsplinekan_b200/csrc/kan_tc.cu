@@ -419,11 +419,14 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                 }
             };
             if (kb0 < P.kb_spline) prefetch_spline(kb0);
+            // position inside the chain, kept as a counter (kb0 starts a chain): a division per block in
+            // each of the 512 workers is a measurable share of their instruction stream
+            int in_chain = 0;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t stage = it % FWD_A_STAGES;
                 const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                 const uint32_t a_lo = a_hi + TILE_A_BYTES;
-                const bool chunk_start = (kb % P.chunk_kb) == 0;
+                const bool chunk_start = in_chain == 0;
                 if (kb < P.kb_spline) {
                     int f0, cw0, f1, cw1;
                     chunk_pair(kb, f0, cw0, f1, cw1);
@@ -482,7 +485,8 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                         break;
                     }
                 }
-                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1) {
+                if (++in_chain == P.chunk_kb) in_chain = 0;
+                if (in_chain == 0 || kb + 1 == kb1) {
                     pend = true;
                     pend_first = P.n_ksplit > 1 || kb < P.chunk_kb;
                     pend_mt = mt;
@@ -507,12 +511,14 @@ tc_forward_kernel(const float* __restrict__ x, const float* __restrict__ tab, co
                 const int64_t mt = tile / P.n_opairs;
                 const int op = (int)(tile - mt * P.n_opairs);
                 const int nsub = (P.n_otiles - 2 * op) >= 2 ? 2 : 1;
+                int in_chain = 0;
                 for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
                     const uint32_t stage = it % FWD_A_STAGES;
                     const uint32_t a_hi = sbase + FWD_SMEM_A + stage * FWD_A_STAGE_BYTES;
                     const uint32_t a_lo = a_hi + TILE_A_BYTES;
-                    const bool chunk_start = (kb % P.chunk_kb) == 0;
-                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1;
+                    const bool chunk_start = in_chain == 0;
+                    if (++in_chain == P.chunk_kb) in_chain = 0;
+                    const bool chunk_end = in_chain == 0 || kb + 1 == kb1;
                     if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FWD_A_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -748,9 +754,10 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                     if (cw1 == cpf) { f1 = f0 + 1; cw1 = 0; }
                 }
             };
+            int in_chain = 0;                                      // position inside the chain (kb0 starts one)
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t stage = it % FTS_A_STAGES;
-                const bool chunk_start = (kb % P.chunk_kb) == 0;
+                const bool chunk_start = in_chain == 0;
                 if ((int)stage == part) {
                     // operand stage in tensor memory: 32 columns of bf16 pairs (hi), then 32 (lo)
                     const uint32_t a_hi = tmem_base + ((uint32_t)(quad * 32) << 16) + FTS_TMEM_A + stage * 64;
@@ -833,7 +840,8 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                         break;
                     }
                 }
-                if ((kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1) {
+                if (++in_chain == P.chunk_kb) in_chain = 0;
+                if (in_chain == 0 || kb + 1 == kb1) {
                     pend = true;
                     pend_first = P.n_ksplit > 1 || kb < P.chunk_kb;
                     pend_mt = mt;
@@ -856,12 +864,14 @@ tc_forward_ts_kernel(const float* __restrict__ x, const float* __restrict__ tab,
                 float* dst;
                 fwd_item(P, item, y, tile, kb0, kb1, dst);
                 const int nsub = 1;
+                int in_chain = 0;
                 for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
                     const uint32_t stage = it % FTS_A_STAGES;
                     const uint32_t a_hi = tmem_base + FTS_TMEM_A + stage * 64;
                     const uint32_t a_lo = a_hi + 32;
-                    const bool chunk_start = (kb % P.chunk_kb) == 0;
-                    const bool chunk_end = (kb + 1) % P.chunk_kb == 0 || kb + 1 == kb1;
+                    const bool chunk_start = in_chain == 0;
+                    if (++in_chain == P.chunk_kb) in_chain = 0;
+                    const bool chunk_end = in_chain == 0 || kb + 1 == kb1;
                     if (!mbar_wait(smem_u32(&ctrl->fullA[stage]), (it / FTS_A_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -1156,11 +1166,14 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                 }
             };
             if (spline) prefetch_spline(kb0);
+            // position inside the chain, kept as a counter: a 64-bit division per block in each of the 512
+            // workers is a measurable share of their instruction stream
+            int in_chain = 0;
             for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
                 const uint32_t stage = it % BWD_G_STAGES;
                 const uint32_t g_hi = sbase + BWD_SMEM_G + stage * BWD_G_STAGE_BYTES;
                 const uint32_t g_lo = g_hi + TILE_B_BYTES;
-                const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
+                const bool chunk_start = in_chain == 0;
                 if (spline) {
                     float xv[4];
 #pragma unroll
@@ -1226,7 +1239,8 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                         break;
                     }
                 }
-                if (((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1) {
+                if (++in_chain == plan.chunk_kb) in_chain = 0;
+                if (in_chain == 0 || kb + 1 == kb1) {
                     pend = true;
                     pend_first = (kb - kb0) < plan.chunk_kb;
                     pend_sp = sp;
@@ -1247,12 +1261,14 @@ tc_bwd_param_kernel(const float* __restrict__ x, const float* __restrict__ tab, 
                 decode(item, sp, ot, ct);
                 int64_t kb0, kb1;
                 k_range(sp, kb0, kb1);
+                int in_chain = 0;
                 for (int64_t kb = kb0; kb < kb1 && ok; ++kb, ++it) {
                     const uint32_t stage = it % BWD_G_STAGES;
                     const uint32_t g_hi = sbase + BWD_SMEM_G + stage * BWD_G_STAGE_BYTES;
                     const uint32_t g_lo = g_hi + TILE_B_BYTES;
-                    const bool chunk_start = ((kb - kb0) % plan.chunk_kb) == 0;
-                    const bool chunk_end = ((kb - kb0) + 1) % plan.chunk_kb == 0 || kb + 1 == kb1;
+                    const bool chunk_start = in_chain == 0;
+                    if (++in_chain == plan.chunk_kb) in_chain = 0;
+                    const bool chunk_end = in_chain == 0 || kb + 1 == kb1;
                     if (!mbar_wait(smem_u32(&ctrl->fullG[stage]), (it / BWD_G_STAGES) & 1u, abort_flag)) {
                         ok = false;
                         break;
