@@ -775,10 +775,15 @@ cudaError_t launch_edge_narrow(const T* x, const T* s, const T* grid, const T* b
     const int64_t rows = (N + splits - 1) / splits;
     const dim3 blocks(I, splits);
     // outputs whose accumulators (nine each with gradients, one without) fit the register file:
-    // float 16 (8 when the layer has no more), double 4 with gradients and 8 without
+    // float 16 (12 or 8 when the layer has no more: idle output slots cost their share of the work), double 4
+    // with gradients and 8 without
     constexpr int OT_SMALL = sizeof(T) == 4 ? 8 : (GRAD ? 4 : 8);
     constexpr int OT_WIDE = sizeof(T) == 4 ? 16 : OT_SMALL;
-    if (O > OT_SMALL && OT_WIDE > OT_SMALL) {
+    constexpr int OT_MID = sizeof(T) == 4 ? 12 : OT_SMALL;
+    if (O > OT_SMALL && O <= OT_MID && OT_MID > OT_SMALL) {
+        KAN_EDGE_K(k, (edge_narrow_kernel<T, KK, OT_MID, GRAD><<<blocks, EN_THREADS, 0, st>>>(
+                          x, s, grid, bw, W, ga, pa, pdW, pdbw, gx, ds, N, I, O, R, rows)));
+    } else if (O > OT_SMALL && OT_WIDE > OT_SMALL) {
         KAN_EDGE_K(k, (edge_narrow_kernel<T, KK, OT_WIDE, GRAD><<<blocks, EN_THREADS, 0, st>>>(
                           x, s, grid, bw, W, ga, pa, pdW, pdbw, gx, ds, N, I, O, R, rows)));
     } else {
