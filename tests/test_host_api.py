@@ -47,6 +47,15 @@ def test_mode_resolution_and_workspace_sizes():
     # wide grids (a feature owns ceil((G + k) / 8) chunks of 8 columns) stay on the tensor cores
     assert _native.resolve_mode(_native.MODE_AUTO, f32, 16384, 512, 512, 64, 3) == _native.MODE_TC_BF16X3
     assert _native.resolve_mode(_native.MODE_AUTO, f32, 16384, 512, 512, 8, 4) == _native.MODE_SIMT   # k > 3
+    # the forward alone moves to the tensor cores earlier than the backward (kanb200_resolve_mode_for)
+    assert _native.resolve_mode(_native.MODE_AUTO, f32, 1024, 256, 10, 5, 3) == _native.MODE_SIMT
+    assert _native.resolve_mode(_native.MODE_AUTO, f32, 1024, 256, 10, 5, 3, _native.OP_FORWARD) == _native.MODE_TC_BF16X3
+    assert _native.resolve_mode(_native.MODE_AUTO, f32, 1024, 32, 8, 5, 3, _native.OP_FORWARD) == _native.MODE_SIMT
+    assert _native.resolve_mode(_native.MODE_AUTO, f64, 65536, 64, 1, 8, 3, _native.OP_FORWARD) == _native.MODE_SIMT
+    # scalar heads with many rows run on the narrow-layer kernels: no forward scratch, slabs for the gradients
+    assert _native.workspace_bytes(_native.OP_FORWARD, _native.MODE_AUTO, f64, 131072, 64, 1, 8, 3) == 0
+    assert _native.workspace_bytes(_native.OP_BACKWARD, _native.MODE_AUTO, f64, 131072, 64, 1, 8, 3, True, True) > 256
+    assert _native.workspace_bytes(_native.OP_BACKWARD, _native.MODE_AUTO, f64, 131072, 64, 1, 8, 3, True, False) == 0
     with pytest.raises(RuntimeError, match="tensor-core"):
         _native.resolve_mode(_native.MODE_TC_BF16X3, f64, 1024, 64, 64, 5, 3)
     # G = 64, k = 3: 71 knots -> 76 + 20 * 71 floats per feature; 9 chunks per feature -> 576 column
